@@ -1,0 +1,170 @@
+/* itb.h -- C ABI of the B200 backend for the Inferred-Thoughts hybrid-MoE token loop.
+ *
+ * The boundary this library drops in behind is the reference's backend trait `Ops`
+ * (src/ops/mod.rs:489-1426), selected by `--backend` (src/main.rs:167-168, :535-625). Each
+ * `itb_*` op below replaces one trait method; the citation beside it is the method it stands for.
+ *
+ * Conventions carried over from the reference's own device backend:
+ *  - Activation buffers are HOST addresses used as handles: the library keeps a device mirror per
+ *    host address (src/ops/cuda/ops/residency.rs:23-57). Never pass a sub-slice of a buffer the
+ *    library has seen under another address (src/ops/mod.rs:531-536).
+ *  - Ops return nothing; the first failure is kept and fetched with itb_take_error()
+ *    (src/ops/cuda/ops/mod.rs:91-110).
+ *  - Weights are borrowed host bytes in the file's block layout, uploaded and repacked on first
+ *    sight, keyed by pointer (src/ops/cuda/mod.rs:59-68). Keep them alive and unmoved.
+ *  - Single-threaded per context (src/ops/cuda/mod.rs:756).
+ *
+ * There is no CPU fallback: every entry point fails loudly when no CUDA device is usable.
+ */
+#ifndef ITB_H
+#define ITB_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct itb_ctx itb_ctx;
+
+/* ggml type codes understood (src/gguf/types.rs): 0 F32, 1 F16, 8 Q8_0 (34 B / 32), 40 NVFP4 (36 B / 64). */
+enum { ITB_F32 = 0, ITB_F16 = 1, ITB_Q8_0 = 8, ITB_NVFP4 = 40 };
+
+/* src/ops/mod.rs:62-92 `Weights` */
+typedef struct { const uint8_t* data; size_t bytes; uint32_t ggml_type; size_t n_in, n_out; int pooled; } itb_weights;
+/* src/ops/mod.rs:107-152 `Experts`; scale = n_expert little-endian f32 or NULL (= 1.0) */
+typedef struct { const uint8_t* data; size_t bytes; uint32_t ggml_type; size_t n_in, n_out, n_expert;
+                 const uint8_t* scale; size_t scale_bytes; } itb_experts;
+/* src/ops/mod.rs:176-218 `Route`. on_device=1: ids/weights stay in the library (the ctx's current
+ * route); on_device=0: host arrays of n_tok*n_used entries that the ops must honour. */
+typedef struct { int on_device; size_t n_used, n_tok; const size_t* ids; const float* weights; } itb_route_t;
+/* src/ops/mod.rs:228-276 `Attn`; k/v are the layer's slabs (host addresses, keys of device slabs). */
+typedef struct { const float* q; size_t q_len; const uint16_t* k; const uint16_t* v; size_t slab_len;
+                 size_t kv_dim, n_pos, head_dim, n_head, n_head_kv; float scale; } itb_attn;
+/* src/ops/mod.rs:337-358 `Delta`; n_tokens is derived by the reference from v's length. */
+typedef struct { const float *q, *k, *v, *alpha, *beta, *ssm_a, *dt_bias; size_t n_tokens,
+                 head_k_dim, head_v_dim, n_k_heads, n_v_heads; } itb_delta;
+
+/* ---- context ---- */
+/* opts: "key=value,..." ; keys: kv=f16|bf16 (default f16, the reference's KV dtype, src/cache/mod.rs:8-15),
+ * exact=0|1 (1: F32 dots accumulate serially like the CPU path; default 1 for the op-level seam). */
+int         itb_create(int device_ordinal, const char* opts, itb_ctx** out);   /* 0 ok */
+void        itb_destroy(itb_ctx*);
+const char* itb_take_error(itb_ctx*);   /* NULL if none; clears (src/ops/cuda/ops/mod.rs:91-110) */
+const char* itb_last_create_error(void);
+
+/* ---- pass / residency protocol (src/ops/mod.rs:1360-1419) ---- */
+void itb_begin_pass(itb_ctx*, size_t n_tokens);                /* :1372 */
+void itb_end_pass(itb_ctx*);                                    /* :1376 */
+void itb_host_wrote(itb_ctx*, const float* buf, size_t len);    /* :1360 */
+void itb_host_needs(itb_ctx*, float* buf, size_t len);          /* :1363 */
+void itb_forget_state(itb_ctx*);                                /* :1401 */
+void itb_read_state(itb_ctx*, float* host, size_t len);         /* :1419 */
+void itb_reserve_activations(itb_ctx*, size_t bytes);           /* :1305 */
+/* KV slabs live on the device once written; this brings one home (tests, checkpoints). */
+void itb_read_kv(itb_ctx*, uint16_t* slab, size_t slab_len);
+
+/* ---- ops, one per trait method ---- */
+void itb_rms_norm(itb_ctx*, const float* x, size_t x_len, const float* w, size_t w_len, float eps, float* out);   /* :497 */
+void itb_rms_norm_heads(itb_ctx*, float* x, size_t len, const float* w, size_t head_dim, float eps);              /* :502 */
+void itb_matmul(itb_ctx*, const itb_weights*, const float* x, size_t x_len, float* out, size_t out_len);          /* :520 */
+void itb_matmul_pair(itb_ctx*, const itb_weights* a, const itb_weights* b, const float* x, size_t x_len,
+                     float* out_a, size_t out_a_len, float* out_b, size_t out_b_len);                             /* :1012 */
+void itb_rope_neox(itb_ctx*, float* x, size_t len, size_t pos, size_t head_dim, size_t n_rot, size_t n_heads, float theta); /* :545 */
+void itb_softmax(itb_ctx*, float* x, size_t len, size_t row);                                                     /* :567 */
+void itb_attend(itb_ctx*, const itb_attn*, float* out, size_t out_len);                                           /* :589 */
+void itb_kv_write(itb_ctx*, uint16_t* slab, size_t slab_len, size_t offset, const float* src, size_t n);          /* :1421 */
+void itb_silu_mul(itb_ctx*, float* gate, const float* up, size_t n);                                              /* :592 */
+void itb_sigmoid_mul(itb_ctx*, float* x, const float* g, size_t n);                                               /* :746 */
+void itb_scale(itb_ctx*, float* buf, size_t n, float s);                                                          /* :600 */
+void itb_add_assign(itb_ctx*, float* a, const float* b, size_t n);                                                /* :788 */
+void itb_add_scaled(itb_ctx*, float* a, const float* b, size_t n, float s);                                       /* :1265 */
+void itb_add_scaled_rows(itb_ctx*, float* acc, size_t n, const float* rows, const float* scales, size_t n_rows);  /* :1228 */
+void itb_add_scaled_sigmoid(itb_ctx*, float* acc, const float* b, size_t n, const float* logit);                  /* :1250 */
+void itb_gather_chunks(itb_ctx*, const float* src, size_t src_len, size_t chunk, size_t stride, size_t offset,
+                       float* out, size_t out_len);                                                               /* :664 */
+void itb_scatter_chunks(itb_ctx*, const float* src, size_t src_len, size_t chunk, size_t stride, size_t offset,
+                        float* dst, size_t dst_len);                                                              /* :730 */
+void itb_l2_norm_heads(itb_ctx*, float* x, size_t len, size_t head_dim, float eps);                               /* :613 */
+void itb_ssm_conv(itb_ctx*, float* state, size_t state_len, const float* x, size_t x_len, const float* w,
+                  size_t w_len, size_t kernel, float* out);                                                       /* :647 */
+void itb_delta_rule(itb_ctx*, const itb_delta*, float* state, size_t state_len, float* out, size_t out_len);      /* :785 */
+/* Chooses on the device and returns on_device=1 in *out (src/ops/cuda/ops/mod.rs:299-302). */
+void itb_route(itb_ctx*, float* probs, size_t len, size_t n_expert, size_t n_used, itb_route_t* out);               /* :1191 */
+void itb_matmul_experts(itb_ctx*, const itb_experts*, const itb_route_t*, const float* x, size_t x_len,
+                        float* out, size_t out_len);                                                              /* :1049 */
+void itb_moe_glu(itb_ctx*, const itb_experts* gate, const itb_experts* up, const itb_route_t*, const float* x,
+                 size_t x_len, float* out, size_t out_len, float* scratch);                                       /* :1105 */
+void itb_moe_finish(itb_ctx*, float* out, size_t out_len, size_t at, size_t n, const float* rows, size_t rows_len,
+                    const itb_route_t*, const float* shared, const float* logit, size_t logit_at);                  /* :1134 */
+void itb_prefetch_hint(itb_ctx*, const itb_weights* next_router, const float* x, size_t x_len, size_t k);         /* :924 */
+/* Brings the current device route home: n_tok*n_used ids and weights (tests; breaks graph capture). */
+void itb_read_route(itb_ctx*, int32_t* ids, float* weights, size_t n);
+
+/* ---- observability (src/ops/mod.rs:1300-1358) ---- */
+int  itb_config_report(itb_ctx*, char* buf, size_t cap);
+void itb_device_report(itb_ctx*);
+/* kernels launched by this context since creation */
+uint64_t itb_launch_count(itb_ctx*);
+
+/* ==== model / engine level =====================================================================
+ * The reference drives the ops above from Qwen35::forward (src/model/qwen35.rs:956-1127) under
+ * Engine::{prefill,decode,generate} (src/engine/mod.rs:352-437). The same two layers are provided
+ * natively so a token step is a handful of fused kernels replayed as one CUDA graph:
+ * the reference hides launch cost the same way (src/ops/cuda/mod.rs:600-647).
+ */
+typedef struct {
+    uint32_t n_layer, n_embd, n_head, n_head_kv, head_dim, n_vocab;
+    float rope_theta, rms_eps;
+    uint32_t n_rot, ssm_d_conv, ssm_d_inner, ssm_d_state, ssm_dt_rank, ssm_n_group, full_attention_interval;
+    uint32_t n_expert, n_expert_used, expert_ff, shared_ff;
+} itb_model_dims;   /* src/model/qwen35.rs:193-249 `Config` + `Moe` */
+
+typedef struct itb_model itb_model;
+typedef struct itb_engine itb_engine;
+
+int  itb_model_create(itb_ctx*, const itb_model_dims*, itb_model** out);
+void itb_model_destroy(itb_model*);
+/* Tensor by GGUF name (src/model/qwen35.rs:755-858) from host bytes in the file's block layout.
+ * `scale`: n_expert f32 for NVFP4 expert stacks (the `.scale` tensor), else NULL. */
+int  itb_model_set_tensor(itb_model*, const char* name, uint32_t ggml_type, const void* data, size_t bytes,
+                          const float* scale, size_t n_scale);
+/* Fill every tensor from the deterministic generator, on the device (seeded synthetic weights).
+ * expert_lo/expert_hi restrict routed-expert storage to [lo,hi) (expert-parallel shard); 0,0 = all. */
+int  itb_model_synth(itb_model*, uint64_t seed, uint32_t expert_lo, uint32_t expert_hi);
+/* Regenerate one synthetic tensor in the file's block layout and copy it to the host. */
+int  itb_model_synth_read(itb_model*, uint64_t seed, const char* name, void* out, size_t bytes, float* scale_out);
+/* Algorithmic bytes one decode step reads/writes at the given fill (weights once, state r+w, KV read). */
+uint64_t itb_model_decode_bytes(itb_model*, uint32_t n_seq, uint32_t n_pos, uint32_t distinct_experts_per_layer);
+
+/* n_seq independent sequences (the reference engine holds one, src/engine/mod.rs:44-59). */
+int  itb_engine_create(itb_model*, uint32_t n_ctx, uint32_t n_seq, itb_engine** out);
+void itb_engine_destroy(itb_engine*);
+void itb_engine_reset(itb_engine*);                                               /* src/engine/mod.rs:296-308 */
+uint32_t itb_engine_pos(itb_engine*, uint32_t seq);
+/* Engine::prefill (src/engine/mod.rs:352-356) for every sequence in lockstep: tokens [n_seq][n] host ids in,
+ * logits of each sequence's last token out, [n_seq][n_vocab] (may be NULL). */
+int  itb_engine_prefill(itb_engine*, const uint32_t* tokens, size_t n, float* logits_out);
+/* Engine::decode for every sequence at once: tokens[n_seq] in; logits_out [n_seq][n_vocab] (may be NULL),
+ * next_out[n_seq] greedy argmax (strict '>', lowest index wins, src/profile.rs:192-213) (may be NULL). */
+int  itb_engine_decode(itb_engine*, const uint32_t* tokens, float* logits_out, uint32_t* next_out);
+/* Device-resident greedy loop: `steps` decode steps feeding each argmax back in, no host traffic inside. */
+int  itb_engine_decode_loop(itb_engine*, const uint32_t* first_tokens, uint32_t steps, uint32_t* tokens_out);
+/* Engine::generate (src/engine/mod.rs:399-437) for sequence 0: prefill, then greedy tokens; each step
+ * copies the token id to the device and the chosen id back. Returns tokens produced, <0 on error. */
+long itb_engine_generate(itb_engine*, const uint32_t* prompt, size_t n_prompt, size_t max_new, uint32_t* out);
+/* Last step's routing decisions [moe layer][seq][n_used] (integer parity checks). */
+int  itb_engine_read_routes(itb_engine*, int32_t* ids, size_t cap);
+/* Recurrent state / KV of one sequence, layer il (absolute layer index) */
+int  itb_engine_read_ssm_state(itb_engine*, uint32_t seq, uint32_t il, float* out, size_t len);
+/* Device time of the last decode step or loop in milliseconds (CUDA events on the engine's stream). */
+float itb_engine_last_ms(itb_engine*);
+uint64_t itb_engine_launches_per_step(itb_engine*);
+
+/* Device generator check: element i of stream `key` (tests compare with the CPU generator). */
+int  itb_synth_values(itb_ctx*, uint64_t key, uint64_t first, size_t n, int dist, float std_, float* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,153 @@
+// Internal declarations shared by the library's translation units.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/itb.h"
+
+// ------------------------------------------------------------------ device-side weight layouts
+// Q8_0 matrix repacked from 34-byte blocks (src/quant/mod.rs:90-106) into two planes so rows can be
+// read with 16-byte loads: quants [n_out][n_in] int8, scales [n_out][n_in/32] f16 bits.
+struct DevQ8 {
+    const int8_t* q = nullptr;
+    const uint16_t* s = nullptr;
+    int n_in = 0, n_out = 0;
+};
+// NVFP4 stack repacked from 36-byte blocks (src/quant/mod.rs:338-357): nibbles [E][n_out][n_in/2] with
+// nibble k of byte-pair order = element order (low nibble first), scales [E][n_out][n_in/16] UE4M3 codes
+// with bit 7 cleared and 0x7f mapped to 0 (both read as the reference reads them, src/quant/mod.rs:271-284).
+struct DevFp4 {
+    const uint8_t* nib = nullptr;
+    const uint8_t* sc = nullptr;
+    const float* scale2 = nullptr;  // per expert, or null
+    int n_in = 0, n_out = 0, n_expert = 0;
+    int expert_lo = 0;              // first expert stored (expert-parallel shard); ids are global
+};
+struct DevF32 {
+    const float* w = nullptr;
+    int n_in = 0, n_out = 0;
+};
+
+// ------------------------------------------------------------------ context
+struct Mirror {
+    void* dev = nullptr;
+    size_t bytes = 0;
+    bool device_current = false;
+};
+struct WeightEntry {
+    uint32_t ty = 0;
+    size_t n_in = 0, n_out = 0, n_expert = 1;
+    void* a = nullptr;  // Q8: quants; FP4: nibbles; F32/F16: values as f32
+    void* b = nullptr;  // Q8: scales; FP4: block scales
+    float* scale2 = nullptr;
+    size_t bytes = 0;
+};
+
+struct itb_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string error;       // sticky first error
+    std::string error_out;   // storage handed back by take_error
+    bool kv_bf16 = false;
+    bool exact = true;
+    bool in_pass = false;
+    uint64_t launches = 0;
+    int sm_count = 148;
+    std::unordered_map<const void*, Mirror> mirrors;
+    std::unordered_map<const void*, Mirror> states;   // recurrent slabs: device owns after first touch
+    std::unordered_map<const void*, Mirror> kv;       // KV slabs, keyed by host slab address
+    std::unordered_map<const void*, WeightEntry> weights;
+    // current device route (src/ops/cuda/ops/mod.rs:299-302)
+    int32_t* route_ids = nullptr;
+    float* route_w = nullptr;
+    size_t route_cap = 0, route_n_tok = 0, route_n_used = 0;
+    // scratch for activation quantisation
+    int8_t* xq = nullptr; float* xs = nullptr; size_t xq_cap = 0;
+    float* tmp_f32 = nullptr; size_t tmp_cap = 0;
+    const void* last_state_key = nullptr;
+    size_t mirror_bytes = 0, weight_bytes = 0;
+};
+
+bool itb_fail(itb_ctx* c, const char* what, cudaError_t e);
+bool itb_fail_msg(itb_ctx* c, const std::string& msg);
+#define ITB_CUDA(c, call)                                              \
+    do {                                                               \
+        cudaError_t e__ = (call);                                      \
+        if (e__ != cudaSuccess) { itb_fail((c), #call, e__); return; } \
+    } while (0)
+#define ITB_CUDA_RET(c, call, ret)                                           \
+    do {                                                                     \
+        cudaError_t e__ = (call);                                            \
+        if (e__ != cudaSuccess) { itb_fail((c), #call, e__); return (ret); } \
+    } while (0)
+#define ITB_LAUNCHED(c)                                                  \
+    do {                                                                 \
+        (c)->launches++;                                                 \
+        cudaError_t e__ = cudaGetLastError();                            \
+        if (e__ != cudaSuccess) itb_fail((c), "kernel launch", e__);     \
+    } while (0)
+
+// mirrors (itb_ctx.cu)
+float* itb_mirror_in(itb_ctx* c, const float* host, size_t len);
+float* itb_mirror_out(itb_ctx* c, const float* host, size_t len);
+float* itb_mirror_inout(itb_ctx* c, float* host, size_t len);
+float* itb_state_slab(itb_ctx* c, float* host, size_t len);
+uint16_t* itb_kv_slab(itb_ctx* c, const uint16_t* host, size_t len);
+const WeightEntry* itb_weight(itb_ctx* c, const uint8_t* data, size_t bytes, uint32_t ty, size_t n_in, size_t n_out,
+                              size_t n_expert, const uint8_t* scale, size_t scale_bytes);
+bool itb_ensure_route(itb_ctx* c, size_t n_pairs);
+bool itb_ensure_xq(itb_ctx* c, size_t n_elems);
+
+// repack (itb_ctx.cu): raw reference-layout bytes on the device -> kernel layouts
+void itb_repack_q8(cudaStream_t st, const uint8_t* raw, int8_t* q, uint16_t* s, size_t n_blocks_total);
+void itb_repack_fp4(cudaStream_t st, const uint8_t* raw, uint8_t* nib, uint8_t* sc, size_t n_blocks64_total);
+void itb_f16_to_f32(cudaStream_t st, const uint16_t* raw, float* out, size_t n);
+
+// ------------------------------------------------------------------ device helpers
+#ifdef __CUDACC__
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// exp in f32 through the f64 unit: correctly rounded for all but a vanishing fraction of inputs, so
+// results track the CPU's libm far closer than the fast f32 expf does. Only a handful of elements
+// per token go through it.
+__device__ __forceinline__ float exp_f(float x) { return (float)exp((double)x); }
+__device__ __forceinline__ float log_f(float x) { return (float)log((double)x); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + exp_f(-x)); }
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + exp_f(-x)); }
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ float bf16_bits_to_f32(uint16_t h) { return __uint_as_float((uint32_t)h << 16); }
+__device__ __forceinline__ uint16_t f32_to_f16_bits(float f) { return __half_as_ushort(__float2half_rn(f)); }
+__device__ __forceinline__ uint16_t f32_to_bf16_bits(float f) {
+    uint32_t b = __float_as_uint(f);
+    if ((b & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((b >> 16) | 0x40);
+    b += 0x7fffu + ((b >> 16) & 1u);
+    return (uint16_t)(b >> 16);
+}
+// UE4M3 scale code (bit 7 already cleared, 0x7f already mapped to 0), halved: (8+m)*2^(e-11) or m*2^-10.
+__device__ __forceinline__ float ue4m3_half_dev(uint32_t x) {
+    uint32_t e = (x >> 3) & 0xf, m = x & 7;
+    float mant = (float)(e == 0 ? m : 8 + m);
+    float p = __uint_as_float((e == 0 ? 117u : 116u + e) << 23);
+    return x == 0 ? 0.0f : mant * p;
+}
+#endif

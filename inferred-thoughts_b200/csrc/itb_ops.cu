@@ -1,0 +1,337 @@
+// The op-level seam: one extern "C" entry per method of the reference's backend trait
+// (src/ops/mod.rs:489-1426), operating on host-address-keyed device mirrors.
+#include "itb_kernels.cuh"
+
+static inline unsigned blocks_for(size_t n, int per = 256) { return (unsigned)((n + per - 1) / per); }
+
+#define EW_LAUNCH(c, kernel, n, ...)                                      \
+    do {                                                                  \
+        if ((n) > 0) {                                                    \
+            kernel<<<blocks_for(n), 256, 0, (c)->stream>>>(__VA_ARGS__);  \
+            ITB_LAUNCHED(c);                                              \
+        }                                                                 \
+    } while (0)
+
+extern "C" void itb_silu_mul(itb_ctx* c, float* gate, const float* up, size_t n) {
+    float* g = itb_mirror_inout(c, gate, n); const float* u = itb_mirror_in(c, up, n);
+    if (!g || !u) return;
+    EW_LAUNCH(c, k_silu_mul, n, g, u, n);
+}
+extern "C" void itb_sigmoid_mul(itb_ctx* c, float* x, const float* gate, size_t n) {
+    float* xd = itb_mirror_inout(c, x, n); const float* g = itb_mirror_in(c, gate, n);
+    if (!xd || !g) return;
+    EW_LAUNCH(c, k_sigmoid_mul, n, xd, g, n);
+}
+extern "C" void itb_scale(itb_ctx* c, float* buf, size_t n, float s) {
+    float* b = itb_mirror_inout(c, buf, n);
+    if (!b) return;
+    EW_LAUNCH(c, k_scale, n, b, n, s);
+}
+extern "C" void itb_add_assign(itb_ctx* c, float* a, const float* b, size_t n) {
+    float* ad = itb_mirror_inout(c, a, n); const float* bd = itb_mirror_in(c, b, n);
+    if (!ad || !bd) return;
+    EW_LAUNCH(c, k_add_assign, n, ad, bd, n);
+}
+extern "C" void itb_add_scaled(itb_ctx* c, float* a, const float* b, size_t n, float s) {
+    float* ad = itb_mirror_inout(c, a, n); const float* bd = itb_mirror_in(c, b, n);
+    if (!ad || !bd) return;
+    EW_LAUNCH(c, k_add_scaled, n, ad, bd, n, s, (const float*)nullptr);
+}
+extern "C" void itb_add_scaled_sigmoid(itb_ctx* c, float* acc, const float* b, size_t n, const float* logit) {
+    float* ad = itb_mirror_inout(c, acc, n); const float* bd = itb_mirror_in(c, b, n); const float* lg = itb_mirror_in(c, logit, 1);
+    if (!ad || !bd || !lg) return;
+    EW_LAUNCH(c, k_add_scaled, n, ad, bd, n, 0.0f, lg);
+}
+extern "C" void itb_add_scaled_rows(itb_ctx* c, float* acc, size_t n, const float* rows, const float* scales, size_t n_rows) {
+    const float* r = itb_mirror_in(c, rows, n * n_rows); const float* s = itb_mirror_in(c, scales, n_rows);
+    float* a = itb_mirror_out(c, acc, n);
+    if (!a || !r || !s) return;
+    EW_LAUNCH(c, k_add_scaled_rows, n, a, n, r, s, n_rows);
+}
+extern "C" void itb_gather_chunks(itb_ctx* c, const float* src, size_t src_len, size_t chunk, size_t stride, size_t offset,
+                                  float* out, size_t out_len) {
+    if (chunk == 0 || out_len % chunk) { itb_fail_msg(c, "gather_chunks: out is not whole chunks"); return; }
+    size_t n_chunks = out_len / chunk;
+    if (n_chunks && (n_chunks - 1) * stride + offset + chunk > src_len) { itb_fail_msg(c, "gather_chunks: reads past src"); return; }
+    const float* s = itb_mirror_in(c, src, src_len); float* o = itb_mirror_out(c, out, out_len);
+    if (!s || !o) return;
+    EW_LAUNCH(c, k_gather_chunks, out_len, s, chunk, stride, offset, o, out_len);
+}
+extern "C" void itb_scatter_chunks(itb_ctx* c, const float* src, size_t src_len, size_t chunk, size_t stride, size_t offset,
+                                   float* dst, size_t dst_len) {
+    if (chunk == 0 || src_len % chunk) { itb_fail_msg(c, "scatter_chunks: src is not whole chunks"); return; }
+    size_t n_chunks = src_len / chunk;
+    if (n_chunks && (n_chunks - 1) * stride + offset + chunk > dst_len) { itb_fail_msg(c, "scatter_chunks: writes past dst"); return; }
+    const float* s = itb_mirror_in(c, src, src_len); float* d = itb_mirror_inout(c, dst, dst_len);
+    if (!s || !d) return;
+    EW_LAUNCH(c, k_scatter_chunks, src_len, s, src_len, chunk, stride, offset, d);
+}
+
+extern "C" void itb_rms_norm(itb_ctx* c, const float* x, size_t x_len, const float* w, size_t nd, float eps, float* out) {
+    if (nd == 0 || x_len % nd) { itb_fail_msg(c, "rms_norm: x is not whole rows"); return; }
+    const float* xd = itb_mirror_in(c, x, x_len); const float* wd = itb_mirror_in(c, w, nd);
+    float* od = itb_mirror_out(c, out, x_len);
+    if (!xd || !wd || !od) return;
+    k_rms_norm<<<(unsigned)(x_len / nd), 256, 32 * 8 + nd * 4, c->stream>>>(xd, wd, (int)nd, eps, od);
+    ITB_LAUNCHED(c);
+}
+extern "C" void itb_rms_norm_heads(itb_ctx* c, float* x, size_t len, const float* w, size_t head_dim, float eps) {
+    if (head_dim == 0 || len % head_dim) { itb_fail_msg(c, "rms_norm_heads: x is not whole heads"); return; }
+    float* xd = itb_mirror_inout(c, x, len); const float* wd = itb_mirror_in(c, w, head_dim);
+    if (!xd || !wd) return;
+    k_rms_norm<<<(unsigned)(len / head_dim), 64, 32 * 8 + head_dim * 4, c->stream>>>(xd, wd, (int)head_dim, eps, xd);
+    ITB_LAUNCHED(c);
+}
+extern "C" void itb_l2_norm_heads(itb_ctx* c, float* x, size_t len, size_t head_dim, float eps) {
+    if (head_dim == 0 || len % head_dim) { itb_fail_msg(c, "l2_norm_heads: x is not whole heads"); return; }
+    float* xd = itb_mirror_inout(c, x, len);
+    if (!xd) return;
+    size_t nh = len / head_dim;
+    k_l2_norm_heads<<<blocks_for(nh, 8), 256, 0, c->stream>>>(xd, nh, (int)head_dim, eps);
+    ITB_LAUNCHED(c);
+}
+extern "C" void itb_softmax(itb_ctx* c, float* x, size_t len, size_t row) {
+    if (row == 0) return;
+    if (len % row) { itb_fail_msg(c, "softmax: x is not whole rows"); return; }
+    float* xd = itb_mirror_inout(c, x, len);
+    if (!xd) return;
+    k_softmax_rows<<<blocks_for(len / row, 8), 256, 0, c->stream>>>(xd, len / row, (int)row);
+    ITB_LAUNCHED(c);
+}
+extern "C" void itb_rope_neox(itb_ctx* c, float* x, size_t len, size_t pos, size_t head_dim, size_t n_rot, size_t n_heads, float theta) {
+    size_t per_row = head_dim * n_heads;
+    if (per_row == 0 || len % per_row || n_rot % 2 || n_rot > head_dim) { itb_fail_msg(c, "rope_neox: bad shape"); return; }
+    float* xd = itb_mirror_inout(c, x, len);
+    if (!xd) return;
+    size_t n_rows = len / per_row, total = n_rows * n_heads * (n_rot / 2);
+    EW_LAUNCH(c, k_rope, total, xd, n_rows, (int)n_heads, (int)head_dim, (int)n_rot, theta, pos, (const int*)nullptr);
+}
+extern "C" void itb_kv_write(itb_ctx* c, uint16_t* slab, size_t slab_len, size_t offset, const float* src, size_t n) {
+    if (offset + n > slab_len) { itb_fail_msg(c, "kv_write: past the slab"); return; }
+    uint16_t* sd = itb_kv_slab(c, slab, slab_len); const float* s = itb_mirror_in(c, src, n);
+    if (!sd || !s) return;
+    EW_LAUNCH(c, k_kv_write, n, sd, offset, s, n, (int)c->kv_bf16);
+}
+extern "C" void itb_ssm_conv(itb_ctx* c, float* state, size_t state_len, const float* x, size_t x_len, const float* w,
+                             size_t w_len, size_t kernel, float* out) {
+    if (kernel < 2 || kernel > 9 || w_len % kernel) { itb_fail_msg(c, "ssm_conv: bad kernel width"); return; }
+    size_t nc = w_len / kernel;
+    if (state_len != nc * (kernel - 1) || x_len % nc) { itb_fail_msg(c, "ssm_conv: bad shape"); return; }
+    float* sd = itb_state_slab(c, state, state_len);
+    const float* xd = itb_mirror_in(c, x, x_len); const float* wd = itb_mirror_in(c, w, w_len);
+    float* od = itb_mirror_out(c, out, x_len);
+    if (!sd || !xd || !wd || !od) return;
+    k_ssm_conv<<<blocks_for(nc, 128), 128, 0, c->stream>>>(sd, xd, x_len / nc, (int)nc, wd, (int)kernel, od);
+    ITB_LAUNCHED(c);
+}
+extern "C" void itb_delta_rule(itb_ctx* c, const itb_delta* d, float* state, size_t state_len, float* out, size_t out_len) {
+    size_t kper = d->n_k_heads * d->head_k_dim, vper = d->n_v_heads * d->head_v_dim, nt = d->n_tokens;
+    if (state_len != d->n_v_heads * d->head_k_dim * d->head_v_dim || out_len != nt * vper || d->n_k_heads == 0) {
+        itb_fail_msg(c, "delta_rule: bad shape"); return;
+    }
+    float* sd = itb_state_slab(c, state, state_len);
+    const float* q = itb_mirror_in(c, d->q, nt * kper); const float* k = itb_mirror_in(c, d->k, nt * kper);
+    const float* v = itb_mirror_in(c, d->v, nt * vper);
+    const float* al = itb_mirror_in(c, d->alpha, nt * d->n_v_heads); const float* be = itb_mirror_in(c, d->beta, nt * d->n_v_heads);
+    const float* sa = itb_mirror_in(c, d->ssm_a, d->n_v_heads); const float* dt = itb_mirror_in(c, d->dt_bias, d->n_v_heads);
+    float* od = itb_mirror_out(c, out, out_len);
+    if (!sd || !q || !k || !v || !al || !be || !sa || !dt || !od) return;
+    constexpr int ROWS = 32;
+    int sk = (int)d->head_k_dim, sv = (int)d->head_v_dim;
+    dim3 grid((unsigned)d->n_v_heads, (unsigned)((sv + ROWS - 1) / ROWS));
+    size_t smem = (size_t)(ROWS * (sk + 1) + 2 * sk) * 4;
+    k_delta_rule<ROWS><<<grid, 128, smem, c->stream>>>(q, k, v, al, be, sa, dt, nt, sk, sv, (int)d->n_k_heads, (int)d->n_v_heads, sd, od);
+    ITB_LAUNCHED(c);
+}
+
+// ------------------------------------------------------------------ matmuls
+static bool quantize_rows(itb_ctx* c, const float* xd, size_t n_rows, size_t n_in) {
+    if (!itb_ensure_xq(c, n_rows * n_in)) return false;
+    k_quant_q8<<<(unsigned)n_rows, 256, 0, c->stream>>>(xd, (int)n_in, c->xq, c->xs);
+    ITB_LAUNCHED(c);
+    return true;
+}
+
+static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od) {
+    DevQ8 dw{(const int8_t*)w->a, (const uint16_t*)w->b, (int)w->n_in, (int)w->n_out};
+    int nb = (int)w->n_in / 32, gsh = lanes_shift(nb), nw = 8;
+    int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);
+    if (gx < 1) gx = 1;
+    size_t smem = w->n_in + nb * 4 + (size_t)nw * terms_floats(4, gsh, nb) * 4;
+    dim3 grid(gx, (unsigned)n_tok);
+    cudaFuncSetAttribute(k_matmul_q8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k_matmul_q8<<<grid, nw * 32, smem, c->stream>>>(dw, c->xq, c->xs, od);
+    ITB_LAUNCHED(c);
+}
+
+// ids==nullptr: dense NVFP4 matrix, one "pair" per token reading its own row.
+static void launch_fp4(itb_ctx* c, const WeightEntry* w, const int32_t* ids, size_t n_pairs, int n_used, int rows_mode, float* od) {
+    DevFp4 dw{(const uint8_t*)w->a, (const uint8_t*)w->b, w->scale2, (int)w->n_in, (int)w->n_out, (int)w->n_expert, 0};
+    int nb = (int)w->n_in / 32, nsb = (int)w->n_in / 16, gsh = lanes_shift(nb), nw = 8;
+    int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);
+    if (gx < 1) gx = 1;
+    size_t smem = w->n_in + nb * 4 + (size_t)nw * terms_floats(4, gsh, nsb) * 4;
+    dim3 grid(gx, (unsigned)n_pairs);
+    cudaFuncSetAttribute(k_matmul_fp4, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k_matmul_fp4<<<grid, nw * 32, smem, c->stream>>>(dw, ids, n_used, rows_mode, c->xq, c->xs, od);
+    ITB_LAUNCHED(c);
+}
+
+static void launch_f32(itb_ctx* c, const WeightEntry* w, const float* xd, size_t n_tok, float* od) {
+    DevF32 dw{(const float*)w->a, (int)w->n_in, (int)w->n_out};
+    int nw = 4;
+    int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);
+    if (gx < 1) gx = 1;
+    size_t smem = w->n_in * 4 + (size_t)nw * 32 * 33 * 4;
+    dim3 grid(gx, (unsigned)n_tok);
+    if (c->exact) {
+        cudaFuncSetAttribute(k_matmul_f32<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_matmul_f32<true><<<grid, nw * 32, smem, c->stream>>>(dw, xd, od);
+    } else {
+        cudaFuncSetAttribute(k_matmul_f32<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k_matmul_f32<false><<<grid, nw * 32, smem, c->stream>>>(dw, xd, od);
+    }
+    ITB_LAUNCHED(c);
+}
+
+static void matmul_dev(itb_ctx* c, const itb_weights* w, const float* xd, size_t n_tok, float* od) {
+    const WeightEntry* we = itb_weight(c, w->data, w->bytes, w->ggml_type, w->n_in, w->n_out, 1, nullptr, 0);
+    if (!we) return;
+    if (we->ty == ITB_Q8_0) { if (quantize_rows(c, xd, n_tok, w->n_in)) launch_q8(c, we, n_tok, od); }
+    else if (we->ty == ITB_NVFP4) { if (quantize_rows(c, xd, n_tok, w->n_in)) launch_fp4(c, we, nullptr, n_tok, 1, 0, od); }
+    else launch_f32(c, we, xd, n_tok, od);
+}
+
+extern "C" void itb_matmul(itb_ctx* c, const itb_weights* w, const float* x, size_t x_len, float* out, size_t out_len) {
+    if (w->n_in == 0 || x_len % w->n_in || out_len != x_len / w->n_in * w->n_out) { itb_fail_msg(c, "matmul: bad shape"); return; }
+    const float* xd = itb_mirror_in(c, x, x_len); float* od = itb_mirror_out(c, out, out_len);
+    if (!xd || !od) return;
+    matmul_dev(c, w, xd, x_len / w->n_in, od);
+}
+extern "C" void itb_matmul_pair(itb_ctx* c, const itb_weights* a, const itb_weights* b, const float* x, size_t x_len,
+                                float* out_a, size_t out_a_len, float* out_b, size_t out_b_len) {
+    if (a->n_in != b->n_in || a->n_in == 0 || x_len % a->n_in) { itb_fail_msg(c, "matmul_pair: bad shape"); return; }
+    size_t nt = x_len / a->n_in;
+    if (out_a_len != nt * a->n_out || out_b_len != nt * b->n_out) { itb_fail_msg(c, "matmul_pair: bad output length"); return; }
+    const float* xd = itb_mirror_in(c, x, x_len);
+    float* oa = itb_mirror_out(c, out_a, out_a_len); float* ob = itb_mirror_out(c, out_b, out_b_len);
+    if (!xd || !oa || !ob) return;
+    matmul_dev(c, a, xd, nt, oa);
+    matmul_dev(c, b, xd, nt, ob);
+}
+
+// ------------------------------------------------------------------ routing and experts
+extern "C" void itb_route(itb_ctx* c, float* probs, size_t len, size_t n_expert, size_t n_used, itb_route_t* out) {
+    if (n_expert == 0 || len % n_expert || n_used == 0 || n_used > 16 || n_used > n_expert || n_expert > 4096) {
+        itb_fail_msg(c, "route: bad shape"); return;
+    }
+    size_t nt = len / n_expert;
+    const float* p = itb_mirror_in(c, probs, len);
+    if (!p || !itb_ensure_route(c, nt * n_used)) return;
+    k_route<<<(unsigned)nt, 256, 0, c->stream>>>(p, (int)n_expert, (int)n_used, c->route_ids, c->route_w);
+    ITB_LAUNCHED(c);
+    c->route_n_tok = nt; c->route_n_used = n_used;
+    out->on_device = 1; out->n_used = n_used; out->n_tok = nt; out->ids = nullptr; out->weights = nullptr;
+}
+extern "C" void itb_read_route(itb_ctx* c, int32_t* ids, float* weights, size_t n) {
+    if (n > c->route_n_tok * c->route_n_used) { itb_fail_msg(c, "read_route: more than the current route holds"); return; }
+    ITB_CUDA(c, cudaMemcpyAsync(ids, c->route_ids, n * 4, cudaMemcpyDeviceToHost, c->stream));
+    ITB_CUDA(c, cudaMemcpyAsync(weights, c->route_w, n * 4, cudaMemcpyDeviceToHost, c->stream));
+    ITB_CUDA(c, cudaStreamSynchronize(c->stream));
+}
+// A host-chosen route is honoured by staging it into the device route (src/ops/cuda/ops/moe.rs:878-921).
+static bool stage_route(itb_ctx* c, const itb_route_t* r) {
+    if (r->on_device) return c->route_n_tok == r->n_tok && c->route_n_used == r->n_used ? true : itb_fail_msg(c, "route: device route does not match");
+    size_t n = r->n_tok * r->n_used;
+    if (!itb_ensure_route(c, n)) return false;
+    std::vector<int32_t> ids(n);
+    for (size_t i = 0; i < n; ++i) ids[i] = (int32_t)r->ids[i];
+    cudaMemcpyAsync(c->route_ids, ids.data(), n * 4, cudaMemcpyHostToDevice, c->stream);
+    if (r->weights) cudaMemcpyAsync(c->route_w, r->weights, n * 4, cudaMemcpyHostToDevice, c->stream);
+    cudaStreamSynchronize(c->stream);
+    c->route_n_tok = r->n_tok; c->route_n_used = r->n_used;
+    return true;
+}
+static void experts_dev(itb_ctx* c, const itb_experts* w, const itb_route_t* r, const float* xd, size_t x_len, float* od) {
+    if (w->ggml_type != ITB_NVFP4) { itb_fail_msg(c, "routed experts: only NVFP4 has a kernel here"); return; }  // src/ops/mod.rs:29-55
+    const WeightEntry* we = itb_weight(c, w->data, w->bytes, w->ggml_type, w->n_in, w->n_out, w->n_expert, w->scale, w->scale_bytes);
+    if (!we) return;
+    size_t n_pairs = r->n_tok * r->n_used, rows = x_len / w->n_in;
+    int mode = rows == n_pairs ? 0 : rows > 1 ? 1 : 2;
+    if (!quantize_rows(c, xd, rows, w->n_in)) return;
+    launch_fp4(c, we, c->route_ids, n_pairs, (int)r->n_used, mode, od);
+}
+extern "C" void itb_matmul_experts(itb_ctx* c, const itb_experts* w, const itb_route_t* r, const float* x, size_t x_len,
+                                   float* out, size_t out_len) {
+    if (w->n_in == 0 || x_len % w->n_in || out_len != r->n_tok * r->n_used * w->n_out) { itb_fail_msg(c, "matmul_experts: bad shape"); return; }
+    if (!stage_route(c, r)) return;
+    const float* xd = itb_mirror_in(c, x, x_len); float* od = itb_mirror_out(c, out, out_len);
+    if (!xd || !od) return;
+    experts_dev(c, w, r, xd, x_len, od);
+}
+extern "C" void itb_moe_glu(itb_ctx* c, const itb_experts* gate, const itb_experts* up, const itb_route_t* r, const float* x,
+                            size_t x_len, float* out, size_t out_len, float* scratch) {
+    if (gate->n_in != up->n_in || gate->n_out != up->n_out || out_len != r->n_tok * r->n_used * gate->n_out) {
+        itb_fail_msg(c, "moe_glu: bad shape"); return;
+    }
+    if (!stage_route(c, r)) return;
+    const float* xd = itb_mirror_in(c, x, x_len);
+    float* od = itb_mirror_out(c, out, out_len); float* sd = itb_mirror_out(c, scratch, out_len);
+    if (!xd || !od || !sd) return;
+    experts_dev(c, gate, r, xd, x_len, od);
+    experts_dev(c, up, r, xd, x_len, sd);
+    EW_LAUNCH(c, k_silu_mul, out_len, od, sd, out_len);
+}
+extern "C" void itb_moe_finish(itb_ctx* c, float* out, size_t out_len, size_t at, size_t n, const float* rows, size_t rows_len,
+                               const itb_route_t* r, const float* shared, const float* logit, size_t logit_at) {
+    size_t nt = r->n_tok;
+    if (rows_len != nt * r->n_used * n || at + nt * n > out_len) { itb_fail_msg(c, "moe_finish: bad shape"); return; }
+    if (!stage_route(c, r)) return;
+    float* od = itb_mirror_inout(c, out, out_len);
+    const float* rd = itb_mirror_in(c, rows, rows_len); const float* sh = itb_mirror_in(c, shared, nt * n);
+    const float* lg = itb_mirror_in(c, logit, logit_at + nt);
+    if (!od || !rd || !sh || !lg) return;
+    EW_LAUNCH(c, k_moe_finish, nt * n, od, at, (int)n, rd, c->route_w, (int)r->n_used, nt, sh, lg, logit_at);
+}
+
+// ------------------------------------------------------------------ attention
+void itb_attend_dev(itb_ctx* c, cudaStream_t st, const float* q, const uint16_t* k, const uint16_t* v, int kv_dim, int n_pos, int n_q,
+                    int hd, int n_head, int n_head_kv, float scale, int bf16, const int* n_pos_dev, const float* gate,
+                    float* part_acc, float* part_ml, int n_split, float* out) {
+    int group = n_head / n_head_kv, nw = 8;
+    dim3 grid(n_head_kv, n_q, n_split);
+    size_t smem = (size_t)nw * 8 * 2 * 4 + (size_t)nw * 8 * hd * 4;
+#define ATT_CASE(H)                                                                                                   \
+    case H:                                                                                                           \
+        cudaFuncSetAttribute(k_attn_partial<H, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        k_attn_partial<H, 8><<<grid, nw * 32, smem, st>>>(q, k, v, kv_dim, n_pos, n_q, n_head, n_head_kv, scale, bf16, \
+                                                          n_pos_dev, part_acc, part_ml);                              \
+        break;
+    if (group > 8) { itb_fail_msg(c, "attend: more than 8 query heads per kv head"); return; }
+    switch (hd) { ATT_CASE(64) ATT_CASE(128) ATT_CASE(256) default: itb_fail_msg(c, "attend: head_dim must be 64, 128 or 256"); return; }
+#undef ATT_CASE
+    ITB_LAUNCHED(c);
+    k_attn_combine<<<(unsigned)(n_q * n_head), hd, 0, st>>>(part_acc, part_ml, n_split, hd, gate, out);
+    ITB_LAUNCHED(c);
+}
+
+extern "C" void itb_attend(itb_ctx* c, const itb_attn* a, float* out, size_t out_len) {
+    size_t per = a->n_head * a->head_dim;
+    if (per == 0 || a->q_len % per || a->n_head_kv == 0 || a->n_head % a->n_head_kv) { itb_fail_msg(c, "attend: bad shape"); return; }
+    size_t n_q = a->q_len / per;
+    if (out_len != a->q_len || a->n_pos < n_q || a->n_pos * a->kv_dim > a->slab_len) { itb_fail_msg(c, "attend: bad lengths"); return; }
+    const float* qd = itb_mirror_in(c, a->q, a->q_len);
+    uint16_t* kd = itb_kv_slab(c, a->k, a->slab_len); uint16_t* vd = itb_kv_slab(c, a->v, a->slab_len);
+    float* od = itb_mirror_out(c, out, out_len);
+    if (!qd || !kd || !vd || !od) return;
+    int n_split = (int)std::max<size_t>(1, std::min<size_t>((a->n_pos + 63) / 64, (size_t)(2 * c->sm_count) / (a->n_head_kv * n_q) + 1));
+    size_t need = n_q * a->n_head * n_split * (a->head_dim + 2);
+    if (c->tmp_cap < need) {
+        cudaFree(c->tmp_f32);
+        if (cudaMalloc(&c->tmp_f32, need * 4) != cudaSuccess) { itb_fail_msg(c, "cudaMalloc(attention partials)"); return; }
+        c->tmp_cap = need;
+    }
+    float* pa = c->tmp_f32; float* pm = pa + n_q * a->n_head * n_split * a->head_dim;
+    itb_attend_dev(c, c->stream, qd, kd, vd, (int)a->kv_dim, (int)a->n_pos, (int)n_q, (int)a->head_dim, (int)a->n_head,
+                   (int)a->n_head_kv, a->scale, (int)c->kv_bf16, nullptr, nullptr, pa, pm, n_split, od);
+}

@@ -1,0 +1,205 @@
+"""Model-level parity on the GPU: the tiny synthetic hybrid MoE (BASELINE config 1) through the fused engine
+against the CPU oracle on identical seeded weights.
+
+Checks, in the reference's order of strength (tests/cuda_ops.rs:544-626 there): routing ids bit-exact per
+layer per token, logits within max-abs 2e-2 / cosine >= 0.999 under TEACHER FORCING (the oracle's tokens are
+fed to both sides, never each side's own argmax), greedy tokens equal, recurrent state left behind.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle_py as O
+from tests.util import TINY, cosine, host_dims, oracle_dims, prompt_ids
+
+pytestmark = pytest.mark.gpu
+SEED = 0
+
+
+@pytest.fixture(scope="module")
+def oracle():
+    m = O.OracleModel(oracle_dims(TINY)); m.synth(SEED, threads=8)
+    return m
+
+
+@pytest.fixture(scope="module")
+def gpu():
+    from inferred_thoughts_b200 import host
+    ops = host.B200Ops(0, "exact=1")
+    model = host.Model(ops, host_dims(TINY)); model.synth(SEED)
+    yield ops, model
+    ops.check()
+
+
+def test_device_generator_equals_cpu_generator(oracle, gpu):
+    _, model = gpu
+    for name in ("blk.0.attn_qkv.weight", "blk.3.attn_q.weight", "blk.1.ffn_gate_exps.weight", "blk.2.ffn_down_exps.weight",
+                 "blk.0.ssm_a", "output_norm.weight", "token_embd.weight", "blk.3.ffn_gate_inp.weight"):
+        spec = next(s for s in oracle.specs if s["name"] == name)
+        want, wsc = oracle.tensor(name)
+        got, gsc = model.synth_read(SEED, name, spec["bytes"], spec["n_expert"] if spec["has_scale"] else 0)
+        assert got.tobytes() == want.tobytes(), name
+        if wsc is not None:
+            assert gsc.tobytes() == wsc.tobytes(), name + " second scales"
+
+
+def _teacher_forced(oracle, eng, prompt, n_new):
+    """Prefill + n_new decode steps with the ORACLE's greedy tokens fed to both sides."""
+    oracle.begin(128, log_routes=True)
+    eng.reset()
+    o_logits = [oracle.forward(prompt)]
+    g_logits = [eng.prefill(prompt)]
+    toks = []
+    L = TINY["n_layer"]; K = TINY["n_expert_used"]
+    o_routes = oracle.route_log().reshape(L, len(prompt), K)   # prefill pass: [layer][token][k]
+    g_routes_last = eng.read_routes(L, K)[:, 0, :]
+    assert g_routes_last.tolist() == o_routes[:, -1, :].tolist(), "routing of the last prompt token"
+    for _ in range(n_new):
+        t = int(np.argmax(o_logits[-1]))          # np.argmax returns the first maximum, like the reference's scan
+        toks.append(t)
+        oracle.clear_route_log()
+        o_logits.append(oracle.forward([t]))
+        lg, _ = eng.decode([t])
+        g_logits.append(lg[0])
+        assert eng.read_routes(L, K)[:, 0, :].tolist() == oracle.route_log().reshape(L, K).tolist(), f"routing at step {len(toks)}"
+    return np.array(o_logits), np.array(g_logits), toks
+
+
+def test_tiny_model_teacher_forced_logits_and_routing(oracle, gpu):
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 128, 1)
+    prompt = prompt_ids(1, 64, TINY["n_vocab"])
+    o, g, _ = _teacher_forced(oracle, eng, prompt, 32)
+    err = np.abs(o - g).max()
+    cos = min(cosine(a, b) for a, b in zip(o, g))
+    print(f"tiny teacher-forced: max-abs {err:.3e}, min cosine {cos:.8f}, exact logits {(o == g).mean():.3f}")
+    assert err <= 2e-2 and cos >= 0.999
+    assert (np.argmax(o, 1) == np.argmax(g, 1)).all()
+    # recurrent state left behind
+    for il in range(3):
+        so, sg = oracle.ssm_state(il), eng.read_ssm_state(il)
+        assert np.abs(so - sg).max() <= 1e-4 * max(1.0, float(np.abs(so).max())), il
+    eng.close()
+
+
+def test_tiny_model_greedy_tokens_match(oracle, gpu):
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 128, 1)
+    prompt = prompt_ids(1, 64, TINY["n_vocab"])
+    oracle.begin(128)
+    want, margins = oracle.generate(prompt, 32)
+    got = eng.generate(prompt, 32)
+    first_div = next((i for i in range(len(want)) if want[i] != got[i]), None)
+    assert first_div is None, f"first divergence at {first_div}, oracle top-2 margin there {margins[first_div]:.3e}"
+    # the device-resident loop produces the same tokens
+    eng.reset(); eng.prefill(prompt)
+    loop = eng.decode_loop([want[0]], 31)
+    assert loop[:, 0].tolist() == want[1:].tolist()
+    eng.close()
+
+
+def test_loaded_tensors_equal_generated_tensors(oracle, gpu):
+    """set_tensor (host bytes, the drop-in path) and the device generator give the same engine outputs."""
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    m2 = host.Model(ops, host_dims(TINY))
+    for s in oracle.specs:
+        data, sc = oracle.tensor(s["name"])
+        m2.set_tensor(s["name"], s["ty"], data, sc)
+    prompt = prompt_ids(2, 16, TINY["n_vocab"])
+    e1, e2 = host.Engine(model, 64, 1), host.Engine(m2, 64, 1)
+    a, b = e1.prefill(prompt), e2.prefill(prompt)
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    e1.close(); e2.close(); m2.close()
+
+
+def test_batch_of_sequences_equals_single_sequences(oracle, gpu):
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    prompts = np.stack([prompt_ids(10 + i, 12, TINY["n_vocab"]) for i in range(3)])
+    eb = host.Engine(model, 64, 3)
+    logits_b = eb.prefill(prompts)
+    ops.check()
+    for i in range(3):
+        e1 = host.Engine(model, 64, 1)
+        l1 = e1.prefill(prompts[i])
+        assert l1.view(np.uint32).tolist() == logits_b[i].view(np.uint32).tolist(), i
+        e1.close()
+    eb.close()
+
+
+def test_context_overflow_is_refused_before_any_write(oracle, gpu):
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 8, 1)
+    eng.prefill(prompt_ids(1, 6, TINY["n_vocab"]))
+    with pytest.raises(RuntimeError, match="context overflow"):
+        eng.prefill([1, 2, 3])
+    assert eng.pos() == 6
+    eng.close()
+
+
+def test_seam_ops_drive_a_whole_layer_like_the_reference_model_does(oracle, gpu):
+    """Qwen35::gated_delta + moe_batch (src/model/qwen35.rs:1232-1328, :1587-1699 there) written against the op-level
+    seam with host buffers as handles, exactly as the reference's model code calls its backend; compared with the
+    oracle's first-layer output through the embedding of one token."""
+    from inferred_thoughts_b200 import host
+    ops, _ = gpu
+    c = TINY; H = c["n_embd"]
+    T = lambda n: oracle.tensor(n)
+    def W(n, ty, n_in, n_out): return host.Weights(T(n)[0], ty, n_in, n_out)
+    def V(n): return np.ascontiguousarray(T(n)[0]).view(np.float32)
+    def E(n, n_in, n_out): d, s = T(n); return host.Experts(d, host.NVFP4, n_in, n_out, c["n_expert"], s)
+    key_dim = c["ssm_d_state"] * c["ssm_n_group"]; vd = c["ssm_d_inner"]; cd = 2 * key_dim + vd; nv = c["ssm_dt_rank"]; sk = c["ssm_d_state"]
+    tok = 17
+    x = V("token_embd.weight")[tok * H:(tok + 1) * H].copy()
+    f = lambda n: np.zeros(n, np.float32)
+    normed, qkv, z, alpha, beta, conv, qp, kp, vp, core, mixed = f(H), f(cd), f(vd), f(nv), f(nv), f(cd), f(key_dim), f(key_dim), f(vd), f(vd), f(H)
+    conv_state, ssm_state = f(cd * 3), f(nv * sk * sk)
+    P = "blk.0."
+    ops.begin_pass(1); ops.host_wrote(x)
+    ops.rms_norm(x, V(P + "attn_norm.weight"), c["rms_eps"], normed)
+    ops.matmul(W(P + "attn_qkv.weight", host.Q8_0, H, cd), normed, qkv)
+    ops.matmul(W(P + "attn_gate.weight", host.Q8_0, H, vd), normed, z)
+    ops.matmul_pair(W(P + "ssm_alpha.weight", host.F32, H, nv), W(P + "ssm_beta.weight", host.F32, H, nv), normed, alpha, beta)
+    ops.ssm_conv(conv_state, qkv, V(P + "ssm_conv1d.weight"), 4, conv)
+    ops.gather_chunks(conv, key_dim, cd, 0, qp); ops.gather_chunks(conv, key_dim, cd, key_dim, kp); ops.gather_chunks(conv, vd, cd, 2 * key_dim, vp)
+    ops.l2_norm_heads(qp, sk, c["rms_eps"]); ops.l2_norm_heads(kp, sk, c["rms_eps"])
+    ops.delta_rule(qp, kp, vp, alpha, beta, V(P + "ssm_a"), V(P + "ssm_dt.bias"), sk, sk, c["ssm_n_group"], nv, ssm_state, core)
+    ops.rms_norm_heads(core, V(P + "ssm_norm.weight"), sk, c["rms_eps"])
+    ops.silu_mul(z, core)
+    ops.matmul(W(P + "ssm_out.weight", host.Q8_0, vd, H), z, mixed)
+    ops.add_assign(x, mixed)
+    # routed FFN
+    e_in, router, logit = f(H), f(c["n_expert"]), f(1)
+    ff, K = c["expert_ff"], c["n_expert_used"]
+    g_all, u_all, o_all, e_gate, e_up, e_out, ffn_out = f(K * ff), f(K * ff), f(K * H), f(c["shared_ff"]), f(c["shared_ff"]), f(H), f(H)
+    ops.rms_norm(x, V(P + "post_attention_norm.weight"), c["rms_eps"], normed)
+    ops.gather_chunks(normed, H, H, 0, e_in)
+    ops.matmul_pair(W(P + "ffn_gate_inp.weight", host.F32, H, c["n_expert"]), W(P + "ffn_gate_inp_shexp.weight", host.F32, H, 1), e_in, router, logit)
+    ops.softmax(router, c["n_expert"])
+    route = ops.route(router, c["n_expert"], K)
+    ops.moe_glu(E(P + "ffn_gate_exps.weight", H, ff), E(P + "ffn_up_exps.weight", H, ff), route, e_in, g_all, u_all)
+    ops.matmul_experts(E(P + "ffn_down_exps.weight", ff, H), route, g_all, o_all)
+    ops.matmul(W(P + "ffn_gate_shexp.weight", host.Q8_0, H, c["shared_ff"]), e_in, e_gate)
+    ops.matmul(W(P + "ffn_up_shexp.weight", host.Q8_0, H, c["shared_ff"]), e_in, e_up)
+    ops.silu_mul(e_gate, e_up)
+    ops.matmul(W(P + "ffn_down_shexp.weight", host.Q8_0, c["shared_ff"], H), e_gate, e_out)
+    ops.moe_finish(ffn_out, 0, H, o_all, route, e_out, logit, 0)
+    ops.add_assign(x, ffn_out)
+    ops.end_pass(); ops.host_needs(x); ops.check()
+    ids, _ = ops.read_route(route)
+    # the oracle, one layer only: a model with the same tensors but n_layer = 1
+    one = dict(TINY); one["n_layer"] = 1
+    om = O.OracleModel(oracle_dims(one))
+    for s in om.specs:
+        d, sc = oracle.tensor(s["name"]); om.set_tensor(s["name"], d, sc)
+    om.begin(8, log_routes=True)
+    om.forward([tok])
+    assert ids.tolist() == om.route_log().tolist()
+    # x after the layer is not exposed by the oracle's forward; compare through its recurrent state instead
+    ops.read_state(ssm_state)
+    so = om.ssm_state(0)
+    assert np.abs(ssm_state - so).max() <= 1e-5 * max(1.0, float(np.abs(so).max()))
+    ops.forget_state()
