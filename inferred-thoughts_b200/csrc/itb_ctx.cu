@@ -270,7 +270,15 @@ void itb_f16_to_f32(cudaStream_t st, const uint16_t* raw, float* out, size_t n) 
 const WeightEntry* itb_weight(itb_ctx* c, const uint8_t* data, size_t bytes, uint32_t ty, size_t n_in, size_t n_out,
                               size_t n_expert, const uint8_t* scale, size_t scale_bytes) {
     auto it = c->weights.find(data);
-    if (it != c->weights.end()) return &it->second;
+    if (it != c->weights.end()) {
+        const WeightEntry& h = it->second;
+        if (h.ty == ty && h.n_in == n_in && h.n_out == n_out && h.n_expert == n_expert) return &it->second;
+        // The address now names a different tensor (the caller freed and reallocated): drop the old upload.
+        cudaStreamSynchronize(c->stream);
+        cudaFree(h.a); cudaFree(h.b); cudaFree(h.scale2);
+        c->weight_bytes -= h.bytes;
+        c->weights.erase(it);
+    }
     WeightEntry w;
     w.ty = ty; w.n_in = n_in; w.n_out = n_out; w.n_expert = n_expert;
     size_t elems = n_in * n_out * n_expert;

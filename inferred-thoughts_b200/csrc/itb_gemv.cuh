@@ -113,13 +113,19 @@ __device__ __forceinline__ void q8_rows(const DevQ8& w, int r0, int r1, const in
 // permute per four codes: the selector's bit 3 asks for the sign of the selected (positive) byte, i.e. 0,
 // so `prmt(pool, w)` yields the magnitudes of the positive codes and zeros elsewhere, and the same on
 // `w ^ 0x8888` yields the magnitudes of the negative codes.
+// (The __byte_perm intrinsic masks bit 3 of each selector, so the PTX instruction is issued directly.)
+__device__ __forceinline__ uint32_t prmt_raw(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(sel));
+    return d;
+}
 __device__ __forceinline__ int fp4_dot8(uint32_t w, uint32_t a0, uint32_t a1) {
     const uint32_t P0 = 0x03020100u, P1 = 0x0c080604u;
     uint32_t n = w ^ 0x88888888u;
-    int pos = __dp4a((int)__byte_perm(P0, P1, w), (int)a0, 0);
-    pos = __dp4a((int)__byte_perm(P0, P1, w >> 16), (int)a1, pos);
-    int neg = __dp4a((int)__byte_perm(P0, P1, n), (int)a0, 0);
-    neg = __dp4a((int)__byte_perm(P0, P1, n >> 16), (int)a1, neg);
+    int pos = __dp4a((int)prmt_raw(P0, P1, w), (int)a0, 0);
+    pos = __dp4a((int)prmt_raw(P0, P1, w >> 16), (int)a1, pos);
+    int neg = __dp4a((int)prmt_raw(P0, P1, n), (int)a0, 0);
+    neg = __dp4a((int)prmt_raw(P0, P1, n >> 16), (int)a1, neg);
     return pos - neg;
 }
 

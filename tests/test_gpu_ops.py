@@ -24,6 +24,16 @@ def ops():
     o.close()
 
 
+# Host addresses are the library's handles (weights, KV slabs): an array that has been passed in must stay alive,
+# or a later allocation can reuse its address and meet the stale device copy. Same rule as the reference's mmap.
+KEEP = []
+
+
+def keep(a):
+    KEEP.append(a)
+    return a
+
+
 def bits(a):
     return np.ascontiguousarray(a, np.float32).view(np.uint32)
 
@@ -43,7 +53,7 @@ def q8_weights(n_out, n_in, seed):
     w = noise(n_out * n_in, seed, 0.02)
     out = np.zeros(n_out * n_in // 32 * 34, np.uint8)
     L.orc_q8_0_blocks(w, w.size, out)
-    return out
+    return keep(out)
 
 
 def nvfp4_weights(n_expert, n_out, n_in, seed):
@@ -54,7 +64,7 @@ def nvfp4_weights(n_expert, n_out, n_in, seed):
     blk[:, :4] = rng.integers(0x20, 0x50, (nb, 4))
     blk[:, 4:] = rng.integers(0, 256, (nb, 32))
     scale = (rng.random(n_expert).astype(np.float32) + 0.5) * 1e-3
-    return blk.reshape(-1), scale
+    return keep(blk.reshape(-1)), keep(scale)
 
 
 @pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 96, 1), (4096, 40, 1), (512, 64, 3), (256, 33, 2), (128, 7, 1), (3072, 16, 1), (768, 24, 1)])
@@ -84,7 +94,7 @@ def test_matmul_nvfp4_golden_rows(ops):
     from pathlib import Path
     from inferred_thoughts_b200 import host
     d = np.load(Path(__file__).parent / "golden" / "dot_nvfp4_q8_0.npz")
-    wb = np.ascontiguousarray(d["weights"]); x = np.ascontiguousarray(d["activation"])
+    wb = keep(np.ascontiguousarray(d["weights"])); x = np.ascontiguousarray(d["activation"])
     out = np.zeros(64, np.float32)
     ops.begin_pass(1)
     ops.matmul(host.Weights(wb, host.NVFP4, 2048, 64), x, out); ops.host_needs(out); ops.check()
@@ -94,7 +104,7 @@ def test_matmul_nvfp4_golden_rows(ops):
 @pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 256, 1), (2048, 1, 2), (256, 40, 3)])
 def test_matmul_f32_exact_serial(ops, n_in, n_out, n_tok):
     from inferred_thoughts_b200 import host
-    w = noise(n_out * n_in, 30, 0.02)
+    w = keep(noise(n_out * n_in, 30, 0.02))
     x = noise(n_tok * n_in, 31); out = np.zeros(n_tok * n_out, np.float32); want = np.zeros_like(out)
     ops.begin_pass(n_tok)
     ops.matmul(host.Weights(w, host.F32, n_in, n_out), x, out); ops.host_needs(out); ops.check()
@@ -105,7 +115,7 @@ def test_matmul_f32_exact_serial(ops, n_in, n_out, n_tok):
 def test_matmul_pair_and_f16(ops):
     from inferred_thoughts_b200 import host
     n_in = 256
-    wa = noise(32 * n_in, 40, 0.02); wb16 = noise(3 * n_in, 41, 0.02).astype(np.float16)
+    wa = keep(noise(32 * n_in, 40, 0.02)); wb16 = keep(noise(3 * n_in, 41, 0.02).astype(np.float16))
     x = noise(2 * n_in, 42); oa = np.zeros(64, np.float32); ob = np.zeros(6, np.float32)
     ops.begin_pass(2)
     ops.matmul_pair(host.Weights(wa, host.F32, n_in, 32), host.Weights(wb16, host.F16, n_in, 3), x, oa, ob)
@@ -164,7 +174,7 @@ def test_gather_scatter_kv_write(ops):
     ops.gather_chunks(src, 32, 96, 64, out); ops.host_needs(out); L.orc_gather_chunks(src, 32, 96, 64, want, want.size); exact(out, want, "gather")
     dst = noise(4 * 96, 81); dst2 = dst.copy()
     ops.scatter_chunks(out, 32, 96, 5, dst); ops.host_needs(dst); L.orc_scatter_chunks(out, out.size, 32, 96, 5, dst2); exact(dst, dst2, "scatter")
-    slab = np.zeros(64 * 8, np.uint16); slab2 = slab.copy(); kv = noise(3 * 64, 82, 50.0)
+    slab = keep(np.zeros(64 * 8, np.uint16)); slab2 = slab.copy(); kv = noise(3 * 64, 82, 50.0)
     ops.kv_write(slab, 2 * 64, kv); ops.read_kv(slab); L.orc_kv_write(slab2, 2 * 64, kv, kv.size, 0)
     assert (slab == slab2).all()
     ops.check()
@@ -179,7 +189,7 @@ def test_bad_shapes_set_the_sticky_error_and_nothing_runs(ops):
 
 def test_ssm_conv_and_state(ops):
     nc, kern, nt = 512, 4, 5
-    st = noise(nc * 3, 100); st2 = st.copy(); x = noise(nt * nc, 101); w = noise(nc * kern, 102, 0.5)
+    st = keep(noise(nc * 3, 100)); st2 = st.copy(); x = noise(nt * nc, 101); w = noise(nc * kern, 102, 0.5)
     out = np.zeros_like(x); want = np.zeros_like(x)
     ops.begin_pass(nt)
     ops.ssm_conv(st, x, w, kern, out); ops.host_needs(out); ops.read_state(st); ops.check()
@@ -193,7 +203,7 @@ def test_ssm_conv_and_state(ops):
 def test_delta_rule_and_state(ops, sk, nk, nv, nt):
     q = noise(nt * nk * sk, 110, 0.1); k = noise(nt * nk * sk, 111, 0.1); v = noise(nt * nv * sk, 112)
     al = noise(nt * nv, 113); be = noise(nt * nv, 114); sa = -np.abs(noise(nv, 115)); dt = noise(nv, 116, 0.02)
-    st = noise(nv * sk * sk, 117, 0.1); st2 = st.copy()
+    st = keep(noise(nv * sk * sk, 117, 0.1)); st2 = st.copy()
     out = np.zeros(nt * nv * sk, np.float32); want = np.zeros_like(out)
     ops.begin_pass(nt)
     ops.delta_rule(q, k, v, al, be, sa, dt, sk, sk, nk, nv, st, out); ops.host_needs(out); ops.read_state(st); ops.check()
@@ -261,7 +271,7 @@ def test_attend_close(ops, hd, nh, nkv, n_pos, n_q):
     kvd = hd * nkv; n_ctx = n_pos + 8
     q = noise(n_q * nh * hd, 140)
     kf = noise(n_ctx * kvd, 141); vf = noise(n_ctx * kvd, 142)
-    ks = np.zeros(n_ctx * kvd, np.uint16); vs = np.zeros_like(ks)
+    ks = keep(np.zeros(n_ctx * kvd, np.uint16)); vs = keep(np.zeros_like(ks))
     L.orc_kv_write(ks, 0, kf, kf.size, 0); L.orc_kv_write(vs, 0, vf, vf.size, 0)
     out = np.zeros(n_q * nh * hd, np.float32); want = np.zeros_like(out)
     scale = 1.0 / np.sqrt(hd)
