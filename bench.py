@@ -1,0 +1,287 @@
+"""Benchmark of the hybrid-MoE token loop on B200: decode tok/s on the 35B-A3B-shape NVFP4 model.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl reference]
+
+A step is one decode step (one token for each of B sequences) after a 512-token random prompt at a KV
+capacity of 8192 (BASELINE.json config 3). Prints ONE JSON line: device-timed throughput (`value`), the same
+through the C ABI with host buffers (`e2e`), the roofline of the dominant kernel measured live with CUDA
+events, the CPU oracle timed on the host cores beside it, clocks sampled during the timed region.
+With N > 1 (torchrun) every rank decodes its own sequences on its own full copy of the model: the path
+shards by sequence with no data-path collective, and the whole-job value is the sum.
+"""
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from inferred_thoughts_b200 import configs  # noqa: E402
+
+PROMPT, N_CTX = 512, 8192
+FALLBACK_HBM = 6650.0
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_HBM, "fallback 6650 GB/s (no MEASURED_PEAKS.json)"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--id={device}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.p.terminate(); self.p.wait()
+        self.f.flush(); self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.f.name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def prompts(batch, seed, n_vocab):
+    return np.stack([np.random.default_rng(seed + i).integers(0, n_vocab, PROMPT).astype(np.uint32) for i in range(batch)])
+
+
+def cpu_oracle_tok_s(model, dims, seed, budget_s, threads):
+    """The CPU oracle (C++ restatement of the reference CPU path) on the same weights, copied back from the device.
+    Bounded sample: decode tokens from an empty context until about `budget_s` seconds of CPU work are spent."""
+    from oracle import oracle_py as O
+    om = O.OracleModel(O.ModelDims(**dims))
+    t0 = time.time()
+    for s in om.specs:
+        data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+        om.set_tensor(s["name"], data, sc)
+    load_s = time.time() - t0
+    O.lib().orc_set_threads(threads)
+    om.begin(64)
+    rng = np.random.default_rng(seed)
+    n, t0 = 0, time.time()
+    tok = int(rng.integers(0, dims["n_vocab"]))
+    while True:
+        logits = om.forward([tok]); n += 1
+        tok = int(np.argmax(logits))
+        if time.time() - t0 > budget_s or n >= 48:
+            break
+    dt = time.time() - t0
+    return n / dt, n, load_s
+
+
+def kernel_breakdown(eng, tok):
+    from inferred_thoughts_b200 import host  # noqa: F401
+
+    class Stat(C.Structure):
+        _fields_ = [("name", C.c_char * 32), ("launches", C.c_uint32), ("ms", C.c_float), ("bytes", C.c_uint64)]
+    arr = (Stat * 16)()
+    n = C.c_size_t()
+    t = np.ascontiguousarray(tok, np.uint32)
+    acc = {}
+    reps = 3
+    for _ in range(reps):
+        if eng.L.itb_engine_profile_step(eng.h, C.c_void_p(t.ctypes.data), arr, C.c_size_t(16), C.byref(n)):
+            eng.model.ops.check(); raise RuntimeError("profile_step failed")
+        for i in range(n.value):
+            a = acc.setdefault(arr[i].name.decode(), [0, 0.0, 0])
+            a[0] += arr[i].launches; a[1] += arr[i].ms; a[2] += arr[i].bytes
+    out = []
+    for name, (launches, ms, nbytes) in acc.items():
+        if launches:
+            out.append(dict(kernel=name, launches_per_step=launches // reps, ms_per_step=ms / reps, bytes_per_step=nbytes // reps,
+                            gbs=nbytes / ms / 1e6 if ms > 0 else None))
+    return sorted(out, key=lambda k: -k["ms_per_step"])
+
+
+def run_product(args, rank, world):
+    from inferred_thoughts_b200 import host
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank))))
+    device = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(device)
+    dims = dict(configs.M35B)
+    seed = configs.SEEDS["m35b"]
+    kv = "bf16"
+    ops = host.B200Ops(device, f"kv={kv},exact={args.exact}")
+    model = host.Model(ops, host.ModelDims(**dims))
+    t0 = time.time()
+    model.synth(seed)
+    synth_s = time.time() - t0
+    B = args.batch
+    eng = host.Engine(model, N_CTX, B)
+    pr = prompts(B, seed + 1000 * rank, dims["n_vocab"])
+    eng.prefill(pr, want_logits=False)
+    first = np.zeros(B, np.uint32)
+    # warm-up (also builds the graph): W steps
+    if args.warmup:
+        first = eng.decode_loop(first, args.warmup)[-1]
+    # ---- device-timed region: K steps, inputs resident in HBM ----
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(device) if rank == 0 else None
+    toks = eng.decode_loop(first, args.steps)
+    torch.cuda.synchronize()
+    dev_ms = eng.last_ms()
+    # ---- end to end through the C ABI: host token in, host token out, every step ----
+    cur = toks[-1].copy()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _, cur = eng.decode(cur, want_logits=False)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop() if sampler else None
+    if dist is not None:
+        t = torch.tensor([dev_ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_s = float(t[0]), float(t[1])
+    n_pos = eng.pos(0)
+    if rank != 0:
+        return
+    hbm, hbm_src = peaks()
+    kb = kernel_breakdown(eng, cur)
+    dom = kb[0]
+    per_launch_bytes = dom["bytes_per_step"] / dom["launches_per_step"]
+    per_launch_ms = dom["ms_per_step"] / dom["launches_per_step"]
+    achieved = per_launch_bytes / per_launch_ms / 1e6
+    step_bytes = model.decode_bytes(B, n_pos, min(dims["n_expert"], dims["n_expert_used"] * B))
+    ms_per_step = dev_ms / args.steps
+    value = world * B * args.steps / (dev_ms / 1e3)
+    line = {
+        "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)", "value": value, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8 (int8 x int8 / e2m1 x int8 dots, f32 accumulate; f32 state)",
+        "data": "synthetic (seeded Gaussian weights quantised to NVFP4 / Q8_0, uniform-random token ids)",
+        "config": {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}", "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": kv,
+                   "n_pos_at_end": n_pos, "f32_dots": "serial-k" if args.exact else "tree", "parallelism": "replicas" if world > 1 else "single",
+                   "l2": "each step streams ~2.8 GB of weights, far beyond the 126 MB L2; no flush needed"},
+        "e2e": {"value": world * B * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                "api": "itb_engine_decode (host token ids in, host argmax ids out)"},
+        "gpu_launches": int(eng.launches_per_step()) * args.steps * 2,
+        "roofline": {"bound": "hbm", "kernel": dom["kernel"], "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                     "traffic": None, "peak_source": hbm_src, "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
+        "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / ms_per_step / 1e6, "peak": hbm, "unit": "GB/s",
+                          "frac": step_bytes / ms_per_step / 1e6 / hbm, "frac_of_8TBs_nominal": step_bytes / ms_per_step / 1e6 / 8000.0},
+        "kernels": kb, "clocks": clocks, "synth_s": synth_s,
+    }
+    if world == 1 and not args.no_cpu:
+        try:
+            from oracle import oracle_py as O
+            threads = O.lib().orc_hw_threads()
+            v, n, load_s = cpu_oracle_tok_s(model, dims, seed, args.cpu_budget, threads)
+            line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": f"{n} decode tokens from an empty context, same weights (copied back from the device in {load_s:.0f} s), batch 1"}
+        except Exception as ex:  # the baseline is a report, never a reason to lose the measurement
+            line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
+    print(json.dumps(line), flush=True)
+    eng.close(); model.close(); ops.close()
+
+
+def run_reference(args, rank, world):
+    """The reference's CPU path (its algorithm, restated in C++: the reference itself is Rust and cannot be built here)
+    on the host cores, on the same config and metric. Weights come from the device generator when a GPU is there
+    (bit-identical to the CPU generator, and minutes faster for 35 B parameters), else from the CPU generator."""
+    if rank != 0:
+        return
+    from oracle import oracle_py as O
+    dims = dict(configs.M35B)
+    seed = configs.SEEDS["m35b"]
+    threads = O.lib().orc_hw_threads()
+    om = O.OracleModel(O.ModelDims(**dims))
+    src = "cpu generator"
+    try:
+        from inferred_thoughts_b200 import host
+        ops = host.B200Ops(0)
+        model = host.Model(ops, host.ModelDims(**dims))
+        for s in om.specs:
+            data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+            om.set_tensor(s["name"], data, sc)
+        model.close(); ops.close()
+        src = "device generator, copied to the host"
+    except Exception:
+        om.synth(seed, threads)
+    O.lib().orc_set_threads(threads)
+    om.begin(64 + args.steps + args.warmup)
+    tok = 1
+    for _ in range(args.warmup):
+        tok = int(np.argmax(om.forward([tok])))
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = int(np.argmax(om.forward([tok])))
+    dt = time.perf_counter() - t0
+    v = args.steps / dt
+    print(json.dumps({
+        "impl": "reference", "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)", "value": v, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": f"synthetic ({src})",
+        "config": {"workload": "cfg3-decode-35B-A3B-shape-bs1", "batch_per_gpu": 1, "n_ctx": N_CTX, "sample": "decode tokens from an empty context"},
+        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
+                         "sample": f"{args.steps} decode tokens from an empty context after {args.warmup} warm-up tokens"},
+        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--impl", default="product")
+    ap.add_argument("--exact", type=int, default=0, help="1: F32 dots accumulate serially like the CPU path")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--prompt", type=int, default=512, help="prompt tokens before the timed decode steps (BASELINE: 512)")
+    ap.add_argument("--cpu-budget", type=float, default=12.0)
+    args = ap.parse_args()
+    global PROMPT
+    PROMPT = args.prompt
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    if args.impl == "reference":
+        args.steps = min(args.steps, 256)   # a CPU step is a whole 2.8 GB token: keep the run within minutes
+        run_reference(args, rank, world)
+    else:
+        run_product(args, rank, world)
+
+
+if __name__ == "__main__":
+    main()

@@ -161,6 +161,11 @@ int  itb_engine_read_ssm_state(itb_engine*, uint32_t seq, uint32_t il, float* ou
 float itb_engine_last_ms(itb_engine*);
 uint64_t itb_engine_launches_per_step(itb_engine*);
 
+/* Per-kernel-class totals of one eagerly launched decode step, timed with a CUDA event after every launch:
+ * launches, summed milliseconds, summed algorithmic bytes (weights once, state read+write, KV read). */
+typedef struct { char name[32]; uint32_t launches; float ms; uint64_t bytes; } itb_kernel_stat;
+int  itb_engine_profile_step(itb_engine*, const uint32_t* tokens, itb_kernel_stat* out, size_t cap, size_t* n_out);
+
 /* Device generator check: element i of stream `key` (tests compare with the CPU generator). */
 int  itb_synth_values(itb_ctx*, uint64_t key, uint64_t first, size_t n, int dist, float std_, float* out);
 

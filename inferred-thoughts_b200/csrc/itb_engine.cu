@@ -19,434 +19,7 @@ void itb_synth_q8_raw(cudaStream_t st, uint64_t key, size_t n_blocks, int dist, 
 void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t e_lo, size_t e_hi, int dist, float sd,
                        unsigned* amax_tmp, float* scale2, uint8_t* raw);
 
-// =====================================================================================================
-// Fused kernels
-// =====================================================================================================
-struct InProj {
-    const float* x; int x_stride;                 // [B][n_embd] residual stream (or embedding rows)
-    const float* norm_w; float eps; int n_embd;
-    int nq; DevQ8 q[3]; float* qout[3]; int qstride[3];
-    int nf; DevF32 f[2]; float* fout[2]; int fstride[2];
-    const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;  // conv epilogue on q[0]
-    int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
-    int exact;
-};
-
-// RMSNorm + Q8_0 quantise prologue, then up to three Q8_0 matrices and two F32 matrices against the same
-// row. Warps 0..nw-2 stream the Q8_0 rows; the last warp of a block takes one unit of F32 rows.
-// With conv_w set, rows of q[0] go through the depthwise causal conv + SiLU (src/ops/naive.rs:275-315) in
-// the epilogue, the lane that owns a row also advancing that channel's window.
-__global__ void __launch_bounds__(288) k_in_proj(InProj p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int RP = 4;
-    const int n = p.n_embd, nb = n / 32, gsh = lanes_shift(nb);
-    double* red = (double*)smem;
-    float* xn = (float*)(red + 32);
-    int8_t* xq = (int8_t*)(xn + n);
-    float* xs = (float*)(xq + n);
-    float* scratch = xs + nb;
-    const int b = blockIdx.y, wid = threadIdx.x >> 5, nw = blockDim.x >> 5, nwq = nw - 1;
-    block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
-    block_quant_q8(xn, n, xq, xs);
-    if (p.xq_out && blockIdx.x == 0) {
-        for (int i = threadIdx.x; i < n; i += blockDim.x) p.xq_out[(size_t)b * n + i] = xq[i];
-        for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
-    }
-    if (wid < nwq) {
-        float* terms = scratch + wid * terms_floats(RP, gsh, nb);
-        int total = 0;
-        for (int m = 0; m < p.nq; ++m) total += p.q[m].n_out;
-        int b0, b1, r0, r1;
-        share(total, gridDim.x, blockIdx.x, b0, b1);
-        share(b1 - b0, nwq, wid, r0, r1);
-        r0 += b0; r1 += b0;
-        int base = 0;
-        for (int m = 0; m < p.nq; ++m) {
-            int lo = max(r0, base) - base, hi = min(r1, base + p.q[m].n_out) - base;
-            if (lo < hi) {
-                float* o = p.qout[m] + (size_t)b * p.qstride[m];
-                if (m == 0 && p.conv_w) {
-                    const int kernel = p.conv_kernel, keep = kernel - 1;
-                    float* st = p.conv_state + (size_t)b * p.conv_state_stride;
-                    q8_rows<RP>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) {
-                        float* past = st + (size_t)row * keep;
-                        const float* w = p.conv_w + (size_t)row * kernel;
-                        float sum = 0.0f;
-                        for (int k = 0; k < keep; ++k) sum += past[k] * w[k];
-                        sum += v * w[keep];
-                        o[row] = silu_f(sum);
-                        for (int k = 0; k + 1 < keep; ++k) past[k] = past[k + 1];
-                        past[keep - 1] = v;
-                    });
-                } else {
-                    q8_rows<RP>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) { o[row] = v; });
-                }
-            }
-            base += p.q[m].n_out;
-        }
-    } else {
-        // F32 rows: units of 32 rows (serial-k mode) or 4 rows; unit u goes to block u.
-        const int unit = p.exact ? 32 : 4;
-        float* tile = scratch + nwq * terms_floats(RP, gsh, nb);
-        int ubase = 0;
-        for (int m = 0; m < p.nf; ++m) {
-            int units = (p.f[m].n_out + unit - 1) / unit;
-            for (int u = (int)blockIdx.x - ubase; u < units; u += gridDim.x) {
-                if (u < 0) continue;
-                int lo = u * unit, hi = min(p.f[m].n_out, lo + unit);
-                float* o = p.fout[m] + (size_t)b * p.fstride[m];
-                if (p.exact) f32_rows<true>(p.f[m].w, n, lo, hi, xn, tile, [&](int row, float v) { o[row] = v; });
-                else f32_rows<false>(p.f[m].w, n, lo, hi, xn, tile, [&](int row, float v) { o[row] = v; });
-            }
-            ubase = (ubase + units) % gridDim.x;
-        }
-    }
-}
-static size_t in_proj_smem(int n, int nw) {
-    int nb = n / 32, gsh = lanes_shift(nb);
-    return 256 + (size_t)n * 4 + n + (size_t)nb * 4 + (size_t)(nw - 1) * terms_floats(4, gsh, nb) * 4 + 32 * 33 * 4;
-}
-
-// Output projection with the residual add fused: x[b] += W . quantise(a[b]) (src/model/qwen35.rs:1017, :1220, :1325).
-struct OutProj { const float* a; int a_stride; int n_in; DevQ8 w; float* x; int x_stride; };
-__global__ void __launch_bounds__(256) k_out_proj(OutProj p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int RP = 4;
-    const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
-    float* an = (float*)smem;
-    int8_t* aq = (int8_t*)(an + n);
-    float* as = (float*)(aq + n);
-    const int b = blockIdx.y, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    float* terms = as + nb + wid * terms_floats(RP, gsh, nb);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) an[i] = p.a[(size_t)b * p.a_stride + i];
-    __syncthreads();
-    block_quant_q8(an, n, aq, as);
-    int b0, b1, r0, r1;
-    share(p.w.n_out, gridDim.x, blockIdx.x, b0, b1);
-    share(b1 - b0, nw, wid, r0, r1);
-    float* x = p.x + (size_t)b * p.x_stride;
-    q8_rows<RP>(p.w, b0 + r0, b0 + r1, aq, as, terms, gsh, [&](int row, float v) { x[row] += v; });
-}
-static size_t out_proj_smem(int n, int nw) {
-    int nb = n / 32, gsh = lanes_shift(nb);
-    return (size_t)n * 4 + n + (size_t)nb * 4 + (size_t)nw * terms_floats(4, gsh, nb) * 4;
-}
-
-// GatedDeltaNet core for one (value head, sequence): l2-norm of q and k, gated delta rule over the
-// head's [sv][sk] state, gated RMSNorm and the SiLU(z) gate (src/model/qwen35.rs:1298-1322,
-// src/ops/naive.rs:86-135, :254-273). One thread per value row, keys walked serially.
-struct GdnCore {
-    const float* conv; int conv_stride;           // [B][conv_dim] = q | k | v after conv + SiLU
-    const float* z; const float* alpha; const float* beta;  // [B][value_dim], [B][n_v], [B][n_v]
-    const float* ssm_a; const float* dt_bias; const float* ssm_norm;
-    float* state; size_t state_stride;             // [B][n_v][sv][sk]
-    float* out;                                    // [B][value_dim]: silu(z) * norm(core)
-    int sk, sv, n_k, n_v; float eps;
-};
-__global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    const int sk = p.sk, sv = p.sv, h = blockIdx.x, b = blockIdx.y, kh = h % p.n_k, tid = threadIdx.x;
-    const int lane = tid & 31, wid = tid >> 5;
-    float* S = (float*)smem;                 // [sv][sk+1]
-    float* kq = S + sv * (sk + 1);           // k[sk] | q[sk]
-    float* o = kq + 2 * sk;                  // [sv]
-    __shared__ double red2[8];
-    const int key_dim = p.n_k * sk;
-    const float* cv = p.conv + (size_t)b * p.conv_stride;
-    float* sg = p.state + (size_t)b * p.state_stride + (size_t)h * sv * sk;
-    for (int i = tid; i < sv * sk / 4; i += blockDim.x) {
-        float4 v = ((const float4*)sg)[i];
-        int r = (i * 4) / sk, c0 = (i * 4) % sk;
-        float* d = S + r * (sk + 1) + c0;
-        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
-    }
-    // warp 0 normalises k, warp 1 normalises q (f64 tree sum, narrowing before the root)
-    if (wid < 2) {
-        const float* src = cv + (wid == 0 ? key_dim : 0) + kh * sk;
-        double acc = 0.0;
-        for (int i = lane; i < sk; i += 32) { float v = src[i]; acc += (double)(v * v); }
-        acc = warp_sum_d(acc);
-        float sc = 1.0f / fmaxf(sqrtf((float)acc), p.eps);
-        float qs = 1.0f / sqrtf((float)sk);
-        for (int i = lane; i < sk; i += 32) {
-            float v = src[i] * sc;
-            kq[wid * sk + i] = wid == 0 ? v : v * qs;
-        }
-    }
-    __syncthreads();
-    if (tid < sv) {
-        float a = p.alpha[(size_t)b * p.n_v + h] + p.dt_bias[h];
-        float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
-        float g = exp_f(sp * p.ssm_a[h]);
-        float bt = sigmoid_f(p.beta[(size_t)b * p.n_v + h]);
-        float* row = S + tid * (sk + 1);
-        float pred = 0.0f;
-        for (int i = 0; i < sk; ++i) { float s = row[i] * g; row[i] = s; pred += s * kq[i]; }
-        float d = bt * (cv[2 * key_dim + h * sv + tid] - pred);
-        float acc = 0.0f;
-        for (int i = 0; i < sk; ++i) { float s = row[i] + kq[i] * d; row[i] = s; acc += s * kq[sk + i]; }
-        o[tid] = acc;
-    }
-    __syncthreads();
-    // gated RMSNorm over the head's sv outputs, then * silu(z)
-    {
-        double acc = 0.0;
-        for (int i = tid; i < sv; i += blockDim.x) acc += (double)(o[i] * o[i]);
-        acc = warp_sum_d(acc);
-        if (lane == 0) red2[wid] = acc;
-        __syncthreads();
-        double tot = 0.0;
-        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red2[w];
-        float mean = (float)(tot / (double)sv);
-        float sc = 1.0f / sqrtf(mean + p.eps);
-        if (tid < sv) {
-            float core = o[tid] * sc * p.ssm_norm[tid];
-            size_t idx = (size_t)b * p.n_v * sv + (size_t)h * sv + tid;
-            p.out[idx] = silu_f(p.z[idx]) * core;
-        }
-    }
-    for (int i = tid; i < sv * sk / 4; i += blockDim.x) {
-        int r = (i * 4) / sk, c0 = (i * 4) % sk;
-        const float* s = S + r * (sk + 1) + c0;
-        ((float4*)sg)[i] = make_float4(s[0], s[1], s[2], s[3]);
-    }
-}
-
-// Attention prologue per head: de-interleave q|gate, QK RMSNorm, partial NEOX RoPE at the sequence's
-// position, KV write (src/model/qwen35.rs:1175-1198). grid (n_head + 2*n_head_kv, B), block = head_dim.
-struct AttnPrep {
-    const float* qg; const float* k; const float* v;      // [B][2*hd*n_head], [B][kv_dim], [B][kv_dim]
-    const float* q_norm; const float* k_norm;
-    float* q_out; float* g_out;                            // [B][n_head*hd]
-    uint16_t* kslab; uint16_t* vslab; size_t slab_stride;  // per sequence [n_ctx][kv_dim]
-    const int* pos; int* npos_out;                         // position of this token; positions to attend over
-    int hd, n_head, n_head_kv, n_rot; float theta, eps; int bf16;
-};
-__global__ void k_attn_prep(AttnPrep p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    float* val = (float*)smem;  // [hd]
-    __shared__ double red[8];
-    const int job = blockIdx.x, b = blockIdx.y, d = threadIdx.x, hd = p.hd, kvd = p.n_head_kv * hd;
-    const int pos = p.pos[b];
-    if (job == 0 && d == 0) p.npos_out[b] = pos + 1;
-    const bool is_q = job < p.n_head, is_k = !is_q && job < p.n_head + p.n_head_kv;
-    const int hk = is_q ? job : is_k ? job - p.n_head : job - p.n_head - p.n_head_kv;
-    float v;
-    if (is_q) {
-        v = p.qg[(size_t)b * 2 * hd * p.n_head + (size_t)hk * 2 * hd + d];
-        p.g_out[((size_t)b * p.n_head + hk) * hd + d] = p.qg[(size_t)b * 2 * hd * p.n_head + (size_t)hk * 2 * hd + hd + d];
-    } else {
-        v = (is_k ? p.k : p.v)[(size_t)b * kvd + hk * hd + d];
-    }
-    if (is_q || is_k) {
-        double acc = warp_sum_d((double)(v * v));
-        if ((d & 31) == 0) red[d >> 5] = acc;
-        __syncthreads();
-        double tot = 0.0;
-        for (int w = 0; w < hd / 32; ++w) tot += red[w];
-        float mean = (float)(tot / (double)hd);
-        float sc = 1.0f / sqrtf(mean + p.eps);
-        v = v * sc * (is_q ? p.q_norm : p.k_norm)[d];
-        val[d] = v;
-        __syncthreads();
-        const int half = p.n_rot / 2;
-        if (d < half) {
-            double freq = pow((double)p.theta, -2.0 * (double)d / (double)p.n_rot);
-            double th = (double)pos * freq;
-            float sn = (float)sin(th), cs = (float)cos(th);
-            float x0 = val[d], x1 = val[d + half];
-            val[d] = x0 * cs - x1 * sn;
-            val[d + half] = x0 * sn + x1 * cs;
-        }
-        __syncthreads();
-        v = val[d];
-    }
-    if (is_q) p.q_out[((size_t)b * p.n_head + hk) * hd + d] = v;
-    else {
-        uint16_t* slab = (is_k ? p.kslab : p.vslab) + (size_t)b * p.slab_stride + (size_t)pos * kvd + hk * hd + d;
-        *slab = p.bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
-    }
-}
-
-// Routed experts, gated half: softmax over all experts, top-k, then for every pick
-// h = silu(gate_e . x * s_g) * (up_e . x * s_u) (src/model/qwen35.rs:1626-1656, src/ops/mod.rs:1105-1117).
-// Every block redoes the (tiny) softmax + top-k so no grid-wide step separates routing from the experts.
-struct MoeGlu {
-    const float* router; int n_expert, n_used;      // [B][n_expert] logits
-    const int8_t* xq; const float* xs; int n_embd;  // quantised normed row [B][n_embd]
-    DevFp4 gate, up;
-    float* h;                                       // [B][n_used][ff]
-    int32_t* ids_out; float* w_out;                 // [B][n_used]
-};
-__global__ void __launch_bounds__(256) k_moe_glu(MoeGlu p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int RP = 4;
-    __shared__ float sval[32];
-    __shared__ int sidx[32];
-    __shared__ int32_t ids[16];
-    __shared__ float wts[16];
-    const int n = p.n_embd, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = p.gate.n_out;
-    const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5, lane = tid & 31;
-    float* probs = (float*)smem;                  // [n_expert]
-    int8_t* xq = (int8_t*)(probs + p.n_expert);
-    float* xs = (float*)(xq + n);
-    float* terms = xs + nb + wid * terms_floats(RP, gsh, nsb);
-    for (int i = tid; i < n / 16; i += blockDim.x) ((uint4*)xq)[i] = ((const uint4*)(p.xq + (size_t)b * n))[i];
-    for (int i = tid; i < nb; i += blockDim.x) xs[i] = p.xs[(size_t)b * nb + i];
-    // softmax (src/ops/naive.rs:362-376): max, exp, serial sum in index order, divide
-    const float* lg = p.router + (size_t)b * p.n_expert;
-    float mx = -INFINITY;
-    for (int i = tid; i < p.n_expert; i += blockDim.x) mx = fmaxf(mx, lg[i]);
-    mx = warp_max(mx);
-    if (lane == 0) sval[wid] = mx;
-    __syncthreads();
-    mx = sval[0];
-    for (int w = 1; w < nw; ++w) mx = fmaxf(mx, sval[w]);
-    __syncthreads();
-    for (int i = tid; i < p.n_expert; i += blockDim.x) probs[i] = exp_f(lg[i] - mx);
-    __syncthreads();
-    if (tid == 0) { float s = 0.0f; for (int i = 0; i < p.n_expert; ++i) s += probs[i]; sval[0] = s; }
-    __syncthreads();
-    float sum = sval[0];
-    __syncthreads();
-    for (int i = tid; i < p.n_expert; i += blockDim.x) probs[i] /= sum;
-    __syncthreads();
-    block_topk(probs, p.n_expert, p.n_used, ids, wts, sval, sidx);
-    if (blockIdx.x == 0 && tid < p.n_used) {
-        p.ids_out[(size_t)b * p.n_used + tid] = ids[tid];
-        p.w_out[(size_t)b * p.n_used + tid] = wts[tid];
-    }
-    int b0, b1, r0, r1;
-    share(p.n_used * ff, gridDim.x, blockIdx.x, b0, b1);
-    share(b1 - b0, nw, wid, r0, r1);
-    r0 += b0; r1 += b0;
-    for (int i = 0; i < p.n_used; ++i) {
-        int lo = max(r0, i * ff) - i * ff, hi = min(r1, (i + 1) * ff) - i * ff;
-        if (lo >= hi) continue;
-        int el = ids[i] - p.gate.expert_lo;
-        if (el < 0 || el >= p.gate.n_expert) continue;
-        float* h = p.h + ((size_t)b * p.n_used + i) * ff;
-        const size_t eo = (size_t)el * ff;
-        const bool has_g = p.gate.scale2 != nullptr, has_u = p.up.scale2 != nullptr;
-        const float sg2 = has_g ? p.gate.scale2[el] : 1.0f, su2 = has_u ? p.up.scale2[el] : 1.0f;
-        fp4_rows<RP>(p.gate.nib + eo * (n / 2), p.gate.sc + eo * nsb, n, lo, hi, xq, xs, terms, gsh,
-                     [&](int row, float v) { h[row] = has_g ? v * sg2 : v; });
-        fp4_rows<RP>(p.up.nib + eo * (n / 2), p.up.sc + eo * nsb, n, lo, hi, xq, xs, terms, gsh,
-                     [&](int row, float v) { float u = has_u ? v * su2 : v; h[row] = silu_f(h[row]) * u; });
-    }
-}
-static size_t moe_glu_smem(int n_expert, int n, int nw) {
-    int nb = n / 32, gsh = lanes_shift(nb);
-    return (size_t)n_expert * 4 + n + (size_t)nb * 4 + (size_t)nw * terms_floats(4, gsh, n / 16) * 4;
-}
-
-// Routed experts, second half, with the whole FFN tail fused: down projections of the picks, the shared
-// expert's SiLU gate and down projection, the weighted sum in pick order, the sigmoid-gated shared term
-// and the residual add (src/model/qwen35.rs:1659-1699, src/ops/mod.rs:1134-1171, src/model/qwen35.rs:1090).
-struct MoeDown {
-    const float* h; int n_used, ff;                // [B][n_used][ff]
-    const int32_t* ids; const float* wts;          // [B][n_used]
-    DevFp4 down;
-    const float* sg; const float* su; int sff;     // shared expert gate/up outputs [B][sff]
-    DevQ8 shared_down;
-    const float* logit;                            // [B]
-    float* x; int x_stride;                        // residual, [B][n_embd]
-    int local_only;                                // expert-parallel: write partial sums to `partial` instead
-    float* partial;
-};
-__global__ void __launch_bounds__(256) k_moe_down(MoeDown p) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int RP = 4;
-    const int ff = p.ff, sff = p.sff, nbf = ff / 32, nbs = sff / 32;
-    const int gf = lanes_shift(nbf), gs = lanes_shift(nbs);
-    const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5;
-    const int n_out = p.down.n_out;
-    float* hf = (float*)smem;                                   // [max(ff,sff)] staging
-    int8_t* hq = (int8_t*)(hf + max(ff, sff));                  // [n_used][ff]
-    float* hs = (float*)(hq + p.n_used * ff);                   // [n_used][nbf]
-    int8_t* sq = (int8_t*)(hs + p.n_used * nbf);                // [sff]
-    float* ss = (float*)(sq + sff);                             // [nbs]
-    int b0, b1, r0, r1;
-    share(n_out, gridDim.x, blockIdx.x, b0, b1);
-    float* acc = ss + nbs;                                      // [rows of this block]
-    int tf = max(terms_floats(RP, gf, ff / 16), terms_floats(RP, gs, nbs));
-    float* terms = acc + (b1 - b0 + 1) + wid * tf;
-    for (int i = 0; i < p.n_used; ++i) {
-        for (int k = tid; k < ff; k += blockDim.x) hf[k] = p.h[((size_t)b * p.n_used + i) * ff + k];
-        __syncthreads();
-        block_quant_q8(hf, ff, hq + i * ff, hs + i * nbf);
-    }
-    for (int k = tid; k < sff; k += blockDim.x) hf[k] = silu_f(p.sg[(size_t)b * sff + k]) * p.su[(size_t)b * sff + k];
-    __syncthreads();
-    block_quant_q8(hf, sff, sq, ss);
-    share(b1 - b0, nw, wid, r0, r1);
-    r0 += b0; r1 += b0;
-    const int lane = tid & 31;
-    for (int r = r0 + lane; r < r1; r += 32) acc[r - b0] = 0.0f;
-    __syncwarp();
-    const int nsb = ff / 16;
-    for (int i = 0; i < p.n_used; ++i) {
-        int el = p.ids[(size_t)b * p.n_used + i] - p.down.expert_lo;
-        if (el < 0 || el >= p.down.n_expert) continue;
-        const size_t eo = (size_t)el * n_out;
-        const bool has_s = p.down.scale2 != nullptr;
-        const float s2 = has_s ? p.down.scale2[el] : 1.0f, wt = p.wts[(size_t)b * p.n_used + i];
-        fp4_rows<RP>(p.down.nib + eo * (ff / 2), p.down.sc + eo * nsb, ff, r0, r1, hq + i * ff, hs + i * nbf, terms, gf,
-                     [&](int row, float v) { float o = has_s ? v * s2 : v; acc[row - b0] += wt * o; });
-        __syncwarp();
-    }
-    if (p.local_only) {
-        for (int r = r0 + lane; r < r1; r += 32) p.partial[(size_t)b * n_out + r] = acc[r - b0];
-        return;
-    }
-    const float g = sigmoid_f(p.logit[b]);
-    float* x = p.x + (size_t)b * p.x_stride;
-    q8_rows<RP>(p.shared_down, r0, r1, sq, ss, terms, gs, [&](int row, float v) {
-        float t = acc[row - b0];
-        t += v * g;
-        x[row] += t;
-    });
-}
-static size_t moe_down_smem(int n_used, int ff, int sff, int rows_per_block, int nw) {
-    int gf = lanes_shift(ff / 32), gs = lanes_shift(sff / 32);
-    int tf = std::max(terms_floats(4, gf, ff / 16), terms_floats(4, gs, sff / 32));
-    return (size_t)std::max(ff, sff) * 4 + (size_t)n_used * ff + (size_t)n_used * (ff / 32) * 4 + sff + (size_t)(sff / 32) * 4 +
-           (size_t)(rows_per_block + 2) * 4 + (size_t)nw * tf * 4 + 64;
-}
-
-__global__ void k_embed(const float* table, int n_embd, const int32_t* tokens, float* x) {
-    int b = blockIdx.x;
-    const float* row = table + (size_t)tokens[b] * n_embd;
-    for (int i = threadIdx.x; i < n_embd; i += blockDim.x) x[(size_t)b * n_embd + i] = row[i];
-}
-
-// Greedy argmax with strict '>' (lowest index wins, src/profile.rs:192-213), feeding the choice back as the
-// next input token and advancing the position. One block per sequence.
-__global__ void k_argmax_advance(const float* logits, int n_vocab, int32_t* tokens, int* pos, int32_t* next_out,
-                                 int32_t* history, int* step_counter, int n_seq) {
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
-    const float* l = logits + (size_t)b * n_vocab;
-    float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int i = tid; i < n_vocab; i += blockDim.x) { float v = l[i]; if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; } }
-    for (int o = 16; o > 0; o >>= 1) {
-        float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
-    }
-    if (lane == 0) { sv[wid] = bv; si[wid] = bi; }
-    __syncthreads();
-    if (tid == 0) {
-        for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
-            if (si[w] != 0x7fffffff && (bi == 0x7fffffff || sv[w] > bv || (sv[w] == bv && si[w] < bi))) { bv = sv[w]; bi = si[w]; }
-        tokens[b] = bi;
-        next_out[b] = bi;
-        pos[b] += 1;
-        if (history) history[(size_t)step_counter[0] * n_seq + b] = bi;
-    }
-    if (b == 0 && tid == 0 && history) { __threadfence(); }
-}
-__global__ void k_bump(int* counter) { counter[0] += 1; }
+#include "itb_fused.cuh"
 
 // =====================================================================================================
 // Model
@@ -497,7 +70,7 @@ extern "C" int itb_model_create(itb_ctx* c, const itb_model_dims* d, itb_model**
     if (d->n_expert_used == 0 || d->n_expert_used > d->n_expert || d->n_expert_used > 16) return bad("expert_used_count out of range");
     if (d->n_embd % 64 || d->expert_ff % 64 || d->shared_ff % 32 || d->ssm_d_inner % 32 || (d->head_dim * d->n_head) % 32) return bad("dimensions must be whole quantisation blocks");
     if (d->head_dim != 64 && d->head_dim != 128 && d->head_dim != 256) return bad("head_dim must be 64, 128 or 256");
-    if (d->ssm_d_state > 128 || d->ssm_d_conv < 2 || d->ssm_d_conv > 8 || d->n_expert > 1024) return bad("dimension beyond what the kernels hold");
+    if ((d->ssm_d_state != 64 && d->ssm_d_state != 128) || d->ssm_d_conv < 2 || d->ssm_d_conv > 8 || d->n_expert > 1024) return bad("dimension beyond what the kernels hold");
     itb_model* m = new itb_model();
     m->c = c; m->d = *d;
     *out = m;
@@ -726,6 +299,8 @@ struct itb_engine {
     int8_t* xq = nullptr; float* xs = nullptr;
     int32_t* route_ids = nullptr; float* route_w = nullptr;  // [n_layer][B][n_used]
     int32_t* history = nullptr; int* step_counter = nullptr; uint32_t history_cap = 0;
+    int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr;
+    int8_t *aq = nullptr, *hq = nullptr, *sq = nullptr; float *as = nullptr, *hs = nullptr, *ss = nullptr;  // producer-quantised activations
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
     int n_split = 1;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
@@ -736,6 +311,27 @@ struct itb_engine {
     std::vector<void*> allocs;
 };
 
+// Per-launch CUDA-event timing of one eagerly launched step, grouped by kernel class.
+enum KClass { KC_EMBED, KC_GDN_IN, KC_GDN_CORE, KC_OUT_PROJ, KC_ATTN_IN, KC_ATTN_PREP, KC_ATTN, KC_FFN_IN, KC_MOE_GLU, KC_MOE_DOWN,
+              KC_LM_HEAD, KC_ARGMAX, KC_COUNT };
+static const char* const KC_NAMES[KC_COUNT] = {"k_embed", "k_in_proj[gdn]", "k_gdn_core", "k_out_proj", "k_in_proj[attn]", "k_attn_prep",
+                                               "k_attn_partial+combine", "k_in_proj[ffn]", "k_moe_glu", "k_moe_down",
+                                               "k_in_proj[lm_head]", "k_argmax_advance"};
+struct StepProf {
+    std::vector<cudaEvent_t> ev;
+    std::vector<int> cls;
+    std::vector<uint64_t> bytes;
+    void mark(int c, uint64_t b, cudaStream_t st) {
+        cudaEvent_t e; cudaEventCreate(&e); cudaEventRecord(e, st);
+        ev.push_back(e); cls.push_back(c); bytes.push_back(b);
+    }
+};
+// Keeps the stream busy for a bounded time so a whole step can be queued behind it and then run back to back.
+__global__ void k_hold(long long cycles) {
+    long long t0 = clock64();
+    while (clock64() - t0 < cycles) {}
+}
+
 template <class T>
 static bool dalloc(itb_engine* e, T** p, size_t count) {
     if (cudaMalloc((void**)p, std::max<size_t>(count, 1) * sizeof(T)) != cudaSuccess) return itb_fail_msg(e->c, "engine: out of device memory");
@@ -744,24 +340,42 @@ static bool dalloc(itb_engine* e, T** p, size_t count) {
     return true;
 }
 
-static void set_smem(const void* fn, size_t bytes) { cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes); }
+static void set_smem(const void* fn, size_t bytes) {
+    cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) fprintf(stderr, "[itb] cudaFuncSetAttribute(%zu bytes) failed: %s\n", bytes, cudaGetErrorString(e));
+}
 
 // One decode step for all B sequences, enqueued on `st`.
-static void enqueue_step(itb_engine* e, cudaStream_t st) {
+static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
     const itb_model_dims& d = m->d;
     const int B = e->B, H = d.n_embd, sms = c->sm_count;
     const int key_dim = d.ssm_d_state * d.ssm_n_group, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
     const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv;
-    const int NW_IN = 9, NW = 8;
+    const int TPB = NWG * 32;
     uint64_t launches = 0;
-    k_embed<<<B, 256, 0, st>>>(m->tok_embd.w, H, e->tokens, e->x); launches++;
-    const size_t smem_in = in_proj_smem(H, NW_IN);
-    set_smem((const void*)k_in_proj, smem_in);
+    auto q8b = [](uint64_t a, uint64_t b) { return a * b / 32 * 34; };
+    auto f4b = [](uint64_t a, uint64_t b) { return a * b / 64 * 36; };
+#define MARK(cls, by) do { launches++; if (prof) prof->mark((cls), (uint64_t)(by), st); } while (0)
+    // grid for a row-streaming kernel: about two rows per warp and pass, one block of 16 warps per SM
+    auto grid_rows = [&](int rows) { return std::max(1, std::min(sms, (rows + 2 * NWG - 1) / (2 * NWG))); };
+    const size_t smem_in = in_proj_smem(H, c->exact);
+    static bool attrs_set = false;
+    if (!attrs_set) {
+        set_smem((const void*)k_in_proj, 100 * 1024); set_smem((const void*)k_out_proj, 100 * 1024);
+        set_smem((const void*)k_moe_glu, 100 * 1024);
+        set_smem((const void*)k_moe_down<1>, 100 * 1024); set_smem((const void*)k_moe_down<2>, 100 * 1024);
+        set_smem((const void*)k_moe_down<4>, 100 * 1024); set_smem((const void*)k_moe_down<8>, 100 * 1024);
+        set_smem((const void*)k_gdn_core<128>, 100 * 1024); set_smem((const void*)k_gdn_core<64>, 100 * 1024);
+        attrs_set = true;
+    }
+    if (prof) prof->mark(-1, 0, st);
+    k_embed<<<B, 256, 0, st>>>(m->tok_embd.w, H, e->tokens, e->x); MARK(KC_EMBED, (uint64_t)B * H * 8);
     for (uint32_t il = 0; il < d.n_layer; ++il) {
         const DevLayer& L = m->layers[il];
         if (L.recurrent) {
             int rs = e->slot_of[il];
+            size_t state_stride = (size_t)d.ssm_dt_rank * d.ssm_d_state * d.ssm_d_state;
             InProj p{};
             p.x = e->x; p.x_stride = H; p.norm_w = L.attn_norm; p.eps = d.rms_eps; p.n_embd = H;
             p.nq = 2; p.q[0] = L.wqkv; p.qout[0] = e->qkvc; p.qstride[0] = cd; p.q[1] = L.wgate; p.qout[1] = e->z; p.qstride[1] = vd;
@@ -770,21 +384,21 @@ static void enqueue_step(itb_engine* e, cudaStream_t st) {
             p.conv_w = L.conv1d; p.conv_kernel = d.ssm_d_conv; p.conv_state_stride = (size_t)cd * (d.ssm_d_conv - 1);
             p.conv_state = e->conv_state + (size_t)rs * B * p.conv_state_stride;
             p.exact = c->exact;
-            int gx = std::min(sms, std::max(1, (cd + vd) / 8));
-            k_in_proj<<<dim3(gx, B), NW_IN * 32, smem_in, st>>>(p); launches++;
+            k_in_proj<<<dim3(grid_rows(cd + vd), B), TPB, smem_in, st>>>(p);
+            MARK(KC_GDN_IN, q8b(H, cd) + q8b(H, vd) + 2ull * H * d.ssm_dt_rank * 4 + (uint64_t)cd * d.ssm_d_conv * 4 +
+                                (uint64_t)B * (2ull * cd * (d.ssm_d_conv - 1) * 4 + (H + cd + vd) * 4));
             GdnCore g{};
             g.conv = e->qkvc; g.conv_stride = cd; g.z = e->z; g.alpha = e->alpha; g.beta = e->beta;
             g.ssm_a = L.ssm_a; g.dt_bias = L.dt_bias; g.ssm_norm = L.ssm_norm;
-            g.state_stride = (size_t)d.ssm_dt_rank * d.ssm_d_state * d.ssm_d_state;
-            g.state = e->ssm_state + (size_t)rs * B * g.state_stride;
-            g.out = e->zc; g.sk = d.ssm_d_state; g.sv = d.ssm_d_state; g.n_k = d.ssm_n_group; g.n_v = d.ssm_dt_rank; g.eps = d.rms_eps;
+            g.state_stride = state_stride; g.state = e->ssm_state + (size_t)rs * B * state_stride;
+            g.out_q = e->aq; g.out_s = e->as; g.sk = d.ssm_d_state; g.sv = d.ssm_d_state; g.n_k = d.ssm_n_group; g.n_v = d.ssm_dt_rank; g.eps = d.rms_eps;
             size_t smem_g = (size_t)(g.sv * (g.sk + 1) + 2 * g.sk + g.sv) * 4;
-            set_smem((const void*)k_gdn_core, smem_g);
-            k_gdn_core<<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g); launches++;
-            OutProj o{e->zc, vd, vd, L.ssm_out, e->x, H};
-            size_t smem_o = out_proj_smem(vd, NW);
-            set_smem((const void*)k_out_proj, smem_o);
-            k_out_proj<<<dim3(std::min(sms, std::max(1, H / 8)), B), NW * 32, smem_o, st>>>(o); launches++;
+            if (d.ssm_d_state == 128) k_gdn_core<128><<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g);
+            else k_gdn_core<64><<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g);
+            MARK(KC_GDN_CORE, (uint64_t)B * (2ull * g.state_stride * 4 + (cd + 2ull * vd) * 4));
+            OutProj o{e->aq, e->as, vd, L.ssm_out, e->x, H};
+            k_out_proj<<<dim3(grid_rows(H), B), TPB, out_proj_smem(vd), st>>>(o);
+            MARK(KC_OUT_PROJ, q8b(vd, H) + (uint64_t)B * (vd + 2ull * H) * 4);
         } else {
             int as = e->slot_of[il];
             InProj p{};
@@ -792,28 +406,40 @@ static void enqueue_step(itb_engine* e, cudaStream_t st) {
             p.nq = 3; p.q[0] = L.wq; p.qout[0] = e->qg; p.qstride[0] = 2 * qd; p.q[1] = L.wk; p.qout[1] = e->kbuf; p.qstride[1] = kvd;
             p.q[2] = L.wv; p.qout[2] = e->vbuf; p.qstride[2] = kvd;
             p.exact = c->exact;
-            int gx = std::min(sms, std::max(1, (2 * qd + 2 * kvd) / 8));
-            k_in_proj<<<dim3(gx, B), NW_IN * 32, smem_in, st>>>(p); launches++;
+            k_in_proj<<<dim3(grid_rows(2 * qd + 2 * kvd), B), TPB, smem_in, st>>>(p);
+            MARK(KC_ATTN_IN, q8b(H, 2 * qd) + 2 * q8b(H, kvd) + (uint64_t)B * (H + 2ull * qd + 2ull * kvd) * 4);
             AttnPrep a{};
             a.qg = e->qg; a.k = e->kbuf; a.v = e->vbuf; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.q_out = e->qn; a.g_out = e->gate;
             a.slab_stride = (size_t)e->n_ctx * kvd;
             a.kslab = e->kslab + (size_t)as * B * a.slab_stride; a.vslab = e->vslab + (size_t)as * B * a.slab_stride;
             a.pos = e->pos; a.npos_out = e->npos; a.hd = d.head_dim; a.n_head = d.n_head; a.n_head_kv = d.n_head_kv; a.n_rot = d.n_rot;
             a.theta = d.rope_theta; a.eps = d.rms_eps; a.bf16 = c->kv_bf16;
-            k_attn_prep<<<dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st>>>(a); launches++;
-            // one launch per sequence: each has its own slab and position
+            k_attn_prep<<<dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st>>>(a);
+            MARK(KC_ATTN_PREP, (uint64_t)B * (4ull * qd + 3ull * kvd) * 4);
+            // split-K partials, one launch per sequence (own slab, own position), then one combine for all
+            const float scale = 1.0f / sqrtf((float)d.head_dim);
+            const int nwa = 8;
+            const size_t smem_a = (size_t)nwa * 8 * 2 * 4 + (size_t)nwa * 8 * d.head_dim * 4;
             for (int b = 0; b < B; ++b) {
                 size_t po = (size_t)b * d.n_head * e->n_split;
-                itb_attend_dev(c, st, e->qn + (size_t)b * qd, a.kslab + (size_t)b * a.slab_stride, a.vslab + (size_t)b * a.slab_stride, kvd, 0, 1,
-                               d.head_dim, d.n_head, d.n_head_kv, 1.0f / sqrtf((float)d.head_dim), c->kv_bf16, e->npos + b,
-                               e->gate + (size_t)b * qd, e->part_acc + po * d.head_dim, e->part_ml + po * 2, e->n_split,
-                               e->att + (size_t)b * qd);
-                launches += 2; c->launches -= 2;
+                dim3 grid(d.n_head_kv, 1, e->n_split);
+#define ATT_CASE(HD)                                                                                                             \
+    case HD:                                                                                                                      \
+        set_smem((const void*)k_attn_partial<HD, 8>, smem_a);                                                                     \
+        k_attn_partial<HD, 8><<<grid, nwa * 32, smem_a, st>>>(e->qn + (size_t)b * qd, a.kslab + (size_t)b * a.slab_stride,        \
+            a.vslab + (size_t)b * a.slab_stride, kvd, 0, 1, d.n_head, d.n_head_kv, scale, c->kv_bf16, e->npos + b,                 \
+            e->part_acc + po * d.head_dim, e->part_ml + po * 2);                                                                  \
+        break;
+                switch (d.head_dim) { ATT_CASE(64) ATT_CASE(128) ATT_CASE(256) }
+#undef ATT_CASE
+                MARK(KC_ATTN, 2ull * kvd * 2 * (e->host_pos[b] + 1) + 3ull * qd * 4);
             }
-            OutProj o{e->att, qd, qd, L.wo, e->x, H};
-            size_t smem_o = out_proj_smem(qd, NW);
-            set_smem((const void*)k_out_proj, smem_o);
-            k_out_proj<<<dim3(std::min(sms, std::max(1, H / 8)), B), NW * 32, smem_o, st>>>(o); launches++;
+            k_attn_combine_q<<<B * d.n_head, d.head_dim, 0, st>>>(e->part_acc, e->part_ml, e->n_split, d.head_dim, e->gate, e->npos,
+                                                                  d.n_head, e->aq, e->as);
+            MARK(KC_ATTN, 0);
+            OutProj o{e->aq, e->as, qd, L.wo, e->x, H};
+            k_out_proj<<<dim3(grid_rows(H), B), TPB, out_proj_smem(qd), st>>>(o);
+            MARK(KC_OUT_PROJ, q8b(qd, H) + (uint64_t)B * (qd + 2ull * H) * 4);
         }
         // routed FFN
         InProj f{};
@@ -822,30 +448,41 @@ static void enqueue_step(itb_engine* e, cudaStream_t st) {
         f.nf = 2; f.f[0] = L.gate_inp; f.fout[0] = e->router; f.fstride[0] = d.n_expert;
         f.f[1] = L.shared_gate_inp; f.fout[1] = e->shlogit; f.fstride[1] = 1;
         f.xq_out = e->xq; f.xs_out = e->xs; f.exact = c->exact;
-        int units = c->exact ? (d.n_expert + 31) / 32 + 1 : (d.n_expert + 3) / 4 + 1;
-        int gxf = std::min(sms, std::max(units, (int)(2 * d.shared_ff) / 8));
-        k_in_proj<<<dim3(gxf, B), NW_IN * 32, smem_in, st>>>(f); launches++;
+        int gxf = c->exact ? std::max((int)(d.n_expert + 31) / 32 + 1, grid_rows(2 * d.shared_ff))
+                           : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));
+        k_in_proj<<<dim3(gxf, B), TPB, smem_in, st>>>(f);
+        MARK(KC_FFN_IN, (uint64_t)H * d.n_expert * 4 + 2 * q8b(H, d.shared_ff) + (uint64_t)H * 4 + (uint64_t)B * (2ull * H + d.n_expert + 2ull * d.shared_ff) * 4);
         MoeGlu g{};
         g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
-        g.gate = L.gate; g.up = L.up; g.h = e->h;
+        g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
+        g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * B * d.n_expert_used; g.w_out = e->route_w + (size_t)il * B * d.n_expert_used;
-        size_t smem_g = moe_glu_smem(d.n_expert, H, NW);
-        set_smem((const void*)k_moe_glu, smem_g);
-        k_moe_glu<<<dim3(std::min(sms, std::max(1, (int)(d.n_expert_used * d.expert_ff) / 8)), B), NW * 32, smem_g, st>>>(g); launches++;
+        k_moe_glu<<<dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st>>>(g);
+        MARK(KC_MOE_GLU, (uint64_t)B * (2ull * d.n_expert_used * f4b(H, d.expert_ff) + (uint64_t)d.n_expert_used * d.expert_ff * 4));
         MoeDown w{};
-        w.h = e->h; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
-        w.sg = e->sg; w.su = e->su; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
-        int gxd = std::min(sms, std::max(1, H / 8));
-        size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, (H + gxd - 1) / gxd + 1, NW);
-        set_smem((const void*)k_moe_down, smem_d);
-        k_moe_down<<<dim3(gxd, B), NW * 32, smem_d, st>>>(w); launches++;
+        w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
+        w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
+        {
+            int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
+            int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+            dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), B);
+            size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
+            if (rp == 1) k_moe_down<1><<<grid, TPB, smem_d, st>>>(w);
+            else if (rp == 2) k_moe_down<2><<<grid, TPB, smem_d, st>>>(w);
+            else if (rp == 4) k_moe_down<4><<<grid, TPB, smem_d, st>>>(w);
+            else k_moe_down<8><<<grid, TPB, smem_d, st>>>(w);
+        }
+        MARK(KC_MOE_DOWN, (uint64_t)B * d.n_expert_used * f4b(d.expert_ff, H) + q8b(d.shared_ff, H) + (uint64_t)B * ((uint64_t)d.n_expert_used * d.expert_ff + 2ull * H) * 4);
     }
     InProj hp{};
     hp.x = e->x; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
     hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
-    k_in_proj<<<dim3(std::min(sms * 2, std::max(1, (int)d.n_vocab / 8)), B), NW_IN * 32, smem_in, st>>>(hp); launches++;
-    k_argmax_advance<<<B, 1024, 0, st>>>(e->logits, d.n_vocab, e->tokens, e->pos, e->next, e->history, e->step_counter, B); launches++;
-    k_bump<<<1, 1, 0, st>>>(e->step_counter); launches++;
+    k_in_proj<<<dim3(grid_rows(d.n_vocab), B), TPB, smem_in, st>>>(hp);
+    MARK(KC_LM_HEAD, q8b(H, d.n_vocab) + (uint64_t)B * (H + d.n_vocab) * 4);
+    k_argmax_partial<<<dim3(ARGMAX_PARTS, B), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
+    k_argmax_advance<<<B, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, e->step_counter, B);
+    MARK(KC_ARGMAX, (uint64_t)B * d.n_vocab * 4);
+#undef MARK
     e->launches_per_step = launches;
 }
 
@@ -879,7 +516,10 @@ extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, i
               dalloc(E, &e->h, B * d.n_expert_used * d.expert_ff) && dalloc(E, &e->logits, B * d.n_vocab) &&
               dalloc(E, &e->xq, B * H) && dalloc(E, &e->xs, B * H / 32) &&
               dalloc(E, &e->route_ids, (size_t)d.n_layer * B * d.n_expert_used) && dalloc(E, &e->route_w, (size_t)d.n_layer * B * d.n_expert_used) &&
-              dalloc(E, &e->step_counter, 1);
+              dalloc(E, &e->step_counter, B) && dalloc(E, &e->err, 1) && dalloc(E, &e->arg_v, B * ARGMAX_PARTS) && dalloc(E, &e->arg_i, B * ARGMAX_PARTS) &&
+              dalloc(E, &e->aq, B * std::max(vd, qd)) && dalloc(E, &e->as, B * std::max(vd, qd) / 32) &&
+              dalloc(E, &e->hq, B * d.n_expert_used * d.expert_ff) && dalloc(E, &e->hs, B * d.n_expert_used * d.expert_ff / 32) &&
+              dalloc(E, &e->sq, B * d.shared_ff) && dalloc(E, &e->ss, B * d.shared_ff / 32);
     if (!ok) { for (void* p : e->allocs) cudaFree(p); return 1; }
     e->host_pos.assign(B, 0);
     cudaEventCreate(&e->ev0); cudaEventCreate(&e->ev1);
@@ -933,6 +573,14 @@ static bool ensure_graph(itb_engine* e) {
     return true;
 }
 
+// A kernel that gave up waiting for its staged weights sets the flag; turn it into the sticky error.
+static bool check_flag(itb_engine* e) {
+    int f = 0;
+    if (cudaMemcpy(&f, e->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return itb_fail_msg(e->c, "engine: cannot read the device status word");
+    if (f) { cudaMemset(e->err, 0, 4); return itb_fail_msg(e->c, "engine: a kernel gave up waiting for staged weights (bounded wait ran out)"); }
+    return true;
+}
+
 static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
     itb_ctx* c = e->c;
     if (!ensure_graph(e)) return false;
@@ -958,7 +606,7 @@ extern "C" int itb_engine_decode(itb_engine* e, const uint32_t* tokens, float* l
     if (logits_out) cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->m->d.n_vocab * 4, cudaMemcpyDeviceToHost, st);
     ITB_CUDA_RET(c, cudaStreamSynchronize(st), 1);
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
-    return 0;
+    return check_flag(e) ? 0 : 1;
 }
 
 extern "C" int itb_engine_decode_loop(itb_engine* e, const uint32_t* first, uint32_t steps, uint32_t* tokens_out) {
@@ -973,12 +621,12 @@ extern "C" int itb_engine_decode_loop(itb_engine* e, const uint32_t* first, uint
         e->history_cap = steps;
     }
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, first, e->B * 4, cudaMemcpyHostToDevice, st), 1);
-    cudaMemsetAsync(e->step_counter, 0, 4, st);
+    cudaMemsetAsync(e->step_counter, 0, e->B * 4, st);
     if (!run_steps(e, steps, true)) return 1;
     if (tokens_out) cudaMemcpyAsync(tokens_out, e->history, (size_t)steps * e->B * 4, cudaMemcpyDeviceToHost, st);
     ITB_CUDA_RET(c, cudaStreamSynchronize(st), 1);
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
-    return 0;
+    return check_flag(e) ? 0 : 1;
 }
 
 // Prefill, token by token through the decode graph: the state left behind and the last logits are those of
@@ -1011,7 +659,7 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
     if (logits_out) cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->m->d.n_vocab * 4, cudaMemcpyDeviceToHost, st);
     ITB_CUDA_RET(c, cudaStreamSynchronize(st), 1);
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
-    return 0;
+    return check_flag(e) ? 0 : 1;
 }
 
 // src/engine/mod.rs:399-437 for sequence 0 of a single-sequence engine.
@@ -1045,5 +693,37 @@ extern "C" int itb_engine_read_ssm_state(itb_engine* e, uint32_t seq, uint32_t i
     if (len != per) { itb_fail_msg(e->c, "read_ssm_state: wrong length"); return 1; }
     ITB_CUDA_RET(e->c, cudaStreamSynchronize(e->c->stream), 1);
     ITB_CUDA_RET(e->c, cudaMemcpy(out, e->ssm_state + ((size_t)e->slot_of[il] * e->B + seq) * per, per * 4, cudaMemcpyDeviceToHost), 1);
+    return 0;
+}
+
+// One eagerly launched step (no graph) with an event after every launch. The stream is first held busy for
+// about a millisecond so the whole step is queued before it starts and the kernels run back to back, as they
+// do under the graph. Fills per-class launch counts, summed milliseconds and summed algorithmic bytes.
+extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, itb_kernel_stat* out, size_t cap, size_t* n_out) {
+    itb_ctx* c = e->c;
+    cudaStream_t st = c->stream;
+    for (uint32_t b = 0; b < e->B; ++b)
+        if (e->host_pos[b] + 1 > e->n_ctx) { itb_fail_msg(c, "context overflow: the step would write past n_ctx"); return 1; }
+    if (!ensure_graph(e)) return 1;  // function attributes are set during capture
+    ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
+    StepProf prof;
+    k_hold<<<1, 1, 0, st>>>(3000000LL);
+    enqueue_step(e, st, &prof);
+    cudaError_t err = cudaStreamSynchronize(st);
+    if (err != cudaSuccess) { itb_fail(c, "profile_step", err); return 1; }
+    c->launches += e->launches_per_step;
+    for (uint32_t b = 0; b < e->B; ++b) e->host_pos[b] += 1;
+    std::vector<itb_kernel_stat> acc(KC_COUNT);
+    for (int k = 0; k < KC_COUNT; ++k) { memset(&acc[k], 0, sizeof acc[k]); snprintf(acc[k].name, sizeof acc[k].name, "%s", KC_NAMES[k]); }
+    for (size_t i = 1; i < prof.ev.size(); ++i) {
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, prof.ev[i - 1], prof.ev[i]);
+        int k = prof.cls[i];
+        acc[k].launches++; acc[k].ms += ms; acc[k].bytes += prof.bytes[i];
+    }
+    for (auto ev : prof.ev) cudaEventDestroy(ev);
+    size_t n = std::min<size_t>(cap, KC_COUNT);
+    for (size_t k = 0; k < n; ++k) out[k] = acc[k];
+    if (n_out) *n_out = n;
     return 0;
 }

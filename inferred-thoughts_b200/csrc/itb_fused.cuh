@@ -1,0 +1,586 @@
+// Fused decode kernels of the engine: one kernel per dependent stage of a layer, written lean -- small loop
+// bodies, 16 warps per block, prologues done once, and every activation quantised to Q8_0 by the kernel
+// that produces it (the consumer's matmul would quantise it the same way, src/ops/naive.rs:49-56).
+#pragma once
+#include "itb_kernels.cuh"
+
+namespace {
+
+constexpr int RPG = 2;          // row groups per pass in the streaming GEMVs
+constexpr int NWG = 16;         // warps per block in the GEMV kernels
+constexpr int CONV_CAP = 8;     // rows per warp whose conv window and taps are fetched ahead (8 floats each)
+
+// ------------------------------------------------------------------------------------------------------
+// Input projections: RMSNorm + Q8_0 quantise prologue, then up to three Q8_0 matrices and two F32 matrices
+// against the same row (src/model/qwen35.rs:1010, :1167-1179, :1262-1273, :1626). With conv_w set, rows of
+// q[0] go through the depthwise causal conv (src/ops/naive.rs:275-315) in the epilogue -- the lane that owns
+// a row also advances that channel's window -- and the PRE-activation sum is stored: the consumer applies SiLU.
+struct InProj {
+    const float* x; int x_stride;                 // [B][n_embd] residual stream
+    const float* norm_w; float eps; int n_embd;
+    int nq; DevQ8 q[3]; float* qout[3]; int qstride[3];
+    int nf; DevF32 f[2]; float* fout[2]; int fstride[2];
+    const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
+    int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
+    int exact;
+};
+
+__global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int n = p.n_embd, nb = n / 32, gsh = lanes_shift(nb);
+    const int b = blockIdx.y, wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    double* red = (double*)smem;
+    float* xn = (float*)(red + 32);
+    int8_t* xq = (int8_t*)(xn + n);
+    float* xs = (float*)(xq + n);
+    float* tile = xs + nb;                                        // 32*33 floats, serial-k F32 mode only
+    const int tfl = terms_floats(RPG, gsh, nb);
+    float* terms = tile + (p.exact ? 32 * 33 : 0) + wid * (tfl + CONV_CAP * 8);
+    float* cpre = terms + tfl;
+
+    // this warp's share of the concatenated Q8_0 rows
+    int total = 0;
+    for (int m = 0; m < p.nq; ++m) total += p.q[m].n_out;
+    int b0, b1, r0, r1;
+    share(total, gridDim.x, blockIdx.x, b0, b1);
+    share(b1 - b0, nw, wid, r0, r1);
+    r0 += b0; r1 += b0;
+    const int keep = p.conv_kernel - 1;
+    int conv_lo = 0;
+    if (p.conv_w && r0 < min(r1, p.q[0].n_out)) {
+        // conv window and taps of the rows this warp will finish, fetched before anything depends on them
+        const int nr = min(min(r1, p.q[0].n_out) - r0, CONV_CAP);
+        const float* cs = p.conv_state + (size_t)b * p.conv_state_stride + (size_t)r0 * keep;
+        const float* cw = p.conv_w + (size_t)r0 * p.conv_kernel;
+        for (int i = lane; i < nr * keep; i += 32) cpre[(i / keep) * 8 + i % keep] = cs[i];
+        for (int i = lane; i < nr * p.conv_kernel; i += 32) cpre[(i / p.conv_kernel) * 8 + keep + i % p.conv_kernel] = cw[i];
+        conv_lo = r0;
+    }
+    block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
+    block_quant_q8(xn, n, xq, xs);
+    if (p.xq_out && blockIdx.x == 0) {
+        for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
+        for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
+    }
+    int base = 0;
+#pragma unroll 1
+    for (int m = 0; m < p.nq; ++m) {
+        const int lo = max(r0, base) - base, hi = min(r1, base + p.q[m].n_out) - base;
+        if (lo < hi) {
+            float* o = p.qout[m] + (size_t)b * p.qstride[m];
+            if (m == 0 && p.conv_w) {
+                float* cs = p.conv_state + (size_t)b * p.conv_state_stride;
+                const float* cw = p.conv_w;
+                const int kernel = p.conv_kernel;
+                q8_rows<RPG>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) {
+                    float* past = cs + (size_t)row * keep;
+                    const bool pre = row - conv_lo < CONV_CAP;
+                    const float* pin = pre ? cpre + (row - conv_lo) * 8 : past;
+                    const float* w = pre ? cpre + (row - conv_lo) * 8 + keep : cw + (size_t)row * kernel;
+                    float sum = 0.0f;
+                    for (int k = 0; k < keep; ++k) sum += pin[k] * w[k];
+                    sum += v * w[keep];
+                    o[row] = sum;
+                    for (int k = 0; k + 1 < keep; ++k) past[k] = pin[k + 1];
+                    past[keep - 1] = v;
+                });
+            } else {
+                q8_rows<RPG>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) { o[row] = v; });
+            }
+        }
+        base += p.q[m].n_out;
+    }
+    // F32 rows. Serial-k mode: units of 32 rows, unit u on warp 0 of block u (it owns the tile). Otherwise one
+    // row per warp, handed out from the far end of the grid's warps.
+    if (p.exact) {
+        if (wid == 0) {
+            int ubase = 0;
+#pragma unroll 1
+            for (int m = 0; m < p.nf; ++m) {
+                int units = (p.f[m].n_out + 31) / 32;
+                float* o = p.fout[m] + (size_t)b * p.fstride[m];
+                for (int u = (int)blockIdx.x - ubase; u < units; u += gridDim.x) {
+                    if (u < 0) continue;
+                    f32_rows<true>(p.f[m].w, n, u * 32, min(p.f[m].n_out, u * 32 + 32), xn, tile, [&](int row, float v) { o[row] = v; });
+                }
+                ubase = (ubase + units) % gridDim.x;
+            }
+        }
+    } else {
+        const int ngw = gridDim.x * nw, gw = ngw - 1 - (blockIdx.x * nw + wid);
+        int rbase = 0;
+#pragma unroll 1
+        for (int m = 0; m < p.nf; ++m) {
+            float* o = p.fout[m] + (size_t)b * p.fstride[m];
+            for (int r = gw - rbase; r < p.f[m].n_out; r += ngw) {
+                if (r < 0) continue;
+                f32_rows<false>(p.f[m].w, n, r, r + 1, xn, tile, [&](int row, float v) { o[row] = v; });
+            }
+            rbase = (rbase + p.f[m].n_out) % ngw;
+        }
+    }
+}
+size_t in_proj_smem(int n, int exact) {
+    int nb = n / 32, gsh = lanes_shift(nb);
+    return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (terms_floats(RPG, gsh, nb) + CONV_CAP * 8) * 4 + 64;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Output projection with the residual add fused: x[b] += W . a[b], the activation arriving already quantised
+// (src/model/qwen35.rs:1017, :1220, :1325).
+struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; };
+__global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
+    const int b = blockIdx.y, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    int8_t* aq = (int8_t*)smem;
+    float* as = (float*)(aq + n);
+    float* terms = as + nb + wid * terms_floats(RPG, gsh, nb);
+    for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) as[i] = p.as[(size_t)b * nb + i];
+    __syncthreads();
+    int b0, b1, r0, r1;
+    share(p.w.n_out, gridDim.x, blockIdx.x, b0, b1);
+    share(b1 - b0, nw, wid, r0, r1);
+    float* x = p.x + (size_t)b * p.x_stride;
+    q8_rows<RPG>(p.w, b0 + r0, b0 + r1, aq, as, terms, gsh, [&](int row, float v) { x[row] += v; });
+}
+size_t out_proj_smem(int n) {
+    int nb = n / 32, gsh = lanes_shift(nb);
+    return (size_t)n + (size_t)nb * 4 + (size_t)NWG * terms_floats(RPG, gsh, nb) * 4 + 64;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// GatedDeltaNet core for one (value head, sequence): SiLU of the conv sums, l2-norm of q and k, gated delta
+// rule over the head's [sv][sk] state, gated RMSNorm, the SiLU(z) gate, and the Q8_0 quantisation the output
+// projection would apply (src/model/qwen35.rs:1280-1325, src/ops/naive.rs:86-135, :254-273). One thread per
+// value row, keys walked serially so every sum has the CPU's order.
+struct GdnCore {
+    const float* conv; int conv_stride;           // [B][conv_dim] = q | k | v conv sums (pre-SiLU)
+    const float* z; const float* alpha; const float* beta;
+    const float* ssm_a; const float* dt_bias; const float* ssm_norm;
+    float* state; size_t state_stride;
+    int8_t* out_q; float* out_s;                  // [B][value_dim] int8, [B][value_dim/32] scales
+    int sk, sv, n_k, n_v; float eps;
+};
+template <int SK>
+__global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int sk = SK, sv = SK, LD = SK * SK / 4 / 256;   // float4 loads per thread
+    const int h = blockIdx.x, b = blockIdx.y, kh = h % p.n_k, tid = threadIdx.x;
+    const int lane = tid & 31, wid = tid >> 5;
+    float* S = (float*)smem;                 // [sv][sk+1]
+    float* kq = S + sv * (sk + 1);           // k[sk] | q[sk]
+    float* o = kq + 2 * sk;                  // [sv]
+    __shared__ double red2[8];
+    const int key_dim = p.n_k * sk;
+    const float* cv = p.conv + (size_t)b * p.conv_stride;
+    float* sg = p.state + (size_t)b * p.state_stride + (size_t)h * sv * sk;
+    float4 ld[LD];
+#pragma unroll
+    for (int i = 0; i < LD; ++i) ld[i] = __ldcs((const float4*)sg + tid + i * 256);
+    // SiLU of this head's conv sums: threads [0, 2*sk) take k then q, threads [0, sv) their v element later
+    if (tid < 2 * sk) kq[tid] = silu_f(cv[(tid < sk ? key_dim : 0) + kh * sk + (tid < sk ? tid : tid - sk)]);
+    float vj = 0.0f;
+    if (tid < sv) vj = silu_f(cv[2 * key_dim + h * sv + tid]);
+#pragma unroll
+    for (int i = 0; i < LD; ++i) {
+        int e = (tid + i * 256) * 4, r = e / sk, c0 = e % sk;
+        float* d = S + r * (sk + 1) + c0;
+        d[0] = ld[i].x; d[1] = ld[i].y; d[2] = ld[i].z; d[3] = ld[i].w;
+    }
+    __syncthreads();
+    // warp 0 normalises k, warp 1 normalises q (f64 tree sum, narrowing before the root)
+    if (wid < 2) {
+        float* src = kq + wid * sk;
+        double acc = 0.0;
+        for (int i = lane; i < sk; i += 32) { float v = src[i]; acc += (double)(v * v); }
+        acc = warp_sum_d(acc);
+        float sc = 1.0f / fmaxf(sqrtf((float)acc), p.eps);
+        float qs = 1.0f / sqrtf((float)sk);
+        for (int i = lane; i < sk; i += 32) {
+            float v = src[i] * sc;
+            src[i] = wid == 0 ? v : v * qs;
+        }
+    }
+    __syncthreads();
+    if (tid < sv) {
+        float a = p.alpha[(size_t)b * p.n_v + h] + p.dt_bias[h];
+        float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
+        float g = exp_f(sp * p.ssm_a[h]);
+        float bt = sigmoid_f(p.beta[(size_t)b * p.n_v + h]);
+        float* row = S + tid * (sk + 1);
+        float pred = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < sk; ++i) { float s = row[i] * g; row[i] = s; pred += s * kq[i]; }
+        float d = bt * (vj - pred);
+        float acc = 0.0f;
+#pragma unroll 4
+        for (int i = 0; i < sk; ++i) { float s = row[i] + kq[i] * d; row[i] = s; acc += s * kq[sk + i]; }
+        o[tid] = acc;
+    }
+    __syncthreads();
+    {
+        double acc = 0.0;
+        for (int i = tid; i < sv; i += blockDim.x) acc += (double)(o[i] * o[i]);
+        acc = warp_sum_d(acc);
+        if (lane == 0) red2[wid] = acc;
+        __syncthreads();
+        double tot = 0.0;
+        for (int w = 0; w < 8; ++w) tot += red2[w];
+        float mean = (float)(tot / (double)sv);
+        float sc = 1.0f / sqrtf(mean + p.eps);
+        if (tid < sv) {   // whole warps: sv is a multiple of 32
+            float core = o[tid] * sc * p.ssm_norm[tid];
+            size_t idx = (size_t)b * p.n_v * sv + (size_t)h * sv + tid;
+            float val = silu_f(p.z[idx]) * core;
+            float dq;
+            int8_t q = warp_quant_q8(val, &dq);
+            p.out_q[idx] = q;
+            if (lane == 0) p.out_s[idx / 32] = dq;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < LD; ++i) {
+        int e = (tid + i * 256) * 4, r = e / sk, c0 = e % sk;
+        const float* s = S + r * (sk + 1) + c0;
+        __stcs((float4*)sg + tid + i * 256, make_float4(s[0], s[1], s[2], s[3]));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Attention prologue per head: de-interleave q|gate, QK RMSNorm, partial NEOX RoPE at the sequence's
+// position, KV write (src/model/qwen35.rs:1175-1198). grid (n_head + 2*n_head_kv, B), block = head_dim.
+struct AttnPrep {
+    const float* qg; const float* k; const float* v;
+    const float* q_norm; const float* k_norm;
+    float* q_out; float* g_out;
+    uint16_t* kslab; uint16_t* vslab; size_t slab_stride;
+    const int* pos; int* npos_out;
+    int hd, n_head, n_head_kv, n_rot; float theta, eps; int bf16;
+};
+__global__ void k_attn_prep(AttnPrep p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* val = (float*)smem;
+    __shared__ double red[8];
+    const int job = blockIdx.x, b = blockIdx.y, d = threadIdx.x, hd = p.hd, kvd = p.n_head_kv * hd;
+    const int pos = p.pos[b];
+    if (job == 0 && d == 0) p.npos_out[b] = pos + 1;
+    const bool is_q = job < p.n_head, is_k = !is_q && job < p.n_head + p.n_head_kv;
+    const int hk = is_q ? job : is_k ? job - p.n_head : job - p.n_head - p.n_head_kv;
+    float v;
+    if (is_q) {
+        v = p.qg[(size_t)b * 2 * hd * p.n_head + (size_t)hk * 2 * hd + d];
+        p.g_out[((size_t)b * p.n_head + hk) * hd + d] = p.qg[(size_t)b * 2 * hd * p.n_head + (size_t)hk * 2 * hd + hd + d];
+    } else {
+        v = (is_k ? p.k : p.v)[(size_t)b * kvd + hk * hd + d];
+    }
+    if (is_q || is_k) {
+        double acc = warp_sum_d((double)(v * v));
+        if ((d & 31) == 0) red[d >> 5] = acc;
+        __syncthreads();
+        double tot = 0.0;
+        for (int w = 0; w < hd / 32; ++w) tot += red[w];
+        float mean = (float)(tot / (double)hd);
+        float sc = 1.0f / sqrtf(mean + p.eps);
+        v = v * sc * (is_q ? p.q_norm : p.k_norm)[d];
+        val[d] = v;
+        __syncthreads();
+        const int half = p.n_rot / 2;
+        if (d < half) {
+            double freq = pow((double)p.theta, -2.0 * (double)d / (double)p.n_rot);
+            double th = (double)pos * freq;
+            float sn = (float)sin(th), cs = (float)cos(th);
+            float x0 = val[d], x1 = val[d + half];
+            val[d] = x0 * cs - x1 * sn;
+            val[d + half] = x0 * sn + x1 * cs;
+        }
+        __syncthreads();
+        v = val[d];
+    }
+    if (is_q) p.q_out[((size_t)b * p.n_head + hk) * hd + d] = v;
+    else {
+        uint16_t* slab = (is_k ? p.kslab : p.vslab) + (size_t)b * p.slab_stride + (size_t)pos * kvd + hk * hd + d;
+        *slab = p.bf16 ? f32_to_bf16_bits(v) : f32_to_f16_bits(v);
+    }
+}
+
+// Combine of the attention splits for the engine: as k_attn_combine, over the splits that hold positions only,
+// with the sigmoid output gate (src/model/qwen35.rs:1216-1218) and the Q8_0 quantisation the output projection
+// would apply. grid (B * n_head), block hd.
+__global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, int n_split, int hd, const float* gate,
+                                 const int* n_pos_dev, int n_head, int8_t* out_q, float* out_s) {
+    const size_t th = blockIdx.x;
+    const int d = threadIdx.x, b = (int)(th / n_head);
+    const int n_pos = n_pos_dev[b], per = max(ATTN_MIN_SPLIT, (n_pos + n_split - 1) / n_split), n_act = (n_pos + per - 1) / per;
+    float M = -INFINITY;
+    for (int s = 0; s < n_act; ++s) M = fmaxf(M, part_ml[(th * n_split + s) * 2]);
+    float L = 0.0f, A = 0.0f;
+    for (int s = 0; s < n_act; ++s) {
+        float ms = part_ml[(th * n_split + s) * 2];
+        float c = ms == -INFINITY ? 0.0f : __expf(ms - M);
+        L += part_ml[(th * n_split + s) * 2 + 1] * c;
+        A += part_acc[(th * n_split + s) * hd + d] * c;
+    }
+    float v = A / L;
+    v *= sigmoid_f(gate[th * hd + d]);
+    float dq;
+    int8_t q = warp_quant_q8(v, &dq);
+    out_q[th * hd + d] = q;
+    if ((d & 31) == 0) out_s[(th * hd + d) / 32] = dq;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Routed experts, gated half. One block per 32 output rows of one pick (so the block can quantise its own
+// Q8_0 block of the result), plus one block per 32 rows of the shared expert's activation.
+// Warp 0 redoes the routing (softmax over all experts, top-k; src/model/qwen35.rs:1626-1638,
+// src/ops/mod.rs:1191-1216) while the others fetch the activation; then
+// h = silu(gate_e . x * s_g) * (up_e . x * s_u) (src/ops/mod.rs:1105-1117) -> Q8_0.
+struct MoeGlu {
+    const float* router; int n_expert, n_used;
+    const int8_t* xq; const float* xs; int n_embd;
+    DevFp4 gate, up;
+    const float* sg; const float* su; int sff;     // shared expert's gate/up outputs [B][sff]
+    int8_t* hq; float* hs;                          // [B][n_used*ff] int8, [B][n_used*ff/32]
+    int8_t* sq; float* ss;                          // [B][sff] int8, [B][sff/32]: silu(sg)*su quantised
+    int32_t* ids_out; float* w_out;
+};
+__global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int32_t s_ids[16];
+    __shared__ float s_wts[16];
+    __shared__ float s_gu[64];
+    const int n = p.n_embd, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = p.gate.n_out, upp = ff / 32;
+    const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int unit = blockIdx.x, n_units = p.n_used * upp;
+    if (unit >= n_units) {
+        // shared expert: silu(gate) * up for 32 elements, quantised (src/model/qwen35.rs:1669-1678)
+        if (wid == 0) {
+            const int k = (unit - n_units) * 32 + lane;
+            float v = silu_f(p.sg[(size_t)b * p.sff + k]) * p.su[(size_t)b * p.sff + k];
+            float dq;
+            int8_t q = warp_quant_q8(v, &dq);
+            p.sq[(size_t)b * p.sff + k] = q;
+            if (lane == 0) p.ss[(size_t)b * (p.sff / 32) + (unit - n_units)] = dq;
+        }
+        return;
+    }
+    float* probs = (float*)smem;                  // [n_expert rounded up to 32]
+    int8_t* xq = (int8_t*)(probs + ((p.n_expert + 31) & ~31));
+    float* xs = (float*)(xq + n);
+    float* terms = xs + nb + wid * terms_floats(4, gsh, nsb);
+    if (wid == 0) {
+        // softmax (src/ops/naive.rs:362-376): max, exp, serial sum in index order, divide; then top-k
+        const float* lg = p.router + (size_t)b * p.n_expert;
+        float mx = -INFINITY;
+        for (int i = lane; i < p.n_expert; i += 32) mx = fmaxf(mx, lg[i]);
+        mx = warp_max(mx);
+        const int ne32 = (p.n_expert + 31) & ~31;
+        for (int i = lane; i < ne32; i += 32) probs[i] = i < p.n_expert ? exp_f(lg[i] - mx) : 0.0f;
+        __syncwarp();
+        float sum = 0.0f;
+        if (lane == 0) {
+#pragma unroll 1
+            for (int i0 = 0; i0 < p.n_expert; i0 += 32) {
+                float4 q[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) q[j] = *(const float4*)(probs + i0 + 4 * j);
+                const int lim = p.n_expert - i0;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (4 * j < lim) sum += q[j].x;
+                    if (4 * j + 1 < lim) sum += q[j].y;
+                    if (4 * j + 2 < lim) sum += q[j].z;
+                    if (4 * j + 3 < lim) sum += q[j].w;
+                }
+            }
+        }
+        sum = __shfl_sync(0xffffffffu, sum, 0);
+        for (int i = lane; i < p.n_expert; i += 32) probs[i] /= sum;
+        __syncwarp();
+        int32_t ids[16];
+        float wts[16];
+        warp_topk_any(probs, p.n_expert, p.n_used, ids, wts);
+        if (lane == 0)
+            for (int r = 0; r < p.n_used; ++r) {
+                s_ids[r] = ids[r]; s_wts[r] = wts[r];
+                if (unit == 0) { p.ids_out[(size_t)b * p.n_used + r] = ids[r]; p.w_out[(size_t)b * p.n_used + r] = wts[r]; }
+            }
+    } else {
+        for (int i = tid - 32; i < n / 16; i += blockDim.x - 32) ((uint4*)xq)[i] = ((const uint4*)(p.xq + (size_t)b * n))[i];
+        for (int i = tid - 32; i < nb; i += blockDim.x - 32) xs[i] = p.xs[(size_t)b * nb + i];
+    }
+    __syncthreads();
+    const int pick = unit / upp, row0 = (unit % upp) * 32;
+    const int el = s_ids[pick] - p.gate.expert_lo;
+    if (el < 0 || el >= p.gate.n_expert) return;   // this pick's expert lives on another device
+    // 64 row-dots (32 gate rows, 32 up rows) spread over the block's warps
+    const size_t eo = (size_t)el * ff;
+    int k0, k1;
+    share(64, blockDim.x >> 5, wid, k0, k1);
+    const uint8_t* gn = p.gate.nib + eo * (n / 2); const uint8_t* gs = p.gate.sc + eo * nsb;
+    const uint8_t* un = p.up.nib + eo * (n / 2); const uint8_t* us = p.up.sc + eo * nsb;
+    rows_list<MK_FP4, 4>(k1 - k0, n, terms, gsh,
+        [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+            const int kk = k0 + k, row = row0 + (kk & 31);
+            pa = (kk < 32 ? gn : un) + (size_t)row * (n / 2);
+            pb = (kk < 32 ? gs : us) + (size_t)row * nsb;
+            q = xq; s = xs;
+        },
+        [&](int k, float v) { s_gu[k0 + k] = v; });
+    __syncthreads();
+    if (wid == 0) {
+        const bool has_g = p.gate.scale2 != nullptr, has_u = p.up.scale2 != nullptr;
+        float g = s_gu[lane], u = s_gu[32 + lane];
+        if (has_g) g = g * p.gate.scale2[el];
+        if (has_u) u = u * p.up.scale2[el];
+        float v = silu_f(g) * u;
+        float dq;
+        int8_t q = warp_quant_q8(v, &dq);
+        p.hq[((size_t)b * p.n_used + pick) * ff + row0 + lane] = q;
+        if (lane == 0) p.hs[((size_t)b * p.n_used + pick) * upp + unit % upp] = dq;
+    }
+}
+size_t moe_glu_smem(int n_expert, int n) {
+    int nb = n / 32, gsh = lanes_shift(nb);
+    return (size_t)((n_expert + 31) & ~31) * 4 + n + (size_t)nb * 4 + (size_t)NWG * terms_floats(4, gsh, n / 16) * 4 + 64;
+}
+
+// ------------------------------------------------------------------------------------------------------
+// Routed experts, second half, with the whole FFN tail fused: down projections of the picks and of the
+// shared expert, the weighted sum in pick order, the sigmoid-gated shared term and the residual add
+// (src/model/qwen35.rs:1659-1699, src/ops/mod.rs:1134-1171, src/model/qwen35.rs:1090). A warp takes one
+// output row at a time and runs all its streams (picks + shared) in one pass, so their loads share one round trip.
+struct MoeDown {
+    const int8_t* hq; const float* hs; int n_used, ff;
+    const int32_t* ids; const float* wts;
+    DevFp4 down;
+    const int8_t* sq; const float* ss; int sff;
+    DevQ8 shared_down;
+    const float* logit;
+    float* x; int x_stride;
+    int local_only; float* partial;
+};
+template <int RP>
+__global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_el[16];
+    __shared__ float s_wt[16], s_s2[16];
+    __shared__ float s_g;
+    const int ff = p.ff, sff = p.sff, nbf = ff / 32, nbs = sff / 32, nsb = ff / 16;
+    const int gf = lanes_shift(nbf), gs = lanes_shift(nbs);
+    const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5, lane = tid & 31;
+    const int n_out = p.down.n_out;
+    int8_t* hq = (int8_t*)smem;                           // [n_used][ff]
+    float* hs = (float*)(hq + p.n_used * ff);             // [n_used][nbf]
+    int8_t* sq = (int8_t*)(hs + p.n_used * nbf);          // [sff]
+    float* ss = (float*)(sq + sff);                       // [nbs]
+    const int tf = max(terms_floats(RP, gf, nsb), terms_floats(1, gs, nbs));
+    float* terms = ss + nbs + wid * (tf + 32);
+    float* outv = terms + tf;                             // this warp's per-stream results
+    for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];
+    for (int i = tid; i < p.n_used * nbf; i += blockDim.x) hs[i] = p.hs[(size_t)b * p.n_used * nbf + i];
+    for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + (size_t)b * sff))[i];
+    for (int i = tid; i < nbs; i += blockDim.x) ss[i] = p.ss[(size_t)b * nbs + i];
+    if (tid < p.n_used) {
+        int el = p.ids[(size_t)b * p.n_used + tid] - p.down.expert_lo;
+        s_el[tid] = (el < 0 || el >= p.down.n_expert) ? -1 : el;
+        s_wt[tid] = p.wts[(size_t)b * p.n_used + tid];
+        s_s2[tid] = (p.down.scale2 && s_el[tid] >= 0) ? p.down.scale2[s_el[tid]] : 1.0f;
+    }
+    if (tid == 32) s_g = sigmoid_f(p.logit[b]);
+    __syncthreads();
+    int b0, b1, r0, r1;
+    share(n_out, gridDim.x, blockIdx.x, b0, b1);
+    share(b1 - b0, nw, wid, r0, r1);
+    const bool has_s = p.down.scale2 != nullptr;
+    float* x = p.x + (size_t)b * p.x_stride;
+#pragma unroll 1
+    for (int row = b0 + r0; row < b0 + r1; ++row) {
+        // routed picks: item k = pick k of this row
+        rows_list<MK_FP4, RP>(p.n_used, ff, terms, gf,
+            [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+                const int el = max(s_el[k], 0);
+                pa = p.down.nib + ((size_t)el * n_out + row) * (ff / 2);
+                pb = p.down.sc + ((size_t)el * n_out + row) * nsb;
+                q = hq + k * ff; s = hs + k * nbf;
+            },
+            [&](int k, float v) { outv[k] = v; });
+        float sh = 0.0f;
+        if (!p.local_only) {
+            rows_list<MK_Q8, 1>(1, sff, terms, gs,
+                [&](int, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+                    pa = (const uint8_t*)p.shared_down.q + (size_t)row * sff;
+                    pb = (const uint8_t*)p.shared_down.s + (size_t)row * (sff / 16);
+                    q = sq; s = ss;
+                },
+                [&](int, float v) { outv[31] = v; });
+        }
+        __syncwarp();
+        if (lane == 0) {
+            float acc = 0.0f;                                   // experts in pick order from zero, shared last
+            for (int k = 0; k < p.n_used; ++k) {
+                if (s_el[k] < 0) continue;
+                float o = has_s ? outv[k] * s_s2[k] : outv[k];
+                acc += s_wt[k] * o;
+            }
+            if (p.local_only) p.partial[(size_t)b * n_out + row] = acc;
+            else { sh = outv[31]; acc += sh * s_g; x[row] += acc; }
+        }
+        __syncwarp();
+    }
+}
+size_t moe_down_smem(int n_used, int ff, int sff, int rp) {
+    int gf = lanes_shift(ff / 32), gs = lanes_shift(sff / 32);
+    int tf = std::max(terms_floats(rp, gf, ff / 16), terms_floats(1, gs, sff / 32));
+    return (size_t)n_used * ff + (size_t)n_used * (ff / 32) * 4 + sff + (size_t)(sff / 32) * 4 + (size_t)NWG * (tf + 32) * 4 + 64;
+}
+
+// ------------------------------------------------------------------------------------------------------
+__global__ void k_embed(const float* table, int n_embd, const int32_t* tokens, float* x) {
+    int b = blockIdx.x;
+    const float* row = table + (size_t)tokens[b] * n_embd;
+    for (int i = threadIdx.x; i < n_embd; i += blockDim.x) x[(size_t)b * n_embd + i] = row[i];
+}
+
+// Greedy argmax with strict '>' (lowest index wins, src/profile.rs:192-213) in two stages: partial
+// (value, index) pairs per sequence, then one warp per sequence that also feeds the choice back as the next
+// input token, advances the position and appends to the history.
+constexpr int ARGMAX_PARTS = 64;
+__device__ __forceinline__ void argmax_merge(float& bv, int& bi, float ov, int oi) {
+    if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+}
+__global__ void __launch_bounds__(256) k_argmax_partial(const float* logits, int n_vocab, float* pv, int* pi) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    int part = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    int lo, hi;
+    share(n_vocab, gridDim.x, part, lo, hi);
+    const float* l = logits + (size_t)b * n_vocab;
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int i = lo + tid; i < hi; i += blockDim.x) { float v = l[i]; if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; } }
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) { sv[wid] = bv; si[wid] = bi; }
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < 8; ++w) argmax_merge(bv, bi, sv[w], si[w]);
+        pv[(size_t)b * gridDim.x + part] = bv; pi[(size_t)b * gridDim.x + part] = bi;
+    }
+}
+__global__ void k_argmax_advance(const float* pv, const int* pi, int n_part, int32_t* tokens, int* pos, int32_t* next_out,
+                                 int32_t* history, int* step_counter, int n_seq) {
+    int b = blockIdx.x, lane = threadIdx.x;
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int i = lane; i < n_part; i += 32) argmax_merge(bv, bi, pv[(size_t)b * n_part + i], pi[(size_t)b * n_part + i]);
+    for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
+    if (lane == 0) {
+        tokens[b] = bi;
+        next_out[b] = bi;
+        pos[b] += 1;
+        int s = step_counter[b];
+        if (history) history[(size_t)s * n_seq + b] = bi;
+        step_counter[b] = s + 1;
+    }
+}
+
+}  // namespace

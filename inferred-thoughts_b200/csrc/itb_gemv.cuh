@@ -2,10 +2,14 @@
 // quantisation block, and an order-preserving f32 fold so every output equals the CPU path's
 // `sumf += term_b` chain to the bit (src/ops/naive.rs:691-734).
 //
-// Work split inside a warp: G lanes share a row (G = power of two dividing the row's block count),
+// Shape of the code: small loop bodies and many warps. A decode GEMV touches every instruction once per
+// row, so straight-line unrolled kernels spend their time fetching instructions; here a warp loops over
+// its rows RP at a time with all loads of a trip issued before the first dot.
+//
+// Work split inside a warp: G lanes share a row (G = power of two dividing the row's unit count),
 // 32/G rows run side by side, RP such groups per pass. Each lane owns fixed K-columns, computes the
-// integer sums of its blocks, turns them into f32 terms in shared memory; then one lane per row folds
-// that row's terms in ascending block order.
+// integer sums of its 32-element units, turns them into f32 terms in shared memory; then one lane per row
+// folds that row's terms in ascending order.
 #pragma once
 #include "itb_internal.cuh"
 
@@ -15,7 +19,6 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 
 // ---- activation prologues ------------------------------------------------------------------------
 // RMSNorm of one row into shared memory: f32 squares, f64 accumulation (tree), (x*scale)*w
@@ -36,18 +39,23 @@ __device__ __forceinline__ void block_rms_norm(const float* __restrict__ x, cons
     __syncthreads();
 }
 
-// Q8_0 activation quantiser over a row in shared memory (src/ops/naive.rs:653-675): one warp per
-// 32-block, d = amax/127 through f16, q = roundf(v * (1/d)).
+// One Q8_0 block of 32 values held one per lane (src/ops/naive.rs:653-675): d = amax/127 through f16,
+// q = roundf(v * (1/d)). Returns the lane's quant; *d_out (all lanes) the f16-rounded scale.
+__device__ __forceinline__ int8_t warp_quant_q8(float v, float* d_out) {
+    float amax = warp_max(fabsf(v));
+    float d = amax / 127.0f;
+    float id = d != 0.0f ? 1.0f / d : 0.0f;
+    float r = roundf(v * id);
+    *d_out = __half2float(__float2half_rn(d));
+    return (int8_t)fminf(127.0f, fmaxf(-128.0f, r));
+}
+// Q8_0 activation quantiser over a row in shared or global memory: one warp per 32-block.
 __device__ __forceinline__ void block_quant_q8(const float* xn, int n, int8_t* xq, float* xs) {
     int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     for (int b = wid; b < n / 32; b += nw) {
-        float v = xn[b * 32 + lane];
-        float amax = warp_max(fabsf(v));
-        float d = amax / 127.0f;
-        float id = d != 0.0f ? 1.0f / d : 0.0f;
-        float r = roundf(v * id);
-        xq[b * 32 + lane] = (int8_t)fminf(127.0f, fmaxf(-128.0f, r));
-        if (lane == 0) xs[b] = __half2float(__float2half_rn(d));
+        float d;
+        xq[b * 32 + lane] = warp_quant_q8(xn[b * 32 + lane], &d);
+        if (lane == 0) xs[b] = d;
     }
     __syncthreads();
 }
@@ -61,54 +69,6 @@ __host__ __device__ __forceinline__ int lanes_shift(int units) {
 // shared-memory floats one warp needs for its term matrix
 __host__ __device__ __forceinline__ int terms_floats(int rp, int gsh, int n_terms) { return rp * (32 >> gsh) * (n_terms + 1); }
 
-// ---- Q8_0 rows -------------------------------------------------------------------------------------
-// Rows [r0, r1) of `w` for this warp against one quantised activation (xq, xs in shared memory).
-// terms: warp-private shared scratch of RP*(32/G)*(nb+1) floats. epi(row, value) is called by one lane.
-template <int RP, class Epi>
-__device__ __forceinline__ void q8_rows(const DevQ8& w, int r0, int r1, const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
-    const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
-    const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
-    const int nb = w.n_in >> 5, stride = nb + 1;
-    for (int r = r0; r < r1; r += ROWS) {
-        for (int b = sub; b < nb; b += G) {
-            uint4 wa[RP], wb[RP];
-            uint16_t ws[RP];
-#pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                int row = r + i * SLOTS + slot;
-                if (row < r1) {
-                    const int8_t* p = w.q + (size_t)row * w.n_in + b * 32;
-                    wa[i] = ld_stream16(p); wb[i] = ld_stream16(p + 16);
-                    ws[i] = __ldg(w.s + (size_t)row * nb + b);
-                }
-            }
-            const uint4 xa = *(const uint4*)(xq + b * 32), xb = *(const uint4*)(xq + b * 32 + 16);
-            const float dx = xs[b];
-#pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                int row = r + i * SLOTS + slot;
-                if (row < r1) {
-                    int s = 0;
-                    s = __dp4a((int)wa[i].x, (int)xa.x, s); s = __dp4a((int)wa[i].y, (int)xa.y, s);
-                    s = __dp4a((int)wa[i].z, (int)xa.z, s); s = __dp4a((int)wa[i].w, (int)xa.w, s);
-                    s = __dp4a((int)wb[i].x, (int)xb.x, s); s = __dp4a((int)wb[i].y, (int)xb.y, s);
-                    s = __dp4a((int)wb[i].z, (int)xb.z, s); s = __dp4a((int)wb[i].w, (int)xb.w, s);
-                    terms[(i * SLOTS + slot) * stride + b] = (float)s * (f16_bits_to_f32(ws[i]) * dx);
-                }
-            }
-        }
-        __syncwarp();
-        if (lane < ROWS && r + lane < r1) {
-            const float* t = terms + lane * stride;
-            float sum = 0.0f;
-            for (int b = 0; b < nb; ++b) sum += t[b];
-            epi(r + lane, sum);
-        }
-        __syncwarp();
-    }
-}
-
-// ---- NVFP4 rows ------------------------------------------------------------------------------------
 // E2M1 codes to doubled integer magnitudes {0,1,2,3,4,6,8,12} (src/quant/mod.rs:265) with one byte
 // permute per four codes: the selector's bit 3 asks for the sign of the selected (positive) byte, i.e. 0,
 // so `prmt(pool, w)` yields the magnitudes of the positive codes and zeros elsewhere, and the same on
@@ -129,51 +89,134 @@ __device__ __forceinline__ int fp4_dot8(uint32_t w, uint32_t a0, uint32_t a1) {
     return pos - neg;
 }
 
-// Rows [r0, r1) of one NVFP4 matrix (nib: [rows][n_in/2], sc: [rows][n_in/16]) against a Q8_0 activation
-// (src/ops/naive.rs:714-734): term per 16-element sub-block = (dy*d)*(float)(lo+hi), folded ascending.
-// A lane's unit is a 16-byte chunk = two sub-blocks.
-template <int RP, class Epi>
-__device__ __forceinline__ void fp4_rows(const uint8_t* __restrict__ nib, const uint8_t* __restrict__ sc, int n_in, int r0, int r1,
-                                         const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
+// Matrix kinds the row cores understand. Plane A: Q8_0 int8 quants (n_in bytes per row) or NVFP4 nibbles
+// (n_in/2); plane B: f16 scales per 32 (n_in/16 bytes per row) or UE4M3 codes per 16 (n_in/16).
+enum { MK_Q8 = 0, MK_FP4 = 1 };
+template <int KIND> __host__ __device__ __forceinline__ int plane_a_bytes(int n_in) { return KIND == MK_Q8 ? n_in : n_in / 2; }
+__host__ __device__ __forceinline__ int plane_b_bytes(int n_in) { return n_in / 16; }
+// f32 terms per row: one per Q8_0 block of 32, or one per NVFP4 sub-block of 16.
+template <int KIND> __host__ __device__ __forceinline__ int row_terms(int n_in) { return KIND == MK_Q8 ? n_in / 32 : n_in / 16; }
+
+// One lane's 32-element unit of one row: 32 bytes (Q8_0) or 16 bytes (NVFP4) of weights plus the 2 scale bytes.
+struct UnitW { uint4 a, b; uint32_t s; };
+template <int KIND>
+__device__ __forceinline__ void unit_load(UnitW& w, const uint8_t* pa, const uint8_t* pb, int u) {
+    if (KIND == MK_Q8) { w.a = ld_stream16(pa + u * 32); w.b = ld_stream16(pa + u * 32 + 16); }
+    else w.a = ld_stream16(pa + u * 16);
+    w.s = __ldg((const uint16_t*)(pb + u * 2));
+}
+// The unit's f32 term(s) into t (row's term array), against the activation unit xa|xb with scale dx.
+template <int KIND>
+__device__ __forceinline__ void unit_terms(const UnitW& w, const uint4& xa, const uint4& xb, float dx, float* t, int u) {
+    if (KIND == MK_Q8) {
+        int s = 0;
+        s = __dp4a((int)w.a.x, (int)xa.x, s); s = __dp4a((int)w.a.y, (int)xa.y, s);
+        s = __dp4a((int)w.a.z, (int)xa.z, s); s = __dp4a((int)w.a.w, (int)xa.w, s);
+        s = __dp4a((int)w.b.x, (int)xb.x, s); s = __dp4a((int)w.b.y, (int)xb.y, s);
+        s = __dp4a((int)w.b.z, (int)xb.z, s); s = __dp4a((int)w.b.w, (int)xb.w, s);
+        t[u] = (float)s * (f16_bits_to_f32((uint16_t)w.s) * dx);               // src/ops/naive.rs:701
+    } else {
+        int s0 = fp4_dot8(w.a.x, xa.x, xa.y) + fp4_dot8(w.a.y, xa.z, xa.w);
+        int s1 = fp4_dot8(w.a.z, xb.x, xb.y) + fp4_dot8(w.a.w, xb.z, xb.w);
+        t[2 * u] = dx * ue4m3_half_dev(w.s & 0xff) * (float)s0;                // src/ops/naive.rs:730
+        t[2 * u + 1] = dx * ue4m3_half_dev(w.s >> 8) * (float)s1;
+    }
+}
+// Ascending fold of one row's terms.
+__device__ __forceinline__ float fold_terms(const float* t, int nt) {
+    float sum = 0.0f;
+#pragma unroll 4
+    for (int b = 0; b < nt; ++b) sum += t[b];
+    return sum;
+}
+
+// Rows [r0, r1) of one matrix (planes pa/pb, row 0 first) against one quantised activation (xq, xs in shared
+// memory). terms: warp-private shared scratch of terms_floats(RP, gsh, row_terms) floats. epi(row, value) is
+// called by one lane per row. Two units per lane and trip are loaded before the first dot.
+template <int KIND, int RP, class Epi>
+__device__ __forceinline__ void rows_direct(const uint8_t* __restrict__ pa, const uint8_t* __restrict__ pb, int n_in, int r0, int r1,
+                                            const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
     const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
     const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
-    const int nch = n_in >> 5, nsb = n_in >> 4, stride = nsb + 1;
+    const int nunits = n_in >> 5, nt = row_terms<KIND>(n_in), stride = nt + 1;
+    const int arb = plane_a_bytes<KIND>(n_in), brb = plane_b_bytes(n_in);
+#pragma unroll 1
     for (int r = r0; r < r1; r += ROWS) {
-        for (int ch = sub; ch < nch; ch += G) {
-            uint4 wv[RP];
-            uint16_t sv[RP];
+#pragma unroll 1
+        for (int u0 = sub; u0 < nunits; u0 += 2 * G) {
+            UnitW w[2][RP];
+            const bool two = u0 + G < nunits;
 #pragma unroll
             for (int i = 0; i < RP; ++i) {
                 int row = r + i * SLOTS + slot;
                 if (row < r1) {
-                    wv[i] = ld_stream16(nib + (size_t)row * (n_in >> 1) + ch * 16);
-                    sv[i] = __ldg((const uint16_t*)(sc + (size_t)row * nsb) + ch);
+                    unit_load<KIND>(w[0][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0);
+                    if (two) unit_load<KIND>(w[1][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0 + G);
                 }
             }
-            const uint4 xa = *(const uint4*)(xq + ch * 32), xb = *(const uint4*)(xq + ch * 32 + 16);
-            const float dy = xs[ch];  // a 32-element Q8_0 block spans both sub-blocks of the chunk
 #pragma unroll
-            for (int i = 0; i < RP; ++i) {
-                int row = r + i * SLOTS + slot;
-                if (row < r1) {
-                    int s0 = fp4_dot8(wv[i].x, xa.x, xa.y) + fp4_dot8(wv[i].y, xa.z, xa.w);
-                    int s1 = fp4_dot8(wv[i].z, xb.x, xb.y) + fp4_dot8(wv[i].w, xb.z, xb.w);
-                    float d0 = ue4m3_half_dev(sv[i] & 0xff), d1 = ue4m3_half_dev(sv[i] >> 8);
-                    float* t = terms + (i * SLOTS + slot) * stride + ch * 2;
-                    t[0] = dy * d0 * (float)s0;
-                    t[1] = dy * d1 * (float)s1;
+            for (int h = 0; h < 2; ++h) {
+                if (h == 0 || two) {
+                    const int u = u0 + h * G;
+                    const uint4 xa = *(const uint4*)(xq + u * 32), xb = *(const uint4*)(xq + u * 32 + 16);
+                    const float dx = xs[u];
+#pragma unroll
+                    for (int i = 0; i < RP; ++i)
+                        if (r + i * SLOTS + slot < r1) unit_terms<KIND>(w[h][i], xa, xb, dx, terms + (i * SLOTS + slot) * stride, u);
                 }
             }
         }
         __syncwarp();
-        if (lane < ROWS && r + lane < r1) {
-            const float* t = terms + lane * stride;
-            float sum = 0.0f;
-            for (int b = 0; b < nsb; ++b) sum += t[b];
-            epi(r + lane, sum);
-        }
+        if (lane < ROWS && r + lane < r1) epi(r + lane, fold_terms(terms + lane * stride, nt));
         __syncwarp();
     }
+}
+
+// A list of independent row-dots, each with its own weight row and its own activation: item k of [0, n) is
+// described by src(k, pa, pb, xq, xs) (weight planes of THE ROW, activation in shared memory). One pass
+// takes RP*(32/G) items with every load issued before the first dot; epi(k, value) by one lane per item.
+template <int KIND, int RP, class Src, class Epi>
+__device__ __forceinline__ void rows_list(int n, int n_in, float* terms, int gsh, Src src, Epi epi) {
+    const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
+    const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
+    const int nunits = n_in >> 5, nt = row_terms<KIND>(n_in), stride = nt + 1;
+#pragma unroll 1
+    for (int k0 = 0; k0 < n; k0 += ROWS) {
+        const uint8_t *pa[RP], *pb[RP];
+        const int8_t* xq[RP];
+        const float* xs[RP];
+#pragma unroll
+        for (int i = 0; i < RP; ++i) {
+            int k = k0 + i * SLOTS + slot;
+            if (k < n) src(k, pa[i], pb[i], xq[i], xs[i]);
+        }
+#pragma unroll 1
+        for (int u = sub; u < nunits; u += G) {
+            UnitW w[RP];
+#pragma unroll
+            for (int i = 0; i < RP; ++i)
+                if (k0 + i * SLOTS + slot < n) unit_load<KIND>(w[i], pa[i], pb[i], u);
+#pragma unroll
+            for (int i = 0; i < RP; ++i)
+                if (k0 + i * SLOTS + slot < n) {
+                    const uint4 xa = *(const uint4*)(xq[i] + u * 32), xb = *(const uint4*)(xq[i] + u * 32 + 16);
+                    unit_terms<KIND>(w[i], xa, xb, xs[i][u], terms + (i * SLOTS + slot) * stride, u);
+                }
+        }
+        __syncwarp();
+        if (lane < ROWS && k0 + lane < n) epi(k0 + lane, fold_terms(terms + lane * stride, nt));
+        __syncwarp();
+    }
+}
+
+template <int RP, class Epi>
+__device__ __forceinline__ void q8_rows(const DevQ8& w, int r0, int r1, const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
+    rows_direct<MK_Q8, RP>((const uint8_t*)w.q, (const uint8_t*)w.s, w.n_in, r0, r1, xq, xs, terms, gsh, epi);
+}
+template <int RP, class Epi>
+__device__ __forceinline__ void fp4_rows(const uint8_t* nib, const uint8_t* sc, int n_in, int r0, int r1, const int8_t* xq,
+                                         const float* xs, float* terms, int gsh, Epi epi) {
+    rows_direct<MK_FP4, RP>(nib, sc, n_in, r0, r1, xq, xs, terms, gsh, epi);
 }
 
 // ---- F32 rows --------------------------------------------------------------------------------------
@@ -198,9 +241,11 @@ __device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, 
             if (r + lane < r1) epi(r + lane, sum);
         }
     } else {
+#pragma unroll 1
         for (int r = r0; r < r1; ++r) {
             const float* p = w + (size_t)r * n_in;
             float s = 0.0f;
+#pragma unroll 4
             for (int k = lane * 4; k < n_in; k += 128) {
                 float4 v = __ldg((const float4*)(p + k));
                 s += v.x * x[k] + v.y * x[k + 1] + v.z * x[k + 2] + v.w * x[k + 3];

@@ -130,8 +130,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // exp in f32 through the f64 unit: correctly rounded for all but a vanishing fraction of inputs, so
 // results track the CPU's libm far closer than the fast f32 expf does. Only a handful of elements
 // per token go through it.
-__device__ __forceinline__ float exp_f(float x) { return (float)exp((double)x); }
-__device__ __forceinline__ float log_f(float x) { return (float)log((double)x); }
+// Not inlined: the f64 routines are long, and one copy per kernel keeps the instruction footprint small.
+static __device__ __noinline__ float exp_f(float x) { return (float)exp((double)x); }
+static __device__ __noinline__ float log_f(float x) { return (float)log((double)x); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + exp_f(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + exp_f(-x)); }
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }

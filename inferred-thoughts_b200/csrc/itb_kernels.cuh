@@ -207,6 +207,44 @@ __device__ __forceinline__ void block_topk(const float* p, int n_expert, int n_u
     }
     __syncthreads();
 }
+// The same rule inside ONE warp, probabilities in registers (expert e = lane + 32*j), no block barrier:
+// every round is a lane-local scan plus a five-step shuffle reduction. All lanes return the picks in
+// ids/wts (arrays of 16). p may be shared or global memory; n_expert <= 32*EPL.
+template <int EPL>
+__device__ __forceinline__ void warp_topk(const float* p, int n_expert, int n_used, int32_t* ids, float* wts) {
+    const int lane = threadIdx.x & 31;
+    float v[EPL];
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) v[j] = lane + 32 * j < n_expert ? p[lane + 32 * j] : 0.0f;
+    uint32_t taken = 0;
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) if (lane + 32 * j >= n_expert) taken |= 1u << j;
+    float sum = 0.0f;
+    for (int r = 0; r < n_used; ++r) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j)   // ascending ids within the lane: strict '>' keeps the lower one
+            if (!((taken >> j) & 1u) && (bi == 0x7fffffff || v[j] > bv)) { bv = v[j]; bi = lane + 32 * j; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, bv, o); int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        ids[r] = bi; wts[r] = bv;
+        sum += bv;                      // summed in pick order (src/ops/mod.rs:1211)
+    }
+    float denom = fmaxf(sum, 6.103515625e-5f);
+    for (int r = 0; r < n_used; ++r) wts[r] = wts[r] / denom;
+}
+__device__ __forceinline__ void warp_topk_any(const float* p, int n_expert, int n_used, int32_t* ids, float* wts) {
+    if (n_expert <= 32) warp_topk<1>(p, n_expert, n_used, ids, wts);
+    else if (n_expert <= 128) warp_topk<4>(p, n_expert, n_used, ids, wts);
+    else if (n_expert <= 256) warp_topk<8>(p, n_expert, n_used, ids, wts);
+    else if (n_expert <= 512) warp_topk<16>(p, n_expert, n_used, ids, wts);
+    else warp_topk<32>(p, n_expert, n_used, ids, wts);
+}
+
 __global__ void k_route(const float* probs, int n_expert, int n_used, int32_t* ids, float* wts) {
     __shared__ float sval[32];
     __shared__ int sidx[32];
@@ -303,6 +341,7 @@ __global__ void k_matmul_f32(DevF32 w, const float* x, float* out) {
 // grid (n_head_kv, n_q, n_split); block 256. Each warp walks positions p0+warp, +8, ...; a lane owns
 // hd/32 contiguous dims; all `group` query heads of the kv head are scored against each K row read.
 // Partials: m, l per (t, head, split) and acc[hd].
+constexpr int ATTN_MIN_SPLIT = 64;   // a split never covers fewer positions than this (short contexts use few splits)
 template <int HD, int MAXG>
 __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint16_t* vslab, int kv_dim, int n_pos_last, int n_q,
                                int n_head, int n_head_kv, float scale, int bf16, const int* n_pos_dev,
@@ -312,8 +351,16 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
     int group = n_head / n_head_kv;
     int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     int n_pos = n_pos_dev ? n_pos_dev[t] : n_pos_last - n_q + 1 + t;
-    int per = (n_pos + n_split - 1) / n_split;
+    int per = max(ATTN_MIN_SPLIT, (n_pos + n_split - 1) / n_split);
     int p0 = sp * per, p1 = min(n_pos, p0 + per);
+    if (p0 >= p1) {   // no positions in this split: neutral partials
+        for (int idx = threadIdx.x; idx < group * HD; idx += blockDim.x) {
+            size_t o = (((size_t)t * n_head + hk * group + idx / HD) * n_split + sp);
+            part_acc[o * HD + idx % HD] = 0.0f;
+            if (idx % HD == 0) { part_ml[o * 2] = -INFINITY; part_ml[o * 2 + 1] = 0.0f; }
+        }
+        return;
+    }
     float qr[MAXG][DPL];
 #pragma unroll
     for (int g = 0; g < MAXG; ++g)
@@ -329,10 +376,14 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
         const uint16_t* kr = kslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
         const uint16_t* vr = vslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
         float kf[DPL], vf[DPL];
+        uint16_t kb[DPL], vb[DPL];
+        if (DPL == 8) { *(uint4*)kb = *(const uint4*)kr; *(uint4*)vb = *(const uint4*)vr; }
+        else if (DPL == 4) { *(uint2*)kb = *(const uint2*)kr; *(uint2*)vb = *(const uint2*)vr; }
+        else { *(uint32_t*)kb = *(const uint32_t*)kr; *(uint32_t*)vb = *(const uint32_t*)vr; }
 #pragma unroll
         for (int d = 0; d < DPL; ++d) {
-            kf[d] = bf16 ? bf16_bits_to_f32(kr[d]) : f16_bits_to_f32(kr[d]);
-            vf[d] = bf16 ? bf16_bits_to_f32(vr[d]) : f16_bits_to_f32(vr[d]);
+            kf[d] = bf16 ? bf16_bits_to_f32(kb[d]) : f16_bits_to_f32(kb[d]);
+            vf[d] = bf16 ? bf16_bits_to_f32(vb[d]) : f16_bits_to_f32(vb[d]);
         }
 #pragma unroll
         for (int g = 0; g < MAXG; ++g) {
