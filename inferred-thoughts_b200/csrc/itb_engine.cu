@@ -359,10 +359,22 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
 #define MARK(cls, by) do { launches++; if (prof) prof->mark((cls), (uint64_t)(by), st); } while (0)
     // grid for a row-streaming kernel: about two rows per warp and pass, one block of 16 warps per SM
     auto grid_rows = [&](int rows) { return std::max(1, std::min(sms, (rows + 2 * NWG - 1) / (2 * NWG))); };
-    const size_t smem_in = in_proj_smem(H, c->exact);
+    // rows a warp folds together: what it owns, rounded up to whole passes, at most 32
+    const int pass_in = 2 * (32 >> lanes_shift(H / 32));
+    auto launch_in = [&](InProj& p, int rows, int gx) {
+        int per_warp = (rows + gx * NWG - 1) / (gx * NWG) + 1;
+        p.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+        k_in_proj<<<dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st>>>(p);
+    };
+    auto launch_out = [&](OutProj& o, int n_in) {
+        int gx = std::max(1, std::min(sms, H / NWG)), pass = 32 >> lanes_shift(n_in / 32);
+        int per_warp = (H + gx * NWG - 1) / (gx * NWG) + 1;
+        o.br = std::min(std::max(32 / pass, 1) * pass, (per_warp + pass - 1) / pass * pass);
+        k_out_proj<<<dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st>>>(o);
+    };
     static bool attrs_set = false;
     if (!attrs_set) {
-        set_smem((const void*)k_in_proj, 100 * 1024); set_smem((const void*)k_out_proj, 100 * 1024);
+        set_smem((const void*)k_in_proj, 200 * 1024); set_smem((const void*)k_out_proj, 200 * 1024);
         set_smem((const void*)k_moe_glu, 100 * 1024);
         set_smem((const void*)k_moe_down<1>, 100 * 1024); set_smem((const void*)k_moe_down<2>, 100 * 1024);
         set_smem((const void*)k_moe_down<4>, 100 * 1024); set_smem((const void*)k_moe_down<8>, 100 * 1024);
@@ -384,7 +396,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             p.conv_w = L.conv1d; p.conv_kernel = d.ssm_d_conv; p.conv_state_stride = (size_t)cd * (d.ssm_d_conv - 1);
             p.conv_state = e->conv_state + (size_t)rs * B * p.conv_state_stride;
             p.exact = c->exact;
-            k_in_proj<<<dim3(grid_rows(cd + vd), B), TPB, smem_in, st>>>(p);
+            launch_in(p, cd + vd, grid_rows(cd + vd));
             MARK(KC_GDN_IN, q8b(H, cd) + q8b(H, vd) + 2ull * H * d.ssm_dt_rank * 4 + (uint64_t)cd * d.ssm_d_conv * 4 +
                                 (uint64_t)B * (2ull * cd * (d.ssm_d_conv - 1) * 4 + (H + cd + vd) * 4));
             GdnCore g{};
@@ -397,7 +409,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             else k_gdn_core<64><<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g);
             MARK(KC_GDN_CORE, (uint64_t)B * (2ull * g.state_stride * 4 + (cd + 2ull * vd) * 4));
             OutProj o{e->aq, e->as, vd, L.ssm_out, e->x, H};
-            k_out_proj<<<dim3(grid_rows(H), B), TPB, out_proj_smem(vd), st>>>(o);
+            launch_out(o, vd);
             MARK(KC_OUT_PROJ, q8b(vd, H) + (uint64_t)B * (vd + 2ull * H) * 4);
         } else {
             int as = e->slot_of[il];
@@ -406,7 +418,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             p.nq = 3; p.q[0] = L.wq; p.qout[0] = e->qg; p.qstride[0] = 2 * qd; p.q[1] = L.wk; p.qout[1] = e->kbuf; p.qstride[1] = kvd;
             p.q[2] = L.wv; p.qout[2] = e->vbuf; p.qstride[2] = kvd;
             p.exact = c->exact;
-            k_in_proj<<<dim3(grid_rows(2 * qd + 2 * kvd), B), TPB, smem_in, st>>>(p);
+            launch_in(p, 2 * qd + 2 * kvd, grid_rows(2 * qd + 2 * kvd));
             MARK(KC_ATTN_IN, q8b(H, 2 * qd) + 2 * q8b(H, kvd) + (uint64_t)B * (H + 2ull * qd + 2ull * kvd) * 4);
             AttnPrep a{};
             a.qg = e->qg; a.k = e->kbuf; a.v = e->vbuf; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.q_out = e->qn; a.g_out = e->gate;
@@ -438,7 +450,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
                                                                   d.n_head, e->aq, e->as);
             MARK(KC_ATTN, 0);
             OutProj o{e->aq, e->as, qd, L.wo, e->x, H};
-            k_out_proj<<<dim3(grid_rows(H), B), TPB, out_proj_smem(qd), st>>>(o);
+            launch_out(o, qd);
             MARK(KC_OUT_PROJ, q8b(qd, H) + (uint64_t)B * (qd + 2ull * H) * 4);
         }
         // routed FFN
@@ -450,7 +462,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         f.xq_out = e->xq; f.xs_out = e->xs; f.exact = c->exact;
         int gxf = c->exact ? std::max((int)(d.n_expert + 31) / 32 + 1, grid_rows(2 * d.shared_ff))
                            : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));
-        k_in_proj<<<dim3(gxf, B), TPB, smem_in, st>>>(f);
+        launch_in(f, 2 * d.shared_ff, gxf);
         MARK(KC_FFN_IN, (uint64_t)H * d.n_expert * 4 + 2 * q8b(H, d.shared_ff) + (uint64_t)H * 4 + (uint64_t)B * (2ull * H + d.n_expert + 2ull * d.shared_ff) * 4);
         MoeGlu g{};
         g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
@@ -477,7 +489,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     InProj hp{};
     hp.x = e->x; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
     hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
-    k_in_proj<<<dim3(grid_rows(d.n_vocab), B), TPB, smem_in, st>>>(hp);
+    launch_in(hp, d.n_vocab, grid_rows(d.n_vocab));
     MARK(KC_LM_HEAD, q8b(H, d.n_vocab) + (uint64_t)B * (H + d.n_vocab) * 4);
     k_argmax_partial<<<dim3(ARGMAX_PARTS, B), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
     k_argmax_advance<<<B, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, e->step_counter, B);

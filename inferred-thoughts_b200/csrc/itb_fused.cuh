@@ -22,7 +22,7 @@ struct InProj {
     int nf; DevF32 f[2]; float* fout[2]; int fstride[2];
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
-    int exact;
+    int exact; int br;                             // br: rows whose terms a warp collects before folding them together
 };
 
 __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     int8_t* xq = (int8_t*)(xn + n);
     float* xs = (float*)(xq + n);
     float* tile = xs + nb;                                        // 32*33 floats, serial-k F32 mode only
-    const int tfl = terms_floats(RPG, gsh, nb);
+    const int tfl = p.br * (nb + 1);
     float* terms = tile + (p.exact ? 32 * 33 : 0) + wid * (tfl + CONV_CAP * 8);
     float* cpre = terms + tfl;
 
@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
                 float* cs = p.conv_state + (size_t)b * p.conv_state_stride;
                 const float* cw = p.conv_w;
                 const int kernel = p.conv_kernel;
-                q8_rows<RPG>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) {
+                rows_batched<MK_Q8, 2, 2>((const uint8_t*)p.q[m].q, (const uint8_t*)p.q[m].s, n, lo, hi, xq, xs, terms, p.br, gsh, [&](int row, float v) {
                     float* past = cs + (size_t)row * keep;
                     const bool pre = row - conv_lo < CONV_CAP;
                     const float* pin = pre ? cpre + (row - conv_lo) * 8 : past;
@@ -85,7 +85,8 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
                     past[keep - 1] = v;
                 });
             } else {
-                q8_rows<RPG>(p.q[m], lo, hi, xq, xs, terms, gsh, [&](int row, float v) { o[row] = v; });
+                rows_batched<MK_Q8, 2, 2>((const uint8_t*)p.q[m].q, (const uint8_t*)p.q[m].s, n, lo, hi, xq, xs, terms, p.br, gsh,
+                                          [&](int row, float v) { o[row] = v; });
             }
         }
         base += p.q[m].n_out;
@@ -120,22 +121,23 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         }
     }
 }
-size_t in_proj_smem(int n, int exact) {
-    int nb = n / 32, gsh = lanes_shift(nb);
-    return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (terms_floats(RPG, gsh, nb) + CONV_CAP * 8) * 4 + 64;
+// br a multiple of the pass size 2 * (32 >> gsh)
+size_t in_proj_smem(int n, int exact, int br) {
+    int nb = n / 32;
+    return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (br * (nb + 1) + CONV_CAP * 8) * 4 + 64;
 }
 
 // ------------------------------------------------------------------------------------------------------
 // Output projection with the residual add fused: x[b] += W . a[b], the activation arriving already quantised
 // (src/model/qwen35.rs:1017, :1220, :1325).
-struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; };
+struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; };
 __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
     const int b = blockIdx.y, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     int8_t* aq = (int8_t*)smem;
     float* as = (float*)(aq + n);
-    float* terms = as + nb + wid * terms_floats(RPG, gsh, nb);
+    float* terms = as + nb + wid * (p.br * (nb + 1));
     for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
     for (int i = threadIdx.x; i < nb; i += blockDim.x) as[i] = p.as[(size_t)b * nb + i];
     __syncthreads();
@@ -143,11 +145,12 @@ __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     share(p.w.n_out, gridDim.x, blockIdx.x, b0, b1);
     share(b1 - b0, nw, wid, r0, r1);
     float* x = p.x + (size_t)b * p.x_stride;
-    q8_rows<RPG>(p.w, b0 + r0, b0 + r1, aq, as, terms, gsh, [&](int row, float v) { x[row] += v; });
+    rows_batched<MK_Q8, 1, 4>((const uint8_t*)p.w.q, (const uint8_t*)p.w.s, n, b0 + r0, b0 + r1, aq, as, terms, p.br, gsh,
+                              [&](int row, float v) { x[row] += v; });
 }
-size_t out_proj_smem(int n) {
-    int nb = n / 32, gsh = lanes_shift(nb);
-    return (size_t)n + (size_t)nb * 4 + (size_t)NWG * terms_floats(RPG, gsh, nb) * 4 + 64;
+size_t out_proj_smem(int n, int br) {
+    int nb = n / 32;
+    return (size_t)n + (size_t)nb * 4 + (size_t)NWG * br * (nb + 1) * 4 + 64;
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -179,6 +182,10 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     float4 ld[LD];
 #pragma unroll
     for (int i = 0; i < LD; ++i) ld[i] = __ldcs((const float4*)sg + tid + i * 256);
+    // every other global operand is requested now too, so the kernel has one memory round trip
+    const float r_alpha = p.alpha[(size_t)b * p.n_v + h], r_dt = p.dt_bias[h], r_a = p.ssm_a[h], r_beta = p.beta[(size_t)b * p.n_v + h];
+    const size_t oidx = (size_t)b * p.n_v * sv + (size_t)h * sv + (tid < sv ? tid : 0);
+    const float r_z = p.z[oidx], r_nw = p.ssm_norm[tid < sv ? tid : 0];
     // SiLU of this head's conv sums: threads [0, 2*sk) take k then q, threads [0, sv) their v element later
     if (tid < 2 * sk) kq[tid] = silu_f(cv[(tid < sk ? key_dim : 0) + kh * sk + (tid < sk ? tid : tid - sk)]);
     float vj = 0.0f;
@@ -205,10 +212,10 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     }
     __syncthreads();
     if (tid < sv) {
-        float a = p.alpha[(size_t)b * p.n_v + h] + p.dt_bias[h];
+        float a = r_alpha + r_dt;
         float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
-        float g = exp_f(sp * p.ssm_a[h]);
-        float bt = sigmoid_f(p.beta[(size_t)b * p.n_v + h]);
+        float g = exp_f(sp * r_a);
+        float bt = sigmoid_f(r_beta);
         float* row = S + tid * (sk + 1);
         float pred = 0.0f;
 #pragma unroll 4
@@ -231,9 +238,9 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
         float mean = (float)(tot / (double)sv);
         float sc = 1.0f / sqrtf(mean + p.eps);
         if (tid < sv) {   // whole warps: sv is a multiple of 32
-            float core = o[tid] * sc * p.ssm_norm[tid];
-            size_t idx = (size_t)b * p.n_v * sv + (size_t)h * sv + tid;
-            float val = silu_f(p.z[idx]) * core;
+            float core = o[tid] * sc * r_nw;
+            size_t idx = oidx;
+            float val = silu_f(r_z) * core;
             float dq;
             int8_t q = warp_quant_q8(val, &dq);
             p.out_q[idx] = q;
@@ -369,15 +376,20 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     int8_t* xq = (int8_t*)(probs + ((p.n_expert + 31) & ~31));
     float* xs = (float*)(xq + n);
     float* terms = xs + nb + wid * terms_floats(4, gsh, nsb);
-    if (wid == 0) {
-        // softmax (src/ops/naive.rs:362-376): max, exp, serial sum in index order, divide; then top-k
+    {
+        // softmax numerators (src/ops/naive.rs:362-376) by the whole block: every warp finds the max itself
         const float* lg = p.router + (size_t)b * p.n_expert;
         float mx = -INFINITY;
         for (int i = lane; i < p.n_expert; i += 32) mx = fmaxf(mx, lg[i]);
         mx = warp_max(mx);
         const int ne32 = (p.n_expert + 31) & ~31;
-        for (int i = lane; i < ne32; i += 32) probs[i] = i < p.n_expert ? exp_f(lg[i] - mx) : 0.0f;
-        __syncwarp();
+        for (int i = tid; i < ne32; i += blockDim.x) probs[i] = i < p.n_expert ? exp_f(lg[i] - mx) : 0.0f;
+        for (int i = tid; i < n / 16; i += blockDim.x) ((uint4*)xq)[i] = ((const uint4*)(p.xq + (size_t)b * n))[i];
+        for (int i = tid; i < nb; i += blockDim.x) xs[i] = p.xs[(size_t)b * nb + i];
+    }
+    __syncthreads();
+    if (wid == 0) {
+        // serial sum in index order, divide, then top-k
         float sum = 0.0f;
         if (lane == 0) {
 #pragma unroll 1
@@ -406,9 +418,6 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
                 s_ids[r] = ids[r]; s_wts[r] = wts[r];
                 if (unit == 0) { p.ids_out[(size_t)b * p.n_used + r] = ids[r]; p.w_out[(size_t)b * p.n_used + r] = wts[r]; }
             }
-    } else {
-        for (int i = tid - 32; i < n / 16; i += blockDim.x - 32) ((uint4*)xq)[i] = ((const uint4*)(p.xq + (size_t)b * n))[i];
-        for (int i = tid - 32; i < nb; i += blockDim.x - 32) xs[i] = p.xs[(size_t)b * nb + i];
     }
     __syncthreads();
     const int pick = unit / upp, row0 = (unit % upp) * 32;

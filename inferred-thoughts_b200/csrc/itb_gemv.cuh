@@ -132,9 +132,9 @@ __device__ __forceinline__ float fold_terms(const float* t, int nt) {
 
 // Rows [r0, r1) of one matrix (planes pa/pb, row 0 first) against one quantised activation (xq, xs in shared
 // memory). terms: warp-private shared scratch of terms_floats(RP, gsh, row_terms) floats. epi(row, value) is
-// called by one lane per row. Two units per lane and trip are loaded before the first dot.
-template <int KIND, int RP, class Epi>
-__device__ __forceinline__ void rows_direct(const uint8_t* __restrict__ pa, const uint8_t* __restrict__ pb, int n_in, int r0, int r1,
+// called by one lane per row. UB units per lane and trip are loaded before the first dot.
+template <int KIND, int RP, int UB, class Epi>
+__device__ __forceinline__ void rows_direct_ub(const uint8_t* __restrict__ pa, const uint8_t* __restrict__ pb, int n_in, int r0, int r1,
                                             const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
     const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
     const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
@@ -143,20 +143,20 @@ __device__ __forceinline__ void rows_direct(const uint8_t* __restrict__ pa, cons
 #pragma unroll 1
     for (int r = r0; r < r1; r += ROWS) {
 #pragma unroll 1
-        for (int u0 = sub; u0 < nunits; u0 += 2 * G) {
-            UnitW w[2][RP];
-            const bool two = u0 + G < nunits;
+        for (int u0 = sub; u0 < nunits; u0 += UB * G) {
+            UnitW w[UB][RP];
 #pragma unroll
             for (int i = 0; i < RP; ++i) {
                 int row = r + i * SLOTS + slot;
                 if (row < r1) {
-                    unit_load<KIND>(w[0][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0);
-                    if (two) unit_load<KIND>(w[1][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0 + G);
+#pragma unroll
+                    for (int h = 0; h < UB; ++h)
+                        if (u0 + h * G < nunits) unit_load<KIND>(w[h][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0 + h * G);
                 }
             }
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                if (h == 0 || two) {
+            for (int h = 0; h < UB; ++h) {
+                if (u0 + h * G < nunits) {
                     const int u = u0 + h * G;
                     const uint4 xa = *(const uint4*)(xq + u * 32), xb = *(const uint4*)(xq + u * 32 + 16);
                     const float dx = xs[u];
@@ -209,6 +209,60 @@ __device__ __forceinline__ void rows_list(int n, int n_in, float* terms, int gsh
     }
 }
 
+// As rows_direct_ub, but the terms of up to `br` rows are collected first and then folded by `br` lanes at
+// once: the fold is a serial chain per row, so folding one or two rows at a time leaves most lanes idle and
+// costs as many instructions as the dots themselves. terms: br * (row_terms + 1) floats, warp-private.
+template <int KIND, int RP, int UB, class Epi>
+__device__ __forceinline__ void rows_batched(const uint8_t* __restrict__ pa, const uint8_t* __restrict__ pb, int n_in, int r0, int r1,
+                                             const int8_t* xq, const float* xs, float* terms, int br, int gsh, Epi epi) {
+    const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
+    const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
+    const int nunits = n_in >> 5, nt = row_terms<KIND>(n_in), stride = nt + 1;
+    const int arb = plane_a_bytes<KIND>(n_in), brb = plane_b_bytes(n_in);
+    br = min(br, 32) / ROWS * ROWS;   // whole passes per batch (the caller sizes terms for at least one pass)
+#pragma unroll 1
+    for (int rb = r0; rb < r1; rb += br) {
+        const int rend = min(r1, rb + br);
+#pragma unroll 1
+        for (int r = rb; r < rend; r += ROWS) {
+#pragma unroll 1
+            for (int u0 = sub; u0 < nunits; u0 += UB * G) {
+                UnitW w[UB][RP];
+#pragma unroll
+                for (int i = 0; i < RP; ++i) {
+                    const int row = r + i * SLOTS + slot;
+                    if (row < rend) {
+#pragma unroll
+                        for (int h = 0; h < UB; ++h)
+                            if (u0 + h * G < nunits) unit_load<KIND>(w[h][i], pa + (size_t)row * arb, pb + (size_t)row * brb, u0 + h * G);
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < UB; ++h) {
+                    if (u0 + h * G < nunits) {
+                        const int u = u0 + h * G;
+                        const uint4 xa = *(const uint4*)(xq + u * 32), xb = *(const uint4*)(xq + u * 32 + 16);
+                        const float dx = xs[u];
+#pragma unroll
+                        for (int i = 0; i < RP; ++i) {
+                            const int row = r + i * SLOTS + slot;
+                            if (row < rend) unit_terms<KIND>(w[h][i], xa, xb, dx, terms + (row - rb) * stride, u);
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (rb + lane < rend) epi(rb + lane, fold_terms(terms + lane * stride, nt));
+        __syncwarp();
+    }
+}
+
+template <int KIND, int RP, class Epi>
+__device__ __forceinline__ void rows_direct(const uint8_t* __restrict__ pa, const uint8_t* __restrict__ pb, int n_in, int r0, int r1,
+                                            const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
+    rows_direct_ub<KIND, RP, 2>(pa, pb, n_in, r0, r1, xq, xs, terms, gsh, epi);
+}
 template <int RP, class Epi>
 __device__ __forceinline__ void q8_rows(const DevQ8& w, int r0, int r1, const int8_t* xq, const float* xs, float* terms, int gsh, Epi epi) {
     rows_direct<MK_Q8, RP>((const uint8_t*)w.q, (const uint8_t*)w.s, w.n_in, r0, r1, xq, xs, terms, gsh, epi);
@@ -245,10 +299,16 @@ __device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, 
         for (int r = r0; r < r1; ++r) {
             const float* p = w + (size_t)r * n_in;
             float s = 0.0f;
-#pragma unroll 4
-            for (int k = lane * 4; k < n_in; k += 128) {
-                float4 v = __ldg((const float4*)(p + k));
-                s += v.x * x[k] + v.y * x[k + 1] + v.z * x[k + 2] + v.w * x[k + 3];
+#pragma unroll 1
+            for (int k0 = lane * 4; k0 < n_in; k0 += 128 * 8) {
+                float4 v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) if (k0 + 128 * j < n_in) v[j] = __ldg((const float4*)(p + k0 + 128 * j));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int k = k0 + 128 * j;
+                    if (k < n_in) s += v[j].x * x[k] + v[j].y * x[k + 1] + v[j].z * x[k + 2] + v[j].w * x[k + 3];
+                }
             }
             s = warp_sum(s);
             if (lane == 0) epi(r, s);
