@@ -166,6 +166,20 @@ uint64_t itb_engine_launches_per_step(itb_engine*);
 typedef struct { char name[32]; uint32_t launches; float ms; uint64_t bytes; } itb_kernel_stat;
 int  itb_engine_profile_step(itb_engine*, const uint32_t* tokens, itb_kernel_stat* out, size_t cap, size_t* n_out);
 
+/* Decode attention that allocates nothing. No counterpart in the reference: added for callers that must not
+ * allocate device memory while serving (cudaMalloc/cudaFree synchronise the whole device) or that run under a
+ * memory budget fixed at start-up. All pointers are DEVICE pointers the caller already owns: q [n_head*head_dim]
+ * f32, k/v KV slabs (f16 bits, or bf16 bits if kv_bf16) position-major with stride kv_dim, out
+ * [n_head*head_dim] f32; `stream` is a cudaStream_t (NULL = default stream). One query row attends over
+ * positions [0, n_pos). The split-K partials live in a fixed ~2.1 MB array inside the library (held by every
+ * GPU that loads it until the process exits); limits: n_head <= 64, head_dim in {64,128,256}, at most 8 query
+ * heads per KV head -- anything beyond is refused with a message in `err`. The first call on a device looks the
+ * array's address up: make it with that device current and before any stream capture. Calls share the array, so
+ * calls that overlap on the GPU race; issue them one after the other. Returns 0, or 1 with `err` filled. */
+int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t* k_dev, const uint16_t* v_dev,
+                               size_t kv_dim, size_t n_pos, size_t head_dim, size_t n_head, size_t n_head_kv, float scale,
+                               int kv_bf16, float* out_dev, char* err, size_t err_cap);
+
 /* Device generator check: element i of stream `key` (tests compare with the CPU generator). */
 int  itb_synth_values(itb_ctx*, uint64_t key, uint64_t first, size_t n, int dist, float std_, float* out);
 
