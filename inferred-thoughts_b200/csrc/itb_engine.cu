@@ -20,6 +20,7 @@ void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t 
                        unsigned* amax_tmp, float* scale2, uint8_t* raw);
 
 #include "itb_fused.cuh"
+#include "itb_rows.cuh"
 
 // =====================================================================================================
 // Model
@@ -299,10 +300,13 @@ struct itb_engine {
     int8_t* xq = nullptr; float* xs = nullptr;
     int32_t* route_ids = nullptr; float* route_w = nullptr;  // [n_layer][B][n_used]
     int32_t* history = nullptr; int* step_counter = nullptr; uint32_t history_cap = 0;
-    int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr;
+    int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr; long long* stamps = nullptr; int n_stamped = 0;
     int8_t *aq = nullptr, *hq = nullptr, *sq = nullptr; float *as = nullptr, *hs = nullptr, *ss = nullptr;  // producer-quantised activations
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
-    int n_split = 1;
+    int n_split = 1, n_split_rows = 4;
+    uint32_t R = 0;                                   // rows the multi-row pass can hold (>= B)
+    uint32_t last_n_tok = 1;                          // tokens per sequence in the most recent pass
+    float *xn = nullptr, *qh = nullptr, *kh = nullptr, *vh = nullptr, *gb = nullptr, *core = nullptr, *xlast = nullptr;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.0f;
@@ -348,6 +352,7 @@ static void set_smem(const void* fn, size_t bytes) {
 // One decode step for all B sequences, enqueued on `st`.
 static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
+    e->n_stamped = 0;
     const itb_model_dims& d = m->d;
     const int B = e->B, H = d.n_embd, sms = c->sm_count;
     const int key_dim = d.ssm_d_state * d.ssm_n_group, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
@@ -364,6 +369,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     auto launch_in = [&](InProj& p, int rows, int gx) {
         int per_warp = (rows + gx * NWG - 1) / (gx * NWG) + 1;
         p.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+        if (e->stamps) { p.stamps = e->stamps + 8 * (e->n_stamped % 400); e->n_stamped++; }
         k_in_proj<<<dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st>>>(p);
     };
     auto launch_out = [&](OutProj& o, int n_in) {
@@ -468,7 +474,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
         g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
-        g.ids_out = e->route_ids + (size_t)il * B * d.n_expert_used; g.w_out = e->route_w + (size_t)il * B * d.n_expert_used;
+        g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
         k_moe_glu<<<dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st>>>(g);
         MARK(KC_MOE_GLU, (uint64_t)B * (2ull * d.n_expert_used * f4b(H, d.expert_ff) + (uint64_t)d.n_expert_used * d.expert_ff * 4));
         MoeDown w{};
@@ -492,10 +498,144 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     launch_in(hp, d.n_vocab, grid_rows(d.n_vocab));
     MARK(KC_LM_HEAD, q8b(H, d.n_vocab) + (uint64_t)B * (H + d.n_vocab) * 4);
     k_argmax_partial<<<dim3(ARGMAX_PARTS, B), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
-    k_argmax_advance<<<B, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, e->step_counter, B);
+    k_argmax_advance<<<B, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, (int)e->history_cap, e->step_counter, B);
     MARK(KC_ARGMAX, (uint64_t)B * d.n_vocab * 4);
 #undef MARK
     e->launches_per_step = launches;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// The multi-row pass: n_seq sequences x n_tok consecutive tokens each (rows = n_seq * n_tok <= e->R), token ids in
+// `tok_rows` (device, row-major). Batched decode is (B, 1); a prefill chunk of one sequence is (1, T).
+// Ends with the LM head on each sequence's last row, the greedy argmax and the position advance.
+static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_tok, const int32_t* tok_rows) {
+    itb_model* m = e->m; itb_ctx* c = e->c;
+    const itb_model_dims& d = m->d;
+    const int R = n_seq * n_tok, H = d.n_embd, sms = c->sm_count;
+    const int sk = d.ssm_d_state, n_k = d.ssm_n_group, n_v = d.ssm_dt_rank;
+    const int key_dim = sk * n_k, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
+    const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv;
+    const int TPB = NWG * 32;
+    uint64_t launches = 0;
+    static bool attrs_set = false;
+    if (!attrs_set) {
+        set_smem((const void*)k_gemm_q8, 200 * 1024);
+        set_smem((const void*)k_matmul_f32<true>, 100 * 1024); set_smem((const void*)k_matmul_f32<false>, 100 * 1024);
+        set_smem((const void*)k_gdn_scan<32>, 100 * 1024);
+        attrs_set = true;
+    }
+    auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode) {
+        dim3 g((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (R + MMA_TOK - 1) / MMA_TOK);
+        k_gemm_q8<<<g, 256, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
+        launches++;
+    };
+    auto f32mm = [&](const DevF32& w, const float* x, float* out) {
+        const int nw = 4;
+        dim3 g(std::max(1, std::min(2 * sms, (w.n_out + 31) / 32)), R);
+        size_t sm = (size_t)w.n_in * 4 + (size_t)nw * 32 * 33 * 4;
+        if (c->exact) k_matmul_f32<true><<<g, nw * 32, sm, st>>>(w, x, out);
+        else k_matmul_f32<false><<<g, nw * 32, sm, st>>>(w, x, out);
+        launches++;
+    };
+    const size_t smem_nq = 256 + (size_t)H * 4;
+    k_embed<<<R, 256, 0, st>>>(m->tok_embd.w, H, tok_rows, e->x); launches++;
+    for (uint32_t il = 0; il < d.n_layer; ++il) {
+        const DevLayer& L = m->layers[il];
+        k_norm_quant<<<R, 256, smem_nq, st>>>(e->x, L.attn_norm, H, d.rms_eps, e->xn, e->xq, e->xs); launches++;
+        if (L.recurrent) {
+            const int rs = e->slot_of[il];
+            const size_t state_stride = (size_t)n_v * sk * sk, conv_stride = (size_t)cd * (d.ssm_d_conv - 1);
+            gemm(L.wqkv, e->xq, e->xs, e->qkvc, cd, 0);
+            gemm(L.wgate, e->xq, e->xs, e->z, vd, 0);
+            f32mm(L.ssm_alpha, e->xn, e->alpha);
+            f32mm(L.ssm_beta, e->xn, e->beta);
+            k_conv_rows<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(e->conv_state + (size_t)rs * e->B * conv_stride, conv_stride, e->qkvc,
+                                                                       n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
+            k_gdn_pre<<<dim3(R, 2 * n_k + n_v), sk, 0, st>>>(e->qkvc, cd, e->alpha, e->beta, L.ssm_a, L.dt_bias, sk, n_k, n_v, d.rms_eps,
+                                                            e->qh, e->kh, e->vh, e->gb); launches++;
+            k_gdn_scan<32><<<dim3(n_v, sk / 32, n_seq), 128, (size_t)(32 * (sk + 1) + 2 * sk) * 4, st>>>(
+                e->qh, e->kh, e->vh, e->gb, n_tok, sk, n_k, n_v, e->ssm_state + (size_t)rs * e->B * state_stride, state_stride, e->core); launches++;
+            k_gdn_post<<<dim3(R, n_v), sk, 0, st>>>(e->core, e->z, L.ssm_norm, sk, n_v, d.rms_eps, e->aq, e->as); launches++;
+            gemm(L.ssm_out, e->aq, e->as, e->x, H, 1);
+        } else {
+            const int as = e->slot_of[il];
+            gemm(L.wq, e->xq, e->xs, e->qg, 2 * qd, 0);
+            gemm(L.wk, e->xq, e->xs, e->kbuf, kvd, 0);
+            gemm(L.wv, e->xq, e->xs, e->vbuf, kvd, 0);
+            AttnPrepRows a{};
+            a.qg = e->qg; a.k = e->kbuf; a.v = e->vbuf; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.q_out = e->qn; a.g_out = e->gate;
+            a.slab_stride = (size_t)e->n_ctx * kvd;
+            a.kslab = e->kslab + (size_t)as * e->B * a.slab_stride; a.vslab = e->vslab + (size_t)as * e->B * a.slab_stride;
+            a.pos = e->pos; a.npos_out = e->npos; a.n_tok = n_tok; a.hd = d.head_dim; a.n_head = d.n_head; a.n_head_kv = d.n_head_kv;
+            a.n_rot = d.n_rot; a.theta = d.rope_theta; a.eps = d.rms_eps; a.bf16 = c->kv_bf16;
+            k_attn_prep_rows<<<dim3(d.n_head + 2 * d.n_head_kv, R), d.head_dim, d.head_dim * 4, st>>>(a); launches++;
+            const float scale = 1.0f / sqrtf((float)d.head_dim);
+            const int nwa = 8, ns = n_tok > 1 ? e->n_split_rows : e->n_split;
+            const size_t smem_a = (size_t)nwa * 8 * 2 * 4 + (size_t)nwa * 8 * d.head_dim * 4;
+            for (int s = 0; s < n_seq; ++s) {
+                const size_t r0 = (size_t)s * n_tok, po = r0 * d.n_head * ns;
+                dim3 grid(d.n_head_kv, n_tok, ns);
+#define ATT_CASE(HD)                                                                                                       \
+    case HD:                                                                                                                \
+        set_smem((const void*)k_attn_partial<HD, 8>, smem_a);                                                               \
+        k_attn_partial<HD, 8><<<grid, nwa * 32, smem_a, st>>>(e->qn + r0 * qd, a.kslab + (size_t)s * a.slab_stride,         \
+            a.vslab + (size_t)s * a.slab_stride, kvd, 0, n_tok, d.n_head, d.n_head_kv, scale, c->kv_bf16, e->npos + r0,     \
+            e->part_acc + po * d.head_dim, e->part_ml + po * 2);                                                            \
+        break;
+                switch (d.head_dim) { ATT_CASE(64) ATT_CASE(128) ATT_CASE(256) }
+#undef ATT_CASE
+                launches++;
+            }
+            k_attn_combine_rows<<<R * d.n_head, d.head_dim, 0, st>>>(e->part_acc, e->part_ml, ns, d.head_dim, e->gate, e->npos, d.n_head,
+                                                                    e->aq, e->as); launches++;
+            gemm(L.wo, e->aq, e->as, e->x, H, 1);
+        }
+        // routed FFN
+        k_norm_quant<<<R, 256, smem_nq, st>>>(e->x, L.ffn_norm, H, d.rms_eps, e->xn, e->xq, e->xs); launches++;
+        gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
+        gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0);
+        f32mm(L.gate_inp, e->xn, e->router);
+        f32mm(L.shared_gate_inp, e->xn, e->shlogit);
+        MoeGlu g{};
+        g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
+        g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
+        g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
+        g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
+        k_moe_glu<<<dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, R), TPB, moe_glu_smem(d.n_expert, H), st>>>(g); launches++;
+        MoeDown w{};
+        w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
+        w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
+        {
+            int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
+            int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
+            dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), R);
+            size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
+            if (rp == 1) k_moe_down<1><<<grid, TPB, smem_d, st>>>(w);
+            else if (rp == 2) k_moe_down<2><<<grid, TPB, smem_d, st>>>(w);
+            else if (rp == 4) k_moe_down<4><<<grid, TPB, smem_d, st>>>(w);
+            else k_moe_down<8><<<grid, TPB, smem_d, st>>>(w);
+            launches++;
+        }
+    }
+    // LM head on each sequence's last row
+    const float* xl = e->x;
+    if (n_tok > 1) { k_gather_last<<<n_seq, 256, 0, st>>>(e->x, H, n_tok, e->xlast); launches++; xl = e->xlast; }
+    InProj hp{};
+    hp.x = xl; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
+    hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
+    {
+        const int pass_in = 2 * (32 >> lanes_shift(H / 32));
+        int gx = std::max(1, std::min(sms, ((int)d.n_vocab + 2 * NWG - 1) / (2 * NWG)));
+        int per_warp = ((int)d.n_vocab + gx * NWG - 1) / (gx * NWG) + 1;
+        hp.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+        set_smem((const void*)k_in_proj, 200 * 1024);
+        k_in_proj<<<dim3(gx, n_seq), TPB, in_proj_smem(H, c->exact, hp.br), st>>>(hp); launches++;
+    }
+    k_argmax_partial<<<dim3(ARGMAX_PARTS, n_seq), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
+    if (n_tok > 1) { k_advance_pos<<<(n_seq + 127) / 128, 128, 0, st>>>(e->pos, n_seq, n_tok - 1); launches++; }
+    k_argmax_advance<<<n_seq, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, (int)e->history_cap, e->step_counter, n_seq);
+    launches++;
+    return launches;
 }
 
 extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, itb_engine** out) {
@@ -515,25 +655,29 @@ extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, i
     const size_t qd = (size_t)d.head_dim * d.n_head, kvd = (size_t)d.head_dim * d.n_head_kv;
     e->n_split = (int)std::max<size_t>(1, std::min<size_t>({(size_t)64, ((size_t)n_ctx + 127) / 128, (size_t)(2 * c->sm_count) / d.n_head_kv + 1}));
     itb_engine* E = e.get();
+    e->R = std::max<uint32_t>(n_seq, getenv("ITB_ROWS") ? (uint32_t)atoi(getenv("ITB_ROWS")) : 512u);
+    const size_t R = e->R, K = d.n_expert_used;
+    const size_t n_parts = std::max<size_t>(B * d.n_head * e->n_split, R * d.n_head * e->n_split_rows);
     bool ok = dalloc(E, &e->kslab, (size_t)e->n_attn * B * n_ctx * kvd) && dalloc(E, &e->vslab, (size_t)e->n_attn * B * n_ctx * kvd) &&
               dalloc(E, &e->conv_state, (size_t)e->n_rec * B * cd * (d.ssm_d_conv - 1)) &&
               dalloc(E, &e->ssm_state, (size_t)e->n_rec * B * d.ssm_dt_rank * d.ssm_d_state * d.ssm_d_state) &&
-              dalloc(E, &e->pos, B) && dalloc(E, &e->npos, B) && dalloc(E, &e->tokens, B) && dalloc(E, &e->next, B) && dalloc(E, &e->x, B * H) &&
-              dalloc(E, &e->qkvc, B * cd) && dalloc(E, &e->z, B * vd) && dalloc(E, &e->alpha, B * d.ssm_dt_rank) &&
-              dalloc(E, &e->beta, B * d.ssm_dt_rank) && dalloc(E, &e->zc, B * vd) && dalloc(E, &e->qg, B * 2 * qd) &&
-              dalloc(E, &e->kbuf, B * kvd) && dalloc(E, &e->vbuf, B * kvd) && dalloc(E, &e->qn, B * qd) && dalloc(E, &e->gate, B * qd) &&
-              dalloc(E, &e->att, B * qd) && dalloc(E, &e->part_acc, B * d.n_head * e->n_split * d.head_dim) &&
-              dalloc(E, &e->part_ml, B * d.n_head * e->n_split * 2) && dalloc(E, &e->router, B * d.n_expert) &&
-              dalloc(E, &e->shlogit, B) && dalloc(E, &e->sg, B * d.shared_ff) && dalloc(E, &e->su, B * d.shared_ff) &&
-              dalloc(E, &e->h, B * d.n_expert_used * d.expert_ff) && dalloc(E, &e->logits, B * d.n_vocab) &&
-              dalloc(E, &e->xq, B * H) && dalloc(E, &e->xs, B * H / 32) &&
-              dalloc(E, &e->route_ids, (size_t)d.n_layer * B * d.n_expert_used) && dalloc(E, &e->route_w, (size_t)d.n_layer * B * d.n_expert_used) &&
+              dalloc(E, &e->pos, B) && dalloc(E, &e->npos, R) && dalloc(E, &e->tokens, B) && dalloc(E, &e->next, B) && dalloc(E, &e->x, R * H) &&
+              dalloc(E, &e->qkvc, R * cd) && dalloc(E, &e->z, R * vd) && dalloc(E, &e->alpha, R * d.ssm_dt_rank) &&
+              dalloc(E, &e->beta, R * d.ssm_dt_rank) && dalloc(E, &e->qg, R * 2 * qd) &&
+              dalloc(E, &e->kbuf, R * kvd) && dalloc(E, &e->vbuf, R * kvd) && dalloc(E, &e->qn, R * qd) && dalloc(E, &e->gate, R * qd) &&
+              dalloc(E, &e->part_acc, n_parts * d.head_dim) && dalloc(E, &e->part_ml, n_parts * 2) && dalloc(E, &e->router, R * d.n_expert) &&
+              dalloc(E, &e->shlogit, R) && dalloc(E, &e->sg, R * d.shared_ff) && dalloc(E, &e->su, R * d.shared_ff) &&
+              dalloc(E, &e->logits, B * d.n_vocab) && dalloc(E, &e->xq, R * H) && dalloc(E, &e->xs, R * H / 32) &&
+              dalloc(E, &e->route_ids, (size_t)d.n_layer * R * K) && dalloc(E, &e->route_w, (size_t)d.n_layer * R * K) &&
               dalloc(E, &e->step_counter, B) && dalloc(E, &e->err, 1) && dalloc(E, &e->arg_v, B * ARGMAX_PARTS) && dalloc(E, &e->arg_i, B * ARGMAX_PARTS) &&
-              dalloc(E, &e->aq, B * std::max(vd, qd)) && dalloc(E, &e->as, B * std::max(vd, qd) / 32) &&
-              dalloc(E, &e->hq, B * d.n_expert_used * d.expert_ff) && dalloc(E, &e->hs, B * d.n_expert_used * d.expert_ff / 32) &&
-              dalloc(E, &e->sq, B * d.shared_ff) && dalloc(E, &e->ss, B * d.shared_ff / 32);
+              dalloc(E, &e->aq, R * std::max(vd, qd)) && dalloc(E, &e->as, R * std::max(vd, qd) / 32) &&
+              dalloc(E, &e->hq, R * K * d.expert_ff) && dalloc(E, &e->hs, R * K * d.expert_ff / 32) &&
+              dalloc(E, &e->sq, R * d.shared_ff) && dalloc(E, &e->ss, R * d.shared_ff / 32) &&
+              dalloc(E, &e->xn, R * H) && dalloc(E, &e->qh, R * key_dim) && dalloc(E, &e->kh, R * key_dim) && dalloc(E, &e->vh, R * vd) &&
+              dalloc(E, &e->gb, R * d.ssm_dt_rank * 2) && dalloc(E, &e->core, R * vd) && dalloc(E, &e->xlast, B * H);
     if (!ok) { for (void* p : e->allocs) cudaFree(p); return 1; }
     e->host_pos.assign(B, 0);
+    if (getenv("ITB_STAMPS")) dalloc(E, &e->stamps, 8 * 400);   // debug: phase clocks of k_in_proj
     cudaEventCreate(&e->ev0); cudaEventCreate(&e->ev1);
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) { itb_fail_msg(c, "engine: device error during set-up"); return 1; }
     *out = e.release();
@@ -577,7 +721,8 @@ static bool ensure_graph(itb_engine* e) {
     cudaStream_t st = c->stream;
     // one eager step's worth of attribute set-up happens inside enqueue_step; capture it once
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return itb_fail_msg(c, "engine: cannot begin capture");
-    enqueue_step(e, st);
+    if (e->B == 1) enqueue_step(e, st);
+    else e->launches_per_step = enqueue_rows(e, st, (int)e->B, 1, e->tokens);
     cudaError_t err = cudaStreamEndCapture(st, &e->graph);
     if (err != cudaSuccess) return itb_fail(c, "engine: capture", err);
     err = cudaGraphInstantiate(&e->exec, e->graph, 0);
@@ -606,6 +751,7 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
     c->launches += (uint64_t)steps * e->launches_per_step;
     if (timed) cudaEventRecord(e->ev1, c->stream);
     for (uint32_t b = 0; b < e->B; ++b) e->host_pos[b] += steps;
+    e->last_n_tok = 1;
     return true;
 }
 
@@ -641,31 +787,48 @@ extern "C" int itb_engine_decode_loop(itb_engine* e, const uint32_t* first, uint
     return check_flag(e) ? 0 : 1;
 }
 
-// Prefill, token by token through the decode graph: the state left behind and the last logits are those of
-// a batched pass (the reference asserts the two are identical, tests/qwen35.rs:94-139 there).
+// Prefill in multi-row passes: every sequence advances `chunk` tokens per pass (rows = n_seq * chunk <= R), each
+// weight row read once per 32 rows. The arithmetic order per token is the decode path's, so the state left
+// behind and the logits equal a token-by-token run (the reference asserts the same of its own backends,
+// tests/qwen35.rs:94-139 there). ITB_PREFILL_STEPWISE=1 runs the old token-by-token loop (A/B and tests).
 extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t n, float* logits_out) {
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
     if (n == 0) { itb_fail_msg(c, "prefill: no tokens supplied"); return 1; }
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + n > e->n_ctx) { itb_fail_msg(c, "context overflow: the prompt would write past n_ctx"); return 1; }
+    for (size_t i = 0; i < n * e->B; ++i)
+        if (tokens[i] >= e->m->d.n_vocab) { itb_fail_msg(c, "token id out of range"); return 1; }
+    const bool stepwise = getenv("ITB_PREFILL_STEPWISE") != nullptr;
+    const size_t chunk = stepwise ? 1 : std::max<size_t>(1, e->R / e->B);
+    // token ids laid out pass by pass, row-major inside a pass: [pass][seq][t]
+    std::vector<int32_t> tr(n * e->B);
+    size_t off = 0;
+    for (size_t t0 = 0; t0 < n; t0 += chunk) {
+        const size_t nt = std::min(chunk, n - t0);
+        for (size_t b = 0; b < e->B; ++b)
+            for (size_t t = 0; t < nt; ++t) tr[off++] = (int32_t)tokens[b * n + t0 + t];
+    }
     if (e->prompt_cap < n * e->B) {
         cudaStreamSynchronize(st);
         cudaFree(e->prompt);
         ITB_CUDA_RET(c, cudaMalloc(&e->prompt, n * e->B * 4), 1);
         e->prompt_cap = n * e->B;
     }
-    std::vector<int32_t> tr(n * e->B);  // [t][b]
-    for (size_t b = 0; b < e->B; ++b)
-        for (size_t t = 0; t < n; ++t) {
-            if (tokens[b * n + t] >= e->m->d.n_vocab) { itb_fail_msg(c, "token id out of range"); return 1; }
-            tr[t * e->B + b] = (int32_t)tokens[b * n + t];
-        }
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, st), 1);
     cudaEventRecord(e->ev0, st);
-    for (size_t t = 0; t < n; ++t) {
-        cudaMemcpyAsync(e->tokens, e->prompt + t * e->B, e->B * 4, cudaMemcpyDeviceToDevice, st);
-        if (!run_steps(e, 1, false)) return 1;
+    off = 0;
+    for (size_t t0 = 0; t0 < n; t0 += chunk) {
+        const size_t nt = std::min(chunk, n - t0);
+        if (stepwise || (e->B == 1 && nt == 1)) {
+            cudaMemcpyAsync(e->tokens, e->prompt + off, e->B * 4, cudaMemcpyDeviceToDevice, st);
+            if (!run_steps(e, 1, false)) return 1;
+        } else {
+            c->launches += enqueue_rows(e, st, (int)e->B, (int)nt, e->prompt + off);
+            e->last_n_tok = (uint32_t)nt;
+            for (uint32_t b = 0; b < e->B; ++b) e->host_pos[b] += (uint32_t)nt;
+        }
+        off += nt * e->B;
     }
     cudaEventRecord(e->ev1, st);
     if (logits_out) cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->m->d.n_vocab * 4, cudaMemcpyDeviceToHost, st);
@@ -693,9 +856,13 @@ extern "C" long itb_engine_generate(itb_engine* e, const uint32_t* prompt, size_
 }
 
 extern "C" int itb_engine_read_routes(itb_engine* e, int32_t* ids, size_t cap) {
-    size_t n = (size_t)e->m->d.n_layer * e->B * e->m->d.n_expert_used;
+    const size_t K = e->m->d.n_expert_used, per = (size_t)e->B * K, n = (size_t)e->m->d.n_layer * per;
     if (cap < n) { itb_fail_msg(e->c, "read_routes: buffer too small"); return 1; }
-    ITB_CUDA_RET(e->c, cudaMemcpy(ids, e->route_ids, n * 4, cudaMemcpyDeviceToHost), 1);
+    ITB_CUDA_RET(e->c, cudaStreamSynchronize(e->c->stream), 1);
+    const size_t nt = e->last_n_tok;   // the last pass held nt tokens per sequence: report each sequence's last one
+    for (uint32_t il = 0; il < e->m->d.n_layer; ++il)
+        for (uint32_t b = 0; b < e->B; ++b)
+            ITB_CUDA_RET(e->c, cudaMemcpy(ids + il * per + b * K, e->route_ids + ((size_t)il * e->R + b * nt + nt - 1) * K, K * 4, cudaMemcpyDeviceToHost), 1);
     return 0;
 }
 extern "C" int itb_engine_read_ssm_state(itb_engine* e, uint32_t seq, uint32_t il, float* out, size_t len) {
@@ -716,6 +883,7 @@ extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, it
     cudaStream_t st = c->stream;
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + 1 > e->n_ctx) { itb_fail_msg(c, "context overflow: the step would write past n_ctx"); return 1; }
+    if (e->B != 1) { itb_fail_msg(c, "profile_step: single-sequence engines only"); return 1; }
     if (!ensure_graph(e)) return 1;  // function attributes are set during capture
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     StepProf prof;
@@ -738,4 +906,10 @@ extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, it
     for (size_t k = 0; k < n; ++k) out[k] = acc[k];
     if (n_out) *n_out = n;
     return 0;
+}
+
+extern "C" int itb_engine_debug_stamps(itb_engine* e, long long* out, size_t n) {
+    if (!e->stamps) return 1;
+    cudaStreamSynchronize(e->c->stream);
+    return cudaMemcpy(out, e->stamps, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
 }

@@ -23,12 +23,15 @@ struct InProj {
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
+    long long* stamps;                             // debug: clock64 at phase boundaries of block 0 warp 0
 };
+#define STAMP(i) do { if (p.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) p.stamps[i] = clock64(); } while (0)
 
 __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_embd, nb = n / 32, gsh = lanes_shift(nb);
     const int b = blockIdx.y, wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    STAMP(0);
     double* red = (double*)smem;
     float* xn = (float*)(red + 32);
     int8_t* xq = (int8_t*)(xn + n);
@@ -56,8 +59,11 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = lane; i < nr * p.conv_kernel; i += 32) cpre[(i / p.conv_kernel) * 8 + keep + i % p.conv_kernel] = cw[i];
         conv_lo = r0;
     }
+    STAMP(1);
     block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
+    STAMP(2);
     block_quant_q8(xn, n, xq, xs);
+    STAMP(3);
     if (p.xq_out && blockIdx.x == 0) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
         for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
@@ -91,6 +97,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         }
         base += p.q[m].n_out;
     }
+    STAMP(4);
     // F32 rows. Serial-k mode: units of 32 rows, unit u on warp 0 of block u (it owns the tile). Otherwise one
     // row per warp, handed out from the far end of the grid's warps.
     if (p.exact) {
@@ -120,6 +127,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
             rbase = (rbase + p.f[m].n_out) % ngw;
         }
     }
+    STAMP(5);
 }
 // br a multiple of the pass size 2 * (32 >> gsh)
 size_t in_proj_smem(int n, int exact, int br) {
@@ -577,7 +585,7 @@ __global__ void __launch_bounds__(256) k_argmax_partial(const float* logits, int
     }
 }
 __global__ void k_argmax_advance(const float* pv, const int* pi, int n_part, int32_t* tokens, int* pos, int32_t* next_out,
-                                 int32_t* history, int* step_counter, int n_seq) {
+                                 int32_t* history, int history_cap, int* step_counter, int n_seq) {
     int b = blockIdx.x, lane = threadIdx.x;
     float bv = -INFINITY; int bi = 0x7fffffff;
     for (int i = lane; i < n_part; i += 32) argmax_merge(bv, bi, pv[(size_t)b * n_part + i], pi[(size_t)b * n_part + i]);
@@ -587,7 +595,7 @@ __global__ void k_argmax_advance(const float* pv, const int* pi, int n_part, int
         next_out[b] = bi;
         pos[b] += 1;
         int s = step_counter[b];
-        if (history) history[(size_t)s * n_seq + b] = bi;
+        if (history && s < history_cap) history[(size_t)s * n_seq + b] = bi;
         step_counter[b] = s + 1;
     }
 }

@@ -1,6 +1,7 @@
 // Device kernels shared by the op-level seam (itb_ops.cu) and the fused engine (itb_engine.cu).
 #pragma once
 #include "itb_gemv.cuh"
+#include "itb_mma.cuh"
 
 namespace {  // each translation unit gets its own copy of these kernels
 
@@ -317,6 +318,38 @@ __global__ void k_matmul_fp4(DevFp4 w, const int32_t* ids, int n_used, int rows_
     float* o = out + i * w.n_out;
     fp4_rows<RP>(nib, sc, w.n_in, b0 + r0, b0 + r1, xq, xs, terms, gsh, [&](int row, float v) { o[row] = has_s2 ? v * s2 : v; });
 }
+
+// Multi-token matmuls on the int8 MMA path: grid (row tiles of 128, token tiles of 32), block 256.
+// mode 0: out[t][row] = v; mode 1: out[t][row] += v (residual add).
+__global__ void __launch_bounds__(256) k_gemm_q8(DevQ8 w, const int8_t* xq, const float* xs, int n_tok, float* out, size_t out_stride, int mode) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    int8_t* sq = (int8_t*)smem;
+    float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(w.n_in));
+    const int t0 = blockIdx.y * MMA_TOK, r0 = blockIdx.x * MMA_ROWS + (threadIdx.x >> 5) * 16;
+    mma_stage_act(xq, xs, w.n_in, t0, n_tok, sq, ss);
+    if (r0 >= w.n_out) return;
+    float acc[4][4];
+    mma_q8_rows16(w, r0, sq, ss, acc);
+    mma_foreach(acc, r0, w.n_out, [&](int t, int row, float v) {
+        if (t0 + t < n_tok) { float* o = out + (size_t)(t0 + t) * out_stride + row; *o = mode ? *o + v : v; }
+    });
+}
+// Dense NVFP4 matrix (one expert), same tiling; `s2` multiplies the result when has_s2 (the tensor's second scale).
+__global__ void __launch_bounds__(256) k_gemm_fp4(const uint8_t* nib, const uint8_t* sc, int k, int n_rows, const int8_t* xq, const float* xs,
+                                                  int n_tok, float* out, size_t out_stride, float s2, int has_s2) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    int8_t* sq = (int8_t*)smem;
+    float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(k));
+    const int t0 = blockIdx.y * MMA_TOK, r0 = blockIdx.x * MMA_ROWS + (threadIdx.x >> 5) * 16;
+    mma_stage_act(xq, xs, k, t0, n_tok, sq, ss);
+    if (r0 >= n_rows) return;
+    float acc[4][4];
+    mma_fp4_rows16(nib, sc, k, n_rows, r0, sq, ss, acc);
+    mma_foreach(acc, r0, n_rows, [&](int t, int row, float v) {
+        if (t0 + t < n_tok) out[(size_t)(t0 + t) * out_stride + row] = has_s2 ? v * s2 : v;
+    });
+}
+static inline size_t gemm_smem(int k) { return (size_t)MMA_TOK * mma_act_stride(k) + (size_t)MMA_TOK * (k / 32) * 4; }
 
 template <bool EXACT>
 __global__ void k_matmul_f32(DevF32 w, const float* x, float* out) {

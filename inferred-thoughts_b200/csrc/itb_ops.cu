@@ -154,6 +154,15 @@ static bool quantize_rows(itb_ctx* c, const float* xd, size_t n_rows, size_t n_i
 
 static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od) {
     DevQ8 dw{(const int8_t*)w->a, (const uint16_t*)w->b, (int)w->n_in, (int)w->n_out};
+    if (n_tok >= 2 && w->n_in % 32 == 0 && gemm_smem((int)w->n_in) <= 200 * 1024) {
+        // several tokens: every weight row is read once per 32 tokens, on the int8 tensor-core path
+        size_t sm = gemm_smem((int)w->n_in);
+        cudaFuncSetAttribute(k_gemm_q8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        dim3 g((unsigned)((w->n_out + MMA_ROWS - 1) / MMA_ROWS), (unsigned)((n_tok + MMA_TOK - 1) / MMA_TOK));
+        k_gemm_q8<<<g, 256, sm, c->stream>>>(dw, c->xq, c->xs, (int)n_tok, od, w->n_out, 0);
+        ITB_LAUNCHED(c);
+        return;
+    }
     int nb = (int)w->n_in / 32, gsh = lanes_shift(nb), nw = 8;
     int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);
     if (gx < 1) gx = 1;
@@ -166,6 +175,15 @@ static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od)
 
 // ids==nullptr: dense NVFP4 matrix, one "pair" per token reading its own row.
 static void launch_fp4(itb_ctx* c, const WeightEntry* w, const int32_t* ids, size_t n_pairs, int n_used, int rows_mode, float* od) {
+    if (!ids && n_pairs >= 2 && gemm_smem((int)w->n_in) <= 200 * 1024) {
+        size_t sm = gemm_smem((int)w->n_in);
+        cudaFuncSetAttribute(k_gemm_fp4, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        dim3 g((unsigned)((w->n_out + MMA_ROWS - 1) / MMA_ROWS), (unsigned)((n_pairs + MMA_TOK - 1) / MMA_TOK));
+        k_gemm_fp4<<<g, 256, sm, c->stream>>>((const uint8_t*)w->a, (const uint8_t*)w->b, (int)w->n_in, (int)w->n_out, c->xq, c->xs,
+                                             (int)n_pairs, od, w->n_out, 1.0f, 0);
+        ITB_LAUNCHED(c);
+        return;
+    }
     DevFp4 dw{(const uint8_t*)w->a, (const uint8_t*)w->b, w->scale2, (int)w->n_in, (int)w->n_out, (int)w->n_expert, 0};
     int nb = (int)w->n_in / 32, nsb = (int)w->n_in / 16, gsh = lanes_shift(nb), nw = 8;
     int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);

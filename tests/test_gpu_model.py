@@ -115,18 +115,59 @@ def test_loaded_tensors_equal_generated_tensors(oracle, gpu):
 
 
 def test_batch_of_sequences_equals_single_sequences(oracle, gpu):
+    """Three sequences in one engine (multi-row passes: int8-MMA matmuls, per-sequence state and KV) give the bits the
+    same sequences give alone, through prefill and through decode steps."""
     from inferred_thoughts_b200 import host
     ops, model = gpu
     prompts = np.stack([prompt_ids(10 + i, 12, TINY["n_vocab"]) for i in range(3)])
     eb = host.Engine(model, 64, 3)
     logits_b = eb.prefill(prompts)
     ops.check()
+    singles = [host.Engine(model, 64, 1) for _ in range(3)]
     for i in range(3):
-        e1 = host.Engine(model, 64, 1)
-        l1 = e1.prefill(prompts[i])
+        l1 = singles[i].prefill(prompts[i])
         assert l1.view(np.uint32).tolist() == logits_b[i].view(np.uint32).tolist(), i
-        e1.close()
+    toks = np.argmax(logits_b, 1).astype(np.uint32)
+    for step in range(4):
+        lb, nb = eb.decode(toks)
+        for i in range(3):
+            l1, n1 = singles[i].decode([toks[i]])
+            assert l1[0].view(np.uint32).tolist() == lb[i].view(np.uint32).tolist(), (step, i)
+            assert n1[0] == nb[i]
+        toks = nb
+    for i in range(3):
+        singles[i].close()
     eb.close()
+
+
+def test_multi_row_prefill_equals_token_by_token(oracle, gpu):
+    """Prefill in multi-row passes == the same tokens fed one at a time, to the bit: logits, recurrent state, and the
+    decode steps that follow (the reference's own invariant, tests/qwen35.rs:94-139 there), and both equal the oracle."""
+    import os
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    prompt = prompt_ids(3, 50, TINY["n_vocab"])
+    e1, e2 = host.Engine(model, 128, 1), host.Engine(model, 128, 1)
+    a = e1.prefill(prompt)
+    os.environ["ITB_PREFILL_STEPWISE"] = "1"
+    try:
+        b = e2.prefill(prompt)
+    finally:
+        del os.environ["ITB_PREFILL_STEPWISE"]
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    for il in range(3):
+        assert e1.read_ssm_state(il).view(np.uint32).tolist() == e2.read_ssm_state(il).view(np.uint32).tolist(), il
+    oracle.begin(128)
+    want = oracle.forward(prompt)
+    assert np.abs(want - a).max() <= 2e-2
+    t = int(np.argmax(a))
+    la, _ = e1.decode([t]); lb, _ = e2.decode([t])
+    assert la.view(np.uint32).tolist() == lb.view(np.uint32).tolist()
+    # a second chunk appended after the first (split prefill == single prefill, tests/kv_cache.rs:109-133 there)
+    e3 = host.Engine(model, 128, 1)
+    e3.prefill(prompt[:21]); c = e3.prefill(prompt[21:])
+    assert c.view(np.uint32).tolist() == a.view(np.uint32).tolist()
+    e1.close(); e2.close(); e3.close()
 
 
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):

@@ -67,7 +67,8 @@ def nvfp4_weights(n_expert, n_out, n_in, seed):
     return keep(blk.reshape(-1)), keep(scale)
 
 
-@pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 96, 1), (4096, 40, 1), (512, 64, 3), (256, 33, 2), (128, 7, 1), (3072, 16, 1), (768, 24, 1)])
+@pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 96, 1), (4096, 40, 1), (512, 64, 3), (256, 33, 2), (128, 7, 1), (3072, 16, 1), (768, 24, 1),
+                                              (2048, 300, 33), (4096, 130, 70), (512, 17, 5), (3072, 144, 32)])
 def test_matmul_q8_0_exact(ops, n_in, n_out, n_tok):
     from inferred_thoughts_b200 import host
     wb = q8_weights(n_out, n_in, 10 + n_in)
@@ -78,7 +79,7 @@ def test_matmul_q8_0_exact(ops, n_in, n_out, n_tok):
     exact(out, want, "Q8_0 matmul")
 
 
-@pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 64, 1), (512, 48, 2), (256, 16, 1), (128, 9, 3), (768, 8, 1)])
+@pytest.mark.parametrize("n_in,n_out,n_tok", [(2048, 64, 1), (512, 48, 2), (256, 16, 1), (128, 9, 3), (768, 8, 1), (2048, 200, 40), (512, 130, 33)])
 def test_matmul_nvfp4_dense_exact(ops, n_in, n_out, n_tok):
     from inferred_thoughts_b200 import host
     wb, _ = nvfp4_weights(1, n_out, n_in, 20 + n_in)
