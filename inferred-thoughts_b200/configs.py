@@ -5,6 +5,11 @@ TINY = dict(n_layer=4, n_embd=256, n_head=4, n_head_kv=1, head_dim=64, n_vocab=1
             n_rot=16, ssm_d_conv=4, ssm_d_inner=256, ssm_d_state=64, ssm_dt_rank=4, ssm_n_group=2,
             full_attention_interval=4, n_expert=16, n_expert_used=4, expert_ff=128, shared_ff=128)
 
+# A small shape whose every matrix has k a multiple of 256, so the pipelined multi-row kernels (which need that) run in tests.
+MID = dict(n_layer=4, n_embd=512, n_head=4, n_head_kv=1, head_dim=64, n_vocab=1024, rope_theta=1e7, rms_eps=1e-6,
+           n_rot=16, ssm_d_conv=4, ssm_d_inner=512, ssm_d_state=128, ssm_dt_rank=4, ssm_n_group=2,
+           full_attention_interval=4, n_expert=64, n_expert_used=4, expert_ff=256, shared_ff=256)
+
 # cfg 2-4: 35B-A3B shape. 40 layers (3 GDN : 1 attention), 256 experts top-8 + shared.
 M35B = dict(n_layer=40, n_embd=2048, n_head=16, n_head_kv=2, head_dim=256, n_vocab=248320, rope_theta=1e7, rms_eps=1e-6,
             n_rot=64, ssm_d_conv=4, ssm_d_inner=4096, ssm_d_state=128, ssm_dt_rank=32, ssm_n_group=16,
@@ -15,7 +20,7 @@ L177B = dict(n_layer=48, n_embd=3072, n_head=32, n_head_kv=4, head_dim=256, n_vo
              n_rot=64, ssm_d_conv=4, ssm_d_inner=6144, ssm_d_state=128, ssm_dt_rank=48, ssm_n_group=16,
              full_attention_interval=4, n_expert=512, n_expert_used=10, expert_ff=768, shared_ff=768)
 
-SEEDS = dict(tiny=0, m35b=3, l177b=4)
+SEEDS = dict(tiny=0, mid=5, m35b=3, l177b=4)
 
 
 def with_layers(cfg, n_layer):

@@ -302,6 +302,7 @@ struct itb_engine {
     int32_t* history = nullptr; int* step_counter = nullptr; uint32_t history_cap = 0;
     int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr; long long* stamps = nullptr; int n_stamped = 0;
     int8_t *aq = nullptr, *hq = nullptr, *sq = nullptr; float *as = nullptr, *hs = nullptr, *ss = nullptr;  // producer-quantised activations
+    float *h_all = nullptr, *o_all = nullptr, *shd = nullptr, *qkvc2 = nullptr; int *pair_off = nullptr, *pair_list = nullptr;  // grouped experts (multi-row path)
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
     int n_split = 1, n_split_rows = 4;
     uint32_t R = 0;                                   // rows the multi-row pass can hold (>= B)
@@ -519,16 +520,33 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     uint64_t launches = 0;
     static bool attrs_set = false;
     if (!attrs_set) {
-        set_smem((const void*)k_gemm_q8, 200 * 1024);
+        set_smem((const void*)k_gemm_q8<4>, 200 * 1024); set_smem((const void*)k_gemm_q8<1>, 200 * 1024);
+        set_smem((const void*)k_glu_grouped, 200 * 1024); set_smem((const void*)k_down_grouped, 200 * 1024);
+        set_smem((const void*)k_tile_q8<2, 256>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<4, 256>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<2, 256>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<1, 256>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256>, 226 * 1024);
+        set_smem((const void*)k_glu_gemv, 100 * 1024); set_smem((const void*)k_down_gemv<4>, 100 * 1024); set_smem((const void*)k_down_gemv<8>, 100 * 1024);
         set_smem((const void*)k_matmul_f32<true>, 100 * 1024); set_smem((const void*)k_matmul_f32<false>, 100 * 1024);
-        set_smem((const void*)k_gdn_scan<32>, 100 * 1024);
         attrs_set = true;
     }
-    auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode) {
-        dim3 g((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (R + MMA_TOK - 1) / MMA_TOK);
-        k_gemm_q8<<<g, 256, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
+    // Pipelined tile kernels when k is a multiple of the chunk (every matrix of the 35B and 177B shapes); the
+    // direct-load MMA kernels otherwise.
+    const bool skinny = R <= 32;
+    auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R) {
+        const int k = w.n_in;
+        const bool skinny = R <= 32;
+        if (skinny && k % 256 == 0) {
+            const int ns = std::min(k / 256, TILE_STAGES);
+            k_tile_q8<2, 256><<<dim3((w.n_out + 63) / 64, (R + 31) / 32), 256, tile_smem<MK_Q8, 2, 256>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
+        } else if (!skinny && k % 256 == 0) {
+            const int ns = std::min(k / 256, TILE_STAGES);
+            k_tile_q8<4, 256><<<dim3((w.n_out + 63) / 64, (R + 63) / 64), 256, tile_smem<MK_Q8, 4, 256>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
+        } else if (skinny) k_gemm_q8<1><<<dim3((w.n_out + 63) / 64, 1), 512, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
+        else k_gemm_q8<4><<<dim3((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (R + MMA_TOK - 1) / MMA_TOK), 256, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
         launches++;
     };
+    auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode) { gemm_n(w, xq, xs, out, stride, mode, R); };
     auto f32mm = [&](const DevF32& w, const float* x, float* out) {
         const int nw = 4;
         dim3 g(std::max(1, std::min(2 * sms, (w.n_out + 31) / 32)), R);
@@ -549,12 +567,18 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             gemm(L.wgate, e->xq, e->xs, e->z, vd, 0);
             f32mm(L.ssm_alpha, e->xn, e->alpha);
             f32mm(L.ssm_beta, e->xn, e->beta);
-            k_conv_rows<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(e->conv_state + (size_t)rs * e->B * conv_stride, conv_stride, e->qkvc,
-                                                                       n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
-            k_gdn_pre<<<dim3(R, 2 * n_k + n_v), sk, 0, st>>>(e->qkvc, cd, e->alpha, e->beta, L.ssm_a, L.dt_bias, sk, n_k, n_v, d.rms_eps,
+            float* cst = e->conv_state + (size_t)rs * e->B * conv_stride;
+            k_conv_rows<<<dim3((cd + 127) / 128, R), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
+            k_conv_state<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(cst, conv_stride, e->qkvc, n_tok, cd, d.ssm_d_conv); launches++;
+            k_gdn_pre<<<dim3(R, 2 * n_k + n_v), sk, 0, st>>>(e->qkvc2, cd, e->alpha, e->beta, L.ssm_a, L.dt_bias, sk, n_k, n_v, d.rms_eps,
                                                             e->qh, e->kh, e->vh, e->gb); launches++;
-            k_gdn_scan<32><<<dim3(n_v, sk / 32, n_seq), 128, (size_t)(32 * (sk + 1) + 2 * sk) * 4, st>>>(
-                e->qh, e->kh, e->vh, e->gb, n_tok, sk, n_k, n_v, e->ssm_state + (size_t)rs * e->B * state_stride, state_stride, e->core); launches++;
+            {
+                const dim3 gs(n_v, sk / 32, n_seq);
+                float* sst = e->ssm_state + (size_t)rs * e->B * state_stride;
+                if (sk == 128) k_gdn_scan<128><<<gs, 32, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);
+                else k_gdn_scan<64><<<gs, 32, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);   // 64 or 128 only (checked at model creation)
+            }
+            launches++;
             k_gdn_post<<<dim3(R, n_v), sk, 0, st>>>(e->core, e->z, L.ssm_norm, sk, n_v, d.rms_eps, e->aq, e->as); launches++;
             gemm(L.ssm_out, e->aq, e->as, e->x, H, 1);
         } else {
@@ -572,15 +596,13 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             const float scale = 1.0f / sqrtf((float)d.head_dim);
             const int nwa = 8, ns = n_tok > 1 ? e->n_split_rows : e->n_split;
             const size_t smem_a = (size_t)nwa * 8 * 2 * 4 + (size_t)nwa * 8 * d.head_dim * 4;
-            for (int s = 0; s < n_seq; ++s) {
-                const size_t r0 = (size_t)s * n_tok, po = r0 * d.n_head * ns;
-                dim3 grid(d.n_head_kv, n_tok, ns);
-#define ATT_CASE(HD)                                                                                                       \
-    case HD:                                                                                                                \
-        set_smem((const void*)k_attn_partial<HD, 8>, smem_a);                                                               \
-        k_attn_partial<HD, 8><<<grid, nwa * 32, smem_a, st>>>(e->qn + r0 * qd, a.kslab + (size_t)s * a.slab_stride,         \
-            a.vslab + (size_t)s * a.slab_stride, kvd, 0, n_tok, d.n_head, d.n_head_kv, scale, c->kv_bf16, e->npos + r0,     \
-            e->part_acc + po * d.head_dim, e->part_ml + po * 2);                                                            \
+            {
+                dim3 grid(d.n_head_kv, R, ns);
+#define ATT_CASE(HD)                                                                                                          \
+    case HD:                                                                                                                   \
+        set_smem((const void*)k_attn_partial<HD, 8>, smem_a);                                                                  \
+        k_attn_partial<HD, 8><<<grid, nwa * 32, smem_a, st>>>(e->qn, a.kslab, a.vslab, kvd, 0, n_tok, d.n_head, d.n_head_kv,    \
+            scale, c->kv_bf16, e->npos, e->part_acc, e->part_ml, n_tok, a.slab_stride);                                        \
         break;
                 switch (d.head_dim) { ATT_CASE(64) ATT_CASE(128) ATT_CASE(256) }
 #undef ATT_CASE
@@ -596,40 +618,66 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0);
         f32mm(L.gate_inp, e->xn, e->router);
         f32mm(L.shared_gate_inp, e->xn, e->shlogit);
-        MoeGlu g{};
-        g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
-        g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
-        g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
-        g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
-        k_moe_glu<<<dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, R), TPB, moe_glu_smem(d.n_expert, H), st>>>(g); launches++;
-        MoeDown w{};
-        w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
-        w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
         {
-            int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
-            int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-            dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), R);
-            size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
-            if (rp == 1) k_moe_down<1><<<grid, TPB, smem_d, st>>>(w);
-            else if (rp == 2) k_moe_down<2><<<grid, TPB, smem_d, st>>>(w);
-            else if (rp == 4) k_moe_down<4><<<grid, TPB, smem_d, st>>>(w);
-            else k_moe_down<8><<<grid, TPB, smem_d, st>>>(w);
+            const int K = d.n_expert_used, E = d.n_expert, ff = d.expert_ff, P = R * K;
+            int32_t* ids = e->route_ids + (size_t)il * e->R * K;
+            float* wts = e->route_w + (size_t)il * e->R * K;
+            k_route_rows<<<(R + 3) / 4, 128, (size_t)4 * ((E + 31) & ~31) * 4, st>>>(e->router, R, E, K, ids, wts); launches++;
+            if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
+            else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
             launches++;
+            if (R <= 64) {
+                // few rows per expert: fused dequant-and-dot per (pair, row), experts' pairs adjacent
+                k_glu_gemv<<<dim3(ff / 32, E), TPB, glu_gemv_smem(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->hq, e->hs); launches++;
+                const int slots = 32 >> lanes_shift(ff / 32), rp = slots == 1 ? 8 : slots <= 8 ? 4 : 1;
+                dim3 gd(std::max(1, (H + 8 * NWG - 1) / (8 * NWG)), E);
+                if (rp == 4) k_down_gemv<4><<<gd, TPB, down_gemv_smem(ff, 4), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
+                else if (rp == 8) k_down_gemv<8><<<gd, TPB, down_gemv_smem(ff, 8), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
+                else k_down_gemv<1><<<gd, TPB, down_gemv_smem(ff, 1), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
+                launches++;
+            } else {
+                // tokens per expert decide the tile width: 16-, 32- or 64-token tiles (a tile's empty columns cost as much as full ones)
+                const bool tile_w = H % 256 == 0 && ff % 256 == 0;
+                const int per_e = (P + E - 1) / E, nj = per_e <= 16 ? 1 : per_e <= 32 ? 2 : 4;
+                const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
+                const dim3 gg(E, (ff + 63) / 64), gdn(E, (H + 63) / 64);
+#define GLU_TILE(NJ) k_tile_glu<NJ, 256><<<gg, 256, tile_smem<MK_FP4, NJ, 256>(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all, ns_g)
+#define DOWN_TILE(NJ) k_tile_down<NJ, 256><<<gdn, 256, tile_smem<MK_FP4, NJ, 256>(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
+                if (tile_w) { if (nj == 1) GLU_TILE(1); else if (nj == 2) GLU_TILE(2); else GLU_TILE(4); }
+                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all);
+                launches++;
+                k_quant_rows<<<P, 128, 0, st>>>(e->h_all, ff, e->hq, e->hs); launches++;
+                if (tile_w) { if (nj == 1) DOWN_TILE(1); else if (nj == 2) DOWN_TILE(2); else DOWN_TILE(4); }
+#undef GLU_TILE
+#undef DOWN_TILE
+                else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
+                launches++;
+            }
+            k_shared_act_rows<<<R, 128, 0, st>>>(e->sg, e->su, d.shared_ff, e->sq, e->ss); launches++;
+            gemm(L.shared_down, e->sq, e->ss, e->shd, H, 0);
+            const size_t total = (size_t)R * H;
+            k_moe_finish_rows<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(e->x, H, e->o_all, wts, K, e->shd, e->shlogit, total); launches++;
         }
     }
     // LM head on each sequence's last row
     const float* xl = e->x;
     if (n_tok > 1) { k_gather_last<<<n_seq, 256, 0, st>>>(e->x, H, n_tok, e->xlast); launches++; xl = e->xlast; }
-    InProj hp{};
-    hp.x = xl; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
-    hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
-    {
-        const int pass_in = 2 * (32 >> lanes_shift(H / 32));
-        int gx = std::max(1, std::min(sms, ((int)d.n_vocab + 2 * NWG - 1) / (2 * NWG)));
-        int per_warp = ((int)d.n_vocab + gx * NWG - 1) / (gx * NWG) + 1;
-        hp.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
-        set_smem((const void*)k_in_proj, 200 * 1024);
-        k_in_proj<<<dim3(gx, n_seq), TPB, in_proj_smem(H, c->exact, hp.br), st>>>(hp); launches++;
+    if (n_seq > 1) {
+        // several sequences: one pass over the output matrix for all of them
+        k_norm_quant<<<n_seq, 256, smem_nq, st>>>(xl, m->output_norm, H, d.rms_eps, nullptr, e->xq, e->xs); launches++;
+        gemm_n(m->output, e->xq, e->xs, e->logits, d.n_vocab, 0, n_seq);
+    } else {
+        InProj hp{};
+        hp.x = xl; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
+        hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
+        {
+            const int pass_in = 2 * (32 >> lanes_shift(H / 32));
+            int gx = std::max(1, std::min(sms, ((int)d.n_vocab + 2 * NWG - 1) / (2 * NWG)));
+            int per_warp = ((int)d.n_vocab + gx * NWG - 1) / (gx * NWG) + 1;
+            hp.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+            set_smem((const void*)k_in_proj, 200 * 1024);
+            k_in_proj<<<dim3(gx, n_seq), TPB, in_proj_smem(H, c->exact, hp.br), st>>>(hp); launches++;
+        }
     }
     k_argmax_partial<<<dim3(ARGMAX_PARTS, n_seq), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
     if (n_tok > 1) { k_advance_pos<<<(n_seq + 127) / 128, 128, 0, st>>>(e->pos, n_seq, n_tok - 1); launches++; }
@@ -674,7 +722,9 @@ extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, i
               dalloc(E, &e->hq, R * K * d.expert_ff) && dalloc(E, &e->hs, R * K * d.expert_ff / 32) &&
               dalloc(E, &e->sq, R * d.shared_ff) && dalloc(E, &e->ss, R * d.shared_ff / 32) &&
               dalloc(E, &e->xn, R * H) && dalloc(E, &e->qh, R * key_dim) && dalloc(E, &e->kh, R * key_dim) && dalloc(E, &e->vh, R * vd) &&
-              dalloc(E, &e->gb, R * d.ssm_dt_rank * 2) && dalloc(E, &e->core, R * vd) && dalloc(E, &e->xlast, B * H);
+              dalloc(E, &e->gb, R * d.ssm_dt_rank * 2) && dalloc(E, &e->core, R * vd) && dalloc(E, &e->xlast, B * H) &&
+              dalloc(E, &e->h_all, R * K * d.expert_ff) && dalloc(E, &e->o_all, R * K * H) && dalloc(E, &e->shd, R * H) &&
+              dalloc(E, &e->qkvc2, R * cd) && dalloc(E, &e->pair_off, (size_t)d.n_expert + 1) && dalloc(E, &e->pair_list, R * K);
     if (!ok) { for (void* p : e->allocs) cudaFree(p); return 1; }
     e->host_pos.assign(B, 0);
     if (getenv("ITB_STAMPS")) dalloc(E, &e->stamps, 8 * 400);   // debug: phase clocks of k_in_proj

@@ -319,22 +319,29 @@ __global__ void k_matmul_fp4(DevFp4 w, const int32_t* ids, int n_used, int rows_
     fp4_rows<RP>(nib, sc, w.n_in, b0 + r0, b0 + r1, xq, xs, terms, gsh, [&](int row, float v) { o[row] = has_s2 ? v * s2 : v; });
 }
 
-// Multi-token matmuls on the int8 MMA path: grid (row tiles of 128, token tiles of 32), block 256.
+// Multi-token matmuls on the int8 MMA path: grid (row tiles, token tiles of 32). A warp owns 16 rows and NJ of
+// the tile's 4 groups of 8 tokens: NJ=4, 8 warps and 128 rows per block when there are many token tiles (prefill);
+// NJ=1, 16 warps and 64 rows per block for one token tile (batched decode), where the only other source of
+// parallelism is the rows and 4x the warps keep 4x the weight bytes in flight.
 // mode 0: out[t][row] = v; mode 1: out[t][row] += v (residual add).
-__global__ void __launch_bounds__(256) k_gemm_q8(DevQ8 w, const int8_t* xq, const float* xs, int n_tok, float* out, size_t out_stride, int mode) {
+template <int NJ>
+__global__ void __launch_bounds__(NJ == 4 ? 256 : 512) k_gemm_q8(DevQ8 w, const int8_t* xq, const float* xs, int n_tok, float* out, size_t out_stride, int mode) {
     extern __shared__ __align__(16) unsigned char smem[];
     int8_t* sq = (int8_t*)smem;
     float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(w.n_in));
-    const int t0 = blockIdx.y * MMA_TOK, r0 = blockIdx.x * MMA_ROWS + (threadIdx.x >> 5) * 16;
+    const int wid = threadIdx.x >> 5;
+    const int t0 = blockIdx.y * MMA_TOK;
+    const int r0 = NJ == 4 ? blockIdx.x * MMA_ROWS + wid * 16 : blockIdx.x * 64 + (wid >> 2) * 16, jb = NJ == 4 ? 0 : (wid & 3);
     mma_stage_act(xq, xs, w.n_in, t0, n_tok, sq, ss);
-    if (r0 >= w.n_out) return;
-    float acc[4][4];
-    mma_q8_rows16(w, r0, sq, ss, acc);
-    mma_foreach(acc, r0, w.n_out, [&](int t, int row, float v) {
+    if (r0 >= w.n_out || t0 + 8 * jb >= n_tok) return;
+    float acc[NJ][4];
+    mma_q8_rows16<NJ, NJ == 4 ? 4 : 8>(w, r0, sq, ss, jb, acc);
+    mma_foreach<NJ>(acc, r0, w.n_out, jb, [&](int t, int row, float v) {
         if (t0 + t < n_tok) { float* o = out + (size_t)(t0 + t) * out_stride + row; *o = mode ? *o + v : v; }
     });
 }
-// Dense NVFP4 matrix (one expert), same tiling; `s2` multiplies the result when has_s2 (the tensor's second scale).
+// Dense NVFP4 matrix (one expert), 128 rows x 32 tokens per block; `s2` multiplies the result when has_s2 (the
+// tensor's second scale).
 __global__ void __launch_bounds__(256) k_gemm_fp4(const uint8_t* nib, const uint8_t* sc, int k, int n_rows, const int8_t* xq, const float* xs,
                                                   int n_tok, float* out, size_t out_stride, float s2, int has_s2) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -344,8 +351,8 @@ __global__ void __launch_bounds__(256) k_gemm_fp4(const uint8_t* nib, const uint
     mma_stage_act(xq, xs, k, t0, n_tok, sq, ss);
     if (r0 >= n_rows) return;
     float acc[4][4];
-    mma_fp4_rows16(nib, sc, k, n_rows, r0, sq, ss, acc);
-    mma_foreach(acc, r0, n_rows, [&](int t, int row, float v) {
+    mma_fp4_rows16<4, 8>(nib, sc, k, n_rows, r0, sq, ss, 0, acc);
+    mma_foreach<4>(acc, r0, n_rows, 0, [&](int t, int row, float v) {
         if (t0 + t < n_tok) out[(size_t)(t0 + t) * out_stride + row] = has_s2 ? v * s2 : v;
     });
 }
@@ -378,9 +385,13 @@ constexpr int ATTN_MIN_SPLIT = 64;   // a split never covers fewer positions tha
 template <int HD, int MAXG>
 __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint16_t* vslab, int kv_dim, int n_pos_last, int n_q,
                                int n_head, int n_head_kv, float scale, int bf16, const int* n_pos_dev,
-                               float* part_acc, float* part_ml) {
+                               float* part_acc, float* part_ml, int rows_per_seq = 0, size_t slab_stride = 0) {
     constexpr int DPL = HD / 32;  // dims per lane
     int hk = blockIdx.x, t = blockIdx.y, sp = blockIdx.z, n_split = gridDim.z;
+    if (rows_per_seq > 0) {       // rows of several sequences in one launch: row t reads the slabs of sequence t / rows_per_seq
+        const size_t so = (size_t)(t / rows_per_seq) * slab_stride;
+        kslab += so; vslab += so;
+    }
     int group = n_head / n_head_kv;
     int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     int n_pos = n_pos_dev ? n_pos_dev[t] : n_pos_last - n_q + 1 + t;

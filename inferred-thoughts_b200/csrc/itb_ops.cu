@@ -157,9 +157,9 @@ static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od)
     if (n_tok >= 2 && w->n_in % 32 == 0 && gemm_smem((int)w->n_in) <= 200 * 1024) {
         // several tokens: every weight row is read once per 32 tokens, on the int8 tensor-core path
         size_t sm = gemm_smem((int)w->n_in);
-        cudaFuncSetAttribute(k_gemm_q8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+        cudaFuncSetAttribute(k_gemm_q8<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
         dim3 g((unsigned)((w->n_out + MMA_ROWS - 1) / MMA_ROWS), (unsigned)((n_tok + MMA_TOK - 1) / MMA_TOK));
-        k_gemm_q8<<<g, 256, sm, c->stream>>>(dw, c->xq, c->xs, (int)n_tok, od, w->n_out, 0);
+        k_gemm_q8<4><<<g, 256, sm, c->stream>>>(dw, c->xq, c->xs, (int)n_tok, od, w->n_out, 0);
         ITB_LAUNCHED(c);
         return;
     }

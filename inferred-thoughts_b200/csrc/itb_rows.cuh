@@ -6,6 +6,7 @@
 // reference asserts of its own backends (tests/qwen35.rs:94-139 there).
 #pragma once
 #include "itb_kernels.cuh"
+#include "itb_tile.cuh"
 
 namespace {
 
@@ -26,27 +27,36 @@ __global__ void __launch_bounds__(256) k_norm_quant(const float* x, const float*
     }
 }
 
-// Depthwise causal conv over the tokens of each sequence in order (src/ops/naive.rs:275-315); writes the
-// PRE-activation sum in place and leaves the window advanced. grid (ceil(nc/128), n_seq).
-__global__ void k_conv_rows(float* state, size_t state_stride, float* x, int n_tok, int nc, const float* w, int kernel) {
+// Depthwise causal conv (src/ops/naive.rs:275-315), every (row, channel) on its own thread: the window of row t is
+// the sequence's earlier rows of this pass, or the saved state where it reaches before the pass. Writes the
+// PRE-activation sum to `out` (the input rows stay intact for the neighbours). grid (ceil(nc/128), rows).
+__global__ void k_conv_rows(const float* state, size_t state_stride, const float* x, float* out, int n_tok, int nc, const float* w, int kernel) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= nc) return;
+    const size_t r = blockIdx.y;
+    const int s = (int)(r / n_tok), t = (int)(r % n_tok), keep = kernel - 1;
+    const float* st = state + (size_t)s * state_stride + (size_t)c * keep;
+    float sum = 0.0f;
+    for (int k = 0; k < keep; ++k) {
+        const int idx = t - keep + k;
+        const float past = idx >= 0 ? x[((size_t)s * n_tok + idx) * nc + c] : st[keep + idx];
+        sum += past * w[(size_t)c * kernel + k];
+    }
+    sum += x[r * nc + c] * w[(size_t)c * kernel + keep];
+    out[r * nc + c] = sum;
+}
+// The window each sequence leaves behind: its last kernel-1 inputs, oldest first. grid (ceil(nc/128), n_seq).
+__global__ void k_conv_state(float* state, size_t state_stride, const float* x, int n_tok, int nc, int kernel) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;
     if (c >= nc) return;
     const int keep = kernel - 1;
     float* st = state + (size_t)s * state_stride + (size_t)c * keep;
-    float past[8], wt[8];
-    for (int k = 0; k < keep; ++k) past[k] = st[k];
-    for (int k = 0; k < kernel; ++k) wt[k] = w[(size_t)c * kernel + k];
-    for (int t = 0; t < n_tok; ++t) {
-        float* px = x + ((size_t)s * n_tok + t) * nc + c;
-        const float xv = *px;
-        float sum = 0.0f;
-        for (int k = 0; k < keep; ++k) sum += past[k] * wt[k];
-        sum += xv * wt[keep];
-        *px = sum;
-        for (int k = 0; k + 1 < keep; ++k) past[k] = past[k + 1];
-        past[keep - 1] = xv;
+    float nv[8];
+    for (int k = 0; k < keep; ++k) {
+        const int idx = n_tok - keep + k;
+        nv[k] = idx >= 0 ? x[((size_t)s * n_tok + idx) * nc + c] : st[keep + idx];
     }
-    for (int k = 0; k < keep; ++k) st[k] = past[k];
+    for (int k = 0; k < keep; ++k) st[k] = nv[k];
 }
 
 // Everything of the GatedDeltaNet block that does not depend on the state, per row: SiLU of the conv sums,
@@ -83,40 +93,87 @@ __global__ void k_gdn_pre(const float* conv, int cd, const float* alpha, const f
     }
 }
 
-// The recurrence itself (src/ops/naive.rs:109-132): block = (value head, slice of ROWS value rows, sequence), one
-// thread per value row, keys walked serially, the slice of state held in shared memory across the pass's tokens.
-template <int ROWS>
-__global__ void k_gdn_scan(const float* qh, const float* kh, const float* vh, const float* gb, int n_tok, int sk, int n_k, int n_v,
-                           float* state, size_t state_stride, float* out) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    float* S = (float*)smem;             // [ROWS][sk+1]
-    float* kq = S + ROWS * (sk + 1);     // k[sk] | q[sk]
-    const int h = blockIdx.x, j0 = blockIdx.y * ROWS, s = blockIdx.z, khd = h % n_k, tid = threadIdx.x;
-    float* sg = state + (size_t)s * state_stride + ((size_t)h * sk + j0) * sk;
-    for (int i = tid; i < ROWS * sk; i += blockDim.x) S[(i / sk) * (sk + 1) + i % sk] = sg[i];
-    for (int t = 0; t < n_tok; ++t) {
-        const size_t r = (size_t)s * n_tok + t;
-        __syncthreads();
-        for (int i = tid; i < sk; i += blockDim.x) {
-            kq[i] = kh[(r * n_k + khd) * sk + i];
-            kq[sk + i] = qh[(r * n_k + khd) * sk + i];
-        }
-        __syncthreads();
-        if (tid < ROWS) {
-            const float g = gb[(r * n_v + h) * 2], b = gb[(r * n_v + h) * 2 + 1];
-            float* row = S + tid * (sk + 1);
-            float pred = 0.0f;
-#pragma unroll 4
-            for (int i = 0; i < sk; ++i) { float v = row[i] * g; row[i] = v; pred += v * kq[i]; }
-            const float d = b * (vh[(r * n_v + h) * sk + j0 + tid] - pred);
-            float o = 0.0f;
-#pragma unroll 4
-            for (int i = 0; i < sk; ++i) { float v = row[i] + kq[i] * d; row[i] = v; o += v * kq[sk + i]; }
-            out[(r * n_v + h) * sk + j0 + tid] = o;
+// The recurrence itself (src/ops/naive.rs:109-132): one warp per (value head, 32 value rows, sequence), one lane per
+// value row with that row of the state in REGISTERS across the pass's tokens, keys walked serially in the CPU
+// path's order. The state enters and leaves through a padded shared tile so global accesses stay coalesced;
+// the next token's k, q, v, g, beta are fetched while the current one is computed.
+template <int SK>
+__global__ void __launch_bounds__(32) k_gdn_scan(const float* qh, const float* kh, const float* vh, const float* gb, int n_tok, int n_k, int n_v,
+                                                 float* state, size_t state_stride, float* out) {
+    constexpr int PL = SK / 32;            // k (and q) values per lane
+    __shared__ float tile[32 * (SK + 1)];
+    __shared__ __align__(16) float kq[2 * SK];
+    const int h = blockIdx.x, j0 = blockIdx.y * 32, s = blockIdx.z, khd = h % n_k, lane = threadIdx.x;
+    float* sg = state + (size_t)s * state_stride + ((size_t)h * SK + j0) * SK;
+    {
+        float4 v[8];
+#pragma unroll 1
+        for (int i0 = 0; i0 < 32 * SK / 4; i0 += 8 * 32) {
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = ((const float4*)sg)[i0 + u * 32 + lane];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = (i0 + u * 32 + lane) * 4, r = e / SK, c = e % SK;
+                float* d = tile + r * (SK + 1) + c;
+                d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w;
+            }
         }
     }
-    __syncthreads();
-    for (int i = tid; i < ROWS * sk; i += blockDim.x) sg[i] = S[(i / sk) * (sk + 1) + i % sk];
+    __syncwarp();
+    float S[SK];
+#pragma unroll
+    for (int i = 0; i < SK; ++i) S[i] = tile[lane * (SK + 1) + i];
+    float kn[PL], qn[PL], vn, gn, bn;
+    auto fetch = [&](int t) {
+        const size_t r = (size_t)s * n_tok + t;
+#pragma unroll
+        for (int u = 0; u < PL; ++u) {
+            kn[u] = kh[(r * n_k + khd) * SK + u * 32 + lane];
+            qn[u] = qh[(r * n_k + khd) * SK + u * 32 + lane];
+        }
+        vn = vh[(r * n_v + h) * SK + j0 + lane];
+        gn = gb[(r * n_v + h) * 2]; bn = gb[(r * n_v + h) * 2 + 1];
+    };
+    fetch(0);
+#pragma unroll 1
+    for (int t = 0; t < n_tok; ++t) {
+        const float v = vn, g = gn, b = bn;
+        __syncwarp();
+#pragma unroll
+        for (int u = 0; u < PL; ++u) { kq[u * 32 + lane] = kn[u]; kq[SK + u * 32 + lane] = qn[u]; }
+        __syncwarp();
+        if (t + 1 < n_tok) fetch(t + 1);
+        float pred = 0.0f;
+#pragma unroll
+        for (int i = 0; i < SK; i += 4) {
+            const float4 k4 = *(const float4*)(kq + i);
+            S[i] = S[i] * g; pred += S[i] * k4.x;
+            S[i + 1] = S[i + 1] * g; pred += S[i + 1] * k4.y;
+            S[i + 2] = S[i + 2] * g; pred += S[i + 2] * k4.z;
+            S[i + 3] = S[i + 3] * g; pred += S[i + 3] * k4.w;
+        }
+        const float d = b * (v - pred);
+        float o = 0.0f;
+#pragma unroll
+        for (int i = 0; i < SK; i += 4) {
+            const float4 k4 = *(const float4*)(kq + i), q4 = *(const float4*)(kq + SK + i);
+            S[i] = S[i] + k4.x * d; o += S[i] * q4.x;
+            S[i + 1] = S[i + 1] + k4.y * d; o += S[i + 1] * q4.y;
+            S[i + 2] = S[i + 2] + k4.z * d; o += S[i + 2] * q4.z;
+            S[i + 3] = S[i + 3] + k4.w * d; o += S[i + 3] * q4.w;
+        }
+        out[(((size_t)s * n_tok + t) * n_v + h) * SK + j0 + lane] = o;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < SK; ++i) tile[lane * (SK + 1) + i] = S[i];
+    __syncwarp();
+#pragma unroll 1
+    for (int i0 = 0; i0 < 32 * SK / 4; i0 += 32) {
+        const int e = (i0 + lane) * 4, r = e / SK, c = e % SK;
+        const float* d = tile + r * (SK + 1) + c;
+        ((float4*)sg)[i0 + lane] = make_float4(d[0], d[1], d[2], d[3]);
+    }
 }
 
 // Gated RMSNorm of the recurrence's output, the SiLU(z) gate and the Q8_0 quantisation of the result
@@ -231,6 +288,324 @@ __global__ void k_advance_pos(int* pos, int n_seq, int by) {
 __global__ void k_gather_last(const float* x, int n, int n_tok, float* out) {
     const int s = blockIdx.x;
     for (int i = threadIdx.x; i < n; i += blockDim.x) out[(size_t)s * n + i] = x[((size_t)s * n_tok + n_tok - 1) * n + i];
+}
+
+}  // namespace
+
+// =====================================================================================================
+// Routed experts for many rows: route once per row, group the (row, pick) pairs by expert, and run each
+// expert's rows through the int8-MMA NVFP4 kernels so an expert's weights are read once per pass
+// (the reference groups the same way, kernels/moe.cuh:62-133 there; the order inside an expert is ascending
+// pair index, so results do not depend on scheduling).
+// =====================================================================================================
+namespace {
+
+// Softmax over all experts + top-k per row (src/model/qwen35.rs:1626-1638, src/ops/mod.rs:1191-1216). One warp per row.
+__global__ void k_route_rows(const float* router, int n_rows, int n_expert, int n_used, int32_t* ids_out, float* w_out) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    const int ne32 = (n_expert + 31) & ~31;
+    float* probs = (float*)smem + wid * ne32;
+    const int r = blockIdx.x * nw + wid;
+    if (r >= n_rows) return;
+    const float* lg = router + (size_t)r * n_expert;
+    float mx = -INFINITY;
+    for (int i = lane; i < n_expert; i += 32) mx = fmaxf(mx, lg[i]);
+    mx = warp_max(mx);
+    for (int i = lane; i < ne32; i += 32) probs[i] = i < n_expert ? exp_f(lg[i] - mx) : 0.0f;
+    __syncwarp();
+    float sum = 0.0f;
+    if (lane == 0) for (int i = 0; i < n_expert; ++i) sum += probs[i];
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (int i = lane; i < n_expert; i += 32) probs[i] /= sum;
+    __syncwarp();
+    int32_t ids[16];
+    float wts[16];
+    warp_topk_any(probs, n_expert, n_used, ids, wts);
+    if (lane == 0)
+        for (int k = 0; k < n_used; ++k) { ids_out[(size_t)r * n_used + k] = ids[k]; w_out[(size_t)r * n_used + k] = wts[k]; }
+}
+
+// Counting sort of the pairs by expert, ascending pair index inside an expert. One block, thread e owns expert e.
+// off: [n_expert + 1], list: [n_pairs] pair indices.
+__global__ void k_group_pairs(const int32_t* ids, int n_pairs, int n_expert, int* off, int* list) {
+    extern __shared__ int cnt[];
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n_pairs; ++i) c += ids[i] == e;
+        cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int acc = 0;
+        for (int e = 0; e < n_expert; ++e) { off[e] = acc; acc += cnt[e]; }
+        off[n_expert] = acc;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) {
+        int at = off[e];
+        for (int i = 0; i < n_pairs; ++i) if (ids[i] == e) list[at++] = i;
+    }
+}
+
+// Activation rows of up to 32 listed pairs into the MMA tile: pair p reads row p / div of (xq, xs).
+__device__ __forceinline__ void stage_pairs(const int8_t* xq, const float* xs, int k, const int* list, int n, int div, int8_t* sq, float* ss) {
+    const int nb = k / 32, stride = mma_act_stride(k);
+    for (int i = threadIdx.x; i < MMA_TOK * (k / 16); i += blockDim.x) {
+        int t = i / (k / 16), c = i % (k / 16);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < n) v = *(const uint4*)(xq + (size_t)(list[t] / div) * k + c * 16);
+        *(uint4*)(sq + (size_t)t * stride + c * 16) = v;
+    }
+    for (int i = threadIdx.x; i < MMA_TOK * nb; i += blockDim.x) {
+        int t = i / nb;
+        ss[i] = t < n ? xs[(size_t)(list[t] / div) * nb + i % nb] : 0.0f;
+    }
+    __syncthreads();
+}
+
+// Gate and up of one expert for its pairs, SiLU-gated: h[pair][row] (src/ops/mod.rs:1105-1117). grid (n_expert, ff/128).
+__global__ void __launch_bounds__(256) k_glu_grouped(DevFp4 gate, DevFp4 up, const int8_t* xq, const float* xs, int n_used,
+                                                     const int* off, const int* list, float* h) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int e = blockIdx.x, k = gate.n_in, ff = gate.n_out, nsb = k / 16;
+    const int el = e - gate.expert_lo;
+    const int p0 = off[e], p1 = off[e + 1];
+    if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
+    int8_t* sq = (int8_t*)smem;
+    float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(k));
+    const int r0 = blockIdx.y * MMA_ROWS + (threadIdx.x >> 5) * 16;
+    const size_t eo = (size_t)el * ff;
+    const bool has_g = gate.scale2 != nullptr, has_u = up.scale2 != nullptr;
+    const float sg2 = has_g ? gate.scale2[el] : 1.0f, su2 = has_u ? up.scale2[el] : 1.0f;
+    for (int t0 = p0; t0 < p1; t0 += MMA_TOK) {
+        const int n = min(MMA_TOK, p1 - t0);
+        __syncthreads();
+        stage_pairs(xq, xs, k, list + t0, n, n_used, sq, ss);
+        if (r0 < ff) {
+            float g[4][4], u[4][4];
+            mma_fp4_rows16<4, 8>(gate.nib + eo * (k / 2), gate.sc + eo * nsb, k, ff, r0, sq, ss, 0, g);
+            mma_fp4_rows16<4, 8>(up.nib + eo * (k / 2), up.sc + eo * nsb, k, ff, r0, sq, ss, 0, u);
+            const int lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int t = 8 * j + 2 * tq + (i & 1), row = r0 + gq + (i >> 1) * 8;
+                    if (t < n && row < ff) {
+                        float gv = has_g ? g[j][i] * sg2 : g[j][i], uv = has_u ? u[j][i] * su2 : u[j][i];
+                        h[(size_t)list[t0 + t] * ff + row] = silu_f(gv) * uv;
+                    }
+                }
+        }
+    }
+}
+
+// Down projection of one expert for its pairs: o[pair][row], times the expert's second scale
+// (src/ops/mod.rs:1049-1088). grid (n_expert, n_out/128). Activation rows are per pair (div = 1).
+__global__ void __launch_bounds__(256) k_down_grouped(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int e = blockIdx.x, k = down.n_in, n_out = down.n_out, nsb = k / 16;
+    const int el = e - down.expert_lo;
+    const int p0 = off[e], p1 = off[e + 1];
+    if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
+    int8_t* sq = (int8_t*)smem;
+    float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(k));
+    const int r0 = blockIdx.y * MMA_ROWS + (threadIdx.x >> 5) * 16;
+    const size_t eo = (size_t)el * n_out;
+    const bool has_s = down.scale2 != nullptr;
+    const float s2 = has_s ? down.scale2[el] : 1.0f;
+    for (int t0 = p0; t0 < p1; t0 += MMA_TOK) {
+        const int n = min(MMA_TOK, p1 - t0);
+        __syncthreads();
+        stage_pairs(hq, hs, k, list + t0, n, 1, sq, ss);
+        if (r0 < n_out) {
+            float acc[4][4];
+            mma_fp4_rows16<4, 8>(down.nib + eo * (k / 2), down.sc + eo * nsb, k, n_out, r0, sq, ss, 0, acc);
+            mma_foreach<4>(acc, r0, n_out, 0, [&](int t, int row, float v) {
+                if (t < n) o[(size_t)list[t0 + t] * n_out + row] = has_s ? v * s2 : v;
+            });
+        }
+    }
+}
+
+// Q8_0 quantisation of rows of f32 (block per row).
+__global__ void k_quant_rows(const float* x, int n, int8_t* xq, float* xs) {
+    const size_t r = blockIdx.x;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int b = wid; b < n / 32; b += nw) {
+        float d;
+        xq[r * n + b * 32 + lane] = warp_quant_q8(x[r * n + b * 32 + lane], &d);
+        if (lane == 0) xs[r * (n / 32) + b] = d;
+    }
+}
+// silu(gate) * up of the shared expert per row, quantised (src/model/qwen35.rs:1669-1678). block per row.
+__global__ void k_shared_act_rows(const float* sg, const float* su, int n, int8_t* q, float* s) {
+    const size_t r = blockIdx.x;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int b = wid; b < n / 32; b += nw) {
+        const size_t i = r * n + b * 32 + lane;
+        float d;
+        q[i] = warp_quant_q8(silu_f(sg[i]) * su[i], &d);
+        if (lane == 0) s[r * (n / 32) + b] = d;
+    }
+}
+// Weighted expert sum in pick order, gated shared expert, residual add (src/ops/mod.rs:1134-1171, src/model/qwen35.rs:1090).
+__global__ void k_moe_finish_rows(float* x, int n, const float* o, const float* wts, int n_used, const float* shared, const float* logit, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t r = i / n; const int j = (int)(i % n);
+    const float g = sigmoid_f(logit[r]);
+    float v = 0.0f;
+    for (int k = 0; k < n_used; ++k) v += wts[r * n_used + k] * o[(r * n_used + k) * n + j];
+    v += shared[r * n + j] * g;
+    x[i] += v;
+}
+
+}  // namespace
+
+// =====================================================================================================
+// Routed experts when an expert sees only a few rows (batched decode): below about eight rows per expert
+// the MMA tile wastes most of its columns and the per-element scaling costs more instructions than the
+// fused dequant-and-dot does, so each (pair, row) is a dp4a row-dot as in the one-token path, with the
+// pairs taken expert by expert so an expert's weights come from DRAM once and from cache after that.
+// =====================================================================================================
+namespace {
+
+constexpr int GEMV_PAIRS = 4;   // pairs staged per pass
+
+// grid (ff/32, n_expert), block NWG*32: 32 gate rows + 32 up rows of expert e for each of its pairs ->
+// h = silu(gate.x * s_g) * (up.x * s_u), quantised to Q8_0 (src/ops/mod.rs:1105-1117): hq[pair][ff], hs[pair][ff/32].
+__global__ void __launch_bounds__(NWG * 32) k_glu_gemv(DevFp4 gate, DevFp4 up, const int8_t* xq, const float* xs, int n_used,
+                                                       const int* off, const int* list, int8_t* hq, float* hs) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float s_gu[GEMV_PAIRS * 64];
+    __shared__ int s_pair[GEMV_PAIRS];
+    const int e = blockIdx.y, el = e - gate.expert_lo;
+    const int p0 = off[e], p1 = off[e + 1];
+    if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
+    const int n = gate.n_in, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = gate.n_out, upp = ff / 32;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
+    const int row0 = blockIdx.x * 32;
+    int8_t* xq_s = (int8_t*)smem;                                  // [GEMV_PAIRS][n]
+    float* xs_s = (float*)(xq_s + (size_t)GEMV_PAIRS * n);         // [GEMV_PAIRS][nb]
+    float* terms = xs_s + GEMV_PAIRS * nb + wid * terms_floats(4, gsh, nsb);
+    const size_t eo = (size_t)el * ff;
+    const uint8_t* gn = gate.nib + eo * (n / 2); const uint8_t* gs = gate.sc + eo * nsb;
+    const uint8_t* un = up.nib + eo * (n / 2); const uint8_t* us = up.sc + eo * nsb;
+    const bool has_g = gate.scale2 != nullptr, has_u = up.scale2 != nullptr;
+    const float sg2 = has_g ? gate.scale2[el] : 1.0f, su2 = has_u ? up.scale2[el] : 1.0f;
+    for (int t0 = p0; t0 < p1; t0 += GEMV_PAIRS) {
+        const int np = min(GEMV_PAIRS, p1 - t0);
+        __syncthreads();
+        if (tid < np) s_pair[tid] = list[t0 + tid];
+        for (int i = tid; i < np * (n / 16); i += blockDim.x) {
+            const int pr = i / (n / 16), c = i % (n / 16);
+            ((uint4*)xq_s)[pr * (n / 16) + c] = ((const uint4*)(xq + (size_t)(list[t0 + pr] / n_used) * n))[c];
+        }
+        for (int i = tid; i < np * nb; i += blockDim.x) xs_s[i] = xs[(size_t)(list[t0 + i / nb] / n_used) * nb + i % nb];
+        __syncthreads();
+        int k0, k1;
+        share(np * 64, nw, wid, k0, k1);
+        rows_list<MK_FP4, 4>(k1 - k0, n, terms, gsh,
+            [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+                const int kk = k0 + k, pr = kk >> 6, rd = kk & 63, row = row0 + (rd & 31);
+                pa = (rd < 32 ? gn : un) + (size_t)row * (n / 2);
+                pb = (rd < 32 ? gs : us) + (size_t)row * nsb;
+                q = xq_s + (size_t)pr * n; s = xs_s + pr * nb;
+            },
+            [&](int k, float v) { s_gu[k0 + k] = v; });
+        __syncthreads();
+        if (wid < np) {
+            float g = s_gu[wid * 64 + lane], u = s_gu[wid * 64 + 32 + lane];
+            if (has_g) g = g * sg2;
+            if (has_u) u = u * su2;
+            float dq;
+            const int8_t q = warp_quant_q8(silu_f(g) * u, &dq);
+            const size_t pi = (size_t)s_pair[wid];
+            hq[pi * ff + row0 + lane] = q;
+            if (lane == 0) hs[pi * upp + blockIdx.x] = dq;
+        }
+    }
+}
+static inline size_t glu_gemv_smem(int n) {
+    const int nb = n / 32, gsh = lanes_shift(nb);
+    return (size_t)GEMV_PAIRS * n + (size_t)GEMV_PAIRS * nb * 4 + (size_t)NWG * terms_floats(4, gsh, n / 16) * 4 + 64;
+}
+
+// grid (row chunks, n_expert), block NWG*32: the down rows of expert e for each of its pairs, times the
+// expert's second scale (src/ops/mod.rs:1049-1088): o[pair][row].
+template <int RP>
+__global__ void __launch_bounds__(NWG * 32) k_down_gemv(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ int s_pair[GEMV_PAIRS];
+    const int e = blockIdx.y, el = e - down.expert_lo;
+    const int p0 = off[e], p1 = off[e + 1];
+    if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
+    const int ff = down.n_in, nbf = ff / 32, nsb = ff / 16, gf = lanes_shift(nbf), n_out = down.n_out;
+    const int tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5;
+    int8_t* hq_s = (int8_t*)smem;                                  // [GEMV_PAIRS][ff]
+    float* hs_s = (float*)(hq_s + (size_t)GEMV_PAIRS * ff);        // [GEMV_PAIRS][nbf]
+    float* terms = hs_s + GEMV_PAIRS * nbf + wid * terms_floats(RP, gf, nsb);
+    const bool has_s = down.scale2 != nullptr;
+    const float s2 = has_s ? down.scale2[el] : 1.0f;
+    int b0, b1, r0, r1;
+    share(n_out, gridDim.x, blockIdx.x, b0, b1);
+    share(b1 - b0, nw, wid, r0, r1);
+    r0 += b0; r1 += b0;
+    const uint8_t* dn = down.nib + (size_t)el * n_out * (ff / 2);
+    const uint8_t* ds = down.sc + (size_t)el * n_out * nsb;
+    for (int t0 = p0; t0 < p1; t0 += GEMV_PAIRS) {
+        const int np = min(GEMV_PAIRS, p1 - t0);
+        __syncthreads();
+        if (tid < np) s_pair[tid] = list[t0 + tid];
+        for (int i = tid; i < np * (ff / 16); i += blockDim.x) {
+            const int pr = i / (ff / 16), c = i % (ff / 16);
+            ((uint4*)hq_s)[pr * (ff / 16) + c] = ((const uint4*)(hq + (size_t)list[t0 + pr] * ff))[c];
+        }
+        for (int i = tid; i < np * nbf; i += blockDim.x) hs_s[i] = hs[(size_t)list[t0 + i / nbf] * nbf + i % nbf];
+        __syncthreads();
+        rows_list<MK_FP4, RP>((r1 - r0) * np, ff, terms, gf,
+            [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+                const int row = r0 + k / np, pr = k % np;
+                pa = dn + (size_t)row * (ff / 2); pb = ds + (size_t)row * nsb;
+                q = hq_s + (size_t)pr * ff; s = hs_s + pr * nbf;
+            },
+            [&](int k, float v) { o[(size_t)s_pair[k % np] * n_out + r0 + k / np] = has_s ? v * s2 : v; });
+    }
+}
+static inline size_t down_gemv_smem(int ff, int rp) {
+    const int gf = lanes_shift(ff / 32);
+    return (size_t)GEMV_PAIRS * ff + (size_t)GEMV_PAIRS * (ff / 32) * 4 + (size_t)NWG * terms_floats(rp, gf, ff / 16) * 4 + 64;
+}
+
+// Pairs grouped by expert without a serial scan: counts by shared-memory atomics, an exclusive scan, then each
+// pair takes the next free place of its expert. The order inside an expert depends on scheduling; results do
+// not, since every pair is computed on its own. One block.
+__global__ void __launch_bounds__(1024) k_group_pairs_fast(const int32_t* ids, int n_pairs, int n_expert, int* off, int* list) {
+    extern __shared__ int cnt[];    // [n_expert] counts, then cursors
+    __shared__ int s_off[1025];
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) atomicAdd(&cnt[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        // warp scan over experts in chunks of 32
+        int carry = 0;
+        for (int e0 = 0; e0 < n_expert; e0 += 32) {
+            const int e = e0 + threadIdx.x;
+            const int c = e < n_expert ? cnt[e] : 0;
+            int inc = c;
+            for (int o = 1; o < 32; o <<= 1) { int v = __shfl_up_sync(0xffffffffu, inc, o); if ((int)threadIdx.x >= o) inc += v; }
+            if (e < n_expert) { off[e] = carry + inc - c; s_off[e] = carry + inc - c; }
+            carry += __shfl_sync(0xffffffffu, inc, 31);
+        }
+        if (threadIdx.x == 0) off[n_expert] = carry;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_expert; e += blockDim.x) cnt[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) { const int e = ids[i]; list[s_off[e] + atomicAdd(&cnt[e], 1)] = i; }
 }
 
 }  // namespace

@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle_py as O
-from tests.util import TINY, cosine, host_dims, oracle_dims, prompt_ids
+from tests.util import MID, TINY, cosine, host_dims, oracle_dims, prompt_ids
 
 pytestmark = pytest.mark.gpu
 SEED = 0
@@ -146,7 +146,7 @@ def test_multi_row_prefill_equals_token_by_token(oracle, gpu):
     import os
     from inferred_thoughts_b200 import host
     ops, model = gpu
-    prompt = prompt_ids(3, 50, TINY["n_vocab"])
+    prompt = prompt_ids(3, 80, TINY["n_vocab"])   # 80 rows: the grouped MMA expert kernels; the 21/59 split below: the few-rows ones
     e1, e2 = host.Engine(model, 128, 1), host.Engine(model, 128, 1)
     a = e1.prefill(prompt)
     os.environ["ITB_PREFILL_STEPWISE"] = "1"
@@ -168,6 +168,78 @@ def test_multi_row_prefill_equals_token_by_token(oracle, gpu):
     e3.prefill(prompt[:21]); c = e3.prefill(prompt[21:])
     assert c.view(np.uint32).tolist() == a.view(np.uint32).tolist()
     e1.close(); e2.close(); e3.close()
+
+
+@pytest.fixture(scope="module")
+def mid():
+    """A shape with every k a multiple of 256: the pipelined (cp.async ring) multi-row kernels run, not the direct ones."""
+    from inferred_thoughts_b200 import host
+    om = O.OracleModel(oracle_dims(MID)); om.synth(5, threads=8)
+    ops = host.B200Ops(0, "exact=1")
+    model = host.Model(ops, host_dims(MID)); model.synth(5)
+    yield om, ops, model
+    ops.check()
+
+
+@pytest.mark.parametrize("n_tok", [70, 300, 640])
+def test_pipelined_rows_prefill_equals_token_by_token_and_oracle(mid, n_tok):
+    """One pass of n_tok rows: 70, 300 and 640 rows give the routed experts about 5, 19 and 40 rows each, i.e. the 16-, 32- and
+    64-token expert tiles; the dense tiles are 64 tokens wide with a ragged last tile in every case."""
+    import os
+    from inferred_thoughts_b200 import host
+    om, ops, model = mid
+    prompt = prompt_ids(4, n_tok, MID["n_vocab"])
+    os.environ["ITB_ROWS"] = "640"
+    try:
+        e1, e2 = host.Engine(model, 768, 1), host.Engine(model, 768, 1)
+    finally:
+        del os.environ["ITB_ROWS"]
+    a = e1.prefill(prompt)
+    os.environ["ITB_PREFILL_STEPWISE"] = "1"
+    try:
+        b = e2.prefill(prompt)
+    finally:
+        del os.environ["ITB_PREFILL_STEPWISE"]
+    ops.check()
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    L, K = MID["n_layer"], MID["n_expert_used"]
+    assert e1.read_routes(L, K).tolist() == e2.read_routes(L, K).tolist()
+    for il in range(3):
+        assert e1.read_ssm_state(il).view(np.uint32).tolist() == e2.read_ssm_state(il).view(np.uint32).tolist(), il
+    om.begin(768, log_routes=True)
+    want = om.forward(prompt)
+    assert om.route_log().reshape(L, len(prompt), K)[:, -1, :].tolist() == e1.read_routes(L, K)[:, 0, :].tolist()
+    err = np.abs(want - a).max()
+    print(f"mid prefill vs oracle: max-abs {err:.3e}, exact {(want == a).mean():.3f}")
+    assert err <= 2e-2 and cosine(want, a) >= 0.999 and int(np.argmax(want)) == int(np.argmax(a))
+    e1.close(); e2.close()
+
+
+@pytest.mark.parametrize("n_seq", [5, 33])
+def test_pipelined_rows_batched_decode_equals_single_sequences(mid, n_seq):
+    """n_seq <= 32 runs the 32-token tiles, 33 the 64-token ones; both must give each sequence the bits it gets alone."""
+    from inferred_thoughts_b200 import host
+    om, ops, model = mid
+    prompts = np.stack([prompt_ids(20 + i, 9, MID["n_vocab"]) for i in range(n_seq)])
+    eb = host.Engine(model, 64, n_seq)
+    logits_b = eb.prefill(prompts)
+    ops.check()
+    probe = sorted({0, n_seq // 2, n_seq - 1})
+    singles = {i: host.Engine(model, 64, 1) for i in probe}
+    for i in probe:
+        l1 = singles[i].prefill(prompts[i])
+        assert l1.view(np.uint32).tolist() == logits_b[i].view(np.uint32).tolist(), i
+    toks = np.argmax(logits_b, 1).astype(np.uint32)
+    for step in range(3):
+        lb, nb = eb.decode(toks)
+        for i in probe:
+            l1, n1 = singles[i].decode([toks[i]])
+            assert l1[0].view(np.uint32).tolist() == lb[i].view(np.uint32).tolist(), (step, i)
+            assert n1[0] == nb[i]
+        toks = nb
+    for i in probe:
+        singles[i].close()
+    eb.close()
 
 
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):
