@@ -142,7 +142,7 @@ def other_configs(host, model, dims, seed, hbm, args):
         eng.prefill(pr, want_logits=False)
         ms = eng.last_ms()
         out["prefill_5548"] = {"value": 5548 / (ms / 1e3), "unit": "tok/s", "ms": ms, "rows_per_pass": 512,
-                               "note": "multi-row passes, exact int8-MMA matmuls; routed experts still per (token, pick)"}
+                               "note": "512-row passes; exact int8-MMA tile matmuls (dense Q8_0 and expert-grouped NVFP4), serial-order GDN scan"}
         eng.close()
     except Exception as ex:
         out["prefill_5548"] = {"error": str(ex)}
@@ -177,6 +177,8 @@ def run_product(args, rank, world):
     device = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(device)
     dims = dict(configs.M35B)
+    if args.layers:
+        dims = configs.with_layers(dims, args.layers)   # profiling aid only: a line with "layers" set is not a bench number
     seed = configs.SEEDS["m35b"]
     kv = "bf16"
     ops = host.B200Ops(device, f"kv={kv},exact={args.exact}")
@@ -197,8 +199,10 @@ def run_product(args, rank, world):
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(device) if rank == 0 else None
+    torch.cuda.profiler.start()     # a profiler run with --profile-from-start off sees exactly the timed steps
     toks = eng.decode_loop(first, args.steps)
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     dev_ms = eng.last_ms()
     # ---- end to end through the C ABI: host token in, host token out, every step ----
     cur = toks[-1].copy()
@@ -230,7 +234,7 @@ def run_product(args, rank, world):
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 (int8 x int8 / e2m1 x int8 dots, f32 accumulate; f32 state)",
         "data": "synthetic (seeded Gaussian weights quantised to NVFP4 / Q8_0, uniform-random token ids)",
         "config": {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}", "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": kv,
-                   "n_pos_at_end": n_pos, "f32_dots": "serial-k" if args.exact else "tree", "parallelism": "replicas" if world > 1 else "single",
+                   "n_pos_at_end": n_pos, **({"layers": args.layers, "not_a_bench_number": True} if args.layers else {}), "f32_dots": "serial-k" if args.exact else "tree", "parallelism": "replicas" if world > 1 else "single",
                    "l2": "each step streams ~2.8 GB of weights, far beyond the 126 MB L2; no flush needed"},
         "e2e": {"value": world * B * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                 "api": "itb_engine_decode (host token ids in, host argmax ids out)"},
@@ -312,6 +316,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill and batch-32 measurements")
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens before the timed decode steps (BASELINE: 512)")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
+    ap.add_argument("--layers", type=int, default=0, help="profiling aid: the same shape with fewer layers (small device footprint for ncu captures)")
     args = ap.parse_args()
     global PROMPT
     PROMPT = args.prompt

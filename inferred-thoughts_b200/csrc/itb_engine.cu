@@ -522,11 +522,11 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     if (!attrs_set) {
         set_smem((const void*)k_gemm_q8<4>, 200 * 1024); set_smem((const void*)k_gemm_q8<1>, 200 * 1024);
         set_smem((const void*)k_glu_grouped, 200 * 1024); set_smem((const void*)k_down_grouped, 200 * 1024);
-        set_smem((const void*)k_tile_q8<2, 256>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256>, 226 * 1024);
-        set_smem((const void*)k_tile_glu<4, 256>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256>, 226 * 1024);
-        set_smem((const void*)k_tile_glu<2, 256>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256>, 226 * 1024);
-        set_smem((const void*)k_tile_glu<1, 256>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256>, 226 * 1024);
-        set_smem((const void*)k_glu_gemv, 100 * 1024); set_smem((const void*)k_down_gemv<4>, 100 * 1024); set_smem((const void*)k_down_gemv<8>, 100 * 1024);
+        set_smem((const void*)k_tile_q8<2, 256, 2>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<2, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256, 1>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<4, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256, 1>, 226 * 1024);
+        set_smem((const void*)k_tile_glu<4, 256, 2>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256, 2>, 226 * 1024);
         set_smem((const void*)k_matmul_f32<true>, 100 * 1024); set_smem((const void*)k_matmul_f32<false>, 100 * 1024);
         attrs_set = true;
     }
@@ -538,10 +538,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         const bool skinny = R <= 32;
         if (skinny && k % 256 == 0) {
             const int ns = std::min(k / 256, TILE_STAGES);
-            k_tile_q8<2, 256><<<dim3((w.n_out + 63) / 64, (R + 31) / 32), 256, tile_smem<MK_Q8, 2, 256>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
+            k_tile_q8<2, 256, 2><<<dim3((w.n_out + 63) / 64, (R + 31) / 32), 256, tile_smem<MK_Q8, 2, 256, 2>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
         } else if (!skinny && k % 256 == 0) {
             const int ns = std::min(k / 256, TILE_STAGES);
-            k_tile_q8<4, 256><<<dim3((w.n_out + 63) / 64, (R + 63) / 64), 256, tile_smem<MK_Q8, 4, 256>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
+            k_tile_q8<4, 256, 2><<<dim3((w.n_out + 63) / 64, (R + 63) / 64), 256, tile_smem<MK_Q8, 4, 256, 2>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
         } else if (skinny) k_gemm_q8<1><<<dim3((w.n_out + 63) / 64, 1), 512, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
         else k_gemm_q8<4><<<dim3((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (R + MMA_TOK - 1) / MMA_TOK), 256, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
         launches++;
@@ -626,28 +626,19 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
             else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
             launches++;
-            if (R <= 64) {
-                // few rows per expert: fused dequant-and-dot per (pair, row), experts' pairs adjacent
-                k_glu_gemv<<<dim3(ff / 32, E), TPB, glu_gemv_smem(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->hq, e->hs); launches++;
-                const int slots = 32 >> lanes_shift(ff / 32), rp = slots == 1 ? 8 : slots <= 8 ? 4 : 1;
-                dim3 gd(std::max(1, (H + 8 * NWG - 1) / (8 * NWG)), E);
-                if (rp == 4) k_down_gemv<4><<<gd, TPB, down_gemv_smem(ff, 4), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
-                else if (rp == 8) k_down_gemv<8><<<gd, TPB, down_gemv_smem(ff, 8), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
-                else k_down_gemv<1><<<gd, TPB, down_gemv_smem(ff, 1), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
-                launches++;
-            } else {
-                // tokens per expert decide the tile width: 16-, 32- or 64-token tiles (a tile's empty columns cost as much as full ones)
+            {
+                // rows per expert decide the tile shape (a tile's empty token columns cost as much as full ones)
                 const bool tile_w = H % 256 == 0 && ff % 256 == 0;
-                const int per_e = (P + E - 1) / E, nj = per_e <= 16 ? 1 : per_e <= 32 ? 2 : 4;
+                // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64
+                const int per_e = (P + E - 1) / E, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
                 const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
-                const dim3 gg(E, (ff + 63) / 64), gdn(E, (H + 63) / 64);
-#define GLU_TILE(NJ) k_tile_glu<NJ, 256><<<gg, 256, tile_smem<MK_FP4, NJ, 256>(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all, ns_g)
-#define DOWN_TILE(NJ) k_tile_down<NJ, 256><<<gdn, 256, tile_smem<MK_FP4, NJ, 256>(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
-                if (tile_w) { if (nj == 1) GLU_TILE(1); else if (nj == 2) GLU_TILE(2); else GLU_TILE(4); }
+#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all, ns_g)
+#define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
+                if (tile_w) { if (nj == 1) GLU_TILE(1, 1); else if (nj == 2) GLU_TILE(2, 1); else if (nj == 4) GLU_TILE(4, 1); else GLU_TILE(4, 2); }
                 else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all);
                 launches++;
                 k_quant_rows<<<P, 128, 0, st>>>(e->h_all, ff, e->hq, e->hs); launches++;
-                if (tile_w) { if (nj == 1) DOWN_TILE(1); else if (nj == 2) DOWN_TILE(2); else DOWN_TILE(4); }
+                if (tile_w) { if (nj == 1) DOWN_TILE(1, 1); else if (nj == 2) DOWN_TILE(2, 1); else if (nj == 4) DOWN_TILE(4, 1); else DOWN_TILE(4, 2); }
 #undef GLU_TILE
 #undef DOWN_TILE
                 else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);

@@ -464,120 +464,7 @@ __global__ void k_moe_finish_rows(float* x, int n, const float* o, const float* 
 
 }  // namespace
 
-// =====================================================================================================
-// Routed experts when an expert sees only a few rows (batched decode): below about eight rows per expert
-// the MMA tile wastes most of its columns and the per-element scaling costs more instructions than the
-// fused dequant-and-dot does, so each (pair, row) is a dp4a row-dot as in the one-token path, with the
-// pairs taken expert by expert so an expert's weights come from DRAM once and from cache after that.
-// =====================================================================================================
 namespace {
-
-constexpr int GEMV_PAIRS = 4;   // pairs staged per pass
-
-// grid (ff/32, n_expert), block NWG*32: 32 gate rows + 32 up rows of expert e for each of its pairs ->
-// h = silu(gate.x * s_g) * (up.x * s_u), quantised to Q8_0 (src/ops/mod.rs:1105-1117): hq[pair][ff], hs[pair][ff/32].
-__global__ void __launch_bounds__(NWG * 32) k_glu_gemv(DevFp4 gate, DevFp4 up, const int8_t* xq, const float* xs, int n_used,
-                                                       const int* off, const int* list, int8_t* hq, float* hs) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ float s_gu[GEMV_PAIRS * 64];
-    __shared__ int s_pair[GEMV_PAIRS];
-    const int e = blockIdx.y, el = e - gate.expert_lo;
-    const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
-    const int n = gate.n_in, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = gate.n_out, upp = ff / 32;
-    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31, nw = blockDim.x >> 5;
-    const int row0 = blockIdx.x * 32;
-    int8_t* xq_s = (int8_t*)smem;                                  // [GEMV_PAIRS][n]
-    float* xs_s = (float*)(xq_s + (size_t)GEMV_PAIRS * n);         // [GEMV_PAIRS][nb]
-    float* terms = xs_s + GEMV_PAIRS * nb + wid * terms_floats(4, gsh, nsb);
-    const size_t eo = (size_t)el * ff;
-    const uint8_t* gn = gate.nib + eo * (n / 2); const uint8_t* gs = gate.sc + eo * nsb;
-    const uint8_t* un = up.nib + eo * (n / 2); const uint8_t* us = up.sc + eo * nsb;
-    const bool has_g = gate.scale2 != nullptr, has_u = up.scale2 != nullptr;
-    const float sg2 = has_g ? gate.scale2[el] : 1.0f, su2 = has_u ? up.scale2[el] : 1.0f;
-    for (int t0 = p0; t0 < p1; t0 += GEMV_PAIRS) {
-        const int np = min(GEMV_PAIRS, p1 - t0);
-        __syncthreads();
-        if (tid < np) s_pair[tid] = list[t0 + tid];
-        for (int i = tid; i < np * (n / 16); i += blockDim.x) {
-            const int pr = i / (n / 16), c = i % (n / 16);
-            ((uint4*)xq_s)[pr * (n / 16) + c] = ((const uint4*)(xq + (size_t)(list[t0 + pr] / n_used) * n))[c];
-        }
-        for (int i = tid; i < np * nb; i += blockDim.x) xs_s[i] = xs[(size_t)(list[t0 + i / nb] / n_used) * nb + i % nb];
-        __syncthreads();
-        int k0, k1;
-        share(np * 64, nw, wid, k0, k1);
-        rows_list<MK_FP4, 4>(k1 - k0, n, terms, gsh,
-            [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
-                const int kk = k0 + k, pr = kk >> 6, rd = kk & 63, row = row0 + (rd & 31);
-                pa = (rd < 32 ? gn : un) + (size_t)row * (n / 2);
-                pb = (rd < 32 ? gs : us) + (size_t)row * nsb;
-                q = xq_s + (size_t)pr * n; s = xs_s + pr * nb;
-            },
-            [&](int k, float v) { s_gu[k0 + k] = v; });
-        __syncthreads();
-        if (wid < np) {
-            float g = s_gu[wid * 64 + lane], u = s_gu[wid * 64 + 32 + lane];
-            if (has_g) g = g * sg2;
-            if (has_u) u = u * su2;
-            float dq;
-            const int8_t q = warp_quant_q8(silu_f(g) * u, &dq);
-            const size_t pi = (size_t)s_pair[wid];
-            hq[pi * ff + row0 + lane] = q;
-            if (lane == 0) hs[pi * upp + blockIdx.x] = dq;
-        }
-    }
-}
-static inline size_t glu_gemv_smem(int n) {
-    const int nb = n / 32, gsh = lanes_shift(nb);
-    return (size_t)GEMV_PAIRS * n + (size_t)GEMV_PAIRS * nb * 4 + (size_t)NWG * terms_floats(4, gsh, n / 16) * 4 + 64;
-}
-
-// grid (row chunks, n_expert), block NWG*32: the down rows of expert e for each of its pairs, times the
-// expert's second scale (src/ops/mod.rs:1049-1088): o[pair][row].
-template <int RP>
-__global__ void __launch_bounds__(NWG * 32) k_down_gemv(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o) {
-    extern __shared__ __align__(16) unsigned char smem[];
-    __shared__ int s_pair[GEMV_PAIRS];
-    const int e = blockIdx.y, el = e - down.expert_lo;
-    const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
-    const int ff = down.n_in, nbf = ff / 32, nsb = ff / 16, gf = lanes_shift(nbf), n_out = down.n_out;
-    const int tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5;
-    int8_t* hq_s = (int8_t*)smem;                                  // [GEMV_PAIRS][ff]
-    float* hs_s = (float*)(hq_s + (size_t)GEMV_PAIRS * ff);        // [GEMV_PAIRS][nbf]
-    float* terms = hs_s + GEMV_PAIRS * nbf + wid * terms_floats(RP, gf, nsb);
-    const bool has_s = down.scale2 != nullptr;
-    const float s2 = has_s ? down.scale2[el] : 1.0f;
-    int b0, b1, r0, r1;
-    share(n_out, gridDim.x, blockIdx.x, b0, b1);
-    share(b1 - b0, nw, wid, r0, r1);
-    r0 += b0; r1 += b0;
-    const uint8_t* dn = down.nib + (size_t)el * n_out * (ff / 2);
-    const uint8_t* ds = down.sc + (size_t)el * n_out * nsb;
-    for (int t0 = p0; t0 < p1; t0 += GEMV_PAIRS) {
-        const int np = min(GEMV_PAIRS, p1 - t0);
-        __syncthreads();
-        if (tid < np) s_pair[tid] = list[t0 + tid];
-        for (int i = tid; i < np * (ff / 16); i += blockDim.x) {
-            const int pr = i / (ff / 16), c = i % (ff / 16);
-            ((uint4*)hq_s)[pr * (ff / 16) + c] = ((const uint4*)(hq + (size_t)list[t0 + pr] * ff))[c];
-        }
-        for (int i = tid; i < np * nbf; i += blockDim.x) hs_s[i] = hs[(size_t)list[t0 + i / nbf] * nbf + i % nbf];
-        __syncthreads();
-        rows_list<MK_FP4, RP>((r1 - r0) * np, ff, terms, gf,
-            [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
-                const int row = r0 + k / np, pr = k % np;
-                pa = dn + (size_t)row * (ff / 2); pb = ds + (size_t)row * nsb;
-                q = hq_s + (size_t)pr * ff; s = hs_s + pr * nbf;
-            },
-            [&](int k, float v) { o[(size_t)s_pair[k % np] * n_out + r0 + k / np] = has_s ? v * s2 : v; });
-    }
-}
-static inline size_t down_gemv_smem(int ff, int rp) {
-    const int gf = lanes_shift(ff / 32);
-    return (size_t)GEMV_PAIRS * ff + (size_t)GEMV_PAIRS * (ff / 32) * 4 + (size_t)NWG * terms_floats(rp, gf, ff / 16) * 4 + 64;
-}
 
 // Pairs grouped by expert without a serial scan: counts by shared-memory atomics, an exclusive scan, then each
 // pair takes the next free place of its expert. The order inside an expert depends on scheduling; results do

@@ -4,15 +4,16 @@
 // per k-block. The arithmetic is the exact chain of itb_mma.cuh: one int8 MMA per quantisation block, its int32
 // sum scaled and added to an f32 accumulator in ascending block order (src/ops/naive.rs:691-734).
 //
-// 8 warps: warp w owns rows 16*(w&3).. and the token half (w>>2) of the tile, NJ groups of 8 tokens each
-// (TOK = 16*NJ). Token rows are named by a per-tile index array so the same loop serves dense matmuls
-// (consecutive rows) and grouped experts (rows gathered by an expert's pair list).
+// 8 warps, split TH ways over the tile's tokens: TH=2 -> warp w owns rows 16*(w&3).. and token half w>>2 (64 rows x
+// 16*NJ tokens, for wide token tiles); TH=1 -> warp w owns rows 16*w.. and all 8*NJ tokens (128 rows, for the few
+// rows an expert sees: every weight is decoded by exactly one warp). NJ = groups of 8 tokens per warp. Token rows
+// are named by a per-tile index array so the same loop serves dense matmuls (consecutive rows) and grouped
+// experts (rows gathered by an expert's pair list).
 #pragma once
 #include "itb_mma.cuh"
 
 namespace {
 
-constexpr int TILE_ROWS = 64;
 constexpr int TILE_STAGES = 4;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -25,45 +26,55 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
 // KIND: MK_Q8 (int8 rows, f16 scale per 32) or MK_FP4 (E2M1 nibbles in element order, UE4M3 scale per 16).
-template <int KIND, int NJ, int KC>
+// Two UE4M3 scale codes (bit 7 clear, 0x7f already mapped to 0: plain positive e4m3) to their halved f32 values by
+// the hardware e4m3 -> f16 conversion, which is exact for every code.
+__device__ __forceinline__ void ue4m3x2_half(uint32_t two, float& lo, float& hi) {
+    uint32_t h2;
+    asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(h2) : "r"(two));
+    const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
+    lo = __low2float(hh) * 0.5f; hi = __high2float(hh) * 0.5f;
+}
+
+template <int KIND, int NJ, int KC, int TH = 2>
 struct TileCfg {
-    static constexpr int TOK = 16 * NJ;
+    static constexpr int ROWS = 128 / TH;
+    static constexpr int TOK = 8 * NJ * TH;
     static constexpr int WB = KIND == MK_Q8 ? KC : KC / 2;            // weight bytes per row and chunk
     static constexpr int WSTR = WB + (KIND == MK_Q8 ? 32 : 16);       // padded row stride: fragment reads hit distinct banks
     static constexpr int SB = KIND == MK_Q8 ? KC / 32 * 2 : KC / 16;  // scale bytes per row and chunk
     static constexpr int XSTR = KC + (KIND == MK_Q8 ? 32 : 16);
     static constexpr int XSB = KC / 32 * 4;                           // activation scale bytes per token and chunk
     static constexpr int XSF = KC / 32 + 4;                           // padded scale row in floats (distinct banks for the 4 token pairs)
-    static constexpr int OFF_WS = TILE_ROWS * WSTR;
-    static constexpr int OFF_XQ = OFF_WS + TILE_ROWS * SB;
+    static constexpr int OFF_WS = ROWS * WSTR;
+    static constexpr int OFF_XQ = OFF_WS + ROWS * SB;
     static constexpr int OFF_XS = OFF_XQ + TOK * XSTR;
     static constexpr int STAGE = OFF_XS + TOK * XSF * 4;
     static_assert(WB % 16 == 0 && SB % 16 == 0 && XSB % 16 == 0 && STAGE % 16 == 0, "16-byte copies");
 };
-template <int KIND, int NJ, int KC>
+template <int KIND, int NJ, int KC, int TH = 2>
 static inline size_t tile_smem(int k) {
     int n = k / KC; if (n > TILE_STAGES) n = TILE_STAGES; if (n < 1) n = 1;
-    return (size_t)n * TileCfg<KIND, NJ, KC>::STAGE + 64 * 4;
+    return (size_t)n * TileCfg<KIND, NJ, KC, TH>::STAGE + 64 * 4;
 }
 
-// One (64-row, TOK-token) tile. wq/ws: the matrix's quants and scales (row-major, k elements per row); rows
-// [r0, r0+64) clamped to n_rows-1. tok_idx[TOK] (shared memory): activation row of each tile token or -1.
-// Results in acc[NJ][4] in the MMA C layout for rows r0 + 16*(w&3) + {g, g+8}, tokens 8*(NJ*(w>>2)+j) + 2t, +1.
-template <int KIND, int NJ, int KC>
+// One (ROWS-row, TOK-token) tile. wq/ws: the matrix's quants and scales (row-major, k elements per row); rows
+// [r0, r0+ROWS) clamped to n_rows-1. tok_idx[TOK] (shared memory): activation row of each tile token or -1.
+// Results in acc[NJ][4] in the MMA C layout for the warp's rows {g, g+8} and tokens 8*j + 2t, +1 of its token share.
+template <int KIND, int NJ, int KC, int TH>
 __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, int k, int n_rows, int r0, const int8_t* xq, const float* xs,
                                           const int* tok_idx, unsigned char* ring, int n_stage, float (&acc)[NJ][4]) {
-    using C = TileCfg<KIND, NJ, KC>;
+    using C = TileCfg<KIND, NJ, KC, TH>;
     const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5, g = lane >> 2, t = lane & 3;
     const int n_chunk = k / KC, nb = k / 32;
     const size_t wrow = KIND == MK_Q8 ? (size_t)k : (size_t)k / 2, srow = KIND == MK_Q8 ? (size_t)nb * 2 : (size_t)k / 16;
     auto load = [&](int c) {
         unsigned char* st = ring + (size_t)(c % n_stage) * C::STAGE;
         constexpr int WP = C::WB / 16, SP = C::SB / 16, XP = KC / 16, XSP = C::XSB / 16;
-        for (int i = tid; i < TILE_ROWS * WP; i += 256) {
+        for (int i = tid; i < C::ROWS * WP; i += 256) {
             const int r = i / WP, p = i % WP, row = min(r0 + r, n_rows - 1);
             cp_async16(st + r * C::WSTR + p * 16, wq + (size_t)row * wrow + (size_t)c * C::WB + p * 16, true);
         }
-        for (int i = tid; i < TILE_ROWS * SP; i += 256) {
+        for (int i = tid; i < C::ROWS * SP; i += 256) {
             const int r = i / SP, p = i % SP, row = min(r0 + r, n_rows - 1);
             cp_async16(st + C::OFF_WS + r * C::SB + p * 16, ws + (size_t)row * srow + (size_t)c * C::SB + p * 16, true);
         }
@@ -81,7 +92,7 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
     for (int c = 0; c < n_stage - 1; ++c) { if (c < n_chunk) load(c); cp_async_commit(); }
-    const int rw = (wid & 3) * 16, tb = (wid >> 2) * NJ * 8;
+    const int rw = (TH == 2 ? (wid & 3) : wid) * 16, tb = TH == 2 ? (wid >> 2) * NJ * 8 : 0;
     for (int c = 0; c < n_chunk; ++c) {
         if (n_stage == 1) { __syncthreads(); load(c); cp_async_commit(); }
         if (n_stage >= 4) cp_async_wait<2>(); else if (n_stage == 3) cp_async_wait<1>(); else cp_async_wait<0>();
@@ -114,21 +125,30 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
             }
         } else {
 #pragma unroll 2
-            for (int s = 0; s < KC / 16; ++s) {
-                // elements 4t..4t+3 of the sub-block on both sides (within a block the k order is free)
+            for (int s = 0; s < KC / 16; s += 2) {
+                // the two sub-blocks of one 32-block; elements 4t..4t+3 of each on both sides (within a block the k order is free)
                 const uint32_t a0 = fp4x4_to_s8(*(const uint16_t*)(wa + s * 8 + 2 * t)), a1 = fp4x4_to_s8(*(const uint16_t*)(wb + s * 8 + 2 * t));
-                const float da = ue4m3_half_dev(sa[s]), db = ue4m3_half_dev(sb[s]);
+                const uint32_t c0 = fp4x4_to_s8(*(const uint16_t*)(wa + s * 8 + 8 + 2 * t)), c1 = fp4x4_to_s8(*(const uint16_t*)(wb + s * 8 + 8 + 2 * t));
+                float da0, da1, db0, db1;
+                ue4m3x2_half(*(const uint16_t*)(sa + s), da0, da1);
+                ue4m3x2_half(*(const uint16_t*)(sb + s), db0, db1);
 #pragma unroll
                 for (int j = 0; j < NJ; ++j) {
                     const int tj = tb + 8 * j;
-                    const uint32_t x = *(const uint32_t*)(xq_s + (tj + g) * C::XSTR + s * 16 + 4 * t);
-                    int cc[4];
-                    mma_s8_k16(cc, a0, a1, x);
+                    const uint32_t x0 = *(const uint32_t*)(xq_s + (tj + g) * C::XSTR + s * 16 + 4 * t);
+                    const uint32_t x1 = *(const uint32_t*)(xq_s + (tj + g) * C::XSTR + s * 16 + 16 + 4 * t);
+                    int cc[4], dd[4];
+                    mma_s8_k16(cc, a0, a1, x0);
+                    mma_s8_k16(dd, c0, c1, x1);
                     const float dy0 = xs_s[(tj + 2 * t) * C::XSF + (s >> 1)], dy1 = xs_s[(tj + 2 * t + 1) * C::XSF + (s >> 1)];
-                    acc[j][0] += dy0 * da * (float)cc[0];
-                    acc[j][1] += dy1 * da * (float)cc[1];
-                    acc[j][2] += dy0 * db * (float)cc[2];
-                    acc[j][3] += dy1 * db * (float)cc[3];
+                    acc[j][0] += dy0 * da0 * (float)cc[0];
+                    acc[j][1] += dy1 * da0 * (float)cc[1];
+                    acc[j][2] += dy0 * db0 * (float)cc[2];
+                    acc[j][3] += dy1 * db0 * (float)cc[3];
+                    acc[j][0] += dy0 * da1 * (float)dd[0];
+                    acc[j][1] += dy1 * da1 * (float)dd[1];
+                    acc[j][2] += dy0 * db1 * (float)dd[2];
+                    acc[j][3] += dy1 * db1 * (float)dd[3];
                 }
             }
         }
@@ -138,10 +158,10 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
 }
 
 // Visit this warp's results: f(token_in_tile, row, value).
-template <int NJ, class F>
+template <int NJ, int TH, class F>
 __device__ __forceinline__ void tile_foreach(const float (&acc)[NJ][4], int r0, int n_rows, F f) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int ra = r0 + (wid & 3) * 16 + g, rb = ra + 8, tb = (wid >> 2) * NJ * 8;
+    const int ra = r0 + (TH == 2 ? (wid & 3) : wid) * 16 + g, rb = ra + 8, tb = TH == 2 ? (wid >> 2) * NJ * 8 : 0;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int tj = tb + 8 * j + 2 * t;
@@ -150,79 +170,75 @@ __device__ __forceinline__ void tile_foreach(const float (&acc)[NJ][4], int r0, 
     }
 }
 
-// Dense Q8_0 matmul: grid (ceil(rows/64), ceil(n_tok/TOK)). mode 0: out = v; mode 1: out += v.
-template <int NJ, int KC>
+// Dense Q8_0 matmul: grid (ceil(rows/ROWS), ceil(n_tok/TOK)). mode 0: out = v; mode 1: out += v.
+template <int NJ, int KC, int TH>
 __global__ void __launch_bounds__(256) k_tile_q8(DevQ8 w, const int8_t* xq, const float* xs, int n_tok, float* out, size_t out_stride, int mode, int n_stage) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int TOK = 16 * NJ;
+    using C = TileCfg<MK_Q8, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
-    const int t0 = blockIdx.y * TOK, r0 = blockIdx.x * TILE_ROWS;
-    if ((int)threadIdx.x < TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < n_tok ? ti : -1; }
+    const int t0 = blockIdx.y * C::TOK, r0 = blockIdx.x * C::ROWS;
+    if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < n_tok ? ti : -1; }
     __syncthreads();
     float acc[NJ][4];
-    tile_gemm<MK_Q8, NJ, KC>((const uint8_t*)w.q, (const uint8_t*)w.s, w.n_in, w.n_out, r0, xq, xs, tok_idx, smem + 256, n_stage, acc);
-    tile_foreach<NJ>(acc, r0, w.n_out, [&](int t, int row, float v) {
+    tile_gemm<MK_Q8, NJ, KC, TH>((const uint8_t*)w.q, (const uint8_t*)w.s, w.n_in, w.n_out, r0, xq, xs, tok_idx, smem + 256, n_stage, acc);
+    tile_foreach<NJ, TH>(acc, r0, w.n_out, [&](int t, int row, float v) {
         if (t0 + t < n_tok) { float* o = out + (size_t)(t0 + t) * out_stride + row; *o = mode ? *o + v : v; }
     });
 }
 
 // Gate and up of one expert for the pairs routed to it, SiLU-gated (src/ops/mod.rs:1105-1117):
-// h[pair][row] = silu(gate.x * s_gate) * (up.x * s_up). grid (n_expert, ceil(ff/64)); pair p reads activation row p / n_used.
-template <int NJ, int KC>
+// h[pair][row] = silu(gate.x * s_gate) * (up.x * s_up). grid (n_expert, ceil(ff/ROWS)); pair p reads activation row p / n_used.
+template <int NJ, int KC, int TH>
 __global__ void __launch_bounds__(256) k_tile_glu(DevFp4 gate, DevFp4 up, const int8_t* xq, const float* xs, int n_used, const int* off, const int* list,
                                                   float* h, int n_stage) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int TOK = 16 * NJ;
+    using C = TileCfg<MK_FP4, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
     const int e = blockIdx.x, k = gate.n_in, ff = gate.n_out, el = e - gate.expert_lo;
     const int p0 = off[e], p1 = off[e + 1];
     if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
-    const int r0 = blockIdx.y * TILE_ROWS;
+    const int r0 = blockIdx.y * C::ROWS;
     const size_t eo = (size_t)el * ff;
     const bool has_g = gate.scale2 != nullptr, has_u = up.scale2 != nullptr;
     const float sg2 = has_g ? gate.scale2[el] : 1.0f, su2 = has_u ? up.scale2[el] : 1.0f;
-    for (int t0 = p0; t0 < p1; t0 += TOK) {
+    for (int t0 = p0; t0 < p1; t0 += C::TOK) {
         __syncthreads();
-        if ((int)threadIdx.x < TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] / n_used : -1; }
+        if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] / n_used : -1; }
         __syncthreads();
         float g[NJ][4], u[NJ][4];
-        tile_gemm<MK_FP4, NJ, KC>(gate.nib + eo * (k / 2), gate.sc + eo * (k / 16), k, ff, r0, xq, xs, tok_idx, smem + 256, n_stage, g);
-        tile_gemm<MK_FP4, NJ, KC>(up.nib + eo * (k / 2), up.sc + eo * (k / 16), k, ff, r0, xq, xs, tok_idx, smem + 256, n_stage, u);
-        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, gq = lane >> 2, tq = lane & 3;
+        tile_gemm<MK_FP4, NJ, KC, TH>(gate.nib + eo * (k / 2), gate.sc + eo * (k / 16), k, ff, r0, xq, xs, tok_idx, smem + 256, n_stage, g);
+        tile_gemm<MK_FP4, NJ, KC, TH>(up.nib + eo * (k / 2), up.sc + eo * (k / 16), k, ff, r0, xq, xs, tok_idx, smem + 256, n_stage, u);
 #pragma unroll
         for (int j = 0; j < NJ; ++j)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int t = (wid >> 2) * NJ * 8 + 8 * j + 2 * tq + (i & 1), row = r0 + (wid & 3) * 16 + gq + (i >> 1) * 8;
-                if (t0 + t < p1 && row < ff) {
-                    const float gv = has_g ? g[j][i] * sg2 : g[j][i], uv = has_u ? u[j][i] * su2 : u[j][i];
-                    h[(size_t)list[t0 + t] * ff + row] = silu_f(gv) * uv;
-                }
-            }
+            for (int i = 0; i < 4; ++i) { const float gv = has_g ? g[j][i] * sg2 : g[j][i], uv = has_u ? u[j][i] * su2 : u[j][i]; g[j][i] = silu_f(gv) * uv; }
+        tile_foreach<NJ, TH>(g, r0, ff, [&](int t, int row, float v) {
+            if (t0 + t < p1) h[(size_t)list[t0 + t] * ff + row] = v;
+        });
     }
 }
 
 // Down projection of one expert for its pairs (src/ops/mod.rs:1049-1088): o[pair][row], times the expert's second
-// scale. grid (n_expert, ceil(n_out/64)); activation rows are per pair.
-template <int NJ, int KC>
+// scale. grid (n_expert, ceil(n_out/ROWS)); activation rows are per pair.
+template <int NJ, int KC, int TH>
 __global__ void __launch_bounds__(256) k_tile_down(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o, int n_stage) {
     extern __shared__ __align__(16) unsigned char smem[];
-    constexpr int TOK = 16 * NJ;
+    using C = TileCfg<MK_FP4, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
     const int e = blockIdx.x, k = down.n_in, n_out = down.n_out, el = e - down.expert_lo;
     const int p0 = off[e], p1 = off[e + 1];
     if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
-    const int r0 = blockIdx.y * TILE_ROWS;
+    const int r0 = blockIdx.y * C::ROWS;
     const size_t eo = (size_t)el * n_out;
     const bool has_s = down.scale2 != nullptr;
     const float s2 = has_s ? down.scale2[el] : 1.0f;
-    for (int t0 = p0; t0 < p1; t0 += TOK) {
+    for (int t0 = p0; t0 < p1; t0 += C::TOK) {
         __syncthreads();
-        if ((int)threadIdx.x < TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] : -1; }
+        if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] : -1; }
         __syncthreads();
         float acc[NJ][4];
-        tile_gemm<MK_FP4, NJ, KC>(down.nib + eo * (k / 2), down.sc + eo * (k / 16), k, n_out, r0, hq, hs, tok_idx, smem + 256, n_stage, acc);
-        tile_foreach<NJ>(acc, r0, n_out, [&](int t, int row, float v) {
+        tile_gemm<MK_FP4, NJ, KC, TH>(down.nib + eo * (k / 2), down.sc + eo * (k / 16), k, n_out, r0, hq, hs, tok_idx, smem + 256, n_stage, acc);
+        tile_foreach<NJ, TH>(acc, r0, n_out, [&](int t, int row, float v) {
             if (t0 + t < p1) o[(size_t)list[t0 + t] * n_out + row] = has_s ? v * s2 : v;
         });
     }

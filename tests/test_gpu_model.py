@@ -181,10 +181,10 @@ def mid():
     ops.check()
 
 
-@pytest.mark.parametrize("n_tok", [70, 300, 640])
+@pytest.mark.parametrize("n_tok", [70, 200, 300, 640])
 def test_pipelined_rows_prefill_equals_token_by_token_and_oracle(mid, n_tok):
-    """One pass of n_tok rows: 70, 300 and 640 rows give the routed experts about 5, 19 and 40 rows each, i.e. the 16-, 32- and
-    64-token expert tiles; the dense tiles are 64 tokens wide with a ragged last tile in every case."""
+    """One pass of n_tok rows: 70, 200, 300 and 640 rows give the routed experts about 5, 13, 19 and 40 rows each, i.e. the 8-, 16-,
+    32- and 64-token expert tiles; the dense tiles are 64 tokens wide with a ragged last tile in every case."""
     import os
     from inferred_thoughts_b200 import host
     om, ops, model = mid
