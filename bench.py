@@ -29,6 +29,10 @@ from inferred_thoughts_b200 import configs  # noqa: E402
 
 PROMPT, N_CTX = 512, 8192
 FALLBACK_HBM = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
+# profiles/decode_step_bs1_kernels_4layer_ncu_full.md (per-launch traffic does not depend on the layer count)
+NCU_TRAFFIC = {"k_moe_glu": 9530624, "k_moe_down": 5878784, "k_in_proj[gdn]": 27561984, "k_in_proj[ffn]": 4402944,
+               "k_out_proj": 8940544, "k_gdn_core": 2169600}
 
 
 def peaks():
@@ -240,7 +244,7 @@ def run_product(args, rank, world):
                 "api": "itb_engine_decode (host token ids in, host argmax ids out)"},
         "gpu_launches": int(eng.launches_per_step()) * args.steps * 2,
         "roofline": {"bound": "hbm", "kernel": dom["kernel"], "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                     "traffic": None, "peak_source": hbm_src, "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
+                     "traffic": NCU_TRAFFIC.get(dom["kernel"]), "peak_source": hbm_src, "bytes_per_launch": per_launch_bytes, "ms_per_launch": per_launch_ms},
         "step_roofline": {"algorithmic_bytes_per_step": step_bytes, "achieved": step_bytes / ms_per_step / 1e6, "peak": hbm, "unit": "GB/s",
                           "frac": step_bytes / ms_per_step / 1e6 / hbm, "frac_of_8TBs_nominal": step_bytes / ms_per_step / 1e6 / 8000.0},
         "kernels": kb, "clocks": clocks, "synth_s": synth_s,
