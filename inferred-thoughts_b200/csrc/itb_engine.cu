@@ -350,6 +350,20 @@ static void set_smem(const void* fn, size_t bytes) {
     if (e != cudaSuccess) fprintf(stderr, "[itb] cudaFuncSetAttribute(%zu bytes) failed: %s\n", bytes, cudaGetErrorString(e));
 }
 
+// Launch with (pdl) or without the programmatic-serialization attribute: with it the kernel may be scheduled
+// while its predecessor in the stream still runs and orders itself by griddepcontrol.wait (pdl_wait()).
+template <class... KA, class... A>
+static void launch_k(bool pdl, void (*k)(KA...), dim3 g, dim3 b, size_t sm, cudaStream_t st, A&&... a) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = g; cfg.blockDim = b; cfg.dynamicSmemBytes = sm; cfg.stream = st;
+    cudaLaunchAttribute at{};
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at; cfg.numAttrs = pdl ? 1 : 0;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, k, KA(std::forward<A>(a))...);
+    if (err != cudaSuccess) fprintf(stderr, "[itb] kernel launch failed: %s\n", cudaGetErrorString(err));
+}
+
 // One decode step for all B sequences, enqueued on `st`.
 static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
@@ -360,6 +374,9 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv;
     const int TPB = NWG * 32;
     uint64_t launches = 0;
+    // overlap each kernel's launch and weight prefetch with its predecessor's tail (off while profiling per kernel)
+    static const bool pdl_env = !(getenv("ITB_PDL") && atoi(getenv("ITB_PDL")) == 0);
+    const bool pdl = pdl_env && !prof;
     auto q8b = [](uint64_t a, uint64_t b) { return a * b / 32 * 34; };
     auto f4b = [](uint64_t a, uint64_t b) { return a * b / 64 * 36; };
 #define MARK(cls, by) do { launches++; if (prof) prof->mark((cls), (uint64_t)(by), st); } while (0)
@@ -370,14 +387,16 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     auto launch_in = [&](InProj& p, int rows, int gx) {
         int per_warp = (rows + gx * NWG - 1) / (gx * NWG) + 1;
         p.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+        p.prefetch = pdl;
         if (e->stamps) { p.stamps = e->stamps + 8 * (e->n_stamped % 400); e->n_stamped++; }
-        k_in_proj<<<dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st>>>(p);
+        launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
     };
     auto launch_out = [&](OutProj& o, int n_in) {
         int gx = std::max(1, std::min(sms, H / NWG)), pass = 32 >> lanes_shift(n_in / 32);
         int per_warp = (H + gx * NWG - 1) / (gx * NWG) + 1;
         o.br = std::min(std::max(32 / pass, 1) * pass, (per_warp + pass - 1) / pass * pass);
-        k_out_proj<<<dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st>>>(o);
+        o.prefetch = pdl;
+        launch_k(pdl, k_out_proj, dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st, o);
     };
     static bool attrs_set = false;
     if (!attrs_set) {
@@ -389,7 +408,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         attrs_set = true;
     }
     if (prof) prof->mark(-1, 0, st);
-    k_embed<<<B, 256, 0, st>>>(m->tok_embd.w, H, e->tokens, e->x); MARK(KC_EMBED, (uint64_t)B * H * 8);
+    launch_k(pdl, k_embed, B, 256, 0, st, m->tok_embd.w, H, e->tokens, e->x); MARK(KC_EMBED, (uint64_t)B * H * 8);
     for (uint32_t il = 0; il < d.n_layer; ++il) {
         const DevLayer& L = m->layers[il];
         if (L.recurrent) {
@@ -412,8 +431,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             g.state_stride = state_stride; g.state = e->ssm_state + (size_t)rs * B * state_stride;
             g.out_q = e->aq; g.out_s = e->as; g.sk = d.ssm_d_state; g.sv = d.ssm_d_state; g.n_k = d.ssm_n_group; g.n_v = d.ssm_dt_rank; g.eps = d.rms_eps;
             size_t smem_g = (size_t)(g.sv * (g.sk + 1) + 2 * g.sk + g.sv) * 4;
-            if (d.ssm_d_state == 128) k_gdn_core<128><<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g);
-            else k_gdn_core<64><<<dim3(d.ssm_dt_rank, B), 256, smem_g, st>>>(g);
+            if (d.ssm_d_state == 128) launch_k(pdl, k_gdn_core<128>, dim3(d.ssm_dt_rank, B), 256, smem_g, st, g);
+            else launch_k(pdl, k_gdn_core<64>, dim3(d.ssm_dt_rank, B), 256, smem_g, st, g);
             MARK(KC_GDN_CORE, (uint64_t)B * (2ull * g.state_stride * 4 + (cd + 2ull * vd) * 4));
             OutProj o{e->aq, e->as, vd, L.ssm_out, e->x, H};
             launch_out(o, vd);
@@ -433,7 +452,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             a.kslab = e->kslab + (size_t)as * B * a.slab_stride; a.vslab = e->vslab + (size_t)as * B * a.slab_stride;
             a.pos = e->pos; a.npos_out = e->npos; a.hd = d.head_dim; a.n_head = d.n_head; a.n_head_kv = d.n_head_kv; a.n_rot = d.n_rot;
             a.theta = d.rope_theta; a.eps = d.rms_eps; a.bf16 = c->kv_bf16;
-            k_attn_prep<<<dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st>>>(a);
+            launch_k(pdl, k_attn_prep, dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st, a);
             MARK(KC_ATTN_PREP, (uint64_t)B * (4ull * qd + 3ull * kvd) * 4);
             // split-K partials, one launch per sequence (own slab, own position), then one combine for all
             const float scale = 1.0f / sqrtf((float)d.head_dim);
@@ -445,15 +464,15 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
 #define ATT_CASE(HD)                                                                                                             \
     case HD:                                                                                                                      \
         set_smem((const void*)k_attn_partial<HD, 8>, smem_a);                                                                     \
-        k_attn_partial<HD, 8><<<grid, nwa * 32, smem_a, st>>>(e->qn + (size_t)b * qd, a.kslab + (size_t)b * a.slab_stride,        \
+        launch_k(pdl, k_attn_partial<HD, 8>, grid, nwa * 32, smem_a, st, e->qn + (size_t)b * qd, a.kslab + (size_t)b * a.slab_stride,        \
             a.vslab + (size_t)b * a.slab_stride, kvd, 0, 1, d.n_head, d.n_head_kv, scale, c->kv_bf16, e->npos + b,                 \
-            e->part_acc + po * d.head_dim, e->part_ml + po * 2);                                                                  \
+            e->part_acc + po * d.head_dim, e->part_ml + po * 2, 0, (size_t)0);                                                    \
         break;
                 switch (d.head_dim) { ATT_CASE(64) ATT_CASE(128) ATT_CASE(256) }
 #undef ATT_CASE
                 MARK(KC_ATTN, 2ull * kvd * 2 * (e->host_pos[b] + 1) + 3ull * qd * 4);
             }
-            k_attn_combine_q<<<B * d.n_head, d.head_dim, 0, st>>>(e->part_acc, e->part_ml, e->n_split, d.head_dim, e->gate, e->npos,
+            launch_k(pdl, k_attn_combine_q, B * d.n_head, d.head_dim, 0, st, e->part_acc, e->part_ml, e->n_split, d.head_dim, e->gate, e->npos,
                                                                   d.n_head, e->aq, e->as);
             MARK(KC_ATTN, 0);
             OutProj o{e->aq, e->as, qd, L.wo, e->x, H};
@@ -476,20 +495,21 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
-        k_moe_glu<<<dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st>>>(g);
+        launch_k(pdl, k_moe_glu, dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st, g);
         MARK(KC_MOE_GLU, (uint64_t)B * (2ull * d.n_expert_used * f4b(H, d.expert_ff) + (uint64_t)d.n_expert_used * d.expert_ff * 4));
         MoeDown w{};
         w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
         w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
+        w.prefetch = pdl;
         {
             int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
             int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
             dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), B);
             size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
-            if (rp == 1) k_moe_down<1><<<grid, TPB, smem_d, st>>>(w);
-            else if (rp == 2) k_moe_down<2><<<grid, TPB, smem_d, st>>>(w);
-            else if (rp == 4) k_moe_down<4><<<grid, TPB, smem_d, st>>>(w);
-            else k_moe_down<8><<<grid, TPB, smem_d, st>>>(w);
+            if (rp == 1) launch_k(pdl, k_moe_down<1>, grid, TPB, smem_d, st, w);
+            else if (rp == 2) launch_k(pdl, k_moe_down<2>, grid, TPB, smem_d, st, w);
+            else if (rp == 4) launch_k(pdl, k_moe_down<4>, grid, TPB, smem_d, st, w);
+            else launch_k(pdl, k_moe_down<8>, grid, TPB, smem_d, st, w);
         }
         MARK(KC_MOE_DOWN, (uint64_t)B * d.n_expert_used * f4b(d.expert_ff, H) + q8b(d.shared_ff, H) + (uint64_t)B * ((uint64_t)d.n_expert_used * d.expert_ff + 2ull * H) * 4);
     }
@@ -498,8 +518,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
     launch_in(hp, d.n_vocab, grid_rows(d.n_vocab));
     MARK(KC_LM_HEAD, q8b(H, d.n_vocab) + (uint64_t)B * (H + d.n_vocab) * 4);
-    k_argmax_partial<<<dim3(ARGMAX_PARTS, B), 256, 0, st>>>(e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
-    k_argmax_advance<<<B, 32, 0, st>>>(e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, (int)e->history_cap, e->step_counter, B);
+    launch_k(pdl, k_argmax_partial, dim3(ARGMAX_PARTS, B), 256, 0, st, e->logits, d.n_vocab, e->arg_v, e->arg_i); launches++;
+    launch_k(pdl, k_argmax_advance, B, 32, 0, st, e->arg_v, e->arg_i, ARGMAX_PARTS, e->tokens, e->pos, e->next, e->history, (int)e->history_cap, e->step_counter, B);
     MARK(KC_ARGMAX, (uint64_t)B * d.n_vocab * 4);
 #undef MARK
     e->launches_per_step = launches;

@@ -23,6 +23,7 @@ struct InProj {
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
+    int prefetch;                                  // ask L2 for the warp's weight rows before waiting for the predecessor
     long long* stamps;                             // debug: clock64 at phase boundaries of block 0 warp 0
 };
 #define STAMP(i) do { if (p.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) p.stamps[i] = clock64(); } while (0)
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     const int n = p.n_embd, nb = n / 32, gsh = lanes_shift(nb);
     const int b = blockIdx.y, wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
     STAMP(0);
+    pdl_trigger();
     double* red = (double*)smem;
     float* xn = (float*)(red + 32);
     int8_t* xq = (int8_t*)(xn + n);
@@ -59,6 +61,19 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = lane; i < nr * p.conv_kernel; i += 32) cpre[(i / p.conv_kernel) * 8 + keep + i % p.conv_kernel] = cw[i];
         conv_lo = r0;
     }
+    if (p.prefetch && lane == 0) {
+        // this warp's weight rows into L2 while the predecessor kernel finishes
+        int base = 0;
+        for (int m = 0; m < p.nq; ++m) {
+            const int lo = max(r0, base) - base, hi = min(r1, base + p.q[m].n_out) - base;
+            if (lo < hi) {
+                l2_prefetch(p.q[m].q + (size_t)lo * n, (size_t)(hi - lo) * n);
+                l2_prefetch(p.q[m].s + (size_t)lo * nb, (size_t)(hi - lo) * nb * 2);
+            }
+            base += p.q[m].n_out;
+        }
+    }
+    pdl_wait();
     STAMP(1);
     block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
     STAMP(2);
@@ -138,7 +153,7 @@ size_t in_proj_smem(int n, int exact, int br) {
 // ------------------------------------------------------------------------------------------------------
 // Output projection with the residual add fused: x[b] += W . a[b], the activation arriving already quantised
 // (src/model/qwen35.rs:1017, :1220, :1325).
-struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; };
+struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; int prefetch; };
 __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
@@ -146,12 +161,18 @@ __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     int8_t* aq = (int8_t*)smem;
     float* as = (float*)(aq + n);
     float* terms = as + nb + wid * (p.br * (nb + 1));
-    for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
-    for (int i = threadIdx.x; i < nb; i += blockDim.x) as[i] = p.as[(size_t)b * nb + i];
-    __syncthreads();
     int b0, b1, r0, r1;
     share(p.w.n_out, gridDim.x, blockIdx.x, b0, b1);
     share(b1 - b0, nw, wid, r0, r1);
+    pdl_trigger();
+    if (p.prefetch && (threadIdx.x & 31) == 0 && r0 < r1) {
+        l2_prefetch(p.w.q + (size_t)(b0 + r0) * n, (size_t)(r1 - r0) * n);
+        l2_prefetch(p.w.s + (size_t)(b0 + r0) * nb, (size_t)(r1 - r0) * nb * 2);
+    }
+    pdl_wait();
+    for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
+    for (int i = threadIdx.x; i < nb; i += blockDim.x) as[i] = p.as[(size_t)b * nb + i];
+    __syncthreads();
     float* x = p.x + (size_t)b * p.x_stride;
     rows_batched<MK_Q8, 1, 4>((const uint8_t*)p.w.q, (const uint8_t*)p.w.s, n, b0 + r0, b0 + r1, aq, as, terms, p.br, gsh,
                               [&](int row, float v) { x[row] += v; });
@@ -187,13 +208,17 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     const int key_dim = p.n_k * sk;
     const float* cv = p.conv + (size_t)b * p.conv_stride;
     float* sg = p.state + (size_t)b * p.state_stride + (size_t)h * sv * sk;
+    pdl_trigger();
+    // the state belongs to this layer alone: its loads are in flight while the predecessor kernel finishes
     float4 ld[LD];
 #pragma unroll
     for (int i = 0; i < LD; ++i) ld[i] = __ldcs((const float4*)sg + tid + i * 256);
+    const float r_dt = p.dt_bias[h], r_a = p.ssm_a[h], r_nw = p.ssm_norm[tid < sv ? tid : 0];
+    pdl_wait();
     // every other global operand is requested now too, so the kernel has one memory round trip
-    const float r_alpha = p.alpha[(size_t)b * p.n_v + h], r_dt = p.dt_bias[h], r_a = p.ssm_a[h], r_beta = p.beta[(size_t)b * p.n_v + h];
+    const float r_alpha = p.alpha[(size_t)b * p.n_v + h], r_beta = p.beta[(size_t)b * p.n_v + h];
     const size_t oidx = (size_t)b * p.n_v * sv + (size_t)h * sv + (tid < sv ? tid : 0);
-    const float r_z = p.z[oidx], r_nw = p.ssm_norm[tid < sv ? tid : 0];
+    const float r_z = p.z[oidx];
     // SiLU of this head's conv sums: threads [0, 2*sk) take k then q, threads [0, sv) their v element later
     if (tid < 2 * sk) kq[tid] = silu_f(cv[(tid < sk ? key_dim : 0) + kh * sk + (tid < sk ? tid : tid - sk)]);
     float vj = 0.0f;
@@ -279,6 +304,7 @@ __global__ void k_attn_prep(AttnPrep p) {
     float* val = (float*)smem;
     __shared__ double red[8];
     const int job = blockIdx.x, b = blockIdx.y, d = threadIdx.x, hd = p.hd, kvd = p.n_head_kv * hd;
+    pdl_trigger(); pdl_wait();
     const int pos = p.pos[b];
     if (job == 0 && d == 0) p.npos_out[b] = pos + 1;
     const bool is_q = job < p.n_head, is_k = !is_q && job < p.n_head + p.n_head_kv;
@@ -327,6 +353,7 @@ __global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, in
                                  const int* n_pos_dev, int n_head, int8_t* out_q, float* out_s) {
     const size_t th = blockIdx.x;
     const int d = threadIdx.x, b = (int)(th / n_head);
+    pdl_trigger(); pdl_wait();
     const int n_pos = n_pos_dev[b], per = max(ATTN_MIN_SPLIT, (n_pos + n_split - 1) / n_split), n_act = (n_pos + per - 1) / per;
     float M = -INFINITY;
     for (int s = 0; s < n_act; ++s) M = fmaxf(M, part_ml[(th * n_split + s) * 2]);
@@ -368,6 +395,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     const int n = p.n_embd, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = p.gate.n_out, upp = ff / 32;
     const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x, n_units = p.n_used * upp;
+    pdl_trigger(); pdl_wait();
     if (unit >= n_units) {
         // shared expert: silu(gate) * up for 32 elements, quantised (src/model/qwen35.rs:1669-1678)
         if (wid == 0) {
@@ -477,6 +505,7 @@ struct MoeDown {
     const float* logit;
     float* x; int x_stride;
     int local_only; float* partial;
+    int prefetch;
 };
 template <int RP>
 __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
@@ -495,6 +524,15 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     const int tf = max(terms_floats(RP, gf, nsb), terms_floats(1, gs, nbs));
     float* terms = ss + nbs + wid * (tf + 32);
     float* outv = terms + tf;                             // this warp's per-stream results
+    int b0, b1, r0, r1;
+    share(n_out, gridDim.x, blockIdx.x, b0, b1);
+    share(b1 - b0, nw, wid, r0, r1);
+    pdl_trigger();
+    if (p.prefetch && !p.local_only && lane == 0 && r0 < r1) {
+        l2_prefetch(p.shared_down.q + (size_t)(b0 + r0) * sff, (size_t)(r1 - r0) * sff);
+        l2_prefetch(p.shared_down.s + (size_t)(b0 + r0) * nbs, (size_t)(r1 - r0) * nbs * 2);
+    }
+    pdl_wait();
     for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];
     for (int i = tid; i < p.n_used * nbf; i += blockDim.x) hs[i] = p.hs[(size_t)b * p.n_used * nbf + i];
     for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + (size_t)b * sff))[i];
@@ -507,9 +545,6 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     }
     if (tid == 32) s_g = sigmoid_f(p.logit[b]);
     __syncthreads();
-    int b0, b1, r0, r1;
-    share(n_out, gridDim.x, blockIdx.x, b0, b1);
-    share(b1 - b0, nw, wid, r0, r1);
     const bool has_s = p.down.scale2 != nullptr;
     float* x = p.x + (size_t)b * p.x_stride;
 #pragma unroll 1
@@ -556,6 +591,7 @@ size_t moe_down_smem(int n_used, int ff, int sff, int rp) {
 // ------------------------------------------------------------------------------------------------------
 __global__ void k_embed(const float* table, int n_embd, const int32_t* tokens, float* x) {
     int b = blockIdx.x;
+    pdl_trigger(); pdl_wait();
     const float* row = table + (size_t)tokens[b] * n_embd;
     for (int i = threadIdx.x; i < n_embd; i += blockDim.x) x[(size_t)b * n_embd + i] = row[i];
 }
@@ -573,6 +609,7 @@ __global__ void __launch_bounds__(256) k_argmax_partial(const float* logits, int
     int part = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     int lo, hi;
     share(n_vocab, gridDim.x, part, lo, hi);
+    pdl_trigger(); pdl_wait();
     const float* l = logits + (size_t)b * n_vocab;
     float bv = -INFINITY; int bi = 0x7fffffff;
     for (int i = lo + tid; i < hi; i += blockDim.x) { float v = l[i]; if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; } }
@@ -587,6 +624,7 @@ __global__ void __launch_bounds__(256) k_argmax_partial(const float* logits, int
 __global__ void k_argmax_advance(const float* pv, const int* pi, int n_part, int32_t* tokens, int* pos, int32_t* next_out,
                                  int32_t* history, int history_cap, int* step_counter, int n_seq) {
     int b = blockIdx.x, lane = threadIdx.x;
+    pdl_trigger(); pdl_wait();
     float bv = -INFINITY; int bi = 0x7fffffff;
     for (int i = lane; i < n_part; i += 32) argmax_merge(bv, bi, pv[(size_t)b * n_part + i], pi[(size_t)b * n_part + i]);
     for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));

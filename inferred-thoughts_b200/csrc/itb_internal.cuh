@@ -122,6 +122,17 @@ __device__ __forceinline__ double warp_sum_d(double v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while
+// its predecessor still runs. pdl_trigger() lets the successor be scheduled; pdl_wait() returns once every
+// predecessor grid has completed and its writes are visible. Before pdl_wait() a kernel may touch only memory no
+// kernel of the same chain writes (weights, its own layer's state). Both are no-ops in an ordinary launch.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Ask the L2 for [p, p+bytes) (trimmed inwards to 16-byte multiples); no completion to wait for.
+__device__ __forceinline__ void l2_prefetch(const void* p, size_t bytes) {
+    const uintptr_t a = ((uintptr_t)p + 15) & ~(uintptr_t)15, e = ((uintptr_t)p + bytes) & ~(uintptr_t)15;
+    if (e > a) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"((uint32_t)(e - a)) : "memory");
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

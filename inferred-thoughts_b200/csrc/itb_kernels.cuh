@@ -388,6 +388,7 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
                                float* part_acc, float* part_ml, int rows_per_seq = 0, size_t slab_stride = 0) {
     constexpr int DPL = HD / 32;  // dims per lane
     int hk = blockIdx.x, t = blockIdx.y, sp = blockIdx.z, n_split = gridDim.z;
+    pdl_trigger(); pdl_wait();
     if (rows_per_seq > 0) {       // rows of several sequences in one launch: row t reads the slabs of sequence t / rows_per_seq
         const size_t so = (size_t)(t / rows_per_seq) * slab_stride;
         kslab += so; vslab += so;
