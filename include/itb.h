@@ -139,6 +139,15 @@ uint64_t itb_model_decode_bytes(itb_model*, uint32_t n_seq, uint32_t n_pos, uint
 
 /* n_seq independent sequences (the reference engine holds one, src/engine/mod.rs:44-59). */
 int  itb_engine_create(itb_model*, uint32_t n_ctx, uint32_t n_seq, itb_engine** out);
+/* Expert parallelism over `world` processes, one GPU each (the reference's placement seam: src/ops/mod.rs:1024-1048;
+ * its grouped kernels: kernels/moe.cuh:62-133). The model must hold exactly experts [rank*E/world, (rank+1)*E/world)
+ * (itb_model_synth with that range, or set_tensor of that slice); everything else is replicated and each rank runs its
+ * own n_seq sequences. Per MoE layer: all-gather of the quantised rows and routing, local experts over the pairs that
+ * name them, sum reduce-scatter of the per-pair output rows (one non-zero contribution each, so the result is exact and
+ * equals the single-GPU bits). Every rank must make the same engine calls with the same shapes.
+ * itb_ep_unique_id: 128 bytes naming a new NCCL communicator (rank 0 makes them; hand the same bytes to every rank). */
+int  itb_ep_unique_id(uint8_t* out128);
+int  itb_engine_create_ep(itb_model*, uint32_t n_ctx, uint32_t n_seq, const uint8_t* unique_id128, int rank, int world, itb_engine** out);
 void itb_engine_destroy(itb_engine*);
 void itb_engine_reset(itb_engine*);                                               /* src/engine/mod.rs:296-308 */
 uint32_t itb_engine_pos(itb_engine*, uint32_t seq);

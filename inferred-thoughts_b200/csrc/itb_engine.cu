@@ -283,8 +283,55 @@ extern "C" uint64_t itb_model_decode_bytes(itb_model* m, uint32_t n_seq, uint32_
 // =====================================================================================================
 // Engine
 // =====================================================================================================
+
+// ---------------------------------------------------------------------------------------------------------
+// Expert parallelism (src/ops/mod.rs:1024-1048 describes the reference's placement seam). Routed experts are
+// sharded by contiguous ranges across ranks, everything else is replicated and every rank decodes its own
+// sequences. Per MoE layer the ranks all-gather the quantised rows and their routing, each rank runs its own
+// experts over the pairs that name them (the grouped kernels skip experts stored elsewhere), and a sum
+// reduce-scatter brings every pair's output row back to the rank that owns the token. Each output row has
+// exactly one non-zero contribution, so the reduction is exact and the pick-order combine that follows gives
+// the single-GPU bits. NCCL is bound at run time from the library already in the process (no link-time
+// dependency: a single-GPU user never loads it).
+#include <dlfcn.h>
+struct NcclApi {
+    typedef struct { char internal[128]; } UniqueId;
+    int (*GetUniqueId)(UniqueId*) = nullptr;
+    int (*CommInitRank)(void**, int, UniqueId, int) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+    static constexpr int Int8 = 0, Int32 = 2, Float32 = 7, Sum = 0;   // ncclDataType_t / ncclRedOp_t values of the public ABI
+};
+static NcclApi& nccl_api() {
+    static NcclApi api;
+    static bool tried = false;
+    if (tried) return api;
+    tried = true;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD | RTLD_GLOBAL);   // the copy the process already holds
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return api;
+#define NCCL_SYM(f) *(void**)&api.f = dlsym(h, "nccl" #f)
+    NCCL_SYM(GetUniqueId); NCCL_SYM(CommInitRank); NCCL_SYM(CommDestroy); NCCL_SYM(AllGather); NCCL_SYM(ReduceScatter);
+    NCCL_SYM(GroupStart); NCCL_SYM(GroupEnd); NCCL_SYM(GetErrorString);
+#undef NCCL_SYM
+    api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.ReduceScatter && api.GroupStart && api.GroupEnd;
+    return api;
+}
+struct EpState {
+    void* comm = nullptr;
+    int rank = 0, world = 1;
+    int8_t* gxq = nullptr; float* gxs = nullptr; int32_t* gids = nullptr;   // gathered rows of all ranks, rank-major
+    float* o_mine = nullptr;                                                // this rank's pairs after the reduce-scatter
+};
+
 struct itb_engine {
     itb_model* m = nullptr;
+    EpState* ep = nullptr;   // set in expert-parallel engines
     itb_ctx* c = nullptr;
     uint32_t n_ctx = 0, B = 0, n_attn = 0, n_rec = 0;
     std::vector<int> slot_of;  // absolute layer -> attention slot or recurrent slot
@@ -639,12 +686,26 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         f32mm(L.gate_inp, e->xn, e->router);
         f32mm(L.shared_gate_inp, e->xn, e->shlogit);
         {
-            const int K = d.n_expert_used, E = d.n_expert, ff = d.expert_ff, P = R * K;
+            const int K = d.n_expert_used, E = d.n_expert, ff = d.expert_ff;
             int32_t* ids = e->route_ids + (size_t)il * e->R * K;
             float* wts = e->route_w + (size_t)il * e->R * K;
             k_route_rows<<<(R + 3) / 4, 128, (size_t)4 * ((E + 31) & ~31) * 4, st>>>(e->router, R, E, K, ids, wts); launches++;
-            if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
-            else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids, P, E, e->pair_off, e->pair_list);
+            // expert parallel: the pairs of every rank's rows, rank-major; otherwise just ours
+            const int W = e->ep ? e->ep->world : 1, P = W * R * K;
+            const int8_t* xq_src = e->xq; const float* xs_src = e->xs; const int32_t* ids_src = ids;
+            if (e->ep) {
+                NcclApi& nc = nccl_api();
+                nc.GroupStart();
+                nc.AllGather(e->xq, e->ep->gxq, (size_t)R * H, NcclApi::Int8, e->ep->comm, st);
+                nc.AllGather(e->xs, e->ep->gxs, (size_t)R * (H / 32), NcclApi::Float32, e->ep->comm, st);
+                nc.AllGather(ids, e->ep->gids, (size_t)R * K, NcclApi::Int32, e->ep->comm, st);
+                nc.GroupEnd();
+                launches++;
+                xq_src = e->ep->gxq; xs_src = e->ep->gxs; ids_src = e->ep->gids;
+                cudaMemsetAsync(e->o_all, 0, (size_t)P * H * sizeof(float), st);   // rows of pairs served elsewhere stay zero
+            }
+            if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
+            else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             launches++;
             {
                 // rows per expert decide the tile shape (a tile's empty token columns cost as much as full ones)
@@ -652,10 +713,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64
                 const int per_e = (P + E - 1) / E, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
                 const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
-#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all, ns_g)
+#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(L.gate, L.up, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all, ns_g)
 #define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
                 if (tile_w) { if (nj == 1) GLU_TILE(1, 1); else if (nj == 2) GLU_TILE(2, 1); else if (nj == 4) GLU_TILE(4, 1); else GLU_TILE(4, 2); }
-                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(L.gate, L.up, e->xq, e->xs, K, e->pair_off, e->pair_list, e->h_all);
+                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(L.gate, L.up, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all);
                 launches++;
                 k_quant_rows<<<P, 128, 0, st>>>(e->h_all, ff, e->hq, e->hs); launches++;
                 if (tile_w) { if (nj == 1) DOWN_TILE(1, 1); else if (nj == 2) DOWN_TILE(2, 1); else if (nj == 4) DOWN_TILE(4, 1); else DOWN_TILE(4, 2); }
@@ -664,10 +725,16 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
                 launches++;
             }
+            const float* o_src = e->o_all;
+            if (e->ep) {
+                nccl_api().ReduceScatter(e->o_all, e->ep->o_mine, (size_t)R * K * H, NcclApi::Float32, NcclApi::Sum, e->ep->comm, st);
+                launches++;
+                o_src = e->ep->o_mine;
+            }
             k_shared_act_rows<<<R, 128, 0, st>>>(e->sg, e->su, d.shared_ff, e->sq, e->ss); launches++;
             gemm(L.shared_down, e->sq, e->ss, e->shd, H, 0);
             const size_t total = (size_t)R * H;
-            k_moe_finish_rows<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(e->x, H, e->o_all, wts, K, e->shd, e->shlogit, total); launches++;
+            k_moe_finish_rows<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(e->x, H, o_src, wts, K, e->shd, e->shlogit, total); launches++;
         }
     }
     // LM head on each sequence's last row
@@ -697,12 +764,12 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     return launches;
 }
 
-extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, itb_engine** out) {
+static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world, itb_engine** out) {
     *out = nullptr;
     itb_ctx* c = m->c;
     if (!finalize(m)) return 1;
     if (n_seq == 0 || n_ctx == 0) { itb_fail_msg(c, "engine: n_seq and n_ctx must be positive"); return 1; }
-    if (m->expert_hi && (m->expert_lo != 0 || m->expert_hi != m->d.n_expert)) {
+    if (world == 1 && m->expert_hi && (m->expert_lo != 0 || m->expert_hi != m->d.n_expert)) {
         itb_fail_msg(c, "engine: this model holds an expert shard; use the expert-parallel engine"); return 1;
     }
     const itb_model_dims& d = m->d;
@@ -715,7 +782,7 @@ extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, i
     e->n_split = (int)std::max<size_t>(1, std::min<size_t>({(size_t)64, ((size_t)n_ctx + 127) / 128, (size_t)(2 * c->sm_count) / d.n_head_kv + 1}));
     itb_engine* E = e.get();
     e->R = std::max<uint32_t>(n_seq, getenv("ITB_ROWS") ? (uint32_t)atoi(getenv("ITB_ROWS")) : 512u);
-    const size_t R = e->R, K = d.n_expert_used;
+    const size_t R = e->R, K = d.n_expert_used, W = (size_t)world;   // W: ranks whose pairs the expert buffers hold
     const size_t n_parts = std::max<size_t>(B * d.n_head * e->n_split, R * d.n_head * e->n_split_rows);
     bool ok = dalloc(E, &e->kslab, (size_t)e->n_attn * B * n_ctx * kvd) && dalloc(E, &e->vslab, (size_t)e->n_attn * B * n_ctx * kvd) &&
               dalloc(E, &e->conv_state, (size_t)e->n_rec * B * cd * (d.ssm_d_conv - 1)) &&
@@ -730,18 +797,60 @@ extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, i
               dalloc(E, &e->route_ids, (size_t)d.n_layer * R * K) && dalloc(E, &e->route_w, (size_t)d.n_layer * R * K) &&
               dalloc(E, &e->step_counter, B) && dalloc(E, &e->err, 1) && dalloc(E, &e->arg_v, B * ARGMAX_PARTS) && dalloc(E, &e->arg_i, B * ARGMAX_PARTS) &&
               dalloc(E, &e->aq, R * std::max(vd, qd)) && dalloc(E, &e->as, R * std::max(vd, qd) / 32) &&
-              dalloc(E, &e->hq, R * K * d.expert_ff) && dalloc(E, &e->hs, R * K * d.expert_ff / 32) &&
+              dalloc(E, &e->hq, W * R * K * d.expert_ff) && dalloc(E, &e->hs, W * R * K * d.expert_ff / 32) &&
               dalloc(E, &e->sq, R * d.shared_ff) && dalloc(E, &e->ss, R * d.shared_ff / 32) &&
               dalloc(E, &e->xn, R * H) && dalloc(E, &e->qh, R * key_dim) && dalloc(E, &e->kh, R * key_dim) && dalloc(E, &e->vh, R * vd) &&
               dalloc(E, &e->gb, R * d.ssm_dt_rank * 2) && dalloc(E, &e->core, R * vd) && dalloc(E, &e->xlast, B * H) &&
-              dalloc(E, &e->h_all, R * K * d.expert_ff) && dalloc(E, &e->o_all, R * K * H) && dalloc(E, &e->shd, R * H) &&
-              dalloc(E, &e->qkvc2, R * cd) && dalloc(E, &e->pair_off, (size_t)d.n_expert + 1) && dalloc(E, &e->pair_list, R * K);
+              dalloc(E, &e->h_all, W * R * K * d.expert_ff) && dalloc(E, &e->o_all, W * R * K * H) && dalloc(E, &e->shd, R * H) &&
+              dalloc(E, &e->qkvc2, R * cd) && dalloc(E, &e->pair_off, (size_t)d.n_expert + 1) && dalloc(E, &e->pair_list, W * R * K);
     if (!ok) { for (void* p : e->allocs) cudaFree(p); return 1; }
     e->host_pos.assign(B, 0);
     if (getenv("ITB_STAMPS")) dalloc(E, &e->stamps, 8 * 400);   // debug: phase clocks of k_in_proj
     cudaEventCreate(&e->ev0); cudaEventCreate(&e->ev1);
+    cudaMemsetAsync(e->h_all, 0, W * R * K * d.expert_ff * sizeof(float), c->stream);   // pairs served elsewhere are quantised too: keep them finite
+    if (world > 1) {
+        e->ep = new EpState();
+        e->ep->world = world;
+        if (!(dalloc(E, &e->ep->gxq, W * R * H) && dalloc(E, &e->ep->gxs, W * R * H / 32) && dalloc(E, &e->ep->gids, W * R * K) &&
+              dalloc(E, &e->ep->o_mine, R * K * H))) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
+    }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) { itb_fail_msg(c, "engine: device error during set-up"); return 1; }
     *out = e.release();
+    return 0;
+}
+
+extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, itb_engine** out) { return engine_create(m, n_ctx, n_seq, 1, out); }
+
+extern "C" int itb_ep_unique_id(uint8_t* out128) {
+    NcclApi& nc = nccl_api();
+    if (!nc.ok) return 1;
+    NcclApi::UniqueId id;
+    if (nc.GetUniqueId(&id) != 0) return 1;
+    memcpy(out128, id.internal, 128);
+    return 0;
+}
+
+extern "C" int itb_engine_create_ep(itb_model* m, uint32_t n_ctx, uint32_t n_seq, const uint8_t* unique_id128, int rank, int world, itb_engine** out) {
+    *out = nullptr;
+    itb_ctx* c = m->c;
+    NcclApi& nc = nccl_api();
+    if (!nc.ok) { itb_fail_msg(c, "expert-parallel engine: libnccl.so.2 is not loadable in this process"); return 1; }
+    const uint32_t E = m->d.n_expert;
+    if (world < 2 || rank < 0 || rank >= world || E % (uint32_t)world) { itb_fail_msg(c, "expert-parallel engine: world must be >= 2 and divide n_expert"); return 1; }
+    const uint32_t per = E / (uint32_t)world;
+    if (m->expert_lo != per * (uint32_t)rank || m->expert_hi != per * (uint32_t)(rank + 1)) {
+        itb_fail_msg(c, "expert-parallel engine: the model must hold exactly this rank's expert range"); return 1;
+    }
+    if (engine_create(m, n_ctx, n_seq, world, out)) return 1;
+    itb_engine* e = *out;
+    e->ep->rank = rank;
+    NcclApi::UniqueId id;
+    memcpy(id.internal, unique_id128, 128);
+    int rc = nc.CommInitRank(&e->ep->comm, world, id, rank);
+    if (rc != 0) {
+        itb_fail_msg(c, (std::string("expert-parallel engine: ncclCommInitRank failed: ") + (nc.GetErrorString ? nc.GetErrorString(rc) : "?")).c_str());
+        itb_engine_destroy(e); *out = nullptr; return 1;
+    }
     return 0;
 }
 
@@ -755,6 +864,7 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     if (!e) return;
     cudaStreamSynchronize(e->c->stream);
     drop_graph(e);
+    if (e->ep) { if (e->ep->comm) nccl_api().CommDestroy(e->ep->comm); delete e->ep; e->ep = nullptr; }
     for (void* p : e->allocs) cudaFree(p);
     cudaFree(e->history); cudaFree(e->prompt);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
@@ -782,7 +892,7 @@ static bool ensure_graph(itb_engine* e) {
     cudaStream_t st = c->stream;
     // one eager step's worth of attribute set-up happens inside enqueue_step; capture it once
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return itb_fail_msg(c, "engine: cannot begin capture");
-    if (e->B == 1) enqueue_step(e, st);
+    if (e->B == 1 && !e->ep) enqueue_step(e, st);
     else e->launches_per_step = enqueue_rows(e, st, (int)e->B, 1, e->tokens);
     cudaError_t err = cudaStreamEndCapture(st, &e->graph);
     if (err != cudaSuccess) return itb_fail(c, "engine: capture", err);
@@ -801,13 +911,20 @@ static bool check_flag(itb_engine* e) {
 
 static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
     itb_ctx* c = e->c;
-    if (!ensure_graph(e)) return false;
+    // expert-parallel steps hold NCCL calls; they are captured like the rest unless ITB_EP_GRAPH=0 asks for eager launches
+    static const bool ep_graph = !(getenv("ITB_EP_GRAPH") && atoi(getenv("ITB_EP_GRAPH")) == 0);
+    const bool use_graph = !e->ep || ep_graph;
+    if (use_graph && !ensure_graph(e)) return false;
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + steps > e->n_ctx) return itb_fail_msg(c, "context overflow: the step would write past n_ctx");  // src/model/qwen35.rs:984-990
     if (timed) cudaEventRecord(e->ev0, c->stream);
     for (uint32_t s = 0; s < steps; ++s) {
-        cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
-        if (err != cudaSuccess) return itb_fail(c, "engine: graph launch", err);
+        if (use_graph) {
+            cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
+            if (err != cudaSuccess) return itb_fail(c, "engine: graph launch", err);
+        } else {
+            e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
+        }
     }
     c->launches += (uint64_t)steps * e->launches_per_step;
     if (timed) cudaEventRecord(e->ev1, c->stream);

@@ -279,13 +279,53 @@ class Model:
         return self.L.itb_model_decode_bytes(self.h, n_seq, n_pos, distinct_experts)
 
 
+def expert_range(rank, world, n_expert):
+    """The contiguous range of routed experts rank `rank` of `world` stores (src/ops/mod.rs:1024-1048: placement by range)."""
+    if world < 1 or not 0 <= rank < world or n_expert % world:
+        raise ValueError("world must divide n_expert and 0 <= rank < world")
+    per = n_expert // world
+    return per * rank, per * (rank + 1)
+
+
+def ep_unique_id(lib_=None):
+    """128 bytes that name a new NCCL communicator; rank 0 makes them, every rank passes the same bytes to Engine(ep=...)."""
+    L = lib_ or lib()
+    out = np.zeros(128, np.uint8)
+    if L.itb_ep_unique_id(_p(out)):
+        raise RuntimeError("NCCL is not loadable in this process")
+    return out.tobytes()
+
+
+def share_unique_id(rank, lib_=None, group=None):
+    """Rank 0's unique id handed to every rank of an initialised torch.distributed group (any backend)."""
+    import torch
+    import torch.distributed as dist
+    t = torch.zeros(128, dtype=torch.uint8)
+    if rank == 0:
+        t = torch.frombuffer(bytearray(ep_unique_id(lib_)), dtype=torch.uint8).clone()
+    if dist.get_backend(group) == "nccl":
+        t = t.cuda(); dist.broadcast(t, 0, group=group); t = t.cpu()
+    else:
+        dist.broadcast(t, 0, group=group)
+    return t.numpy().tobytes()
+
+
 class Engine:
     """Engine::{prefill, decode, generate} (src/engine/mod.rs:352-437) over n_seq independent sequences."""
 
-    def __init__(self, model: Model, n_ctx, n_seq=1):
+    def __init__(self, model: Model, n_ctx, n_seq=1, ep=None):
+        """ep = (rank, world, unique_id bytes): an expert-parallel engine over a model that holds this rank's expert range
+        (`expert_range`); every rank must then make the same calls with the same shapes (each on its own sequences)."""
         self.model, self.L, self.n_seq = model, model.L, n_seq
         h = C.c_void_p()
-        if self.L.itb_engine_create(model.h, n_ctx, n_seq, C.byref(h)):
+        if ep is None:
+            rc = self.L.itb_engine_create(model.h, n_ctx, n_seq, C.byref(h))
+        else:
+            rank, world, uid = ep
+            uid = np.frombuffer(bytes(uid), np.uint8).copy()
+            assert uid.size == 128
+            rc = self.L.itb_engine_create_ep(model.h, n_ctx, n_seq, _p(uid), int(rank), int(world), C.byref(h))
+        if rc:
             model.ops.check(); raise RuntimeError("itb_engine_create failed")
         self.h = h
         self.n_vocab = model.dims.n_vocab
