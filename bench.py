@@ -171,6 +171,32 @@ def other_configs(host, model, dims, seed, hbm, args):
     return out
 
 
+def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
+    """The same decode workload with the routed experts sharded over the ranks (each rank: its expert range, the dense
+    layers replicated, its own sequences; per MoE layer an all-gather and a reduce-scatter over NCCL). Every rank runs
+    this in lockstep; returns the whole-job figure (max time over ranks)."""
+    B = args.batch
+    uid = host.share_unique_id(rank)
+    lo, hi = host.expert_range(rank, world, dims["n_expert"])
+    shard = host.Model(ops, host.ModelDims(**dims)); shard.synth(seed, lo, hi)
+    eng = host.Engine(shard, N_CTX, B, ep=(rank, world, uid))
+    eng.prefill(prompts(B, seed + 1000 * rank, dims["n_vocab"]), want_logits=False)
+    first = eng.decode_loop(np.zeros(B, np.uint32), max(args.warmup, 3))[-1]
+    dist.barrier(); torch.cuda.synchronize()
+    eng.decode_loop(first, args.steps)
+    torch.cuda.synchronize()
+    t = torch.tensor([eng.last_ms()], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t[0])
+    n_moe = dims["n_layer"]
+    out = {"value": world * B * args.steps / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms / args.steps, "batch_per_gpu": B,
+           "experts_per_gpu": hi - lo, "collectives_per_step": 2 * n_moe, "launches_per_step": int(eng.launches_per_step()),
+           "note": "experts sharded by range, dense replicated; per MoE layer all-gather(rows, routing) + exact sum reduce-scatter(pair outputs) "
+                   "over NCCL, captured in the step's CUDA graph"}
+    eng.close(); shard.close()
+    return out
+
+
 def run_product(args, rank, world):
     from inferred_thoughts_b200 import host
     import torch
@@ -180,10 +206,10 @@ def run_product(args, rank, world):
         dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", rank))))
     device = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(device)
-    dims = dict(configs.M35B)
+    dims = dict(configs.L177B if args.model == "l177b" else configs.M35B)
     if args.layers:
         dims = configs.with_layers(dims, args.layers)   # profiling aid only: a line with "layers" set is not a bench number
-    seed = configs.SEEDS["m35b"]
+    seed = configs.SEEDS[args.model]
     kv = "bf16"
     ops = host.B200Ops(device, f"kv={kv},exact={args.exact}")
     model = host.Model(ops, host.ModelDims(**dims))
@@ -221,6 +247,12 @@ def run_product(args, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, e2e_s = float(t[0]), float(t[1])
     n_pos = eng.pos(0)
+    ep = None
+    if world > 1 and not args.no_extra and dims["n_expert"] % world == 0:
+        try:
+            ep = expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch)
+        except Exception as ex:   # every rank takes the same branch: failures here are set-up failures common to all
+            ep = {"error": str(ex)}
     if rank != 0:
         return
     hbm, hbm_src = peaks()
@@ -233,11 +265,11 @@ def run_product(args, rank, world):
     ms_per_step = dev_ms / args.steps
     value = world * B * args.steps / (dev_ms / 1e3)
     line = {
-        "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)", "value": value, "unit": "tok/s",
+        "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)" if args.model == "m35b" else "decode tok/s, ~177B-shape NVFP4 (BASELINE.json config 5)", "value": value, "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 (int8 x int8 / e2m1 x int8 dots, f32 accumulate; f32 state)",
         "data": "synthetic (seeded Gaussian weights quantised to NVFP4 / Q8_0, uniform-random token ids)",
-        "config": {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}", "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": kv,
+        "config": {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}" if args.model == "m35b" else f"cfg5-decode-177B-shape-bs{B}", "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": kv,
                    "n_pos_at_end": n_pos, **({"layers": args.layers, "not_a_bench_number": True} if args.layers else {}), "f32_dots": "serial-k" if args.exact else "tree", "parallelism": "replicas" if world > 1 else "single",
                    "l2": "each step streams ~2.8 GB of weights, far beyond the 126 MB L2; no flush needed"},
         "e2e": {"value": world * B * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
@@ -249,6 +281,8 @@ def run_product(args, rank, world):
                           "frac": step_bytes / ms_per_step / 1e6 / hbm, "frac_of_8TBs_nominal": step_bytes / ms_per_step / 1e6 / 8000.0},
         "kernels": kb, "clocks": clocks, "synth_s": synth_s,
     }
+    if ep is not None:
+        line["expert_parallel"] = ep
     if world == 1 and not args.no_extra:
         line["other_configs"] = other_configs(host, model, dims, seed, hbm, args)
     if world == 1 and not args.no_cpu:
@@ -320,6 +354,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the prefill and batch-32 measurements")
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens before the timed decode steps (BASELINE: 512)")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
+    ap.add_argument("--model", default="m35b", choices=["m35b", "l177b"], help="m35b: the headline 35B-A3B shape; l177b: BASELINE config 5's ~177B shape")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: the same shape with fewer layers (small device footprint for ncu captures)")
     args = ap.parse_args()
     global PROMPT

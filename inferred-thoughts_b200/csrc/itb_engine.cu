@@ -411,6 +411,8 @@ static void launch_k(bool pdl, void (*k)(KA...), dim3 g, dim3 b, size_t sm, cuda
     if (err != cudaSuccess) fprintf(stderr, "[itb] kernel launch failed: %s\n", cudaGetErrorString(err));
 }
 
+constexpr size_t SMEM_BUDGET = 200 * 1024;   // dynamic shared memory the row-streaming kernels are allowed (set_smem below)
+
 // One decode step for all B sequences, enqueued on `st`.
 static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
@@ -434,6 +436,9 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     auto launch_in = [&](InProj& p, int rows, int gx) {
         int per_warp = (rows + gx * NWG - 1) / (gx * NWG) + 1;
         p.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+        // the warps' term matrices must fit the block's shared memory (wide rows: fewer rows folded together)
+        const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
+        p.br = std::max(pass_in, std::min(p.br, cap / pass_in * pass_in));
         p.prefetch = pdl;
         if (e->stamps) { p.stamps = e->stamps + 8 * (e->n_stamped % 400); e->n_stamped++; }
         launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
@@ -442,6 +447,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         int gx = std::max(1, std::min(sms, H / NWG)), pass = 32 >> lanes_shift(n_in / 32);
         int per_warp = (H + gx * NWG - 1) / (gx * NWG) + 1;
         o.br = std::min(std::max(32 / pass, 1) * pass, (per_warp + pass - 1) / pass * pass);
+        const int cap = (int)((SMEM_BUDGET - (size_t)n_in - (size_t)(n_in / 32) * 4 - 64) / (NWG * 4) / (n_in / 32 + 1));
+        o.br = std::max(pass, std::min(o.br, cap / pass * pass));
         o.prefetch = pdl;
         launch_k(pdl, k_out_proj, dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st, o);
     };
@@ -753,6 +760,8 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             int gx = std::max(1, std::min(sms, ((int)d.n_vocab + 2 * NWG - 1) / (2 * NWG)));
             int per_warp = ((int)d.n_vocab + gx * NWG - 1) / (gx * NWG) + 1;
             hp.br = std::min(std::max(32 / pass_in, 1) * pass_in, (per_warp + pass_in - 1) / pass_in * pass_in);
+            const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
+            hp.br = std::max(pass_in, std::min(hp.br, cap / pass_in * pass_in));
             set_smem((const void*)k_in_proj, 200 * 1024);
             k_in_proj<<<dim3(gx, n_seq), TPB, in_proj_smem(H, c->exact, hp.br), st>>>(hp); launches++;
         }
