@@ -596,7 +596,9 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     if (!attrs_set) {
         set_smem((const void*)k_gemm_q8<4>, 200 * 1024); set_smem((const void*)k_gemm_q8<1>, 200 * 1024);
         set_smem((const void*)k_glu_grouped, 200 * 1024); set_smem((const void*)k_down_grouped, 200 * 1024);
-        set_smem((const void*)k_tile_q8<2, 256, 2>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
+        set_smem((const void*)k_matmul_f32_rows<20>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<24>, 64 * 1024);
+        set_smem((const void*)k_matmul_f32_rows<28>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<32>, 64 * 1024);
+        set_smem((const void*)k_tile_q8<1, 256, 4>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
         set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<2, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<4, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256, 1>, 226 * 1024);
@@ -612,7 +614,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         const bool skinny = R <= 32;
         if (skinny && k % 256 == 0) {
             const int ns = std::min(k / 256, TILE_STAGES);
-            k_tile_q8<2, 256, 2><<<dim3((w.n_out + 63) / 64, (R + 31) / 32), 256, tile_smem<MK_Q8, 2, 256, 2>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
+            k_tile_q8<1, 256, 4><<<dim3((w.n_out + 31) / 32, (R + 31) / 32), 256, tile_smem<MK_Q8, 1, 256, 4>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
         } else if (!skinny && k % 256 == 0) {
             const int ns = std::min(k / 256, TILE_STAGES);
             k_tile_q8<4, 256, 2><<<dim3((w.n_out + 63) / 64, (R + 63) / 64), 256, tile_smem<MK_Q8, 4, 256, 2>(k), st>>>(w, xq, xs, R, out, stride, mode, ns);
@@ -622,6 +624,17 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     };
     auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode) { gemm_n(w, xq, xs, out, stride, mode, R); };
     auto f32mm = [&](const DevF32& w, const float* x, float* out) {
+        if (!c->exact && w.n_in % 512 == 0 && w.n_in <= 4096) {
+            const dim3 g((w.n_out + 7) / 8, (R + F32_TOK - 1) / F32_TOK);
+            const size_t sm = (size_t)F32_TOK * w.n_in * 4;
+            switch (w.n_in / 128) {
+#define F32_CASE(NV) case NV: k_matmul_f32_rows<NV><<<g, 256, sm, st>>>(w, x, R, out); break;
+                F32_CASE(4) F32_CASE(8) F32_CASE(12) F32_CASE(16) F32_CASE(20) F32_CASE(24) F32_CASE(28) F32_CASE(32)
+#undef F32_CASE
+            }
+            launches++;
+            return;
+        }
         const int nw = 4;
         dim3 g(std::max(1, std::min(2 * sms, (w.n_out + 31) / 32)), R);
         size_t sm = (size_t)w.n_in * 4 + (size_t)nw * 32 * 33 * 4;

@@ -10,6 +10,47 @@
 
 namespace {
 
+// F32 matrix against many rows (router logits, alpha/beta, shared-expert gate), tree mode. A block takes 8 weight rows
+// (one per warp, held in registers) and F32_TOK token rows (staged in shared memory with every load in flight at once):
+// two memory round trips per block, blocks for every (row group, token group). Per lane the products are summed in the
+// order of f32_rows<false> (the one-token path), then the same shuffle tree, so a row gets the bits it gets alone.
+// grid (ceil(n_out/8), ceil(n_rows/F32_TOK)), block 256, dynamic smem F32_TOK * n_in floats; n_in = 128 * NV.
+constexpr int F32_TOK = 4;
+template <int NV>
+__global__ void __launch_bounds__(256) k_matmul_f32_rows(DevF32 w, const float* x, int n_rows, float* out) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* xs = (float*)smem;
+    constexpr int n = 128 * NV;
+    const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + wid, t0 = blockIdx.y * F32_TOK, nt = min(n_rows - t0, F32_TOK);
+    float4 wv[NV];
+    const float* wr = w.w + (size_t)min(row, w.n_out - 1) * n;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) wv[j] = __ldg((const float4*)(wr + lane * 4 + 128 * j));
+    constexpr int PER = F32_TOK * n / 4 / 256;   // float4 per thread of the token tile
+    float4 xv[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+        const int e = threadIdx.x + 256 * i, t = e / (n / 4);
+        xv[i] = t < nt ? __ldg((const float4*)(x + (size_t)t0 * n) + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < PER; ++i) ((float4*)xs)[threadIdx.x + 256 * i] = xv[i];
+    __syncthreads();
+    if (row >= w.n_out) return;
+    for (int t = 0; t < nt; ++t) {
+        const float* xr = xs + (size_t)t * n + lane * 4;
+        float s = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            const float4 v = *(const float4*)(xr + 128 * j);
+            s += wv[j].x * v.x + wv[j].y * v.y + wv[j].z * v.z + wv[j].w * v.w;
+        }
+        s = warp_sum(s);
+        if (lane == 0) out[(size_t)(t0 + t) * w.n_out + row] = s;
+    }
+}
+
 // RMSNorm + Q8_0 quantisation of each row (src/ops/naive.rs:139-152, :653-675): normalised f32 row, int8 quants,
 // scales. grid = rows, block 256.
 __global__ void __launch_bounds__(256) k_norm_quant(const float* x, const float* w, int n, float eps, float* xn_out, int8_t* xq, float* xs) {

@@ -4,9 +4,10 @@
 // per k-block. The arithmetic is the exact chain of itb_mma.cuh: one int8 MMA per quantisation block, its int32
 // sum scaled and added to an f32 accumulator in ascending block order (src/ops/naive.rs:691-734).
 //
-// 8 warps, split TH ways over the tile's tokens: TH=2 -> warp w owns rows 16*(w&3).. and token half w>>2 (64 rows x
-// 16*NJ tokens, for wide token tiles); TH=1 -> warp w owns rows 16*w.. and all 8*NJ tokens (128 rows, for the few
-// rows an expert sees: every weight is decoded by exactly one warp). NJ = groups of 8 tokens per warp. Token rows
+// 8 warps, split TH ways over the tile's tokens and 8/TH ways over its rows: TH=1 -> warp w owns rows 16*w.. and all
+// 8*NJ tokens (128 rows: for the few rows an expert sees, every weight is decoded by exactly one warp); TH=2 -> 64 rows
+// x 16*NJ tokens (wide token tiles); TH=4 -> 32 rows x 32*NJ tokens (batched decode of dense matrices: small blocks,
+// so every SM gets several and their pipelines overlap). NJ = groups of 8 tokens per warp. Token rows
 // are named by a per-tile index array so the same loop serves dense matmuls (consecutive rows) and grouped
 // experts (rows gathered by an expert's pair list).
 #pragma once
@@ -34,6 +35,10 @@ __device__ __forceinline__ void ue4m3x2_half(uint32_t two, float& lo, float& hi)
     const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
     lo = __low2float(hh) * 0.5f; hi = __high2float(hh) * 0.5f;
 }
+
+// Exact int32 -> f32 for |v| < 2^22 without the conversion pipe: add v to the bit pattern of 1.5 * 2^23, whose ulp is
+// 1, and subtract 1.5 * 2^23 again (block sums here stay below 32 * 127 * 127 < 2^19).
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
 
 template <int KIND, int NJ, int KC, int TH = 2>
 struct TileCfg {
@@ -92,7 +97,8 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[j][i] = 0.0f;
     for (int c = 0; c < n_stage - 1; ++c) { if (c < n_chunk) load(c); cp_async_commit(); }
-    const int rw = (TH == 2 ? (wid & 3) : wid) * 16, tb = TH == 2 ? (wid >> 2) * NJ * 8 : 0;
+    constexpr int RG = 8 / TH;   // row groups of 16 among the 8 warps
+    const int rw = (wid % RG) * 16, tb = (wid / RG) * NJ * 8;
     for (int c = 0; c < n_chunk; ++c) {
         if (n_stage == 1) { __syncthreads(); load(c); cp_async_commit(); }
         if (n_stage >= 4) cp_async_wait<2>(); else if (n_stage == 3) cp_async_wait<1>(); else cp_async_wait<0>();
@@ -117,10 +123,10 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
                     int cc[4];
                     mma_s8_k32(cc, va.x, vb.x, va.y, vb.y, x.x, x.y);
                     const float dx0 = xs_s[(tj + 2 * t) * C::XSF + b], dx1 = xs_s[(tj + 2 * t + 1) * C::XSF + b];
-                    acc[j][0] += (float)cc[0] * (dwa * dx0);
-                    acc[j][1] += (float)cc[1] * (dwa * dx1);
-                    acc[j][2] += (float)cc[2] * (dwb * dx0);
-                    acc[j][3] += (float)cc[3] * (dwb * dx1);
+                    acc[j][0] += i2f_small(cc[0]) * (dwa * dx0);
+                    acc[j][1] += i2f_small(cc[1]) * (dwa * dx1);
+                    acc[j][2] += i2f_small(cc[2]) * (dwb * dx0);
+                    acc[j][3] += i2f_small(cc[3]) * (dwb * dx1);
                 }
             }
         } else {
@@ -141,14 +147,14 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
                     mma_s8_k16(cc, a0, a1, x0);
                     mma_s8_k16(dd, c0, c1, x1);
                     const float dy0 = xs_s[(tj + 2 * t) * C::XSF + (s >> 1)], dy1 = xs_s[(tj + 2 * t + 1) * C::XSF + (s >> 1)];
-                    acc[j][0] += dy0 * da0 * (float)cc[0];
-                    acc[j][1] += dy1 * da0 * (float)cc[1];
-                    acc[j][2] += dy0 * db0 * (float)cc[2];
-                    acc[j][3] += dy1 * db0 * (float)cc[3];
-                    acc[j][0] += dy0 * da1 * (float)dd[0];
-                    acc[j][1] += dy1 * da1 * (float)dd[1];
-                    acc[j][2] += dy0 * db1 * (float)dd[2];
-                    acc[j][3] += dy1 * db1 * (float)dd[3];
+                    acc[j][0] += dy0 * da0 * i2f_small(cc[0]);
+                    acc[j][1] += dy1 * da0 * i2f_small(cc[1]);
+                    acc[j][2] += dy0 * db0 * i2f_small(cc[2]);
+                    acc[j][3] += dy1 * db0 * i2f_small(cc[3]);
+                    acc[j][0] += dy0 * da1 * i2f_small(dd[0]);
+                    acc[j][1] += dy1 * da1 * i2f_small(dd[1]);
+                    acc[j][2] += dy0 * db1 * i2f_small(dd[2]);
+                    acc[j][3] += dy1 * db1 * i2f_small(dd[3]);
                 }
             }
         }
@@ -161,7 +167,8 @@ __device__ __forceinline__ void tile_gemm(const uint8_t* wq, const uint8_t* ws, 
 template <int NJ, int TH, class F>
 __device__ __forceinline__ void tile_foreach(const float (&acc)[NJ][4], int r0, int n_rows, F f) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int ra = r0 + (TH == 2 ? (wid & 3) : wid) * 16 + g, rb = ra + 8, tb = TH == 2 ? (wid >> 2) * NJ * 8 : 0;
+    constexpr int RG = 8 / TH;
+    const int ra = r0 + (wid % RG) * 16 + g, rb = ra + 8, tb = (wid / RG) * NJ * 8;
 #pragma unroll
     for (int j = 0; j < NJ; ++j) {
         const int tj = tb + 8 * j + 2 * t;

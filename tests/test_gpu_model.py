@@ -242,6 +242,37 @@ def test_pipelined_rows_batched_decode_equals_single_sequences(mid, n_seq):
     eb.close()
 
 
+def test_tree_mode_rows_equal_single_rows():
+    """exact=0 (F32 dots by a shuffle tree, the benchmark's mode): the multi-row F32 kernel keeps the one-token kernel's
+    summation order, so batched decode and multi-row prefill still give each row the bits it gets alone."""
+    import os
+    from inferred_thoughts_b200 import host
+    ops = host.B200Ops(0, "exact=0")
+    model = host.Model(ops, host_dims(MID)); model.synth(5)
+    prompts = np.stack([prompt_ids(40 + i, 11, MID["n_vocab"]) for i in range(5)])
+    eb = host.Engine(model, 64, 5)
+    lb = eb.prefill(prompts)
+    singles = [host.Engine(model, 64, 1) for _ in range(5)]
+    os.environ["ITB_PREFILL_STEPWISE"] = "1"
+    try:
+        ls = [e.prefill(p) for e, p in zip(singles, prompts)]     # token by token through the fused one-token kernels
+    finally:
+        del os.environ["ITB_PREFILL_STEPWISE"]
+    for i in range(5):
+        assert ls[i].view(np.uint32).tolist() == lb[i].view(np.uint32).tolist(), i
+    toks = np.argmax(lb, 1).astype(np.uint32)
+    for step in range(3):
+        l2, nb = eb.decode(toks)
+        for i in range(5):
+            l1, n1 = singles[i].decode([toks[i]])
+            assert l1[0].view(np.uint32).tolist() == l2[i].view(np.uint32).tolist(), (step, i)
+        toks = nb
+    ops.check()
+    for e in singles:
+        e.close()
+    eb.close(); model.close(); ops.close()
+
+
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):
     from inferred_thoughts_b200 import host
     ops, model = gpu
