@@ -347,7 +347,7 @@ struct itb_engine {
     int8_t* xq = nullptr; float* xs = nullptr;
     int32_t* route_ids = nullptr; float* route_w = nullptr;  // [n_layer][B][n_used]
     int32_t* history = nullptr; int* step_counter = nullptr; uint32_t history_cap = 0;
-    int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr; long long* stamps = nullptr; int n_stamped = 0;
+    int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr;
     int8_t *aq = nullptr, *hq = nullptr, *sq = nullptr; float *as = nullptr, *hs = nullptr, *ss = nullptr;  // producer-quantised activations
     float *h_all = nullptr, *o_all = nullptr, *shd = nullptr, *qkvc2 = nullptr; int *pair_off = nullptr, *pair_list = nullptr;  // grouped experts (multi-row path)
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
@@ -416,7 +416,6 @@ constexpr size_t SMEM_BUDGET = 200 * 1024;   // dynamic shared memory the row-st
 // One decode step for all B sequences, enqueued on `st`.
 static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
-    e->n_stamped = 0;
     const itb_model_dims& d = m->d;
     const int B = e->B, H = d.n_embd, sms = c->sm_count;
     const int key_dim = d.ssm_d_state * d.ssm_n_group, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
@@ -440,7 +439,6 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
         p.br = std::max(pass_in, std::min(p.br, cap / pass_in * pass_in));
         p.prefetch = pdl;
-        if (e->stamps) { p.stamps = e->stamps + 8 * (e->n_stamped % 400); e->n_stamped++; }
         launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
     };
     auto launch_out = [&](OutProj& o, int n_in) {
@@ -608,7 +606,6 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     }
     // Pipelined tile kernels when k is a multiple of the chunk (every matrix of the 35B and 177B shapes); the
     // direct-load MMA kernels otherwise.
-    const bool skinny = R <= 32;
     auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R) {
         const int k = w.n_in;
         const bool skinny = R <= 32;
@@ -827,7 +824,6 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
               dalloc(E, &e->qkvc2, R * cd) && dalloc(E, &e->pair_off, (size_t)d.n_expert + 1) && dalloc(E, &e->pair_list, W * R * K);
     if (!ok) { for (void* p : e->allocs) cudaFree(p); return 1; }
     e->host_pos.assign(B, 0);
-    if (getenv("ITB_STAMPS")) dalloc(E, &e->stamps, 8 * 400);   // debug: phase clocks of k_in_proj
     cudaEventCreate(&e->ev0); cudaEventCreate(&e->ev1);
     cudaMemsetAsync(e->h_all, 0, W * R * K * d.expert_ff * sizeof(float), c->stream);   // pairs served elsewhere are quantised too: keep them finite
     if (world > 1) {
@@ -1108,8 +1104,24 @@ extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, it
     return 0;
 }
 
-extern "C" int itb_engine_debug_stamps(itb_engine* e, long long* out, size_t n) {
-    if (!e->stamps) return 1;
+// Phase timeline of the engine's kernels (see tl_mark): arm with a capacity, run steps, read the (tag, ns) pairs.
+extern "C" int itb_timeline_arm(itb_engine* e, uint32_t capacity) {
+    static unsigned long long* buf = nullptr;
+    static uint32_t cap = 0;
     cudaStreamSynchronize(e->c->stream);
-    return cudaMemcpy(out, e->stamps, n * 8, cudaMemcpyDeviceToHost) == cudaSuccess ? 0 : 1;
+    if (capacity > cap) { cudaFree(buf); buf = nullptr; if (cudaMalloc(&buf, (size_t)capacity * 16) != cudaSuccess) return 1; cap = capacity; }
+    unsigned long long* b = capacity ? buf : nullptr;
+    const unsigned zero = 0, c = capacity;
+    if (cudaMemcpyToSymbol(g_tl_n, &zero, 4) != cudaSuccess || cudaMemcpyToSymbol(g_tl_cap, &c, 4) != cudaSuccess ||
+        cudaMemcpyToSymbol(g_tl_buf, &b, 8) != cudaSuccess) return 1;
+    return 0;
+}
+extern "C" long itb_timeline_read(itb_engine* e, uint64_t* out_pairs, uint32_t capacity) {
+    cudaStreamSynchronize(e->c->stream);
+    unsigned n = 0; unsigned long long* b = nullptr;
+    if (cudaMemcpyFromSymbol(&n, g_tl_n, 4) != cudaSuccess || cudaMemcpyFromSymbol(&b, g_tl_buf, 8) != cudaSuccess || !b) return -1;
+    unsigned cap = 0; cudaMemcpyFromSymbol(&cap, g_tl_cap, 4);
+    n = std::min(std::min(n, cap), capacity);
+    if (n && cudaMemcpy(out_pairs, b, (size_t)n * 16, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    return (long)n;
 }

@@ -24,15 +24,13 @@ struct InProj {
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
     int prefetch;                                  // ask L2 for the warp's weight rows before waiting for the predecessor
-    long long* stamps;                             // debug: clock64 at phase boundaries of block 0 warp 0
 };
-#define STAMP(i) do { if (p.stamps && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) p.stamps[i] = clock64(); } while (0)
 
 __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_embd, nb = n / 32, gsh = lanes_shift(nb);
     const int b = blockIdx.y, wid = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    STAMP(0);
+    TL(TLK_IN_PROJ, 0);
     pdl_trigger();
     double* red = (double*)smem;
     float* xn = (float*)(red + 32);
@@ -74,11 +72,11 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         }
     }
     pdl_wait();
-    STAMP(1);
+    TL(TLK_IN_PROJ, 1);
     block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
-    STAMP(2);
+    TL(TLK_IN_PROJ, 2);
     block_quant_q8(xn, n, xq, xs);
-    STAMP(3);
+    TL(TLK_IN_PROJ, 3);
     if (p.xq_out && blockIdx.x == 0) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
         for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
@@ -112,7 +110,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         }
         base += p.q[m].n_out;
     }
-    STAMP(4);
+    TL(TLK_IN_PROJ, 4);
     // F32 rows. Serial-k mode: units of 32 rows, unit u on warp 0 of block u (it owns the tile). Otherwise one
     // row per warp, handed out from the far end of the grid's warps.
     if (p.exact) {
@@ -142,7 +140,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
             rbase = (rbase + p.f[m].n_out) % ngw;
         }
     }
-    STAMP(5);
+    TL(TLK_IN_PROJ, 5);
 }
 // br a multiple of the pass size 2 * (32 >> gsh)
 size_t in_proj_smem(int n, int exact, int br) {
@@ -164,18 +162,22 @@ __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     int b0, b1, r0, r1;
     share(p.w.n_out, gridDim.x, blockIdx.x, b0, b1);
     share(b1 - b0, nw, wid, r0, r1);
+    TL(TLK_OUT_PROJ, 0);
     pdl_trigger();
     if (p.prefetch && (threadIdx.x & 31) == 0 && r0 < r1) {
         l2_prefetch(p.w.q + (size_t)(b0 + r0) * n, (size_t)(r1 - r0) * n);
         l2_prefetch(p.w.s + (size_t)(b0 + r0) * nb, (size_t)(r1 - r0) * nb * 2);
     }
     pdl_wait();
+    TL(TLK_OUT_PROJ, 1);
     for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
     for (int i = threadIdx.x; i < nb; i += blockDim.x) as[i] = p.as[(size_t)b * nb + i];
     __syncthreads();
+    TL(TLK_OUT_PROJ, 2);
     float* x = p.x + (size_t)b * p.x_stride;
     rows_batched<MK_Q8, 1, 4>((const uint8_t*)p.w.q, (const uint8_t*)p.w.s, n, b0 + r0, b0 + r1, aq, as, terms, p.br, gsh,
                               [&](int row, float v) { x[row] += v; });
+    TL(TLK_OUT_PROJ, 3);
 }
 size_t out_proj_smem(int n, int br) {
     int nb = n / 32;
@@ -208,6 +210,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     const int key_dim = p.n_k * sk;
     const float* cv = p.conv + (size_t)b * p.conv_stride;
     float* sg = p.state + (size_t)b * p.state_stride + (size_t)h * sv * sk;
+    TL(TLK_GDN_CORE, 0);
     pdl_trigger();
     // the state belongs to this layer alone: its loads are in flight while the predecessor kernel finishes
     float4 ld[LD];
@@ -215,6 +218,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     for (int i = 0; i < LD; ++i) ld[i] = __ldcs((const float4*)sg + tid + i * 256);
     const float r_dt = p.dt_bias[h], r_a = p.ssm_a[h], r_nw = p.ssm_norm[tid < sv ? tid : 0];
     pdl_wait();
+    TL(TLK_GDN_CORE, 1);
     // every other global operand is requested now too, so the kernel has one memory round trip
     const float r_alpha = p.alpha[(size_t)b * p.n_v + h], r_beta = p.beta[(size_t)b * p.n_v + h];
     const size_t oidx = (size_t)b * p.n_v * sv + (size_t)h * sv + (tid < sv ? tid : 0);
@@ -230,6 +234,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
         d[0] = ld[i].x; d[1] = ld[i].y; d[2] = ld[i].z; d[3] = ld[i].w;
     }
     __syncthreads();
+    TL(TLK_GDN_CORE, 2);
     // warp 0 normalises k, warp 1 normalises q (f64 tree sum, narrowing before the root)
     if (wid < 2) {
         float* src = kq + wid * sk;
@@ -244,22 +249,42 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
         }
     }
     __syncthreads();
+    TL(TLK_GDN_CORE, 3);
     if (tid < sv) {
         float a = r_alpha + r_dt;
         float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
         float g = exp_f(sp * r_a);
         float bt = sigmoid_f(r_beta);
+        // the thread's state row lives in registers for both passes (src/ops/naive.rs:109-132 order: decay, predict, update, read out)
         float* row = S + tid * (sk + 1);
+        float R[SK];
+#pragma unroll
+        for (int i = 0; i < SK; ++i) R[i] = row[i];
         float pred = 0.0f;
-#pragma unroll 4
-        for (int i = 0; i < sk; ++i) { float s = row[i] * g; row[i] = s; pred += s * kq[i]; }
+#pragma unroll
+        for (int i = 0; i < SK; i += 4) {
+            const float4 k4 = *(const float4*)(kq + i);
+            R[i] = R[i] * g; pred += R[i] * k4.x;
+            R[i + 1] = R[i + 1] * g; pred += R[i + 1] * k4.y;
+            R[i + 2] = R[i + 2] * g; pred += R[i + 2] * k4.z;
+            R[i + 3] = R[i + 3] * g; pred += R[i + 3] * k4.w;
+        }
         float d = bt * (vj - pred);
         float acc = 0.0f;
-#pragma unroll 4
-        for (int i = 0; i < sk; ++i) { float s = row[i] + kq[i] * d; row[i] = s; acc += s * kq[sk + i]; }
+#pragma unroll
+        for (int i = 0; i < SK; i += 4) {
+            const float4 k4 = *(const float4*)(kq + i), q4 = *(const float4*)(kq + SK + i);
+            R[i] = R[i] + k4.x * d; acc += R[i] * q4.x;
+            R[i + 1] = R[i + 1] + k4.y * d; acc += R[i + 1] * q4.y;
+            R[i + 2] = R[i + 2] + k4.z * d; acc += R[i + 2] * q4.z;
+            R[i + 3] = R[i + 3] + k4.w * d; acc += R[i + 3] * q4.w;
+        }
+#pragma unroll
+        for (int i = 0; i < SK; ++i) row[i] = R[i];
         o[tid] = acc;
     }
     __syncthreads();
+    TL(TLK_GDN_CORE, 4);
     {
         double acc = 0.0;
         for (int i = tid; i < sv; i += blockDim.x) acc += (double)(o[i] * o[i]);
@@ -286,6 +311,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
         const float* s = S + r * (sk + 1) + c0;
         __stcs((float4*)sg + tid + i * 256, make_float4(s[0], s[1], s[2], s[3]));
     }
+    TL(TLK_GDN_CORE, 5);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -304,7 +330,9 @@ __global__ void k_attn_prep(AttnPrep p) {
     float* val = (float*)smem;
     __shared__ double red[8];
     const int job = blockIdx.x, b = blockIdx.y, d = threadIdx.x, hd = p.hd, kvd = p.n_head_kv * hd;
+    TL(TLK_ATTN_PREP, 0);
     pdl_trigger(); pdl_wait();
+    TL(TLK_ATTN_PREP, 1);
     const int pos = p.pos[b];
     if (job == 0 && d == 0) p.npos_out[b] = pos + 1;
     const bool is_q = job < p.n_head, is_k = !is_q && job < p.n_head + p.n_head_kv;
@@ -353,23 +381,46 @@ __global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, in
                                  const int* n_pos_dev, int n_head, int8_t* out_q, float* out_s) {
     const size_t th = blockIdx.x;
     const int d = threadIdx.x, b = (int)(th / n_head);
+    TL(TLK_ATTN_COMB, 0);
     pdl_trigger(); pdl_wait();
+    TL(TLK_ATTN_COMB, 1);
     const int n_pos = n_pos_dev[b], per = max(ATTN_MIN_SPLIT, (n_pos + n_split - 1) / n_split), n_act = (n_pos + per - 1) / per;
+    // splits in trips of 8 with every load of a trip in flight; the combine itself keeps ascending split order
+    const float gt = gate[th * hd + d];
     float M = -INFINITY;
-    for (int s = 0; s < n_act; ++s) M = fmaxf(M, part_ml[(th * n_split + s) * 2]);
+    for (int s0 = 0; s0 < n_act; s0 += 8) {
+        float mv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mv[j] = s0 + j < n_act ? part_ml[(th * n_split + s0 + j) * 2] : -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) M = fmaxf(M, mv[j]);
+    }
     float L = 0.0f, A = 0.0f;
-    for (int s = 0; s < n_act; ++s) {
-        float ms = part_ml[(th * n_split + s) * 2];
-        float c = ms == -INFINITY ? 0.0f : __expf(ms - M);
-        L += part_ml[(th * n_split + s) * 2 + 1] * c;
-        A += part_acc[(th * n_split + s) * hd + d] * c;
+    for (int s0 = 0; s0 < n_act; s0 += 8) {
+        float mv[8], lv[8], av[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const bool in = s0 + j < n_act;
+            mv[j] = in ? part_ml[(th * n_split + s0 + j) * 2] : -INFINITY;
+            lv[j] = in ? part_ml[(th * n_split + s0 + j) * 2 + 1] : 0.0f;
+            av[j] = in ? part_acc[(th * n_split + s0 + j) * hd + d] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (s0 + j < n_act) {
+                const float c = mv[j] == -INFINITY ? 0.0f : __expf(mv[j] - M);
+                L += lv[j] * c;
+                A += av[j] * c;
+            }
+        }
     }
     float v = A / L;
-    v *= sigmoid_f(gate[th * hd + d]);
+    v *= sigmoid_f(gt);
     float dq;
     int8_t q = warp_quant_q8(v, &dq);
     out_q[th * hd + d] = q;
     if ((d & 31) == 0) out_s[(th * hd + d) / 32] = dq;
+    TL(TLK_ATTN_COMB, 2);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -392,10 +443,13 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     __shared__ int32_t s_ids[16];
     __shared__ float s_wts[16];
     __shared__ float s_gu[64];
+    __shared__ float s_sum;
     const int n = p.n_embd, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = p.gate.n_out, upp = ff / 32;
     const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x, n_units = p.n_used * upp;
+    TL(TLK_MOE_GLU, 0);
     pdl_trigger(); pdl_wait();
+    TL(TLK_MOE_GLU, 1);
     if (unit >= n_units) {
         // shared expert: silu(gate) * up for 32 elements, quantised (src/model/qwen35.rs:1669-1678)
         if (wid == 0) {
@@ -416,7 +470,15 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
         // softmax numerators (src/ops/naive.rs:362-376) by the whole block: every warp finds the max itself
         const float* lg = p.router + (size_t)b * p.n_expert;
         float mx = -INFINITY;
-        for (int i = lane; i < p.n_expert; i += 32) mx = fmaxf(mx, lg[i]);
+        if (p.n_expert <= 512) {
+            float lv[16];   // every load of the warp's pass over the logits in flight at once
+#pragma unroll
+            for (int j = 0; j < 16; ++j) lv[j] = lane + 32 * j < p.n_expert ? lg[lane + 32 * j] : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) mx = fmaxf(mx, lv[j]);
+        } else {
+            for (int i = lane; i < p.n_expert; i += 32) mx = fmaxf(mx, lg[i]);
+        }
         mx = warp_max(mx);
         const int ne32 = (p.n_expert + 31) & ~31;
         for (int i = tid; i < ne32; i += blockDim.x) probs[i] = i < p.n_expert ? exp_f(lg[i] - mx) : 0.0f;
@@ -424,48 +486,75 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
         for (int i = tid; i < nb; i += blockDim.x) xs[i] = p.xs[(size_t)b * nb + i];
     }
     __syncthreads();
-    if (wid == 0) {
-        // serial sum in index order, divide, then top-k
+    TL(TLK_MOE_GLU, 2);
+    // softmax denominator: serial sum in index order (src/ops/naive.rs:362-376), one thread
+    if (tid == 0) {
         float sum = 0.0f;
-        if (lane == 0) {
 #pragma unroll 1
-            for (int i0 = 0; i0 < p.n_expert; i0 += 32) {
-                float4 q[8];
+        for (int i0 = 0; i0 < p.n_expert; i0 += 32) {
+            float4 q[8];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) q[j] = *(const float4*)(probs + i0 + 4 * j);
-                const int lim = p.n_expert - i0;
+            for (int j = 0; j < 8; ++j) q[j] = *(const float4*)(probs + i0 + 4 * j);
+            const int lim = p.n_expert - i0;
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (4 * j < lim) sum += q[j].x;
-                    if (4 * j + 1 < lim) sum += q[j].y;
-                    if (4 * j + 2 < lim) sum += q[j].z;
-                    if (4 * j + 3 < lim) sum += q[j].w;
-                }
+            for (int j = 0; j < 8; ++j) {
+                if (4 * j < lim) sum += q[j].x;
+                if (4 * j + 1 < lim) sum += q[j].y;
+                if (4 * j + 2 < lim) sum += q[j].z;
+                if (4 * j + 3 < lim) sum += q[j].w;
             }
         }
-        sum = __shfl_sync(0xffffffffu, sum, 0);
-        for (int i = lane; i < p.n_expert; i += 32) probs[i] /= sum;
-        __syncwarp();
-        int32_t ids[16];
-        float wts[16];
-        warp_topk_any(probs, p.n_expert, p.n_used, ids, wts);
-        if (lane == 0)
-            for (int r = 0; r < p.n_used; ++r) {
-                s_ids[r] = ids[r]; s_wts[r] = wts[r];
-                if (unit == 0) { p.ids_out[(size_t)b * p.n_used + r] = ids[r]; p.w_out[(size_t)b * p.n_used + r] = wts[r]; }
-            }
+        s_sum = sum;
+    }
+    TL(TLK_MOE_GLU, 6);
+    __syncthreads();
+    {
+        const float sum = s_sum;
+        for (int i = tid; i < p.n_expert; i += blockDim.x) probs[i] /= sum;
     }
     __syncthreads();
+    TL(TLK_MOE_GLU, 7);
+    // top-k without serial rounds: an expert's place in the pick order is the number of experts that beat it (greater
+    // probability, or equal and lower id: src/ops/mod.rs:1191-1216 picks by strict '>' scanning ascending ids)
+    {
+        const int ne32 = (p.n_expert + 31) & ~31;
+        for (int t = tid; t < p.n_expert; t += blockDim.x) {
+            const float pt = probs[t];
+            int rank = 0;
+            for (int j = 0; j < ne32; j += 4) {
+                const float4 q = *(const float4*)(probs + j);
+                rank += (q.x > pt || (q.x == pt && j < t)) + (q.y > pt || (q.y == pt && j + 1 < t)) +
+                        (q.z > pt || (q.z == pt && j + 2 < t)) + (q.w > pt || (q.w == pt && j + 3 < t));
+            }
+            if (rank < p.n_used) { s_ids[rank] = t; s_wts[rank] = pt; }
+        }
+    }
+    __syncthreads();
+    TL(TLK_MOE_GLU, 8);
+    if (tid == 0) {
+        float sum = 0.0f;
+        for (int r = 0; r < p.n_used; ++r) sum += s_wts[r];                 // summed in pick order (src/ops/mod.rs:1211)
+        const float denom = fmaxf(sum, 6.103515625e-5f);
+        for (int r = 0; r < p.n_used; ++r) {
+            const float w = s_wts[r] / denom;
+            s_wts[r] = w;
+            if (unit == 0) { p.ids_out[(size_t)b * p.n_used + r] = s_ids[r]; p.w_out[(size_t)b * p.n_used + r] = w; }
+        }
+    }
+    __syncthreads();
+    TL(TLK_MOE_GLU, 3);
     const int pick = unit / upp, row0 = (unit % upp) * 32;
     const int el = s_ids[pick] - p.gate.expert_lo;
     if (el < 0 || el >= p.gate.n_expert) return;   // this pick's expert lives on another device
     // 64 row-dots (32 gate rows, 32 up rows) spread over the block's warps
     const size_t eo = (size_t)el * ff;
+    const bool has_g = p.gate.scale2 != nullptr, has_u = p.up.scale2 != nullptr;
+    const float sg2 = has_g ? p.gate.scale2[el] : 1.0f, su2 = has_u ? p.up.scale2[el] : 1.0f;   // in flight under the row dots
     int k0, k1;
     share(64, blockDim.x >> 5, wid, k0, k1);
     const uint8_t* gn = p.gate.nib + eo * (n / 2); const uint8_t* gs = p.gate.sc + eo * nsb;
     const uint8_t* un = p.up.nib + eo * (n / 2); const uint8_t* us = p.up.sc + eo * nsb;
-    rows_list<MK_FP4, 4>(k1 - k0, n, terms, gsh,
+    rows_list<MK_FP4, 4, 2>(k1 - k0, n, terms, gsh,
         [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
             const int kk = k0 + k, row = row0 + (kk & 31);
             pa = (kk < 32 ? gn : un) + (size_t)row * (n / 2);
@@ -474,17 +563,18 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
         },
         [&](int k, float v) { s_gu[k0 + k] = v; });
     __syncthreads();
+    TL(TLK_MOE_GLU, 4);
     if (wid == 0) {
-        const bool has_g = p.gate.scale2 != nullptr, has_u = p.up.scale2 != nullptr;
         float g = s_gu[lane], u = s_gu[32 + lane];
-        if (has_g) g = g * p.gate.scale2[el];
-        if (has_u) u = u * p.up.scale2[el];
+        if (has_g) g = g * sg2;
+        if (has_u) u = u * su2;
         float v = silu_f(g) * u;
         float dq;
         int8_t q = warp_quant_q8(v, &dq);
         p.hq[((size_t)b * p.n_used + pick) * ff + row0 + lane] = q;
         if (lane == 0) p.hs[((size_t)b * p.n_used + pick) * upp + unit % upp] = dq;
     }
+    TL(TLK_MOE_GLU, 5);
 }
 size_t moe_glu_smem(int n_expert, int n) {
     int nb = n / 32, gsh = lanes_shift(nb);
@@ -527,12 +617,14 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     int b0, b1, r0, r1;
     share(n_out, gridDim.x, blockIdx.x, b0, b1);
     share(b1 - b0, nw, wid, r0, r1);
+    TL(TLK_MOE_DOWN, 0);
     pdl_trigger();
     if (p.prefetch && !p.local_only && lane == 0 && r0 < r1) {
         l2_prefetch(p.shared_down.q + (size_t)(b0 + r0) * sff, (size_t)(r1 - r0) * sff);
         l2_prefetch(p.shared_down.s + (size_t)(b0 + r0) * nbs, (size_t)(r1 - r0) * nbs * 2);
     }
     pdl_wait();
+    TL(TLK_MOE_DOWN, 1);
     for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];
     for (int i = tid; i < p.n_used * nbf; i += blockDim.x) hs[i] = p.hs[(size_t)b * p.n_used * nbf + i];
     for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + (size_t)b * sff))[i];
@@ -545,6 +637,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     }
     if (tid == 32) s_g = sigmoid_f(p.logit[b]);
     __syncthreads();
+    TL(TLK_MOE_DOWN, 2);
     const bool has_s = p.down.scale2 != nullptr;
     float* x = p.x + (size_t)b * p.x_stride;
 #pragma unroll 1
@@ -581,6 +674,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
         }
         __syncwarp();
     }
+    TL(TLK_MOE_DOWN, 3);
 }
 size_t moe_down_smem(int n_used, int ff, int sff, int rp) {
     int gf = lanes_shift(ff / 32), gs = lanes_shift(sff / 32);
@@ -593,6 +687,18 @@ __global__ void k_embed(const float* table, int n_embd, const int32_t* tokens, f
     int b = blockIdx.x;
     pdl_trigger(); pdl_wait();
     const float* row = table + (size_t)tokens[b] * n_embd;
+    if ((n_embd & 3) == 0) {
+        const int nv = n_embd >> 2;
+        float4* dst = (float4*)(x + (size_t)b * n_embd);
+        for (int i0 = threadIdx.x; i0 < nv; i0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) if (i0 + j * (int)blockDim.x < nv) v[j] = __ldg((const float4*)row + i0 + j * blockDim.x);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) if (i0 + j * (int)blockDim.x < nv) dst[i0 + j * blockDim.x] = v[j];
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < n_embd; i += blockDim.x) x[(size_t)b * n_embd + i] = row[i];
 }
 
@@ -612,7 +718,16 @@ __global__ void __launch_bounds__(256) k_argmax_partial(const float* logits, int
     pdl_trigger(); pdl_wait();
     const float* l = logits + (size_t)b * n_vocab;
     float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int i = lo + tid; i < hi; i += blockDim.x) { float v = l[i]; if (bi == 0x7fffffff || v > bv) { bv = v; bi = i; } }
+    for (int i0 = lo + tid; i0 < hi; i0 += 8 * blockDim.x) {
+        float v[8];   // eight strided loads in flight per trip; the scan below keeps ascending index order per thread
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = i0 + j * (int)blockDim.x < hi ? l[i0 + j * blockDim.x] : -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = i0 + j * blockDim.x;
+            if (i < hi && (bi == 0x7fffffff || v[j] > bv)) { bv = v[j]; bi = i; }
+        }
+    }
     for (int o = 16; o > 0; o >>= 1) argmax_merge(bv, bi, __shfl_xor_sync(0xffffffffu, bv, o), __shfl_xor_sync(0xffffffffu, bi, o));
     if (lane == 0) { sv[wid] = bv; si[wid] = bi; }
     __syncthreads();

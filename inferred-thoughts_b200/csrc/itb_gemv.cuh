@@ -25,10 +25,39 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // (src/ops/naive.rs:139-152, :633-640). `red` holds blockDim.x/32 doubles.
 __device__ __forceinline__ void block_rms_norm(const float* __restrict__ x, const float* __restrict__ w, int n, float eps,
                                                float* xn, double* red) {
+    const int wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if ((n & 3) == 0 && n <= 16 * (int)blockDim.x && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)xn)) & 15) == 0) {
+        // the row and the norm weights as float4, every load in flight before the first use: one memory round trip
+        float4 xv[4], wv[4];
+        const int nv = n >> 2;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < nv) { xv[j] = ((const float4*)x)[i]; wv[j] = __ldg((const float4*)w + i); }
+        }
+        double acc = 0.0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if ((int)(threadIdx.x + j * blockDim.x) < nv)
+                acc += (double)(xv[j].x * xv[j].x) + (double)(xv[j].y * xv[j].y) + (double)(xv[j].z * xv[j].z) + (double)(xv[j].w * xv[j].w);
+        acc = warp_sum_d(acc);
+        if ((threadIdx.x & 31) == 0) red[wid] = acc;
+        __syncthreads();
+        double tot = 0.0;
+        for (int i = 0; i < nw; ++i) tot += red[i];
+        const float mean = (float)(tot / (double)n);
+        const float sc = 1.0f / sqrtf(mean + eps);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int i = threadIdx.x + j * blockDim.x;
+            if (i < nv) ((float4*)xn)[i] = make_float4(xv[j].x * sc * wv[j].x, xv[j].y * sc * wv[j].y, xv[j].z * sc * wv[j].z, xv[j].w * sc * wv[j].w);
+        }
+        __syncthreads();
+        return;
+    }
     double acc = 0.0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = x[i]; xn[i] = v; acc += (double)(v * v); }
     acc = warp_sum_d(acc);
-    int wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     if ((threadIdx.x & 31) == 0) red[wid] = acc;
     __syncthreads();
     double tot = 0.0;
@@ -114,19 +143,21 @@ __device__ __forceinline__ void unit_terms(const UnitW& w, const uint4& xa, cons
         s = __dp4a((int)w.a.z, (int)xa.z, s); s = __dp4a((int)w.a.w, (int)xa.w, s);
         s = __dp4a((int)w.b.x, (int)xb.x, s); s = __dp4a((int)w.b.y, (int)xb.y, s);
         s = __dp4a((int)w.b.z, (int)xb.z, s); s = __dp4a((int)w.b.w, (int)xb.w, s);
-        t[u] = (float)s * (f16_bits_to_f32((uint16_t)w.s) * dx);               // src/ops/naive.rs:701
+        t[u] = i2f_small(s) * (f16_bits_to_f32((uint16_t)w.s) * dx);           // src/ops/naive.rs:701
     } else {
         int s0 = fp4_dot8(w.a.x, xa.x, xa.y) + fp4_dot8(w.a.y, xa.z, xa.w);
         int s1 = fp4_dot8(w.a.z, xb.x, xb.y) + fp4_dot8(w.a.w, xb.z, xb.w);
-        t[2 * u] = dx * ue4m3_half_dev(w.s & 0xff) * (float)s0;                // src/ops/naive.rs:730
-        t[2 * u + 1] = dx * ue4m3_half_dev(w.s >> 8) * (float)s1;
+        float d0, d1;
+        ue4m3x2_half(w.s, d0, d1);
+        t[2 * u] = dx * d0 * i2f_small(s0);                                    // src/ops/naive.rs:730
+        t[2 * u + 1] = dx * d1 * i2f_small(s1);
     }
 }
 // Ascending fold of one row's terms.
 __device__ __forceinline__ float fold_terms(const float* t, int nt) {
     float sum = 0.0f;
-#pragma unroll 4
-    for (int b = 0; b < nt; ++b) sum += t[b];
+#pragma unroll 16
+    for (int b = 0; b < nt; ++b) sum += t[b];   // a deep unroll keeps the loads ahead of the dependent adds
     return sum;
 }
 
@@ -175,7 +206,7 @@ __device__ __forceinline__ void rows_direct_ub(const uint8_t* __restrict__ pa, c
 // A list of independent row-dots, each with its own weight row and its own activation: item k of [0, n) is
 // described by src(k, pa, pb, xq, xs) (weight planes of THE ROW, activation in shared memory). One pass
 // takes RP*(32/G) items with every load issued before the first dot; epi(k, value) by one lane per item.
-template <int KIND, int RP, class Src, class Epi>
+template <int KIND, int RP, int UB = 1, class Src, class Epi>
 __device__ __forceinline__ void rows_list(int n, int n_in, float* terms, int gsh, Src src, Epi epi) {
     const int G = 1 << gsh, lane = threadIdx.x & 31, sub = lane & (G - 1), slot = lane >> gsh;
     const int SLOTS = 32 >> gsh, ROWS = RP * SLOTS;
@@ -191,17 +222,22 @@ __device__ __forceinline__ void rows_list(int n, int n_in, float* terms, int gsh
             if (k < n) src(k, pa[i], pb[i], xq[i], xs[i]);
         }
 #pragma unroll 1
-        for (int u = sub; u < nunits; u += G) {
-            UnitW w[RP];
+        for (int u0 = sub; u0 < nunits; u0 += UB * G) {
+            UnitW w[UB][RP];
 #pragma unroll
-            for (int i = 0; i < RP; ++i)
-                if (k0 + i * SLOTS + slot < n) unit_load<KIND>(w[i], pa[i], pb[i], u);
+            for (int h = 0; h < UB; ++h)
 #pragma unroll
-            for (int i = 0; i < RP; ++i)
-                if (k0 + i * SLOTS + slot < n) {
-                    const uint4 xa = *(const uint4*)(xq[i] + u * 32), xb = *(const uint4*)(xq[i] + u * 32 + 16);
-                    unit_terms<KIND>(w[i], xa, xb, xs[i][u], terms + (i * SLOTS + slot) * stride, u);
-                }
+                for (int i = 0; i < RP; ++i)
+                    if (k0 + i * SLOTS + slot < n && u0 + h * G < nunits) unit_load<KIND>(w[h][i], pa[i], pb[i], u0 + h * G);
+#pragma unroll
+            for (int h = 0; h < UB; ++h)
+#pragma unroll
+                for (int i = 0; i < RP; ++i)
+                    if (k0 + i * SLOTS + slot < n && u0 + h * G < nunits) {
+                        const int u = u0 + h * G;
+                        const uint4 xa = *(const uint4*)(xq[i] + u * 32), xb = *(const uint4*)(xq[i] + u * 32 + 16);
+                        unit_terms<KIND>(w[h][i], xa, xb, xs[i][u], terms + (i * SLOTS + slot) * stride, u);
+                    }
         }
         __syncwarp();
         if (lane < ROWS && k0 + lane < n) epi(k0 + lane, fold_terms(terms + lane * stride, nt));

@@ -122,6 +122,36 @@ __device__ __forceinline__ double warp_sum_d(double v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+// Two UE4M3 scale codes (bit 7 clear, 0x7f already mapped to 0: plain positive e4m3) to their halved f32 values by
+// the hardware e4m3 -> f16 conversion, which is exact for every code.
+__device__ __forceinline__ void ue4m3x2_half(uint32_t two, float& lo, float& hi) {
+    uint32_t h2;
+    asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(h2) : "r"(two));
+    const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
+    lo = __low2float(hh) * 0.5f; hi = __high2float(hh) * 0.5f;
+}
+
+// Exact int32 -> f32 for |v| < 2^22 without the conversion pipe: add v to the bit pattern of 1.5 * 2^23, whose ulp is
+// 1, and subtract 1.5 * 2^23 again (block sums here stay below 32 * 127 * 127 < 2^19).
+__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
+
+// Phase timeline (observability): when a buffer is armed (itb_timeline_arm), thread 0 of block 0 of every launch
+// appends (tag, %globaltimer ns) at each TL(tag) site; tags are kernel * 16 + phase. One predicate per site otherwise.
+static __device__ unsigned long long* g_tl_buf = nullptr;
+static __device__ unsigned int g_tl_cap = 0, g_tl_n = 0;
+__device__ __forceinline__ void tl_mark(unsigned tag) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_tl_buf) {
+        const unsigned i = atomicAdd(&g_tl_n, 1u);
+        if (i < g_tl_cap) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+            g_tl_buf[2 * i] = tag; g_tl_buf[2 * i + 1] = t;
+        }
+    }
+}
+#define TL(kernel, phase) tl_mark((kernel) * 16 + (phase))
+enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TLK_ATTN_PART, TLK_ATTN_COMB, TLK_MOE_GLU, TLK_MOE_DOWN, TLK_ARGMAX_P, TLK_ARGMAX_A };
+
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while
 // its predecessor still runs. pdl_trigger() lets the successor be scheduled; pdl_wait() returns once every
 // predecessor grid has completed and its writes are visible. Before pdl_wait() a kernel may touch only memory no

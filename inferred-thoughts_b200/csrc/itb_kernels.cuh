@@ -388,7 +388,9 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
                                float* part_acc, float* part_ml, int rows_per_seq = 0, size_t slab_stride = 0) {
     constexpr int DPL = HD / 32;  // dims per lane
     int hk = blockIdx.x, t = blockIdx.y, sp = blockIdx.z, n_split = gridDim.z;
+    TL(TLK_ATTN_PART, 0);
     pdl_trigger(); pdl_wait();
+    TL(TLK_ATTN_PART, 1);
     if (rows_per_seq > 0) {       // rows of several sequences in one launch: row t reads the slabs of sequence t / rows_per_seq
         const size_t so = (size_t)(t / rows_per_seq) * slab_stride;
         kslab += so; vslab += so;
@@ -417,35 +419,47 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
     for (int g = 0; g < MAXG; ++g) { m[g] = -INFINITY; l[g] = 0.0f;
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[g][d] = 0.0f; }
-    for (int p = p0 + wid; p < p1; p += nw) {
-        const uint16_t* kr = kslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
-        const uint16_t* vr = vslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
-        float kf[DPL], vf[DPL];
-        uint16_t kb[DPL], vb[DPL];
-        if (DPL == 8) { *(uint4*)kb = *(const uint4*)kr; *(uint4*)vb = *(const uint4*)vr; }
-        else if (DPL == 4) { *(uint2*)kb = *(const uint2*)kr; *(uint2*)vb = *(const uint2*)vr; }
-        else { *(uint32_t*)kb = *(const uint32_t*)kr; *(uint32_t*)vb = *(const uint32_t*)vr; }
+    constexpr int PU = 4;   // positions per trip: their K and V rows are all requested before the first is used
+    for (int pb = p0 + wid; pb < p1; pb += PU * nw) {
+        uint16_t kb[PU][DPL], vb[PU][DPL];
 #pragma unroll
-        for (int d = 0; d < DPL; ++d) {
-            kf[d] = bf16 ? bf16_bits_to_f32(kb[d]) : f16_bits_to_f32(kb[d]);
-            vf[d] = bf16 ? bf16_bits_to_f32(vb[d]) : f16_bits_to_f32(vb[d]);
+        for (int u = 0; u < PU; ++u) {
+            const int p = pb + u * nw;
+            if (p < p1) {
+                const uint16_t* kr = kslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
+                const uint16_t* vr = vslab + (size_t)p * kv_dim + hk * HD + lane * DPL;
+                if (DPL == 8) { *(uint4*)kb[u] = *(const uint4*)kr; *(uint4*)vb[u] = *(const uint4*)vr; }
+                else if (DPL == 4) { *(uint2*)kb[u] = *(const uint2*)kr; *(uint2*)vb[u] = *(const uint2*)vr; }
+                else { *(uint32_t*)kb[u] = *(const uint32_t*)kr; *(uint32_t*)vb[u] = *(const uint32_t*)vr; }
+            }
         }
 #pragma unroll
-        for (int g = 0; g < MAXG; ++g) {
-            if (g < group) {
-                float s = 0.0f;
+        for (int u = 0; u < PU; ++u) {
+            if (pb + u * nw >= p1) break;
+            float kf[DPL], vf[DPL];
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) s += qr[g][d] * kf[d];
-                s = warp_sum(s) * scale;
-                float mn = fmaxf(m[g], s);
-                float corr = __expf(m[g] - mn), pw = __expf(s - mn);
-                l[g] = l[g] * corr + pw;
+            for (int d = 0; d < DPL; ++d) {
+                kf[d] = bf16 ? bf16_bits_to_f32(kb[u][d]) : f16_bits_to_f32(kb[u][d]);
+                vf[d] = bf16 ? bf16_bits_to_f32(vb[u][d]) : f16_bits_to_f32(vb[u][d]);
+            }
 #pragma unroll
-                for (int d = 0; d < DPL; ++d) acc[g][d] = acc[g][d] * corr + pw * vf[d];
-                m[g] = mn;
+            for (int g = 0; g < MAXG; ++g) {
+                if (g < group) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) s += qr[g][d] * kf[d];
+                    s = warp_sum(s) * scale;
+                    float mn = fmaxf(m[g], s);
+                    float corr = __expf(m[g] - mn), pw = __expf(s - mn);
+                    l[g] = l[g] * corr + pw;
+#pragma unroll
+                    for (int d = 0; d < DPL; ++d) acc[g][d] = acc[g][d] * corr + pw * vf[d];
+                    m[g] = mn;
+                }
             }
         }
     }
+    TL(TLK_ATTN_PART, 2);
     // merge the block's warps through shared memory
     extern __shared__ __align__(16) unsigned char smem[];
     float* s_ml = (float*)smem;              // [nw][MAXG][2]

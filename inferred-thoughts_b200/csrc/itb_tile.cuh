@@ -27,19 +27,6 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
 
 // KIND: MK_Q8 (int8 rows, f16 scale per 32) or MK_FP4 (E2M1 nibbles in element order, UE4M3 scale per 16).
-// Two UE4M3 scale codes (bit 7 clear, 0x7f already mapped to 0: plain positive e4m3) to their halved f32 values by
-// the hardware e4m3 -> f16 conversion, which is exact for every code.
-__device__ __forceinline__ void ue4m3x2_half(uint32_t two, float& lo, float& hi) {
-    uint32_t h2;
-    asm("{ .reg .b16 t; cvt.u16.u32 t, %1; cvt.rn.f16x2.e4m3x2 %0, t; }" : "=r"(h2) : "r"(two));
-    const __half2 hh = *reinterpret_cast<const __half2*>(&h2);
-    lo = __low2float(hh) * 0.5f; hi = __high2float(hh) * 0.5f;
-}
-
-// Exact int32 -> f32 for |v| < 2^22 without the conversion pipe: add v to the bit pattern of 1.5 * 2^23, whose ulp is
-// 1, and subtract 1.5 * 2^23 again (block sums here stay below 32 * 127 * 127 < 2^19).
-__device__ __forceinline__ float i2f_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
-
 template <int KIND, int NJ, int KC, int TH = 2>
 struct TileCfg {
     static constexpr int ROWS = 128 / TH;
