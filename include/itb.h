@@ -139,11 +139,12 @@ uint64_t itb_model_decode_bytes(itb_model*, uint32_t n_seq, uint32_t n_pos, uint
 
 /* n_seq independent sequences (the reference engine holds one, src/engine/mod.rs:44-59). */
 int  itb_engine_create(itb_model*, uint32_t n_ctx, uint32_t n_seq, itb_engine** out);
-/* Phase timeline (observability; the reference's counterpart is its per-op profiler, src/profile.rs): arm a buffer
- * of `capacity` records (0 disarms), run engine calls, read back (tag, nanoseconds) pairs in arrival order.
- * Thread 0 of block 0 of each launch records at its phase marks; tag = kernel * 16 + phase. */
-int  itb_timeline_arm(itb_engine*, uint32_t capacity);
-long itb_timeline_read(itb_engine*, uint64_t* out_pairs, uint32_t capacity);
+/* Phase timeline (observability; the reference's counterpart is its per-op profiler, src/profile.rs): arm `slots`
+ * launch slots (0 disarms), run single-sequence decode steps, read back slots * 16 words. Thread 0 of block 0 of the
+ * step's n-th structured launch stores (nanoseconds << 8) | kernel id at word n * 16 + phase for each of its phase
+ * marks; words never written stay 0. Costs one predicate per mark when disarmed. */
+int  itb_timeline_arm(itb_engine*, uint32_t slots);
+long itb_timeline_read(itb_engine*, uint64_t* out_words, uint32_t slots);
 /* Expert parallelism over `world` processes, one GPU each (the reference's placement seam: src/ops/mod.rs:1024-1048;
  * its grouped kernels: kernels/moe.cuh:62-133). The model must hold exactly experts [rank*E/world, (rank+1)*E/world)
  * (itb_model_synth with that range, or set_tensor of that slice); everything else is replicated and each rank runs its

@@ -422,6 +422,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv;
     const int TPB = NWG * 32;
     uint64_t launches = 0;
+    int tl = 0;   // phase-timeline slots: launch ordinals of the structured kernels of this step
     // overlap each kernel's launch and weight prefetch with its predecessor's tail (off while profiling per kernel)
     static const bool pdl_env = !(getenv("ITB_PDL") && atoi(getenv("ITB_PDL")) == 0);
     const bool pdl = pdl_env && !prof;
@@ -438,7 +439,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         // the warps' term matrices must fit the block's shared memory (wide rows: fewer rows folded together)
         const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
         p.br = std::max(pass_in, std::min(p.br, cap / pass_in * pass_in));
-        p.prefetch = pdl;
+        p.tl_slot = tl++;
         launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
     };
     auto launch_out = [&](OutProj& o, int n_in) {
@@ -447,7 +448,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         o.br = std::min(std::max(32 / pass, 1) * pass, (per_warp + pass - 1) / pass * pass);
         const int cap = (int)((SMEM_BUDGET - (size_t)n_in - (size_t)(n_in / 32) * 4 - 64) / (NWG * 4) / (n_in / 32 + 1));
         o.br = std::max(pass, std::min(o.br, cap / pass * pass));
-        o.prefetch = pdl;
+        o.tl_slot = tl++;
         launch_k(pdl, k_out_proj, dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st, o);
     };
     static bool attrs_set = false;
@@ -482,6 +483,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             g.ssm_a = L.ssm_a; g.dt_bias = L.dt_bias; g.ssm_norm = L.ssm_norm;
             g.state_stride = state_stride; g.state = e->ssm_state + (size_t)rs * B * state_stride;
             g.out_q = e->aq; g.out_s = e->as; g.sk = d.ssm_d_state; g.sv = d.ssm_d_state; g.n_k = d.ssm_n_group; g.n_v = d.ssm_dt_rank; g.eps = d.rms_eps;
+            g.tl_slot = tl++;
             size_t smem_g = (size_t)(g.sv * (g.sk + 1) + 2 * g.sk + g.sv) * 4;
             if (d.ssm_d_state == 128) launch_k(pdl, k_gdn_core<128>, dim3(d.ssm_dt_rank, B), 256, smem_g, st, g);
             else launch_k(pdl, k_gdn_core<64>, dim3(d.ssm_dt_rank, B), 256, smem_g, st, g);
@@ -504,6 +506,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             a.kslab = e->kslab + (size_t)as * B * a.slab_stride; a.vslab = e->vslab + (size_t)as * B * a.slab_stride;
             a.pos = e->pos; a.npos_out = e->npos; a.hd = d.head_dim; a.n_head = d.n_head; a.n_head_kv = d.n_head_kv; a.n_rot = d.n_rot;
             a.theta = d.rope_theta; a.eps = d.rms_eps; a.bf16 = c->kv_bf16;
+            a.tl_slot = tl++;
             launch_k(pdl, k_attn_prep, dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st, a);
             MARK(KC_ATTN_PREP, (uint64_t)B * (4ull * qd + 3ull * kvd) * 4);
             // split-K partials, one launch per sequence (own slab, own position), then one combine for all
@@ -547,16 +550,17 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
+        g.tl_slot = tl++;
         launch_k(pdl, k_moe_glu, dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st, g);
         MARK(KC_MOE_GLU, (uint64_t)B * (2ull * d.n_expert_used * f4b(H, d.expert_ff) + (uint64_t)d.n_expert_used * d.expert_ff * 4));
         MoeDown w{};
         w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
         w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
-        w.prefetch = pdl;
         {
             int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
             int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
             dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), B);
+            w.tl_slot = tl++;
             size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
             if (rp == 1) launch_k(pdl, k_moe_down<1>, grid, TPB, smem_d, st, w);
             else if (rp == 2) launch_k(pdl, k_moe_down<2>, grid, TPB, smem_d, st, w);
@@ -764,7 +768,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     } else {
         InProj hp{};
         hp.x = xl; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
-        hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact;
+        hp.nq = 1; hp.q[0] = m->output; hp.qout[0] = e->logits; hp.qstride[0] = d.n_vocab; hp.exact = c->exact; hp.tl_slot = -1;
         {
             const int pass_in = 2 * (32 >> lanes_shift(H / 32));
             int gx = std::max(1, std::min(sms, ((int)d.n_vocab + 2 * NWG - 1) / (2 * NWG)));
@@ -1104,24 +1108,24 @@ extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, it
     return 0;
 }
 
-// Phase timeline of the engine's kernels (see tl_mark): arm with a capacity, run steps, read the (tag, ns) pairs.
-extern "C" int itb_timeline_arm(itb_engine* e, uint32_t capacity) {
+// Phase timeline of the decode step's kernels (see tl_mark): arm `slots` launch slots of 16 phase stamps each (0 disarms),
+// run steps, read back slots * 16 words: (nanoseconds << 8) | kernel id, 0 where nothing was recorded.
+extern "C" int itb_timeline_arm(itb_engine* e, uint32_t slots) {
     static unsigned long long* buf = nullptr;
     static uint32_t cap = 0;
     cudaStreamSynchronize(e->c->stream);
-    if (capacity > cap) { cudaFree(buf); buf = nullptr; if (cudaMalloc(&buf, (size_t)capacity * 16) != cudaSuccess) return 1; cap = capacity; }
-    unsigned long long* b = capacity ? buf : nullptr;
-    const unsigned zero = 0, c = capacity;
-    if (cudaMemcpyToSymbol(g_tl_n, &zero, 4) != cudaSuccess || cudaMemcpyToSymbol(g_tl_cap, &c, 4) != cudaSuccess ||
-        cudaMemcpyToSymbol(g_tl_buf, &b, 8) != cudaSuccess) return 1;
+    if (slots > cap) { cudaFree(buf); buf = nullptr; if (cudaMalloc(&buf, (size_t)slots * 128) != cudaSuccess) return 1; cap = slots; }
+    if (slots) cudaMemset(buf, 0, (size_t)slots * 128);
+    unsigned long long* b = slots ? buf : nullptr;
+    const unsigned c = slots;
+    if (cudaMemcpyToSymbol(g_tl_cap, &c, 4) != cudaSuccess || cudaMemcpyToSymbol(g_tl_buf, &b, 8) != cudaSuccess) return 1;
     return 0;
 }
-extern "C" long itb_timeline_read(itb_engine* e, uint64_t* out_pairs, uint32_t capacity) {
+extern "C" long itb_timeline_read(itb_engine* e, uint64_t* out_words, uint32_t slots) {
     cudaStreamSynchronize(e->c->stream);
-    unsigned n = 0; unsigned long long* b = nullptr;
-    if (cudaMemcpyFromSymbol(&n, g_tl_n, 4) != cudaSuccess || cudaMemcpyFromSymbol(&b, g_tl_buf, 8) != cudaSuccess || !b) return -1;
-    unsigned cap = 0; cudaMemcpyFromSymbol(&cap, g_tl_cap, 4);
-    n = std::min(std::min(n, cap), capacity);
-    if (n && cudaMemcpy(out_pairs, b, (size_t)n * 16, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    unsigned cap = 0; unsigned long long* b = nullptr;
+    if (cudaMemcpyFromSymbol(&cap, g_tl_cap, 4) != cudaSuccess || cudaMemcpyFromSymbol(&b, g_tl_buf, 8) != cudaSuccess || !b) return -1;
+    const unsigned n = std::min(cap, slots);
+    if (n && cudaMemcpy(out_words, b, (size_t)n * 128, cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     return (long)n;
 }

@@ -23,7 +23,7 @@ struct InProj {
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
-    int prefetch;                                  // ask L2 for the warp's weight rows before waiting for the predecessor
+    int tl_slot;                                   // phase-timeline slot of this launch (-1: none)
 };
 
 __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
@@ -58,18 +58,6 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = lane; i < nr * keep; i += 32) cpre[(i / keep) * 8 + i % keep] = cs[i];
         for (int i = lane; i < nr * p.conv_kernel; i += 32) cpre[(i / p.conv_kernel) * 8 + keep + i % p.conv_kernel] = cw[i];
         conv_lo = r0;
-    }
-    if (p.prefetch && lane == 0) {
-        // this warp's weight rows into L2 while the predecessor kernel finishes
-        int base = 0;
-        for (int m = 0; m < p.nq; ++m) {
-            const int lo = max(r0, base) - base, hi = min(r1, base + p.q[m].n_out) - base;
-            if (lo < hi) {
-                l2_prefetch(p.q[m].q + (size_t)lo * n, (size_t)(hi - lo) * n);
-                l2_prefetch(p.q[m].s + (size_t)lo * nb, (size_t)(hi - lo) * nb * 2);
-            }
-            base += p.q[m].n_out;
-        }
     }
     pdl_wait();
     TL(TLK_IN_PROJ, 1);
@@ -151,7 +139,7 @@ size_t in_proj_smem(int n, int exact, int br) {
 // ------------------------------------------------------------------------------------------------------
 // Output projection with the residual add fused: x[b] += W . a[b], the activation arriving already quantised
 // (src/model/qwen35.rs:1017, :1220, :1325).
-struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; int prefetch; };
+struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; int tl_slot; };
 __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
@@ -164,10 +152,6 @@ __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     share(b1 - b0, nw, wid, r0, r1);
     TL(TLK_OUT_PROJ, 0);
     pdl_trigger();
-    if (p.prefetch && (threadIdx.x & 31) == 0 && r0 < r1) {
-        l2_prefetch(p.w.q + (size_t)(b0 + r0) * n, (size_t)(r1 - r0) * n);
-        l2_prefetch(p.w.s + (size_t)(b0 + r0) * nb, (size_t)(r1 - r0) * nb * 2);
-    }
     pdl_wait();
     TL(TLK_OUT_PROJ, 1);
     for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)aq)[i] = ((const uint4*)(p.aq + (size_t)b * n))[i];
@@ -196,6 +180,7 @@ struct GdnCore {
     float* state; size_t state_stride;
     int8_t* out_q; float* out_s;                  // [B][value_dim] int8, [B][value_dim/32] scales
     int sk, sv, n_k, n_v; float eps;
+    int tl_slot;
 };
 template <int SK>
 __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
@@ -324,6 +309,7 @@ struct AttnPrep {
     uint16_t* kslab; uint16_t* vslab; size_t slab_stride;
     const int* pos; int* npos_out;
     int hd, n_head, n_head_kv, n_rot; float theta, eps; int bf16;
+    int tl_slot;
 };
 __global__ void k_attn_prep(AttnPrep p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -381,9 +367,7 @@ __global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, in
                                  const int* n_pos_dev, int n_head, int8_t* out_q, float* out_s) {
     const size_t th = blockIdx.x;
     const int d = threadIdx.x, b = (int)(th / n_head);
-    TL(TLK_ATTN_COMB, 0);
     pdl_trigger(); pdl_wait();
-    TL(TLK_ATTN_COMB, 1);
     const int n_pos = n_pos_dev[b], per = max(ATTN_MIN_SPLIT, (n_pos + n_split - 1) / n_split), n_act = (n_pos + per - 1) / per;
     // splits in trips of 8 with every load of a trip in flight; the combine itself keeps ascending split order
     const float gt = gate[th * hd + d];
@@ -420,7 +404,6 @@ __global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, in
     int8_t q = warp_quant_q8(v, &dq);
     out_q[th * hd + d] = q;
     if ((d & 31) == 0) out_s[(th * hd + d) / 32] = dq;
-    TL(TLK_ATTN_COMB, 2);
 }
 
 // ------------------------------------------------------------------------------------------------------
@@ -429,6 +412,7 @@ __global__ void k_attn_combine_q(const float* part_acc, const float* part_ml, in
 // Warp 0 redoes the routing (softmax over all experts, top-k; src/model/qwen35.rs:1626-1638,
 // src/ops/mod.rs:1191-1216) while the others fetch the activation; then
 // h = silu(gate_e . x * s_g) * (up_e . x * s_u) (src/ops/mod.rs:1105-1117) -> Q8_0.
+constexpr int MOE_CAND = 512;   // 32 groups x 16 picks at most (n_expert <= 1024, n_used <= 16)
 struct MoeGlu {
     const float* router; int n_expert, n_used;
     const int8_t* xq; const float* xs; int n_embd;
@@ -437,6 +421,7 @@ struct MoeGlu {
     int8_t* hq; float* hs;                          // [B][n_used*ff] int8, [B][n_used*ff/32]
     int8_t* sq; float* ss;                          // [B][sff] int8, [B][sff/32]: silu(sg)*su quantised
     int32_t* ids_out; float* w_out;
+    int tl_slot;
 };
 __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -444,6 +429,8 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     __shared__ float s_wts[16];
     __shared__ float s_gu[64];
     __shared__ float s_sum;
+    __shared__ float s_cand_p[MOE_CAND];        // the first n_used of every 32-group: probability and id
+    __shared__ int s_cand_i[MOE_CAND];
     const int n = p.n_embd, nb = n / 32, nsb = n / 16, gsh = lanes_shift(nb), ff = p.gate.n_out, upp = ff / 32;
     const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int unit = blockIdx.x, n_units = p.n_used * upp;
@@ -506,31 +493,46 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
         }
         s_sum = sum;
     }
-    TL(TLK_MOE_GLU, 6);
     __syncthreads();
     {
         const float sum = s_sum;
         for (int i = tid; i < p.n_expert; i += blockDim.x) probs[i] /= sum;
     }
     __syncthreads();
-    TL(TLK_MOE_GLU, 7);
-    // top-k without serial rounds: an expert's place in the pick order is the number of experts that beat it (greater
-    // probability, or equal and lower id: src/ops/mod.rs:1191-1216 picks by strict '>' scanning ascending ids)
+    // top-k without serial rounds, in two stages of counting. An expert's place in an order is the number of experts
+    // that beat it: greater probability, or equal and lower id (src/ops/mod.rs:1191-1216 picks by strict '>' scanning
+    // ascending ids). Stage 1: every 32-group ranks itself by shuffles and keeps its first n_used; stage 2: those
+    // candidates (the overall picks are among them) are ranked against each other.
     {
-        const int ne32 = (p.n_expert + 31) & ~31;
-        for (int t = tid; t < p.n_expert; t += blockDim.x) {
-            const float pt = probs[t];
+        const int ng = (p.n_expert + 31) >> 5, nu = p.n_used;
+        for (int g = wid; g < ng; g += (int)(blockDim.x >> 5)) {
+            const int t = g * 32 + lane;
+            const float v = t < p.n_expert ? probs[t] : -1.0f;
             int rank = 0;
-            for (int j = 0; j < ne32; j += 4) {
-                const float4 q = *(const float4*)(probs + j);
-                rank += (q.x > pt || (q.x == pt && j < t)) + (q.y > pt || (q.y == pt && j + 1 < t)) +
-                        (q.z > pt || (q.z == pt && j + 2 < t)) + (q.w > pt || (q.w == pt && j + 3 < t));
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float q = __shfl_sync(0xffffffffu, v, j);
+                rank += (int)(q > v) | ((int)(q == v) & (int)(j < lane));   // bitwise: no branches
             }
-            if (rank < p.n_used) { s_ids[rank] = t; s_wts[rank] = pt; }
+            if (rank < nu) { s_cand_p[g * nu + rank] = v; s_cand_i[g * nu + rank] = t < p.n_expert ? t : -1; }
+        }
+        __syncthreads();
+        const int cnt = ng * nu;
+        for (int c = tid; c < cnt; c += blockDim.x) {
+            const float v = s_cand_p[c];
+            const int id = s_cand_i[c];
+            if (id < 0) continue;
+            int rank = 0;
+#pragma unroll 8
+            for (int j = 0; j < cnt; ++j) {   // unrolled so the shared-memory reads run ahead of the compares
+                const float q = s_cand_p[j];
+                const int qi = s_cand_i[j];
+                rank += (int)(qi >= 0) & ((int)(q > v) | ((int)(q == v) & (int)(qi < id)));
+            }
+            if (rank < nu) { s_ids[rank] = id; s_wts[rank] = v; }
         }
     }
     __syncthreads();
-    TL(TLK_MOE_GLU, 8);
     if (tid == 0) {
         float sum = 0.0f;
         for (int r = 0; r < p.n_used; ++r) sum += s_wts[r];                 // summed in pick order (src/ops/mod.rs:1211)
@@ -595,7 +597,7 @@ struct MoeDown {
     const float* logit;
     float* x; int x_stride;
     int local_only; float* partial;
-    int prefetch;
+    int tl_slot;
 };
 template <int RP>
 __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
@@ -619,10 +621,6 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     share(b1 - b0, nw, wid, r0, r1);
     TL(TLK_MOE_DOWN, 0);
     pdl_trigger();
-    if (p.prefetch && !p.local_only && lane == 0 && r0 < r1) {
-        l2_prefetch(p.shared_down.q + (size_t)(b0 + r0) * sff, (size_t)(r1 - r0) * sff);
-        l2_prefetch(p.shared_down.s + (size_t)(b0 + r0) * nbs, (size_t)(r1 - r0) * nbs * 2);
-    }
     pdl_wait();
     TL(TLK_MOE_DOWN, 1);
     for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];

@@ -135,21 +135,19 @@ __device__ __forceinline__ void ue4m3x2_half(uint32_t two, float& lo, float& hi)
 // 1, and subtract 1.5 * 2^23 again (block sums here stay below 32 * 127 * 127 < 2^19).
 __device__ __forceinline__ float i2f_small(int v) { return __int_as_float(0x4B400000 + v) - 12582912.0f; }
 
-// Phase timeline (observability): when a buffer is armed (itb_timeline_arm), thread 0 of block 0 of every launch
-// appends (tag, %globaltimer ns) at each TL(tag) site; tags are kernel * 16 + phase. One predicate per site otherwise.
+// Phase timeline (observability): when a buffer is armed (itb_timeline_arm), thread 0 of block 0 of a launch that was
+// given a slot stores %globaltimer at each TL(kernel, phase) site into buf[slot * 16 + phase] -- a plain store, nothing to
+// wait for. Slots are the launch ordinals of one decode step; slot < 0 = not recorded.
 static __device__ unsigned long long* g_tl_buf = nullptr;
-static __device__ unsigned int g_tl_cap = 0, g_tl_n = 0;
-__device__ __forceinline__ void tl_mark(unsigned tag) {
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_tl_buf) {
-        const unsigned i = atomicAdd(&g_tl_n, 1u);
-        if (i < g_tl_cap) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            g_tl_buf[2 * i] = tag; g_tl_buf[2 * i + 1] = t;
-        }
+static __device__ unsigned int g_tl_cap = 0;
+__device__ __forceinline__ void tl_mark(int slot, unsigned kernel, unsigned phase) {
+    if (slot >= 0 && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && g_tl_buf && (unsigned)slot < g_tl_cap) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
     }
 }
-#define TL(kernel, phase) tl_mark((kernel) * 16 + (phase))
+#define TL(kernel, phase) tl_mark(p.tl_slot, (kernel), (phase))
 enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TLK_ATTN_PART, TLK_ATTN_COMB, TLK_MOE_GLU, TLK_MOE_DOWN, TLK_ARGMAX_P, TLK_ARGMAX_A };
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may start while
@@ -158,11 +156,6 @@ enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TL
 // kernel of the same chain writes (weights, its own layer's state). Both are no-ops in an ordinary launch.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-// Ask the L2 for [p, p+bytes) (trimmed inwards to 16-byte multiples); no completion to wait for.
-__device__ __forceinline__ void l2_prefetch(const void* p, size_t bytes) {
-    const uintptr_t a = ((uintptr_t)p + 15) & ~(uintptr_t)15, e = ((uintptr_t)p + bytes) & ~(uintptr_t)15;
-    if (e > a) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a), "r"((uint32_t)(e - a)) : "memory");
-}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -388,9 +388,7 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
                                float* part_acc, float* part_ml, int rows_per_seq = 0, size_t slab_stride = 0) {
     constexpr int DPL = HD / 32;  // dims per lane
     int hk = blockIdx.x, t = blockIdx.y, sp = blockIdx.z, n_split = gridDim.z;
-    TL(TLK_ATTN_PART, 0);
     pdl_trigger(); pdl_wait();
-    TL(TLK_ATTN_PART, 1);
     if (rows_per_seq > 0) {       // rows of several sequences in one launch: row t reads the slabs of sequence t / rows_per_seq
         const size_t so = (size_t)(t / rows_per_seq) * slab_stride;
         kslab += so; vslab += so;
@@ -459,7 +457,6 @@ __global__ void k_attn_partial(const float* q, const uint16_t* kslab, const uint
             }
         }
     }
-    TL(TLK_ATTN_PART, 2);
     // merge the block's warps through shared memory
     extern __shared__ __align__(16) unsigned char smem[];
     float* s_ml = (float*)smem;              // [nw][MAXG][2]
