@@ -31,8 +31,8 @@ PROMPT, N_CTX = 512, 8192
 FALLBACK_HBM = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu capture summarised in
 # profiles/decode_step_bs1_kernels_4layer_ncu_full.md (per-launch traffic does not depend on the layer count)
-NCU_TRAFFIC = {"k_moe_glu": 9530624, "k_moe_down": 5878784, "k_in_proj[gdn]": 27561984, "k_in_proj[ffn]": 4402944,
-               "k_out_proj": 8940544, "k_gdn_core": 2169600}
+NCU_TRAFFIC = {"k_moe_glu": 9503000, "k_moe_down": 5881000, "k_in_proj[gdn]": 27570000, "k_in_proj[ffn]": 4413000,
+               "k_out_proj": 8943000, "k_gdn_core": 2192000}
 
 
 def peaks():
