@@ -663,8 +663,8 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             {
                 const dim3 gs(n_v, sk / 32, n_seq);
                 float* sst = e->ssm_state + (size_t)rs * e->B * state_stride;
-                if (sk == 128) k_gdn_scan<128><<<gs, 32, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);
-                else k_gdn_scan<64><<<gs, 32, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);   // 64 or 128 only (checked at model creation)
+                if (sk == 128) k_gdn_scan<128><<<gs, 128, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);
+                else k_gdn_scan<64><<<gs, 128, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);   // 64 or 128 only (checked at model creation)
             }
             launches++;
             k_gdn_post<<<dim3(R, n_v), sk, 0, st>>>(e->core, e->z, L.ssm_norm, sk, n_v, d.rms_eps, e->aq, e->as); launches++;

@@ -134,87 +134,97 @@ __global__ void k_gdn_pre(const float* conv, int cd, const float* alpha, const f
     }
 }
 
-// The recurrence itself (src/ops/naive.rs:109-132): one warp per (value head, 32 value rows, sequence), one lane per
-// value row with that row of the state in REGISTERS across the pass's tokens, keys walked serially in the CPU
-// path's order. The state enters and leaves through a padded shared tile so global accesses stay coalesced;
-// the next token's k, q, v, g, beta are fetched while the current one is computed.
+// The recurrence itself (src/ops/naive.rs:109-132). A block is (value head, 32 value rows, sequence); a warp takes 8 of
+// the rows, FOUR lanes per row, each lane holding a quarter of the row's state in registers across the pass's tokens.
+// The CPU's serial sums over the 128 keys are kept to the bit: lane 0 of a row adds its quarter's products in order
+// and hands the running sum to lane 1, and so on, so the chain is the CPU's chain; what the split buys is four times
+// the warps (the chain's latency is hidden by other rows) and a quarter of the per-lane multiplies. The next token's
+// k, q, v, g, beta are fetched while the current one is computed.
 template <int SK>
-__global__ void __launch_bounds__(32) k_gdn_scan(const float* qh, const float* kh, const float* vh, const float* gb, int n_tok, int n_k, int n_v,
-                                                 float* state, size_t state_stride, float* out) {
-    constexpr int PL = SK / 32;            // k (and q) values per lane
-    __shared__ float tile[32 * (SK + 1)];
-    __shared__ __align__(16) float kq[2 * SK];
-    const int h = blockIdx.x, j0 = blockIdx.y * 32, s = blockIdx.z, khd = h % n_k, lane = threadIdx.x;
-    float* sg = state + (size_t)s * state_stride + ((size_t)h * SK + j0) * SK;
-    {
-        float4 v[8];
-#pragma unroll 1
-        for (int i0 = 0; i0 < 32 * SK / 4; i0 += 8 * 32) {
+__global__ void __launch_bounds__(128) k_gdn_scan(const float* qh, const float* kh, const float* vh, const float* gb, int n_tok, int n_k, int n_v,
+                                                  float* state, size_t state_stride, float* out) {
+    constexpr int CW = SK / 4;             // state columns per lane
+    constexpr int DEPTH = 4;               // tokens whose operands are in flight (cp.async ring, one group per token)
+    constexpr int SLOT = 2 * SK + 8 + 4;   // floats per token and warp: k | q | v of the warp's 8 rows | g, beta, pad
+    __shared__ __align__(16) float ring_all[4][DEPTH][SLOT];
+    const int h = blockIdx.x, s = blockIdx.z, khd = h % n_k, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int r = lane >> 2, part = lane & 3, j0 = blockIdx.y * 32 + wid * 8, j = j0 + r;      // j: value row of the head
+    float* sg = state + (size_t)s * state_stride + ((size_t)h * SK + j) * SK + part * CW;
+    float S[CW];
 #pragma unroll
-            for (int u = 0; u < 8; ++u) v[u] = ((const float4*)sg)[i0 + u * 32 + lane];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int e = (i0 + u * 32 + lane) * 4, r = e / SK, c = e % SK;
-                float* d = tile + r * (SK + 1) + c;
-                d[0] = v[u].x; d[1] = v[u].y; d[2] = v[u].z; d[3] = v[u].w;
+    for (int i = 0; i < CW; i += 4) { const float4 v = *(const float4*)(sg + i); S[i] = v.x; S[i + 1] = v.y; S[i + 2] = v.z; S[i + 3] = v.w; }
+    auto fetch = [&](int t) {
+        if (t < n_tok) {
+            const size_t row = (size_t)s * n_tok + t;
+            float* slot = ring_all[wid][t % DEPTH];
+            if (lane * 4 < SK) {
+                cp_async16(slot + lane * 4, kh + (row * n_k + khd) * SK + lane * 4, true);
+                cp_async16(slot + SK + lane * 4, qh + (row * n_k + khd) * SK + lane * 4, true);
+            }
+            if (lane < 2) cp_async16(slot + 2 * SK + lane * 4, vh + (row * n_v + h) * SK + j0 + lane * 4, true);
+            if (lane == 2) {
+                const uint32_t dst = (uint32_t)__cvta_generic_to_shared(slot + 2 * SK + 8);
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(dst), "l"(gb + (row * n_v + h) * 2));
             }
         }
-    }
-    __syncwarp();
-    float S[SK];
-#pragma unroll
-    for (int i = 0; i < SK; ++i) S[i] = tile[lane * (SK + 1) + i];
-    float kn[PL], qn[PL], vn, gn, bn;
-    auto fetch = [&](int t) {
-        const size_t r = (size_t)s * n_tok + t;
-#pragma unroll
-        for (int u = 0; u < PL; ++u) {
-            kn[u] = kh[(r * n_k + khd) * SK + u * 32 + lane];
-            qn[u] = qh[(r * n_k + khd) * SK + u * 32 + lane];
-        }
-        vn = vh[(r * n_v + h) * SK + j0 + lane];
-        gn = gb[(r * n_v + h) * 2]; bn = gb[(r * n_v + h) * 2 + 1];
+        cp_async_commit();
     };
-    fetch(0);
+    for (int t = 0; t < DEPTH - 1; ++t) fetch(t);
+    float po[CW];
+#pragma unroll
+    for (int i = 0; i < CW; ++i) po[i] = 0.0f;
 #pragma unroll 1
     for (int t = 0; t < n_tok; ++t) {
-        const float v = vn, g = gn, b = bn;
+        cp_async_wait<DEPTH - 2>();
         __syncwarp();
+        fetch(t + DEPTH - 1);            // refills the slot token t-1 used: every lane is past it (the __syncwarp above)
+        const float* slot = ring_all[wid][t % DEPTH];
+        const float v = slot[2 * SK + r], g = slot[2 * SK + 8], b = slot[2 * SK + 9];
+        float kk[CW], pr[CW];
 #pragma unroll
-        for (int u = 0; u < PL; ++u) { kq[u * 32 + lane] = kn[u]; kq[SK + u * 32 + lane] = qn[u]; }
-        __syncwarp();
-        if (t + 1 < n_tok) fetch(t + 1);
-        float pred = 0.0f;
-#pragma unroll
-        for (int i = 0; i < SK; i += 4) {
-            const float4 k4 = *(const float4*)(kq + i);
-            S[i] = S[i] * g; pred += S[i] * k4.x;
-            S[i + 1] = S[i + 1] * g; pred += S[i + 1] * k4.y;
-            S[i + 2] = S[i + 2] * g; pred += S[i + 2] * k4.z;
-            S[i + 3] = S[i + 3] * g; pred += S[i + 3] * k4.w;
+        for (int i = 0; i < CW; i += 4) {
+            const float4 k4 = *(const float4*)(slot + part * CW + i);
+            kk[i] = k4.x; kk[i + 1] = k4.y; kk[i + 2] = k4.z; kk[i + 3] = k4.w;
         }
-        const float d = b * (v - pred);
-        float o = 0.0f;
 #pragma unroll
-        for (int i = 0; i < SK; i += 4) {
-            const float4 k4 = *(const float4*)(kq + i), q4 = *(const float4*)(kq + SK + i);
-            S[i] = S[i] + k4.x * d; o += S[i] * q4.x;
-            S[i + 1] = S[i + 1] + k4.y * d; o += S[i + 1] * q4.y;
-            S[i + 2] = S[i + 2] + k4.z * d; o += S[i + 2] * q4.z;
-            S[i + 3] = S[i + 3] + k4.w * d; o += S[i + 3] * q4.w;
+        for (int i = 0; i < CW; ++i) { S[i] = S[i] * g; pr[i] = S[i] * kk[i]; }
+        // Two serial sums side by side: this token's prediction (needed before the state can move on) and the
+        // PREVIOUS token's read-out, whose products po were formed last trip. They do not depend on each other,
+        // so their adds interleave and the second chain's latency disappears behind the first.
+        float run = 0.0f, runo = 0.0f;
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {
+            float a = run, c = runo;
+#pragma unroll
+            for (int i = 0; i < CW; ++i) { a += pr[i]; c += po[i]; }
+            run = __shfl_sync(0xffffffffu, a, (lane & ~3) | ph);
+            runo = __shfl_sync(0xffffffffu, c, (lane & ~3) | ph);
         }
-        out[(((size_t)s * n_tok + t) * n_v + h) * SK + j0 + lane] = o;
-    }
-    __syncwarp();
+        if (part == 0 && t > 0) out[(((size_t)s * n_tok + t - 1) * n_v + h) * SK + j] = runo;
+        const float d = b * (v - run);
 #pragma unroll
-    for (int i = 0; i < SK; ++i) tile[lane * (SK + 1) + i] = S[i];
-    __syncwarp();
-#pragma unroll 1
-    for (int i0 = 0; i0 < 32 * SK / 4; i0 += 32) {
-        const int e = (i0 + lane) * 4, r = e / SK, c = e % SK;
-        const float* d = tile + r * (SK + 1) + c;
-        ((float4*)sg)[i0 + lane] = make_float4(d[0], d[1], d[2], d[3]);
+        for (int i = 0; i < CW; i += 4) {
+            const float4 q4 = *(const float4*)(slot + SK + part * CW + i);
+            S[i] = S[i] + kk[i] * d; po[i] = S[i] * q4.x;
+            S[i + 1] = S[i + 1] + kk[i + 1] * d; po[i + 1] = S[i + 1] * q4.y;
+            S[i + 2] = S[i + 2] + kk[i + 2] * d; po[i + 2] = S[i + 2] * q4.z;
+            S[i + 3] = S[i + 3] + kk[i + 3] * d; po[i + 3] = S[i + 3] * q4.w;
+        }
     }
+    {
+        float runo = 0.0f;                  // read-out of the last token
+#pragma unroll
+        for (int ph = 0; ph < 4; ++ph) {
+            float c = runo;
+#pragma unroll
+            for (int i = 0; i < CW; ++i) c += po[i];
+            runo = __shfl_sync(0xffffffffu, c, (lane & ~3) | ph);
+        }
+        if (part == 0 && n_tok > 0) out[(((size_t)s * n_tok + n_tok - 1) * n_v + h) * SK + j] = runo;
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int i = 0; i < CW; i += 4) *(float4*)(sg + i) = make_float4(S[i], S[i + 1], S[i + 2], S[i + 3]);
 }
 
 // Gated RMSNorm of the recurrence's output, the SiLU(z) gate and the Q8_0 quantisation of the result
