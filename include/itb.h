@@ -129,6 +129,11 @@ void itb_model_destroy(itb_model*);
  * `scale`: n_expert f32 for NVFP4 expert stacks (the `.scale` tensor), else NULL. */
 int  itb_model_set_tensor(itb_model*, const char* name, uint32_t ggml_type, const void* data, size_t bytes,
                           const float* scale, size_t n_scale);
+/* Load a GGUF v3 file of architecture qwen35moe (src/gguf/mod.rs:143-296, src/model/qwen35.rs:333-486, :755-858): the
+ * hyper-parameters come from its metadata, every tensor (F32, F16, Q8_0, NVFP4, `<name>.scale` beside expert stacks) goes
+ * to the device through itb_model_set_tensor straight from the mapping. On failure returns non-zero with a message in err. */
+int  itb_model_load_gguf(itb_ctx*, const char* path, itb_model** out, char* err, size_t err_cap);
+void itb_model_dims_of(itb_model*, itb_model_dims* out);   /* the hyper-parameters a model was created or loaded with */
 /* Fill every tensor from the deterministic generator, on the device (seeded synthetic weights).
  * expert_lo/expert_hi restrict routed-expert storage to [lo,hi) (expert-parallel shard); 0,0 = all. */
 int  itb_model_synth(itb_model*, uint64_t seed, uint32_t expert_lo, uint32_t expert_hi);

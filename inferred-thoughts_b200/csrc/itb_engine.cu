@@ -77,6 +77,7 @@ extern "C" int itb_model_create(itb_ctx* c, const itb_model_dims* d, itb_model**
     *out = m;
     return 0;
 }
+extern "C" void itb_model_dims_of(itb_model* m, itb_model_dims* out) { *out = m->d; }
 extern "C" void itb_model_destroy(itb_model* m) {
     if (!m) return;
     cudaStreamSynchronize(m->c->stream);

@@ -264,6 +264,20 @@ class Model:
         if self.L.itb_model_set_tensor(self.h, name.encode(), ty, _p(data), SZ(data.size), _p(sc), SZ(0 if sc is None else sc.size)):
             self.ops.check(); raise RuntimeError(f"set_tensor({name}) failed")
 
+    @classmethod
+    def from_gguf(cls, ops, path):
+        """Load a qwen35moe GGUF file (src/gguf/mod.rs, src/model/qwen35.rs:333-486): dims from its metadata, tensors from the mapping."""
+        h = C.c_void_p()
+        err = C.create_string_buffer(512)
+        if ops.L.itb_model_load_gguf(ops.h, str(path).encode(), C.byref(h), err, SZ(512)):
+            raise RuntimeError("gguf: " + err.value.decode(errors="replace"))
+        self = cls.__new__(cls)
+        self.ops, self.L, self.h = ops, ops.L, h
+        d = ModelDims()
+        ops.L.itb_model_dims_of(h, C.byref(d))
+        self.dims = d
+        return self
+
     def synth(self, seed, expert_lo=0, expert_hi=0):
         if self.L.itb_model_synth(self.h, C.c_uint64(seed), expert_lo, expert_hi):
             self.ops.check(); raise RuntimeError("model synth failed")
