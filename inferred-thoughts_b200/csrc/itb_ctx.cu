@@ -57,6 +57,7 @@ extern "C" void itb_destroy(itb_ctx* c) {
     cudaStreamSynchronize(c->stream);
     free_map(c->mirrors); free_map(c->states); free_map(c->kv);
     for (auto& w : c->weights) { cudaFree(w.second.a); cudaFree(w.second.b); cudaFree(w.second.scale2); }
+    cudaFree(c->pair_off); cudaFree(c->pair_list);
     cudaFree(c->route_ids); cudaFree(c->route_w); cudaFree(c->xq); cudaFree(c->xs); cudaFree(c->tmp_f32);
     cudaStreamDestroy(c->stream);
     delete c;

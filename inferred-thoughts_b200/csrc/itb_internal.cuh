@@ -66,6 +66,7 @@ struct itb_ctx {
     std::unordered_map<const void*, WeightEntry> weights;
     // current device route (src/ops/cuda/ops/mod.rs:299-302)
     int32_t* route_ids = nullptr;
+    int* pair_off = nullptr; int* pair_list = nullptr; size_t pair_cap = 0, pair_experts = 0;   // pairs grouped by expert (many-row expert matmuls)
     float* route_w = nullptr;
     size_t route_cap = 0, route_n_tok = 0, route_n_used = 0;
     // scratch for activation quantisation

@@ -1,6 +1,7 @@
 // The op-level seam: one extern "C" entry per method of the reference's backend trait
 // (src/ops/mod.rs:489-1426), operating on host-address-keyed device mirrors.
 #include "itb_kernels.cuh"
+#include "itb_rows.cuh"
 
 static inline unsigned blocks_for(size_t n, int per = 256) { return (unsigned)((n + per - 1) / per); }
 
@@ -185,6 +186,32 @@ static void launch_fp4(itb_ctx* c, const WeightEntry* w, const int32_t* ids, siz
         return;
     }
     DevFp4 dw{(const uint8_t*)w->a, (const uint8_t*)w->b, w->scale2, (int)w->n_in, (int)w->n_out, (int)w->n_expert, 0};
+    if (ids && n_pairs >= 16 && w->n_in % 256 == 0 && w->n_expert <= 1024) {
+        // many pairs: group them by expert and run each expert's rows through the int8-MMA tiles, so an expert's weights
+        // are read once (the reference groups the same way, kernels/moe.cuh:62-133 there)
+        const size_t E = w->n_expert;
+        if (c->pair_cap < n_pairs || c->pair_experts < E) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(c->pair_off); cudaFree(c->pair_list); c->pair_off = nullptr; c->pair_list = nullptr;
+            if (cudaMalloc(&c->pair_off, (E + 1) * 4) != cudaSuccess || cudaMalloc(&c->pair_list, n_pairs * 4) != cudaSuccess) { itb_fail_msg(c, "experts: out of device memory"); return; }
+            c->pair_cap = n_pairs; c->pair_experts = E;
+        }
+        k_group_pairs_fast<<<1, 1024, E * 4, c->stream>>>(ids, (int)n_pairs, (int)E, c->pair_off, c->pair_list);
+        ITB_LAUNCHED(c);
+        const int per_e = (int)((n_pairs + E - 1) / E), nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
+        const int ns = std::min((int)w->n_in / 256, TILE_STAGES);
+        const int div = rows_mode == 0 ? 1 : rows_mode == 1 ? n_used : 0x7fffffff;
+#define EXP_TILE(NJ, TH)                                                                                                          \
+    do {                                                                                                                         \
+        cudaFuncSetAttribute(k_tile_down<NJ, 256, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);                 \
+        k_tile_down<NJ, 256, TH><<<dim3((unsigned)E, (unsigned)((w->n_out + 128 / TH - 1) / (128 / TH))), 256,                    \
+                                   tile_smem<MK_FP4, NJ, 256, TH>((int)w->n_in), c->stream>>>(dw, c->xq, c->xs, c->pair_off, c->pair_list, od, ns, div); \
+    } while (0)
+        if (nj == 1) EXP_TILE(1, 1); else if (nj == 2) EXP_TILE(2, 1); else if (nj == 4) EXP_TILE(4, 1); else EXP_TILE(4, 2);
+#undef EXP_TILE
+        ITB_LAUNCHED(c);
+        return;
+    }
     int nb = (int)w->n_in / 32, nsb = (int)w->n_in / 16, gsh = lanes_shift(nb), nw = 8;
     int gx = (int)std::min<size_t>((w->n_out + 31) / 32, (size_t)c->sm_count * 2);
     if (gx < 1) gx = 1;

@@ -213,9 +213,11 @@ __global__ void __launch_bounds__(256) k_tile_glu(DevFp4 gate, DevFp4 up, const 
 }
 
 // Down projection of one expert for its pairs (src/ops/mod.rs:1049-1088): o[pair][row], times the expert's second
-// scale. grid (n_expert, ceil(n_out/ROWS)); activation rows are per pair.
+// scale. grid (n_expert, ceil(n_out/ROWS)); pair p reads activation row p / div (1: a row per pair; n_used: a row per
+// token; larger than the pair count: one row for all).
 template <int NJ, int KC, int TH>
-__global__ void __launch_bounds__(256) k_tile_down(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o, int n_stage) {
+__global__ void __launch_bounds__(256) k_tile_down(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o, int n_stage,
+                                                   int div = 1) {
     extern __shared__ __align__(16) unsigned char smem[];
     using C = TileCfg<MK_FP4, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(256) k_tile_down(DevFp4 down, const int8_t* hq
     const float s2 = has_s ? down.scale2[el] : 1.0f;
     for (int t0 = p0; t0 < p1; t0 += C::TOK) {
         __syncthreads();
-        if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] : -1; }
+        if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < p1 ? list[ti] / div : -1; }
         __syncthreads();
         float acc[NJ][4];
         tile_gemm<MK_FP4, NJ, KC, TH>(down.nib + eo * (k / 2), down.sc + eo * (k / 16), k, n_out, r0, hq, hs, tok_idx, smem + 256, n_stage, acc);

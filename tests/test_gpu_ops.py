@@ -234,6 +234,71 @@ def test_route_exact_including_tie_tables(ops):
     assert ids.tolist() == tied[:10]
 
 
+def _zipf_logits(n_tok, n_expert, seed, s=1.1):
+    """Router logits whose softmax is Zipf(s) over a per-token random ranking of the experts (BASELINE config 2's skew)."""
+    rng = np.random.default_rng(seed)
+    base = (-s * np.log(np.arange(1, n_expert + 1))).astype(np.float32)
+    return keep(np.concatenate([base[rng.permutation(n_expert)] for _ in range(n_tok)]).astype(np.float32))
+
+
+@pytest.fixture(scope="module")
+def cfg2_experts():
+    """BASELINE config 2's stack: hidden 2048, expert FFN 512, 256 experts, top-8."""
+    H, ff, E = 2048, 512, 256
+    g = nvfp4_weights(E, ff, H, 140); u = nvfp4_weights(E, ff, H, 141); d = nvfp4_weights(E, H, ff, 142)
+    for _, sc in (g, u, d):
+        sc *= 300
+    return H, ff, E, 8, g, u, d
+
+
+@pytest.mark.parametrize("n_tok", [1, 8, 32, 200])
+def test_grouped_expert_matmuls_config2_exact(ops, cfg2_experts, n_tok):
+    """gate/up/SiLU and down over Zipf-skewed routing at the microbenchmark's shapes: 1 and 8 tokens take the per-pair
+    dequant-and-dot kernels, 32 and 200 the expert-grouped int8-MMA tiles (8- and 16-token tiles); routing ids bit-exact,
+    the down matmul bit-exact on the same inputs, gate/up within the exp tolerance."""
+    from inferred_thoughts_b200 import host
+    H, ff, E, K, (gb, gs), (ub, us), (db, ds) = cfg2_experts
+    x = noise(n_tok * H, 143)
+    probs = _zipf_logits(n_tok, E, 2).copy(); L.orc_softmax(probs, probs.size, E)
+    want_ids = np.zeros(n_tok * K, np.int32); want_w = np.zeros(n_tok * K, np.float32)
+    L.orc_route(probs.copy(), probs.size, E, K, want_ids, want_w)
+    ops.begin_pass(n_tok)
+    route = ops.route(probs, E, K); ids, wts = ops.read_route(route)
+    assert ids.tolist() == want_ids.tolist()
+    h = keep(np.zeros(n_tok * K * ff, np.float32)); scratch = keep(np.zeros_like(h)); o = keep(np.zeros(n_tok * K * H, np.float32))
+    G, U, D = host.Experts(gb, host.NVFP4, H, ff, E, gs), host.Experts(ub, host.NVFP4, H, ff, E, us), host.Experts(db, host.NVFP4, ff, H, E, ds)
+    ops.moe_glu(G, U, route, x, h, scratch)
+    ops.matmul_experts(D, route, h, o)
+    ops.host_needs(h); ops.host_needs(o); ops.check()
+    h_want = np.zeros_like(h); o_want = np.zeros_like(o)
+    L.orc_moe_glu(gb, gs.ctypes.data, ub, us.ctypes.data, H, ff, E, ids, ids.size, K, x, x.size, h_want, 0)
+    close(h, h_want, 8 * EPS, "moe_glu (through silu)")
+    L.orc_matmul_experts(db, ff, H, E, ds.ctypes.data, ids, ids.size, K, h, h.size, o_want, 0)
+    exact(o, o_want, "matmul_experts(down)")
+
+
+def test_grouped_expert_matmuls_at_8192_tokens_repeat_the_small_case(ops, cfg2_experts):
+    """At the microbenchmark's largest size the CPU check is too slow; instead 8,192 tokens made of 16 copies of 512 distinct
+    ones must give 16 copies of the 512-token result (the tiles are 64 tokens wide there, 16 wide at 512 tokens)."""
+    from inferred_thoughts_b200 import host
+    H, ff, E, K, (gb, gs), (ub, us), (db, ds) = cfg2_experts
+    G, U, D = host.Experts(gb, host.NVFP4, H, ff, E, gs), host.Experts(ub, host.NVFP4, H, ff, E, us), host.Experts(db, host.NVFP4, ff, H, E, ds)
+    outs = []
+    for reps in (1, 16):
+        n_tok = 512 * reps
+        x = keep(np.tile(noise(512 * H, 144), reps)); probs = keep(np.tile(_zipf_logits(512, E, 3), reps)); L.orc_softmax(probs, probs.size, E)
+        ops.begin_pass(n_tok)
+        route = ops.route(probs, E, K)
+        h = keep(np.zeros(n_tok * K * ff, np.float32)); scratch = keep(np.zeros_like(h)); o = keep(np.zeros(n_tok * K * H, np.float32))
+        ops.moe_glu(G, U, route, x, h, scratch)
+        ops.matmul_experts(D, route, h, o)
+        ops.host_needs(o); ops.check()
+        outs.append(o)
+    small = outs[0].view(np.uint32)
+    for i, part in enumerate(outs[1].view(np.uint32).reshape(16, -1)):
+        assert (part == small).all(), f"copy {i} differs from the 512-token result"
+
+
 @pytest.mark.parametrize("n_tok", [1, 3])
 def test_routed_experts_exact(ops, n_tok):
     from inferred_thoughts_b200 import host
