@@ -134,6 +134,48 @@ def kernel_breakdown(eng, tok):
     return sorted(out, key=lambda k: -k["ms_per_step"])
 
 
+def experts_microbench(host, ops, hbm):
+    """BASELINE config 2: the routed-expert matmuls alone (gate+up with SiLU, then down) at hidden 2048, expert FFN 512,
+    256 experts, top-8, Zipf(1.1)-skewed routing, through the op-level seam with buffers resident on the device
+    (`moe_glu` + `matmul_experts`, src/ops/mod.rs:1049-1117). Weights are random valid NVFP4 blocks."""
+    import torch
+    H, ff, E, K = 2048, 512, 256, 8
+    rng = np.random.default_rng(2)
+
+    def blocks(n_out, n_in):
+        nb = E * n_out * n_in // 64
+        b = np.zeros((nb, 36), np.uint8)
+        b[:, :4] = rng.integers(0x20, 0x50, (nb, 4)); b[:, 4:] = rng.integers(0, 256, (nb, 32))
+        return b.reshape(-1), ((rng.random(E).astype(np.float32) + 0.5) * 0.3)
+    (gb, gs), (ub, us), (db, ds) = blocks(ff, H), blocks(ff, H), blocks(H, ff)
+    G, U, D = host.Experts(gb, host.NVFP4, H, ff, E, gs), host.Experts(ub, host.NVFP4, H, ff, E, us), host.Experts(db, host.NVFP4, ff, H, E, ds)
+    base = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32)
+    out = {}
+    for T in (1, 8, 32, 512, 8192):
+        x = rng.standard_normal(T * H).astype(np.float32)
+        lg = np.concatenate([base[rng.permutation(E)] for _ in range(T)]).astype(np.float32)
+        e = np.exp(lg.reshape(T, E) - lg.reshape(T, E).max(1, keepdims=True)); probs = (e / e.sum(1, keepdims=True)).astype(np.float32).reshape(-1)
+        h = np.zeros(T * K * ff, np.float32); scratch = np.zeros_like(h); o = np.zeros(T * K * H, np.float32)
+        ops.begin_pass(T)
+        route = ops.route(probs, E, K)
+        ids, _ = ops.read_route(route)
+        for _ in range(2):
+            ops.moe_glu(G, U, route, x, h, scratch); ops.matmul_experts(D, route, h, o)
+        ops.check(); torch.cuda.synchronize()
+        iters = 50 if T <= 32 else 10 if T <= 512 else 3
+        t0 = time.perf_counter()
+        for _ in range(iters):
+            ops.moe_glu(G, U, route, x, h, scratch); ops.matmul_experts(D, route, h, o)
+        torch.cuda.synchronize()
+        ms = (time.perf_counter() - t0) / iters * 1e3
+        ops.check()
+        distinct = len(set(ids.tolist()))
+        by = distinct * 3 * (H * ff // 64 * 36) + T * H * 4 + T * K * (ff + H) * 4
+        out[str(T)] = {"ms": ms, "tok_per_s": T / (ms / 1e3), "distinct_experts": distinct, "algorithmic_GBs": by / ms / 1e6,
+                       "frac_of_hbm": by / ms / 1e6 / hbm, "int8_TOPS": 2.0 * T * K * 3 * H * ff / (ms / 1e3) / 1e12}
+    return out
+
+
 def other_configs(host, model, dims, seed, hbm, args):
     """The other halves of the metric on the same model: the 5,548-token prefill (BASELINE config 4) and batch-32 decode
     (config 3). Reported beside the headline line, each with its own roofline fraction."""
@@ -285,6 +327,10 @@ def run_product(args, rank, world):
         line["expert_parallel"] = ep
     if world == 1 and not args.no_extra:
         line["other_configs"] = other_configs(host, model, dims, seed, hbm, args)
+        try:
+            line["other_configs"]["experts_microbench_cfg2"] = experts_microbench(host, ops, hbm)
+        except Exception as ex:
+            line["other_configs"]["experts_microbench_cfg2"] = {"error": str(ex)}
     if world == 1 and not args.no_cpu:
         try:
             from oracle import oracle_py as O

@@ -273,6 +273,39 @@ def test_tree_mode_rows_equal_single_rows():
     eb.close(); model.close(); ops.close()
 
 
+def test_phase_timeline_records_every_structured_launch(oracle, gpu):
+    """itb_timeline_arm/read: one decode step of the tiny model (3 GDN layers + 1 attention layer) fills one slot per structured
+    launch, phase stamps ascending inside a launch and launches in order; disarmed, nothing is written."""
+    import ctypes as C
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 64, 1)
+    eng.prefill(prompt_ids(9, 8, TINY["n_vocab"]))
+    eng.decode([1])
+    L = eng.L
+    L.itb_timeline_read.restype = C.c_long
+    slots = 64
+    assert L.itb_timeline_arm(eng.h, slots) == 0
+    eng.decode([2])
+    words = np.zeros(slots * 16, np.uint64)
+    assert L.itb_timeline_read(eng.h, C.c_void_p(words.ctypes.data), slots) == slots
+    w = words.reshape(slots, 16)
+    used = [i for i in range(slots) if w[i].any()]
+    # per layer: in_proj, core|prep, out_proj, ffn in_proj, glu, down = 6 structured launches, plus the LM head
+    assert used == list(range(4 * 6 + 1))
+    kinds = [int(w[i][w[i] != 0][0]) & 255 for i in used]
+    assert kinds[:6] == [2, 3, 4, 2, 8, 9] and kinds[18:24] == [2, 5, 4, 2, 8, 9] and kinds[24] == 2
+    first = []
+    for i in used:
+        ts = [int(v) >> 8 for v in w[i] if v]
+        assert ts == sorted(ts) or kinds[used.index(i)] == 8, i     # moe_glu's shared-expert blocks return before phase 2
+        first.append(min(ts))
+    assert first == sorted(first)
+    assert L.itb_timeline_arm(eng.h, 0) == 0
+    eng.decode([3]); ops.check()
+    eng.close()
+
+
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):
     from inferred_thoughts_b200 import host
     ops, model = gpu
