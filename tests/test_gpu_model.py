@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle_py as O
-from tests.util import MID, TINY, cosine, host_dims, oracle_dims, prompt_ids
+from tests.util import MID, ODD, TINY, cosine, host_dims, oracle_dims, prompt_ids
 
 pytestmark = pytest.mark.gpu
 SEED = 0
@@ -304,6 +304,49 @@ def test_phase_timeline_records_every_structured_launch(oracle, gpu):
     assert L.itb_timeline_arm(eng.h, 0) == 0
     eng.decode([3]); ops.check()
     eng.close()
+
+
+def test_odd_shape_matches_oracle_through_every_path():
+    """The ~177B model's ratios in small (configs.ODD: 24- and 6-block rows, 10 picks of 48 experts, 3 query heads per kv
+    head, 6 value heads on 3 key heads): fused one-token steps, a multi-row prefill and a batch of sequences all give the
+    oracle's routing and logits, and each other's bits."""
+    import os
+    from inferred_thoughts_b200 import host
+    om = O.OracleModel(oracle_dims(ODD)); om.synth(6, threads=8)
+    ops = host.B200Ops(0, "exact=1")
+    model = host.Model(ops, host_dims(ODD)); model.synth(6)
+    L, K = ODD["n_layer"], ODD["n_expert_used"]
+    prompt = prompt_ids(31, 70, ODD["n_vocab"])
+    om.begin(128, log_routes=True)
+    want = om.forward(prompt)
+    want_routes = om.route_log().reshape(L, len(prompt), K)[:, -1, :]
+    e_rows, e_step = host.Engine(model, 128, 1), host.Engine(model, 128, 1)
+    a = e_rows.prefill(prompt)
+    os.environ["ITB_PREFILL_STEPWISE"] = "1"
+    try:
+        b = e_step.prefill(prompt)
+    finally:
+        del os.environ["ITB_PREFILL_STEPWISE"]
+    ops.check()
+    for name, got, eng in (("multi-row", a, e_rows), ("one token at a time", b, e_step)):
+        err = np.abs(want - got).max()
+        assert err <= 2e-2 and cosine(want, got) >= 0.999 and int(np.argmax(want)) == int(np.argmax(got)), (name, err)
+        assert eng.read_routes(L, K)[:, 0, :].tolist() == want_routes.tolist(), name
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    print(f"odd shape: max-abs vs oracle {np.abs(want - a).max():.3e}, exact {(want == a).mean():.3f}")
+    # decode: the oracle's greedy tokens fed to the fused step and to a 3-sequence batch
+    eb = host.Engine(model, 128, 3)
+    lb = eb.prefill(np.stack([prompt, prompt, prompt]))
+    assert lb[1].view(np.uint32).tolist() == a.view(np.uint32).tolist()
+    t = int(np.argmax(want))
+    for _ in range(6):
+        w = om.forward([t])
+        g1, _ = e_step.decode([t]); g3, _ = eb.decode([t, t, t])
+        assert np.abs(w - g1[0]).max() <= 2e-2 and int(np.argmax(w)) == int(np.argmax(g1[0]))
+        assert g3[2].view(np.uint32).tolist() == g1[0].view(np.uint32).tolist()
+        t = int(np.argmax(w))
+    ops.check()
+    e_rows.close(); e_step.close(); eb.close(); model.close(); ops.close()
 
 
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):

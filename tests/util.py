@@ -1,7 +1,7 @@
 """Shared test helpers: configurations named in BASELINE.json and seeded inputs."""
 import numpy as np
 
-from inferred_thoughts_b200.configs import TINY, MID, M35B, L177B  # noqa: F401
+from inferred_thoughts_b200.configs import TINY, MID, ODD, M35B, L177B  # noqa: F401
 
 
 def oracle_dims(d):
