@@ -144,6 +144,20 @@ uint64_t itb_model_decode_bytes(itb_model*, uint32_t n_seq, uint32_t n_pos, uint
 
 /* n_seq independent sequences (the reference engine holds one, src/engine/mod.rs:44-59). */
 int  itb_engine_create(itb_model*, uint32_t n_ctx, uint32_t n_seq, itb_engine** out);
+/* Expert tiering, HBM <-> pinned host memory (the reference's GCLOCK expert tiers: src/cache, src/ops/cuda/experts.rs:2179-2234,
+ * ops/placement.rs:33-84). itb_model_offload_experts moves the routed-expert stacks of a loaded model to pinned host memory;
+ * itb_engine_create_tiered then keeps `capacity` (layer, expert) entries (gate + up + down) in HBM pools. Per MoE layer of a
+ * pass the routing ids are read on the host, missing experts are copied in over the slots GCLOCK gives up (entries the pass
+ * itself uses are leased), and the grouped expert kernels read through an id -> slot table. Results are bit-identical to an
+ * untiered engine. capacity >= n_seq * n_expert_used; a prefill pass is cut to capacity / n_expert_used rows.
+ * itb_engine_tier_stats: hits, misses, evictions, bytes copied. itb_gclock_*: the policy alone (host only). */
+int  itb_model_offload_experts(itb_model*);
+int  itb_engine_create_tiered(itb_model*, uint32_t n_ctx, uint32_t n_seq, uint32_t capacity, itb_engine** out);
+void itb_engine_tier_stats(itb_engine*, uint64_t* out4);
+void* itb_gclock_create(uint32_t capacity, uint32_t n_keys);
+void itb_gclock_destroy(void*);
+void itb_gclock_next_pass(void*);
+int  itb_gclock_touch(void*, int64_t key, int* hit, int64_t* evicted);   /* slot, or -1: every slot leased by this pass */
 /* Phase timeline (observability; the reference's counterpart is its per-op profiler, src/profile.rs): arm `slots`
  * launch slots (0 disarms), run single-sequence decode steps, read back slots * 16 words. Thread 0 of block 0 of the
  * step's n-th structured launch stores (nanoseconds << 8) | kernel id at word n * 16 + phase for each of its phase

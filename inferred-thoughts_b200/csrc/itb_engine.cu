@@ -6,10 +6,12 @@
 // (src/engine/mod.rs:352-437). The arithmetic of every matmul, norm, conv, delta-rule and routing
 // step keeps the CPU path's order; only exp() and the attention reduction are tolerance class.
 #include <algorithm>
+#include <array>
 #include <memory>
 
 #include "itb_kernels.cuh"
 #include "synth_model.h"
+#include "itb_tier.h"
 
 void itb_attend_dev(itb_ctx* c, cudaStream_t st, const float* q, const uint16_t* k, const uint16_t* v, int kv_dim, int n_pos, int n_q,
                     int hd, int n_head, int n_head_kv, float scale, int bf16, const int* n_pos_dev, const float* gate,
@@ -49,6 +51,10 @@ struct itb_model {
     bool finalized = false;
     uint32_t expert_lo = 0, expert_hi = 0;
     size_t bytes = 0;
+    // routed experts moved to pinned host memory (itb_model_offload_experts): per layer, per stack (gate, up, down)
+    struct HostStack { uint8_t* nib = nullptr; uint8_t* sc = nullptr; std::vector<float> s2; size_t nib_per = 0, sc_per = 0; bool has_s2 = false; };
+    std::vector<std::array<HostStack, 3>> host_experts;
+    bool offloaded = false;
 };
 
 static synth::ModelDims to_synth(const itb_model_dims& d) {
@@ -82,6 +88,7 @@ extern "C" void itb_model_destroy(itb_model* m) {
     if (!m) return;
     cudaStreamSynchronize(m->c->stream);
     for (auto& kv : m->t) { cudaFree(kv.second.a); cudaFree(kv.second.b); cudaFree(kv.second.scale2); }
+    for (auto& l : m->host_experts) for (auto& h : l) { cudaFreeHost(h.nib); cudaFreeHost(h.sc); }
     delete m;
 }
 
@@ -263,6 +270,38 @@ static bool finalize(itb_model* m) {
     return ok;
 }
 
+// Move the routed-expert stacks to pinned host memory and free their device copies: what an expert-tiered engine
+// (itb_engine_create_tiered) starts from. Everything else stays on the device.
+extern "C" int itb_model_offload_experts(itb_model* m) {
+    itb_ctx* c = m->c;
+    if (m->offloaded) return 0;
+    if (!finalize(m)) return 1;
+    if (m->expert_hi && (m->expert_lo != 0 || m->expert_hi != m->d.n_expert)) { itb_fail_msg(c, "offload: the model holds an expert shard"); return 1; }
+    const itb_model_dims& d = m->d;
+    cudaStreamSynchronize(c->stream);
+    m->host_experts.assign(d.n_layer, {});
+    const char* names[3] = {"ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight"};
+    for (uint32_t il = 0; il < d.n_layer; ++il)
+        for (int k = 0; k < 3; ++k) {
+            DevTensor& t = m->t["blk." + std::to_string(il) + "." + names[k]];
+            itb_model::HostStack& h = m->host_experts[il][k];
+            h.nib_per = t.n_out * t.n_in / 2; h.sc_per = t.n_out * t.n_in / 16;
+            const size_t nb = h.nib_per * t.n_expert, sb = h.sc_per * t.n_expert;
+            if (cudaMallocHost(&h.nib, nb) != cudaSuccess || cudaMallocHost(&h.sc, sb) != cudaSuccess) { itb_fail_msg(c, "offload: out of pinned host memory"); return 1; }
+            ITB_CUDA_RET(c, cudaMemcpy(h.nib, t.a, nb, cudaMemcpyDeviceToHost), 1);
+            ITB_CUDA_RET(c, cudaMemcpy(h.sc, t.b, sb, cudaMemcpyDeviceToHost), 1);
+            h.has_s2 = t.scale2 != nullptr;
+            h.s2.assign(t.n_expert, 1.0f);
+            if (h.has_s2) ITB_CUDA_RET(c, cudaMemcpy(h.s2.data(), t.scale2, t.n_expert * 4, cudaMemcpyDeviceToHost), 1);
+            cudaFree(t.a); cudaFree(t.b); cudaFree(t.scale2);
+            m->bytes -= nb + sb;
+            t.a = nullptr; t.b = nullptr; t.scale2 = nullptr;
+        }
+    m->offloaded = true;
+    m->finalized = false;
+    return finalize(m) ? 0 : 1;
+}
+
 // Algorithmic bytes of one decode step: every weight row read once (Q8_0 34/32 B, NVFP4 36/64 B, F32 4 B per
 // element; routed experts only the `distinct` ones hit per layer), recurrent state read + written, KV read
 // at `n_pos`, one embedding row (src/model/qwen35.rs:880-938 counts the same way).
@@ -330,9 +369,29 @@ struct EpState {
     float* o_mine = nullptr;                                                // this rank's pairs after the reduce-scatter
 };
 
+// Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
+// slots of gate+up+down live in HBM pools, chosen by GCLOCK. Per MoE layer of a pass the routing ids come to the host,
+// missing experts are copied into victims' slots on the engine's stream, the id -> slot table is refreshed, and the
+// grouped expert kernels read through the table.
+struct TierState {
+    GClock* g = nullptr;
+    size_t capacity = 0;
+    uint8_t* pool_nib[3] = {nullptr, nullptr, nullptr};
+    uint8_t* pool_sc[3] = {nullptr, nullptr, nullptr};
+    float* pool_s2[3] = {nullptr, nullptr, nullptr};
+    int* slot_map = nullptr;                 // device [n_layer][n_expert]
+    int* slot_map_host = nullptr;            // pinned mirror
+    int32_t* ids_host = nullptr;             // pinned [R * K]
+    float* s2_stage = nullptr;               // pinned [capacity * 3]: second scales in flight to the pools
+    size_t s2_at = 0;
+    uint64_t bytes_moved = 0;
+    std::vector<char> dirty;                 // slot_map rows to refresh
+};
+
 struct itb_engine {
     itb_model* m = nullptr;
     EpState* ep = nullptr;   // set in expert-parallel engines
+    TierState* tier = nullptr;   // set in expert-tiered engines
     itb_ctx* c = nullptr;
     uint32_t n_ctx = 0, B = 0, n_attn = 0, n_rec = 0;
     std::vector<int> slot_of;  // absolute layer -> attention slot or recurrent slot
@@ -582,6 +641,48 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
     e->launches_per_step = launches;
 }
 
+// Make the experts a layer's routing names resident (see TierState). Blocks on the stream once to read the ids.
+static bool tier_ensure(itb_engine* e, cudaStream_t st, uint32_t il, const int32_t* ids_dev, size_t n_pairs) {
+    TierState* t = e->tier; itb_model* m = e->m; itb_ctx* c = e->c;
+    const size_t E = m->d.n_expert;
+    if (cudaMemcpyAsync(t->ids_host, ids_dev, n_pairs * 4, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
+        return itb_fail_msg(c, "tiered experts: cannot read the routing ids");
+    t->g->next_pass();
+    t->s2_at = 0;
+    for (size_t i = 0; i < n_pairs; ++i) {
+        const int32_t ex = t->ids_host[i];
+        if (ex < 0 || (size_t)ex >= E) return itb_fail_msg(c, "tiered experts: routing id out of range");
+        const int64_t key = (int64_t)il * (int64_t)E + ex;
+        bool hit = false; int64_t evicted = -1;
+        const int slot = t->g->touch(key, &hit, &evicted);
+        if (slot < 0) return itb_fail_msg(c, "tiered experts: a pass needs more distinct experts than the HBM pool holds");
+        if (hit) continue;
+        if (evicted >= 0) { t->slot_map_host[evicted] = -1; t->dirty[(size_t)evicted / E] = 1; }
+        for (int k = 0; k < 3; ++k) {
+            const itb_model::HostStack& h = m->host_experts[il][k];
+            cudaMemcpyAsync(t->pool_nib[k] + (size_t)slot * h.nib_per, h.nib + (size_t)ex * h.nib_per, h.nib_per, cudaMemcpyHostToDevice, st);
+            cudaMemcpyAsync(t->pool_sc[k] + (size_t)slot * h.sc_per, h.sc + (size_t)ex * h.sc_per, h.sc_per, cudaMemcpyHostToDevice, st);
+            t->s2_stage[t->s2_at] = h.s2[(size_t)ex];
+            cudaMemcpyAsync(t->pool_s2[k] + slot, t->s2_stage + t->s2_at, 4, cudaMemcpyHostToDevice, st);
+            t->s2_at++;
+            t->bytes_moved += h.nib_per + h.sc_per + 4;
+        }
+        t->slot_map_host[key] = slot; t->dirty[il] = 1;
+    }
+    for (size_t r = 0; r < t->dirty.size(); ++r)
+        if (t->dirty[r]) { cudaMemcpyAsync(t->slot_map + r * E, t->slot_map_host + r * E, E * 4, cudaMemcpyHostToDevice, st); t->dirty[r] = 0; }
+    return true;
+}
+static DevFp4 tier_stack(const itb_engine* e, uint32_t il, int k, const DevFp4& shape) {
+    const TierState* t = e->tier;
+    DevFp4 w = shape;
+    w.nib = t->pool_nib[k]; w.sc = t->pool_sc[k];
+    w.scale2 = e->m->host_experts[il][k].has_s2 ? t->pool_s2[k] : nullptr;
+    w.n_expert = (int)t->capacity; w.expert_lo = 0;
+    w.slot_map = t->slot_map + (size_t)il * e->m->d.n_expert;
+    return w;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // The multi-row pass: n_seq sequences x n_tok consecutive tokens each (rows = n_seq * n_tok <= e->R), token ids in
 // `tok_rows` (device, row-major). Batched decode is (B, 1); a prefill chunk of one sequence is (1, T).
@@ -726,6 +827,11 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 xq_src = e->ep->gxq; xs_src = e->ep->gxs; ids_src = e->ep->gids;
                 cudaMemsetAsync(e->o_all, 0, (size_t)P * H * sizeof(float), st);   // rows of pairs served elsewhere stay zero
             }
+            DevFp4 Lg = L.gate, Lu = L.up, Ld = L.down;
+            if (e->tier) {
+                if (!tier_ensure(e, st, il, ids, (size_t)R * K)) return launches;
+                Lg = tier_stack(e, il, 0, L.gate); Lu = tier_stack(e, il, 1, L.up); Ld = tier_stack(e, il, 2, L.down);
+            }
             if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             launches++;
@@ -735,16 +841,16 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64
                 const int per_e = (P + E - 1) / E, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
                 const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
-#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(L.gate, L.up, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all, ns_g)
-#define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
+#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(Lg, Lu, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all, ns_g)
+#define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(Ld, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
                 if (tile_w) { if (nj == 1) GLU_TILE(1, 1); else if (nj == 2) GLU_TILE(2, 1); else if (nj == 4) GLU_TILE(4, 1); else GLU_TILE(4, 2); }
-                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(L.gate, L.up, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all);
+                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(Lg, Lu, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all);
                 launches++;
                 k_quant_rows<<<P, 128, 0, st>>>(e->h_all, ff, e->hq, e->hs); launches++;
                 if (tile_w) { if (nj == 1) DOWN_TILE(1, 1); else if (nj == 2) DOWN_TILE(2, 1); else if (nj == 4) DOWN_TILE(4, 1); else DOWN_TILE(4, 2); }
 #undef GLU_TILE
 #undef DOWN_TILE
-                else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(L.down, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
+                else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(Ld, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
                 launches++;
             }
             const float* o_src = e->o_all;
@@ -788,7 +894,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     return launches;
 }
 
-static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world, itb_engine** out) {
+static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world, itb_engine** out, uint32_t rows_cap = 0) {
     *out = nullptr;
     itb_ctx* c = m->c;
     if (!finalize(m)) return 1;
@@ -806,6 +912,8 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
     e->n_split = (int)std::max<size_t>(1, std::min<size_t>({(size_t)64, ((size_t)n_ctx + 127) / 128, (size_t)(2 * c->sm_count) / d.n_head_kv + 1}));
     itb_engine* E = e.get();
     e->R = std::max<uint32_t>(n_seq, getenv("ITB_ROWS") ? (uint32_t)atoi(getenv("ITB_ROWS")) : 512u);
+    if (rows_cap) e->R = std::max<uint32_t>(n_seq, std::min<uint32_t>(e->R, rows_cap));   // tiered: a pass may not need more experts than the pool holds
+    if (m->offloaded && !rows_cap) { itb_fail_msg(c, "engine: this model's experts are in host memory; use the tiered engine"); return 1; }
     const size_t R = e->R, K = d.n_expert_used, W = (size_t)world;   // W: ranks whose pairs the expert buffers hold
     const size_t n_parts = std::max<size_t>(B * d.n_head * e->n_split, R * d.n_head * e->n_split_rows);
     bool ok = dalloc(E, &e->kslab, (size_t)e->n_attn * B * n_ctx * kvd) && dalloc(E, &e->vslab, (size_t)e->n_attn * B * n_ctx * kvd) &&
@@ -843,6 +951,53 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
 }
 
 extern "C" int itb_engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, itb_engine** out) { return engine_create(m, n_ctx, n_seq, 1, out); }
+
+extern "C" int itb_engine_create_tiered(itb_model* m, uint32_t n_ctx, uint32_t n_seq, uint32_t capacity, itb_engine** out) {
+    *out = nullptr;
+    itb_ctx* c = m->c;
+    const itb_model_dims& d = m->d;
+    if (!m->offloaded) { itb_fail_msg(c, "tiered engine: call itb_model_offload_experts first"); return 1; }
+    const size_t n_keys = (size_t)d.n_layer * d.n_expert;
+    if (capacity < n_seq * d.n_expert_used) { itb_fail_msg(c, "tiered engine: the pool must hold at least n_seq * n_expert_used experts"); return 1; }
+    capacity = (uint32_t)std::min<size_t>(capacity, n_keys);
+    if (engine_create(m, n_ctx, n_seq, 1, out, std::max<uint32_t>(1, capacity / d.n_expert_used))) return 1;
+    itb_engine* e = *out;
+    TierState* t = new TierState();
+    e->tier = t;
+    t->capacity = capacity;
+    t->g = new GClock(capacity, n_keys);
+    t->dirty.assign(d.n_layer, 1);
+    bool ok = true;
+    for (int k = 0; k < 3; ++k) {
+        const itb_model::HostStack& h = m->host_experts[0][k];
+        ok = ok && dalloc(e, &t->pool_nib[k], (size_t)capacity * h.nib_per) && dalloc(e, &t->pool_sc[k], (size_t)capacity * h.sc_per) &&
+             dalloc(e, &t->pool_s2[k], (size_t)capacity);
+    }
+    ok = ok && dalloc(e, &t->slot_map, n_keys);
+    ok = ok && cudaMallocHost(&t->slot_map_host, n_keys * 4) == cudaSuccess && cudaMallocHost(&t->ids_host, (size_t)e->R * d.n_expert_used * 4) == cudaSuccess &&
+         cudaMallocHost(&t->s2_stage, (size_t)capacity * 3 * 4) == cudaSuccess;
+    if (!ok) { itb_fail_msg(c, "tiered engine: out of memory"); itb_engine_destroy(e); *out = nullptr; return 1; }
+    for (size_t i = 0; i < n_keys; ++i) t->slot_map_host[i] = -1;
+    return 0;
+}
+// hits, misses, evictions, bytes copied host -> HBM since the engine was created
+extern "C" void itb_engine_tier_stats(itb_engine* e, uint64_t* out4) {
+    out4[0] = out4[1] = out4[2] = out4[3] = 0;
+    if (!e->tier) return;
+    out4[0] = e->tier->g->hits; out4[1] = e->tier->g->misses; out4[2] = e->tier->g->evictions; out4[3] = e->tier->bytes_moved;
+}
+// The residency policy on its own (host only, usable without a device): see itb_tier.h.
+extern "C" void* itb_gclock_create(uint32_t capacity, uint32_t n_keys) { return capacity && n_keys ? new GClock(capacity, n_keys) : nullptr; }
+extern "C" void itb_gclock_destroy(void* g) { delete (GClock*)g; }
+extern "C" void itb_gclock_next_pass(void* g) { ((GClock*)g)->next_pass(); }
+extern "C" int itb_gclock_touch(void* g, int64_t key, int* hit, int64_t* evicted) {
+    GClock* q = (GClock*)g;
+    if (key < 0 || (size_t)key >= q->slot_of.size()) return -2;
+    bool h = false;
+    const int s = q->touch(key, &h, evicted);
+    *hit = h ? 1 : 0;
+    return s;
+}
 
 extern "C" int itb_ep_unique_id(uint8_t* out128) {
     NcclApi& nc = nccl_api();
@@ -888,6 +1043,7 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     cudaStreamSynchronize(e->c->stream);
     drop_graph(e);
     if (e->ep) { if (e->ep->comm) nccl_api().CommDestroy(e->ep->comm); delete e->ep; e->ep = nullptr; }
+    if (e->tier) { cudaFreeHost(e->tier->slot_map_host); cudaFreeHost(e->tier->ids_host); cudaFreeHost(e->tier->s2_stage); delete e->tier->g; delete e->tier; e->tier = nullptr; }
     for (void* p : e->allocs) cudaFree(p);
     cudaFree(e->history); cudaFree(e->prompt);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
@@ -915,7 +1071,7 @@ static bool ensure_graph(itb_engine* e) {
     cudaStream_t st = c->stream;
     // one eager step's worth of attribute set-up happens inside enqueue_step; capture it once
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return itb_fail_msg(c, "engine: cannot begin capture");
-    if (e->B == 1 && !e->ep) enqueue_step(e, st);
+    if (e->B == 1 && !e->ep && !e->tier) enqueue_step(e, st);
     else e->launches_per_step = enqueue_rows(e, st, (int)e->B, 1, e->tokens);
     cudaError_t err = cudaStreamEndCapture(st, &e->graph);
     if (err != cudaSuccess) return itb_fail(c, "engine: capture", err);
@@ -936,7 +1092,7 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
     itb_ctx* c = e->c;
     // expert-parallel steps hold NCCL calls; they are captured like the rest unless ITB_EP_GRAPH=0 asks for eager launches
     static const bool ep_graph = !(getenv("ITB_EP_GRAPH") && atoi(getenv("ITB_EP_GRAPH")) == 0);
-    const bool use_graph = !e->ep || ep_graph;
+    const bool use_graph = (!e->ep || ep_graph) && !e->tier;   // a tiered step talks to the host between layers
     if (use_graph && !ensure_graph(e)) return false;
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + steps > e->n_ctx) return itb_fail_msg(c, "context overflow: the step would write past n_ctx");  // src/model/qwen35.rs:984-990
@@ -947,6 +1103,7 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
             if (err != cudaSuccess) return itb_fail(c, "engine: graph launch", err);
         } else {
             e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
+            if (!c->error.empty()) return false;
         }
     }
     c->launches += (uint64_t)steps * e->launches_per_step;
@@ -1035,7 +1192,7 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
     if (logits_out) cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->m->d.n_vocab * 4, cudaMemcpyDeviceToHost, st);
     ITB_CUDA_RET(c, cudaStreamSynchronize(st), 1);
     cudaEventElapsedTime(&e->last_ms, e->ev0, e->ev1);
-    return check_flag(e) ? 0 : 1;
+    return check_flag(e) && c->error.empty() ? 0 : 1;
 }
 
 // src/engine/mod.rs:399-437 for sequence 0 of a single-sequence engine.
@@ -1084,7 +1241,7 @@ extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, it
     cudaStream_t st = c->stream;
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + 1 > e->n_ctx) { itb_fail_msg(c, "context overflow: the step would write past n_ctx"); return 1; }
-    if (e->B != 1) { itb_fail_msg(c, "profile_step: single-sequence engines only"); return 1; }
+    if (e->B != 1 || e->ep || e->tier) { itb_fail_msg(c, "profile_step: plain single-sequence engines only"); return 1; }
     if (!ensure_graph(e)) return 1;  // function attributes are set during capture
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     StepProf prof;

@@ -29,7 +29,16 @@ struct DevFp4 {
     const float* scale2 = nullptr;  // per expert, or null
     int n_in = 0, n_out = 0, n_expert = 0;
     int expert_lo = 0;              // first expert stored (expert-parallel shard); ids are global
+    const int* slot_map = nullptr;  // tiered experts: global id -> slot in the HBM pool (nib/sc/scale2 are the pool), -1 = not resident
 };
+#ifdef __CUDACC__
+// Where expert `e` of a stack lives on this device: its index into nib/sc/scale2, or -1 (stored elsewhere / not resident).
+__device__ __forceinline__ int fp4_slot(const DevFp4& w, int e) {
+    if (w.slot_map) return w.slot_map[e];
+    const int el = e - w.expert_lo;
+    return (el < 0 || el >= w.n_expert) ? -1 : el;
+}
+#endif
 struct DevF32 {
     const float* w = nullptr;
     int n_in = 0, n_out = 0;

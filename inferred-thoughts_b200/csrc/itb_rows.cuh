@@ -420,9 +420,10 @@ __global__ void __launch_bounds__(256) k_glu_grouped(DevFp4 gate, DevFp4 up, con
                                                      const int* off, const int* list, float* h) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int e = blockIdx.x, k = gate.n_in, ff = gate.n_out, nsb = k / 16;
-    const int el = e - gate.expert_lo;
     const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
+    if (p0 >= p1) return;
+    const int el = fp4_slot(gate, e);
+    if (el < 0) return;
     int8_t* sq = (int8_t*)smem;
     float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(k));
     const int r0 = blockIdx.y * MMA_ROWS + (threadIdx.x >> 5) * 16;
@@ -457,9 +458,10 @@ __global__ void __launch_bounds__(256) k_glu_grouped(DevFp4 gate, DevFp4 up, con
 __global__ void __launch_bounds__(256) k_down_grouped(DevFp4 down, const int8_t* hq, const float* hs, const int* off, const int* list, float* o) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int e = blockIdx.x, k = down.n_in, n_out = down.n_out, nsb = k / 16;
-    const int el = e - down.expert_lo;
     const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
+    if (p0 >= p1) return;
+    const int el = fp4_slot(down, e);
+    if (el < 0) return;
     int8_t* sq = (int8_t*)smem;
     float* ss = (float*)(sq + (size_t)MMA_TOK * mma_act_stride(k));
     const int r0 = blockIdx.y * MMA_ROWS + (threadIdx.x >> 5) * 16;

@@ -188,9 +188,11 @@ __global__ void __launch_bounds__(256) k_tile_glu(DevFp4 gate, DevFp4 up, const 
     extern __shared__ __align__(16) unsigned char smem[];
     using C = TileCfg<MK_FP4, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
-    const int e = blockIdx.x, k = gate.n_in, ff = gate.n_out, el = e - gate.expert_lo;
+    const int e = blockIdx.x, k = gate.n_in, ff = gate.n_out;
     const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= gate.n_expert) return;
+    if (p0 >= p1) return;
+    const int el = fp4_slot(gate, e);
+    if (el < 0) return;
     const int r0 = blockIdx.y * C::ROWS;
     const size_t eo = (size_t)el * ff;
     const bool has_g = gate.scale2 != nullptr, has_u = up.scale2 != nullptr;
@@ -221,9 +223,11 @@ __global__ void __launch_bounds__(256) k_tile_down(DevFp4 down, const int8_t* hq
     extern __shared__ __align__(16) unsigned char smem[];
     using C = TileCfg<MK_FP4, NJ, KC, TH>;
     int* tok_idx = (int*)smem;
-    const int e = blockIdx.x, k = down.n_in, n_out = down.n_out, el = e - down.expert_lo;
+    const int e = blockIdx.x, k = down.n_in, n_out = down.n_out;
     const int p0 = off[e], p1 = off[e + 1];
-    if (p0 >= p1 || el < 0 || el >= down.n_expert) return;
+    if (p0 >= p1) return;
+    const int el = fp4_slot(down, e);
+    if (el < 0) return;
     const int r0 = blockIdx.y * C::ROWS;
     const size_t eo = (size_t)el * n_out;
     const bool has_s = down.scale2 != nullptr;

@@ -66,6 +66,7 @@ def lib():
         L.itb_engine_last_ms.restype = C.c_float
         L.itb_engine_launches_per_step.restype = C.c_uint64
         L.itb_engine_generate.restype = C.c_long
+        L.itb_gclock_create.restype = C.c_void_p
     return _LIB
 
 
@@ -278,6 +279,11 @@ class Model:
         self.dims = d
         return self
 
+    def offload_experts(self):
+        """Move the routed experts to pinned host memory; only tiered engines (Engine(tier_capacity=...)) can run the model after."""
+        if self.L.itb_model_offload_experts(self.h):
+            self.ops.check(); raise RuntimeError("offload_experts failed")
+
     def synth(self, seed, expert_lo=0, expert_hi=0):
         if self.L.itb_model_synth(self.h, C.c_uint64(seed), expert_lo, expert_hi):
             self.ops.check(); raise RuntimeError("model synth failed")
@@ -327,12 +333,15 @@ def share_unique_id(rank, lib_=None, group=None):
 class Engine:
     """Engine::{prefill, decode, generate} (src/engine/mod.rs:352-437) over n_seq independent sequences."""
 
-    def __init__(self, model: Model, n_ctx, n_seq=1, ep=None):
+    def __init__(self, model: Model, n_ctx, n_seq=1, ep=None, tier_capacity=None):
         """ep = (rank, world, unique_id bytes): an expert-parallel engine over a model that holds this rank's expert range
         (`expert_range`); every rank must then make the same calls with the same shapes (each on its own sequences)."""
         self.model, self.L, self.n_seq = model, model.L, n_seq
         h = C.c_void_p()
-        if ep is None:
+        if tier_capacity is not None:
+            # experts in pinned host memory (Model.offload_experts), `tier_capacity` (layer, expert) entries cached in HBM
+            rc = self.L.itb_engine_create_tiered(model.h, n_ctx, n_seq, int(tier_capacity), C.byref(h))
+        elif ep is None:
             rc = self.L.itb_engine_create(model.h, n_ctx, n_seq, C.byref(h))
         else:
             rank, world, uid = ep
@@ -354,6 +363,11 @@ class Engine:
     def _chk(self, rc, what):
         if rc:
             self.model.ops.check(); raise RuntimeError(f"{what} failed ({rc})")
+
+    def tier_stats(self):
+        out = (C.c_uint64 * 4)()
+        self.L.itb_engine_tier_stats(self.h, out)
+        return dict(hits=out[0], misses=out[1], evictions=out[2], bytes_moved=out[3])
 
     def reset(self): self.L.itb_engine_reset(self.h)
     def pos(self, seq=0): return self.L.itb_engine_pos(self.h, seq)
