@@ -176,6 +176,25 @@ def experts_microbench(host, ops, hbm):
     return out
 
 
+def tiered_decode(host, ops, dims, seed, frac=0.5, steps=32):
+    """Batch-1 decode with the routed experts in pinned host memory and `frac` of the (layer, expert) entries cached in HBM
+    under GCLOCK (uniform-random routing of the synthetic router: a worst case for any cache)."""
+    cold = host.Model(ops, host.ModelDims(**dims)); cold.synth(seed); cold.offload_experts()
+    cap = int(dims["n_layer"] * dims["n_expert"] * frac)
+    eng = host.Engine(cold, N_CTX, 1, tier_capacity=cap)
+    eng.prefill(prompts(1, seed + 5, dims["n_vocab"]), want_logits=False)
+    first = eng.decode_loop(np.zeros(1, np.uint32), 4)[-1]
+    s0 = eng.tier_stats()
+    eng.decode_loop(first, steps)
+    ms = eng.last_ms() / steps
+    s1 = eng.tier_stats()
+    hits, misses = s1["hits"] - s0["hits"], s1["misses"] - s0["misses"]
+    out = {"value": 1e3 / ms, "unit": "tok/s", "ms_per_step": ms, "pool_entries": cap, "pool_fraction": frac,
+           "hit_rate": hits / max(1, hits + misses), "host_to_hbm_MB_per_token": (s1["bytes_moved"] - s0["bytes_moved"]) / steps / 1e6}
+    eng.close(); cold.close()
+    return out
+
+
 def other_configs(host, model, dims, seed, hbm, args):
     """The other halves of the metric on the same model: the 5,548-token prefill (BASELINE config 4) and batch-32 decode
     (config 3). Reported beside the headline line, each with its own roofline fraction."""
@@ -327,6 +346,10 @@ def run_product(args, rank, world):
         line["expert_parallel"] = ep
     if world == 1 and not args.no_extra:
         line["other_configs"] = other_configs(host, model, dims, seed, hbm, args)
+        try:
+            line["other_configs"]["tiered_experts_half_in_hbm"] = tiered_decode(host, ops, dims, seed)
+        except Exception as ex:
+            line["other_configs"]["tiered_experts_half_in_hbm"] = {"error": str(ex)}
         try:
             line["other_configs"]["experts_microbench_cfg2"] = experts_microbench(host, ops, hbm)
         except Exception as ex:
