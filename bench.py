@@ -240,7 +240,13 @@ def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
     uid = host.share_unique_id(rank)
     lo, hi = host.expert_range(rank, world, dims["n_expert"])
     shard = host.Model(ops, host.ModelDims(**dims)); shard.synth(seed, lo, hi)
-    eng = host.Engine(shard, N_CTX, B, ep=(rank, world, uid))
+    # NCCL may print its version banner on stdout when a communicator is made; this program's stdout carries one JSON line only
+    sys.stdout.flush()
+    saved = os.dup(1); os.dup2(2, 1)
+    try:
+        eng = host.Engine(shard, N_CTX, B, ep=(rank, world, uid))
+    finally:
+        sys.stdout.flush(); os.dup2(saved, 1); os.close(saved)
     eng.prefill(prompts(B, seed + 1000 * rank, dims["n_vocab"]), want_logits=False)
     first = eng.decode_loop(np.zeros(B, np.uint32), max(args.warmup, 3))[-1]
     dist.barrier(); torch.cuda.synchronize()
