@@ -349,6 +349,31 @@ def test_odd_shape_matches_oracle_through_every_path():
     e_rows.close(); e_step.close(); eb.close(); model.close(); ops.close()
 
 
+def test_benchmark_mode_bf16_kv_and_tree_dots_stays_within_tolerance(oracle):
+    """The benchmark runs kv=bf16 (BASELINE config 3) and exact=0; the oracle keeps the reference's f16 cache and serial dots.
+    The difference must stay inside the logits tolerance, and the engine must still agree with itself (multi-row == stepwise)."""
+    import os
+    from inferred_thoughts_b200 import host
+    ops = host.B200Ops(0, "kv=bf16,exact=0")
+    model = host.Model(ops, host_dims(TINY)); model.synth(SEED)
+    prompt = prompt_ids(1, 64, TINY["n_vocab"])
+    oracle.begin(128)
+    want = oracle.forward(prompt)
+    e1, e2 = host.Engine(model, 128, 1), host.Engine(model, 128, 1)
+    a = e1.prefill(prompt)
+    os.environ["ITB_PREFILL_STEPWISE"] = "1"
+    try:
+        b = e2.prefill(prompt)
+    finally:
+        del os.environ["ITB_PREFILL_STEPWISE"]
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    err, cos = float(np.abs(want - a).max()), cosine(want, a)
+    print(f"bf16 kv, tree dots vs oracle: max-abs {err:.3e}, cosine {cos:.7f}")
+    assert err <= 2e-2 and cos >= 0.999
+    ops.check()
+    e1.close(); e2.close(); model.close(); ops.close()
+
+
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):
     from inferred_thoughts_b200 import host
     ops, model = gpu
