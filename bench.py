@@ -240,13 +240,7 @@ def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
     uid = host.share_unique_id(rank)
     lo, hi = host.expert_range(rank, world, dims["n_expert"])
     shard = host.Model(ops, host.ModelDims(**dims)); shard.synth(seed, lo, hi)
-    # NCCL may print its version banner on stdout when a communicator is made; this program's stdout carries one JSON line only
-    sys.stdout.flush()
-    saved = os.dup(1); os.dup2(2, 1)
-    try:
-        eng = host.Engine(shard, N_CTX, B, ep=(rank, world, uid))
-    finally:
-        sys.stdout.flush(); os.dup2(saved, 1); os.close(saved)
+    eng = host.Engine(shard, N_CTX, B, ep=(rank, world, uid))
     eng.prefill(prompts(B, seed + 1000 * rank, dims["n_vocab"]), want_logits=False)
     first = eng.decode_loop(np.zeros(B, np.uint32), max(args.warmup, 3))[-1]
     dist.barrier(); torch.cuda.synchronize()
@@ -369,7 +363,7 @@ def run_product(args, rank, world):
                                     "sample": f"{n} decode tokens from an empty context, same weights (copied back from the device in {load_s:.0f} s), batch 1"}
         except Exception as ex:  # the baseline is a report, never a reason to lose the measurement
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
-    print(json.dumps(line), flush=True)
+    emit(line)
     eng.close(); model.close(); ops.close()
 
 
@@ -406,7 +400,7 @@ def run_reference(args, rank, world):
         tok = int(np.argmax(om.forward([tok])))
     dt = time.perf_counter() - t0
     v = args.steps / dt
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)", "value": v, "unit": "tok/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": f"synthetic ({src})",
@@ -414,7 +408,16 @@ def run_reference(args, rank, world):
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
                          "sample": f"{args.steps} decode tokens from an empty context after {args.warmup} warm-up tokens"},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-    }), flush=True)
+    })
+
+
+_JSON_FD = None
+
+
+def emit(obj):
+    """The run's one JSON line, on the process's real stdout."""
+    data = (json.dumps(obj) + "\n").encode()
+    os.write(_JSON_FD if _JSON_FD is not None else 1, data)
 
 
 def main():
@@ -432,6 +435,12 @@ def main():
     ap.add_argument("--model", default="m35b", choices=["m35b", "l177b"], help="m35b: the headline 35B-A3B shape; l177b: BASELINE config 5's ~177B shape")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: the same shape with fewer layers (small device footprint for ncu captures)")
     args = ap.parse_args()
+    # Libraries print banners on stdout (NCCL's version line, for one); stdout must carry the JSON line alone, so everything
+    # else written to file descriptor 1 during the run goes to stderr.
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
     global PROMPT
     PROMPT = args.prompt
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))

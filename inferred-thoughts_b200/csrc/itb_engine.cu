@@ -367,6 +367,8 @@ struct EpState {
     int rank = 0, world = 1;
     int8_t* gxq = nullptr; float* gxs = nullptr; int32_t* gids = nullptr;   // gathered rows of all ranks, rank-major
     float* o_mine = nullptr;                                                // this rank's pairs after the reduce-scatter
+    float* gw = nullptr;                                                    // routing weights of the gathered rows [world][n_used] (fused one-token step)
+    float* grouter = nullptr;                                               // gathered router logits [world][n_expert] (fused one-token step)
 };
 
 // Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
@@ -605,27 +607,57 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
                            : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));
         launch_in(f, 2 * d.shared_ff, gxf);
         MARK(KC_FFN_IN, (uint64_t)H * d.n_expert * 4 + 2 * q8b(H, d.shared_ff) + (uint64_t)H * 4 + (uint64_t)B * (2ull * H + d.n_expert + 2ull * d.shared_ff) * 4);
+        const int W = e->ep ? e->ep->world : 1, RW = B * W;   // rows the expert kernels see: ours, or every rank's (expert parallel)
         MoeGlu g{};
         g.router = e->router; g.n_expert = d.n_expert; g.n_used = d.n_expert_used; g.xq = e->xq; g.xs = e->xs; g.n_embd = H;
         g.gate = L.gate; g.up = L.up; g.sg = e->sg; g.su = e->su; g.sff = d.shared_ff;
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
+        g.shared_row = -1;
+        if (e->ep) {
+            // every rank's quantised row and router logits (B is 1 here): the kernels below then serve the picks that name a local expert
+            NcclApi& nc = nccl_api();
+            nc.GroupStart();
+            nc.AllGather(e->xq, e->ep->gxq, (size_t)H, NcclApi::Int8, e->ep->comm, st);
+            nc.AllGather(e->xs, e->ep->gxs, (size_t)(H / 32), NcclApi::Float32, e->ep->comm, st);
+            nc.AllGather(e->router, e->ep->grouter, (size_t)d.n_expert, NcclApi::Float32, e->ep->comm, st);
+            nc.GroupEnd();
+            launches++;
+            cudaMemsetAsync(e->o_all, 0, (size_t)W * d.n_expert_used * H * sizeof(float), st);
+            g.router = e->ep->grouter; g.xq = e->ep->gxq; g.xs = e->ep->gxs; g.shared_row = e->ep->rank;
+            g.ids_out = e->ep->gids; g.w_out = e->ep->gw;
+        }
         g.tl_slot = tl++;
-        launch_k(pdl, k_moe_glu, dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, B), TPB, moe_glu_smem(d.n_expert, H), st, g);
+        launch_k(pdl, k_moe_glu, dim3(d.n_expert_used * (d.expert_ff / 32) + d.shared_ff / 32, RW), TPB, moe_glu_smem(d.n_expert, H), st, g);
         MARK(KC_MOE_GLU, (uint64_t)B * (2ull * d.n_expert_used * f4b(H, d.expert_ff) + (uint64_t)d.n_expert_used * d.expert_ff * 4));
         MoeDown w{};
         w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
         w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
+        if (e->ep) { w.o_pairs = e->o_all; w.own_row = e->ep->rank; w.shd = e->shd; }
         {
             int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
             int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-            dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), B);
+            dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), RW);
             w.tl_slot = tl++;
             size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
             if (rp == 1) launch_k(pdl, k_moe_down<1>, grid, TPB, smem_d, st, w);
             else if (rp == 2) launch_k(pdl, k_moe_down<2>, grid, TPB, smem_d, st, w);
             else if (rp == 4) launch_k(pdl, k_moe_down<4>, grid, TPB, smem_d, st, w);
             else launch_k(pdl, k_moe_down<8>, grid, TPB, smem_d, st, w);
+        }
+        if (e->ep) {
+            // each pick's output row comes home (exactly one rank wrote it: an exact sum), then the pick-order combine, the
+            // gated shared expert and the residual add, as k_moe_down does them on one GPU
+            const size_t KH = (size_t)d.n_expert_used * H;
+            nccl_api().ReduceScatter(e->o_all, e->ep->o_mine, KH, NcclApi::Float32, NcclApi::Sum, e->ep->comm, st);
+            k_moe_finish_rows<<<(unsigned)((H + 255) / 256), 256, 0, st>>>(e->x, H, e->ep->o_mine, e->ep->gw + (size_t)e->ep->rank * d.n_expert_used,
+                                                                          d.n_expert_used, e->shd, e->shlogit, (size_t)H);
+            launches += 2;
+            // the routing this rank's token got, where read_routes looks for it
+            cudaMemcpyAsync(e->route_ids + (size_t)il * e->R * d.n_expert_used, e->ep->gids + (size_t)e->ep->rank * d.n_expert_used,
+                            d.n_expert_used * 4, cudaMemcpyDeviceToDevice, st);
+            cudaMemcpyAsync(e->route_w + (size_t)il * e->R * d.n_expert_used, e->ep->gw + (size_t)e->ep->rank * d.n_expert_used,
+                            d.n_expert_used * 4, cudaMemcpyDeviceToDevice, st);
         }
         MARK(KC_MOE_DOWN, (uint64_t)B * d.n_expert_used * f4b(d.expert_ff, H) + q8b(d.shared_ff, H) + (uint64_t)B * ((uint64_t)d.n_expert_used * d.expert_ff + 2ull * H) * 4);
     }
@@ -943,7 +975,7 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
         e->ep = new EpState();
         e->ep->world = world;
         if (!(dalloc(E, &e->ep->gxq, W * R * H) && dalloc(E, &e->ep->gxs, W * R * H / 32) && dalloc(E, &e->ep->gids, W * R * K) &&
-              dalloc(E, &e->ep->o_mine, R * K * H))) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
+              dalloc(E, &e->ep->o_mine, R * K * H) && dalloc(E, &e->ep->grouter, W * d.n_expert) && dalloc(E, &e->ep->gw, W * R * K))) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
     }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) { itb_fail_msg(c, "engine: device error during set-up"); return 1; }
     *out = e.release();
@@ -1071,7 +1103,7 @@ static bool ensure_graph(itb_engine* e) {
     cudaStream_t st = c->stream;
     // one eager step's worth of attribute set-up happens inside enqueue_step; capture it once
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return itb_fail_msg(c, "engine: cannot begin capture");
-    if (e->B == 1 && !e->ep && !e->tier) enqueue_step(e, st);
+    if (e->B == 1 && !e->tier) enqueue_step(e, st);   // expert-parallel engines too: the step gathers and scatters around its expert kernels
     else e->launches_per_step = enqueue_rows(e, st, (int)e->B, 1, e->tokens);
     cudaError_t err = cudaStreamEndCapture(st, &e->graph);
     if (err != cudaSuccess) return itb_fail(c, "engine: capture", err);
@@ -1102,7 +1134,8 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
             cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
             if (err != cudaSuccess) return itb_fail(c, "engine: graph launch", err);
         } else {
-            e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
+            if (e->B == 1 && !e->tier) enqueue_step(e, c->stream);
+            else e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
             if (!c->error.empty()) return false;
         }
     }

@@ -421,6 +421,7 @@ struct MoeGlu {
     int8_t* hq; float* hs;                          // [B][n_used*ff] int8, [B][n_used*ff/32]
     int8_t* sq; float* ss;                          // [B][sff] int8, [B][sff/32]: silu(sg)*su quantised
     int32_t* ids_out; float* w_out;
+    int shared_row;                                 // -1: every row has a shared expert activation; r: only row r, held at index 0 (expert-parallel step)
     int tl_slot;
 };
 __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
@@ -439,13 +440,14 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     TL(TLK_MOE_GLU, 1);
     if (unit >= n_units) {
         // shared expert: silu(gate) * up for 32 elements, quantised (src/model/qwen35.rs:1669-1678)
-        if (wid == 0) {
+        if (wid == 0 && (p.shared_row < 0 || p.shared_row == b)) {
+            const size_t sb = p.shared_row < 0 ? (size_t)b : 0;
             const int k = (unit - n_units) * 32 + lane;
-            float v = silu_f(p.sg[(size_t)b * p.sff + k]) * p.su[(size_t)b * p.sff + k];
+            float v = silu_f(p.sg[sb * p.sff + k]) * p.su[sb * p.sff + k];
             float dq;
             int8_t q = warp_quant_q8(v, &dq);
-            p.sq[(size_t)b * p.sff + k] = q;
-            if (lane == 0) p.ss[(size_t)b * (p.sff / 32) + (unit - n_units)] = dq;
+            p.sq[sb * p.sff + k] = q;
+            if (lane == 0) p.ss[sb * (p.sff / 32) + (unit - n_units)] = dq;
         }
         return;
     }
@@ -597,6 +599,10 @@ struct MoeDown {
     const float* logit;
     float* x; int x_stride;
     int local_only; float* partial;
+    // expert-parallel step: rows are the gathered rows of all ranks; every local pick's output row goes to
+    // o_pairs[(b * n_used + k)][n_out] (others are left as they are: zero), and only row own_row (activation at index 0)
+    // gets its shared-expert row into shd; no combine and no residual here.
+    float* o_pairs; int own_row; float* shd;
     int tl_slot;
 };
 template <int RP>
@@ -605,6 +611,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     __shared__ int s_el[16];
     __shared__ float s_wt[16], s_s2[16];
     __shared__ float s_g;
+    __shared__ int s_loc[16], s_nloc;        // picks whose expert is stored here, in pick order (expert-parallel pairs mode)
     const int ff = p.ff, sff = p.sff, nbf = ff / 32, nbs = sff / 32, nsb = ff / 16;
     const int gf = lanes_shift(nbf), gs = lanes_shift(nbs);
     const int b = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, nw = blockDim.x >> 5, lane = tid & 31;
@@ -625,31 +632,54 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     TL(TLK_MOE_DOWN, 1);
     for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];
     for (int i = tid; i < p.n_used * nbf; i += blockDim.x) hs[i] = p.hs[(size_t)b * p.n_used * nbf + i];
-    for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + (size_t)b * sff))[i];
-    for (int i = tid; i < nbs; i += blockDim.x) ss[i] = p.ss[(size_t)b * nbs + i];
+    const bool pairs = p.o_pairs != nullptr;
+    const size_t shb = pairs ? 0 : (size_t)b;        // where this row's shared-expert activation and gate logit sit
+    if (!pairs || b == p.own_row) {
+        for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + shb * sff))[i];
+        for (int i = tid; i < nbs; i += blockDim.x) ss[i] = p.ss[shb * nbs + i];
+    }
     if (tid < p.n_used) {
         int el = p.ids[(size_t)b * p.n_used + tid] - p.down.expert_lo;
         s_el[tid] = (el < 0 || el >= p.down.n_expert) ? -1 : el;
         s_wt[tid] = p.wts[(size_t)b * p.n_used + tid];
         s_s2[tid] = (p.down.scale2 && s_el[tid] >= 0) ? p.down.scale2[s_el[tid]] : 1.0f;
     }
-    if (tid == 32) s_g = sigmoid_f(p.logit[b]);
+    if (tid == 32 && !pairs) s_g = sigmoid_f(p.logit[b]);
     __syncthreads();
+    if (pairs && tid == 0) { int n = 0; for (int k = 0; k < p.n_used; ++k) if (s_el[k] >= 0) s_loc[n++] = k; s_nloc = n; }
+    if (pairs) __syncthreads();
     TL(TLK_MOE_DOWN, 2);
     const bool has_s = p.down.scale2 != nullptr;
     float* x = p.x + (size_t)b * p.x_stride;
 #pragma unroll 1
     for (int row = b0 + r0; row < b0 + r1; ++row) {
-        // routed picks: item k = pick k of this row
-        rows_list<MK_FP4, RP>(p.n_used, ff, terms, gf,
+        // routed picks: item k = pick k of this row (pairs mode: the k-th LOCAL pick, so no row of an absent expert is read)
+        rows_list<MK_FP4, RP>(pairs ? s_nloc : p.n_used, ff, terms, gf,
             [&](int k, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
-                const int el = max(s_el[k], 0);
+                const int pk = pairs ? s_loc[k] : k;
+                const int el = max(s_el[pk], 0);
                 pa = p.down.nib + ((size_t)el * n_out + row) * (ff / 2);
                 pb = p.down.sc + ((size_t)el * n_out + row) * nsb;
-                q = hq + k * ff; s = hs + k * nbf;
+                q = hq + pk * ff; s = hs + pk * nbf;
             },
-            [&](int k, float v) { outv[k] = v; });
+            [&](int k, float v) { outv[pairs ? s_loc[k] : k] = v; });
         float sh = 0.0f;
+        if (pairs) {
+            if (b == p.own_row) {
+                rows_list<MK_Q8, 1>(1, sff, terms, gs,
+                    [&](int, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {
+                        pa = (const uint8_t*)p.shared_down.q + (size_t)row * sff;
+                        pb = (const uint8_t*)p.shared_down.s + (size_t)row * (sff / 16);
+                        q = sq; s = ss;
+                    },
+                    [&](int, float v) { p.shd[row] = v; });
+            }
+            __syncwarp();
+            if (lane < p.n_used && s_el[lane] >= 0)
+                p.o_pairs[((size_t)b * p.n_used + lane) * n_out + row] = has_s ? outv[lane] * s_s2[lane] : outv[lane];
+            __syncwarp();
+            continue;
+        }
         if (!p.local_only) {
             rows_list<MK_Q8, 1>(1, sff, terms, gs,
                 [&](int, const uint8_t*& pa, const uint8_t*& pb, const int8_t*& q, const float*& s) {

@@ -21,29 +21,33 @@ def main():
     dev = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(dev)
     dist.init_process_group("gloo")          # host-side rendezvous only; the data path is the library's own NCCL communicator
-    uid = host.share_unique_id(rank)
     dims = dict(configs.MID)
     seed = configs.SEEDS["mid"]
     ops = host.B200Ops(dev, "exact=1")
     full = host.Model(ops, host.ModelDims(**dims)); full.synth(seed)
     lo, hi = host.expert_range(rank, world, dims["n_expert"])
     shard = host.Model(ops, host.ModelDims(**dims)); shard.synth(seed, lo, hi)
-    n_seq = 3
+    ok = True
     rng = np.random.default_rng(100 + rank)                 # every rank its own sequences
-    prompts = rng.integers(0, dims["n_vocab"], (n_seq, 40)).astype(np.uint32)
-    e1 = host.Engine(full, 128, n_seq)
-    e2 = host.Engine(shard, 128, n_seq, ep=(rank, world, uid))
-    a, b = e1.prefill(prompts), e2.prefill(prompts)
-    ok = a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
-    toks = np.argmax(a, 1).astype(np.uint32)
-    for _ in range(4):
-        (la, na), (lb, nb) = e1.decode(toks), e2.decode(toks)
-        ok = ok and la.view(np.uint32).tolist() == lb.view(np.uint32).tolist() and na.tolist() == nb.tolist()
-        toks = na
-    ops.check()
+    for n_seq in (3, 1):                                     # 3: the multi-row passes; 1: the fused one-token step around the collectives
+        prompts = rng.integers(0, dims["n_vocab"], (n_seq, 40)).astype(np.uint32)
+        e1 = host.Engine(full, 128, n_seq)
+        e2 = host.Engine(shard, 128, n_seq, ep=(rank, world, host.share_unique_id(rank)))
+        a, b = e1.prefill(prompts), e2.prefill(prompts)
+        a, b = np.atleast_2d(a), np.atleast_2d(b)
+        ok = ok and a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+        toks = np.argmax(a, 1).astype(np.uint32)
+        for _ in range(4):
+            (la, na), (lb, nb) = e1.decode(toks), e2.decode(toks)
+            ok = ok and la.view(np.uint32).tolist() == lb.view(np.uint32).tolist() and na.tolist() == nb.tolist()
+            toks = na
+        L, K = dims["n_layer"], dims["n_expert_used"]
+        ok = ok and e1.read_routes(L, K).tolist() == e2.read_routes(L, K).tolist()
+        ops.check()
+        e2.close(); e1.close()
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-    e2.close(); e1.close(); shard.close(); full.close(); ops.close()
+    shard.close(); full.close(); ops.close()
     dist.destroy_process_group()
     if not ok:
         print(f"ep_check FAILED on rank {rank}", flush=True)
