@@ -61,9 +61,9 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     }
     pdl_wait();
     TL(TLK_IN_PROJ, 1);
-    block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red);
+    const bool quantised = block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red, xq, xs);
     TL(TLK_IN_PROJ, 2);
-    block_quant_q8(xn, n, xq, xs);
+    if (!quantised) block_quant_q8(xn, n, xq, xs);
     TL(TLK_IN_PROJ, 3);
     if (p.xq_out && blockIdx.x == 0) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];

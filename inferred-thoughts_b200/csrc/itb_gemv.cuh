@@ -23,8 +23,10 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // ---- activation prologues ------------------------------------------------------------------------
 // RMSNorm of one row into shared memory: f32 squares, f64 accumulation (tree), (x*scale)*w
 // (src/ops/naive.rs:139-152, :633-640). `red` holds blockDim.x/32 doubles.
-__device__ __forceinline__ void block_rms_norm(const float* __restrict__ x, const float* __restrict__ w, int n, float eps,
-                                               float* xn, double* red) {
+// With xq/xs given, the vector path also quantises the normalised row to Q8_0 in the same pass (8 consecutive lanes hold
+// one 32-block; src/ops/naive.rs:653-675) and returns true; otherwise the caller quantises from xn.
+__device__ __forceinline__ bool block_rms_norm(const float* __restrict__ x, const float* __restrict__ w, int n, float eps,
+                                               float* xn, double* red, int8_t* xq = nullptr, float* xs = nullptr) {
     const int wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     if ((n & 3) == 0 && n <= 16 * (int)blockDim.x && ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)xn)) & 15) == 0) {
         // the row and the norm weights as float4, every load in flight before the first use: one memory round trip
@@ -50,10 +52,25 @@ __device__ __forceinline__ void block_rms_norm(const float* __restrict__ x, cons
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int i = threadIdx.x + j * blockDim.x;
-            if (i < nv) ((float4*)xn)[i] = make_float4(xv[j].x * sc * wv[j].x, xv[j].y * sc * wv[j].y, xv[j].z * sc * wv[j].z, xv[j].w * sc * wv[j].w);
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i < nv) { o = make_float4(xv[j].x * sc * wv[j].x, xv[j].y * sc * wv[j].y, xv[j].z * sc * wv[j].z, xv[j].w * sc * wv[j].w); ((float4*)xn)[i] = o; }
+            if (xq && (int)(j * blockDim.x) < nv) {      // whole warps take this branch together: nv and blockDim are multiples of 8 and 32
+                float amax = fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w)));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                const float d = amax / 127.0f, id = d != 0.0f ? 1.0f / d : 0.0f;
+                if (i < nv) {
+                    char4 q;
+                    q.x = (signed char)fminf(127.0f, fmaxf(-128.0f, roundf(o.x * id))); q.y = (signed char)fminf(127.0f, fmaxf(-128.0f, roundf(o.y * id)));
+                    q.z = (signed char)fminf(127.0f, fmaxf(-128.0f, roundf(o.z * id))); q.w = (signed char)fminf(127.0f, fmaxf(-128.0f, roundf(o.w * id)));
+                    ((char4*)xq)[i] = q;
+                    if ((i & 7) == 0) xs[i >> 3] = __half2float(__float2half_rn(d));
+                }
+            }
         }
         __syncthreads();
-        return;
+        return xq != nullptr;
     }
     double acc = 0.0;
     for (int i = threadIdx.x; i < n; i += blockDim.x) { float v = x[i]; xn[i] = v; acc += (double)(v * v); }
@@ -66,6 +83,7 @@ __device__ __forceinline__ void block_rms_norm(const float* __restrict__ x, cons
     float sc = 1.0f / sqrtf(mean + eps);
     for (int i = threadIdx.x; i < n; i += blockDim.x) xn[i] = xn[i] * sc * w[i];
     __syncthreads();
+    return false;
 }
 
 // One Q8_0 block of 32 values held one per lane (src/ops/naive.rs:653-675): d = amax/127 through f16,
