@@ -58,7 +58,10 @@ __global__ void __launch_bounds__(256) k_norm_quant(const float* x, const float*
     double* red = (double*)smem;
     float* xn = (float*)(red + 32);
     const size_t r = blockIdx.x;
-    block_rms_norm(x + r * n, w, n, eps, xn, red);
+    if (block_rms_norm(x + r * n, w, n, eps, xn, red, xq + r * n, xs + r * (n / 32))) {   // quantised in the same pass
+        if (xn_out) for (int i = threadIdx.x; i < n / 4; i += blockDim.x) ((float4*)(xn_out + r * n))[i] = ((const float4*)xn)[i];
+        return;
+    }
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     for (int b = wid; b < n / 32; b += nw) {
         float v = xn[b * 32 + lane], d;
