@@ -176,6 +176,11 @@ int  itb_engine_create_ep(itb_model*, uint32_t n_ctx, uint32_t n_seq, const uint
 void itb_engine_destroy(itb_engine*);
 void itb_engine_reset(itb_engine*);                                               /* src/engine/mod.rs:296-308 */
 uint32_t itb_engine_pos(itb_engine*, uint32_t seq);
+/* Engine::checkpoint / restore (src/engine/mod.rs:255-294): positions + recurrent state of every sequence into a host buffer of
+ * itb_engine_checkpoint_bytes; restore returns the engine to it (the KV cache is simply truncated to the saved positions). */
+size_t itb_engine_checkpoint_bytes(itb_engine*);
+int  itb_engine_checkpoint(itb_engine*, void* out, size_t cap);
+int  itb_engine_restore(itb_engine*, const void* data, size_t bytes);
 /* Engine::prefill (src/engine/mod.rs:352-356) for every sequence in lockstep: tokens [n_seq][n] host ids in,
  * logits of each sequence's last token out, [n_seq][n_vocab] (may be NULL). */
 int  itb_engine_prefill(itb_engine*, const uint32_t* tokens, size_t n, float* logits_out);

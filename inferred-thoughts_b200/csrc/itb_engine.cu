@@ -1093,6 +1093,45 @@ extern "C" void itb_engine_reset(itb_engine* e) {
     cudaStreamSynchronize(st);
     std::fill(e->host_pos.begin(), e->host_pos.end(), 0u);
 }
+// Engine::checkpoint / restore (src/engine/mod.rs:255-294): the positions plus the recurrent state (conv windows and
+// delta-rule state of every sequence). The KV cache needs no copy: positions past the checkpoint are no longer part of
+// the sequence and the next tokens overwrite them. Layout: u32 magic, u32 n_seq, u32 pos[n_seq], conv f32[], ssm f32[].
+static size_t ckpt_conv_floats(const itb_engine* e) {
+    const itb_model_dims& d = e->m->d;
+    const size_t cd = 2 * (size_t)d.ssm_d_state * d.ssm_n_group + d.ssm_d_inner;
+    return (size_t)e->n_rec * e->B * cd * (d.ssm_d_conv - 1);
+}
+static size_t ckpt_ssm_floats(const itb_engine* e) {
+    const itb_model_dims& d = e->m->d;
+    return (size_t)e->n_rec * e->B * d.ssm_dt_rank * d.ssm_d_state * d.ssm_d_state;
+}
+extern "C" size_t itb_engine_checkpoint_bytes(itb_engine* e) { return 8 + (size_t)e->B * 4 + (ckpt_conv_floats(e) + ckpt_ssm_floats(e)) * 4; }
+extern "C" int itb_engine_checkpoint(itb_engine* e, void* out, size_t cap) {
+    itb_ctx* c = e->c;
+    if (cap < itb_engine_checkpoint_bytes(e)) { itb_fail_msg(c, "checkpoint: buffer too small"); return 1; }
+    uint32_t* h = (uint32_t*)out;
+    h[0] = 0x4b435449u; h[1] = e->B;
+    for (uint32_t b = 0; b < e->B; ++b) h[2 + b] = e->host_pos[b];
+    float* f = (float*)(h + 2 + e->B);
+    ITB_CUDA_RET(c, cudaMemcpyAsync(f, e->conv_state, ckpt_conv_floats(e) * 4, cudaMemcpyDeviceToHost, c->stream), 1);
+    ITB_CUDA_RET(c, cudaMemcpyAsync(f + ckpt_conv_floats(e), e->ssm_state, ckpt_ssm_floats(e) * 4, cudaMemcpyDeviceToHost, c->stream), 1);
+    ITB_CUDA_RET(c, cudaStreamSynchronize(c->stream), 1);
+    return 0;
+}
+extern "C" int itb_engine_restore(itb_engine* e, const void* data, size_t bytes) {
+    itb_ctx* c = e->c;
+    const uint32_t* h = (const uint32_t*)data;
+    if (bytes != itb_engine_checkpoint_bytes(e) || h[0] != 0x4b435449u || h[1] != e->B) { itb_fail_msg(c, "restore: not a checkpoint of an engine of this shape"); return 1; }
+    for (uint32_t b = 0; b < e->B; ++b)
+        if (h[2 + b] > e->n_ctx) { itb_fail_msg(c, "restore: the checkpoint stands past this engine's context"); return 1; }   // src/engine/mod.rs:276-281
+    const float* f = (const float*)(h + 2 + e->B);
+    ITB_CUDA_RET(c, cudaMemcpyAsync(e->pos, h + 2, (size_t)e->B * 4, cudaMemcpyHostToDevice, c->stream), 1);
+    ITB_CUDA_RET(c, cudaMemcpyAsync(e->conv_state, f, ckpt_conv_floats(e) * 4, cudaMemcpyHostToDevice, c->stream), 1);
+    ITB_CUDA_RET(c, cudaMemcpyAsync(e->ssm_state, f + ckpt_conv_floats(e), ckpt_ssm_floats(e) * 4, cudaMemcpyHostToDevice, c->stream), 1);
+    ITB_CUDA_RET(c, cudaStreamSynchronize(c->stream), 1);
+    for (uint32_t b = 0; b < e->B; ++b) e->host_pos[b] = h[2 + b];
+    return 0;
+}
 extern "C" uint32_t itb_engine_pos(itb_engine* e, uint32_t seq) { return seq < e->B ? e->host_pos[seq] : 0; }
 extern "C" float itb_engine_last_ms(itb_engine* e) { return e->last_ms; }
 extern "C" uint64_t itb_engine_launches_per_step(itb_engine* e) { return e->launches_per_step; }

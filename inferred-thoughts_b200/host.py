@@ -364,6 +364,18 @@ class Engine:
         if rc:
             self.model.ops.check(); raise RuntimeError(f"{what} failed ({rc})")
 
+    def checkpoint(self):
+        """Positions + recurrent state as bytes (src/engine/mod.rs:255-270); the KV cache needs no copy."""
+        self.L.itb_engine_checkpoint_bytes.restype = C.c_size_t
+        n = self.L.itb_engine_checkpoint_bytes(self.h)
+        buf = np.zeros(n, np.uint8)
+        self._chk(self.L.itb_engine_checkpoint(self.h, _p(buf), SZ(n)), "checkpoint")
+        return buf
+
+    def restore(self, ckpt):
+        buf = np.ascontiguousarray(ckpt, np.uint8)
+        self._chk(self.L.itb_engine_restore(self.h, _p(buf), SZ(buf.size)), "restore")
+
     def tier_stats(self):
         out = (C.c_uint64 * 4)()
         self.L.itb_engine_tier_stats(self.h, out)

@@ -374,6 +374,31 @@ def test_benchmark_mode_bf16_kv_and_tree_dots_stays_within_tolerance(oracle):
     e1.close(); e2.close(); model.close(); ops.close()
 
 
+def test_checkpoint_restore_replays_the_same_tokens(oracle, gpu):
+    """Engine::checkpoint / restore (src/engine/mod.rs:255-294 there): save after the prompt, decode, go back, decode again:
+    same logits bit for bit; a checkpoint of another shape is refused."""
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 128, 2)
+    prompts = np.stack([prompt_ids(50 + i, 20, TINY["n_vocab"]) for i in range(2)])
+    first = np.argmax(eng.prefill(prompts), 1).astype(np.uint32)
+    ck = eng.checkpoint()
+    run1, t = [], first
+    for _ in range(5):
+        lg, t = eng.decode(t); run1.append(lg.copy())
+    assert eng.pos(0) == 25
+    eng.restore(ck)
+    assert eng.pos(0) == 20 and eng.pos(1) == 20
+    t = first
+    for i in range(5):
+        lg, t = eng.decode(t)
+        assert lg.view(np.uint32).tolist() == run1[i].view(np.uint32).tolist(), i
+    other = host.Engine(model, 128, 1)
+    with pytest.raises(RuntimeError):
+        other.restore(ck)
+    other.close(); eng.close()
+
+
 def test_context_overflow_is_refused_before_any_write(oracle, gpu):
     from inferred_thoughts_b200 import host
     ops, model = gpu
