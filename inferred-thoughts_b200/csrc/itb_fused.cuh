@@ -609,7 +609,7 @@ template <int RP>
 __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_el[16];
-    __shared__ float s_wt[16], s_s2[16];
+    __shared__ float s_wt[16];
     __shared__ float s_g;
     __shared__ int s_loc[16], s_nloc;        // picks whose expert is stored here, in pick order (expert-parallel pairs mode)
     const int ff = p.ff, sff = p.sff, nbf = ff / 32, nbs = sff / 32, nsb = ff / 16;
@@ -642,7 +642,6 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
         int el = p.ids[(size_t)b * p.n_used + tid] - p.down.expert_lo;
         s_el[tid] = (el < 0 || el >= p.down.n_expert) ? -1 : el;
         s_wt[tid] = p.wts[(size_t)b * p.n_used + tid];
-        s_s2[tid] = (p.down.scale2 && s_el[tid] >= 0) ? p.down.scale2[s_el[tid]] : 1.0f;
     }
     if (tid == 32 && !pairs) s_g = sigmoid_f(p.logit[b]);
     __syncthreads();
@@ -651,6 +650,8 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     TL(TLK_MOE_DOWN, 2);
     const bool has_s = p.down.scale2 != nullptr;
     float* x = p.x + (size_t)b * p.x_stride;
+    // lane k keeps pick k's second scale; the load is issued here and first used after the row dots, so it costs no round trip
+    const float s2k = (has_s && lane < p.n_used && s_el[lane] >= 0) ? p.down.scale2[s_el[lane]] : 1.0f;
 #pragma unroll 1
     for (int row = b0 + r0; row < b0 + r1; ++row) {
         // routed picks: item k = pick k of this row (pairs mode: the k-th LOCAL pick, so no row of an absent expert is read)
@@ -676,7 +677,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
             }
             __syncwarp();
             if (lane < p.n_used && s_el[lane] >= 0)
-                p.o_pairs[((size_t)b * p.n_used + lane) * n_out + row] = has_s ? outv[lane] * s_s2[lane] : outv[lane];
+                p.o_pairs[((size_t)b * p.n_used + lane) * n_out + row] = has_s ? outv[lane] * s2k : outv[lane];
             __syncwarp();
             continue;
         }
@@ -690,12 +691,13 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
                 [&](int, float v) { outv[31] = v; });
         }
         __syncwarp();
+        if (has_s && lane < p.n_used) outv[lane] = outv[lane] * s2k;
+        __syncwarp();
         if (lane == 0) {
             float acc = 0.0f;                                   // experts in pick order from zero, shared last
             for (int k = 0; k < p.n_used; ++k) {
                 if (s_el[k] < 0) continue;
-                float o = has_s ? outv[k] * s_s2[k] : outv[k];
-                acc += s_wt[k] * o;
+                acc += s_wt[k] * outv[k];
             }
             if (p.local_only) p.partial[(size_t)b * n_out + row] = acc;
             else { sh = outv[31]; acc += sh * s_g; x[row] += acc; }
