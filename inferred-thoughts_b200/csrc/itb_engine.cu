@@ -519,6 +519,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         set_smem((const void*)k_moe_glu, 100 * 1024);
         set_smem((const void*)k_moe_down<1>, 100 * 1024); set_smem((const void*)k_moe_down<2>, 100 * 1024);
         set_smem((const void*)k_moe_down<4>, 100 * 1024); set_smem((const void*)k_moe_down<8>, 100 * 1024);
+        set_smem((const void*)k_moe_down<1, true>, 100 * 1024); set_smem((const void*)k_moe_down<2, true>, 100 * 1024);
+        set_smem((const void*)k_moe_down<4, true>, 100 * 1024); set_smem((const void*)k_moe_down<8, true>, 100 * 1024);
         set_smem((const void*)k_gdn_core<128>, 100 * 1024); set_smem((const void*)k_gdn_core<64>, 100 * 1024);
         attrs_set = true;
     }
@@ -640,7 +642,12 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             dim3 grid(std::max(1, std::min(sms, (H + NWG - 1) / NWG)), RW);
             w.tl_slot = tl++;
             size_t smem_d = moe_down_smem(d.n_expert_used, d.expert_ff, d.shared_ff, rp);
-            if (rp == 1) launch_k(pdl, k_moe_down<1>, grid, TPB, smem_d, st, w);
+            if (e->ep) {
+                if (rp == 1) launch_k(pdl, k_moe_down<1, true>, grid, TPB, smem_d, st, w);
+                else if (rp == 2) launch_k(pdl, k_moe_down<2, true>, grid, TPB, smem_d, st, w);
+                else if (rp == 4) launch_k(pdl, k_moe_down<4, true>, grid, TPB, smem_d, st, w);
+                else launch_k(pdl, k_moe_down<8, true>, grid, TPB, smem_d, st, w);
+            } else if (rp == 1) launch_k(pdl, k_moe_down<1>, grid, TPB, smem_d, st, w);
             else if (rp == 2) launch_k(pdl, k_moe_down<2>, grid, TPB, smem_d, st, w);
             else if (rp == 4) launch_k(pdl, k_moe_down<4>, grid, TPB, smem_d, st, w);
             else launch_k(pdl, k_moe_down<8>, grid, TPB, smem_d, st, w);

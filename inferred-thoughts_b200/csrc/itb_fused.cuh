@@ -605,7 +605,7 @@ struct MoeDown {
     float* o_pairs; int own_row; float* shd;
     int tl_slot;
 };
-template <int RP>
+template <int RP, bool PAIRS = false>
 __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int s_el[16];
@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
     TL(TLK_MOE_DOWN, 1);
     for (int i = tid; i < p.n_used * ff / 16; i += blockDim.x) ((uint4*)hq)[i] = ((const uint4*)(p.hq + (size_t)b * p.n_used * ff))[i];
     for (int i = tid; i < p.n_used * nbf; i += blockDim.x) hs[i] = p.hs[(size_t)b * p.n_used * nbf + i];
-    const bool pairs = p.o_pairs != nullptr;
+    constexpr bool pairs = PAIRS;            // compile-time: the one-GPU kernel carries none of the expert-parallel branches
     const size_t shb = pairs ? 0 : (size_t)b;        // where this row's shared-expert activation and gate logit sit
     if (!pairs || b == p.own_row) {
         for (int i = tid; i < sff / 16; i += blockDim.x) ((uint4*)sq)[i] = ((const uint4*)(p.sq + shb * sff))[i];
