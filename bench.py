@@ -86,28 +86,81 @@ def prompts(batch, seed, n_vocab):
     return np.stack([np.random.default_rng(seed + i).integers(0, n_vocab, PROMPT).astype(np.uint32) for i in range(batch)])
 
 
-def cpu_oracle_tok_s(model, dims, seed, budget_s, threads):
-    """The CPU oracle (C++ restatement of the reference CPU path) on the same weights, copied back from the device.
-    Bounded sample: decode tokens from an empty context until about `budget_s` seconds of CPU work are spent."""
+def bench_config(args, world):
+    """The `config` object of the JSON line: what both arms (product and --impl reference) run, key for key."""
+    B = args.batch
+    return {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}" if args.model == "m35b" else f"cfg5-decode-177B-shape-bs{B}",
+            "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": "bf16", "parallelism": "replicas" if world > 1 else "single",
+            "l2": "each step streams ~2.8 GB of weights, far beyond the 126 MB L2; no flush needed",
+            **({"layers": args.layers, "not_a_bench_number": True} if args.layers else {})}
+
+
+def load_oracle(model, dims, seed):
+    """The CPU oracle (C++ restatement of the reference CPU path) holding the same weights, copied back from the device
+    generator (bit-identical to the CPU generator, and minutes faster for 35 B parameters)."""
     from oracle import oracle_py as O
     om = O.OracleModel(O.ModelDims(**dims))
     t0 = time.time()
     for s in om.specs:
         data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
         om.set_tensor(s["name"], data, sc)
-    load_s = time.time() - t0
+    return om, time.time() - t0
+
+
+def cpu_decode_tok_s(om, dims, seed, threads, prompt, warmup, steps, budget_s=None):
+    """Decode tokens on the CPU oracle after the same `prompt` the product arm uses, KV in bf16 as there. Timed: `steps`
+    greedy tokens (cut short after `budget_s` seconds when given); untimed: the prompt pass and `warmup` tokens."""
+    from oracle import oracle_py as O
     O.lib().orc_set_threads(threads)
-    om.begin(64)
-    rng = np.random.default_rng(seed)
-    n, t0 = 0, time.time()
-    tok = int(rng.integers(0, dims["n_vocab"]))
-    while True:
-        logits = om.forward([tok]); n += 1
-        tok = int(np.argmax(logits))
-        if time.time() - t0 > budget_s or n >= 48:
+    om.begin(len(prompt) + warmup + steps + 8, kv_bf16=True)
+    t0 = time.perf_counter()
+    tok = int(np.argmax(om.forward(prompt)))
+    prefill_s = time.perf_counter() - t0
+    for _ in range(warmup):
+        tok = int(np.argmax(om.forward([tok])))
+    n, t0 = 0, time.perf_counter()
+    while n < steps:
+        tok = int(np.argmax(om.forward([tok]))); n += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
             break
-    dt = time.time() - t0
-    return n / dt, n, load_s
+    dt = time.perf_counter() - t0
+    return n / dt, n, dt, prefill_s
+
+
+def parity_check(host, model, om, dims, seed, mode, n_prompt=16, n_new=16):
+    """The timed path against the CPU oracle IN THE BENCH'S OWN MODE (`mode`: the ops string of the timed engine): a short
+    prompt in one multi-row pass, then n_new teacher-forced decode steps through the fused one-token step (the oracle's
+    greedy token goes to both sides, tests/cuda_ops.rs:544-626 in the reference). Reports whether every greedy choice agrees,
+    the first divergence with the oracle's top-2 margin there (src/profile.rs:88-93), routing-id mismatches over every
+    layer and step, and the logit distance."""
+    from oracle import oracle_py as O
+    O.lib().orc_set_threads(O.lib().orc_hw_threads())
+    L, K = dims["n_layer"], dims["n_expert_used"]
+    prompt = np.random.default_rng(seed + 11).integers(0, dims["n_vocab"], n_prompt).astype(np.uint32)
+    eng = host.Engine(model, n_prompt + n_new + 8, 1)
+    om.begin(n_prompt + n_new + 8, kv_bf16="kv=bf16" in mode, log_routes=True)
+    o = om.forward(prompt); g = eng.prefill(prompt)
+    mism = int((eng.read_routes(L, K)[:, 0, :] != om.route_log().reshape(L, n_prompt, K)[:, -1, :]).sum())
+    compared = L * K
+    first_div, margin, max_abs, min_cos = None, None, 0.0, 1.0
+    for step in range(n_new + 1):
+        max_abs = max(max_abs, float(np.abs(o - g).max()))
+        a, b = o.astype(np.float64), g.astype(np.float64)
+        min_cos = min(min_cos, float(a @ b / (np.linalg.norm(a) * np.linalg.norm(b) + 1e-300)))
+        t = int(np.argmax(o))
+        if int(np.argmax(g)) != t and first_div is None:
+            top2 = np.partition(o, -2)[-2:]
+            first_div, margin = step, float(top2[1] - top2[0])
+        if step == n_new:
+            break
+        om.clear_route_log()
+        o = om.forward([t])
+        lg, _ = eng.decode([t]); g = lg[0]
+        mism += int((eng.read_routes(L, K)[:, 0, :] != om.route_log().reshape(L, K)).sum()); compared += L * K
+    eng.close()
+    return {"mode": mode, "against": "CPU oracle (port of the reference CPU path), same weights", "prompt": n_prompt, "tokens": n_new + 1,
+            "tokens_equal": first_div is None, "first_divergence": first_div, "oracle_top2_margin_at_divergence": margin,
+            "routing_id_mismatches": mism, "routing_ids_compared": compared, "logits_max_abs": max_abs, "logits_min_cosine": min_cos}
 
 
 def kernel_breakdown(eng, tok):
@@ -220,12 +273,14 @@ def other_configs(host, model, dims, seed, hbm, args):
         steps = 32
         eng.decode_loop(first, steps)
         ms = eng.last_ms() / steps
-        # distinct experts per layer under this run's routing are not read back; uniform-routing expectation E(1-(1-K/E)^B)
-        E, K = dims["n_expert"], dims["n_expert_used"]
-        distinct = int(round(E * (1 - (1 - K / E) ** B)))
+        # distinct experts per layer from this run's routing (the last step's ids, every layer), not a formula
+        K = dims["n_expert_used"]
+        routes = eng.read_routes(dims["n_layer"], K)
+        per_layer = [len(set(routes[il].reshape(-1).tolist())) for il in range(dims["n_layer"])]
+        distinct = int(round(float(np.mean(per_layer))))
         by = model.decode_bytes(B, eng.pos(0), distinct)
         out["decode_bs32"] = {"value": B / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms, "algorithmic_bytes_per_step": by,
-                              "frac_of_hbm": by / ms / 1e6 / hbm, "distinct_experts_assumed": distinct}
+                              "frac_of_hbm": by / ms / 1e6 / hbm, "distinct_experts_per_layer_measured": {"mean": float(np.mean(per_layer)), "min": min(per_layer), "max": max(per_layer)}}
         eng.close()
     except Exception as ex:
         out["decode_bs32"] = {"error": str(ex)}
@@ -272,7 +327,8 @@ def run_product(args, rank, world):
         dims = configs.with_layers(dims, args.layers)   # profiling aid only: a line with "layers" set is not a bench number
     seed = configs.SEEDS[args.model]
     kv = "bf16"
-    ops = host.B200Ops(device, f"kv={kv},exact={args.exact}")
+    mode = f"kv={kv},exact={args.exact}"
+    ops = host.B200Ops(device, mode)
     model = host.Model(ops, host.ModelDims(**dims))
     t0 = time.time()
     model.synth(seed)
@@ -330,9 +386,8 @@ def run_product(args, rank, world):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "u8 (int8 x int8 / e2m1 x int8 dots, f32 accumulate; f32 state)",
         "data": "synthetic (seeded Gaussian weights quantised to NVFP4 / Q8_0, uniform-random token ids)",
-        "config": {"workload": f"cfg3-decode-35B-A3B-shape-bs{B}" if args.model == "m35b" else f"cfg5-decode-177B-shape-bs{B}", "batch_per_gpu": B, "prompt": PROMPT, "n_ctx": N_CTX, "kv": kv,
-                   "n_pos_at_end": n_pos, **({"layers": args.layers, "not_a_bench_number": True} if args.layers else {}), "f32_dots": "serial-k" if args.exact else "tree", "parallelism": "replicas" if world > 1 else "single",
-                   "l2": "each step streams ~2.8 GB of weights, far beyond the 126 MB L2; no flush needed"},
+        "config": bench_config(args, world),
+        "run": {"n_pos_at_end": n_pos, "f32_dots": "serial-k" if args.exact else "tree", "ops": mode},
         "e2e": {"value": world * B * args.steps / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                 "api": "itb_engine_decode (host token ids in, host argmax ids out)"},
         "gpu_launches": int(eng.launches_per_step()) * args.steps * 2,
@@ -355,12 +410,21 @@ def run_product(args, rank, world):
         except Exception as ex:
             line["other_configs"]["experts_microbench_cfg2"] = {"error": str(ex)}
     if world == 1 and not args.no_cpu:
+        om = None
         try:
             from oracle import oracle_py as O
             threads = O.lib().orc_hw_threads()
-            v, n, load_s = cpu_oracle_tok_s(model, dims, seed, args.cpu_budget, threads)
+            om, load_s = load_oracle(model, dims, seed)
+            line["parity"] = parity_check(host, model, om, dims, seed, mode)
+        except Exception as ex:
+            line["parity"] = {"error": str(ex)}
+        try:
+            if om is None:
+                raise RuntimeError("the oracle could not be loaded")
+            v, n, dt, prefill_s = cpu_decode_tok_s(om, dims, seed, threads, pr[0], 1, 48, args.cpu_budget)
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": f"{n} decode tokens from an empty context, same weights (copied back from the device in {load_s:.0f} s), batch 1"}
+                                    "sample": f"{n} decode tokens ({dt:.1f} s) after the same {len(pr[0])}-token prompt (CPU prompt pass {prefill_s:.0f} s, untimed), "
+                                              f"same weights (copied back from the device in {load_s:.0f} s), batch 1, bf16 KV"}
         except Exception as ex:  # the baseline is a report, never a reason to lose the measurement
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
     emit(line)
@@ -369,46 +433,117 @@ def run_product(args, rank, world):
 
 def run_reference(args, rank, world):
     """The reference's CPU path (its algorithm, restated in C++: the reference itself is Rust and cannot be built here)
-    on the host cores, on the same config and metric. Weights come from the device generator when a GPU is there
-    (bit-identical to the CPU generator, and minutes faster for 35 B parameters), else from the CPU generator."""
+    on the host cores, on the product arm's config and metric: the same 512-token prompt (seed and all), bf16 KV, then
+    `warmup` untimed and `steps` timed greedy decode tokens. The weights come from the library's device generator when a GPU
+    is there -- outside the timed region, and tested equal to the CPU generator byte for byte -- else from the CPU generator."""
     if rank != 0:
         return
     from oracle import oracle_py as O
-    dims = dict(configs.M35B)
-    seed = configs.SEEDS["m35b"]
+    dims = dict(configs.L177B if args.model == "l177b" else configs.M35B)
+    if args.layers:
+        dims = configs.with_layers(dims, args.layers)
+    seed = configs.SEEDS[args.model]
     threads = O.lib().orc_hw_threads()
-    om = O.OracleModel(O.ModelDims(**dims))
     src = "cpu generator"
+    om = None
     try:
         from inferred_thoughts_b200 import host
         ops = host.B200Ops(0)
         model = host.Model(ops, host.ModelDims(**dims))
-        for s in om.specs:
-            data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
-            om.set_tensor(s["name"], data, sc)
+        om, _ = load_oracle(model, dims, seed)
         model.close(); ops.close()
         src = "device generator, copied to the host"
     except Exception:
+        om = O.OracleModel(O.ModelDims(**dims))
         om.synth(seed, threads)
-    O.lib().orc_set_threads(threads)
-    om.begin(64 + args.steps + args.warmup)
-    tok = 1
-    for _ in range(args.warmup):
-        tok = int(np.argmax(om.forward([tok])))
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        tok = int(np.argmax(om.forward([tok])))
-    dt = time.perf_counter() - t0
-    v = args.steps / dt
+    pr = prompts(args.batch, seed, dims["n_vocab"])[0]        # rank 0's first sequence, as in the product arm
+    v, n, dt, prefill_s = cpu_decode_tok_s(om, dims, seed, threads, pr, args.warmup, args.steps)
     emit({
-        "impl": "reference", "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)", "value": v, "unit": "tok/s",
-        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": f"synthetic ({src})",
-        "config": {"workload": "cfg3-decode-35B-A3B-shape-bs1", "batch_per_gpu": 1, "n_ctx": N_CTX, "sample": "decode tokens from an empty context"},
+        "impl": "reference", "metric": "decode tok/s, 35B-A3B-shape NVFP4 (BASELINE.json config 3)" if args.model == "m35b" else "decode tok/s, ~177B-shape NVFP4 (BASELINE.json config 5)",
+        "value": v, "unit": "tok/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / n * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u8 (int8 x int8 / e2m1 x int8 dots, f32 accumulate; f32 state)",
+        "data": f"synthetic (seeded Gaussian weights quantised to NVFP4 / Q8_0, uniform-random token ids; weights from the {src})",
+        "config": bench_config(args, world),
+        "run": {"n_pos_at_end": len(pr) + args.warmup + n, "f32_dots": "serial-k", "prompt_pass_s": prefill_s},
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": f"{args.steps} decode tokens from an empty context after {args.warmup} warm-up tokens"},
+                         "sample": f"{n} decode tokens after the {len(pr)}-token prompt and {args.warmup} warm-up tokens, one sequence"},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     })
+
+
+def run_probe(args):
+    """One pass of the engine inside a CUDA profiler range (for `ncu --profile-from-start off`), on the benchmark's shape with
+    --layers layers (default 8: about 5 GB on the device, small enough for a multi-pass capture). Prints the pass's device
+    time to stderr; never a bench line."""
+    import torch
+    from inferred_thoughts_b200 import host
+    mode, _, n = args.probe.partition(":")
+    n = int(n or 1)
+    dims = configs.with_layers(dict(configs.L177B if args.model == "l177b" else configs.M35B), args.layers or 8)
+    ops = host.B200Ops(0, f"kv=bf16,exact={args.exact}")
+    model = host.Model(ops, host.ModelDims(**dims)); model.synth(configs.SEEDS[args.model])
+    rng = np.random.default_rng(3)
+    if mode == "decode":
+        eng = host.Engine(model, 2048, n)
+        eng.prefill(rng.integers(0, dims["n_vocab"], (n, 64)).astype(np.uint32), want_logits=False)
+        t = eng.decode_loop(np.zeros(n, np.uint32), 2)[-1]
+        torch.cuda.synchronize(); torch.cuda.profiler.start()
+        eng.decode_loop(t, 1)
+        torch.cuda.synchronize(); torch.cuda.profiler.stop()
+    elif mode == "prefill":
+        eng = host.Engine(model, 2048, 1)
+        pr = rng.integers(0, dims["n_vocab"], n).astype(np.uint32)
+        eng.prefill(pr[:32], want_logits=False); eng.reset()
+        torch.cuda.synchronize(); torch.cuda.profiler.start()
+        eng.prefill(pr, want_logits=False)
+        torch.cuda.synchronize(); torch.cuda.profiler.stop()
+    elif mode in ("step", "timeline"):
+        eng = host.Engine(model, max(2048, n + 64), 1)
+        eng.prefill((np.arange(n, dtype=np.uint32) * 7919) % dims["n_vocab"], want_logits=False)
+        t = eng.decode_loop([1], 8)[-1]
+        if mode == "timeline":
+            print_timeline(eng, dims, t)
+        else:
+            torch.cuda.synchronize(); torch.cuda.profiler.start()
+            eng.decode_loop(t, 1)
+            torch.cuda.synchronize(); torch.cuda.profiler.stop()
+    else:
+        raise SystemExit("--probe: decode:N | prefill:N | step:N | timeline:N")
+    print(f"{mode} {n}: {eng.last_ms():.3f} ms", file=sys.stderr)
+    eng.close(); model.close(); ops.close()
+
+
+TIMELINE_KERNELS = {2: "k_in_proj", 3: "k_gdn_core", 4: "k_out_proj", 5: "k_attn_prep", 8: "k_moe_glu", 9: "k_moe_down"}
+
+
+def print_timeline(eng, dims, tok):
+    """itb_timeline_arm / itb_timeline_read around one step: per structured launch, the time from one phase mark to the next
+    on block 0 (us), and from the previous launch's last mark to this one's first mark after its dependency wait (the gap)."""
+    import collections
+    L = eng.L
+    L.itb_timeline_read.restype = C.c_long
+    slots = 8 * dims["n_layer"] + 8
+    assert L.itb_timeline_arm(eng.h, slots) == 0
+    eng.decode_loop(tok, 1)
+    words = np.zeros(slots * 16, np.uint64)
+    L.itb_timeline_read(eng.h, C.c_void_p(words.ctypes.data), slots)
+    L.itb_timeline_arm(eng.h, 0)
+    agg = collections.OrderedDict()
+    prev_last = None
+    for w in words.reshape(slots, 16):
+        marks = {i: int(v) >> 8 for i, v in enumerate(w) if v}
+        if not marks:
+            continue
+        name = TIMELINE_KERNELS.get(int(w[w != 0][0]) & 255, "?")
+        order = sorted(marks.items(), key=lambda x: x[1])
+        for (i, a), (j, b) in zip(order, order[1:]):
+            agg.setdefault((name, f"phase {i}->{j}"), []).append((b - a) / 1e3)
+        if prev_last is not None and 1 in marks:
+            agg.setdefault((name, "gap before"), []).append((marks[1] - prev_last) / 1e3)
+        prev_last = max(marks.values())
+    for (name, what), v in sorted(agg.items()):
+        print(f"{name:12s} {what:14s} n={len(v):3d} mean {np.mean(v):6.2f} us  min {np.min(v):6.2f}  max {np.max(v):6.2f}", file=sys.stderr)
 
 
 _JSON_FD = None
@@ -433,6 +568,9 @@ def main():
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens before the timed decode steps (BASELINE: 512)")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
     ap.add_argument("--model", default="m35b", choices=["m35b", "l177b"], help="m35b: the headline 35B-A3B shape; l177b: BASELINE config 5's ~177B shape")
+    ap.add_argument("--probe", default="", help="profiler aid, prints no bench line: 'decode:N' one batched decode step of N sequences, 'prefill:N' one pass of "
+                    "N prompt rows, 'step:N' one fused one-token step at N positions, each inside a CUDA profiler range (ncu --profile-from-start off); "
+                    "'timeline:N' the per-stage timeline of one step at N positions. Use with --layers.")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: the same shape with fewer layers (small device footprint for ncu captures)")
     args = ap.parse_args()
     # Libraries print banners on stdout (NCCL's version line, for one); stdout must carry the JSON line alone, so everything
@@ -444,7 +582,9 @@ def main():
     global PROMPT
     PROMPT = args.prompt
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-    if args.impl == "reference":
+    if args.probe:
+        run_probe(args)
+    elif args.impl == "reference":
         args.steps = min(args.steps, 256)   # a CPU step is a whole 2.8 GB token: keep the run within minutes
         run_reference(args, rank, world)
     else:

@@ -212,7 +212,9 @@ int  itb_engine_profile_step(itb_engine*, const uint32_t* tokens, itb_kernel_sta
  * [n_head*head_dim] f32; `stream` is a cudaStream_t (NULL = default stream). One query row attends over
  * positions [0, n_pos). The split-K partials live in a fixed ~2.1 MB array inside the library (held by every
  * GPU that loads it until the process exits); limits: n_head <= 64, head_dim in {64,128,256}, at most 8 query
- * heads per KV head -- anything beyond is refused with a message in `err`. The first call on a device looks the
+ * heads per KV head -- anything beyond is refused with a message in `err`. Alignment (also checked): kv_dim a
+ * multiple of head_dim/32 elements, k/v aligned to 2*(head_dim/32) bytes, q/out to 4 bytes. One host thread at a time,
+ * like every other entry point. The first call on a device looks the
  * array's address up: make it with that device current and before any stream capture. Calls share the array, so
  * calls that overlap on the GPU race; issue them one after the other. Returns 0, or 1 with `err` filled. */
 int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t* k_dev, const uint16_t* v_dev,

@@ -290,27 +290,37 @@ const WeightEntry* itb_weight(itb_ctx* c, const uint8_t* data, size_t bytes, uin
     cudaError_t e = cudaMalloc(&raw, want);
     if (e != cudaSuccess) { itb_fail(c, "cudaMalloc(weight staging)", e); return nullptr; }
     cudaMemcpyAsync(raw, data, want, cudaMemcpyHostToDevice, c->stream);
+    // Every plane is allocated before any kernel runs; on a failure everything allocated so far is given back and the
+    // caller gets "out of device memory" instead of a kernel writing through a null pointer.
+    const bool want_s2 = scale && scale_bytes >= n_expert * 4;
+    const size_t a_bytes = ty == ITB_F32 ? 0 : ty == ITB_F16 ? elems * 4 : ty == ITB_Q8_0 ? elems : elems / 2;
+    const size_t b_bytes = ty == ITB_Q8_0 ? elems / 32 * 2 : ty == ITB_NVFP4 ? elems / 16 : 0;
+    bool oom = false;
+    if (a_bytes && cudaMalloc(&w.a, a_bytes) != cudaSuccess) { w.a = nullptr; oom = true; }
+    if (!oom && b_bytes && cudaMalloc(&w.b, b_bytes) != cudaSuccess) { w.b = nullptr; oom = true; }
+    if (!oom && want_s2 && cudaMalloc(&w.scale2, n_expert * 4) != cudaSuccess) { w.scale2 = nullptr; oom = true; }
+    if (oom) {
+        cudaStreamSynchronize(c->stream);
+        cudaFree(raw); cudaFree(w.a); cudaFree(w.b); cudaFree(w.scale2);
+        cudaGetLastError();
+        itb_fail_msg(c, "weight: out of device memory");
+        return nullptr;
+    }
     if (ty == ITB_F32) { w.a = raw; raw = nullptr; w.bytes = want; }
     else if (ty == ITB_F16) {
-        cudaMalloc(&w.a, elems * 4);
         itb_f16_to_f32(c->stream, (const uint16_t*)raw, (float*)w.a, elems);
         w.bytes = elems * 4;
     } else if (ty == ITB_Q8_0) {
-        cudaMalloc(&w.a, elems); cudaMalloc(&w.b, elems / 32 * 2);
         itb_repack_q8(c->stream, raw, (int8_t*)w.a, (uint16_t*)w.b, elems / 32);
         w.bytes = elems + elems / 16;
     } else {
-        cudaMalloc(&w.a, elems / 2); cudaMalloc(&w.b, elems / 16);
         itb_repack_fp4(c->stream, raw, (uint8_t*)w.a, (uint8_t*)w.b, elems / 64);
         w.bytes = elems / 2 + elems / 16;
     }
-    if (scale && scale_bytes >= n_expert * 4) {
-        cudaMalloc(&w.scale2, n_expert * 4);
-        cudaMemcpyAsync(w.scale2, scale, n_expert * 4, cudaMemcpyHostToDevice, c->stream);
-    }
+    if (want_s2) cudaMemcpyAsync(w.scale2, scale, n_expert * 4, cudaMemcpyHostToDevice, c->stream);
     e = cudaStreamSynchronize(c->stream);
     if (raw) cudaFree(raw);
-    if (e != cudaSuccess) { itb_fail(c, "weight upload", e); return nullptr; }
+    if (e != cudaSuccess) { cudaFree(w.a); cudaFree(w.b); cudaFree(w.scale2); itb_fail(c, "weight upload", e); return nullptr; }
     c->weight_bytes += w.bytes;
     return &c->weights.emplace(data, w).first->second;
 }

@@ -99,12 +99,18 @@ static int adopt_raw(itb_model* m, const std::string& name, uint32_t ty, size_t 
     DevTensor t;
     t.ty = ty; t.n_in = n_in; t.n_out = n_out; t.n_expert = n_expert; t.e_lo = e_lo; t.e_cnt = e_cnt;
     size_t elems = n_in * n_out * e_cnt;
+    // both planes or neither: a failed second allocation gives the first one back, and nothing is launched
+    auto two = [&](size_t a_bytes, size_t b_bytes) {
+        if (cudaMalloc(&t.a, a_bytes) != cudaSuccess) { t.a = nullptr; return itb_fail_msg(c, "model: out of device memory for " + name); }
+        if (cudaMalloc(&t.b, b_bytes) != cudaSuccess) { cudaFree(t.a); t.a = t.b = nullptr; return itb_fail_msg(c, "model: out of device memory for " + name); }
+        return true;
+    };
     if (ty == ITB_Q8_0) {
-        ITB_CUDA_RET(c, cudaMalloc(&t.a, elems), 1); ITB_CUDA_RET(c, cudaMalloc(&t.b, elems / 32 * 2), 1);
+        if (!two(elems, elems / 32 * 2)) return 1;
         itb_repack_q8(c->stream, raw, (int8_t*)t.a, (uint16_t*)t.b, elems / 32);
         t.bytes = elems + elems / 16;
     } else if (ty == ITB_NVFP4) {
-        ITB_CUDA_RET(c, cudaMalloc(&t.a, elems / 2), 1); ITB_CUDA_RET(c, cudaMalloc(&t.b, elems / 16), 1);
+        if (!two(elems / 2, elems / 16)) return 1;
         itb_repack_fp4(c->stream, raw, (uint8_t*)t.a, (uint8_t*)t.b, elems / 64);
         t.scale2 = scale2_dev;
         t.bytes = elems / 2 + elems / 16;
@@ -143,13 +149,14 @@ extern "C" int itb_model_set_tensor(itb_model* m, const char* name, uint32_t ty,
     }
     uint8_t* raw = nullptr;
     ITB_CUDA_RET(c, cudaMalloc(&raw, bytes), 1);
-    cudaMemcpyAsync(raw, data, bytes, cudaMemcpyHostToDevice, c->stream);
+    if (cudaMemcpyAsync(raw, data, bytes, cudaMemcpyHostToDevice, c->stream) != cudaSuccess) { cudaFree(raw); itb_fail_msg(c, std::string("set_tensor: upload failed for ") + name); return 1; }
     float* s2 = nullptr;
     if (ty == ITB_NVFP4 && scale && n_scale >= s->n_expert) {
-        cudaMalloc(&s2, s->n_expert * 4);
+        if (cudaMalloc(&s2, s->n_expert * 4) != cudaSuccess) { cudaStreamSynchronize(c->stream); cudaFree(raw); itb_fail_msg(c, std::string("set_tensor: out of device memory for ") + name); return 1; }
         cudaMemcpyAsync(s2, scale, s->n_expert * 4, cudaMemcpyHostToDevice, c->stream);
     }
     int rc = adopt_raw(m, name, ty, s->n_in, s->n_out, s->n_expert, 0, s->n_expert, raw, s2);
+    if (rc) cudaFree(s2);
     cudaError_t e = cudaStreamSynchronize(c->stream);
     cudaFree(raw);
     if (e != cudaSuccess) { itb_fail(c, "set_tensor", e); return 1; }
@@ -339,6 +346,7 @@ struct NcclApi {
     int (*GetUniqueId)(UniqueId*) = nullptr;
     int (*CommInitRank)(void**, int, UniqueId, int) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
+    int (*CommAbort)(void*) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
@@ -357,7 +365,7 @@ static NcclApi& nccl_api() {
     if (!h) return api;
 #define NCCL_SYM(f) *(void**)&api.f = dlsym(h, "nccl" #f)
     NCCL_SYM(GetUniqueId); NCCL_SYM(CommInitRank); NCCL_SYM(CommDestroy); NCCL_SYM(AllGather); NCCL_SYM(ReduceScatter);
-    NCCL_SYM(GroupStart); NCCL_SYM(GroupEnd); NCCL_SYM(GetErrorString);
+    NCCL_SYM(GroupStart); NCCL_SYM(GroupEnd); NCCL_SYM(GetErrorString); NCCL_SYM(CommAbort);
 #undef NCCL_SYM
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.ReduceScatter && api.GroupStart && api.GroupEnd;
     return api;
@@ -369,6 +377,8 @@ struct EpState {
     float* o_mine = nullptr;                                                // this rank's pairs after the reduce-scatter
     float* gw = nullptr;                                                    // routing weights of the gathered rows [world][n_used] (fused one-token step)
     float* grouter = nullptr;                                               // gathered router logits [world][n_expert] (fused one-token step)
+    int* agree_dev = nullptr; int* agree_host = nullptr;                    // one "this rank is ready" flag per rank (ep_agree)
+    bool broken = false;                                                    // the communicator was aborted after a failure mid-pass
 };
 
 // Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
@@ -982,7 +992,8 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
         e->ep = new EpState();
         e->ep->world = world;
         if (!(dalloc(E, &e->ep->gxq, W * R * H) && dalloc(E, &e->ep->gxs, W * R * H / 32) && dalloc(E, &e->ep->gids, W * R * K) &&
-              dalloc(E, &e->ep->o_mine, R * K * H) && dalloc(E, &e->ep->grouter, W * d.n_expert) && dalloc(E, &e->ep->gw, W * R * K))) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
+              dalloc(E, &e->ep->o_mine, R * K * H) && dalloc(E, &e->ep->grouter, W * d.n_expert) && dalloc(E, &e->ep->gw, W * R * K) &&
+              dalloc(E, &e->ep->agree_dev, W + 1) && cudaMallocHost(&e->ep->agree_host, (W + 1) * 4) == cudaSuccess)) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
     }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) { itb_fail_msg(c, "engine: device error during set-up"); return 1; }
     *out = e.release();
@@ -1081,7 +1092,7 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     if (!e) return;
     cudaStreamSynchronize(e->c->stream);
     drop_graph(e);
-    if (e->ep) { if (e->ep->comm) nccl_api().CommDestroy(e->ep->comm); delete e->ep; e->ep = nullptr; }
+    if (e->ep) { if (e->ep->comm && !e->ep->broken) nccl_api().CommDestroy(e->ep->comm); cudaFreeHost(e->ep->agree_host); delete e->ep; e->ep = nullptr; }
     if (e->tier) { cudaFreeHost(e->tier->slot_map_host); cudaFreeHost(e->tier->ids_host); cudaFreeHost(e->tier->s2_stage); delete e->tier->g; delete e->tier; e->tier = nullptr; }
     for (void* p : e->allocs) cudaFree(p);
     cudaFree(e->history); cudaFree(e->prompt);
@@ -1166,23 +1177,66 @@ static bool check_flag(itb_engine* e) {
     return true;
 }
 
-static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
+// Expert-parallel engines: a rank that returned early would leave its peers waiting inside the layer's collectives with
+// nothing to end them. So every entry point first validates and allocates locally, then all ranks exchange one flag
+// (a one-int all-gather that every rank always enters) and go on only if every rank is ready; otherwise every rank
+// returns an error and none enqueues anything. A failure after work was enqueued aborts the communicator.
+static bool ep_agree(itb_engine* e, bool ok) {
+    if (!e->ep) return ok;
     itb_ctx* c = e->c;
+    EpState* p = e->ep;
+    if (p->broken) return itb_fail_msg(c, "expert-parallel engine: the communicator was aborted after an earlier failure");
+    const int W = p->world;
+    p->agree_host[W] = ok ? 1 : 0;
+    bool sent = cudaMemcpyAsync(p->agree_dev + W, p->agree_host + W, 4, cudaMemcpyHostToDevice, c->stream) == cudaSuccess &&
+                nccl_api().AllGather(p->agree_dev + W, p->agree_dev, 1, NcclApi::Int32, p->comm, c->stream) == 0 &&
+                cudaMemcpyAsync(p->agree_host, p->agree_dev, (size_t)W * 4, cudaMemcpyDeviceToHost, c->stream) == cudaSuccess &&
+                cudaStreamSynchronize(c->stream) == cudaSuccess;
+    if (!sent) return itb_fail_msg(c, "expert-parallel engine: the ranks could not exchange their ready flags");
+    for (int r = 0; r < W; ++r)
+        if (!p->agree_host[r]) {
+            if (ok) itb_fail_msg(c, "expert-parallel engine: rank " + std::to_string(r) + " refused this call (see its error); nothing was run");
+            return false;
+        }
+    return true;
+}
+static void ep_abort(itb_engine* e) {
+    if (!e->ep || e->ep->broken || !e->ep->comm) return;
+    if (nccl_api().CommAbort) nccl_api().CommAbort(e->ep->comm);
+    e->ep->broken = true;
+}
+
+// src/model/qwen35.rs:866 (TokenOutOfRange): refused on the host, before any copy or launch.
+static bool tokens_in_range(itb_engine* e, const uint32_t* tokens, size_t n) {
+    for (size_t i = 0; i < n; ++i)
+        if (tokens[i] >= e->m->d.n_vocab) return itb_fail_msg(e->c, "token id out of range");
+    return true;
+}
+
+static bool steps_use_graph(const itb_engine* e) {
     // expert-parallel steps hold NCCL calls; they are captured like the rest unless ITB_EP_GRAPH=0 asks for eager launches
     static const bool ep_graph = !(getenv("ITB_EP_GRAPH") && atoi(getenv("ITB_EP_GRAPH")) == 0);
-    const bool use_graph = (!e->ep || ep_graph) && !e->tier;   // a tiered step talks to the host between layers
-    if (use_graph && !ensure_graph(e)) return false;
+    return (!e->ep || ep_graph) && !e->tier;   // a tiered step talks to the host between layers
+}
+// Everything about `steps` decode steps that can fail before a launch: room in the context, the captured graph.
+static bool steps_ready(itb_engine* e, uint32_t steps) {
     for (uint32_t b = 0; b < e->B; ++b)
-        if (e->host_pos[b] + steps > e->n_ctx) return itb_fail_msg(c, "context overflow: the step would write past n_ctx");  // src/model/qwen35.rs:984-990
+        if (e->host_pos[b] + steps > e->n_ctx) return itb_fail_msg(e->c, "context overflow: the step would write past n_ctx");  // src/model/qwen35.rs:984-990
+    return !steps_use_graph(e) || ensure_graph(e);
+}
+// The steps themselves; steps_ready (and, for expert-parallel engines, ep_agree) came first.
+static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
+    itb_ctx* c = e->c;
+    const bool use_graph = steps_use_graph(e);
     if (timed) cudaEventRecord(e->ev0, c->stream);
     for (uint32_t s = 0; s < steps; ++s) {
         if (use_graph) {
             cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
-            if (err != cudaSuccess) return itb_fail(c, "engine: graph launch", err);
+            if (err != cudaSuccess) { ep_abort(e); return itb_fail(c, "engine: graph launch", err); }
         } else {
             if (e->B == 1 && !e->tier) enqueue_step(e, c->stream);
             else e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
-            if (!c->error.empty()) return false;
+            if (!c->error.empty()) { ep_abort(e); return false; }
         }
     }
     c->launches += (uint64_t)steps * e->launches_per_step;
@@ -1195,6 +1249,7 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
 extern "C" int itb_engine_decode(itb_engine* e, const uint32_t* tokens, float* logits_out, uint32_t* next_out) {
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
+    if (!ep_agree(e, tokens_in_range(e, tokens, e->B) && steps_ready(e, 1))) return 1;
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     if (!run_steps(e, 1, true)) return 1;
     if (next_out) cudaMemcpyAsync(next_out, e->next, e->B * 4, cudaMemcpyDeviceToHost, st);
@@ -1208,13 +1263,15 @@ extern "C" int itb_engine_decode_loop(itb_engine* e, const uint32_t* first, uint
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
     if (steps == 0) return 0;
-    if (e->history_cap < steps) {
+    bool ok = tokens_in_range(e, first, e->B);
+    if (ok && e->history_cap < steps) {
         cudaStreamSynchronize(st);
         drop_graph(e);  // the graph holds the history pointer
-        cudaFree(e->history);
-        ITB_CUDA_RET(c, cudaMalloc(&e->history, (size_t)steps * e->B * 4), 1);
-        e->history_cap = steps;
+        cudaFree(e->history); e->history = nullptr; e->history_cap = 0;
+        if (cudaMalloc(&e->history, (size_t)steps * e->B * 4) != cudaSuccess) { e->history = nullptr; ok = itb_fail_msg(c, "decode_loop: out of device memory for the token history"); }
+        else e->history_cap = steps;
     }
+    if (!ep_agree(e, ok && steps_ready(e, steps))) return 1;
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, first, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     cudaMemsetAsync(e->step_counter, 0, e->B * 4, st);
     if (!run_steps(e, steps, true)) return 1;
@@ -1232,10 +1289,18 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
     if (n == 0) { itb_fail_msg(c, "prefill: no tokens supplied"); return 1; }
-    for (uint32_t b = 0; b < e->B; ++b)
-        if (e->host_pos[b] + n > e->n_ctx) { itb_fail_msg(c, "context overflow: the prompt would write past n_ctx"); return 1; }
-    for (size_t i = 0; i < n * e->B; ++i)
-        if (tokens[i] >= e->m->d.n_vocab) { itb_fail_msg(c, "token id out of range"); return 1; }
+    bool ok = true;
+    for (uint32_t b = 0; b < e->B && ok; ++b)
+        if (e->host_pos[b] + n > e->n_ctx) ok = itb_fail_msg(c, "context overflow: the prompt would write past n_ctx");
+    ok = ok && tokens_in_range(e, tokens, n * e->B);
+    if (ok && e->prompt_cap < n * e->B) {
+        cudaStreamSynchronize(st);
+        cudaFree(e->prompt); e->prompt = nullptr; e->prompt_cap = 0;
+        if (cudaMalloc(&e->prompt, n * e->B * 4) != cudaSuccess) { e->prompt = nullptr; ok = itb_fail_msg(c, "prefill: out of device memory for the prompt"); }
+        else e->prompt_cap = n * e->B;
+    }
+    ok = ok && steps_ready(e, 0);   // a one-token pass replays the step graph: have it captured before anything is enqueued
+    if (!ep_agree(e, ok)) return 1;
     const bool stepwise = getenv("ITB_PREFILL_STEPWISE") != nullptr;
     const size_t chunk = stepwise ? 1 : std::max<size_t>(1, e->R / e->B);
     // token ids laid out pass by pass, row-major inside a pass: [pass][seq][t]
@@ -1245,12 +1310,6 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
         const size_t nt = std::min(chunk, n - t0);
         for (size_t b = 0; b < e->B; ++b)
             for (size_t t = 0; t < nt; ++t) tr[off++] = (int32_t)tokens[b * n + t0 + t];
-    }
-    if (e->prompt_cap < n * e->B) {
-        cudaStreamSynchronize(st);
-        cudaFree(e->prompt);
-        ITB_CUDA_RET(c, cudaMalloc(&e->prompt, n * e->B * 4), 1);
-        e->prompt_cap = n * e->B;
     }
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->prompt, tr.data(), tr.size() * 4, cudaMemcpyHostToDevice, st), 1);
     cudaEventRecord(e->ev0, st);
@@ -1262,6 +1321,7 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
             if (!run_steps(e, 1, false)) return 1;
         } else {
             c->launches += enqueue_rows(e, st, (int)e->B, (int)nt, e->prompt + off);
+            if (!c->error.empty()) { ep_abort(e); return 1; }
             e->last_n_tok = (uint32_t)nt;
             for (uint32_t b = 0; b < e->B; ++b) e->host_pos[b] += (uint32_t)nt;
         }
@@ -1318,10 +1378,8 @@ extern "C" int itb_engine_read_ssm_state(itb_engine* e, uint32_t seq, uint32_t i
 extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, itb_kernel_stat* out, size_t cap, size_t* n_out) {
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
-    for (uint32_t b = 0; b < e->B; ++b)
-        if (e->host_pos[b] + 1 > e->n_ctx) { itb_fail_msg(c, "context overflow: the step would write past n_ctx"); return 1; }
     if (e->B != 1 || e->ep || e->tier) { itb_fail_msg(c, "profile_step: plain single-sequence engines only"); return 1; }
-    if (!ensure_graph(e)) return 1;  // function attributes are set during capture
+    if (!tokens_in_range(e, tokens, e->B) || !steps_ready(e, 1)) return 1;  // function attributes are set during capture
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     StepProf prof;
     k_hold<<<1, 1, 0, st>>>(3000000LL);

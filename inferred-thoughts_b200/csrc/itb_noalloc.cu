@@ -16,6 +16,8 @@
 // overlap on the GPU (different streams, or different threads) would overwrite each other's partials: run
 // them one after the other.
 //
+// Threads: like the rest of the library, one host thread at a time (the first-call set-up below is not locked).
+//
 // First call on a device: looks up the array's device address (cudaGetSymbolAddress) and raises two kernels'
 // dynamic shared-memory limit. Make that first call with the device current and before starting any stream
 // capture; later calls only launch kernels.
@@ -47,6 +49,12 @@ extern "C" int itb_attend_decode_noalloc(void* stream, const float* q_dev, const
     if (n_head / n_head_kv > 8) return fail(err, err_cap, "attend_decode_noalloc: more than 8 query heads per kv head");
     if (head_dim != 64 && head_dim != 128 && head_dim != 256) return fail(err, err_cap, "attend_decode_noalloc: head_dim must be 64, 128 or 256");
     if (n_pos == 0 || n_pos > 0x7fffffffu || kv_dim < n_head_kv * head_dim) return fail(err, err_cap, "attend_decode_noalloc: bad n_pos or kv_dim");
+    // The kernel reads head_dim/32 consecutive K (and V) elements per lane with one vector load, so every row of every
+    // head must start on that boundary: kv_dim a multiple of head_dim/32 elements, the slabs aligned to 2*(head_dim/32) bytes.
+    const size_t dpl = head_dim / 32;
+    if (kv_dim > 0x7fffffffu || kv_dim % dpl) return fail(err, err_cap, "attend_decode_noalloc: kv_dim must be a multiple of head_dim/32 and fit an int");
+    if (((uintptr_t)k_dev | (uintptr_t)v_dev) % (2 * dpl)) return fail(err, err_cap, "attend_decode_noalloc: k_dev and v_dev must be aligned to 2*(head_dim/32) bytes");
+    if (((uintptr_t)q_dev | (uintptr_t)out_dev) % 4) return fail(err, err_cap, "attend_decode_noalloc: q_dev and out_dev must be 4-byte aligned");
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(err, err_cap, "attend_decode_noalloc: no current CUDA device");
     const size_t smem = (size_t)8 * 8 * 2 * 4 + (size_t)8 * 8 * head_dim * 4;

@@ -285,9 +285,15 @@ extern "C" void itb_read_route(itb_ctx* c, int32_t* ids, float* weights, size_t 
     ITB_CUDA(c, cudaStreamSynchronize(c->stream));
 }
 // A host-chosen route is honoured by staging it into the device route (src/ops/cuda/ops/moe.rs:878-921).
-static bool stage_route(itb_ctx* c, const itb_route_t* r) {
+// The kernels index shared memory and the expert stack with these ids, so a host-built route is checked here, before any
+// copy or launch: n_used within [1, min(16, n_expert)], every id within [0, n_expert).
+static bool stage_route(itb_ctx* c, const itb_route_t* r, size_t n_expert) {
+    if (r->n_used == 0 || r->n_used > 16 || r->n_used > n_expert) return itb_fail_msg(c, "route: n_used out of range");
     if (r->on_device) return c->route_n_tok == r->n_tok && c->route_n_used == r->n_used ? true : itb_fail_msg(c, "route: device route does not match");
     size_t n = r->n_tok * r->n_used;
+    if (!r->ids) return itb_fail_msg(c, "route: host route without ids");
+    for (size_t i = 0; i < n; ++i)
+        if (r->ids[i] >= n_expert) return itb_fail_msg(c, "route: expert id out of range");
     if (!itb_ensure_route(c, n)) return false;
     std::vector<int32_t> ids(n);
     for (size_t i = 0; i < n; ++i) ids[i] = (int32_t)r->ids[i];
@@ -309,7 +315,7 @@ static void experts_dev(itb_ctx* c, const itb_experts* w, const itb_route_t* r, 
 extern "C" void itb_matmul_experts(itb_ctx* c, const itb_experts* w, const itb_route_t* r, const float* x, size_t x_len,
                                    float* out, size_t out_len) {
     if (w->n_in == 0 || x_len % w->n_in || out_len != r->n_tok * r->n_used * w->n_out) { itb_fail_msg(c, "matmul_experts: bad shape"); return; }
-    if (!stage_route(c, r)) return;
+    if (!stage_route(c, r, w->n_expert)) return;
     const float* xd = itb_mirror_in(c, x, x_len); float* od = itb_mirror_out(c, out, out_len);
     if (!xd || !od) return;
     experts_dev(c, w, r, xd, x_len, od);
@@ -319,7 +325,8 @@ extern "C" void itb_moe_glu(itb_ctx* c, const itb_experts* gate, const itb_exper
     if (gate->n_in != up->n_in || gate->n_out != up->n_out || out_len != r->n_tok * r->n_used * gate->n_out) {
         itb_fail_msg(c, "moe_glu: bad shape"); return;
     }
-    if (!stage_route(c, r)) return;
+    if (gate->n_expert != up->n_expert) { itb_fail_msg(c, "moe_glu: gate and up stacks differ in expert count"); return; }
+    if (!stage_route(c, r, gate->n_expert)) return;
     const float* xd = itb_mirror_in(c, x, x_len);
     float* od = itb_mirror_out(c, out, out_len); float* sd = itb_mirror_out(c, scratch, out_len);
     if (!xd || !od || !sd) return;
@@ -331,7 +338,7 @@ extern "C" void itb_moe_finish(itb_ctx* c, float* out, size_t out_len, size_t at
                                const itb_route_t* r, const float* shared, const float* logit, size_t logit_at) {
     size_t nt = r->n_tok;
     if (rows_len != nt * r->n_used * n || at + nt * n > out_len) { itb_fail_msg(c, "moe_finish: bad shape"); return; }
-    if (!stage_route(c, r)) return;
+    if (!stage_route(c, r, r->on_device ? 16 : 4096)) return;   // the combine reads the weights only; ids just have to be sane
     float* od = itb_mirror_inout(c, out, out_len);
     const float* rd = itb_mirror_in(c, rows, rows_len); const float* sh = itb_mirror_in(c, shared, nt * n);
     const float* lg = itb_mirror_in(c, logit, logit_at + nt);

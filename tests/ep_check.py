@@ -1,11 +1,13 @@
 """Expert-parallel parity check, one process per GPU:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 --master-port 29511 \
-        -m inferred_thoughts_b200.ep_check
+        -m tests.ep_check
 
 Each rank builds (a) the whole `configs.MID` model and a single-GPU engine and (b) its expert shard and an
 expert-parallel engine, runs the same prompts and decode steps through both on ITS OWN sequences, and requires the
-logits to be bit-identical. Exit code 0 and one line "ep_check ok" per rank on success.
+logits to be bit-identical. Then one rank alone is handed a token id outside the vocabulary: every rank must get an
+error back (the ranks agree before anything is enqueued) and the engines must still work afterwards.
+Exit code 0 and one line "ep_check ok" per rank on success.
 """
 import os
 import sys
@@ -16,7 +18,7 @@ import numpy as np
 def main():
     import torch
     import torch.distributed as dist
-    from . import configs, host
+    from inferred_thoughts_b200 import configs, host
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dev = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(dev)
@@ -44,6 +46,19 @@ def main():
         L, K = dims["n_layer"], dims["n_expert_used"]
         ok = ok and e1.read_routes(L, K).tolist() == e2.read_routes(L, K).tolist()
         ops.check()
+        if n_seq == 1:
+            # a failure on ONE rank: rank 0 passes a bad token; no rank may enter the layer's collectives alone
+            bad = np.array([dims["n_vocab"] + 5], np.uint32) if rank == 0 else toks
+            refused = False
+            try:
+                e2.decode(bad)
+            except RuntimeError as ex:
+                refused = True
+                msg = str(ex)
+                ok = ok and (("out of range" in msg) if rank == 0 else ("refused this call" in msg))
+            ok = ok and refused
+            (la, na), (lb, nb) = e1.decode(toks), e2.decode(toks)      # and the next step is in step again on every rank
+            ok = ok and la.view(np.uint32).tolist() == lb.view(np.uint32).tolist()
         e2.close(); e1.close()
     flag = torch.tensor([1 if ok else 0])
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)

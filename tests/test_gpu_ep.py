@@ -18,7 +18,7 @@ def test_two_rank_expert_parallel_equals_single_gpu():
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", "29511", "-m", "inferred_thoughts_b200.ep_check"]
+           "--master-port", "29511", "-m", "tests.ep_check"]
     # own process group, so that a rank stuck in a collective is ended with the launcher instead of outliving the test
     p = subprocess.Popen(cmd, cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
     try:

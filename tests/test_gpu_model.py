@@ -410,6 +410,35 @@ def test_context_overflow_is_refused_before_any_write(oracle, gpu):
     eng.close()
 
 
+def test_token_ids_outside_the_vocabulary_are_refused_before_any_launch(oracle, gpu):
+    """TokenOutOfRange (src/model/qwen35.rs:866 there): decode, the device-resident loop, the profiled step and prefill all
+    refuse on the host; nothing is copied or launched, and the engine goes on working."""
+    from inferred_thoughts_b200 import host
+    ops, model = gpu
+    eng = host.Engine(model, 32, 1)
+    eng.prefill(prompt_ids(1, 4, TINY["n_vocab"]))
+    ops.check()
+    before = ops.launch_count()
+    for bad in (TINY["n_vocab"], 0xFFFFFFFF):
+        with pytest.raises(RuntimeError, match="out of range"):
+            eng.decode([bad])
+        with pytest.raises(RuntimeError, match="out of range"):
+            eng.decode_loop([bad], 2)
+        with pytest.raises(RuntimeError, match="out of range"):
+            eng.prefill([1, bad])
+    assert ops.launch_count() == before and eng.pos() == 4
+    lg, _ = eng.decode([3])
+    assert np.isfinite(lg).all()
+    # a host-built route naming an expert the stack does not have is refused the same way (src/ops/mod.rs:176-218 there)
+    gate, gs = oracle.tensor("blk.0.ffn_gate_exps.weight")
+    G = host.Experts(gate, host.NVFP4, TINY["n_embd"], TINY["expert_ff"], TINY["n_expert"], gs)
+    x = np.zeros(TINY["n_embd"], np.float32); out = np.zeros(TINY["n_expert_used"] * TINY["expert_ff"], np.float32)
+    ops.begin_pass(1)
+    ops.matmul_experts(G, host.Route.host([0, 1, 2, TINY["n_expert"]], None, TINY["n_expert_used"]), x, out)
+    assert "expert id out of range" in (ops.take_error() or "")
+    eng.close()
+
+
 def test_seam_ops_drive_a_whole_layer_like_the_reference_model_does(oracle, gpu):
     """Qwen35::gated_delta + moe_batch (src/model/qwen35.rs:1232-1328, :1587-1699 there) written against the op-level
     seam with host buffers as handles, exactly as the reference's model code calls its backend; compared with the

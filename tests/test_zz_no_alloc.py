@@ -63,4 +63,11 @@ def test_no_alloc_attention_matches_the_ordinary_entry_point_twice_in_a_row():
                                      C.c_size_t(10), C.c_size_t(hd), C.c_size_t(128), C.c_size_t(16), C.c_float(scale), 0,
                                      C.c_void_p(od.data_ptr()), err, C.c_size_t(256))
     assert rc == 1 and b"exceeds the built-in scratch" in err.value
+    # so are a row stride or a slab address the kernel's vector loads could not take
+    for kv_dim_bad, k_off, want_msg in ((kvd + 4, 0, b"multiple of head_dim/32"), (kvd, 2, b"aligned")):
+        err = C.create_string_buffer(256)
+        rc = L.itb_attend_decode_noalloc(None, C.c_void_p(qd.data_ptr()), C.c_void_p(kd.data_ptr() + k_off), C.c_void_p(vd.data_ptr()),
+                                         C.c_size_t(kv_dim_bad), C.c_size_t(10), C.c_size_t(hd), C.c_size_t(nh), C.c_size_t(nkv), C.c_float(scale), 0,
+                                         C.c_void_p(od.data_ptr()), err, C.c_size_t(256))
+        assert rc == 1 and want_msg in err.value, err.value
     ops.check(); ops.close()
