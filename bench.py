@@ -421,9 +421,11 @@ def run_product(args, rank, world):
         try:
             if om is None:
                 raise RuntimeError("the oracle could not be loaded")
-            v, n, dt, prefill_s = cpu_decode_tok_s(om, dims, seed, threads, pr[0], 1, 48, args.cpu_budget)
+            # bounded sample: the first 32 tokens of the prompt only (the CPU needs ~0.4 s per prompt token; `--impl reference`
+            # runs the whole 512-token prompt), then decode tokens for about --cpu-budget seconds
+            v, n, dt, prefill_s = cpu_decode_tok_s(om, dims, seed, threads, pr[0][:32], 1, 48, args.cpu_budget)
             line["cpu_baseline"] = {"value": v, "unit": "tok/s", "cores": threads, "kind": "port",
-                                    "sample": f"{n} decode tokens ({dt:.1f} s) after the same {len(pr[0])}-token prompt (CPU prompt pass {prefill_s:.0f} s, untimed), "
+                                    "sample": f"{n} decode tokens ({dt:.1f} s) after the first 32 tokens of the same prompt (CPU prompt pass {prefill_s:.0f} s, untimed), "
                                               f"same weights (copied back from the device in {load_s:.0f} s), batch 1, bf16 KV"}
         except Exception as ex:  # the baseline is a report, never a reason to lose the measurement
             line["cpu_baseline"] = {"value": None, "unit": "tok/s", "cores": 0, "kind": "port", "sample": f"failed: {ex}"}
@@ -514,7 +516,10 @@ def run_probe(args):
     eng.close(); model.close(); ops.close()
 
 
-TIMELINE_KERNELS = {2: "k_in_proj", 3: "k_gdn_core", 4: "k_out_proj", 5: "k_attn_prep", 8: "k_moe_glu", 9: "k_moe_down"}
+TIMELINE_KERNELS = {2: "k_in_proj", 3: "k_gdn_core", 4: "k_out_proj", 5: "k_attn_prep", 8: "k_moe_glu", 9: "k_moe_down",
+                    # stages of the one-kernel step: marks 0 start, 1 end of the stage's work, 2 past the grid barrier
+                    17: "mega:embed", 18: "mega:rows", 19: "mega:gdn", 20: "mega:out", 21: "mega:attn_prep", 22: "mega:attn_part",
+                    23: "mega:attn_comb", 24: "mega:glu", 25: "mega:down", 26: "mega:advance"}
 
 
 def print_timeline(eng, dims, tok):
@@ -536,6 +541,13 @@ def print_timeline(eng, dims, tok):
         if not marks:
             continue
         name = TIMELINE_KERNELS.get(int(w[w != 0][0]) & 255, "?")
+        if name.startswith("mega:"):
+            # the one-kernel step: intervals against mark 0 (consumers enter the stage); 7/8: the producer reaches the stage's first
+            # chunk / has a free slot for it (negative: it ran ahead); 5/6: consumers start / end waiting for that chunk
+            for i in sorted(marks):
+                if i:
+                    agg.setdefault((name, f"mark {i} - mark 0"), []).append((marks[i] - marks[0]) / 1e3)
+            continue
         order = sorted(marks.items(), key=lambda x: x[1])
         for (i, a), (j, b) in zip(order, order[1:]):
             agg.setdefault((name, f"phase {i}->{j}"), []).append((b - a) / 1e3)

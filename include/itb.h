@@ -47,7 +47,9 @@ typedef struct { const float *q, *k, *v, *alpha, *beta, *ssm_a, *dt_bias; size_t
 
 /* ---- context ---- */
 /* opts: "key=value,..." ; keys: kv=f16|bf16 (default f16, the reference's KV dtype, src/cache/mod.rs:8-15),
- * exact=0|1 (1: F32 dots accumulate serially like the CPU path; default 1 for the op-level seam). */
+ * exact=0|1 (1: F32 dots accumulate serially like the CPU path; default 1 for the op-level seam),
+ * libm=cr (log stays correctly rounded; by default the kernels' log follows the host C library's logf bit for bit through a
+ * correction table built at the first itb_create of the process, 61 MB per device, because that is what the CPU path calls). */
 int         itb_create(int device_ordinal, const char* opts, itb_ctx** out);   /* 0 ok */
 void        itb_destroy(itb_ctx*);
 const char* itb_take_error(itb_ctx*);   /* NULL if none; clears (src/ops/cuda/ops/mod.rs:91-110) */
@@ -198,6 +200,13 @@ int  itb_engine_read_routes(itb_engine*, int32_t* ids, size_t cap);
 int  itb_engine_read_ssm_state(itb_engine*, uint32_t seq, uint32_t il, float* out, size_t len);
 /* Device time of the last decode step or loop in milliseconds (CUDA events on the engine's stream). */
 float itb_engine_last_ms(itb_engine*);
+/* How single-token decode steps of this engine run: 1 = one persistent cooperative kernel per step (a block per SM walks the
+ * step's stages with grid barriers between them while producer warps stream every stage's weights through shared-memory
+ * rings with bulk asynchronous copies, ahead of the dependency chain); 0 = the chain of fused kernels replayed as a CUDA
+ * graph (the reference hides launch cost the same way, src/ops/cuda/mod.rs:600-647), with the reason in `why`. The one-kernel
+ * step needs a single-sequence plain engine and every matrix row a multiple of 256 elements, and is selected by ITB_MEGA=1.
+ * Its waits are bounded (ITB_MEGA_WAIT_MS, default 2000): one that runs out makes the call fail with a message. */
+int  itb_engine_decode_path(itb_engine*, char* why, size_t cap);
 uint64_t itb_engine_launches_per_step(itb_engine*);
 
 /* Per-kernel-class totals of one eagerly launched decode step, timed with a CUDA event after every launch:
@@ -221,6 +230,11 @@ int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t*
                                size_t kv_dim, size_t n_pos, size_t head_dim, size_t n_head, size_t n_head_kv, float scale,
                                int kv_bf16, float* out_dev, char* err, size_t err_cap);
 
+/* exp and log as the kernels compute them, on their own (tests compare with the C library the reference CPU path calls:
+ * Rust's f32::exp / f32::ln, src/ops/naive.rs:101-106, :246-252, :362-376). itb_expf_host: the same expf on the host, no
+ * device needed. itb_eval_unary: kind 0 exp, 1 log, on the device over host arrays. */
+float itb_expf_host(float x);
+int  itb_eval_unary(itb_ctx*, int kind, const float* in, size_t n, float* out);
 /* Device generator check: element i of stream `key` (tests compare with the CPU generator). */
 int  itb_synth_values(itb_ctx*, uint64_t key, uint64_t first, size_t n, int dist, float std_, float* out);
 

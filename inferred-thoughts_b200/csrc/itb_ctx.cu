@@ -1,9 +1,15 @@
 // Context, sticky error, host-address-keyed mirrors, weight upload + repack, pass protocol.
 // Mirrors the reference's device-backend host layer (src/ops/cuda/ops/residency.rs:23-100,
 // src/ops/cuda/ops/mod.rs:91-110, :559-633) with a plain CUDA-runtime implementation.
+#include <math.h>
 #include <string.h>
 
+#include <thread>
+
 #include "itb_internal.cuh"
+
+void itb_ops_use_logf_fix(const uint32_t* dev_tab, uint32_t n);      // itb_ops.cu: points that unit's log_f at the table
+void itb_engine_use_logf_fix(const uint32_t* dev_tab, uint32_t n);   // itb_engine.cu
 
 static std::string g_create_error;
 
@@ -16,6 +22,58 @@ bool itb_fail(itb_ctx* c, const char* what, cudaError_t e) {
 }
 
 extern "C" const char* itb_last_create_error(void) { return g_create_error.empty() ? nullptr : g_create_error.c_str(); }
+
+// ------------------------------------------------------------------ the host C library's logf, as a correction table
+// For every float x of [1, 2^29): how logf(x) differs from the correctly rounded (float)log((double)x) -- 0 same, 1 one
+// ulp above, 2 one ulp below -- two bits each (61 MB). Built once per process with all host threads, uploaded once per
+// device and kept for the life of the process; the kernels' log_f applies it (itb_internal.cuh).
+static const uint32_t LOGF_FIX_N = 29u << 23;
+static std::vector<uint32_t> g_logf_fix_host;
+static uint32_t* g_logf_fix_dev[64];
+static uint64_t g_logf_fix_odd = 0;      // floats whose two results are more than one ulp apart (left uncorrected)
+static void build_logf_fix() {
+    if (!g_logf_fix_host.empty()) return;
+    g_logf_fix_host.assign(LOGF_FIX_N / 16, 0u);
+    const unsigned nt = std::max(1u, std::thread::hardware_concurrency());
+    std::vector<std::thread> th;
+    std::vector<uint64_t> odd(nt, 0);
+    const uint32_t words = LOGF_FIX_N / 16;
+    for (unsigned t = 0; t < nt; ++t)
+        th.emplace_back([=, &odd] {
+            const uint32_t w0 = (uint32_t)((uint64_t)words * t / nt), w1 = (uint32_t)((uint64_t)words * (t + 1) / nt);
+            for (uint32_t w = w0; w < w1; ++w) {
+                uint32_t word = 0;
+                for (uint32_t j = 0; j < 16; ++j) {
+                    const uint32_t bits = 0x3f800000u + w * 16 + j;
+                    float x; memcpy(&x, &bits, 4);
+                    const float lib = logf(x), cr = (float)log((double)x);
+                    uint32_t a, b; memcpy(&a, &lib, 4); memcpy(&b, &cr, 4);
+                    const int32_t d = (int32_t)(a - b);
+                    if (d == 1) word |= 1u << (2 * j);
+                    else if (d == -1) word |= 2u << (2 * j);
+                    else if (d != 0) odd[t]++;
+                }
+                g_logf_fix_host[w] = word;
+            }
+        });
+    for (auto& t : th) t.join();
+    for (uint64_t o : odd) g_logf_fix_odd += o;
+}
+static const uint32_t* logf_fix_on_device(int dev) {
+    if (dev < 0 || dev >= 64) return nullptr;
+    if (g_logf_fix_dev[dev]) return g_logf_fix_dev[dev];
+    build_logf_fix();
+    uint32_t* d = nullptr;
+    if (cudaMalloc(&d, (size_t)LOGF_FIX_N / 4) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaMemcpy(d, g_logf_fix_host.data(), (size_t)LOGF_FIX_N / 4, cudaMemcpyHostToDevice) != cudaSuccess) { cudaFree(d); cudaGetLastError(); return nullptr; }
+    g_logf_fix_dev[dev] = d;
+    return d;
+}
+// The restated expf on the host (tests compare it with the C library's).
+extern "C" float itb_expf_host(float x) {
+    static const unsigned long long tab[32] = {ITB_EXP2_TAB};
+    return itb_expf_lib(x, tab);
+}
 
 extern "C" int itb_create(int device_ordinal, const char* opts, itb_ctx** out) {
     *out = nullptr;
@@ -42,6 +100,10 @@ extern "C" int itb_create(int device_ordinal, const char* opts, itb_ctx** out) {
     std::string o = opts ? opts : "";
     if (o.find("kv=bf16") != std::string::npos) c->kv_bf16 = true;
     if (o.find("exact=0") != std::string::npos) c->exact = false;
+    // libm=cr keeps log correctly rounded instead of following the host C library's logf (see itb_internal.cuh)
+    const uint32_t* fix = o.find("libm=cr") != std::string::npos ? nullptr : logf_fix_on_device(device_ordinal);
+    itb_ops_use_logf_fix(fix, fix ? LOGF_FIX_N : 0);
+    itb_engine_use_logf_fix(fix, fix ? LOGF_FIX_N : 0);
     *out = c;
     return 0;
 }

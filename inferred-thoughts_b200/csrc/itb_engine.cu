@@ -22,7 +22,13 @@ void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t 
                        unsigned* amax_tmp, float* scale2, uint8_t* raw);
 
 #include "itb_fused.cuh"
+#include "itb_mega.cuh"
 #include "itb_rows.cuh"
+
+void itb_engine_use_logf_fix(const uint32_t* dev_tab, uint32_t n) {
+    cudaMemcpyToSymbol(g_logf_fix, &dev_tab, sizeof dev_tab);
+    cudaMemcpyToSymbol(g_logf_fix_n, &n, sizeof n);
+}
 
 // =====================================================================================================
 // Model
@@ -428,6 +434,10 @@ struct itb_engine {
     uint32_t last_n_tok = 1;                          // tokens per sequence in the most recent pass
     float *xn = nullptr, *qh = nullptr, *kh = nullptr, *vh = nullptr, *gb = nullptr, *core = nullptr, *xlast = nullptr;
     cudaGraph_t graph = nullptr; cudaGraphExec_t exec = nullptr;
+    // the one-kernel decode step (itb_mega.cuh): stage table, launch shape, parameters; mega < 0: not yet decided
+    int mega = -1; MStage* mega_stages = nullptr; MegaParams mp{}; size_t mega_smem = 0; int mega_grid = 0;
+    unsigned* mega_sync = nullptr; float* mega_core = nullptr; float* mega_part = nullptr; float* mega_argv = nullptr; int* mega_argi = nullptr;
+    std::string mega_why;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.0f;
     uint64_t launches_per_step = 0;
@@ -1154,6 +1164,163 @@ extern "C" uint32_t itb_engine_pos(itb_engine* e, uint32_t seq) { return seq < e
 extern "C" float itb_engine_last_ms(itb_engine* e) { return e->last_ms; }
 extern "C" uint64_t itb_engine_launches_per_step(itb_engine* e) { return e->launches_per_step; }
 
+// ---------------------------------------------------------------------------------------------------------
+// The one-kernel decode step. Decides once per engine whether the shape fits (single sequence, plain engine, every row a
+// whole number of 16-byte scale spans, shared memory for at least two ring slots each); builds the stage table -- the same
+// dependent stages enqueue_step launches as kernels -- and the shared-memory layout. ITB_MEGA=0 keeps the per-kernel step.
+static bool mega_prepare(itb_engine* e) {
+    if (e->mega >= 0) return e->mega == 1;
+    e->mega = 0;
+    itb_model* m = e->m; itb_ctx* c = e->c;
+    const itb_model_dims& d = m->d;
+    auto no = [&](const char* why) { e->mega_why = why; return false; };
+    if (!(getenv("ITB_MEGA") && atoi(getenv("ITB_MEGA")) == 1)) return no("not asked for (ITB_MEGA=1 selects the one-kernel step)");
+    if (e->B != 1 || e->ep || e->tier) return no("single-sequence plain engines only");
+    const int H = d.n_embd, sk = d.ssm_d_state, n_k = d.ssm_n_group, n_v = d.ssm_dt_rank;
+    const int key_dim = sk * n_k, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
+    const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv, ff = d.expert_ff, sff = d.shared_ff, K = d.n_expert_used;
+    if (H % 256 || vd % 256 || qd % 256 || ff % 256 || sff % 256 || H > 8192) return no("a row is not a whole number of 256-element spans");
+    if (d.n_head / d.n_head_kv > 8 || (int)d.head_dim > MG_CT || d.ssm_d_conv > 8) return no("attention group or conv width beyond the kernel");
+    if (((d.n_expert + 31) / 32) * K > MOE_CAND) return no("too many routing candidates");
+    int dev = 0, coop = 0, sms = c->sm_count;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+    if (!coop) return no("no cooperative launch on this device");
+    const int G = sms;
+    auto per_block = [&](int n) { return (n + G - 1) / G + 1; };
+    const int gdn_rows = per_block(n_v * sk), down_rows = per_block(H);
+    if (gdn_rows > MG_CT || (gdn_rows + sk - 1) / sk + 1 > MG_MAX_LOCAL_HEADS) return no("too many delta-rule rows per block");
+    // shared-memory layout
+    const int nmax = std::max(H, std::max(vd, qd));
+    auto up = [](size_t v) { return (v + 127) & ~(size_t)127; };
+    const size_t act = up(std::max<size_t>((size_t)nmax + (size_t)nmax / 8 + (size_t)H * 4,
+                                           (size_t)K * ff + (size_t)K * ff / 8 + sff + sff / 8 + (size_t)down_rows * (K + 1) * 4));
+    const int max_nt = std::max({H / 16, vd / 32, qd / 32, ff / 16, sff / 32});
+    const int group = d.n_head / d.n_head_kv, parts = MG_NW / group;
+    size_t terms_need = std::max<size_t>({(size_t)gdn_rows * (sk + 1) + (size_t)MG_MAX_LOCAL_HEADS * (2 * sk + 2),
+                                          (size_t)((d.n_expert + 31) & ~31u) + 2 * MOE_CAND,
+                                          (size_t)group * parts * (2 + d.head_dim), (size_t)d.head_dim});
+    int tw = std::max(560, max_nt + 1);
+    while ((size_t)MG_NW * tw < terms_need) tw += 16;
+    const size_t terms = up((size_t)MG_NW * tw * 4);
+    size_t row_max = std::max<size_t>({(size_t)H * 4, (size_t)H + H / 16, (size_t)vd + vd / 16, (size_t)qd + qd / 16, (size_t)sff + sff / 16, (size_t)sk * 4});
+    const size_t slot_b = up(std::max<size_t>(32 * ((size_t)H / 2 + H / 16), (size_t)down_rows * (ff / 2 + ff / 16)));
+    cudaFuncAttributes fa{};
+    if (cudaFuncGetAttributes(&fa, (const void*)k_mega) != cudaSuccess) return no("cannot query the kernel");
+    int max_optin = 0;
+    cudaDeviceGetAttribute(&max_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+    const long budget = (long)max_optin - (long)fa.sharedSizeBytes - 1024;
+    const int ns_b = 2;
+    size_t slot_a = up(std::max<size_t>(row_max, 16 * ((size_t)H + H / 16)));
+    long left = budget - (long)(act + terms + ns_b * slot_b);
+    int ns_a = (int)(left / (long)slot_a);
+    while (ns_a < 2 && slot_a / 2 >= up(row_max)) { slot_a = up(slot_a / 2); ns_a = (int)(left / (long)slot_a); }
+    if (left <= 0 || ns_a < 2) return no("not enough shared memory for the rings");
+    ns_a = std::min(ns_a, MG_MAX_SLOTS);
+    const size_t smem = act + terms + ns_a * slot_a + ns_b * slot_b;
+    if (cudaFuncSetAttribute((const void*)k_mega, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) { cudaGetLastError(); return no("cannot raise the shared-memory limit"); }
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, k_mega, MG_THREADS, smem) != cudaSuccess || occ < 1) { cudaGetLastError(); return no("the kernel does not fit an SM"); }
+    // buffers the step needs beyond the engine's
+    const int n_split = std::max(1, G / (int)d.n_head_kv);
+    if (!dalloc(e, &e->mega_sync, 4) || !dalloc(e, &e->mega_core, (size_t)vd) || !dalloc(e, &e->mega_part, (size_t)d.n_head * n_split * (d.head_dim + 2)) ||
+        !dalloc(e, &e->mega_argv, (size_t)G) || !dalloc(e, &e->mega_argi, (size_t)G)) return no("out of device memory");
+    // the stage table
+    std::vector<MStage> st;
+    auto blank = [](int type) { MStage t; memset(&t, 0, sizeof t); t.type = type; return t; };
+    st.push_back(blank(MS_EMBED));
+    for (uint32_t il = 0; il < d.n_layer; ++il) {
+        const DevLayer& L = m->layers[il];
+        if (L.recurrent) {
+            const int rs = e->slot_of[il];
+            MStage a = blank(MS_ROWS);
+            a.norm_w = L.attn_norm; a.nq = 2; a.q[0] = L.wqkv; a.qout[0] = e->qkvc; a.q[1] = L.wgate; a.qout[1] = e->z;
+            a.nf = 2; a.f[0] = L.ssm_alpha; a.fout[0] = e->alpha; a.f[1] = L.ssm_beta; a.fout[1] = e->beta;
+            a.conv_w = L.conv1d; a.conv_state = e->conv_state + (size_t)rs * cd * (d.ssm_d_conv - 1);
+            st.push_back(a);
+            MStage g = blank(MS_GDN);
+            g.ssm_a = L.ssm_a; g.dt_bias = L.dt_bias; g.state = e->ssm_state + (size_t)rs * n_v * sk * sk;
+            st.push_back(g);
+            MStage o = blank(MS_OUT);
+            o.ssm_norm = L.ssm_norm; o.w = L.ssm_out;
+            st.push_back(o);
+        } else {
+            const int as = e->slot_of[il];
+            MStage a = blank(MS_ROWS);
+            a.norm_w = L.attn_norm; a.nq = 3; a.q[0] = L.wq; a.qout[0] = e->qg; a.q[1] = L.wk; a.qout[1] = e->kbuf; a.q[2] = L.wv; a.qout[2] = e->vbuf;
+            st.push_back(a);
+            MStage pr = blank(MS_ATTN_PREP);
+            pr.q_norm = L.q_norm; pr.k_norm = L.k_norm;
+            pr.kslab = e->kslab + (size_t)as * e->n_ctx * kvd; pr.vslab = e->vslab + (size_t)as * e->n_ctx * kvd;
+            st.push_back(pr);
+            MStage pa = blank(MS_ATTN_PART); pa.kslab = pr.kslab; pa.vslab = pr.vslab;
+            st.push_back(pa);
+            st.push_back(blank(MS_ATTN_COMB));
+            MStage o = blank(MS_OUT);
+            o.flags = MSF_OUT_ATTN; o.w = L.wo;
+            st.push_back(o);
+        }
+        MStage f = blank(MS_ROWS);
+        f.norm_w = L.ffn_norm; f.nq = 2; f.q[0] = L.shared_gate; f.qout[0] = e->sg; f.q[1] = L.shared_up; f.qout[1] = e->su;
+        f.nf = 2; f.f[0] = L.gate_inp; f.fout[0] = e->router; f.f[1] = L.shared_gate_inp; f.fout[1] = e->shlogit;
+        st.push_back(f);
+        MStage gl = blank(MS_GLU);
+        gl.norm_w = L.ffn_norm; gl.gate = L.gate; gl.up = L.up;
+        gl.ids_out = e->route_ids + (size_t)il * e->R * K; gl.w_out = e->route_w + (size_t)il * e->R * K;
+        st.push_back(gl);
+        MStage dn = blank(MS_DOWN);
+        dn.down = L.down; dn.shared_down = L.shared_down; dn.ids_out = gl.ids_out; dn.w_out = gl.w_out;
+        st.push_back(dn);
+    }
+    MStage hd = blank(MS_ROWS);
+    hd.flags = MSF_ARGMAX; hd.norm_w = m->output_norm; hd.nq = 1; hd.q[0] = m->output; hd.qout[0] = e->logits;
+    st.push_back(hd);
+    st.push_back(blank(MS_ADVANCE));
+    if (!dalloc(e, &e->mega_stages, st.size())) return no("out of device memory");
+    if (cudaMemcpyAsync(e->mega_stages, st.data(), st.size() * sizeof(MStage), cudaMemcpyHostToDevice, c->stream) != cudaSuccess ||
+        cudaStreamSynchronize(c->stream) != cudaSuccess) return no("cannot upload the stage table");
+    MegaParams& p = e->mp;
+    memset(&p, 0, sizeof p);
+    p.stages = e->mega_stages; p.n_stages = (int)st.size();
+    p.H = H; p.n_vocab = d.n_vocab; p.cd = cd; p.vd = vd; p.key_dim = key_dim; p.sk = sk; p.n_k = n_k; p.n_v = n_v; p.conv_kernel = d.ssm_d_conv;
+    p.qd = qd; p.kvd = kvd; p.hd = d.head_dim; p.n_head = d.n_head; p.n_head_kv = d.n_head_kv; p.n_rot = d.n_rot; p.n_expert = d.n_expert;
+    p.n_used = K; p.ff = ff; p.sff = sff; p.n_ctx = e->n_ctx; p.eps = d.rms_eps; p.theta = d.rope_theta; p.exact = c->exact; p.kv_bf16 = c->kv_bf16;
+    p.tok_embd = m->tok_embd.w;
+    p.x = e->x; p.qkvc = e->qkvc; p.z = e->z; p.alpha = e->alpha; p.beta = e->beta; p.core = e->mega_core; p.qg = e->qg; p.kbuf = e->kbuf; p.vbuf = e->vbuf;
+    p.qn = e->qn; p.gate = e->gate; p.part_acc = e->mega_part; p.part_ml = e->mega_part + (size_t)d.n_head * n_split * d.head_dim;
+    p.router = e->router; p.shlogit = e->shlogit; p.sg = e->sg; p.su = e->su; p.logits = e->logits;
+    p.aq = e->aq; p.as = e->as; p.hq = e->hq; p.hs = e->hs; p.sq = e->sq; p.ss = e->ss;
+    p.tokens = e->tokens; p.pos = e->pos; p.next = e->next; p.step_counter = e->step_counter;
+    p.arg_v = e->mega_argv; p.arg_i = e->mega_argi;
+    p.bar = e->mega_sync; p.done = e->mega_sync + 1; p.err = e->err;
+    p.n_split = n_split;
+    p.wait_ns = getenv("ITB_MEGA_WAIT_MS") ? (unsigned long long)std::max(1, atoi(getenv("ITB_MEGA_WAIT_MS"))) * 1000000ull : MG_WAIT_NS;
+    p.test_stall = getenv("ITB_MEGA_TEST_STALL") ? atoi(getenv("ITB_MEGA_TEST_STALL")) : 0;
+    p.off_act = 0; p.off_terms = (int)act; p.off_ring_a = (int)(act + terms); p.off_ring_b = (int)(act + terms + ns_a * slot_a);
+    p.ns_a = ns_a; p.ns_b = ns_b; p.slot_a = (int)slot_a; p.slot_b = (int)slot_b; p.tw_floats = tw;
+    e->mega_smem = smem; e->mega_grid = G;
+    e->mega = 1;
+    return true;
+}
+// One decode step as one cooperative launch (every block resident: the grid barriers need it).
+static bool enqueue_mega(itb_engine* e, cudaStream_t st) {
+    MegaParams& p = e->mp;
+    p.history = e->history; p.history_cap = (int)e->history_cap;
+    void* args[] = {&p};
+    cudaError_t err = cudaLaunchCooperativeKernel((const void*)k_mega, dim3(e->mega_grid), dim3(MG_THREADS), args, e->mega_smem, st);
+    if (err != cudaSuccess) return itb_fail(e->c, "engine: cooperative launch of the decode step", err);
+    e->launches_per_step = 1;
+    return true;
+}
+
+// 1: single-token decode steps of this engine run as the one persistent kernel; 0: as the chain of fused kernels, with the
+// reason in `why`. Decides now if no step has run yet.
+extern "C" int itb_engine_decode_path(itb_engine* e, char* why, size_t cap) {
+    const bool mega = mega_prepare(e);
+    if (why && cap) snprintf(why, cap, "%s", mega ? "one persistent kernel per step" : e->mega_why.c_str());
+    return mega ? 1 : 0;
+}
+
 static bool ensure_graph(itb_engine* e) {
     if (e->exec) return true;
     itb_ctx* c = e->c;
@@ -1169,11 +1336,19 @@ static bool ensure_graph(itb_engine* e) {
     return true;
 }
 
-// A kernel that gave up waiting for its staged weights sets the flag; turn it into the sticky error.
+// The one-kernel step's waits are bounded: a wait that ran out stores (stage << 8) | reason in the status word and every
+// block returns. Turn it into the sticky error and put the grid barrier's counters back.
 static bool check_flag(itb_engine* e) {
+    if (e->mega != 1) return true;
     int f = 0;
     if (cudaMemcpy(&f, e->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return itb_fail_msg(e->c, "engine: cannot read the device status word");
-    if (f) { cudaMemset(e->err, 0, 4); return itb_fail_msg(e->c, "engine: a kernel gave up waiting for staged weights (bounded wait ran out)"); }
+    if (f) {
+        cudaMemset(e->err, 0, 4); cudaMemset(e->mega_sync, 0, 16);
+        static const char* const why[] = {"?", "weights never arrived in the ring", "a ring slot was never released", "a grid barrier was never completed",
+                                          "the routing picks were never published", "copies in flight did not land", "shape"};
+        const int r = f & 255;
+        return itb_fail_msg(e->c, std::string("engine: the decode step gave up at stage ") + std::to_string(f >> 8) + ": " + why[r >= 1 && r <= 6 ? r : 0] + " (bounded wait ran out)");
+    }
     return true;
 }
 
@@ -1216,12 +1391,13 @@ static bool tokens_in_range(itb_engine* e, const uint32_t* tokens, size_t n) {
 static bool steps_use_graph(const itb_engine* e) {
     // expert-parallel steps hold NCCL calls; they are captured like the rest unless ITB_EP_GRAPH=0 asks for eager launches
     static const bool ep_graph = !(getenv("ITB_EP_GRAPH") && atoi(getenv("ITB_EP_GRAPH")) == 0);
-    return (!e->ep || ep_graph) && !e->tier;   // a tiered step talks to the host between layers
+    return (!e->ep || ep_graph) && !e->tier && e->mega != 1;   // a tiered step talks to the host between layers; the one-kernel step is one launch already
 }
 // Everything about `steps` decode steps that can fail before a launch: room in the context, the captured graph.
 static bool steps_ready(itb_engine* e, uint32_t steps) {
     for (uint32_t b = 0; b < e->B; ++b)
         if (e->host_pos[b] + steps > e->n_ctx) return itb_fail_msg(e->c, "context overflow: the step would write past n_ctx");  // src/model/qwen35.rs:984-990
+    if (mega_prepare(e)) return true;
     return !steps_use_graph(e) || ensure_graph(e);
 }
 // The steps themselves; steps_ready (and, for expert-parallel engines, ep_agree) came first.
@@ -1230,7 +1406,9 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
     const bool use_graph = steps_use_graph(e);
     if (timed) cudaEventRecord(e->ev0, c->stream);
     for (uint32_t s = 0; s < steps; ++s) {
-        if (use_graph) {
+        if (e->mega == 1) {
+            if (!enqueue_mega(e, c->stream)) return false;
+        } else if (use_graph) {
             cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
             if (err != cudaSuccess) { ep_abort(e); return itb_fail(c, "engine: graph launch", err); }
         } else {

@@ -157,6 +157,14 @@ __device__ __forceinline__ void tl_mark(int slot, unsigned kernel, unsigned phas
         g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
     }
 }
+// The same from whichever thread of block 0 calls it (one caller per mark).
+__device__ __forceinline__ void tl_mark_any(int slot, unsigned kernel, unsigned phase) {
+    if (slot >= 0 && blockIdx.x == 0 && g_tl_buf && (unsigned)slot < g_tl_cap) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
+    }
+}
 #define TL(kernel, phase) tl_mark(p.tl_slot, (kernel), (phase))
 enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TLK_ATTN_PART, TLK_ATTN_COMB, TLK_MOE_GLU, TLK_MOE_DOWN, TLK_ARGMAX_P, TLK_ARGMAX_A };
 
@@ -171,12 +179,79 @@ __device__ __forceinline__ float warp_max(float v) {
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
 }
-// exp in f32 through the f64 unit: correctly rounded for all but a vanishing fraction of inputs, so
-// results track the CPU's libm far closer than the fast f32 expf does. Only a handful of elements
-// per token go through it.
-// Not inlined: the f64 routines are long, and one copy per kernel keeps the instruction footprint small.
-static __device__ __noinline__ float exp_f(float x) { return (float)exp((double)x); }
-static __device__ __noinline__ float log_f(float x) { return (float)log((double)x); }
+// expf and logf as the C library computes them. The reference CPU path calls the platform's libm (Rust's f32::exp and
+// f32::ln), whose single-precision routines are fast table-driven approximations evaluated in double: close to, but not
+// always, the correctly rounded result (measured against glibc: (float)exp((double)x) differs from expf(x) for 0.06 % of
+// inputs, (float)log((double)x) from logf(x) for 1.2 %). A last-bit difference in a GatedDeltaNet decay gate stays in the
+// recurrent state for good, so both functions follow the library here instead of being "more exact" than it.
+//
+// exp_f: the published algorithm of the library routine (exp(x) = 2^(k/32) * 2^(r/32), k = round(x * 32/ln2) by the
+// add-and-subtract-1.5*2^52 trick, 2^(i/32) from a 32-entry table, 2^(r/32) by a cubic polynomial, all in double, one
+// final rounding to float), restated. The table is 2^(i/32) rounded to nearest double minus i << 47, generated from integer
+// arithmetic; the three polynomial coefficients and 32/ln2 are the routine's published constants. Host and device share the
+// code: tests compare the host build with the C library's expf on millions of inputs (mismatches: about 1 in 10^8).
+#define ITB_EXP2_TAB                                                                                   \
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull, \
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull, \
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull, \
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull, \
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull, \
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull, \
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull, \
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
+#ifdef __CUDACC__
+static __device__ __constant__ unsigned long long c_exp2_tab[32] = {ITB_EXP2_TAB};
+#endif
+__host__ __device__ inline float itb_expf_lib(float x, const unsigned long long* tab) {
+    const double N = 32.0, inv_ln2_n = 0x1.71547652b82fep+0 * N, shift = 0x1.8p+52;
+    const double c0 = 0x1.c6af84b912394p-5 / N / N / N, c1 = 0x1.ebfce50fac4f3p-3 / N / N, c2 = 0x1.62e42ff0c52d6p-1 / N;
+    if (!(x > -88.0f && x < 88.0f)) {
+        if (x != x) return x + x;
+        if (x > 0x1.62e42ep6f) return __builtin_huge_valf();     // above log(2^128)
+        if (x < -0x1.9fe368p6f) return 0.0f;                     // below log(2^-150)
+    }
+    double z = inv_ln2_n * (double)x;
+    double kd = z + shift;
+    unsigned long long ki;
+#ifdef __CUDA_ARCH__
+    ki = (unsigned long long)__double_as_longlong(kd);
+#else
+    __builtin_memcpy(&ki, &kd, 8);
+#endif
+    kd -= shift;
+    const double r = z - kd;
+    const unsigned long long t = tab[ki & 31] + (ki << 47);
+    double s;
+#ifdef __CUDA_ARCH__
+    s = __longlong_as_double((long long)t);
+#else
+    __builtin_memcpy(&s, &t, 8);
+#endif
+    z = c0 * r + c1;
+    const double r2 = r * r;
+    double y = c2 * r + 1.0;
+    y = z * r2 + y;
+    y = y * s;
+    return (float)y;
+}
+// log_f: correctly rounded (through the f64 unit), then moved by the one ulp the host's logf differs by, read from a table
+// the context builds on the host by calling logf on every float of [1, 2^29) -- the whole range softplus can ask for
+// (ln(1 + e^a), a <= 20) -- two bits per float. Without a table (g_logf_fix null) the correctly rounded value stands.
+static __device__ const uint32_t* g_logf_fix = nullptr;
+static __device__ uint32_t g_logf_fix_n = 0;
+#ifdef __CUDACC__
+// Not inlined: one copy per kernel keeps the instruction footprint small.
+static __device__ __noinline__ float exp_f(float x) { return itb_expf_lib(x, c_exp2_tab); }
+static __device__ __noinline__ float log_f(float x) {
+    float v = (float)log((double)x);
+    const uint32_t idx = __float_as_uint(x) - 0x3f800000u;
+    if (g_logf_fix && idx < g_logf_fix_n) {
+        const uint32_t f = (g_logf_fix[idx >> 4] >> ((idx & 15u) * 2u)) & 3u;
+        v = __uint_as_float(__float_as_uint(v) + (f == 1u ? 1u : 0u) - (f == 2u ? 1u : 0u));   // results here are positive: +1 bit = +1 ulp
+    }
+    return v;
+}
+#endif
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + exp_f(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + exp_f(-x)); }
 __device__ __forceinline__ float f16_bits_to_f32(uint16_t h) { return __half2float(__ushort_as_half(h)); }

@@ -387,3 +387,26 @@ extern "C" void itb_attend(itb_ctx* c, const itb_attn* a, float* out, size_t out
     itb_attend_dev(c, c->stream, qd, kd, vd, (int)a->kv_dim, (int)a->n_pos, (int)n_q, (int)a->head_dim, (int)a->n_head,
                    (int)a->n_head_kv, a->scale, (int)c->kv_bf16, nullptr, nullptr, pa, pm, n_split, od);
 }
+
+// ------------------------------------------------------------------ the kernels' exp and log on their own
+void itb_ops_use_logf_fix(const uint32_t* dev_tab, uint32_t n) {
+    cudaMemcpyToSymbol(g_logf_fix, &dev_tab, sizeof dev_tab);
+    cudaMemcpyToSymbol(g_logf_fix_n, &n, sizeof n);
+}
+__global__ void k_eval_unary(int kind, const float* in, size_t n, float* out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = kind == 0 ? exp_f(in[i]) : log_f(in[i]);
+}
+// kind 0: exp as every kernel here computes it; 1: log. Host arrays in and out (tests compare with the C library).
+extern "C" int itb_eval_unary(itb_ctx* c, int kind, const float* in, size_t n, float* out) {
+    float *di = nullptr, *dd = nullptr;
+    if (cudaMalloc(&di, n * 4) != cudaSuccess || cudaMalloc(&dd, n * 4) != cudaSuccess) { cudaFree(di); itb_fail_msg(c, "eval_unary: out of device memory"); return 1; }
+    cudaMemcpyAsync(di, in, n * 4, cudaMemcpyHostToDevice, c->stream);
+    if (n) k_eval_unary<<<(unsigned)((n + 255) / 256), 256, 0, c->stream>>>(kind, di, n, dd);
+    ITB_LAUNCHED(c);
+    cudaMemcpyAsync(out, dd, n * 4, cudaMemcpyDeviceToHost, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    cudaFree(di); cudaFree(dd);
+    if (e != cudaSuccess) { itb_fail(c, "eval_unary", e); return 1; }
+    return 0;
+}

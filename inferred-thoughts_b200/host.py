@@ -427,5 +427,10 @@ class Engine:
         self._chk(self.L.itb_engine_read_ssm_state(self.h, seq, il, _p(out), SZ(n)), "read_ssm_state")
         return out
 
+    def decode_path(self):
+        """(1, text) when single-token steps run as the one persistent kernel, else (0, why not)."""
+        why = C.create_string_buffer(256)
+        return self.L.itb_engine_decode_path(self.h, why, SZ(256)), why.value.decode()
+
     def last_ms(self): return self.L.itb_engine_last_ms(self.h)
     def launches_per_step(self): return self.L.itb_engine_launches_per_step(self.h)

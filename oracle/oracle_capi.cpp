@@ -180,6 +180,11 @@ void orc_moe_finish(float* out, size_t at, size_t n, const float* rows, const in
                     size_t n_pairs, size_t n_used, const float* shared, const float* logit, size_t logit_at) {
     moe_finish(out, at, n, rows, mk_route(ids, weights, n_pairs, n_used), shared, logit, logit_at);
 }
+// The C library's expf (kind 0) / logf (kind 1) over an array: what Rust's f32::exp / f32::ln call on this platform
+// (src/ops/naive.rs:101-106, :246-252, :362-376 use them).
+void orc_libm(int kind, const float* in, size_t n, float* out) {
+    for (size_t i = 0; i < n; ++i) out[i] = kind == 0 ? expf(in[i]) : logf(in[i]);
+}
 uint32_t orc_argmax(const float* logits, size_t n, uint32_t* second) { return argmax_top2(logits, n, second); }
 
 // ---- synthetic tensors and model ----

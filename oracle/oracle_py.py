@@ -87,6 +87,7 @@ def lib():
     sig("orc_moe_glu", None, U8P, C.c_void_p, U8P, C.c_void_p, SZ, SZ, SZ, I32P, SZ, SZ, F32P, SZ, F32P, C.c_int)
     sig("orc_moe_finish", None, F32P, SZ, SZ, F32P, I32P, F32P, SZ, SZ, F32P, F32P, SZ)
     sig("orc_argmax", C.c_uint32, F32P, SZ, C.POINTER(C.c_uint32))
+    sig("orc_libm", None, C.c_int, F32P, SZ, F32P)
     sig("orc_tensor_key", C.c_uint64, C.c_uint64, C.c_char_p)
     sig("orc_synth_value", C.c_float, C.c_uint64, C.c_uint64, C.c_int, C.c_float)
     sig("orc_model_create", C.c_void_p, C.POINTER(ModelDims))

@@ -1,0 +1,133 @@
+"""The one-kernel decode step (a persistent cooperative kernel with shared-memory weight rings) against the chain of fused
+kernels it replaces and against the CPU oracle.
+
+Both paths keep the CPU path's arithmetic order, so everything except the attention reduction (split differently: tolerance
+class on both) is bit-identical; routing ids and greedy tokens must be equal, logits equal to within the attention bound.
+The bounded waits are tested by making one run out: the picks of the first layer are never published, every block gives up
+after the (shortened) limit, the call fails with a message, and the engine works again afterwards.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import oracle_py as O
+from tests.util import MID, cosine, host_dims, oracle_dims, prompt_ids
+from inferred_thoughts_b200 import configs
+
+pytestmark = pytest.mark.gpu
+STEPS = 100
+
+
+def _engine(host, model, n_ctx, mega, **env):
+    """An engine whose decode path is decided now, under the given environment."""
+    old = {k: os.environ.get(k) for k in ("ITB_MEGA", *env)}
+    os.environ["ITB_MEGA"] = "1" if mega else "0"
+    os.environ.update({k: str(v) for k, v in env.items()})
+    try:
+        eng = host.Engine(model, n_ctx, 1)
+        kind, why = eng.decode_path()
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    assert kind == (1 if mega else 0), why
+    return eng
+
+
+@pytest.fixture(scope="module", params=["mid", "m35b4"])
+def pair(request):
+    from inferred_thoughts_b200 import host
+    if request.param == "mid":
+        dims, seed = MID, configs.SEEDS["mid"]
+    else:
+        dims, seed = configs.with_layers(configs.M35B, 4), configs.SEEDS["m35b"]
+        dims = dict(dims); dims["n_vocab"] = 4096     # the full vocabulary runs in tests/test_gpu_shapes.py
+    ops = host.B200Ops(0, "exact=1")
+    model = host.Model(ops, host_dims(dims)); model.synth(seed)
+    om = O.OracleModel(oracle_dims(dims))
+    for s in om.specs:
+        data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+        om.set_tensor(s["name"], data, sc)
+    O.lib().orc_set_threads(max(1, O.lib().orc_hw_threads()))
+    yield dims, om, ops, model
+    ops.check()
+    model.close(); ops.close()
+
+
+def test_one_kernel_step_equals_the_kernel_chain_and_the_oracle(pair):
+    from inferred_thoughts_b200 import host
+    dims, om, ops, model = pair
+    L, K = dims["n_layer"], dims["n_expert_used"]
+    prompt = prompt_ids(41, 9, dims["n_vocab"])
+    chain, mega = _engine(host, model, 160, False), _engine(host, model, 160, True)
+    om.begin(160, log_routes=True)
+    o = om.forward(prompt)
+    a, b = chain.prefill(prompt), mega.prefill(prompt)          # the prompt pass is the same multi-row path on both
+    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
+    exact = 0
+    for step in range(STEPS):
+        t = int(np.argmax(o))
+        om.clear_route_log()
+        o = om.forward([t])
+        (la, na), (lb, nb) = chain.decode([t]), mega.decode([t])
+        ops.check()
+        ro = om.route_log().reshape(L, K).tolist()
+        assert mega.read_routes(L, K)[:, 0, :].tolist() == ro, f"routing at step {step}"
+        assert chain.read_routes(L, K)[:, 0, :].tolist() == ro, f"routing of the kernel chain at step {step}"
+        err = float(np.abs(o - lb[0]).max())
+        assert err <= 2e-2 and cosine(o, lb[0]) >= 0.999, (step, err)
+        assert float(np.abs(la[0] - lb[0]).max()) <= 1e-4, step
+        assert int(nb[0]) == int(np.argmax(o)) == int(na[0]), step
+        exact += int((o == lb[0]).all())
+    print(f"{dims['n_embd']}-wide: one-kernel step bit-identical to the oracle in {exact}/{STEPS} steps")
+    for il in range(3):
+        so, sg = om.ssm_state(il), mega.read_ssm_state(il)
+        assert np.abs(so - sg).max() <= 1e-4 * max(1.0, float(np.abs(so).max())), il
+        assert mega.read_ssm_state(il).view(np.uint32).tolist() == chain.read_ssm_state(il).view(np.uint32).tolist(), il
+    chain.close(); mega.close()
+
+
+def test_device_resident_loop_and_tree_mode(pair):
+    """The greedy loop with tokens fed back on the device gives the chain's tokens; so does the tree-dot mode the benchmark can run."""
+    from inferred_thoughts_b200 import host
+    dims, om, ops, model = pair
+    prompt = prompt_ids(42, 7, dims["n_vocab"])
+    chain, mega = _engine(host, model, 96, False), _engine(host, model, 96, True)
+    chain.prefill(prompt); mega.prefill(prompt)
+    a, b = chain.decode_loop([5], 40), mega.decode_loop([5], 40)
+    assert a.tolist() == b.tolist()
+    om.begin(96)
+    om.forward(prompt)
+    want = [5]
+    for _ in range(12):
+        want.append(int(np.argmax(om.forward([want[-1]]))))
+    assert b[:12, 0].tolist() == want[1:]
+    assert mega.pos() == chain.pos() == 7 + 40
+    chain.close(); mega.close()
+    ops2 = host.B200Ops(0, "exact=0,kv=bf16")
+    m2 = host.Model(ops2, host_dims(dims)); m2.synth(configs.SEEDS["mid"] if dims is MID else configs.SEEDS["m35b"])
+    c2, g2 = _engine(host, m2, 96, False), _engine(host, m2, 96, True)
+    c2.prefill(prompt); g2.prefill(prompt)
+    (la, _), (lb, _) = c2.decode([3]), g2.decode([3])
+    assert float(np.abs(la[0] - lb[0]).max()) <= 2e-2 and cosine(la[0], lb[0]) >= 0.999
+    ops2.check()
+    c2.close(); g2.close(); m2.close(); ops2.close()
+
+
+def test_a_wait_that_runs_out_fails_the_call_and_leaves_the_engine_usable():
+    from inferred_thoughts_b200 import host
+    ops = host.B200Ops(0, "exact=1")
+    model = host.Model(ops, host_dims(MID)); model.synth(configs.SEEDS["mid"])
+    good = _engine(host, model, 64, True)
+    stuck = _engine(host, model, 64, True, ITB_MEGA_TEST_STALL=1, ITB_MEGA_WAIT_MS=30)
+    prompt = prompt_ids(43, 5, MID["n_vocab"])
+    good.prefill(prompt); stuck.prefill(prompt)
+    with pytest.raises(RuntimeError, match="gave up at stage"):
+        stuck.decode([1])
+    lg, _ = good.decode([1])                      # the context is intact: another engine of the same model still runs
+    assert np.isfinite(lg).all()
+    ops.check()
+    stuck.close(); good.close(); model.close(); ops.close()

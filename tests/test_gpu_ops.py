@@ -357,3 +357,28 @@ def test_synth_generator_matches_cpu_bit_for_bit(ops):
         want = np.array([L.orc_synth_value(key, 12345 + i, dist, sd) for i in range(4096)], np.float32)
         exact(got, want, f"synth dist {dist}")
     assert abs(float(np.std(ops.synth_values(key, 0, 1 << 16, 0, 1.0))) - 1.0) < 0.02
+
+
+def test_exp_and_log_follow_the_c_library():
+    """exp and log as every kernel computes them against the C library the CPU path calls: exp by the restated library algorithm,
+    log by the correction table built from the host's logf (softplus asks for log(1 + e^a), a <= 20: arguments in [1, 4.9e8))."""
+    import ctypes as C
+    from inferred_thoughts_b200 import host
+    from oracle import oracle_py as O
+    ops = host.B200Ops(0)
+    L = host.lib()
+    rng = np.random.default_rng(8)
+    a = np.concatenate([rng.uniform(-30, 20, 2_000_000), rng.normal(0, 2, 2_000_000)]).astype(np.float32)
+    want_e = np.zeros_like(a); got_e = np.zeros_like(a)
+    O.lib().orc_libm(0, a, a.size, want_e)
+    assert L.itb_eval_unary(ops.h, 0, C.c_void_p(a.ctypes.data), C.c_size_t(a.size), C.c_void_p(got_e.ctypes.data)) == 0
+    bad = int((want_e.view(np.uint32) != got_e.view(np.uint32)).sum())
+    assert bad <= 2, f"exp: {bad} of {a.size} differ"
+    x = (np.float32(1.0) + want_e).astype(np.float32)
+    x = x[x < np.float32(2.0 ** 29)]
+    want_l = np.zeros_like(x); got_l = np.zeros_like(x)
+    O.lib().orc_libm(1, x, x.size, want_l)
+    assert L.itb_eval_unary(ops.h, 1, C.c_void_p(x.ctypes.data), C.c_size_t(x.size), C.c_void_p(got_l.ctypes.data)) == 0
+    bad = int((want_l.view(np.uint32) != got_l.view(np.uint32)).sum())
+    assert bad <= 2, f"log: {bad} of {x.size} differ"
+    ops.check(); ops.close()
