@@ -545,8 +545,10 @@ def print_timeline(eng, dims, tok):
             # the one-kernel step: intervals against mark 0 (consumers enter the stage); 7/8: the producer reaches the stage's first
             # chunk / has a free slot for it (negative: it ran ahead); 5/6: consumers start / end waiting for that chunk
             for i in sorted(marks):
-                if i:
+                if 0 < i < 9:
                     agg.setdefault((name, f"mark {i} - mark 0"), []).append((marks[i] - marks[0]) / 1e3)
+                elif i >= 9:   # raw values: 9 = ns thread 0 waited for ring chunks, 10 = ns it worked on them, 11 = chunks
+                    agg.setdefault((name, {9: "chunk wait us", 10: "chunk work us", 11: "chunks x1000"}[i]), []).append(marks[i] / 1e3)
             continue
         order = sorted(marks.items(), key=lambda x: x[1])
         for (i, a), (j, b) in zip(order, order[1:]):

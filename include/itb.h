@@ -230,6 +230,13 @@ int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t*
                                size_t kv_dim, size_t n_pos, size_t head_dim, size_t n_head, size_t n_head_kv, float scale,
                                int kv_bf16, float* out_dev, char* err, size_t err_cap);
 
+/* The measured ceiling of the block-scaled FP4 tensor-core instruction this backend's expert GEMMs are built on
+ * (tcgen05.mma kind::mxf4nvf4, M 128 x N `n` (128 or 256) x K 64 per instruction, f32 accumulators in tensor memory): one block
+ * per SM issues `iters` accumulating MMAs on unchanging shared-memory operands, nothing else in the loop, and the accumulators
+ * are verified afterwards -- the reference measures its own instructions' ceilings the same way (tests/cuda_ops.rs:5899-5925).
+ * tflops_out: dense TFLOP/s, best of `reps` launches by CUDA events; status_out: 0 verified, 1 a (bounded) wait ran out,
+ * 2 accumulators wrong; mma_cycles_out: SM cycles per MMA on the slowest block. Returns non-zero on a call error. */
+int  itb_fp4_ceiling(itb_ctx*, int n, int iters, int reps, double* tflops_out, int* status_out, double* mma_cycles_out);
 /* exp and log as the kernels compute them, on their own (tests compare with the C library the reference CPU path calls:
  * Rust's f32::exp / f32::ln, src/ops/naive.rs:101-106, :246-252, :362-376). itb_expf_host: the same expf on the host, no
  * device needed. itb_eval_unary: kind 0 exp, 1 log, on the device over host arrays. */

@@ -6,7 +6,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 SO = PKG / "libitb.so"
-SOURCES = ["itb_ctx.cu", "itb_ops.cu", "itb_engine.cu", "itb_synth.cu", "itb_noalloc.cu", "itb_gguf.cu"]
+SOURCES = ["itb_ctx.cu", "itb_ops.cu", "itb_engine.cu", "itb_synth.cu", "itb_noalloc.cu", "itb_gguf.cu", "itb_tc.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "--fmad=false", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-ffp-contract=off", "-Xcompiler", "-O2"]
 

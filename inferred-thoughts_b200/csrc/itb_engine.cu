@@ -24,6 +24,7 @@ void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t 
 #include "itb_fused.cuh"
 #include "itb_mega.cuh"
 #include "itb_rows.cuh"
+#include "itb_attn_exact.cuh"
 
 void itb_engine_use_logf_fix(const uint32_t* dev_tab, uint32_t n) {
     cudaMemcpyToSymbol(g_logf_fix, &dev_tab, sizeof dev_tab);
@@ -421,6 +422,7 @@ struct itb_engine {
     float *x = nullptr, *qkvc = nullptr, *z = nullptr, *alpha = nullptr, *beta = nullptr, *zc = nullptr;
     float *qg = nullptr, *kbuf = nullptr, *vbuf = nullptr, *qn = nullptr, *gate = nullptr, *att = nullptr;
     float *part_acc = nullptr, *part_ml = nullptr;
+    float* scores = nullptr; size_t scores_cap = 0;    // exact attention: [rows][n_head][n_ctx] scores (grown on demand)
     float *router = nullptr, *shlogit = nullptr, *sg = nullptr, *su = nullptr, *h = nullptr, *logits = nullptr;
     int8_t* xq = nullptr; float* xs = nullptr;
     int32_t* route_ids = nullptr; float* route_w = nullptr;  // [n_layer][B][n_used]
@@ -495,6 +497,36 @@ static void launch_k(bool pdl, void (*k)(KA...), dim3 g, dim3 b, size_t sm, cuda
 
 constexpr size_t SMEM_BUDGET = 200 * 1024;   // dynamic shared memory the row-streaming kernels are allowed (set_smem below)
 
+// Attention in the CPU path's order (itb_attn_exact.cuh) for `rows` query rows: scores, then softmax + weighted values + gate +
+// Q8_0 quantisation into e->aq / e->as. Needs a row stride of whole 16-byte spans; the scores buffer holds n_ctx per (row, head).
+static bool exact_attention_ok(const itb_engine* e) { return e->c->exact && (e->m->d.head_dim * e->m->d.n_head_kv) % 8 == 0 && e->m->d.n_head / e->m->d.n_head_kv <= 8; }
+static void drop_graph(itb_engine* e);
+static bool ensure_scores(itb_engine* e, size_t rows) {
+    const size_t need = rows * e->m->d.n_head * e->n_ctx;
+    if (e->scores_cap >= need) return true;
+    cudaStreamSynchronize(e->c->stream);
+    drop_graph(e);        // a captured step holds the old pointer
+    cudaFree(e->scores); e->scores = nullptr; e->scores_cap = 0;
+    if (cudaMalloc(&e->scores, need * 4) != cudaSuccess) { cudaGetLastError(); return itb_fail_msg(e->c, "engine: out of device memory for the attention scores"); }
+    e->scores_cap = need;
+    return true;
+}
+static void enqueue_exact_attention(itb_engine* e, cudaStream_t st, bool pdl, const uint16_t* kslab, const uint16_t* vslab, size_t slab_stride,
+                                    int rows, int rows_per_seq, int n_pos_max) {
+    const itb_model_dims& d = e->m->d;
+    const int hd = d.head_dim, group = d.n_head / d.n_head_kv, kvd = hd * d.n_head_kv;
+    static bool attr = false;
+    if (!attr) { set_smem((const void*)k_attn_out_exact, 200 * 1024); attr = true; }
+    AxScores a{};
+    a.q = e->qn; a.kslab = kslab; a.slab_stride = slab_stride; a.rows_per_seq = rows_per_seq; a.n_pos_dev = e->npos; a.kv_dim = kvd; a.hd = hd;
+    a.n_head = d.n_head; a.n_head_kv = d.n_head_kv; a.scale = 1.0f / sqrtf((float)hd); a.bf16 = e->c->kv_bf16; a.scores = e->scores; a.s_stride = (int)e->n_ctx;
+    launch_k(pdl, k_attn_scores_exact, dim3((n_pos_max + AX_TP - 1) / AX_TP, d.n_head_kv, rows), dim3(AX_TP * group), attn_scores_exact_smem(hd, group), st, a);
+    AxOut o{};
+    o.scores = e->scores; o.s_stride = (int)e->n_ctx; o.vslab = vslab; o.slab_stride = slab_stride; o.rows_per_seq = rows_per_seq; o.n_pos_dev = e->npos;
+    o.kv_dim = kvd; o.hd = hd; o.n_head = d.n_head; o.n_head_kv = d.n_head_kv; o.bf16 = e->c->kv_bf16; o.gate = e->gate; o.out_q = e->aq; o.out_s = e->as;
+    launch_k(pdl, k_attn_out_exact, dim3(hd / 32, d.n_head, rows), dim3(256), attn_out_exact_smem(n_pos_max), st, o);
+}
+
 // One decode step for all B sequences, enqueued on `st`.
 static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullptr) {
     itb_model* m = e->m; itb_ctx* c = e->c;
@@ -521,6 +553,12 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         // the warps' term matrices must fit the block's shared memory (wide rows: fewer rows folded together)
         const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
         p.br = std::max(pass_in, std::min(p.br, cap / pass_in * pass_in));
+        if (c->exact && p.nf) {
+            // serial-k F32 rows stage a row's products in the warp's term scratch: make it hold the whole row (one round trip to
+            // memory instead of one per tile) as far as the block's shared memory goes
+            const int want = (H + H / 32) / (H / 32 + 1) + 1;
+            p.br = std::max(p.br, std::min((want + pass_in - 1) / pass_in * pass_in, cap / pass_in * pass_in));
+        }
         p.tl_slot = tl++;
         launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
     };
@@ -593,6 +631,12 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             a.tl_slot = tl++;
             launch_k(pdl, k_attn_prep, dim3(d.n_head + 2 * d.n_head_kv, B), d.head_dim, d.head_dim * 4, st, a);
             MARK(KC_ATTN_PREP, (uint64_t)B * (4ull * qd + 3ull * kvd) * 4);
+            if (exact_attention_ok(e) && e->scores) {
+                // exact mode: the CPU path's own order. The step is replayed from a graph, so the grids cover the whole context and
+                // blocks past the sequence's length leave at once.
+                enqueue_exact_attention(e, st, pdl, a.kslab, a.vslab, a.slab_stride, B, 1, (int)e->n_ctx);
+                MARK(KC_ATTN, 2ull * kvd * 2 * (e->host_pos[0] + 1) + 3ull * qd * 4); MARK(KC_ATTN, 0);
+            } else {
             // split-K partials, one launch per sequence (own slab, own position), then one combine for all
             const float scale = 1.0f / sqrtf((float)d.head_dim);
             const int nwa = 8;
@@ -614,6 +658,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             launch_k(pdl, k_attn_combine_q, B * d.n_head, d.head_dim, 0, st, e->part_acc, e->part_ml, e->n_split, d.head_dim, e->gate, e->npos,
                                                                   d.n_head, e->aq, e->as);
             MARK(KC_ATTN, 0);
+            }
             OutProj o{e->aq, e->as, qd, L.wo, e->x, H};
             launch_out(o, qd);
             MARK(KC_OUT_PROJ, q8b(qd, H) + (uint64_t)B * (qd + 2ull * H) * 4);
@@ -625,8 +670,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         f.nf = 2; f.f[0] = L.gate_inp; f.fout[0] = e->router; f.fstride[0] = d.n_expert;
         f.f[1] = L.shared_gate_inp; f.fout[1] = e->shlogit; f.fstride[1] = 1;
         f.xq_out = e->xq; f.xs_out = e->xs; f.exact = c->exact;
-        int gxf = c->exact ? std::max((int)(d.n_expert + 31) / 32 + 1, grid_rows(2 * d.shared_ff))
-                           : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));
+        int gxf = c->exact ? sms : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));   // serial-k F32 rows: one per SM
         launch_in(f, 2 * d.shared_ff, gxf);
         MARK(KC_FFN_IN, (uint64_t)H * d.n_expert * 4 + 2 * q8b(H, d.shared_ff) + (uint64_t)H * 4 + (uint64_t)B * (2ull * H + d.n_expert + 2ull * d.shared_ff) * 4);
         const int W = e->ep ? e->ep->world : 1, RW = B * W;   // rows the expert kernels see: ours, or every rank's (expert parallel)
@@ -845,6 +889,13 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             const float scale = 1.0f / sqrtf((float)d.head_dim);
             const int nwa = 8, ns = n_tok > 1 ? e->n_split_rows : e->n_split;
             const size_t smem_a = (size_t)nwa * 8 * 2 * 4 + (size_t)nwa * 8 * d.head_dim * 4;
+            if (exact_attention_ok(e) && e->scores_cap >= (size_t)R * d.n_head * e->n_ctx) {
+                uint32_t top = 0;
+                for (int sq = 0; sq < n_seq; ++sq) top = std::max(top, e->host_pos[sq] + (uint32_t)n_tok);
+                if (n_tok == 1) top = e->n_ctx;        // a decode pass is replayed from a graph: its launches must hold any length
+                enqueue_exact_attention(e, st, false, a.kslab, a.vslab, a.slab_stride, R, n_tok, (int)std::min<uint32_t>(top, e->n_ctx));
+                launches += 2;
+            } else {
             {
                 dim3 grid(d.n_head_kv, R, ns);
 #define ATT_CASE(HD)                                                                                                          \
@@ -859,6 +910,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             }
             k_attn_combine_rows<<<R * d.n_head, d.head_dim, 0, st>>>(e->part_acc, e->part_ml, ns, d.head_dim, e->gate, e->npos, d.n_head,
                                                                     e->aq, e->as); launches++;
+            }
             gemm(L.wo, e->aq, e->as, e->x, H, 1);
         }
         // routed FFN
@@ -1006,6 +1058,7 @@ static int engine_create(itb_model* m, uint32_t n_ctx, uint32_t n_seq, int world
               dalloc(E, &e->ep->agree_dev, W + 1) && cudaMallocHost(&e->ep->agree_host, (W + 1) * 4) == cudaSuccess)) { for (void* p : e->allocs) cudaFree(p); delete e->ep; return 1; }
     }
     if (cudaStreamSynchronize(c->stream) != cudaSuccess) { itb_fail_msg(c, "engine: device error during set-up"); return 1; }
+    if (exact_attention_ok(E) && !ensure_scores(E, B)) { for (void* p : e->allocs) cudaFree(p); return 1; }
     *out = e.release();
     return 0;
 }
@@ -1105,7 +1158,7 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     if (e->ep) { if (e->ep->comm && !e->ep->broken) nccl_api().CommDestroy(e->ep->comm); cudaFreeHost(e->ep->agree_host); delete e->ep; e->ep = nullptr; }
     if (e->tier) { cudaFreeHost(e->tier->slot_map_host); cudaFreeHost(e->tier->ids_host); cudaFreeHost(e->tier->s2_stage); delete e->tier->g; delete e->tier; e->tier = nullptr; }
     for (void* p : e->allocs) cudaFree(p);
-    cudaFree(e->history); cudaFree(e->prompt);
+    cudaFree(e->history); cudaFree(e->prompt); cudaFree(e->scores);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
     delete e;
 }
@@ -1200,7 +1253,7 @@ static bool mega_prepare(itb_engine* e) {
     size_t terms_need = std::max<size_t>({(size_t)gdn_rows * (sk + 1) + (size_t)MG_MAX_LOCAL_HEADS * (2 * sk + 2),
                                           (size_t)((d.n_expert + 31) & ~31u) + 2 * MOE_CAND,
                                           (size_t)group * parts * (2 + d.head_dim), (size_t)d.head_dim});
-    int tw = std::max(560, max_nt + 1);
+    int tw = std::max(560, 2 * (max_nt + 1));   // a warp holds at least two rows' terms
     while ((size_t)MG_NW * tw < terms_need) tw += 16;
     const size_t terms = up((size_t)MG_NW * tw * 4);
     size_t row_max = std::max<size_t>({(size_t)H * 4, (size_t)H + H / 16, (size_t)vd + vd / 16, (size_t)qd + qd / 16, (size_t)sff + sff / 16, (size_t)sk * 4});
@@ -1477,10 +1530,16 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
         if (cudaMalloc(&e->prompt, n * e->B * 4) != cudaSuccess) { e->prompt = nullptr; ok = itb_fail_msg(c, "prefill: out of device memory for the prompt"); }
         else e->prompt_cap = n * e->B;
     }
+    // exact mode: room for the scores of a whole pass (up to 2 GB; beyond that the pass keeps the split-K attention)
+    if (ok && exact_attention_ok(e) && getenv("ITB_PREFILL_STEPWISE") == nullptr) {
+        const size_t rows = e->B * std::min(std::max<size_t>(1, e->R / e->B), n);
+        if (rows * e->m->d.n_head * e->n_ctx * 4 <= ((size_t)2 << 30)) ok = ensure_scores(e, rows);
+    }
     ok = ok && steps_ready(e, 0);   // a one-token pass replays the step graph: have it captured before anything is enqueued
     if (!ep_agree(e, ok)) return 1;
     const bool stepwise = getenv("ITB_PREFILL_STEPWISE") != nullptr;
     const size_t chunk = stepwise ? 1 : std::max<size_t>(1, e->R / e->B);
+
     // token ids laid out pass by pass, row-major inside a pass: [pass][seq][t]
     std::vector<int32_t> tr(n * e->B);
     size_t off = 0;

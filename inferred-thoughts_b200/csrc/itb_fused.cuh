@@ -69,6 +69,21 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
         for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
     }
+    // F32 rows: one row per warp, handed out from the far end of the grid's warps (serial-k fold or shuffle tree inside).
+    {
+        const int ngw = gridDim.x * nw, gw = ngw - 1 - (wid * (int)gridDim.x + (int)blockIdx.x);   // consecutive rows on different blocks
+        int rbase = 0;
+#pragma unroll 1
+        for (int m = 0; m < p.nf; ++m) {
+            float* o = p.fout[m] + (size_t)b * p.fstride[m];
+            for (int r = gw - rbase; r < p.f[m].n_out; r += ngw) {
+                if (r < 0) continue;
+                if (p.exact) f32_rows<true>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; }, tfl);
+                else f32_rows<false>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; });
+            }
+            rbase = (rbase + p.f[m].n_out) % ngw;
+        }
+    }
     int base = 0;
 #pragma unroll 1
     for (int m = 0; m < p.nq; ++m) {
@@ -99,35 +114,6 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         base += p.q[m].n_out;
     }
     TL(TLK_IN_PROJ, 4);
-    // F32 rows. Serial-k mode: units of 32 rows, unit u on warp 0 of block u (it owns the tile). Otherwise one
-    // row per warp, handed out from the far end of the grid's warps.
-    if (p.exact) {
-        if (wid == 0) {
-            int ubase = 0;
-#pragma unroll 1
-            for (int m = 0; m < p.nf; ++m) {
-                int units = (p.f[m].n_out + 31) / 32;
-                float* o = p.fout[m] + (size_t)b * p.fstride[m];
-                for (int u = (int)blockIdx.x - ubase; u < units; u += gridDim.x) {
-                    if (u < 0) continue;
-                    f32_rows<true>(p.f[m].w, n, u * 32, min(p.f[m].n_out, u * 32 + 32), xn, tile, [&](int row, float v) { o[row] = v; });
-                }
-                ubase = (ubase + units) % gridDim.x;
-            }
-        }
-    } else {
-        const int ngw = gridDim.x * nw, gw = ngw - 1 - (blockIdx.x * nw + wid);
-        int rbase = 0;
-#pragma unroll 1
-        for (int m = 0; m < p.nf; ++m) {
-            float* o = p.fout[m] + (size_t)b * p.fstride[m];
-            for (int r = gw - rbase; r < p.f[m].n_out; r += ngw) {
-                if (r < 0) continue;
-                f32_rows<false>(p.f[m].w, n, r, r + 1, xn, tile, [&](int row, float v) { o[row] = v; });
-            }
-            rbase = (rbase + p.f[m].n_out) % ngw;
-        }
-    }
     TL(TLK_IN_PROJ, 5);
 }
 // br a multiple of the pass size 2 * (32 >> gsh)

@@ -328,25 +328,55 @@ __device__ __forceinline__ void fp4_rows(const uint8_t* nib, const uint8_t* sc, 
 }
 
 // ---- F32 rows --------------------------------------------------------------------------------------
-// EXACT: serial-k left fold per output like the CPU path (src/ops/naive.rs:845-849); 32 rows per warp,
-// tiles staged through shared memory so global reads stay coalesced. tile: warp-private 32*33 floats.
-// Otherwise: lane-strided partial sums and a shuffle tree (order differs, value within rounding).
+// EXACT: serial-k left fold per output like the CPU path (src/ops/naive.rs:845-849). A warp takes one row at a time: the lanes
+// fetch the weights (coalesced) and put the products w[k] * x[k] of a tile of the row into the warp's shared scratch, then
+// lane 0 adds the tile's terms in k order -- the adds are the only dependent chain (n_in of them, about 4 cycles each);
+// chains of different warps overlap. `tile`: warp-private scratch of `tile_floats` floats (at least 128).
+// Otherwise: lane-strided partial sums and a shuffle tree (order differs, value within rounding); `tile` unused.
 template <bool EXACT, class Epi>
-__device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, int r0, int r1, const float* x, float* tile, Epi epi) {
+__device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, int r0, int r1, const float* x, float* tile, Epi epi, int tile_floats = 1024) {
     const int lane = threadIdx.x & 31;
     if (EXACT) {
-        for (int r = r0; r < r1; r += 32) {
+        float* t16 = (float*)(((uintptr_t)tile + 15) & ~(uintptr_t)15);        // 16-byte aligned view of the scratch
+        const int T = max(128, (tile_floats - 4) / 128 * 128);
+#pragma unroll 1
+        for (int r = r0; r < r1; ++r) {
+            const float* p = w + (size_t)r * n_in;
             float sum = 0.0f;
-            for (int k0 = 0; k0 < n_in; k0 += 32) {
-#pragma unroll 8
-                for (int rr = 0; rr < 32; ++rr)
-                    tile[rr * 33 + lane] = (r + rr < r1 && k0 + lane < n_in) ? __ldg(w + (size_t)(r + rr) * n_in + k0 + lane) : 0.0f;
+#pragma unroll 1
+            for (int t0 = 0; t0 < n_in; t0 += T) {
+                const int tn = min(T, n_in - t0);
+#pragma unroll 4
+                for (int k = lane * 4; k < tn; k += 128) {
+                    if (k + 4 <= tn) {
+                        const float4 wv = __ldg((const float4*)(p + t0 + k)), xv = *(const float4*)(x + t0 + k);
+                        *(float4*)(t16 + k) = make_float4(wv.x * xv.x, wv.y * xv.y, wv.z * xv.z, wv.w * xv.w);
+                    } else {
+                        for (int j = k; j < tn; ++j) t16[j] = __ldg(p + t0 + j) * x[t0 + j];
+                    }
+                }
                 __syncwarp();
-                int kn = min(32, n_in - k0);
-                for (int k = 0; k < kn; ++k) sum += tile[lane * 33 + k] * x[k0 + k];
+                if (lane == 0) {
+                    // the chain: 16 terms are in registers while the next 16 are on their way from shared memory
+                    int k = 0;
+                    if (tn >= 32) {
+                        float4 a0 = *(const float4*)(t16), a1 = *(const float4*)(t16 + 4), a2 = *(const float4*)(t16 + 8), a3 = *(const float4*)(t16 + 12);
+#pragma unroll 1
+                        for (; k + 32 <= tn; k += 16) {
+                            const float4 b0 = *(const float4*)(t16 + k + 16), b1 = *(const float4*)(t16 + k + 20), b2 = *(const float4*)(t16 + k + 24), b3 = *(const float4*)(t16 + k + 28);
+                            sum += a0.x; sum += a0.y; sum += a0.z; sum += a0.w; sum += a1.x; sum += a1.y; sum += a1.z; sum += a1.w;
+                            sum += a2.x; sum += a2.y; sum += a2.z; sum += a2.w; sum += a3.x; sum += a3.y; sum += a3.z; sum += a3.w;
+                            a0 = b0; a1 = b1; a2 = b2; a3 = b3;
+                        }
+                        sum += a0.x; sum += a0.y; sum += a0.z; sum += a0.w; sum += a1.x; sum += a1.y; sum += a1.z; sum += a1.w;
+                        sum += a2.x; sum += a2.y; sum += a2.z; sum += a2.w; sum += a3.x; sum += a3.y; sum += a3.z; sum += a3.w;
+                        k += 16;
+                    }
+                    for (; k < tn; ++k) sum += t16[k];
+                }
                 __syncwarp();
             }
-            if (r + lane < r1) epi(r + lane, sum);
+            if (lane == 0) epi(r, sum);
         }
     } else {
 #pragma unroll 1

@@ -368,12 +368,10 @@ __global__ void k_matmul_f32(DevF32 w, const float* x, float* out) {
     __syncthreads();
     int b0, b1, r0, r1;
     share(w.n_out, gridDim.x, blockIdx.x, b0, b1);
-    // exact mode walks 32 rows per warp pass: hand out rows in multiples of 32
     int nw = blockDim.x >> 5, wid = threadIdx.x >> 5;
-    if (EXACT) { int per = ((b1 - b0 + nw - 1) / nw + 31) / 32 * 32; r0 = min(b1 - b0, wid * per); r1 = min(b1 - b0, r0 + per); }
-    else share(b1 - b0, nw, wid, r0, r1);
+    share(b1 - b0, nw, wid, r0, r1);
     float* o = out + t * w.n_out;
-    f32_rows<EXACT>(w.w, w.n_in, b0 + r0, b0 + r1, xs, tile, [&](int row, float v) { o[row] = v; });
+    f32_rows<EXACT>(w.w, w.n_in, b0 + r0, b0 + r1, xs, tile, [&](int row, float v) { o[row] = v; }, 32 * 33);
 }
 
 // ---- attention, split over positions (flash-decoding form; tolerance class like the reference's

@@ -1,6 +1,7 @@
 // The op-level seam: one extern "C" entry per method of the reference's backend trait
 // (src/ops/mod.rs:489-1426), operating on host-address-keyed device mirrors.
 #include "itb_kernels.cuh"
+#include "itb_attn_exact.cuh"
 #include "itb_rows.cuh"
 
 static inline unsigned blocks_for(size_t n, int per = 256) { return (unsigned)((n + per - 1) / per); }
@@ -376,6 +377,33 @@ extern "C" void itb_attend(itb_ctx* c, const itb_attn* a, float* out, size_t out
     uint16_t* kd = itb_kv_slab(c, a->k, a->slab_len); uint16_t* vd = itb_kv_slab(c, a->v, a->slab_len);
     float* od = itb_mirror_out(c, out, out_len);
     if (!qd || !kd || !vd || !od) return;
+    if (c->exact && a->kv_dim % 8 == 0 && a->n_head / a->n_head_kv <= 8 && (a->head_dim == 64 || a->head_dim == 128 || a->head_dim == 256) &&
+        attn_out_exact_smem((int)a->n_pos) <= 200 * 1024) {
+        // the CPU path's own order (src/ops/naive.rs:420-466): scores, then softmax and weighted values per 32 dimensions of a head
+        const size_t need_s = n_q * a->n_head * a->n_pos;
+        if (c->tmp_cap < need_s) {
+            cudaFree(c->tmp_f32);
+            if (cudaMalloc(&c->tmp_f32, need_s * 4) != cudaSuccess) { c->tmp_f32 = nullptr; c->tmp_cap = 0; itb_fail_msg(c, "cudaMalloc(attention scores)"); return; }
+            c->tmp_cap = need_s;
+        }
+        const int group = (int)(a->n_head / a->n_head_kv);
+        AxScores sp{};
+        sp.q = qd; sp.kslab = kd; sp.slab_stride = 0; sp.rows_per_seq = (int)n_q; sp.n_pos_dev = nullptr; sp.n_pos_last = (int)a->n_pos; sp.n_q = (int)n_q;
+        sp.kv_dim = (int)a->kv_dim; sp.hd = (int)a->head_dim; sp.n_head = (int)a->n_head; sp.n_head_kv = (int)a->n_head_kv; sp.scale = a->scale; sp.bf16 = c->kv_bf16;
+        sp.scores = c->tmp_f32; sp.s_stride = (int)a->n_pos;
+        k_attn_scores_exact<<<dim3((unsigned)((a->n_pos + AX_TP - 1) / AX_TP), (unsigned)a->n_head_kv, (unsigned)n_q), AX_TP * group,
+                              attn_scores_exact_smem((int)a->head_dim, group), c->stream>>>(sp);
+        ITB_LAUNCHED(c);
+        AxOut op{};
+        op.scores = c->tmp_f32; op.s_stride = (int)a->n_pos; op.vslab = vd; op.slab_stride = 0; op.rows_per_seq = (int)n_q; op.n_pos_dev = nullptr;
+        op.n_pos_last = (int)a->n_pos; op.n_q = (int)n_q; op.kv_dim = (int)a->kv_dim; op.hd = (int)a->head_dim; op.n_head = (int)a->n_head;
+        op.n_head_kv = (int)a->n_head_kv; op.bf16 = c->kv_bf16; op.gate = nullptr; op.out = od; op.out_q = nullptr; op.out_s = nullptr;
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(k_attn_out_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024); attr = true; }
+        k_attn_out_exact<<<dim3((unsigned)(a->head_dim / 32), (unsigned)a->n_head, (unsigned)n_q), 256, attn_out_exact_smem((int)a->n_pos), c->stream>>>(op);
+        ITB_LAUNCHED(c);
+        return;
+    }
     int n_split = (int)std::max<size_t>(1, std::min<size_t>((a->n_pos + 63) / 64, (size_t)(2 * c->sm_count) / (a->n_head_kv * n_q) + 1));
     size_t need = n_q * a->n_head * n_split * (a->head_dim + 2);
     if (c->tmp_cap < need) {

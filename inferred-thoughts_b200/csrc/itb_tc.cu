@@ -1,0 +1,421 @@
+// The 5th-generation tensor-core path: tcgen05.mma kind::mxf4nvf4 (E2M1 values with one UE4M3 scale per 16 elements on BOTH
+// operands, f32 accumulators in tensor memory), operands in shared memory behind matrix descriptors, scale factors copied
+// into tensor memory by tcgen05.cp, completion through an mbarrier (tcgen05.commit), accumulators read back by tcgen05.ld.
+//
+// This file holds the measured ceiling of that instruction -- the denominator of every "fraction of the FP4 tensor peak" --
+// by the reference's own method for its sm_120 instructions (tests/cuda_ops.rs:5899-5925 there): back-to-back MMAs on operands
+// that never change, nothing but the MMA in the loop, accumulators verified afterwards.
+//
+// Every wait is bounded; a kernel that gives up frees its tensor memory and reports through its status word.
+#include "itb_internal.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > limit_ns) return false;
+    }
+}
+// Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` = bytes between the two 16-byte
+// K chunks of a row, `sbo` = bytes between 8-row groups; version 1 (this architecture) in bits 46-47.
+__device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((smem_addr >> 4) & 0x3fff) | ((uint64_t)((lbo >> 4) & 0x3fff) << 16) | ((uint64_t)((sbo >> 4) & 0x3fff) << 32) | (1ull << 46);
+}
+// Instruction descriptor of kind::mxf4nvf4: E2M1 x E2M1 (format code 1), UE4M3 scales (0), both operands K-major, M x N.
+__host__ __device__ constexpr uint32_t tc_idesc_fp4(int m, int n) { return (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
+
+__device__ __forceinline__ void tc_mma_fp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p; }\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+}
+
+// N = 128 or 256 accumulator columns; operands: every E2M1 code 1.0 (0x2), every scale 1.0 (0x38): each accumulator ends at
+// 64 * iters exactly.
+template <int N>
+__global__ void __launch_bounds__(128) k_fp4_ceiling(int iters, int* status, unsigned long long* cycles) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ unsigned long long s_bar;
+    __shared__ uint32_t s_tmem;
+    unsigned char* a = smem;                      // 128 x 64 e2m1: 4096 B
+    unsigned char* b = a + 4096;                  // N x 64 e2m1
+    unsigned char* sfa = b + N * 32;              // 128 rows x 4 scales: 512 B
+    unsigned char* sfb = sfa + 512;               // N rows x 4 scales
+    const int tid = threadIdx.x, wid = tid >> 5;
+    for (int i = tid; i < (4096 + N * 32) / 4; i += 128) ((uint32_t*)a)[i] = 0x22222222u;
+    for (int i = tid; i < (512 + N * 4) / 4; i += 128) ((uint32_t*)sfa)[i] = 0x38383838u;
+    const uint32_t bar = tc_smem(&s_bar);
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // the generic-proxy fills above, before the tensor core reads them
+    __syncthreads();
+    if (wid == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tm = s_tmem, d_tm = tm, sfa_tm = tm + 256, sfb_tm = tm + 264;
+    bool ok = true;
+    unsigned long long c0 = 0, c1 = 0;
+    if (tid == 0) {
+        // scale factors into tensor memory: 32 rows x 16 bytes per copy, replicated to the four lane quarters
+        asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sfa_tm), "l"(tc_desc(tc_smem(sfa), 128, 128)) : "memory");
+        for (int k = 0; k < N / 128; ++k)
+            asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sfb_tm + 4 * k), "l"(tc_desc(tc_smem(sfb) + 512 * k, 128, 128)) : "memory");
+        const uint64_t da = tc_desc(tc_smem(a), 2048, 128), db = tc_desc(tc_smem(b), N * 16, 128);
+        const uint32_t idesc = tc_idesc_fp4(128, N);
+        c0 = clock64();
+        for (int i = 0; i < iters; ++i) tc_mma_fp4(d_tm, da, db, idesc, sfa_tm, sfb_tm, i ? 1u : 0u);
+        asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+    }
+    ok = tc_mbar_wait(bar, 0, 2000000000ull);
+    c1 = clock64();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (ok) {
+        // verify: lane (row) 32 * warp + lane of this warp, all N columns
+        const float want = 64.0f * (float)iters;
+        for (int c = 0; c < N && ok; c += 8) {
+            uint32_t r[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                         : "r"(d_tm + ((uint32_t)(wid * 32) << 16) + (uint32_t)c) : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 8; ++j) if (__uint_as_float(r[j]) != want) ok = false;
+        }
+        if (!ok) atomicCAS(status, 0, 2);          // accumulators are not 64 * iters
+    } else atomicCAS(status, 0, 1);                // the MMAs never completed
+    if (tid == 0 && cycles) cycles[blockIdx.x] = c1 - c0;
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+}
+
+}  // namespace
+
+// Measured ceiling of tcgen05.mma kind::mxf4nvf4 (M 128, N `n` = 128 or 256, K 64 per instruction) with one block per SM:
+// `iters` accumulating MMAs per block, timed with CUDA events over `reps` launches (best taken). tflops_out: dense FP4
+// TFLOP/s (2 * M * N * K per MMA); status_out: 0 accumulators verified, 1 a wait ran out, 2 accumulators wrong.
+extern "C" int itb_fp4_ceiling(itb_ctx* c, int n, int iters, int reps, double* tflops_out, int* status_out, double* mma_cycles_out) {
+    if ((n != 128 && n != 256) || iters < 1 || iters > 200000 || reps < 1) { itb_fail_msg(c, "fp4_ceiling: n must be 128 or 256, 1 <= iters <= 200000"); return 1; }
+    int* status = nullptr; unsigned long long* cyc = nullptr;
+    const int blocks = c->sm_count;
+    if (cudaMalloc(&status, 4) != cudaSuccess || cudaMalloc(&cyc, (size_t)blocks * 8) != cudaSuccess) { cudaFree(status); itb_fail_msg(c, "fp4_ceiling: out of device memory"); return 1; }
+    cudaMemsetAsync(status, 0, 4, c->stream);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    const size_t smem = 4096 + (size_t)n * 32 + 512 + (size_t)n * 4 + 128;
+    float best = 1e30f;
+    for (int r = 0; r < reps + 1; ++r) {           // the first launch warms up
+        cudaEventRecord(e0, c->stream);
+        if (n == 256) k_fp4_ceiling<256><<<blocks, 128, smem, c->stream>>>(iters, status, cyc);
+        else k_fp4_ceiling<128><<<blocks, 128, smem, c->stream>>>(iters, status, cyc);
+        cudaEventRecord(e1, c->stream);
+        ITB_LAUNCHED(c);
+        if (cudaEventSynchronize(e1) != cudaSuccess) break;
+        float ms = 0.0f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (r > 0 && ms < best) best = ms;
+    }
+    int st = -1;
+    std::vector<unsigned long long> hc(blocks, 0);
+    cudaError_t err = cudaMemcpy(&st, status, 4, cudaMemcpyDeviceToHost);
+    if (err == cudaSuccess) err = cudaMemcpy(hc.data(), cyc, (size_t)blocks * 8, cudaMemcpyDeviceToHost);
+    cudaFree(status); cudaFree(cyc);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (err != cudaSuccess) { itb_fail(c, "fp4_ceiling", err); return 1; }
+    unsigned long long worst = 0;
+    for (auto v : hc) worst = std::max(worst, v);
+    if (status_out) *status_out = st;
+    if (tflops_out) *tflops_out = 2.0 * 128.0 * n * 64.0 * (double)iters * blocks / ((double)best * 1e-3) / 1e12;
+    if (mma_cycles_out) *mma_cycles_out = (double)worst / iters;
+    return 0;
+}
+
+// =====================================================================================================
+// Routed experts on the FP4 tensor cores (many tokens per pass: prefill and large batches)
+// =====================================================================================================
+// The reference's default device path quantises the activations to FP4 too and multiplies FP4 x FP4 on its tensor cores
+// (kernels/nvfp4.cuh:232, :344, :434 there; CPU statement: Fp4Row::from_f32 and dot_nvfp4_fp4, src/ops/naive.rs:755-837).
+// Here: the same activation quantiser, bit for bit, writing straight into tensor-core operand tiles; the expert weights
+// re-tiled once into the same form; one block-scaled tcgen05 GEMM per (expert, 128 weight rows, up to 128 tokens) with
+// operands fetched by bulk asynchronous copies (whole tiles are contiguous in HBM) and accumulators in tensor memory.
+// Results are tolerance class against dot_nvfp4_fp4 (the tensor core's accumulation order inside a 64-wide step is its
+// own), exactly as the reference holds its own FP4 path (src/ops/cuda/mod.rs:239-248 there).
+//
+// Operand tile ("K64 block"): rows x 64 E2M1 values = rows x 32 bytes, stored as [2 chunks of 16 bytes][rows / 8][8 rows][16 B]
+// (K-major, no swizzle: 8-row x 16-byte core matrices; descriptor: leading offset = rows * 16, stride offset = 128).
+// Scale tile: 128 rows x 4 scales per K64 block = 512 B at (row % 32) * 16 + (row / 32) * 4 + scale (the layout
+// tcgen05.cp 32x128b.warpx4 spreads over the four lane quarters of tensor memory).
+namespace {
+
+constexpr int TC_M = 128;          // weight rows per tile
+constexpr int TC_NMAX = 128;       // tokens per tile at most
+constexpr int TC_KS = 4;           // K64 blocks per pipeline stage
+constexpr int TC_STAGES = 4;
+
+// ---- E2M1 / UE4M3 helpers (src/ops/naive.rs:794-806, src/quant/mod.rs:265-336) ----
+__device__ __forceinline__ float ue4m3_half(uint32_t c) { return ue4m3_half_dev(c & 0x7f); }
+// Round to nearest even onto the UE4M3 grid, saturating at 0x7e (448); non-positive and NaN give 0.
+__device__ __forceinline__ int f32_to_ue4m3_rn(float x) {
+    if (!(x > 0.0f)) return 0;
+    if (x >= 448.0f) return 0x7e;
+    // codes are monotone in value: binary search on 2 * ue4m3_half(code), then the tie rule on the code's parity
+    int lo = 0, hi = 0x7e;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (2.0f * ue4m3_half((uint32_t)mid) <= x) lo = mid; else hi = mid; }
+    const double v = (double)x, below = v - 2.0 * (double)ue4m3_half((uint32_t)lo), above = 2.0 * (double)ue4m3_half((uint32_t)hi) - v;
+    return (below < above || (below == above && (lo & 1) == 0)) ? lo : hi;
+}
+// Nearest of {0, .5, 1, 1.5, 2, 3, 4, 6} to |x| * inv, the lower one on ties; sign in bit 3.
+__device__ __forceinline__ uint32_t e2m1_of(float x, float inv) {
+    const float ax = fabsf(x) * inv;
+    const uint32_t m = (uint32_t)(ax > 0.25f) + (uint32_t)(ax > 0.75f) + (uint32_t)(ax > 1.25f) + (uint32_t)(ax > 1.75f) + (uint32_t)(ax > 2.5f) +
+                       (uint32_t)(ax > 3.5f) + (uint32_t)(ax > 5.0f);
+    return m | (x < 0.0f ? 8u : 0u);
+}
+// One 16-element block: the scale code of least squared error among the seed and its four neighbours, then the codes.
+__device__ __forceinline__ void fp4_quant_block(const float* blk, uint32_t* scale_code, uint32_t* codes_lo, uint32_t* codes_hi) {
+    const float kv[8] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f};
+    float v[16];
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) { v[j] = blk[j]; amax = fmaxf(amax, fabsf(v[j])); }
+    const int seed = f32_to_ue4m3_rn(amax / 6.0f);
+    const int offs[5] = {0, -1, 1, -2, 2};
+    float best_err = 3.40282347e+38f, best_scale = 0.0f;
+    int best_code = 0;
+#pragma unroll 1
+    for (int o = 0; o < 5; ++o) {
+        const int code = seed + offs[o];
+        if (code < 0 || code > 0x7e) continue;
+        const float sc = ue4m3_half((uint32_t)code);
+        const float inv = sc > 0.0f ? 0.5f / sc : 0.0f;
+        float err = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const uint32_t q = e2m1_of(v[j], inv);
+            const float d = fabsf(v[j]) - kv[q & 7] * sc;
+            err = __fmaf_rn(d, d, err);
+        }
+        if (err < best_err) { best_err = err; best_code = code; best_scale = sc; }
+    }
+    const float inv = best_scale > 0.0f ? 0.5f / best_scale : 0.0f;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { lo |= e2m1_of(v[j], inv) << (4 * j); hi |= e2m1_of(v[8 + j], inv) << (4 * j); }
+    *scale_code = (uint32_t)best_code; *codes_lo = lo; *codes_hi = hi;
+}
+
+// Plain form (tests): codes one per byte, scales one per 16 elements, like the oracle's record.
+__global__ void k_fp4_quant_plain(const float* x, size_t n_blocks, uint8_t* scales, uint8_t* codes) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint32_t sc, lo, hi;
+    fp4_quant_block(x + b * 16, &sc, &lo, &hi);
+    scales[b] = (uint8_t)sc;
+    for (int j = 0; j < 8; ++j) { codes[b * 16 + j] = (lo >> (4 * j)) & 15; codes[b * 16 + 8 + j] = (hi >> (4 * j)) & 15; }
+}
+
+// ---- tiles of one pass ----
+// A tile = up to TC_NMAX pairs of one expert (slots [n0, n0 + cnt) of the expert-sorted pair list), padded to a multiple of 16.
+struct TcTile { int expert, n0, cnt, npad; unsigned b_off, sf_off; };   // offsets in padded rows / in 512-byte scale tiles
+// pair_off[e .. e+1): the expert's slots. One thread walks the experts (a few hundred), then all threads label the slots.
+__global__ void k_tc_build_tiles(const int* pair_off, int n_expert, int expert_lo, int expert_cnt, TcTile* tiles, int* n_tiles_out, int max_tiles, int* slot_tile, int k_blocks) {
+    __shared__ int s_nt;
+    if (threadIdx.x == 0) {
+        int nt = 0; unsigned boff = 0, soff = 0;
+        for (int e = 0; e < n_expert; ++e) {
+            const bool here = e >= expert_lo && e < expert_lo + expert_cnt;
+            const int a = pair_off[e], z = pair_off[e + 1];
+            for (int n0 = a; n0 < z && here; n0 += TC_NMAX) {
+                const int cnt = min(TC_NMAX, z - n0), npad = (cnt + 15) & ~15;
+                if (nt < max_tiles) tiles[nt] = TcTile{e, n0, cnt, npad, boff, soff};
+                nt++; boff += (unsigned)npad; soff += (unsigned)k_blocks;     // one 512-byte scale tile per K64 block (npad <= 128)
+            }
+        }
+        s_nt = min(nt, max_tiles);
+        *n_tiles_out = s_nt;
+    }
+    __syncthreads();
+    for (int t = 0; t < s_nt; ++t)
+        for (int i = threadIdx.x; i < tiles[t].cnt; i += blockDim.x) slot_tile[tiles[t].n0 + i] = t;
+}
+
+// Activation rows -> FP4 operand tiles. One thread per (slot, 16-element block). src row of a slot: pair_list[slot] / rows_div
+// (rows_div = n_used when the rows are tokens shared by a token's picks, 1 when there is a row per pair).
+__global__ void k_tc_quant_tiles(const float* x, int n_in, const int* pair_list, int rows_div, int n_slots, const TcTile* tiles, const int* slot_tile,
+                                 uint8_t* b_img, uint8_t* sf_img) {
+    const int bpr = n_in / 16;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_slots * bpr) return;
+    const int slot = (int)(idx / bpr), b = (int)(idx % bpr);
+    const TcTile t = tiles[slot_tile[slot]];
+    const int n = slot - t.n0;
+    uint32_t sc, lo, hi;
+    fp4_quant_block(x + (size_t)(pair_list[slot] / rows_div) * n_in + b * 16, &sc, &lo, &hi);
+    const int kb = b >> 2, q = b & 3;            // K64 block, 16-element quarter of it: bytes [8q, 8q + 8) of the row's 32
+    uint8_t* blk = b_img + (size_t)t.b_off * (n_in / 2) + (size_t)kb * (t.npad * 32);
+    uint8_t* dst = blk + (q >> 1) * (t.npad * 16) + (n >> 3) * 128 + (n & 7) * 16 + (q & 1) * 8;
+    *(uint2*)dst = make_uint2(lo, hi);
+    sf_img[((size_t)t.sf_off + kb) * 512 + (n & 31) * 16 + (n >> 5) * 4 + q] = (uint8_t)sc;
+}
+
+// Expert weights -> operand tiles, once per stack. One thread per (expert, row, K64 block).
+// out: [expert][row tile][K64 block][4096 B]; scales: [expert][row tile][K64 block][512 B].
+__global__ void k_tc_tile_weights(const uint8_t* nib, const uint8_t* sc, int n_expert, int n_out, int n_in, uint8_t* w_img, uint8_t* sf_img) {
+    const int kbs = n_in / 64;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)n_expert * n_out * kbs) return;
+    const int kb = (int)(idx % kbs); const size_t er = idx / kbs;
+    const int row = (int)(er % n_out); const int e = (int)(er / n_out);
+    const int mt = row / TC_M, r = row % TC_M;
+    const uint4* src = (const uint4*)(nib + ((size_t)e * n_out + row) * (n_in / 2) + kb * 32);
+    uint8_t* blk = w_img + (((size_t)e * (n_out / TC_M) + mt) * kbs + kb) * 4096;
+    *(uint4*)(blk + (r >> 3) * 128 + (r & 7) * 16) = src[0];
+    *(uint4*)(blk + 2048 + (r >> 3) * 128 + (r & 7) * 16) = src[1];
+    const uint32_t s4 = *(const uint32_t*)(sc + ((size_t)e * n_out + row) * (n_in / 16) + kb * 4);
+    *(uint32_t*)(sf_img + (((size_t)e * (n_out / TC_M) + mt) * kbs + kb) * 512 + (r & 31) * 16 + (r >> 5) * 4) = s4;
+}
+
+// ---- the GEMM ----
+struct TcGemm {
+    const uint8_t *wg_img, *wg_sf, *wu_img, *wu_sf;      // weights of the (gate, up) pair, or of the one matrix (wu_* null)
+    const float *s2g, *s2u;                              // per-expert second scales (or null)
+    int expert_lo;
+    const uint8_t *b_img, *b_sf;                         // this pass's activation tiles
+    const TcTile* tiles; const int* n_tiles; const int* pair_list;
+    int n_out, n_in;                                     // rows of one matrix, K
+    float* out; int out_stride;                          // out[pair][n_out]
+    int* status;
+};
+__device__ __forceinline__ void tc_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// grid (max tiles, n_out / 128); block 192: warps 0-3 epilogue (tensor-memory lane quarter = warp), warp 4 producer, warp 5 MMA.
+template <bool GLU>
+__global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc;
+    __shared__ uint32_t s_tmem;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    if ((int)blockIdx.x >= *p.n_tiles) return;
+    const TcTile t = p.tiles[blockIdx.x];
+    const int mt = blockIdx.y, kbs = p.n_in / 64, n_stage = kbs / TC_KS, el = t.expert - p.expert_lo;
+    const uint32_t a_bytes = TC_KS * 4096, b_bytes = (uint32_t)t.npad * 32 * TC_KS, sf_bytes = TC_KS * 512;
+    // stage layout: A_g | A_u | B | SFA_g | SFA_u | SFB
+    const uint32_t o_au = a_bytes, o_b = a_bytes * (GLU ? 2 : 1), o_sfg = o_b + TC_NMAX * 32 * TC_KS, o_sfu = o_sfg + sf_bytes, o_sfb = o_sfu + (GLU ? sf_bytes : 0);
+    const uint32_t stage_bytes = o_sfb + sf_bytes;
+    const uint32_t sbase = tc_smem(smem);
+    if (tid == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_empty[s])) : "memory");
+        }
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_acc)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (wid == 5) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tm = s_tmem;
+    // tensor memory: D_g at 0, D_u at 128, scale factors from 256: per stage slot 48 columns (SFA_g 16, SFA_u 16, SFB 16)
+    const uint32_t d_g = tm, d_u = tm + 128, sf0 = tm + 256;
+    bool ok = true;
+    if (wid == 4 && lane == 0) {
+        const size_t w_tile = ((size_t)el * (p.n_out / TC_M) + mt) * kbs;
+        for (int st = 0; st < n_stage && ok; ++st) {
+            const int s = st % TC_STAGES;
+            if (st >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((st / TC_STAGES) - 1) & 1, 1000000000ull);
+            if (!ok) break;
+            const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * stage_bytes;
+            const uint32_t total = a_bytes * (GLU ? 2 : 1) + b_bytes + sf_bytes * (GLU ? 3 : 2);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(total) : "memory");
+            const size_t kb0 = (size_t)st * TC_KS;
+            tc_bulk(dst, p.wg_img + (w_tile + kb0) * 4096, a_bytes, full);
+            tc_bulk(dst + o_sfg, p.wg_sf + (w_tile + kb0) * 512, sf_bytes, full);
+            if (GLU) {
+                tc_bulk(dst + o_au, p.wu_img + (w_tile + kb0) * 4096, a_bytes, full);
+                tc_bulk(dst + o_sfu, p.wu_sf + (w_tile + kb0) * 512, sf_bytes, full);
+            }
+            tc_bulk(dst + o_b, p.b_img + (size_t)t.b_off * (p.n_in / 2) + kb0 * (t.npad * 32), b_bytes, full);
+            tc_bulk(dst + o_sfb, p.b_sf + ((size_t)t.sf_off + kb0) * 512, sf_bytes, full);
+        }
+        if (!ok) atomicCAS(p.status, 0, 3);
+    } else if (wid == 5 && lane == 0) {
+        const uint32_t idesc = tc_idesc_fp4(TC_M, t.npad);
+        for (int st = 0; st < n_stage && ok; ++st) {
+            const int s = st % TC_STAGES;
+            ok = tc_mbar_wait(tc_smem(&s_full[s]), (st / TC_STAGES) & 1, 1000000000ull);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t src = sbase + s * stage_bytes, sft = sf0 + s * 48;
+            for (int k = 0; k < TC_KS; ++k) {
+                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 4 * k), "l"(tc_desc(src + o_sfg + 512 * k, 128, 128)) : "memory");
+                if (GLU) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 16 + 4 * k), "l"(tc_desc(src + o_sfu + 512 * k, 128, 128)) : "memory");
+                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 32 + 4 * k), "l"(tc_desc(src + o_sfb + 512 * k, 128, 128)) : "memory");
+            }
+            for (int k = 0; k < TC_KS; ++k) {
+                const uint64_t db = tc_desc(src + o_b + k * (t.npad * 32), (uint32_t)t.npad * 16, 128);
+                const uint32_t acc = (st | k) ? 1u : 0u;
+                tc_mma_fp4(d_g, tc_desc(src + k * 4096, 2048, 128), db, idesc, sft + 4 * k, sft + 32 + 4 * k, acc);
+                if (GLU) tc_mma_fp4(d_u, tc_desc(src + o_au + k * 4096, 2048, 128), db, idesc, sft + 16 + 4 * k, sft + 32 + 4 * k, acc);
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
+        }
+        if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc)) : "memory");
+        else { atomicCAS(p.status, 0, 4); asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_acc)) : "memory"); }
+    } else if (wid < 4) {
+        // epilogue: lane quarter `wid` of tensor memory = weight rows 32 * wid .. of this tile; columns = the tile's tokens
+        ok = tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok && *(volatile int*)p.status == 0) {
+            const int row = mt * TC_M + wid * 32 + lane;
+            const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
+            for (int c = 0; c < t.npad; c += 8) {
+                uint32_t g[8], u[8];
+                const uint32_t ta = ((uint32_t)(wid * 32) << 16) + (uint32_t)c;
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                             : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]) : "r"(d_g + ta) : "memory");
+                if (GLU)
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]) : "r"(d_u + ta) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (c + j < t.cnt) {
+                        float v = __uint_as_float(g[j]);
+                        if (p.s2g) v = v * sg;
+                        if (GLU) { float w = __uint_as_float(u[j]); if (p.s2u) w = w * su; v = silu_f(v) * w; }   // src/ops/mod.rs:1105-1117
+                        p.out[(size_t)p.pair_list[t.n0 + c + j] * p.out_stride + row] = v;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+}
+inline size_t tc_gemm_smem(bool glu) {
+    const size_t a = TC_KS * 4096, b = (size_t)TC_NMAX * 32 * TC_KS, sf = TC_KS * 512;
+    return TC_STAGES * (a * (glu ? 2 : 1) + b + sf * (glu ? 3 : 2)) + 128;
+}
+
+}  // namespace

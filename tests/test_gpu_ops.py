@@ -382,3 +382,35 @@ def test_exp_and_log_follow_the_c_library():
     bad = int((want_l.view(np.uint32) != got_l.view(np.uint32)).sum())
     assert bad <= 2, f"log: {bad} of {x.size} differ"
     ops.check(); ops.close()
+
+
+@pytest.mark.parametrize("hd,nh,nkv,n_pos,n_q", [(256, 16, 2, 700, 1), (64, 4, 1, 100, 3), (128, 6, 2, 333, 2), (256, 32, 4, 1500, 1)])
+def test_attend_in_exact_mode_equals_the_cpu_path_bit_for_bit(hd, nh, nkv, n_pos, n_q):
+    """exact=1: scores, softmax and weighted values in the CPU path's own order (src/ops/naive.rs:420-466 there)."""
+    from inferred_thoughts_b200 import host
+    from oracle import oracle_py as O
+    ops = host.B200Ops(0, "exact=1")
+    kvd = hd * nkv
+    q = noise(n_q * nh * hd, 70)
+    ks = noise(n_pos * kvd, 71).astype(np.float16).view(np.uint16)
+    vs = noise(n_pos * kvd, 72).astype(np.float16).view(np.uint16)
+    scale = np.float32(1.0 / np.sqrt(hd))
+    want = np.zeros(n_q * nh * hd, np.float32); got = np.zeros_like(want)
+    O.lib().orc_attend(q, q.size, ks, vs, kvd, n_pos, hd, nh, nkv, scale, 0, want)
+    ops.begin_pass(n_q)
+    ops.attend(q, ks, vs, kvd, n_pos, hd, nh, nkv, float(scale), got); ops.host_needs(got); ops.check()
+    assert got.view(np.uint32).tolist() == want.view(np.uint32).tolist(), float(np.abs(got - want).max())
+    ops.close()
+
+
+def test_fp4_tensor_core_ceiling_runs_and_verifies_its_accumulators():
+    """tcgen05.mma kind::mxf4nvf4 with unchanging operands (every value 1.0, every scale 1.0): each accumulator must end at
+    64 * iters exactly; the rate is the denominator of the expert GEMMs' roofline fraction."""
+    from inferred_thoughts_b200 import host
+    ops = host.B200Ops(0)
+    for n in (128, 256):
+        tflops, status, cycles = ops.fp4_ceiling(n=n, iters=2000, reps=3)
+        print(f"FP4 ceiling N={n}: {tflops:.0f} TFLOP/s dense, {cycles:.1f} cycles per MMA")
+        assert status == 0, status
+        assert tflops > 500.0
+    ops.check(); ops.close()
