@@ -226,6 +226,34 @@ def experts_microbench(host, ops, hbm):
         by = distinct * 3 * (H * ff // 64 * 36) + T * H * 4 + T * K * (ff + H) * 4
         out[str(T)] = {"ms": ms, "tok_per_s": T / (ms / 1e3), "distinct_experts": distinct, "algorithmic_GBs": by / ms / 1e6,
                        "frac_of_hbm": by / ms / 1e6 / hbm, "int8_TOPS": 2.0 * T * K * 3 * H * ff / (ms / 1e3) / 1e12}
+    # the same matmuls as FP4 x FP4 block-scaled tensor-core GEMMs (tcgen05.mma kind::mxf4nvf4), against the measured ceiling of
+    # that instruction on this GPU
+    tc = host.B200Ops(0, "experts=fp4tc")
+    try:
+        peak = max(tc.fp4_ceiling(n=128)[0], tc.fp4_ceiling(n=256)[0])
+        fp4 = {"fp4_peak_TFLOPs_measured": peak, "peak_method": "back-to-back tcgen05.mma kind::mxf4nvf4 on unchanging shared-memory operands, one block per SM, accumulators verified"}
+        for T in (512, 2048, 8192, 32768):
+            x = rng.standard_normal(T * H).astype(np.float32)
+            lg = np.concatenate([base[rng.permutation(E)] for _ in range(T)]).astype(np.float32)
+            e = np.exp(lg.reshape(T, E) - lg.reshape(T, E).max(1, keepdims=True)); probs = (e / e.sum(1, keepdims=True)).astype(np.float32).reshape(-1)
+            h = np.zeros(T * K * ff, np.float32); scratch = np.zeros_like(h); o = np.zeros(T * K * H, np.float32)
+            tc.begin_pass(T)
+            route = tc.route(probs, E, K)
+            for _ in range(2):
+                tc.moe_glu(G, U, route, x, h, scratch); tc.matmul_experts(D, route, h, o)
+            tc.check(); torch.cuda.synchronize()
+            iters = 10 if T <= 2048 else 3
+            t0 = time.perf_counter()
+            for _ in range(iters):
+                tc.moe_glu(G, U, route, x, h, scratch); tc.matmul_experts(D, route, h, o)
+            torch.cuda.synchronize()
+            ms = (time.perf_counter() - t0) / iters * 1e3
+            tc.check()
+            tf = 2.0 * T * K * 3 * H * ff / (ms / 1e3) / 1e12
+            fp4[str(T)] = {"ms": ms, "tok_per_s": T / (ms / 1e3), "fp4_TFLOPs": tf, "frac_of_fp4_peak": tf / peak}
+        out["fp4_tensor_cores"] = fp4
+    finally:
+        tc.close()
     return out
 
 
@@ -483,9 +511,11 @@ def run_probe(args):
     mode, _, n = args.probe.partition(":")
     n = int(n or 1)
     dims = configs.with_layers(dict(configs.L177B if args.model == "l177b" else configs.M35B), args.layers or 8)
-    ops = host.B200Ops(0, f"kv=bf16,exact={args.exact}")
-    model = host.Model(ops, host.ModelDims(**dims)); model.synth(configs.SEEDS[args.model])
+    ops = host.B200Ops(0, f"kv=bf16,exact={args.exact}" + ("," + args.opts if args.opts else ""))
     rng = np.random.default_rng(3)
+    model = None
+    if mode != "experts":
+        model = host.Model(ops, host.ModelDims(**dims)); model.synth(configs.SEEDS[args.model])
     if mode == "decode":
         eng = host.Engine(model, 2048, n)
         eng.prefill(rng.integers(0, dims["n_vocab"], (n, 64)).astype(np.uint32), want_logits=False)
@@ -494,7 +524,7 @@ def run_probe(args):
         eng.decode_loop(t, 1)
         torch.cuda.synchronize(); torch.cuda.profiler.stop()
     elif mode == "prefill":
-        eng = host.Engine(model, 2048, 1)
+        eng = host.Engine(model, max(2048, n + 64), 1)
         pr = rng.integers(0, dims["n_vocab"], n).astype(np.uint32)
         eng.prefill(pr[:32], want_logits=False); eng.reset()
         torch.cuda.synchronize(); torch.cuda.profiler.start()
@@ -510,8 +540,34 @@ def run_probe(args):
             torch.cuda.synchronize(); torch.cuda.profiler.start()
             eng.decode_loop(t, 1)
             torch.cuda.synchronize(); torch.cuda.profiler.stop()
+    elif mode == "experts":
+        # BASELINE config 2's routed-expert matmuls alone (hidden 2048, FFN 512, 256 experts, top-8, Zipf routing) at n tokens
+        H, ff, E, K = 2048, 512, 256, 8
+        def blocks(n_out, n_in):
+            nb = E * n_out * n_in // 64
+            b = np.zeros((nb, 36), np.uint8)
+            b[:, :4] = rng.integers(0x20, 0x50, (nb, 4)); b[:, 4:] = rng.integers(0, 256, (nb, 32))
+            return b.reshape(-1), ((rng.random(E).astype(np.float32) + 0.5) * 0.3)
+        (gb, gs), (ub, us), (db, ds) = blocks(ff, H), blocks(ff, H), blocks(H, ff)
+        G, U, D = host.Experts(gb, host.NVFP4, H, ff, E, gs), host.Experts(ub, host.NVFP4, H, ff, E, us), host.Experts(db, host.NVFP4, ff, H, E, ds)
+        base = (-1.1 * np.log(np.arange(1, E + 1))).astype(np.float32)
+        x = rng.standard_normal(n * H).astype(np.float32)
+        lg = np.concatenate([base[rng.permutation(E)] for _ in range(n)]).astype(np.float32).reshape(n, E)
+        pe = np.exp(lg - lg.max(1, keepdims=True)); probs = (pe / pe.sum(1, keepdims=True)).astype(np.float32).reshape(-1)
+        h = np.zeros(n * K * ff, np.float32); scratch = np.zeros_like(h); o = np.zeros(n * K * H, np.float32)
+        ops.begin_pass(n)
+        route = ops.route(probs, E, K)
+        for _ in range(2):
+            ops.moe_glu(G, U, route, x, h, scratch); ops.matmul_experts(D, route, h, o)
+        ops.check(); torch.cuda.synchronize(); torch.cuda.profiler.start()
+        t0 = time.perf_counter()
+        ops.moe_glu(G, U, route, x, h, scratch); ops.matmul_experts(D, route, h, o)
+        torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        print(f"experts {n}: {(time.perf_counter() - t0) * 1e3:.3f} ms (host clock)", file=sys.stderr)
+        ops.check(); ops.close()
+        return
     else:
-        raise SystemExit("--probe: decode:N | prefill:N | step:N | timeline:N")
+        raise SystemExit("--probe: decode:N | prefill:N | step:N | timeline:N | experts:N")
     print(f"{mode} {n}: {eng.last_ms():.3f} ms", file=sys.stderr)
     eng.close(); model.close(); ops.close()
 
@@ -582,6 +638,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512, help="prompt tokens before the timed decode steps (BASELINE: 512)")
     ap.add_argument("--cpu-budget", type=float, default=12.0)
     ap.add_argument("--model", default="m35b", choices=["m35b", "l177b"], help="m35b: the headline 35B-A3B shape; l177b: BASELINE config 5's ~177B shape")
+    ap.add_argument("--opts", default="", help="extra backend options for --probe runs, e.g. experts=fp4tc")
     ap.add_argument("--probe", default="", help="profiler aid, prints no bench line: 'decode:N' one batched decode step of N sequences, 'prefill:N' one pass of "
                     "N prompt rows, 'step:N' one fused one-token step at N positions, each inside a CUDA profiler range (ncu --profile-from-start off); "
                     "'timeline:N' the per-stage timeline of one step at N positions. Use with --layers.")

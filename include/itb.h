@@ -237,6 +237,11 @@ int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t*
  * tflops_out: dense TFLOP/s, best of `reps` launches by CUDA events; status_out: 0 verified, 1 a (bounded) wait ran out,
  * 2 accumulators wrong; mma_cycles_out: SM cycles per MMA on the slowest block. Returns non-zero on a call error. */
 int  itb_fp4_ceiling(itb_ctx*, int n, int iters, int reps, double* tflops_out, int* status_out, double* mma_cycles_out);
+/* The FP4 activation quantiser of the tensor-core expert path on its own (opts "experts=fp4tc" selects that path for
+ * itb_matmul_experts / itb_moe_glu and for the engine's many-row passes): x[n], n a multiple of 16 -> one UE4M3 scale code per
+ * 16 elements and one E2M1 code (0..15) per element, the CPU statement's record (Fp4Row::from_f32, src/ops/naive.rs:755-788),
+ * bit for bit. Host arrays. Returns 0, or 1 with the context's error set. */
+int  itb_fp4_quantize(itb_ctx*, const float* x, size_t n, uint8_t* scales_out, uint8_t* codes_out);
 /* exp and log as the kernels compute them, on their own (tests compare with the C library the reference CPU path calls:
  * Rust's f32::exp / f32::ln, src/ops/naive.rs:101-106, :246-252, :362-376). itb_expf_host: the same expf on the host, no
  * device needed. itb_eval_unary: kind 0 exp, 1 log, on the device over host arrays. */

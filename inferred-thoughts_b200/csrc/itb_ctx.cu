@@ -100,6 +100,7 @@ extern "C" int itb_create(int device_ordinal, const char* opts, itb_ctx** out) {
     std::string o = opts ? opts : "";
     if (o.find("kv=bf16") != std::string::npos) c->kv_bf16 = true;
     if (o.find("exact=0") != std::string::npos) c->exact = false;
+    if (o.find("experts=fp4tc") != std::string::npos) c->fp4tc = true;
     // libm=cr keeps log correctly rounded instead of following the host C library's logf (see itb_internal.cuh)
     const uint32_t* fix = o.find("libm=cr") != std::string::npos ? nullptr : logf_fix_on_device(device_ordinal);
     itb_ops_use_logf_fix(fix, fix ? LOGF_FIX_N : 0);
@@ -120,6 +121,7 @@ extern "C" void itb_destroy(itb_ctx* c) {
     free_map(c->mirrors); free_map(c->states); free_map(c->kv);
     for (auto& w : c->weights) { cudaFree(w.second.a); cudaFree(w.second.b); cudaFree(w.second.scale2); }
     cudaFree(c->pair_off); cudaFree(c->pair_list);
+    itb_tc_free(c);
     cudaFree(c->route_ids); cudaFree(c->route_w); cudaFree(c->xq); cudaFree(c->xs); cudaFree(c->tmp_f32);
     cudaStreamDestroy(c->stream);
     delete c;

@@ -946,7 +946,15 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             launches++;
-            {
+            cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
+            cudaStreamIsCapturing(st, &cap_st);
+            if (c->fp4tc && n_tok > 1 && !e->ep && !e->tier && cap_st == cudaStreamCaptureStatusNone && itb_tc_shape_ok(Lg) && itb_tc_shape_ok(Lu) && itb_tc_shape_ok(Ld)) {
+                // many rows, experts=fp4tc: FP4 activations times FP4 weights on the tensor cores (the reference's default device
+                // arithmetic, src/ops/cuda/mod.rs:239-248 there); gate/up + SiLU in one GEMM's epilogue, then down
+                if (!itb_tc_experts(c, st, Lg, &Lu, e->xn, K, e->pair_off, e->pair_list, P, e->h_all) ||
+                    !itb_tc_experts(c, st, Ld, nullptr, e->h_all, 1, e->pair_off, e->pair_list, P, e->o_all)) return launches;
+                launches += 6;
+            } else {
                 // rows per expert decide the tile shape (a tile's empty token columns cost as much as full ones)
                 const bool tile_w = H % 256 == 0 && ff % 256 == 0;
                 // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64

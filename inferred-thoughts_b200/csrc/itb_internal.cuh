@@ -83,7 +83,19 @@ struct itb_ctx {
     float* tmp_f32 = nullptr; size_t tmp_cap = 0;
     const void* last_state_key = nullptr;
     size_t mirror_bytes = 0, weight_bytes = 0;
+    // FP4 tensor-core expert path (itb_tc.cu): expert stacks re-tiled once (keyed by the stack's nibble plane), per-pass scratch
+    struct TcWeights { uint8_t* img = nullptr; uint8_t* sf = nullptr; size_t bytes = 0; };
+    std::unordered_map<const void*, TcWeights> tc_weights;
+    void* tc_tiles = nullptr; int* tc_n_tiles = nullptr; int* tc_slot_tile = nullptr; uint8_t* tc_b_img = nullptr; uint8_t* tc_b_sf = nullptr; int* tc_status = nullptr;
+    size_t tc_cap_tiles = 0, tc_cap_slots = 0, tc_cap_b = 0, tc_cap_sf = 0;
+    bool fp4tc = false;      // opts experts=fp4tc: many-row passes multiply FP4 activations on the tensor cores
 };
+// Routed experts over expert-grouped pairs on the FP4 tensor cores (itb_tc.cu). wu != null: out[pair] = silu(Wg x * s_g) * (Wu x * s_u);
+// else out[pair] = W x * s. x: f32 rows on the device, the row of slot s is pair_list[s] / rows_div. False: not run (shape or memory).
+bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4* wu, const float* x, int rows_div, const int* pair_off,
+                    const int* pair_list, int n_pairs, float* out);
+bool itb_tc_shape_ok(const DevFp4& w);
+void itb_tc_free(itb_ctx* c);
 
 bool itb_fail(itb_ctx* c, const char* what, cudaError_t e);
 bool itb_fail_msg(itb_ctx* c, const std::string& msg);

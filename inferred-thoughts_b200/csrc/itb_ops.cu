@@ -175,6 +175,35 @@ static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od)
     ITB_LAUNCHED(c);
 }
 
+// The pairs of a pass sorted by expert: pair_off[e .. e+1) bounds expert e's slots of pair_list.
+static bool group_pairs(itb_ctx* c, const int32_t* ids, size_t n_pairs, size_t E) {
+    if (c->pair_cap < n_pairs || c->pair_experts < E) {
+        cudaStreamSynchronize(c->stream);
+        cudaFree(c->pair_off); cudaFree(c->pair_list); c->pair_off = nullptr; c->pair_list = nullptr; c->pair_cap = 0; c->pair_experts = 0;
+        if (cudaMalloc(&c->pair_off, (E + 1) * 4) != cudaSuccess || cudaMalloc(&c->pair_list, n_pairs * 4) != cudaSuccess) return itb_fail_msg(c, "experts: out of device memory");
+        c->pair_cap = n_pairs; c->pair_experts = E;
+    }
+    k_group_pairs_fast<<<1, 1024, E * 4, c->stream>>>(ids, (int)n_pairs, (int)E, c->pair_off, c->pair_list);
+    ITB_LAUNCHED(c);
+    return true;
+}
+// experts=fp4tc: FP4 activations times FP4 weights on the tensor cores (the reference's default device arithmetic,
+// src/ops/cuda/mod.rs:239-248 there; CPU statement with fp4 activations: src/ops/naive.rs:755-837). True when the pass ran there.
+static bool experts_tc(itb_ctx* c, const itb_experts* g, const itb_experts* u, const itb_route_t* r, const float* xd, size_t x_len, float* od) {
+    if (!c->fp4tc || g->ggml_type != ITB_NVFP4 || (u && u->ggml_type != ITB_NVFP4) || g->n_expert > 1024) return false;
+    const WeightEntry* wg = itb_weight(c, g->data, g->bytes, g->ggml_type, g->n_in, g->n_out, g->n_expert, g->scale, g->scale_bytes);
+    const WeightEntry* wu = u ? itb_weight(c, u->data, u->bytes, u->ggml_type, u->n_in, u->n_out, u->n_expert, u->scale, u->scale_bytes) : nullptr;
+    if (!wg || (u && !wu)) return false;
+    DevFp4 dg{(const uint8_t*)wg->a, (const uint8_t*)wg->b, wg->scale2, (int)wg->n_in, (int)wg->n_out, (int)wg->n_expert, 0};
+    DevFp4 du = dg;
+    if (wu) du = DevFp4{(const uint8_t*)wu->a, (const uint8_t*)wu->b, wu->scale2, (int)wu->n_in, (int)wu->n_out, (int)wu->n_expert, 0};
+    if (!itb_tc_shape_ok(dg) || (wu && !itb_tc_shape_ok(du))) return false;
+    const size_t n_pairs = r->n_tok * r->n_used, rows = x_len / g->n_in;
+    const int div = rows == n_pairs ? 1 : rows > 1 ? (int)r->n_used : 0x7fffffff;
+    if (!group_pairs(c, c->route_ids, n_pairs, g->n_expert)) return true;      // failed loudly: nothing else runs
+    itb_tc_experts(c, c->stream, dg, wu ? &du : nullptr, xd, div, c->pair_off, c->pair_list, (int)n_pairs, od);
+    return true;
+}
 // ids==nullptr: dense NVFP4 matrix, one "pair" per token reading its own row.
 static void launch_fp4(itb_ctx* c, const WeightEntry* w, const int32_t* ids, size_t n_pairs, int n_used, int rows_mode, float* od) {
     if (!ids && n_pairs >= 2 && gemm_smem((int)w->n_in) <= 200 * 1024) {
@@ -191,14 +220,7 @@ static void launch_fp4(itb_ctx* c, const WeightEntry* w, const int32_t* ids, siz
         // many pairs: group them by expert and run each expert's rows through the int8-MMA tiles, so an expert's weights
         // are read once (the reference groups the same way, kernels/moe.cuh:62-133 there)
         const size_t E = w->n_expert;
-        if (c->pair_cap < n_pairs || c->pair_experts < E) {
-            cudaStreamSynchronize(c->stream);
-            cudaFree(c->pair_off); cudaFree(c->pair_list); c->pair_off = nullptr; c->pair_list = nullptr;
-            if (cudaMalloc(&c->pair_off, (E + 1) * 4) != cudaSuccess || cudaMalloc(&c->pair_list, n_pairs * 4) != cudaSuccess) { itb_fail_msg(c, "experts: out of device memory"); return; }
-            c->pair_cap = n_pairs; c->pair_experts = E;
-        }
-        k_group_pairs_fast<<<1, 1024, E * 4, c->stream>>>(ids, (int)n_pairs, (int)E, c->pair_off, c->pair_list);
-        ITB_LAUNCHED(c);
+        if (!group_pairs(c, ids, n_pairs, E)) return;
         const int per_e = (int)((n_pairs + E - 1) / E), nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
         const int ns = std::min((int)w->n_in / 256, TILE_STAGES);
         const int div = rows_mode == 0 ? 1 : rows_mode == 1 ? n_used : 0x7fffffff;
@@ -319,6 +341,7 @@ extern "C" void itb_matmul_experts(itb_ctx* c, const itb_experts* w, const itb_r
     if (!stage_route(c, r, w->n_expert)) return;
     const float* xd = itb_mirror_in(c, x, x_len); float* od = itb_mirror_out(c, out, out_len);
     if (!xd || !od) return;
+    if (experts_tc(c, w, nullptr, r, xd, x_len, od)) return;
     experts_dev(c, w, r, xd, x_len, od);
 }
 extern "C" void itb_moe_glu(itb_ctx* c, const itb_experts* gate, const itb_experts* up, const itb_route_t* r, const float* x,
@@ -331,6 +354,7 @@ extern "C" void itb_moe_glu(itb_ctx* c, const itb_experts* gate, const itb_exper
     const float* xd = itb_mirror_in(c, x, x_len);
     float* od = itb_mirror_out(c, out, out_len); float* sd = itb_mirror_out(c, scratch, out_len);
     if (!xd || !od || !sd) return;
+    if (experts_tc(c, gate, up, r, xd, x_len, od)) return;
     experts_dev(c, gate, r, xd, x_len, od);
     experts_dev(c, up, r, xd, x_len, sd);
     EW_LAUNCH(c, k_silu_mul, out_len, od, sd, out_len);

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(128) k_fp4_ceiling(int iters, int* status, uns
         for (int i = 0; i < iters; ++i) tc_mma_fp4(d_tm, da, db, idesc, sfa_tm, sfb_tm, i ? 1u : 0u);
         asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
     }
-    ok = tc_mbar_wait(bar, 0, 2000000000ull);
+    ok = __all_sync(0xffffffffu, tc_mbar_wait(bar, 0, 2000000000ull));
     c1 = clock64();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok) {
@@ -383,9 +383,9 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
         else { atomicCAS(p.status, 0, 4); asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_acc)) : "memory"); }
     } else if (wid < 4) {
         // epilogue: lane quarter `wid` of tensor memory = weight rows 32 * wid .. of this tile; columns = the tile's tokens
-        ok = tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull);
+        ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull));      // one verdict per warp: the loads below are warp-wide
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok && *(volatile int*)p.status == 0) {
+        if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
             const int row = mt * TC_M + wid * 32 + lane;
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
             for (int c = 0; c < t.npad; c += 8) {
@@ -419,3 +419,104 @@ inline size_t tc_gemm_smem(bool glu) {
 }
 
 }  // namespace
+
+bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n_out % TC_M == 0 && !w.slot_map; }
+void itb_tc_free(itb_ctx* c) {
+    for (auto& kv : c->tc_weights) { cudaFree(kv.second.img); cudaFree(kv.second.sf); }
+    c->tc_weights.clear();
+    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status);
+    c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr;
+    c->tc_cap_tiles = c->tc_cap_slots = c->tc_cap_b = c->tc_cap_sf = 0;
+}
+static const itb_ctx::TcWeights* tc_weights_of(itb_ctx* c, cudaStream_t st, const DevFp4& w) {
+    auto it = c->tc_weights.find(w.nib);
+    if (it != c->tc_weights.end()) return &it->second;
+    itb_ctx::TcWeights t;
+    const size_t kbs = w.n_in / 64, tiles = (size_t)w.n_expert * (w.n_out / TC_M) * kbs;
+    if (cudaMalloc(&t.img, tiles * 4096) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (cudaMalloc(&t.sf, tiles * 512) != cudaSuccess) { cudaFree(t.img); cudaGetLastError(); return nullptr; }
+    t.bytes = tiles * (4096 + 512);
+    const size_t n = (size_t)w.n_expert * w.n_out * kbs;
+    k_tc_tile_weights<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.nib, w.sc, w.n_expert, w.n_out, w.n_in, t.img, t.sf);
+    c->launches++;
+    return &c->tc_weights.emplace(w.nib, t).first->second;
+}
+template <class T>
+static bool tc_grow(T** p, size_t* cap, size_t need, cudaStream_t st) {
+    if (*cap >= need) return true;
+    cudaStreamSynchronize(st);
+    cudaFree(*p); *p = nullptr; *cap = 0;
+    if (cudaMalloc((void**)p, need * sizeof(T)) != cudaSuccess) { cudaGetLastError(); return false; }
+    *cap = need;
+    return true;
+}
+bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4* wu, const float* x, int rows_div, const int* pair_off,
+                    const int* pair_list, int n_pairs, float* out) {
+    if (!itb_tc_shape_ok(wg) || (wu && (!itb_tc_shape_ok(*wu) || wu->n_in != wg.n_in || wu->n_out != wg.n_out)) || n_pairs <= 0) return false;
+    const itb_ctx::TcWeights* tg = tc_weights_of(c, st, wg);
+    const itb_ctx::TcWeights* tu = wu ? tc_weights_of(c, st, *wu) : nullptr;
+    if (!tg || (wu && !tu)) return itb_fail_msg(c, "FP4 tensor path: out of device memory for the tiled expert weights");
+    const int E = wg.expert_lo + wg.n_expert;        // global ids run to the end of this shard at least; pair_off covers every expert the caller grouped
+    const size_t kbs = wg.n_in / 64, max_tiles = (size_t)wg.n_expert + (size_t)n_pairs / TC_NMAX + 1;
+    const size_t b_rows = (size_t)n_pairs + 16 * max_tiles;
+    TcTile* tiles = (TcTile*)c->tc_tiles;
+    size_t cap_t = c->tc_cap_tiles;
+    bool ok = tc_grow(&tiles, &cap_t, max_tiles, st);
+    c->tc_tiles = tiles; c->tc_cap_tiles = cap_t;
+    size_t cap1 = c->tc_n_tiles ? 1 : 0, cap2 = c->tc_status ? 1 : 0;
+    ok = ok && tc_grow(&c->tc_n_tiles, &cap1, 1, st) && tc_grow(&c->tc_status, &cap2, 1, st) && tc_grow(&c->tc_slot_tile, &c->tc_cap_slots, (size_t)n_pairs, st) &&
+         tc_grow(&c->tc_b_img, &c->tc_cap_b, b_rows * (wg.n_in / 2), st) && tc_grow(&c->tc_b_sf, &c->tc_cap_sf, max_tiles * kbs * 512, st);
+    if (!ok) return itb_fail_msg(c, "FP4 tensor path: out of device memory for the pass");
+    cudaMemsetAsync(c->tc_status, 0, 4, st);
+    cudaMemsetAsync(c->tc_b_img, 0, b_rows * (wg.n_in / 2), st);        // padding rows: zero codes, zero scales
+    cudaMemsetAsync(c->tc_b_sf, 0, max_tiles * kbs * 512, st);
+    (void)E;
+    k_tc_build_tiles<<<1, 256, 0, st>>>(pair_off, wg.expert_lo + wg.n_expert, wg.expert_lo, wg.n_expert, tiles, c->tc_n_tiles, (int)max_tiles, c->tc_slot_tile, (int)kbs);
+    const size_t nq = (size_t)n_pairs * (wg.n_in / 16);
+    k_tc_quant_tiles<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(x, wg.n_in, pair_list, rows_div, n_pairs, tiles, c->tc_slot_tile, c->tc_b_img, c->tc_b_sf);
+    TcGemm g{};
+    g.wg_img = tg->img; g.wg_sf = tg->sf; g.wu_img = tu ? tu->img : nullptr; g.wu_sf = tu ? tu->sf : nullptr;
+    g.s2g = wg.scale2; g.s2u = wu ? wu->scale2 : nullptr; g.expert_lo = wg.expert_lo;
+    g.b_img = c->tc_b_img; g.b_sf = c->tc_b_sf; g.tiles = tiles; g.n_tiles = c->tc_n_tiles; g.pair_list = pair_list;
+    g.n_out = wg.n_out; g.n_in = wg.n_in; g.out = out; g.out_stride = wg.n_out; g.status = c->tc_status;
+    static bool attr = false;
+    if (!attr) {
+        cudaFuncSetAttribute(k_tc_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(true));
+        cudaFuncSetAttribute(k_tc_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(false));
+        attr = true;
+    }
+    const dim3 grid((unsigned)max_tiles, (unsigned)(wg.n_out / TC_M));
+    if (wu) k_tc_gemm<true><<<grid, 192, tc_gemm_smem(true), st>>>(g);
+    else k_tc_gemm<false><<<grid, 192, tc_gemm_smem(false), st>>>(g);
+    c->launches += 3;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return itb_fail(c, "FP4 tensor path: launch", e);
+    return true;
+}
+// The status word of the last pass: 0 fine; 3 / 4: a (bounded) wait of the producer / the MMA warp ran out.
+int itb_tc_status(itb_ctx* c, cudaStream_t st) {
+    int v = 0;
+    if (!c->tc_status) return 0;
+    cudaMemcpyAsync(&v, c->tc_status, 4, cudaMemcpyDeviceToHost, st);
+    cudaStreamSynchronize(st);
+    return v;
+}
+
+// FP4 activation quantiser on its own (tests against the CPU statement, src/ops/naive.rs:755-788): x[n] (n a multiple of 16) ->
+// one UE4M3 scale code per 16 elements and one E2M1 code per element (a byte each, like the CPU record).
+extern "C" int itb_fp4_quantize(itb_ctx* c, const float* x, size_t n, uint8_t* scales_out, uint8_t* codes_out) {
+    if (n % 16) { itb_fail_msg(c, "fp4_quantize: length must be a multiple of 16"); return 1; }
+    float* dx = nullptr; uint8_t *ds = nullptr, *dc = nullptr;
+    if (cudaMalloc(&dx, n * 4) != cudaSuccess || cudaMalloc(&ds, n / 16) != cudaSuccess || cudaMalloc(&dc, n) != cudaSuccess) {
+        cudaFree(dx); cudaFree(ds); itb_fail_msg(c, "fp4_quantize: out of device memory"); return 1;
+    }
+    cudaMemcpyAsync(dx, x, n * 4, cudaMemcpyHostToDevice, c->stream);
+    k_fp4_quant_plain<<<(unsigned)((n / 16 + 127) / 128), 128, 0, c->stream>>>(dx, n / 16, ds, dc);
+    ITB_LAUNCHED(c);
+    cudaMemcpyAsync(scales_out, ds, n / 16, cudaMemcpyDeviceToHost, c->stream);
+    cudaMemcpyAsync(codes_out, dc, n, cudaMemcpyDeviceToHost, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    cudaFree(dx); cudaFree(ds); cudaFree(dc);
+    if (e != cudaSuccess) { itb_fail(c, "fp4_quantize", e); return 1; }
+    return 0;
+}

@@ -161,6 +161,14 @@ class B200Ops:
             self.check(); raise RuntimeError("fp4_ceiling failed")
         return t.value, st.value, cy.value
 
+    def fp4_quantize(self, x):
+        """FP4 activation record of x (length a multiple of 16): (UE4M3 scale codes [n/16], E2M1 codes [n]) as the tensor-core path makes them."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        sc = np.zeros(x.size // 16, np.uint8); q = np.zeros(x.size, np.uint8)
+        if self.L.itb_fp4_quantize(self.h, _p(x), SZ(x.size), _p(sc), _p(q)):
+            self.check(); raise RuntimeError("fp4_quantize failed")
+        return sc, q
+
     def config_report(self):
         b = C.create_string_buffer(512)
         self.L.itb_config_report(self.h, b, SZ(512))

@@ -414,3 +414,69 @@ def test_fp4_tensor_core_ceiling_runs_and_verifies_its_accumulators():
         assert status == 0, status
         assert tflops > 500.0
     ops.check(); ops.close()
+
+
+def test_fp4_activation_quantiser_equals_the_cpu_record_bit_for_bit(ops):
+    """The tensor-core path's activation quantiser against Fp4Row::from_f32 as the oracle restates it: scale codes and
+    element codes equal, over ordinary rows, tiny and huge magnitudes, zeros, ties and a saturating block."""
+    rng = np.random.default_rng(7)
+    parts = [noise(16 * 4096, 150), noise(16 * 512, 151, 1e-4), noise(16 * 512, 152, 300.0), np.zeros(64, np.float32),
+             np.tile(np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0], np.float32), 8),
+             (rng.standard_normal(16 * 256) * 10.0 ** rng.uniform(-6, 4, 16 * 256)).astype(np.float32),
+             np.full(32, 5000.0, np.float32)]
+    x = np.ascontiguousarray(np.concatenate(parts), np.float32)
+    sc, q = ops.fp4_quantize(x)
+    want_sc = np.zeros(x.size // 16, np.uint8); want_q = np.zeros(x.size, np.uint8)
+    L.orc_fp4_activation(x, x.size, want_sc, want_q)
+    bad = np.flatnonzero(sc != want_sc)
+    assert bad.size == 0, f"{bad.size} scale codes differ, first block {bad[:4]}: {sc[bad[:4]]} vs {want_sc[bad[:4]]}"
+    bad = np.flatnonzero(q != want_q)
+    assert bad.size == 0, f"{bad.size} element codes differ, first at {bad[:4]}: {q[bad[:4]]} vs {want_q[bad[:4]]}"
+
+
+def _fp4tc_case(tc, H, ff, E, K, n_tok, seed, x=None, zipf=False):
+    """moe_glu + down through experts=fp4tc against the oracle with FP4 activations. Returns (h, h_want, o, o_want)."""
+    from inferred_thoughts_b200 import host
+    (gb, gs), (ub, us), (db, ds) = nvfp4_weights(E, ff, H, seed), nvfp4_weights(E, ff, H, seed + 1), nvfp4_weights(E, H, ff, seed + 2)
+    for s in (gs, us, ds):
+        s *= 300
+    x = keep(noise(n_tok * H, seed + 3) if x is None else np.ascontiguousarray(x, np.float32))
+    probs = _zipf_logits(n_tok, E, seed) if zipf else keep(noise(n_tok * E, seed + 4, 2.0))
+    probs = keep(probs.copy()); L.orc_softmax(probs, probs.size, E)
+    tc.begin_pass(n_tok)
+    route = tc.route(probs, E, K); ids, _ = tc.read_route(route)
+    h = keep(np.zeros(n_tok * K * ff, np.float32)); scratch = keep(np.zeros_like(h)); o = keep(np.zeros(n_tok * K * H, np.float32))
+    G, U, D = host.Experts(gb, host.NVFP4, H, ff, E, gs), host.Experts(ub, host.NVFP4, H, ff, E, us), host.Experts(db, host.NVFP4, ff, H, E, ds)
+    tc.moe_glu(G, U, route, x, h, scratch)
+    tc.matmul_experts(D, route, h, o)
+    tc.host_needs(h); tc.host_needs(o); tc.check()
+    h_want = np.zeros_like(h); o_want = np.zeros_like(o)
+    L.orc_moe_glu(gb, gs.ctypes.data, ub, us.ctypes.data, H, ff, E, ids, ids.size, K, x, x.size, h_want, 1)
+    L.orc_matmul_experts(db, ff, H, E, ds.ctypes.data, ids, ids.size, K, h, h.size, o_want, 1)   # on the GPU's h: isolates the down matmul
+    return h.reshape(n_tok * K, ff), h_want.reshape(n_tok * K, ff), o.reshape(n_tok * K, H), o_want.reshape(n_tok * K, H)
+
+
+def _rel_err(got, want):
+    """Largest error of a row relative to that row's largest magnitude (accumulation-order class)."""
+    scale = np.maximum(np.abs(want).max(axis=1, keepdims=True), 1e-20)
+    return float((np.abs(got.astype(np.float64) - want) / scale).max())
+
+
+FP4TC_TOL = 2e-5     # f32 accumulation in another order over <= 2048 products of like magnitude
+
+
+@pytest.mark.parametrize("H,ff,E,K,n_tok,zipf", [(256, 256, 4, 2, 5, False), (512, 256, 16, 4, 40, False), (2048, 512, 256, 8, 200, True),
+                                                   (2048, 512, 8, 2, 700, False)])
+def test_routed_experts_on_the_fp4_tensor_cores(H, ff, E, K, n_tok, zipf):
+    """experts=fp4tc: FP4 activations (bit-identical quantiser) times FP4 weights by tcgen05.mma kind::mxf4nvf4 against the
+    CPU statement of the same arithmetic (dot_nvfp4_fp4): the products are exact in both, only the f32 summation order inside
+    the tensor core differs. Cases: one ragged tile per expert, several experts, the microbenchmark's stack with Zipf routing,
+    and experts whose pairs span several 128-token tiles."""
+    from inferred_thoughts_b200 import host
+    tc = host.B200Ops(0, "experts=fp4tc")
+    h, h_want, o, o_want = _fp4tc_case(tc, H, ff, E, K, n_tok, 160 + n_tok, zipf=zipf)
+    eh, eo = _rel_err(h, h_want), _rel_err(o, o_want)
+    print(f"fp4tc H={H} ff={ff} E={E} n_tok={n_tok}: gate/up rel err {eh:.2e}, down rel err {eo:.2e}")
+    assert eh <= 4 * FP4TC_TOL, eh          # through silu(gate) * up: both factors carry the order error
+    assert eo <= FP4TC_TOL, eo
+    tc.check(); tc.close()

@@ -125,3 +125,30 @@ def test_three_sequences_against_the_oracle(pair):
         assert routes[:, i, :].tolist() == om.route_log().reshape(L, K).tolist(), f"sequence {i} routing"
         assert int(nxt[i]) == int(np.argmax(o))
     ops.check(); eng.close()
+
+
+def test_prefill_pass_with_fp4_tensor_core_experts_against_the_oracle_with_fp4_activations():
+    """experts=fp4tc at the 35B-A3B shape: a 160-token prompt in one pass, the routed experts as FP4 x FP4 tensor-core GEMMs,
+    against the oracle run with FP4 activations (the reference's default device arithmetic and its CPU statement,
+    src/ops/naive.rs:755-837). Same quantiser bit for bit; the tensor core's summation order is its own, so the logits are
+    held to the north-star tolerance and the routing ids may differ only where the router's margin is at rounding level."""
+    from inferred_thoughts_b200 import host
+    dims, seed = SHAPES["m35b"]
+    ops = host.B200Ops(0, "exact=1,experts=fp4tc")
+    model = host.Model(ops, host_dims(dims)); model.synth(seed)
+    om = O.OracleModel(oracle_dims(dims))
+    for s in om.specs:
+        data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+        om.set_tensor(s["name"], data, sc)
+    O.lib().orc_set_threads(max(1, O.lib().orc_hw_threads()))
+    L, K = dims["n_layer"], dims["n_expert_used"]
+    prompt = prompt_ids(41, 160, dims["n_vocab"])
+    eng = host.Engine(model, 256, 1)
+    om.begin(256, fp4act=True, log_routes=True)
+    o = om.forward(prompt)
+    g = eng.prefill(prompt)
+    err = _check_logits(o, g, "prefill pass, FP4 tensor-core experts")
+    mism = int((eng.read_routes(L, K)[:, 0, :] != om.route_log().reshape(L, len(prompt), K)[:, -1, :]).sum())
+    print(f"fp4tc prefill: logits max-abs {err:.3e}, routing ids differing on the last token {mism}/{L * K}")
+    assert mism <= 2
+    ops.check(); eng.close(); model.close(); ops.close()
