@@ -606,6 +606,8 @@ def print_timeline(eng, dims, tok):
                 elif i >= 9:   # raw values: 9 = ns thread 0 waited for ring chunks, 10 = ns it worked on them, 11 = chunks
                     agg.setdefault((name, {9: "chunk wait us", 10: "chunk work us", 11: "chunks x1000"}[i]), []).append(marks[i] / 1e3)
             continue
+        for i in [i for i in marks if i >= 9]:
+            agg.setdefault((name, f"raw {i} (cycles)"), []).append(marks.pop(i) * 1e3 / 1e3)
         order = sorted(marks.items(), key=lambda x: x[1])
         for (i, a), (j, b) in zip(order, order[1:]):
             agg.setdefault((name, f"phase {i}->{j}"), []).append((b - a) / 1e3)

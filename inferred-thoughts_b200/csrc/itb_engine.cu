@@ -25,6 +25,7 @@ void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t 
 #include "itb_mega.cuh"
 #include "itb_rows.cuh"
 #include "itb_attn_exact.cuh"
+#include "itb_attn_mma.cuh"
 
 void itb_engine_use_logf_fix(const uint32_t* dev_tab, uint32_t n) {
     cudaMemcpyToSymbol(g_logf_fix, &dev_tab, sizeof dev_tab);
@@ -62,6 +63,7 @@ struct itb_model {
     struct HostStack { uint8_t* nib = nullptr; uint8_t* sc = nullptr; std::vector<float> s2; size_t nib_per = 0, sc_per = 0; bool has_s2 = false; };
     std::vector<std::array<HostStack, 3>> host_experts;
     bool offloaded = false;
+    std::vector<void*> extra;      // device copies this model made beside its tensors (k-major F32 copies)
 };
 
 static synth::ModelDims to_synth(const itb_model_dims& d) {
@@ -96,6 +98,7 @@ extern "C" void itb_model_destroy(itb_model* m) {
     cudaStreamSynchronize(m->c->stream);
     for (auto& kv : m->t) { cudaFree(kv.second.a); cudaFree(kv.second.b); cudaFree(kv.second.scale2); }
     for (auto& l : m->host_experts) for (auto& h : l) { cudaFreeHost(h.nib); cudaFreeHost(h.sc); }
+    for (void* p : m->extra) cudaFree(p);
     delete m;
 }
 
@@ -238,6 +241,13 @@ extern "C" int itb_model_synth_read(itb_model* m, uint64_t seed, const char* nam
     return 0;
 }
 
+// w[n_out][n_in] -> units of 32 rows, k-major inside a unit: wt[(u * n_in + k) * 32 + r] = w[u * 32 + r][k] (zero past n_out).
+__global__ void k_f32_kmajor(const float* w, int n_in, int n_out, float* wt) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x, total = (size_t)((n_out + 31) / 32) * n_in * 32;
+    if (i >= total) return;
+    const int r = (int)(i % 32); const size_t uk = i / 32; const int k = (int)(uk % n_in), u = (int)(uk / n_in), row = u * 32 + r;
+    wt[i] = row < n_out ? w[(size_t)row * n_in + k] : 0.0f;
+}
 static bool finalize(itb_model* m) {
     if (m->finalized) return true;
     itb_ctx* c = m->c;
@@ -250,6 +260,18 @@ static bool finalize(itb_model* m) {
     };
     auto q8 = [&](const std::string& n) { const DevTensor* t = get(n); return t ? DevQ8{(const int8_t*)t->a, (const uint16_t*)t->b, (int)t->n_in, (int)t->n_out} : DevQ8{}; };
     auto f32 = [&](const std::string& n) { const DevTensor* t = get(n); return t ? DevF32{(const float*)t->a, (int)t->n_in, (int)t->n_out} : DevF32{}; };
+    // the small F32 matrices of the one-token step (router, shared-expert gate, alpha, beta) also k-major, for the serial-k fold
+    auto f32k = [&](const std::string& n) {
+        DevF32 w = f32(n);
+        if (!w.w || !c->exact) return w;
+        const size_t total = (size_t)((w.n_out + 31) / 32) * w.n_in * 32;
+        float* wt = nullptr;
+        if (cudaMalloc(&wt, total * 4) != cudaSuccess) { cudaGetLastError(); return w; }      // without the copy the row-per-warp path serves
+        k_f32_kmajor<<<(unsigned)((total + 255) / 256), 256, 0, c->stream>>>(w.w, w.n_in, w.n_out, wt);
+        m->extra.push_back(wt); m->bytes += total * 4;
+        w.wt = wt;
+        return w;
+    };
     auto vec = [&](const std::string& n) { const DevTensor* t = get(n); return t ? (const float*)t->a : nullptr; };
     auto fp4 = [&](const std::string& n) {
         const DevTensor* t = get(n);
@@ -267,7 +289,7 @@ static bool finalize(itb_model* m) {
         L.ffn_norm = vec(P + "post_attention_norm.weight");
         if (L.recurrent) {
             L.wqkv = q8(P + "attn_qkv.weight"); L.wgate = q8(P + "attn_gate.weight"); L.ssm_out = q8(P + "ssm_out.weight");
-            L.ssm_alpha = f32(P + "ssm_alpha.weight"); L.ssm_beta = f32(P + "ssm_beta.weight");
+            L.ssm_alpha = f32k(P + "ssm_alpha.weight"); L.ssm_beta = f32k(P + "ssm_beta.weight");
             L.conv1d = vec(P + "ssm_conv1d.weight"); L.ssm_a = vec(P + "ssm_a"); L.dt_bias = vec(P + "ssm_dt.bias");
             L.ssm_norm = vec(P + "ssm_norm.weight");
         } else {
@@ -275,7 +297,7 @@ static bool finalize(itb_model* m) {
             L.wo = q8(P + "attn_output.weight");
             L.q_norm = vec(P + "attn_q_norm.weight"); L.k_norm = vec(P + "attn_k_norm.weight");
         }
-        L.gate_inp = f32(P + "ffn_gate_inp.weight"); L.shared_gate_inp = f32(P + "ffn_gate_inp_shexp.weight");
+        L.gate_inp = f32k(P + "ffn_gate_inp.weight"); L.shared_gate_inp = f32k(P + "ffn_gate_inp_shexp.weight");
         L.gate = fp4(P + "ffn_gate_exps.weight"); L.up = fp4(P + "ffn_up_exps.weight"); L.down = fp4(P + "ffn_down_exps.weight");
         L.shared_gate = q8(P + "ffn_gate_shexp.weight"); L.shared_up = q8(P + "ffn_up_shexp.weight");
         L.shared_down = q8(P + "ffn_down_shexp.weight");
@@ -553,14 +575,22 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         // the warps' term matrices must fit the block's shared memory (wide rows: fewer rows folded together)
         const int cap = (int)(((SMEM_BUDGET - 256 - (size_t)H * 5 - (size_t)(H / 32) * 4 - (c->exact ? 32 * 33 * 4 : 0) - 64) / (NWG * 4) - CONV_CAP * 8) / (H / 32 + 1));
         p.br = std::max(pass_in, std::min(p.br, cap / pass_in * pass_in));
+        p.f32_ring = 0; p.err = e->err;
         if (c->exact && p.nf) {
-            // serial-k F32 rows stage a row's products in the warp's term scratch: make it hold the whole row (one round trip to
-            // memory instead of one per tile) as far as the block's shared memory goes
-            const int want = (H + H / 32) / (H / 32 + 1) + 1;
-            p.br = std::max(p.br, std::min((want + pass_in - 1) / pass_in * pass_in, cap / pass_in * pass_in));
+            // serial-k F32 rows: 32 to a warp (a lane per row) through the block's ring, when every unit gets a block of its own
+            // and the ring fits; otherwise a row per warp, staged in the warp's term scratch (make it hold the whole row)
+            int units = 0;
+            for (int m = 0; m < p.nf; ++m) units += (p.f[m].n_out + 31) / 32;
+            bool kmajor = true;
+            for (int m = 0; m < p.nf; ++m) kmajor = kmajor && p.f[m].wt;
+            if (kmajor && units <= gx && H % F32S_K == 0 && in_proj_smem(H, 1, p.br, 1) <= SMEM_BUDGET) p.f32_ring = 1;
+            else {
+                const int want = (H + H / 32) / (H / 32 + 1) + 1;
+                p.br = std::max(p.br, std::min((want + pass_in - 1) / pass_in * pass_in, cap / pass_in * pass_in));
+            }
         }
         p.tl_slot = tl++;
-        launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br), st, p);
+        launch_k(pdl, k_in_proj, dim3(gx, B), TPB, in_proj_smem(H, c->exact, p.br, p.f32_ring), st, p);
     };
     auto launch_out = [&](OutProj& o, int n_in) {
         int gx = std::max(1, std::min(sms, H / NWG)), pass = 32 >> lanes_shift(n_in / 32);
@@ -841,6 +871,12 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             launches++;
             return;
         }
+        if (c->exact && R >= 8 && w.n_in % SG_K == 0) {
+            // many rows: a chain per (row, output), a thread per 4 x 4 of them, k in order
+            k_sgemm_serial<<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
+            launches++;
+            return;
+        }
         const int nw = 4;
         dim3 g(std::max(1, std::min(2 * sms, (w.n_out + 31) / 32)), R);
         size_t sm = (size_t)w.n_in * 4 + (size_t)nw * 32 * 33 * 4;
@@ -889,7 +925,24 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             const float scale = 1.0f / sqrtf((float)d.head_dim);
             const int nwa = 8, ns = n_tok > 1 ? e->n_split_rows : e->n_split;
             const size_t smem_a = (size_t)nwa * 8 * 2 * 4 + (size_t)nwa * 8 * d.head_dim * 4;
-            if (exact_attention_ok(e) && e->scores_cap >= (size_t)R * d.n_head * e->n_ctx) {
+            const int group = d.n_head / d.n_head_kv;
+            if ((c->attn_mma || !c->exact) && n_tok >= 16 && AM_ROWS % group == 0 && (d.head_dim == 64 || d.head_dim == 128 || d.head_dim == 256) && kvd % 8 == 0) {
+                // many tokens: causal attention as matrix products over (token, head) tiles, one "split" handed to the combine
+                AmParams ap{};
+                ap.q = e->qn; ap.kslab = a.kslab; ap.vslab = a.vslab; ap.slab_stride = a.slab_stride; ap.npos = e->npos; ap.n_tok = n_tok; ap.kv_dim = kvd;
+                ap.n_head = d.n_head; ap.n_head_kv = d.n_head_kv; ap.group = group; ap.scale = scale; ap.part_acc = e->part_acc; ap.part_ml = e->part_ml;
+                const dim3 ga((n_tok + AM_ROWS / group - 1) / (AM_ROWS / group), d.n_head_kv, n_seq);
+#define AM_CASE(HD)                                                                                                      \
+    case HD:                                                                                                              \
+        set_smem((const void*)k_attn_mma<HD, true>, attn_mma_smem<HD>()); set_smem((const void*)k_attn_mma<HD, false>, attn_mma_smem<HD>()); \
+        if (c->kv_bf16) k_attn_mma<HD, true><<<ga, 256, attn_mma_smem<HD>(), st>>>(ap);                                    \
+        else k_attn_mma<HD, false><<<ga, 256, attn_mma_smem<HD>(), st>>>(ap);                                              \
+        break;
+                switch (d.head_dim) { AM_CASE(64) AM_CASE(128) AM_CASE(256) }
+#undef AM_CASE
+                launches++;
+                k_attn_combine_rows<<<R * d.n_head, d.head_dim, 0, st>>>(e->part_acc, e->part_ml, 1, d.head_dim, e->gate, e->npos, d.n_head, e->aq, e->as); launches++;
+            } else if (exact_attention_ok(e) && e->scores_cap >= (size_t)R * d.n_head * e->n_ctx) {
                 uint32_t top = 0;
                 for (int sq = 0; sq < n_seq; ++sq) top = std::max(top, e->host_pos[sq] + (uint32_t)n_tok);
                 if (n_tok == 1) top = e->n_ctx;        // a decode pass is replayed from a graph: its launches must hold any length
@@ -1400,9 +1453,13 @@ static bool ensure_graph(itb_engine* e) {
 // The one-kernel step's waits are bounded: a wait that ran out stores (stage << 8) | reason in the status word and every
 // block returns. Turn it into the sticky error and put the grid barrier's counters back.
 static bool check_flag(itb_engine* e) {
-    if (e->mega != 1) return true;
+    if (e->mega != 1 && !e->c->exact) return true;
     int f = 0;
     if (cudaMemcpy(&f, e->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return itb_fail_msg(e->c, "engine: cannot read the device status word");
+    if (f == F32S_FAIL) {
+        cudaMemset(e->err, 0, 4);
+        return itb_fail_msg(e->c, "engine: an F32 weight row never arrived in its shared-memory ring (bounded wait ran out)");
+    }
     if (f) {
         cudaMemset(e->err, 0, 4); cudaMemset(e->mega_sync, 0, 16);
         static const char* const why[] = {"?", "weights never arrived in the ring", "a ring slot was never released", "a grid barrier was never completed",

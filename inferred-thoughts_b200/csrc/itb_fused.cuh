@@ -23,6 +23,7 @@ struct InProj {
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
+    int f32_ring; int* err;                        // serial-k F32 rows through the block's ring (in_proj_smem counts it); status word of its bounded waits
     int tl_slot;                                   // phase-timeline slot of this launch (-1: none)
 };
 
@@ -40,6 +41,16 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     const int tfl = p.br * (nb + 1);
     float* terms = tile + (p.exact ? 32 * 33 : 0) + wid * (tfl + CONV_CAP * 8);
     float* cpre = terms + tfl;
+    // the block's ring for serial-k F32 rows: after every warp's scratch, 16-byte aligned, its mbarriers behind it
+    // (offset arithmetic on the shared array itself: a pointer that went through an integer would be read with generic loads)
+    const size_t ring_off = ((size_t)((const unsigned char*)(tile + (p.exact ? 32 * 33 : 0) + nw * (tfl + CONV_CAP * 8)) - smem) + 127) & ~(size_t)127;
+    float* ring = (float*)(smem + ring_off);
+    unsigned long long* ring_bars = (unsigned long long*)(ring + F32S_FLOATS);
+    if (p.f32_ring && threadIdx.x == 0) {
+        for (int i = 0; i < F32S_STAGES; ++i)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(ring_bars + i)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
 
     // this warp's share of the concatenated Q8_0 rows
     int total = 0;
@@ -69,19 +80,31 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
         for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
     }
-    // F32 rows: one row per warp, handed out from the far end of the grid's warps (serial-k fold or shuffle tree inside).
+    // F32 rows, handed out from the far end of the grid's warps so that consecutive units land on different blocks.
+    // Serial-k: units of 32 rows, a lane per row (each lane folds its own row in k order); otherwise a row per warp, shuffle tree.
     {
-        const int ngw = gridDim.x * nw, gw = ngw - 1 - (wid * (int)gridDim.x + (int)blockIdx.x);   // consecutive rows on different blocks
-        int rbase = 0;
+        const int ngw = gridDim.x * nw, gw = ngw - 1 - (wid * (int)gridDim.x + (int)blockIdx.x);
+        int ubase = 0;
 #pragma unroll 1
         for (int m = 0; m < p.nf; ++m) {
             float* o = p.fout[m] + (size_t)b * p.fstride[m];
-            for (int r = gw - rbase; r < p.f[m].n_out; r += ngw) {
-                if (r < 0) continue;
-                if (p.exact) f32_rows<true>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; }, tfl);
-                else f32_rows<false>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; });
+            if (p.f32_ring) {
+                // one unit per block at most (the host checked): unit u goes to the last warp of block gridDim.x - 1 - u
+                const int units = (p.f[m].n_out + 31) / 32, u = gw - ubase;
+                if (u >= 0 && u < units) {
+                    if (u == 0 && m == 0 && lane == 0) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 6);
+                    f32_rows32_serial(p.f[m].wt + (size_t)u * 32 * n, n, u * 32, min(32, p.f[m].n_out - u * 32), xn, ring, ring_bars, p.err, [&](int row, float v) { o[row] = v; }, (u == 0 && m == 0) ? p.tl_slot : -1);
+                    if (u == 0 && m == 0 && lane == 0) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 7);
+                }
+                ubase += units;
+            } else {
+                for (int r = gw - ubase; r < p.f[m].n_out; r += ngw) {
+                    if (r < 0) continue;
+                    if (p.exact) f32_rows<true>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; }, tfl);
+                    else f32_rows<false>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; });
+                }
+                ubase = (ubase + p.f[m].n_out) % ngw;
             }
-            rbase = (rbase + p.f[m].n_out) % ngw;
         }
     }
     int base = 0;
@@ -115,11 +138,13 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     }
     TL(TLK_IN_PROJ, 4);
     TL(TLK_IN_PROJ, 5);
+    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == blockDim.x - 32) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 8);
 }
 // br a multiple of the pass size 2 * (32 >> gsh)
-size_t in_proj_smem(int n, int exact, int br) {
+size_t in_proj_smem(int n, int exact, int br, int f32_ring = 0) {
     int nb = n / 32;
-    return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (br * (nb + 1) + CONV_CAP * 8) * 4 + 64;
+    return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (br * (nb + 1) + CONV_CAP * 8) * 4 + 64 +
+           (f32_ring ? (size_t)F32S_FLOATS * 4 + F32S_STAGES * 8 + 128 : 0);
 }
 
 // ------------------------------------------------------------------------------------------------------

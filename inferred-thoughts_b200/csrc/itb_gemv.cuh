@@ -337,7 +337,7 @@ template <bool EXACT, class Epi>
 __device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, int r0, int r1, const float* x, float* tile, Epi epi, int tile_floats = 1024) {
     const int lane = threadIdx.x & 31;
     if (EXACT) {
-        float* t16 = (float*)(((uintptr_t)tile + 15) & ~(uintptr_t)15);        // 16-byte aligned view of the scratch
+        float* t16 = tile + ((4 - (int)(((uintptr_t)tile >> 2) & 3)) & 3);     // 16-byte aligned view of the scratch (still an offset from `tile`: shared-memory loads stay shared-memory loads)
         const int T = max(128, (tile_floats - 4) / 128 * 128);
 #pragma unroll 1
         for (int r = r0; r < r1; ++r) {
@@ -397,6 +397,76 @@ __device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, 
             s = warp_sum(s);
             if (lane == 0) epi(r, s);
         }
+    }
+}
+
+// Serial-k F32 rows, 32 rows per warp: lane = row, every lane folds ITS row in k order (product and sum rounded separately,
+// src/ops/naive.rs:49-56), so 32 chains run side by side at one add latency per k for all of them. The unit's weights come
+// from the k-major copy (DevF32::wt): a stage of 128 k is 16 KB in one piece, fetched by ONE bulk asynchronous copy that
+// signals the stage's mbarrier; in shared memory lane r reads word k * 32 + r, no conflicts. Five stages keep enough bytes
+// in flight for one warp to stream at the pace of the chain. Waits are bounded: one that runs out stores `F32S_FAIL` in *err
+// and the fold goes on over whatever the slot holds (the host reads *err after the step). n_in a multiple of 128.
+constexpr int F32S_K = 128, F32S_STAGES = 5, F32S_STAGE_FLOATS = 32 * F32S_K, F32S_FLOATS = F32S_STAGES * F32S_STAGE_FLOATS;
+constexpr int F32S_FAIL = 0x7001;
+template <class Epi>
+__device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_unit, int n_in, int r0, int nr, const float* x, float* ring,
+                                                  unsigned long long* bars, int* err, Epi epi, int dbg_slot = -1) {
+    const int lane = threadIdx.x & 31, nst = n_in / F32S_K;
+    auto issue = [&](int t) {
+        if (t < nst && lane == 0) {
+            const int slot = t % F32S_STAGES;
+            const uint32_t bar = (uint32_t)__cvta_generic_to_shared(bars + slot);
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + slot * F32S_STAGE_FLOATS);
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(dst), "l"(wt_unit + (size_t)t * F32S_STAGE_FLOATS), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)), "r"(bar) : "memory");
+        }
+    };
+    for (int t = 0; t < F32S_STAGES; ++t) issue(t);
+    float sum = 0.0f;
+    long long waited = 0; const long long t_begin = clock64();
+#pragma unroll 1
+    for (int t = 0; t < nst; ++t) {
+        const int slot = t % F32S_STAGES;
+        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(bars + slot), parity = (uint32_t)(t / F32S_STAGES) & 1u;
+        {
+            const long long t0 = clock64();
+            for (;;) {
+                uint32_t ok;
+                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+                if (ok) break;
+                if (clock64() - t0 > 2000000000ll) { if (err) atomicExch(err, F32S_FAIL); break; }
+            }
+            waited += clock64() - t0;
+        }
+        const float* col = ring + slot * F32S_STAGE_FLOATS + lane;
+        const float* xs = x + t * F32S_K;
+        // the products of the next 16 k are formed while the current 16 are added: the adds are the only chain
+        float pa[16], pb[16];
+        auto prod = [&](float (&pr)[16], int k0) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                const float4 xv = *(const float4*)(xs + k0 + i);
+                pr[i] = __fmul_rn(col[(k0 + i) * 32], xv.x); pr[i + 1] = __fmul_rn(col[(k0 + i + 1) * 32], xv.y);
+                pr[i + 2] = __fmul_rn(col[(k0 + i + 2) * 32], xv.z); pr[i + 3] = __fmul_rn(col[(k0 + i + 3) * 32], xv.w);
+            }
+        };
+        prod(pa, 0);
+#pragma unroll
+        for (int k0 = 0; k0 < F32S_K; k0 += 32) {
+            prod(pb, k0 + 16);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sum = __fadd_rn(sum, pa[i]);
+            if (k0 + 32 < F32S_K) prod(pa, k0 + 32);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sum = __fadd_rn(sum, pb[i]);
+        }
+        __syncwarp();                           // every lane has read the slot: it may be refilled
+        issue(t + F32S_STAGES);
+    }
+    if (lane < nr) epi(r0 + lane, sum);
+    if (dbg_slot >= 0 && lane == 0 && g_tl_buf && (unsigned)dbg_slot < g_tl_cap) {
+        g_tl_buf[(size_t)dbg_slot * 16 + 9] = ((unsigned long long)waited << 8) | 2; g_tl_buf[(size_t)dbg_slot * 16 + 10] = ((unsigned long long)(clock64() - t_begin) << 8) | 2;
     }
 }
 

@@ -42,6 +42,9 @@ __device__ __forceinline__ int fp4_slot(const DevFp4& w, int e) {
 struct DevF32 {
     const float* w = nullptr;
     int n_in = 0, n_out = 0;
+    // optional second copy for the serial-k one-token path: units of 32 rows, k-major inside a unit ([unit][k][32 rows], rows
+    // past n_out zero), so that 128 k of a unit are 16 KB in one piece and a lane per row reads them without bank conflicts
+    const float* wt = nullptr;
 };
 
 // ------------------------------------------------------------------ context
@@ -87,8 +90,10 @@ struct itb_ctx {
     struct TcWeights { uint8_t* img = nullptr; uint8_t* sf = nullptr; size_t bytes = 0; };
     std::unordered_map<const void*, TcWeights> tc_weights;
     void* tc_tiles = nullptr; int* tc_n_tiles = nullptr; int* tc_slot_tile = nullptr; uint8_t* tc_b_img = nullptr; uint8_t* tc_b_sf = nullptr; int* tc_status = nullptr;
-    size_t tc_cap_tiles = 0, tc_cap_slots = 0, tc_cap_b = 0, tc_cap_sf = 0;
+    uint8_t* tc_codes = nullptr; uint8_t* tc_scales = nullptr;      // the pass's activation rows as FP4 records
+    size_t tc_cap_tiles = 0, tc_cap_slots = 0, tc_cap_b = 0, tc_cap_sf = 0, tc_cap_codes = 0, tc_cap_scales = 0;
     bool fp4tc = false;      // opts experts=fp4tc: many-row passes multiply FP4 activations on the tensor cores
+    bool attn_mma = false;   // opts attn=mma: many-token passes run attention as 16-bit matrix products even under exact=1 (exact=0 always does)
 };
 // Routed experts over expert-grouped pairs on the FP4 tensor cores (itb_tc.cu). wu != null: out[pair] = silu(Wg x * s_g) * (Wu x * s_u);
 // else out[pair] = W x * s. x: f32 rows on the device, the row of slot s is pair_list[s] / rows_div. False: not run (shape or memory).
@@ -177,6 +182,14 @@ __device__ __forceinline__ void tl_mark_any(int slot, unsigned kernel, unsigned 
         g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
     }
 }
+// From any one thread of any block (the caller picks it).
+__device__ __forceinline__ void tl_mark_raw(int slot, unsigned kernel, unsigned phase) {
+    if (slot >= 0 && g_tl_buf && (unsigned)slot < g_tl_cap) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
+    }
+}
 #define TL(kernel, phase) tl_mark(p.tl_slot, (kernel), (phase))
 enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TLK_ATTN_PART, TLK_ATTN_COMB, TLK_MOE_GLU, TLK_MOE_DOWN, TLK_ARGMAX_P, TLK_ARGMAX_A };
 
@@ -212,7 +225,8 @@ __device__ __forceinline__ float warp_max(float v) {
     0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull, \
     0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull,
 #ifdef __CUDACC__
-static __device__ __constant__ unsigned long long c_exp2_tab[32] = {ITB_EXP2_TAB};
+// In global memory, read through the L1/read-only path: lanes ask for different entries, which the constant bank would serialise.
+static __device__ const unsigned long long c_exp2_tab[32] = {ITB_EXP2_TAB};
 #endif
 __host__ __device__ inline float itb_expf_lib(float x, const unsigned long long* tab) {
     const double N = 32.0, inv_ln2_n = 0x1.71547652b82fep+0 * N, shift = 0x1.8p+52;

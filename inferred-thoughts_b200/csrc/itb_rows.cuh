@@ -51,6 +51,65 @@ __global__ void __launch_bounds__(256) k_matmul_f32_rows(DevF32 w, const float* 
     }
 }
 
+// F32 matrix against many rows in the CPU path's own order (src/ops/naive.rs:49-56: a left fold over k of w[o][k] * x[r][k],
+// product and sum rounded separately). With many rows there is a chain per (row, output), so no chain needs to be spread over
+// lanes: a thread owns a 4 x 4 block of outputs and walks k in order -- a plain tiled SGEMM whose k loop is never reassociated
+// or fused. grid (ceil(n_out / 64), ceil(n_rows / 64)), block 256; k tiles of 32 through shared memory, next tile in flight.
+constexpr int SG_T = 64, SG_K = 32;
+__global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
+    __shared__ float ws[2][SG_K][SG_T + 4], xs[2][SG_K][SG_T + 4];      // [k][output] and [k][row]: a thread reads 4 consecutive of each
+    const int o0 = blockIdx.x * SG_T, r0 = blockIdx.y * SG_T, n = w.n_in;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;             // outputs 4*tx.., rows 4*ty..
+    // loader: thread -> (line 0..63 of the tile, 8 consecutive k)
+    const int ll = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 8;
+    const float* wsrc = w.w + (size_t)min(o0 + ll, w.n_out - 1) * n + lk;
+    const float* xsrc = x + (size_t)min(r0 + ll, n_rows - 1) * n + lk;
+    float4 wa, wb, xa, xb;
+    auto fetch = [&](int k0) {
+        wa = __ldg((const float4*)(wsrc + k0)); wb = __ldg((const float4*)(wsrc + k0 + 4));
+        xa = __ldg((const float4*)(xsrc + k0)); xb = __ldg((const float4*)(xsrc + k0 + 4));
+    };
+    auto stash = [&](int buf) {
+        ws[buf][lk][ll] = wa.x; ws[buf][lk + 1][ll] = wa.y; ws[buf][lk + 2][ll] = wa.z; ws[buf][lk + 3][ll] = wa.w;
+        ws[buf][lk + 4][ll] = wb.x; ws[buf][lk + 5][ll] = wb.y; ws[buf][lk + 6][ll] = wb.z; ws[buf][lk + 7][ll] = wb.w;
+        xs[buf][lk][ll] = xa.x; xs[buf][lk + 1][ll] = xa.y; xs[buf][lk + 2][ll] = xa.z; xs[buf][lk + 3][ll] = xa.w;
+        xs[buf][lk + 4][ll] = xb.x; xs[buf][lk + 5][ll] = xb.y; xs[buf][lk + 6][ll] = xb.z; xs[buf][lk + 7][ll] = xb.w;
+    };
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+    fetch(0); stash(0);
+    __syncthreads();
+    const int nk = n / SG_K;
+    for (int t = 0; t < nk; ++t) {
+        const int buf = t & 1;
+        if (t + 1 < nk) fetch((t + 1) * SG_K);
+#pragma unroll
+        for (int kk = 0; kk < SG_K; ++kk) {
+            const float4 wv = *(const float4*)&ws[buf][kk][4 * tx], xv = *(const float4*)&xs[buf][kk][4 * ty];
+            const float wq[4] = {wv.x, wv.y, wv.z, wv.w}, xq[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(wq[j], xq[i]));
+        }
+        if (t + 1 < nk) stash(buf ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = r0 + 4 * ty + i;
+        if (r >= n_rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int o = o0 + 4 * tx + j;
+            if (o < w.n_out) out[(size_t)r * w.n_out + o] = acc[i][j];
+        }
+    }
+}
+
 // RMSNorm + Q8_0 quantisation of each row (src/ops/naive.rs:139-152, :653-675): normalised f32 row, int8 quants,
 // scales. grid = rows, block 256.
 __global__ void __launch_bounds__(256) k_norm_quant(const float* x, const float* w, int n, float eps, float* xn_out, int8_t* xq, float* xs) {

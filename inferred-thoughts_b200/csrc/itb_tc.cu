@@ -12,15 +12,18 @@
 namespace {
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
-    unsigned long long t0, t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+// Bounded wait on an mbarrier phase: polls (the try_wait itself suspends for a short, hardware-chosen time) and gives up after
+// `limit_cycles` of this SM's clock (the cheap clock: reading the global timer in the polling loop costs microseconds).
+__device__ __forceinline__ bool tc_mbar_wait(uint32_t bar, uint32_t parity, unsigned long long limit_cycles) {
+    const long long t0 = clock64();
     for (;;) {
         uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        if (t - t0 > limit_ns) return false;
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+            if (ok) return true;
+        }
+        if ((unsigned long long)(clock64() - t0) > limit_cycles) return false;
     }
 }
 // Shared-memory matrix descriptor, K-major, no swizzle: 8-row x 16-byte core matrices; `lbo` = bytes between the two 16-byte
@@ -231,45 +234,71 @@ __global__ void k_fp4_quant_plain(const float* x, size_t n_blocks, uint8_t* scal
 // ---- tiles of one pass ----
 // A tile = up to TC_NMAX pairs of one expert (slots [n0, n0 + cnt) of the expert-sorted pair list), padded to a multiple of 16.
 struct TcTile { int expert, n0, cnt, npad; unsigned b_off, sf_off; };   // offsets in padded rows / in 512-byte scale tiles
-// pair_off[e .. e+1): the expert's slots. One thread walks the experts (a few hundred), then all threads label the slots.
-__global__ void k_tc_build_tiles(const int* pair_off, int n_expert, int expert_lo, int expert_cnt, TcTile* tiles, int* n_tiles_out, int max_tiles, int* slot_tile, int k_blocks) {
-    __shared__ int s_nt;
-    if (threadIdx.x == 0) {
-        int nt = 0; unsigned boff = 0, soff = 0;
-        for (int e = 0; e < n_expert; ++e) {
-            const bool here = e >= expert_lo && e < expert_lo + expert_cnt;
-            const int a = pair_off[e], z = pair_off[e + 1];
-            for (int n0 = a; n0 < z && here; n0 += TC_NMAX) {
-                const int cnt = min(TC_NMAX, z - n0), npad = (cnt + 15) & ~15;
-                if (nt < max_tiles) tiles[nt] = TcTile{e, n0, cnt, npad, boff, soff};
-                nt++; boff += (unsigned)npad; soff += (unsigned)k_blocks;     // one 512-byte scale tile per K64 block (npad <= 128)
-            }
-        }
-        s_nt = min(nt, max_tiles);
-        *n_tiles_out = s_nt;
-    }
+// pair_off[e .. e+1): the expert's slots. One block; a thread per expert counts its tiles, a block-wide scan places them
+// (tiles in expert order, so the blocks that share an expert's weights run next to each other).
+__global__ void __launch_bounds__(1024) k_tc_build_tiles(const int* pair_off, int n_expert, int expert_lo, int expert_cnt, TcTile* tiles, int* n_tiles_out, int max_tiles, int k_blocks) {
+    __shared__ int s_tiles[1024], s_rows[1024];
+    const int e = threadIdx.x;
+    int a = 0, z = 0;
+    if (e < n_expert && e >= expert_lo && e < expert_lo + expert_cnt) { a = pair_off[e]; z = pair_off[e + 1]; }
+    const int cnt = z - a, nt = (cnt + TC_NMAX - 1) / TC_NMAX;
+    // padded rows of this expert's tiles: full tiles are 128, the last one is rounded up to 16
+    const int rows = nt ? (nt - 1) * TC_NMAX + ((cnt - (nt - 1) * TC_NMAX + 15) & ~15) : 0;
+    s_tiles[e] = nt; s_rows[e] = rows;
     __syncthreads();
-    for (int t = 0; t < s_nt; ++t)
-        for (int i = threadIdx.x; i < tiles[t].cnt; i += blockDim.x) slot_tile[tiles[t].n0 + i] = t;
+    for (int d = 1; d < 1024; d <<= 1) {                  // inclusive scans of both counts
+        const int t1 = e >= d ? s_tiles[e - d] : 0, r1 = e >= d ? s_rows[e - d] : 0;
+        __syncthreads();
+        s_tiles[e] += t1; s_rows[e] += r1;
+        __syncthreads();
+    }
+    int ti = s_tiles[e] - nt; unsigned boff = (unsigned)(s_rows[e] - rows);
+    for (int n0 = a; n0 < z; n0 += TC_NMAX, ++ti) {
+        const int c = min(TC_NMAX, z - n0), npad = (c + 15) & ~15;
+        if (ti < max_tiles) tiles[ti] = TcTile{e, n0, c, npad, boff, (unsigned)ti * (unsigned)k_blocks};
+        boff += (unsigned)npad;
+    }
+    if (e == 1023) *n_tiles_out = min(s_tiles[1023], max_tiles);
 }
 
-// Activation rows -> FP4 operand tiles. One thread per (slot, 16-element block). src row of a slot: pair_list[slot] / rows_div
-// (rows_div = n_used when the rows are tokens shared by a token's picks, 1 when there is a row per pair).
-__global__ void k_tc_quant_tiles(const float* x, int n_in, const int* pair_list, int rows_div, int n_slots, const TcTile* tiles, const int* slot_tile,
-                                 uint8_t* b_img, uint8_t* sf_img) {
-    const int bpr = n_in / 16;
-    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= (size_t)n_slots * bpr) return;
-    const int slot = (int)(idx / bpr), b = (int)(idx % bpr);
-    const TcTile t = tiles[slot_tile[slot]];
-    const int n = slot - t.n0;
+// Activation rows -> FP4 records, each row once: codes [row][n_in / 2] (element order, low nibble first), scale codes
+// [row][n_in / 16]. One thread per 16-element block.
+__global__ void k_tc_quant_rows(const float* x, size_t n_blocks, uint8_t* codes, uint8_t* scales) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
     uint32_t sc, lo, hi;
-    fp4_quant_block(x + (size_t)(pair_list[slot] / rows_div) * n_in + b * 16, &sc, &lo, &hi);
-    const int kb = b >> 2, q = b & 3;            // K64 block, 16-element quarter of it: bytes [8q, 8q + 8) of the row's 32
-    uint8_t* blk = b_img + (size_t)t.b_off * (n_in / 2) + (size_t)kb * (t.npad * 32);
-    uint8_t* dst = blk + (q >> 1) * (t.npad * 16) + (n >> 3) * 128 + (n & 7) * 16 + (q & 1) * 8;
-    *(uint2*)dst = make_uint2(lo, hi);
-    sf_img[((size_t)t.sf_off + kb) * 512 + (n & 31) * 16 + (n >> 5) * 4 + q] = (uint8_t)sc;
+    fp4_quant_block(x + b * 16, &sc, &lo, &hi);
+    *(uint2*)(codes + b * 8) = make_uint2(lo, hi);
+    scales[b] = (uint8_t)sc;
+}
+// FP4 records -> the operand tiles of one pass. grid (tiles, row eighths); a thread moves 16 bytes (32 elements) of one slot's row
+// and, for every other chunk, the 4 scale codes of its K64 block. Source row of a slot: pair_list[slot] / rows_div (rows_div =
+// n_used when the rows are tokens shared by a token's picks, 1 when there is a row per pair). Padding rows are written as zeros.
+__global__ void k_tc_gather_tiles(const uint8_t* codes, const uint8_t* scales, int n_in, const int* pair_list, int rows_div, const TcTile* tiles,
+                                  const int* n_tiles, uint8_t* b_img, uint8_t* sf_img) {
+    if ((int)blockIdx.x >= *n_tiles) return;
+    const TcTile t = tiles[blockIdx.x];
+    const int cpr = n_in / 32;                              // 16-byte chunks per row
+    uint8_t* img = b_img + (size_t)t.b_off * (n_in / 2);
+    uint8_t* sf = sf_img + (size_t)t.sf_off * 512;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < t.npad * cpr; i += gridDim.y * blockDim.x) {
+        const int n = i / cpr, ch = i % cpr, kb = ch >> 1, half = ch & 1;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        uint32_t s4 = 0;
+        if (n < t.cnt) {
+            const size_t row = (size_t)(pair_list[t.n0 + n] / rows_div);
+            v = *(const uint4*)(codes + row * (n_in / 2) + (size_t)ch * 16);
+            if (!half) s4 = *(const uint32_t*)(scales + row * (n_in / 16) + kb * 4);
+        }
+        *(uint4*)(img + (size_t)kb * (t.npad * 32) + half * (t.npad * 16) + (n >> 3) * 128 + (n & 7) * 16) = v;
+        if (!half) *(uint32_t*)(sf + (size_t)kb * 512 + (n & 31) * 16 + (n >> 5) * 4) = s4;
+    }
+    // the rest of every 512-byte scale tile (rows npad .. 127): zeros, so a tile never holds codes of an earlier pass
+    const int kbs = n_in / 64, rest = 128 - t.npad;
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < rest * kbs; i += gridDim.y * blockDim.x) {
+        const int n = t.npad + i / kbs, kb = i % kbs;
+        *(uint32_t*)(sf + (size_t)kb * 512 + (n & 31) * 16 + (n >> 5) * 4) = 0u;
+    }
 }
 
 // Expert weights -> operand tiles, once per stack. One thread per (expert, row, K64 block).
@@ -299,6 +328,8 @@ struct TcGemm {
     int n_out, n_in;                                     // rows of one matrix, K
     float* out; int out_stride;                          // out[pair][n_out]
     int* status;
+    int exact_silu;                                      // SiLU through the library-exact exponential (f64 unit: several times the epilogue)
+    long long* prof;                                     // optional: 8 clock64 stamps per block (ITB_TC_PROF=1)
 };
 __device__ __forceinline__ void tc_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
@@ -309,9 +340,11 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc;
     __shared__ uint32_t s_tmem;
+    __shared__ int s_pair[TC_NMAX];
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     if ((int)blockIdx.x >= *p.n_tiles) return;
     const TcTile t = p.tiles[blockIdx.x];
+    if (tid < TC_NMAX) s_pair[tid] = tid < t.cnt ? p.pair_list[t.n0 + tid] : -1;      // where each column's result goes
     const int mt = blockIdx.y, kbs = p.n_in / 64, n_stage = kbs / TC_KS, el = t.expert - p.expert_lo;
     const uint32_t a_bytes = TC_KS * 4096, b_bytes = (uint32_t)t.npad * 32 * TC_KS, sf_bytes = TC_KS * 512;
     // stage layout: A_g | A_u | B | SFA_g | SFA_u | SFB
@@ -335,6 +368,8 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tm = s_tmem;
+    long long* pf = p.prof ? p.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+    if (pf && tid == 0) { pf[0] = clock64(); pf[7] = t.npad; }
     // tensor memory: D_g at 0, D_u at 128, scale factors from 256: per stage slot 48 columns (SFA_g 16, SFA_u 16, SFB 16)
     const uint32_t d_g = tm, d_u = tm + 128, sf0 = tm + 256;
     bool ok = true;
@@ -342,7 +377,7 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
         const size_t w_tile = ((size_t)el * (p.n_out / TC_M) + mt) * kbs;
         for (int st = 0; st < n_stage && ok; ++st) {
             const int s = st % TC_STAGES;
-            if (st >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((st / TC_STAGES) - 1) & 1, 1000000000ull);
+            if (st >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((st / TC_STAGES) - 1) & 1, 2000000000ull);
             if (!ok) break;
             const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * stage_bytes;
             const uint32_t total = a_bytes * (GLU ? 2 : 1) + b_bytes + sf_bytes * (GLU ? 3 : 2);
@@ -360,58 +395,78 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
         if (!ok) atomicCAS(p.status, 0, 3);
     } else if (wid == 5 && lane == 0) {
         const uint32_t idesc = tc_idesc_fp4(TC_M, t.npad);
+        // descriptors of stage slot 0; a slot or K block further on only moves the 14-bit start-address field (address >> 4), which
+        // cannot carry out of it (shared memory ends below 256 KB), so the low words are advanced by plain adds
+        const uint64_t dA = tc_desc(sbase, 2048, 128), dAu = tc_desc(sbase + o_au, 2048, 128), dB = tc_desc(sbase + o_b, (uint32_t)t.npad * 16, 128);
+        const uint64_t dSg = tc_desc(sbase + o_sfg, 128, 128), dSu = tc_desc(sbase + o_sfu, 128, 128), dSb = tc_desc(sbase + o_sfb, 128, 128);
+        const uint32_t b_step = (uint32_t)(t.npad * 32) >> 4;
         for (int st = 0; st < n_stage && ok; ++st) {
             const int s = st % TC_STAGES;
-            ok = tc_mbar_wait(tc_smem(&s_full[s]), (st / TC_STAGES) & 1, 1000000000ull);
+            ok = tc_mbar_wait(tc_smem(&s_full[s]), (st / TC_STAGES) & 1, 2000000000ull);
             if (!ok) break;
+            if (pf && st == 0) pf[1] = clock64();
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t src = sbase + s * stage_bytes, sft = sf0 + s * 48;
+            const uint32_t so = (uint32_t)s * (stage_bytes >> 4), sft = sf0 + s * 48;
+#pragma unroll
             for (int k = 0; k < TC_KS; ++k) {
-                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 4 * k), "l"(tc_desc(src + o_sfg + 512 * k, 128, 128)) : "memory");
-                if (GLU) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 16 + 4 * k), "l"(tc_desc(src + o_sfu + 512 * k, 128, 128)) : "memory");
-                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 32 + 4 * k), "l"(tc_desc(src + o_sfb + 512 * k, 128, 128)) : "memory");
+                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 4 * k), "l"(dSg + so + 32u * k) : "memory");
+                if (GLU) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 16 + 4 * k), "l"(dSu + so + 32u * k) : "memory");
+                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 32 + 4 * k), "l"(dSb + so + 32u * k) : "memory");
             }
+#pragma unroll
             for (int k = 0; k < TC_KS; ++k) {
-                const uint64_t db = tc_desc(src + o_b + k * (t.npad * 32), (uint32_t)t.npad * 16, 128);
+                const uint64_t db = dB + so + b_step * k;
                 const uint32_t acc = (st | k) ? 1u : 0u;
-                tc_mma_fp4(d_g, tc_desc(src + k * 4096, 2048, 128), db, idesc, sft + 4 * k, sft + 32 + 4 * k, acc);
-                if (GLU) tc_mma_fp4(d_u, tc_desc(src + o_au + k * 4096, 2048, 128), db, idesc, sft + 16 + 4 * k, sft + 32 + 4 * k, acc);
+                tc_mma_fp4(d_g, dA + so + 256u * k, db, idesc, sft + 4 * k, sft + 32 + 4 * k, acc);
+                if (GLU) tc_mma_fp4(d_u, dAu + so + 256u * k, db, idesc, sft + 16 + 4 * k, sft + 32 + 4 * k, acc);
             }
             asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
         }
+        if (pf) pf[2] = clock64();
         if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc)) : "memory");
         else { atomicCAS(p.status, 0, 4); asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_acc)) : "memory"); }
     } else if (wid < 4) {
         // epilogue: lane quarter `wid` of tensor memory = weight rows 32 * wid .. of this tile; columns = the tile's tokens
         ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull));      // one verdict per warp: the loads below are warp-wide
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (pf && tid == 0) pf[3] = clock64();
         if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
             const int row = mt * TC_M + wid * 32 + lane;
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
-            for (int c = 0; c < t.npad; c += 8) {
-                uint32_t g[8], u[8];
+            for (int c = 0; c < t.npad; c += 16) {                    // npad is a multiple of 16
+                uint32_t g[16], u[16];
                 const uint32_t ta = ((uint32_t)(wid * 32) << 16) + (uint32_t)c;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                             : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]) : "r"(d_g + ta) : "memory");
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                             : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]),
+                               "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15]) : "r"(d_g + ta) : "memory");
                 if (GLU)
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]) : "r"(d_u + ta) : "memory");
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
+                                   "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]) : "r"(d_u + ta) : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (c + j < t.cnt) {
+                for (int j = 0; j < 16; ++j) {
+                    const int pair = s_pair[c + j];
+                    if (pair >= 0) {
                         float v = __uint_as_float(g[j]);
                         if (p.s2g) v = v * sg;
-                        if (GLU) { float w = __uint_as_float(u[j]); if (p.s2u) w = w * su; v = silu_f(v) * w; }   // src/ops/mod.rs:1105-1117
-                        p.out[(size_t)p.pair_list[t.n0 + c + j] * p.out_stride + row] = v;
+                        if (GLU) {
+                            // SiLU(gate) * up (src/ops/mod.rs:1105-1117). exact=0: the fast exponential (this path is tolerance class
+                            // through the tensor core's summation order anyway); exact=1: the library-exact one, on the f64 unit
+                            float w = __uint_as_float(u[j]); if (p.s2u) w = w * su;
+                            v = (p.exact_silu ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * w;
+                        }
+                        p.out[(size_t)pair * p.out_stride + row] = v;
                     }
                 }
             }
         }
     }
+    if (pf && tid == 0) pf[4] = clock64();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (wid == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+    if (pf && tid == 0) pf[5] = clock64();
 }
 inline size_t tc_gemm_smem(bool glu) {
     const size_t a = TC_KS * 4096, b = (size_t)TC_NMAX * 32 * TC_KS, sf = TC_KS * 512;
@@ -420,12 +475,12 @@ inline size_t tc_gemm_smem(bool glu) {
 
 }  // namespace
 
-bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n_out % TC_M == 0 && !w.slot_map; }
+bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n_out % TC_M == 0 && !w.slot_map && w.expert_lo + w.n_expert <= 1024; }
 void itb_tc_free(itb_ctx* c) {
     for (auto& kv : c->tc_weights) { cudaFree(kv.second.img); cudaFree(kv.second.sf); }
     c->tc_weights.clear();
-    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status);
-    c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr;
+    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales);
+    c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr; c->tc_codes = nullptr; c->tc_scales = nullptr; c->tc_cap_codes = c->tc_cap_scales = 0;
     c->tc_cap_tiles = c->tc_cap_slots = c->tc_cap_b = c->tc_cap_sf = 0;
 }
 static const itb_ctx::TcWeights* tc_weights_of(itb_ctx* c, cudaStream_t st, const DevFp4& w) {
@@ -456,7 +511,6 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
     const itb_ctx::TcWeights* tg = tc_weights_of(c, st, wg);
     const itb_ctx::TcWeights* tu = wu ? tc_weights_of(c, st, *wu) : nullptr;
     if (!tg || (wu && !tu)) return itb_fail_msg(c, "FP4 tensor path: out of device memory for the tiled expert weights");
-    const int E = wg.expert_lo + wg.n_expert;        // global ids run to the end of this shard at least; pair_off covers every expert the caller grouped
     const size_t kbs = wg.n_in / 64, max_tiles = (size_t)wg.n_expert + (size_t)n_pairs / TC_NMAX + 1;
     const size_t b_rows = (size_t)n_pairs + 16 * max_tiles;
     TcTile* tiles = (TcTile*)c->tc_tiles;
@@ -464,21 +518,22 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
     bool ok = tc_grow(&tiles, &cap_t, max_tiles, st);
     c->tc_tiles = tiles; c->tc_cap_tiles = cap_t;
     size_t cap1 = c->tc_n_tiles ? 1 : 0, cap2 = c->tc_status ? 1 : 0;
-    ok = ok && tc_grow(&c->tc_n_tiles, &cap1, 1, st) && tc_grow(&c->tc_status, &cap2, 1, st) && tc_grow(&c->tc_slot_tile, &c->tc_cap_slots, (size_t)n_pairs, st) &&
-         tc_grow(&c->tc_b_img, &c->tc_cap_b, b_rows * (wg.n_in / 2), st) && tc_grow(&c->tc_b_sf, &c->tc_cap_sf, max_tiles * kbs * 512, st);
+    ok = ok && tc_grow(&c->tc_n_tiles, &cap1, 1, st) && tc_grow(&c->tc_status, &cap2, 1, st) &&
+         tc_grow(&c->tc_b_img, &c->tc_cap_b, b_rows * (wg.n_in / 2), st) && tc_grow(&c->tc_b_sf, &c->tc_cap_sf, max_tiles * kbs * 512, st) &&
+         tc_grow(&c->tc_codes, &c->tc_cap_codes, (size_t)n_pairs * (wg.n_in / 2), st) && tc_grow(&c->tc_scales, &c->tc_cap_scales, (size_t)n_pairs * (wg.n_in / 16), st);
     if (!ok) return itb_fail_msg(c, "FP4 tensor path: out of device memory for the pass");
     cudaMemsetAsync(c->tc_status, 0, 4, st);
-    cudaMemsetAsync(c->tc_b_img, 0, b_rows * (wg.n_in / 2), st);        // padding rows: zero codes, zero scales
-    cudaMemsetAsync(c->tc_b_sf, 0, max_tiles * kbs * 512, st);
-    (void)E;
-    k_tc_build_tiles<<<1, 256, 0, st>>>(pair_off, wg.expert_lo + wg.n_expert, wg.expert_lo, wg.n_expert, tiles, c->tc_n_tiles, (int)max_tiles, c->tc_slot_tile, (int)kbs);
-    const size_t nq = (size_t)n_pairs * (wg.n_in / 16);
-    k_tc_quant_tiles<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(x, wg.n_in, pair_list, rows_div, n_pairs, tiles, c->tc_slot_tile, c->tc_b_img, c->tc_b_sf);
+    k_tc_build_tiles<<<1, 1024, 0, st>>>(pair_off, wg.expert_lo + wg.n_expert, wg.expert_lo, wg.n_expert, tiles, c->tc_n_tiles, (int)max_tiles, (int)kbs);
+    const size_t x_rows = rows_div == 1 ? (size_t)n_pairs : rows_div >= n_pairs ? 1 : ((size_t)n_pairs + rows_div - 1) / rows_div;
+    const size_t nq = x_rows * (wg.n_in / 16);
+    k_tc_quant_rows<<<(unsigned)((nq + 255) / 256), 256, 0, st>>>(x, nq, c->tc_codes, c->tc_scales);
+    // scale tiles of a pass are whole 512-byte tiles: rows past npad of a tile's scale tile are never read by a matrix of npad rows
+    k_tc_gather_tiles<<<dim3((unsigned)max_tiles, 4), 256, 0, st>>>(c->tc_codes, c->tc_scales, wg.n_in, pair_list, rows_div, tiles, c->tc_n_tiles, c->tc_b_img, c->tc_b_sf);
     TcGemm g{};
     g.wg_img = tg->img; g.wg_sf = tg->sf; g.wu_img = tu ? tu->img : nullptr; g.wu_sf = tu ? tu->sf : nullptr;
     g.s2g = wg.scale2; g.s2u = wu ? wu->scale2 : nullptr; g.expert_lo = wg.expert_lo;
     g.b_img = c->tc_b_img; g.b_sf = c->tc_b_sf; g.tiles = tiles; g.n_tiles = c->tc_n_tiles; g.pair_list = pair_list;
-    g.n_out = wg.n_out; g.n_in = wg.n_in; g.out = out; g.out_stride = wg.n_out; g.status = c->tc_status;
+    g.n_out = wg.n_out; g.n_in = wg.n_in; g.out = out; g.out_stride = wg.n_out; g.status = c->tc_status; g.exact_silu = c->exact ? 1 : 0;
     static bool attr = false;
     if (!attr) {
         cudaFuncSetAttribute(k_tc_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(true));
@@ -486,9 +541,27 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
         attr = true;
     }
     const dim3 grid((unsigned)max_tiles, (unsigned)(wg.n_out / TC_M));
+    static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
+    const size_t n_blocks = (size_t)grid.x * grid.y;
+    if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
     if (wu) k_tc_gemm<true><<<grid, 192, tc_gemm_smem(true), st>>>(g);
     else k_tc_gemm<false><<<grid, 192, tc_gemm_smem(false), st>>>(g);
-    c->launches += 3;
+    if (prof_on && g.prof) {
+        std::vector<long long> h(n_blocks * 8);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), g.prof, n_blocks * 64, cudaMemcpyDeviceToHost);
+        cudaFree(g.prof);
+        double acc[5] = {0, 0, 0, 0, 0}; size_t n = 0; double cols = 0;
+        for (size_t b = 0; b < n_blocks; ++b) {
+            const long long* q = &h[b * 8];
+            if (!q[0] || !q[5]) continue;
+            acc[0] += (double)(q[1] - q[0]); acc[1] += (double)(q[2] - q[1]); acc[2] += (double)(q[3] - q[2]); acc[3] += (double)(q[4] - q[3]); acc[4] += (double)(q[5] - q[0]);
+            cols += (double)q[7]; ++n;
+        }
+        if (n) fprintf(stderr, "tc_gemm glu=%d blocks %zu (avg cols %.0f): cycles start->first stage %.0f, main loop issue %.0f, issue end->accumulators ready %.0f, epilogue %.0f, whole block %.0f\n",
+                       wu ? 1 : 0, n, cols / n, acc[0] / n, acc[1] / n, acc[2] / n, acc[3] / n, acc[4] / n);
+    }
+    c->launches += 4;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return itb_fail(c, "FP4 tensor path: launch", e);
     return true;

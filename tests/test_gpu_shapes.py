@@ -152,3 +152,54 @@ def test_prefill_pass_with_fp4_tensor_core_experts_against_the_oracle_with_fp4_a
     print(f"fp4tc prefill: logits max-abs {err:.3e}, routing ids differing on the last token {mism}/{L * K}")
     assert mism <= 2
     ops.check(); eng.close(); model.close(); ops.close()
+
+
+@pytest.mark.parametrize("shape,kv", [("mid", "f16"), ("m35b", "f16"), ("m35b", "bf16")])
+def test_prefill_with_tensor_core_attention_against_the_oracle(shape, kv):
+    """attn=mma: many-token passes run causal attention as 16-bit matrix products over (token, head) tiles with a running
+    softmax -- q and the probabilities rounded to the cache's type, sums reassociated -- so the logits are held to the
+    north-star tolerance, not to the bit. A 150-token prompt in one pass (several K/V tiles, a ragged last query tile), 70 more
+    tokens in a second pass (queries that start deep in the cache), then two teacher-forced single-token steps (the split-K
+    path over the cache the tensor-core pass wrote), for head_dim 64 with 4 heads per KV head and head_dim 256 with 8."""
+    from inferred_thoughts_b200 import host
+    dims, seed = (configs.MID, configs.SEEDS["mid"]) if shape == "mid" else SHAPES["m35b"]
+    ops = host.B200Ops(0, "exact=1,attn=mma" + (",kv=bf16" if kv == "bf16" else ""))
+    model = host.Model(ops, host_dims(dims)); model.synth(seed)
+    om = O.OracleModel(oracle_dims(dims))
+    for s in om.specs:
+        data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+        om.set_tensor(s["name"], data, sc)
+    O.lib().orc_set_threads(max(1, O.lib().orc_hw_threads()))
+    prompt = prompt_ids(51, 220, dims["n_vocab"])
+    eng = host.Engine(model, 256, 1)
+    om.begin(256, kv_bf16=(kv == "bf16"))
+    o = om.forward(prompt[:150]); g = eng.prefill(prompt[:150])
+    worst = _check_logits(o, g, "first pass")
+    o = om.forward(prompt[150:]); g = eng.prefill(prompt[150:])
+    worst = max(worst, _check_logits(o, g, "second pass"))
+    for step in range(2):
+        t = int(np.argmax(o))
+        o = om.forward([t]); lg, _ = eng.decode([t]); g = lg[0]
+        worst = max(worst, _check_logits(o, g, f"decode step {step}"))
+    print(f"attn=mma {shape} kv={kv}: worst logits max-abs {worst:.3e}")
+    ops.check(); eng.close(); model.close(); ops.close()
+
+
+def test_three_sequences_with_tensor_core_attention():
+    """Three sequences of 40 tokens in one pass (query tiles never straddle sequences), each against the oracle alone."""
+    from inferred_thoughts_b200 import host
+    dims, seed = SHAPES["m35b"]
+    ops = host.B200Ops(0, "exact=1,attn=mma")
+    model = host.Model(ops, host_dims(dims)); model.synth(seed)
+    om = O.OracleModel(oracle_dims(dims))
+    for s in om.specs:
+        data, sc = model.synth_read(seed, s["name"], s["bytes"], s["n_expert"] if s["has_scale"] else 0)
+        om.set_tensor(s["name"], data, sc)
+    O.lib().orc_set_threads(max(1, O.lib().orc_hw_threads()))
+    prompts = np.stack([prompt_ids(60 + i, 40, dims["n_vocab"]) for i in range(3)])
+    eng = host.Engine(model, N_CTX, 3)
+    g0 = eng.prefill(prompts)
+    for i in range(3):
+        om.begin(N_CTX)
+        _check_logits(om.forward(prompts[i]), g0[i], f"sequence {i}")
+    ops.check(); eng.close(); model.close(); ops.close()
