@@ -47,7 +47,14 @@ typedef struct { const float *q, *k, *v, *alpha, *beta, *ssm_a, *dt_bias; size_t
 
 /* ---- context ---- */
 /* opts: "key=value,..." ; keys: kv=f16|bf16 (default f16, the reference's KV dtype, src/cache/mod.rs:8-15),
- * exact=0|1 (1: F32 dots accumulate serially like the CPU path; default 1 for the op-level seam),
+ * exact=0|1 (1, default: every sum in the CPU path's order -- F32 dots fold serially, attention walks positions in order --
+ *   so results equal the CPU path bit for bit; 0: tree-summed F32 dots, split-K attention, and the many-token kernels below),
+ * many-token passes (each also selectable on its own under exact=1; all tolerance class except dense=q8tc):
+ *   dense=q8tc     dense Q8_0 matmuls as tcgen05 int8 MMAs per 32-element block, scales applied in CPU order (bit-identical),
+ *   experts=fp4tc  routed experts as FP4 x FP4 block-scaled tcgen05 GEMMs (the reference's default device arithmetic,
+ *                  src/ops/cuda/mod.rs:239-248; exact=1 keeps the library-exact SiLU in their epilogue),
+ *   attn=mma       causal attention as 16-bit matrix products over (token, head) tiles,
+ *   gdn=chunk      the delta rule chunk-parallel (64-token chunks),
  * libm=cr (log stays correctly rounded; by default the kernels' log follows the host C library's logf bit for bit through a
  * correction table built at the first itb_create of the process, 61 MB per device, because that is what the CPU path calls). */
 int         itb_create(int device_ordinal, const char* opts, itb_ctx** out);   /* 0 ok */

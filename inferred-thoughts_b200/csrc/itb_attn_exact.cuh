@@ -66,6 +66,7 @@ struct AxOut {
     const int* n_pos_dev; int n_pos_last, n_q;
     int kv_dim, hd, n_head, n_head_kv, bf16;
     const float* gate; float* out; int8_t* out_q; float* out_s;
+    int weights_ready;             // the scores buffer already holds the softmax weights (k_attn_softmax_exact ran): skip the softmax here
 };
 __global__ void __launch_bounds__(256) k_attn_out_exact(AxOut p) {
     extern __shared__ __align__(16) unsigned char smem[];
@@ -88,26 +89,30 @@ __global__ void __launch_bounds__(256) k_attn_out_exact(AxOut p) {
         }
     };
     if (wid > 0 && n_pos > 0) stage(0);
-    float mx = -INFINITY;
-    for (int s = tid; s < n_pos; s += 256) { const float v = sc[s]; w[s] = v; mx = fmaxf(mx, v); }
-    mx = warp_max(mx);
-    if (lane == 0) s_red[wid] = mx;
-    __syncthreads();
-    mx = s_red[0];
-    for (int k = 1; k < 8; ++k) mx = fmaxf(mx, s_red[k]);
-    for (int s = tid; s < n_pos; s += 256) w[s] = exp_f(w[s] - mx);
-    __syncthreads();
-    if (tid == 0) {                                               // the sum in position order
-        float sum = 0.0f;
-        int s = 0;
-        for (; s + 4 <= n_pos; s += 4) { const float4 e = *(const float4*)(w + s); sum += e.x; sum += e.y; sum += e.z; sum += e.w; }
-        for (; s < n_pos; ++s) sum += w[s];
-        s_sum = sum;
-    }
-    __syncthreads();
-    {
-        const float sum = s_sum;
-        for (int s = tid; s < n_pos; s += 256) w[s] /= sum;
+    if (p.weights_ready) {
+        for (int s = tid; s < n_pos; s += 256) w[s] = sc[s];
+    } else {
+        float mx = -INFINITY;
+        for (int s = tid; s < n_pos; s += 256) { const float v = sc[s]; w[s] = v; mx = fmaxf(mx, v); }
+        mx = warp_max(mx);
+        if (lane == 0) s_red[wid] = mx;
+        __syncthreads();
+        mx = s_red[0];
+        for (int k = 1; k < 8; ++k) mx = fmaxf(mx, s_red[k]);
+        for (int s = tid; s < n_pos; s += 256) w[s] = exp_f(w[s] - mx);
+        __syncthreads();
+        if (tid == 0) {                                               // the sum in position order
+            float sum = 0.0f;
+            int s = 0;
+            for (; s + 4 <= n_pos; s += 4) { const float4 e = *(const float4*)(w + s); sum += e.x; sum += e.y; sum += e.z; sum += e.w; }
+            for (; s < n_pos; ++s) sum += w[s];
+            s_sum = sum;
+        }
+        __syncthreads();
+        {
+            const float sum = s_sum;
+            for (int s = tid; s < n_pos; s += 256) w[s] /= sum;
+        }
     }
     __syncthreads();
     float o = 0.0f;
@@ -136,6 +141,38 @@ __global__ void __launch_bounds__(256) k_attn_out_exact(AxOut p) {
             if (lane == 0) p.out_s[idx / 32] = dq;
         } else p.out[idx] = o;
     }
+}
+// The softmax of one (row, head)'s scores on its own, in place (many-row passes: the eight blocks that share a head's weights in
+// k_attn_out_exact would each recompute them, and the library-exact exponential is the expensive part): maximum, exponentials,
+// the sum in position order by one thread, the division. grid (n_head, rows), block 256; dynamic shared memory n_pos_max floats.
+struct AxSoft { float* scores; int s_stride; const int* n_pos_dev; int n_pos_last, n_q, n_head; };
+__global__ void __launch_bounds__(256) k_attn_softmax_exact(AxSoft p) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float s_red[8];
+    __shared__ float s_sum;
+    float* w = (float*)smem;
+    const int h = blockIdx.x, r = blockIdx.y, tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int n_pos = p.n_pos_dev ? p.n_pos_dev[r] : p.n_pos_last - p.n_q + 1 + r;
+    float* sc = p.scores + ((size_t)r * p.n_head + h) * p.s_stride;
+    float mx = -INFINITY;
+    for (int s = tid; s < n_pos; s += 256) { const float v = sc[s]; w[s] = v; mx = fmaxf(mx, v); }
+    mx = warp_max(mx);
+    if (lane == 0) s_red[wid] = mx;
+    __syncthreads();
+    mx = s_red[0];
+    for (int k = 1; k < 8; ++k) mx = fmaxf(mx, s_red[k]);
+    for (int s = tid; s < n_pos; s += 256) w[s] = exp_f(w[s] - mx);
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.0f;
+        int s = 0;
+        for (; s + 4 <= n_pos; s += 4) { const float4 e = *(const float4*)(w + s); sum += e.x; sum += e.y; sum += e.z; sum += e.w; }
+        for (; s < n_pos; ++s) sum += w[s];
+        s_sum = sum;
+    }
+    __syncthreads();
+    const float sum = s_sum;
+    for (int s = tid; s < n_pos; s += 256) sc[s] = w[s] / sum;
 }
 inline size_t attn_out_exact_smem(int n_pos_max) { return (size_t)((n_pos_max + 3) & ~3) * 4 + 2 * AX_VT * 32 * 2; }
 inline size_t attn_scores_exact_smem(int hd, int group) { return (size_t)group * (hd + AX_QSTRIDE_PAD) * 4; }

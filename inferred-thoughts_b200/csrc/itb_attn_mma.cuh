@@ -55,7 +55,7 @@ __device__ __forceinline__ uint32_t am_off(int row, int chunk) { return (uint32_
 // grid (ceil(n_tok / (128 / group)), n_head_kv, n_seq); block 256 (8 warps x 16 rows).
 template <int HD, bool BF16>
 __global__ void __launch_bounds__(256, 1) k_attn_mma(AmParams p) {
-    extern __shared__ __align__(128) unsigned char smem[];
+    extern __shared__ __align__(16) unsigned char smem[];
     constexpr int ROW_B = HD * 2, CH = HD / 8;                 // bytes and 16-byte chunks per row
     constexpr int Q_B = AM_ROWS * ROW_B, T_B = AM_KV * ROW_B;
     const uint32_t sQ = (uint32_t)__cvta_generic_to_shared(smem), sK = sQ + Q_B, sV = sK + 2 * T_B;

@@ -26,6 +26,7 @@ void itb_synth_fp4_raw(cudaStream_t st, uint64_t key, size_t per_expert, size_t 
 #include "itb_rows.cuh"
 #include "itb_attn_exact.cuh"
 #include "itb_attn_mma.cuh"
+#include "itb_gdn_chunk.cuh"
 
 void itb_engine_use_logf_fix(const uint32_t* dev_tab, uint32_t n) {
     cudaMemcpyToSymbol(g_logf_fix, &dev_tab, sizeof dev_tab);
@@ -451,6 +452,7 @@ struct itb_engine {
     int32_t* history = nullptr; int* step_counter = nullptr; uint32_t history_cap = 0;
     int* err = nullptr; float* arg_v = nullptr; int* arg_i = nullptr;
     int8_t *aq = nullptr, *hq = nullptr, *sq = nullptr; float *as = nullptr, *hs = nullptr, *ss = nullptr;  // producer-quantised activations
+    float* gdn_scratch = nullptr; size_t gdn_scratch_cap = 0;     // chunk-parallel delta rule: W, Qg, Kd, U, P of every (chunk, value head) of a pass
     float *h_all = nullptr, *o_all = nullptr, *shd = nullptr, *qkvc2 = nullptr; int *pair_off = nullptr, *pair_list = nullptr;  // grouped experts (multi-row path)
     int32_t* prompt = nullptr; size_t prompt_cap = 0;
     int n_split = 1, n_split_rows = 4;
@@ -544,6 +546,14 @@ static void enqueue_exact_attention(itb_engine* e, cudaStream_t st, bool pdl, co
     a.n_head = d.n_head; a.n_head_kv = d.n_head_kv; a.scale = 1.0f / sqrtf((float)hd); a.bf16 = e->c->kv_bf16; a.scores = e->scores; a.s_stride = (int)e->n_ctx;
     launch_k(pdl, k_attn_scores_exact, dim3((n_pos_max + AX_TP - 1) / AX_TP, d.n_head_kv, rows), dim3(AX_TP * group), attn_scores_exact_smem(hd, group), st, a);
     AxOut o{};
+    if (rows >= 8) {
+        // many rows: the softmax once per (row, head), in place, instead of once per block of the weighted-value kernel
+        AxSoft sm{e->scores, (int)e->n_ctx, e->npos, 0, 0, (int)d.n_head};
+        static bool attr2 = false;
+        if (!attr2) { set_smem((const void*)k_attn_softmax_exact, 200 * 1024); attr2 = true; }
+        launch_k(pdl, k_attn_softmax_exact, dim3(d.n_head, rows), dim3(256), (size_t)((n_pos_max + 3) & ~3) * 4, st, sm);
+        o.weights_ready = 1;
+    }
     o.scores = e->scores; o.s_stride = (int)e->n_ctx; o.vslab = vslab; o.slab_stride = slab_stride; o.rows_per_seq = rows_per_seq; o.n_pos_dev = e->npos;
     o.kv_dim = kvd; o.hd = hd; o.n_head = d.n_head; o.n_head_kv = d.n_head_kv; o.bf16 = e->c->kv_bf16; o.gate = e->gate; o.out_q = e->aq; o.out_s = e->as;
     launch_k(pdl, k_attn_out_exact, dim3(hd / 32, d.n_head, rows), dim3(256), attn_out_exact_smem(n_pos_max), st, o);
@@ -836,6 +846,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         set_smem((const void*)k_matmul_f32_rows<20>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<24>, 64 * 1024);
         set_smem((const void*)k_matmul_f32_rows<28>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<32>, 64 * 1024);
         set_smem((const void*)k_tile_q8<1, 256, 4>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
+        set_smem((const void*)k_gdn_chunk_prep<128>, gdn_chunk_prep_smem<128>()); set_smem((const void*)k_gdn_chunk_scan<128>, gdn_chunk_scan_smem<128>());
         set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<2, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<4, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<4, 256, 1>, 226 * 1024);
@@ -845,8 +856,16 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     }
     // Pipelined tile kernels when k is a multiple of the chunk (every matrix of the 35B and 177B shapes); the
     // direct-load MMA kernels otherwise.
-    auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R) {
+    cudaStreamCaptureStatus cap_rows = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(st, &cap_rows);
+    const bool q8tc = c->q8tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
+    // same: this matmul reads the quantised rows the previous one read (their tensor-core images are still current)
+    auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R, bool same = false) {
         const int k = w.n_in;
+        if (q8tc && R >= 64 && itb_tc_q8_shape_ok(w)) {
+            // many rows, dense=q8tc: integer dots of 128 x 128 (row, token) pairs per tcgen05 MMA, scaled and summed in the CPU's order
+            if (itb_tc_q8_gemm(c, st, w, xq, xs, R, out, stride, mode, same)) { launches++; return; }
+        }
         const bool skinny = R <= 32;
         if (skinny && k % 256 == 0) {
             const int ns = std::min(k / 256, TILE_STAGES);
@@ -858,7 +877,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         else k_gemm_q8<4><<<dim3((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (R + MMA_TOK - 1) / MMA_TOK), 256, gemm_smem(w.n_in), st>>>(w, xq, xs, R, out, stride, mode);
         launches++;
     };
-    auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode) { gemm_n(w, xq, xs, out, stride, mode, R); };
+    auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, bool same = false) { gemm_n(w, xq, xs, out, stride, mode, R, same); };
     auto f32mm = [&](const DevF32& w, const float* x, float* out) {
         if (!c->exact && w.n_in % 512 == 0 && w.n_in <= 4096) {
             const dim3 g((w.n_out + 7) / 8, (R + F32_TOK - 1) / F32_TOK);
@@ -871,9 +890,11 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             launches++;
             return;
         }
-        if (c->exact && R >= 8 && w.n_in % SG_K == 0) {
-            // many rows: a chain per (row, output), a thread per 4 x 4 of them, k in order
-            k_sgemm_serial<<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
+        if (c->exact && w.n_in % SG_K == 0) {
+            // a chain per (row, output), a thread per 4 x 4 of them, k in order (also for a few rows: the tile's k loop is as long as a row's chain either way)
+            const int big = ((w.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T);
+            if (big >= sms / 2) k_sgemm_serial<<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
+            else k_sgemm_serial_small<<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, 0, st>>>(w, x, R, out);
             launches++;
             return;
         }
@@ -893,7 +914,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             const int rs = e->slot_of[il];
             const size_t state_stride = (size_t)n_v * sk * sk, conv_stride = (size_t)cd * (d.ssm_d_conv - 1);
             gemm(L.wqkv, e->xq, e->xs, e->qkvc, cd, 0);
-            gemm(L.wgate, e->xq, e->xs, e->z, vd, 0);
+            gemm(L.wgate, e->xq, e->xs, e->z, vd, 0, true);
             f32mm(L.ssm_alpha, e->xn, e->alpha);
             f32mm(L.ssm_beta, e->xn, e->beta);
             float* cst = e->conv_state + (size_t)rs * e->B * conv_stride;
@@ -901,7 +922,14 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             k_conv_state<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(cst, conv_stride, e->qkvc, n_tok, cd, d.ssm_d_conv); launches++;
             k_gdn_pre<<<dim3(R, 2 * n_k + n_v), sk, 0, st>>>(e->qkvc2, cd, e->alpha, e->beta, L.ssm_a, L.dt_bias, sk, n_k, n_v, d.rms_eps,
                                                             e->qh, e->kh, e->vh, e->gb); launches++;
-            {
+            const size_t chunk_need = (size_t)n_seq * ((n_tok + GC - 1) / GC) * n_v * gdn_chunk_floats<128>();
+            if ((c->gdn_chunk || !c->exact) && n_tok >= 32 && sk == 128 && e->gdn_scratch_cap >= chunk_need) {
+                // many tokens: everything that does not touch the state for all chunks at once, then three small products per chunk
+                float* sst = e->ssm_state + (size_t)rs * e->B * state_stride;
+                k_gdn_chunk_prep<128><<<dim3((n_tok + GC - 1) / GC, n_v, n_seq), 256, gdn_chunk_prep_smem<128>(), st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, e->gdn_scratch);
+                k_gdn_chunk_scan<128><<<dim3(n_v, sk / GC_VS, n_seq), 256, gdn_chunk_scan_smem<128>(), st>>>(e->gdn_scratch, n_tok, n_v, sst, state_stride, e->core);
+                launches++;
+            } else {
                 const dim3 gs(n_v, sk / 32, n_seq);
                 float* sst = e->ssm_state + (size_t)rs * e->B * state_stride;
                 if (sk == 128) k_gdn_scan<128><<<gs, 128, 0, st>>>(e->qh, e->kh, e->vh, e->gb, n_tok, n_k, n_v, sst, state_stride, e->core);
@@ -913,8 +941,8 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         } else {
             const int as = e->slot_of[il];
             gemm(L.wq, e->xq, e->xs, e->qg, 2 * qd, 0);
-            gemm(L.wk, e->xq, e->xs, e->kbuf, kvd, 0);
-            gemm(L.wv, e->xq, e->xs, e->vbuf, kvd, 0);
+            gemm(L.wk, e->xq, e->xs, e->kbuf, kvd, 0, true);
+            gemm(L.wv, e->xq, e->xs, e->vbuf, kvd, 0, true);
             AttnPrepRows a{};
             a.qg = e->qg; a.k = e->kbuf; a.v = e->vbuf; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.q_out = e->qn; a.g_out = e->gate;
             a.slab_stride = (size_t)e->n_ctx * kvd;
@@ -969,7 +997,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         // routed FFN
         k_norm_quant<<<R, 256, smem_nq, st>>>(e->x, L.ffn_norm, H, d.rms_eps, e->xn, e->xq, e->xs); launches++;
         gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
-        gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0);
+        gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, true);
         f32mm(L.gate_inp, e->xn, e->router);
         f32mm(L.shared_gate_inp, e->xn, e->shlogit);
         {
@@ -1219,7 +1247,7 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     if (e->ep) { if (e->ep->comm && !e->ep->broken) nccl_api().CommDestroy(e->ep->comm); cudaFreeHost(e->ep->agree_host); delete e->ep; e->ep = nullptr; }
     if (e->tier) { cudaFreeHost(e->tier->slot_map_host); cudaFreeHost(e->tier->ids_host); cudaFreeHost(e->tier->s2_stage); delete e->tier->g; delete e->tier; e->tier = nullptr; }
     for (void* p : e->allocs) cudaFree(p);
-    cudaFree(e->history); cudaFree(e->prompt); cudaFree(e->scores);
+    cudaFree(e->history); cudaFree(e->prompt); cudaFree(e->scores); cudaFree(e->gdn_scratch);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
     delete e;
 }
@@ -1599,6 +1627,17 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
     if (ok && exact_attention_ok(e) && getenv("ITB_PREFILL_STEPWISE") == nullptr) {
         const size_t rows = e->B * std::min(std::max<size_t>(1, e->R / e->B), n);
         if (rows * e->m->d.n_head * e->n_ctx * 4 <= ((size_t)2 << 30)) ok = ensure_scores(e, rows);
+    }
+    // chunk-parallel delta rule: room for what its first kernel hands its second, for the largest pass of this call
+    if (ok && (c->gdn_chunk || !c->exact) && e->m->d.ssm_d_state == 128 && getenv("ITB_PREFILL_STEPWISE") == nullptr) {
+        const size_t nt = std::min(std::max<size_t>(1, e->R / e->B), n);
+        const size_t need = (size_t)e->B * ((nt + GC - 1) / GC) * e->m->d.ssm_dt_rank * gdn_chunk_floats<128>();
+        if (nt >= 32 && e->gdn_scratch_cap < need) {
+            cudaStreamSynchronize(st);
+            cudaFree(e->gdn_scratch); e->gdn_scratch = nullptr; e->gdn_scratch_cap = 0;
+            if (cudaMalloc(&e->gdn_scratch, need * 4) == cudaSuccess) e->gdn_scratch_cap = need;
+            else cudaGetLastError();             // without it the passes keep the serial-order scan
+        }
     }
     ok = ok && steps_ready(e, 0);   // a one-token pass replays the step graph: have it captured before anything is enqueued
     if (!ep_agree(e, ok)) return 1;

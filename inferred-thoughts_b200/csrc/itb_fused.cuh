@@ -92,9 +92,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
                 // one unit per block at most (the host checked): unit u goes to the last warp of block gridDim.x - 1 - u
                 const int units = (p.f[m].n_out + 31) / 32, u = gw - ubase;
                 if (u >= 0 && u < units) {
-                    if (u == 0 && m == 0 && lane == 0) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 6);
-                    f32_rows32_serial(p.f[m].wt + (size_t)u * 32 * n, n, u * 32, min(32, p.f[m].n_out - u * 32), xn, ring, ring_bars, p.err, [&](int row, float v) { o[row] = v; }, (u == 0 && m == 0) ? p.tl_slot : -1);
-                    if (u == 0 && m == 0 && lane == 0) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 7);
+                    f32_rows32_serial(p.f[m].wt + (size_t)u * 32 * n, n, u * 32, min(32, p.f[m].n_out - u * 32), xn, ring, ring_bars, p.err, [&](int row, float v) { o[row] = v; });
                 }
                 ubase += units;
             } else {
@@ -138,7 +136,6 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     }
     TL(TLK_IN_PROJ, 4);
     TL(TLK_IN_PROJ, 5);
-    if (blockIdx.x == gridDim.x - 1 && threadIdx.x == blockDim.x - 32) tl_mark_raw(p.tl_slot, TLK_IN_PROJ, 8);
 }
 // br a multiple of the pass size 2 * (32 >> gsh)
 size_t in_proj_smem(int n, int exact, int br, int f32_ring = 0) {

@@ -410,7 +410,7 @@ constexpr int F32S_K = 128, F32S_STAGES = 5, F32S_STAGE_FLOATS = 32 * F32S_K, F3
 constexpr int F32S_FAIL = 0x7001;
 template <class Epi>
 __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_unit, int n_in, int r0, int nr, const float* x, float* ring,
-                                                  unsigned long long* bars, int* err, Epi epi, int dbg_slot = -1) {
+                                                  unsigned long long* bars, int* err, Epi epi) {
     const int lane = threadIdx.x & 31, nst = n_in / F32S_K;
     auto issue = [&](int t) {
         if (t < nst && lane == 0) {
@@ -424,7 +424,6 @@ __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_u
     };
     for (int t = 0; t < F32S_STAGES; ++t) issue(t);
     float sum = 0.0f;
-    long long waited = 0; const long long t_begin = clock64();
 #pragma unroll 1
     for (int t = 0; t < nst; ++t) {
         const int slot = t % F32S_STAGES;
@@ -437,7 +436,6 @@ __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_u
                 if (ok) break;
                 if (clock64() - t0 > 2000000000ll) { if (err) atomicExch(err, F32S_FAIL); break; }
             }
-            waited += clock64() - t0;
         }
         const float* col = ring + slot * F32S_STAGE_FLOATS + lane;
         const float* xs = x + t * F32S_K;
@@ -465,9 +463,6 @@ __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_u
         issue(t + F32S_STAGES);
     }
     if (lane < nr) epi(r0 + lane, sum);
-    if (dbg_slot >= 0 && lane == 0 && g_tl_buf && (unsigned)dbg_slot < g_tl_cap) {
-        g_tl_buf[(size_t)dbg_slot * 16 + 9] = ((unsigned long long)waited << 8) | 2; g_tl_buf[(size_t)dbg_slot * 16 + 10] = ((unsigned long long)(clock64() - t_begin) << 8) | 2;
-    }
 }
 
 // Contiguous share [lo, hi) of n items for part `i` of `parts`.

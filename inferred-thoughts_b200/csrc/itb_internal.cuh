@@ -92,7 +92,12 @@ struct itb_ctx {
     void* tc_tiles = nullptr; int* tc_n_tiles = nullptr; int* tc_slot_tile = nullptr; uint8_t* tc_b_img = nullptr; uint8_t* tc_b_sf = nullptr; int* tc_status = nullptr;
     uint8_t* tc_codes = nullptr; uint8_t* tc_scales = nullptr;      // the pass's activation rows as FP4 records
     size_t tc_cap_tiles = 0, tc_cap_slots = 0, tc_cap_b = 0, tc_cap_sf = 0, tc_cap_codes = 0, tc_cap_scales = 0;
+    // Q8_0 tensor path: the pass's activation rows as K32 block images (kept for a following matmul over the same rows)
+    uint8_t* tc_q8_b = nullptr; float* tc_q8_sx = nullptr; size_t tc_cap_q8b = 0, tc_cap_q8sx = 0;
+    const void* tc_q8_src = nullptr; int tc_q8_src_rows = 0, tc_q8_src_in = 0;
+    bool q8tc = false;       // opts dense=q8tc: many-row passes run the dense Q8_0 matmuls as tcgen05 int8 MMAs (bit-identical results)
     bool fp4tc = false;      // opts experts=fp4tc: many-row passes multiply FP4 activations on the tensor cores
+    bool gdn_chunk = false;  // opts gdn=chunk: many-token passes run the delta rule chunk-parallel even under exact=1 (exact=0 always does)
     bool attn_mma = false;   // opts attn=mma: many-token passes run attention as 16-bit matrix products even under exact=1 (exact=0 always does)
 };
 // Routed experts over expert-grouped pairs on the FP4 tensor cores (itb_tc.cu). wu != null: out[pair] = silu(Wg x * s_g) * (Wu x * s_u);
@@ -100,6 +105,8 @@ struct itb_ctx {
 bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4* wu, const float* x, int rows_div, const int* pair_off,
                     const int* pair_list, int n_pairs, float* out);
 bool itb_tc_shape_ok(const DevFp4& w);
+bool itb_tc_q8_shape_ok(const DevQ8& w);
+bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
 void itb_tc_free(itb_ctx* c);
 
 bool itb_fail(itb_ctx* c, const char* what, cudaError_t e);
@@ -177,14 +184,6 @@ __device__ __forceinline__ void tl_mark(int slot, unsigned kernel, unsigned phas
 // The same from whichever thread of block 0 calls it (one caller per mark).
 __device__ __forceinline__ void tl_mark_any(int slot, unsigned kernel, unsigned phase) {
     if (slot >= 0 && blockIdx.x == 0 && g_tl_buf && (unsigned)slot < g_tl_cap) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;
-    }
-}
-// From any one thread of any block (the caller picks it).
-__device__ __forceinline__ void tl_mark_raw(int slot, unsigned kernel, unsigned phase) {
-    if (slot >= 0 && g_tl_buf && (unsigned)slot < g_tl_cap) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         g_tl_buf[(size_t)slot * 16 + phase] = (t << 8) | kernel;

@@ -2,6 +2,8 @@
 // (src/ops/mod.rs:489-1426), operating on host-address-keyed device mirrors.
 #include "itb_kernels.cuh"
 #include "itb_attn_exact.cuh"
+#include "itb_gdn_chunk.cuh"
+#include "itb_attn_mma.cuh"
 #include "itb_rows.cuh"
 
 static inline unsigned blocks_for(size_t n, int per = 256) { return (unsigned)((n + per - 1) / per); }
@@ -126,6 +128,20 @@ extern "C" void itb_ssm_conv(itb_ctx* c, float* state, size_t state_len, const f
     k_ssm_conv<<<blocks_for(nc, 128), 128, 0, c->stream>>>(sd, xd, x_len / nc, (int)nc, wd, (int)kernel, od);
     ITB_LAUNCHED(c);
 }
+// What the chunk kernels take per token besides k and v: q scaled by 1/sqrt(sk), the decay g and the write strength beta
+// (src/ops/naive.rs:101-107). One thread per q element; the first n_tok * n_v threads also do a (token, head)'s g and beta.
+__global__ void k_gdn_op_pre(const float* q, const float* alpha, const float* beta, const float* ssm_a, const float* dt_bias, size_t n_tok, int kper, int n_v,
+                             float q_scale, float* qs, float* gb) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_tok * kper) qs[i] = q[i] * q_scale;
+    if (i < n_tok * n_v) {
+        const int h = (int)(i % n_v);
+        const float a = alpha[i] + dt_bias[h];
+        const float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
+        gb[i * 2] = exp_f(sp * ssm_a[h]);
+        gb[i * 2 + 1] = sigmoid_f(beta[i]);
+    }
+}
 extern "C" void itb_delta_rule(itb_ctx* c, const itb_delta* d, float* state, size_t state_len, float* out, size_t out_len) {
     size_t kper = d->n_k_heads * d->head_k_dim, vper = d->n_v_heads * d->head_v_dim, nt = d->n_tokens;
     if (state_len != d->n_v_heads * d->head_k_dim * d->head_v_dim || out_len != nt * vper || d->n_k_heads == 0) {
@@ -140,6 +156,29 @@ extern "C" void itb_delta_rule(itb_ctx* c, const itb_delta* d, float* state, siz
     if (!sd || !q || !k || !v || !al || !be || !sa || !dt || !od) return;
     constexpr int ROWS = 32;
     int sk = (int)d->head_k_dim, sv = (int)d->head_v_dim;
+    if (c->gdn_chunk && nt >= 32 && sk == 128 && sv == 128) {
+        // gdn=chunk: the chunk-parallel form (tolerance class). Scaled q, decay and write strength per token first, then the two kernels.
+        const int n_k = (int)d->n_k_heads, n_v = (int)d->n_v_heads, n_ch = (int)((nt + GC - 1) / GC);
+        const size_t need = nt * kper + nt * n_v * 2 + (size_t)n_ch * n_v * gdn_chunk_floats<128>();
+        if (c->tmp_cap < need) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(c->tmp_f32); c->tmp_f32 = nullptr; c->tmp_cap = 0;
+            if (cudaMalloc(&c->tmp_f32, need * 4) != cudaSuccess) { cudaGetLastError(); itb_fail_msg(c, "delta_rule: out of device memory for the chunk scratch"); return; }
+            c->tmp_cap = need;
+        }
+        float* qs = c->tmp_f32; float* gbd = qs + nt * kper; float* scr = gbd + nt * n_v * 2;
+        k_gdn_op_pre<<<(unsigned)((nt * kper + 255) / 256), 256, 0, c->stream>>>(q, al, be, sa, dt, nt, n_k * sk, n_v, 1.0f / sqrtf((float)sk), qs, gbd);
+        static bool attr = false;
+        if (!attr) {
+            cudaFuncSetAttribute(k_gdn_chunk_prep<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gdn_chunk_prep_smem<128>());
+            cudaFuncSetAttribute(k_gdn_chunk_scan<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gdn_chunk_scan_smem<128>());
+            attr = true;
+        }
+        k_gdn_chunk_prep<128><<<dim3(n_ch, n_v, 1), 256, gdn_chunk_prep_smem<128>(), c->stream>>>(qs, k, v, gbd, (int)nt, n_k, n_v, scr);
+        k_gdn_chunk_scan<128><<<dim3(n_v, sk / GC_VS, 1), 256, gdn_chunk_scan_smem<128>(), c->stream>>>(scr, (int)nt, n_v, sd, (size_t)n_v * sk * sk, od);
+        ITB_LAUNCHED(c);
+        return;
+    }
     dim3 grid((unsigned)d->n_v_heads, (unsigned)((sv + ROWS - 1) / ROWS));
     size_t smem = (size_t)(ROWS * (sk + 1) + 2 * sk) * 4;
     k_delta_rule<ROWS><<<grid, 128, smem, c->stream>>>(q, k, v, al, be, sa, dt, nt, sk, sv, (int)d->n_k_heads, (int)d->n_v_heads, sd, od);
@@ -392,6 +431,12 @@ void itb_attend_dev(itb_ctx* c, cudaStream_t st, const float* q, const uint16_t*
     ITB_LAUNCHED(c);
 }
 
+// Row i of an n_q-row call sees first + i positions; the many-token kernel's one split divided out.
+__global__ void k_attn_mma_npos(int* npos, int n_q, int first) { const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n_q) npos[i] = first + i; }
+__global__ void k_attn_mma_finish(const float* acc, const float* ml, int hd, float* out) {
+    const size_t th = blockIdx.x;
+    out[th * hd + threadIdx.x] = acc[th * hd + threadIdx.x] / ml[th * 2 + 1];
+}
 extern "C" void itb_attend(itb_ctx* c, const itb_attn* a, float* out, size_t out_len) {
     size_t per = a->n_head * a->head_dim;
     if (per == 0 || a->q_len % per || a->n_head_kv == 0 || a->n_head % a->n_head_kv) { itb_fail_msg(c, "attend: bad shape"); return; }
@@ -401,6 +446,36 @@ extern "C" void itb_attend(itb_ctx* c, const itb_attn* a, float* out, size_t out
     uint16_t* kd = itb_kv_slab(c, a->k, a->slab_len); uint16_t* vd = itb_kv_slab(c, a->v, a->slab_len);
     float* od = itb_mirror_out(c, out, out_len);
     if (!qd || !kd || !vd || !od) return;
+    if (c->attn_mma && n_q >= 16 && AM_ROWS % (a->n_head / a->n_head_kv) == 0 && a->kv_dim % 8 == 0 &&
+        (a->head_dim == 64 || a->head_dim == 128 || a->head_dim == 256)) {
+        // attn=mma: the many-token kernel (tolerance class): per-row visible positions, one "split", then the division
+        const int group = (int)(a->n_head / a->n_head_kv), hd = (int)a->head_dim;
+        const size_t rows = n_q * a->n_head, need_f = rows * hd + rows * 2 + n_q;
+        if (c->tmp_cap < need_f) {
+            cudaStreamSynchronize(c->stream);
+            cudaFree(c->tmp_f32); c->tmp_f32 = nullptr; c->tmp_cap = 0;
+            if (cudaMalloc(&c->tmp_f32, need_f * 4) != cudaSuccess) { cudaGetLastError(); itb_fail_msg(c, "cudaMalloc(attention partials)"); return; }
+            c->tmp_cap = need_f;
+        }
+        float* pa = c->tmp_f32; float* pm = pa + rows * hd; int* npos = (int*)(pm + rows * 2);
+        k_attn_mma_npos<<<(unsigned)((n_q + 255) / 256), 256, 0, c->stream>>>(npos, (int)n_q, (int)(a->n_pos - n_q + 1));
+        AmParams ap{};
+        ap.q = qd; ap.kslab = kd; ap.vslab = vd; ap.slab_stride = 0; ap.npos = npos; ap.n_tok = (int)n_q; ap.kv_dim = (int)a->kv_dim;
+        ap.n_head = (int)a->n_head; ap.n_head_kv = (int)a->n_head_kv; ap.group = group; ap.scale = a->scale; ap.part_acc = pa; ap.part_ml = pm;
+        const dim3 ga((unsigned)((n_q + AM_ROWS / group - 1) / (AM_ROWS / group)), (unsigned)a->n_head_kv, 1);
+#define AM_CASE(HD)                                                                                                                        \
+    case HD:                                                                                                                                \
+        cudaFuncSetAttribute(k_attn_mma<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_mma_smem<HD>());                  \
+        cudaFuncSetAttribute(k_attn_mma<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_mma_smem<HD>());                 \
+        if (c->kv_bf16) k_attn_mma<HD, true><<<ga, 256, attn_mma_smem<HD>(), c->stream>>>(ap);                                              \
+        else k_attn_mma<HD, false><<<ga, 256, attn_mma_smem<HD>(), c->stream>>>(ap);                                                        \
+        break;
+        switch (hd) { AM_CASE(64) AM_CASE(128) AM_CASE(256) }
+#undef AM_CASE
+        k_attn_mma_finish<<<(unsigned)rows, hd, 0, c->stream>>>(pa, pm, hd, od);
+        ITB_LAUNCHED(c);
+        return;
+    }
     if (c->exact && a->kv_dim % 8 == 0 && a->n_head / a->n_head_kv <= 8 && (a->head_dim == 64 || a->head_dim == 128 || a->head_dim == 256) &&
         attn_out_exact_smem((int)a->n_pos) <= 200 * 1024) {
         // the CPU path's own order (src/ops/naive.rs:420-466): scores, then softmax and weighted values per 32 dimensions of a head

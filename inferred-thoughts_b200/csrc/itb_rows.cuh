@@ -110,6 +110,33 @@ __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __r
     }
 }
 
+// The same for few rows or few outputs, where 64 x 64 tiles would leave most SMs idle: a thread per (row, output), 16 x 16 of
+// them per block; every thread's k loop is the row's whole chain either way, so the small tile costs nothing but reuse.
+// grid (ceil(n_out / 16), ceil(n_rows / 16)), block 256.
+__global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
+    __shared__ float ws[2][SG_K][16 + 1], xs[2][SG_K][16 + 1];
+    const int o0 = blockIdx.x * 16, r0 = blockIdx.y * 16, n = w.n_in;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;            // output o0 + tx, row r0 + ty
+    // loader: thread -> (line 0..15 of either tile, 4 consecutive k): threads 0..127 the weights, 128..255 the rows
+    const int half = threadIdx.x >> 7, ll = (threadIdx.x & 127) >> 3, lk = (threadIdx.x & 7) * 4;
+    const float* src = half ? x + (size_t)min(r0 + ll, n_rows - 1) * n + lk : w.w + (size_t)min(o0 + ll, w.n_out - 1) * n + lk;
+    float (*dst)[SG_K][17] = half ? xs : ws;
+    float4 v = __ldg((const float4*)src);
+    dst[0][lk][ll] = v.x; dst[0][lk + 1][ll] = v.y; dst[0][lk + 2][ll] = v.z; dst[0][lk + 3][ll] = v.w;
+    __syncthreads();
+    float acc = 0.0f;
+    const int nk = n / SG_K;
+    for (int t = 0; t < nk; ++t) {
+        const int buf = t & 1;
+        if (t + 1 < nk) v = __ldg((const float4*)(src + (size_t)(t + 1) * SG_K));
+#pragma unroll
+        for (int kk = 0; kk < SG_K; ++kk) acc = __fadd_rn(acc, __fmul_rn(ws[buf][kk][tx], xs[buf][kk][ty]));
+        if (t + 1 < nk) { dst[buf ^ 1][lk][ll] = v.x; dst[buf ^ 1][lk + 1][ll] = v.y; dst[buf ^ 1][lk + 2][ll] = v.z; dst[buf ^ 1][lk + 3][ll] = v.w; }
+        __syncthreads();
+    }
+    if (r0 + ty < n_rows && o0 + tx < w.n_out) out[(size_t)(r0 + ty) * w.n_out + o0 + tx] = acc;
+}
+
 // RMSNorm + Q8_0 quantisation of each row (src/ops/naive.rs:139-152, :653-675): normalised f32 row, int8 quants,
 // scales. grid = rows, block 256.
 __global__ void __launch_bounds__(256) k_norm_quant(const float* x, const float* w, int n, float eps, float* xn_out, int8_t* xq, float* xs) {

@@ -479,7 +479,8 @@ bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n
 void itb_tc_free(itb_ctx* c) {
     for (auto& kv : c->tc_weights) { cudaFree(kv.second.img); cudaFree(kv.second.sf); }
     c->tc_weights.clear();
-    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales);
+    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales); cudaFree(c->tc_q8_b); cudaFree(c->tc_q8_sx);
+    c->tc_q8_b = nullptr; c->tc_q8_sx = nullptr; c->tc_cap_q8b = c->tc_cap_q8sx = 0; c->tc_q8_src = nullptr;
     c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr; c->tc_codes = nullptr; c->tc_scales = nullptr; c->tc_cap_codes = c->tc_cap_scales = 0;
     c->tc_cap_tiles = c->tc_cap_slots = c->tc_cap_b = c->tc_cap_sf = 0;
 }
@@ -592,4 +593,255 @@ extern "C" int itb_fp4_quantize(itb_ctx* c, const float* x, size_t n, uint8_t* s
     cudaFree(dx); cudaFree(ds); cudaFree(dc);
     if (e != cudaSuccess) { itb_fail(c, "fp4_quantize", e); return 1; }
     return 0;
+}
+
+// =====================================================================================================
+// Dense Q8_0 matmuls of many-row passes on the tensor cores, bit for bit
+// =====================================================================================================
+// The CPU path's Q8_0 dot (src/ops/naive.rs:676-712) is, per 32-element block, an integer dot product, converted to f32,
+// times (weight scale * activation scale), added to the row's sum in block order. The integer dot of 128 weight rows against
+// 128 activation rows is ONE tcgen05.mma kind::i8 (M 128, N 128, K 32, s32 accumulators in tensor memory, not accumulating);
+// four accumulator buffers rotate through the 512 columns, so the tensor core runs blocks ahead while eight warps read a
+// finished block back (tcgen05.ld) and apply the two scales and the addition in the CPU's own order and rounding. The result
+// equals the CPU path to the bit; what bounds the kernel is those four f32 instructions per (output, block) on the CUDA
+// cores -- the same count the mma.sync kernels pay, without their shared-memory operand traffic.
+// Operand images ("K32 block": 128 rows x 32 int8 = 4096 B as [2 chunks of 16 B][16][8 rows][16 B], K-major, no swizzle;
+// descriptor leading offset 2048, stride offset 128) are made once per weight matrix and once per pass for the activations.
+namespace {
+
+constexpr int Q8_KB = 4;           // K32 blocks per pipeline stage
+constexpr int Q8_STAGES = 5;
+constexpr int Q8_STAGE_BYTES = 2 * Q8_KB * 4096 + 2 * Q8_KB * 128 * 4;     // A | B | weight scales | activation scales
+
+// kind::i8: s32 accumulators (2 at bit 4), signed 8-bit operands (1 at bits 7 and 10), both K-major, M x N
+__host__ __device__ constexpr uint32_t tc_idesc_i8(int m, int n) { return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
+
+// int8 rows -> K32 block images, scales -> f32 per (row tile, block, row). One thread per (row, block); rows past n_rows are zeros.
+// scales16 (f16, per weight row and block) or scales32 (f32, per activation row and block): whichever is not null.
+__global__ void k_q8_tile(const int8_t* q, const uint16_t* scales16, const float* scales32, int n_rows, int n_in, uint8_t* img, float* sc_out) {
+    const int kbs = n_in / 32;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x, total = (size_t)((n_rows + 127) / 128) * 128 * kbs;
+    if (idx >= total) return;
+    const int kb = (int)(idx % kbs); const size_t row = idx / kbs;
+    const int rt = (int)(row / 128), r = (int)(row % 128);
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    float sc = 0.0f;
+    if (row < (size_t)n_rows) {
+        const uint4* src = (const uint4*)(q + row * n_in + (size_t)kb * 32);
+        lo = src[0]; hi = src[1];
+        sc = scales16 ? f16_bits_to_f32(scales16[row * kbs + kb]) : scales32[row * kbs + kb];
+    }
+    uint8_t* blk = img + ((size_t)rt * kbs + kb) * 4096;
+    *(uint4*)(blk + (r >> 3) * 128 + (r & 7) * 16) = lo;
+    *(uint4*)(blk + 2048 + (r >> 3) * 128 + (r & 7) * 16) = hi;
+    sc_out[((size_t)rt * kbs + kb) * 128 + r] = sc;
+}
+
+struct TcQ8 {
+    const uint8_t* a_img; const float* a_sc;      // weights: [row tile][block][4096 B], [row tile][block][128]
+    const uint8_t* b_img; const float* b_sc;      // activations of the pass, the same form over token tiles
+    int kbs, n_rows, n_out;
+    float* out; size_t stride; int mode;          // out[token][row]; mode 1: += (the residual add of an output projection)
+    int* status;
+    long long* prof;                              // optional: 8 cycle counts per block (ITB_TC_PROF=1)
+};
+// grid (n_out / 128, token tiles); block 320: warps 0-7 read accumulators back and scale (lane quarter = warp % 4, column half =
+// warp / 4), warp 8 fetches operands, warp 9 issues the MMAs.
+__global__ void __launch_bounds__(320, 1) k_tc_q8(TcQ8 p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ unsigned long long s_full[Q8_STAGES], s_empty[Q8_STAGES], s_dfull[4], s_dfree[4];
+    __shared__ uint32_t s_tmem;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int rt = blockIdx.x, tt = blockIdx.y, kbs = p.kbs, n_stage = kbs / Q8_KB;
+    const uint32_t sbase = tc_smem(smem);
+    if (tid == 0) {
+        for (int s = 0; s < Q8_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 9;" ::"r"(tc_smem(&s_empty[s])) : "memory");      // the MMAs' commit + 8 warps done with the scales
+        }
+        for (int i = 0; i < 4; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_dfull[i])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(tc_smem(&s_dfree[i])) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (wid == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tm = s_tmem;
+    constexpr uint32_t O_B = Q8_KB * 4096, O_SA = 2 * Q8_KB * 4096, O_SB = O_SA + Q8_KB * 128 * 4;
+    bool ok = true;
+    if (wid == 8 && lane == 0) {
+        const size_t a0 = (size_t)rt * kbs, b0 = (size_t)tt * kbs;
+        for (int st = 0; st < n_stage && ok; ++st) {
+            const int s = st % Q8_STAGES;
+            if (st >= Q8_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((st / Q8_STAGES) - 1) & 1, 2000000000ull);
+            if (!ok) break;
+            const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * Q8_STAGE_BYTES;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"((uint32_t)Q8_STAGE_BYTES) : "memory");
+            const size_t kb0 = (size_t)st * Q8_KB;
+            tc_bulk(dst, p.a_img + (a0 + kb0) * 4096, Q8_KB * 4096, full);
+            tc_bulk(dst + O_B, p.b_img + (b0 + kb0) * 4096, Q8_KB * 4096, full);
+            tc_bulk(dst + O_SA, p.a_sc + (a0 + kb0) * 128, Q8_KB * 128 * 4, full);
+            tc_bulk(dst + O_SB, p.b_sc + (b0 + kb0) * 128, Q8_KB * 128 * 4, full);
+        }
+        if (!ok) atomicCAS(p.status, 0, 3);
+    } else if (wid == 9 && lane == 0) {
+        const uint32_t idesc = tc_idesc_i8(128, 128);
+        const uint64_t dA = tc_desc(sbase, 2048, 128), dB = tc_desc(sbase + O_B, 2048, 128);
+        for (int b = 0; b < kbs && ok; ++b) {
+            const int s = (b / Q8_KB) % Q8_STAGES, k = b % Q8_KB, db = b & 3;
+            if (k == 0) {
+                ok = tc_mbar_wait(tc_smem(&s_full[s]), ((b / Q8_KB) / Q8_STAGES) & 1, 2000000000ull);
+                if (!ok) break;
+            }
+            if (b >= 4) {
+                ok = tc_mbar_wait(tc_smem(&s_dfree[db]), ((b >> 2) - 1) & 1, 2000000000ull);
+                if (!ok) break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t so = (uint32_t)s * (Q8_STAGE_BYTES >> 4) + 256u * k;
+            asm volatile(
+                "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+                "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p; }\n"
+                ::"r"(tm + 128u * db), "l"(dA + so), "l"(dB + so), "r"(idesc), "r"(0u) : "memory");
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_dfull[db])) : "memory");
+            if (k == Q8_KB - 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
+        }
+        if (!ok) atomicCAS(p.status, 0, 4);
+    } else if (wid < 8) {
+        const int quarter = wid & 3, half = wid >> 2, row = quarter * 32 + lane;
+        float acc[64];
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc[j] = 0.0f;
+        uint32_t d0[32], d1[32];
+        // start reading 32 of this warp's 64 columns of block b's accumulators (asynchronous: tcgen05.wait::ld ends it); the first
+        // half of a block also waits for the block's MMA (and, at a stage's first block, for the stage's scales)
+        auto fetch = [&](int b, int h, uint32_t (&d)[32]) {
+            const int s = (b / Q8_KB) % Q8_STAGES, k = b % Q8_KB, db = b & 3;
+            if (h == 0) {
+                if (k == 0) ok = ok && __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_full[s]), ((b / Q8_KB) / Q8_STAGES) & 1, 2000000000ull));
+                ok = ok && __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_dfull[db]), (b >> 2) & 1, 2000000000ull));
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            if (!ok) return;
+            const uint32_t ta = tm + 128u * db + 64u * half + 32u * h + ((uint32_t)(quarter * 32) << 16);
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                         : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]),
+                           "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]),
+                           "=r"(d[23]), "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31]) : "r"(ta) : "memory");
+        };
+        // scale and add 32 columns of block b in the CPU's order: sum += (float)dot * (dw * dx). The conversion is exact either way
+        // (|dot| <= 32 * 127 * 127 < 2^23); through the magic constant 1.5 * 2^23 it is an integer add and a float add instead of
+        // a quarter-rate convert.
+        auto scale_add = [&](int b, int h, const uint32_t (&d)[32]) {
+            const int s = (b / Q8_KB) % Q8_STAGES, k = b % Q8_KB;
+            const float* sa = (const float*)(smem + (size_t)s * Q8_STAGE_BYTES + O_SA) + k * 128;
+            const float* sb = (const float*)(smem + (size_t)s * Q8_STAGE_BYTES + O_SB) + k * 128 + 64 * half + 32 * h;
+            const float dw = sa[row];
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+                const float4 dx = *(const float4*)(sb + j);
+                const float dxs[4] = {dx.x, dx.y, dx.z, dx.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float f = __fadd_rn(__uint_as_float(0x4b400000u + d[j + i]), -12582912.0f);
+                    acc[32 * h + j + i] = __fadd_rn(acc[32 * h + j + i], __fmul_rn(f, __fmul_rn(dw, dxs[i])));
+                }
+            }
+        };
+        long long* pf = p.prof ? p.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
+        long long t_wait = 0, t_fetch = 0; const long long t_begin = clock64();
+        fetch(0, 0, d0); fetch(0, 1, d1);
+#pragma unroll 1
+        for (int b = 0; b < kbs && ok; ++b) {
+            const long long tw0 = clock64();
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");      // both halves of block b are in registers
+            t_wait += clock64() - tw0;
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_dfree[b & 3])) : "memory");
+            scale_add(b, 0, d0);
+            const long long tf0 = clock64();
+            if (b + 1 < kbs) fetch(b + 1, 0, d0);                             // lands while the second half is being added
+            t_fetch += clock64() - tf0;
+            scale_add(b, 1, d1);
+            if (b + 1 < kbs) fetch(b + 1, 1, d1);
+            if (b % Q8_KB == Q8_KB - 1) {
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_empty[(b / Q8_KB) % Q8_STAGES])) : "memory");
+            }
+        }
+        if (pf && tid == 0) { pf[0] = clock64() - t_begin; pf[1] = t_wait; pf[2] = t_fetch; pf[3] = kbs; }
+        if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
+            const size_t orow = (size_t)rt * 128 + row;
+#pragma unroll
+            for (int j = 0; j < 64; ++j) {
+                const int tok = tt * 128 + 64 * half + j;
+                if (tok < p.n_rows) { float* o = p.out + (size_t)tok * p.stride + orow; *o = p.mode ? __fadd_rn(*o, acc[j]) : acc[j]; }
+            }
+        } else if (!ok) atomicCAS(p.status, 0, 5);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+}
+constexpr size_t tc_q8_smem() { return (size_t)Q8_STAGES * Q8_STAGE_BYTES + 128; }
+
+}  // namespace
+
+bool itb_tc_q8_shape_ok(const DevQ8& w) { return w.n_in % (32 * Q8_KB) == 0 && w.n_out % 128 == 0 && w.q && w.s; }
+// out[token][row] (+)= W x for n_rows quantised activation rows (xq int8 [n_rows][n_in], xs f32 [n_rows][n_in / 32]). False: not run.
+bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts) {
+    if (!itb_tc_q8_shape_ok(w) || n_rows <= 0) return false;
+    const size_t kbs = w.n_in / 32, rts = w.n_out / 128, tts = ((size_t)n_rows + 127) / 128;
+    auto it = c->tc_weights.find(w.q);
+    if (it == c->tc_weights.end()) {
+        itb_ctx::TcWeights t;
+        if (cudaMalloc(&t.img, rts * kbs * 4096) != cudaSuccess) { cudaGetLastError(); return itb_fail_msg(c, "Q8_0 tensor path: out of device memory for the tiled weights"); }
+        if (cudaMalloc(&t.sf, rts * kbs * 128 * 4) != cudaSuccess) { cudaFree(t.img); cudaGetLastError(); return itb_fail_msg(c, "Q8_0 tensor path: out of device memory for the tiled weights"); }
+        t.bytes = rts * kbs * (4096 + 512);
+        const size_t n = rts * 128 * kbs;
+        k_q8_tile<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.q, w.s, nullptr, w.n_out, w.n_in, t.img, (float*)t.sf);
+        c->launches++;
+        it = c->tc_weights.emplace(w.q, t).first;
+    }
+    size_t cap1 = c->tc_status ? 1 : 0;
+    bool ok = tc_grow(&c->tc_status, &cap1, 1, st) && tc_grow(&c->tc_q8_b, &c->tc_cap_q8b, tts * kbs * 4096, st) && tc_grow(&c->tc_q8_sx, &c->tc_cap_q8sx, tts * kbs * 128, st);
+    if (!ok) return itb_fail_msg(c, "Q8_0 tensor path: out of device memory for the pass");
+    // same_acts: the caller vouches that xq/xs hold what the previous call's did (consecutive matmuls over one quantised row set)
+    if (!same_acts || c->tc_q8_src != xq || c->tc_q8_src_rows != n_rows || c->tc_q8_src_in != w.n_in) {
+        const size_t n = tts * 128 * kbs;
+        k_q8_tile<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xq, nullptr, xs, n_rows, w.n_in, c->tc_q8_b, c->tc_q8_sx);
+        c->launches++;
+        c->tc_q8_src = xq; c->tc_q8_src_rows = n_rows; c->tc_q8_src_in = w.n_in;
+    }
+    cudaMemsetAsync(c->tc_status, 0, 4, st);
+    TcQ8 g{};
+    g.a_img = it->second.img; g.a_sc = (const float*)it->second.sf; g.b_img = c->tc_q8_b; g.b_sc = c->tc_q8_sx; g.kbs = (int)kbs; g.n_rows = n_rows; g.n_out = w.n_out;
+    g.out = out; g.stride = stride; g.mode = mode; g.status = c->tc_status;
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(k_tc_q8, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_q8_smem()); attr = true; }
+    static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
+    const size_t n_blocks = rts * tts;
+    if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
+    k_tc_q8<<<dim3((unsigned)rts, (unsigned)tts), 320, tc_q8_smem(), st>>>(g);
+    c->launches++;
+    if (prof_on && g.prof) {
+        std::vector<long long> h(n_blocks * 8);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), g.prof, n_blocks * 64, cudaMemcpyDeviceToHost);
+        cudaFree(g.prof);
+        double a[3] = {0, 0, 0}; size_t n = 0;
+        for (size_t b = 0; b < n_blocks; ++b) if (h[b * 8]) { a[0] += (double)h[b * 8]; a[1] += (double)h[b * 8 + 1]; a[2] += (double)h[b * 8 + 2]; ++n; }
+        if (n) fprintf(stderr, "tc_q8 %d x %d, %zu K32 blocks, %zu blocks: cycles per K32 block %.0f (waiting for the accumulator loads %.0f, for the next block's MMA %.0f)\n",
+                       w.n_out, n_rows, kbs, n, a[0] / n / kbs, a[1] / n / kbs, a[2] / n / kbs);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return itb_fail(c, "Q8_0 tensor path: launch", e);
+    return true;
 }

@@ -350,8 +350,10 @@ def test_odd_shape_matches_oracle_through_every_path():
 
 
 def test_benchmark_mode_bf16_kv_and_tree_dots_stays_within_tolerance(oracle):
-    """The benchmark runs kv=bf16 (BASELINE config 3) and exact=0; the oracle keeps the reference's f16 cache and serial dots.
-    The difference must stay inside the logits tolerance, and the engine must still agree with itself (multi-row == stepwise)."""
+    """kv=bf16 (BASELINE config 3) with exact=0 (tree-summed F32 dots; many-token passes on the tensor-core attention kernel)
+    against the oracle with the reference's f16 cache and serial dots: the difference must stay inside the logits tolerance,
+    for the multi-row pass and for the same prompt token by token (the two no longer share their attention kernel, so they
+    agree with each other to the same tolerance, not to the bit; exact=1 keeps them bit-identical, see the tests above)."""
     import os
     from inferred_thoughts_b200 import host
     ops = host.B200Ops(0, "kv=bf16,exact=0")
@@ -366,10 +368,11 @@ def test_benchmark_mode_bf16_kv_and_tree_dots_stays_within_tolerance(oracle):
         b = e2.prefill(prompt)
     finally:
         del os.environ["ITB_PREFILL_STEPWISE"]
-    assert a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
-    err, cos = float(np.abs(want - a).max()), cosine(want, a)
-    print(f"bf16 kv, tree dots vs oracle: max-abs {err:.3e}, cosine {cos:.7f}")
-    assert err <= 2e-2 and cos >= 0.999
+    for what, g in (("multi-row pass", a), ("token by token", b)):
+        err, cos = float(np.abs(want - g).max()), cosine(want, g)
+        print(f"bf16 kv, tree dots, {what} vs oracle: max-abs {err:.3e}, cosine {cos:.7f}")
+        assert err <= 2e-2 and cos >= 0.999
+    assert float(np.abs(a - b).max()) <= 2e-2
     ops.check()
     e1.close(); e2.close(); model.close(); ops.close()
 

@@ -480,3 +480,62 @@ def test_routed_experts_on_the_fp4_tensor_cores(H, ff, E, K, n_tok, zipf):
     assert eh <= 4 * FP4TC_TOL, eh          # through silu(gate) * up: both factors carry the order error
     assert eo <= FP4TC_TOL, eo
     tc.check(); tc.close()
+
+
+@pytest.mark.parametrize("nk,nv,nt,corr", [(2, 4, 64, 0.0), (2, 4, 150, 0.0), (16, 32, 200, 0.0), (2, 4, 150, 0.8), (2, 2, 33, 0.8)])
+def test_chunk_parallel_delta_rule_against_the_serial_order(nk, nv, nt, corr):
+    """gdn=chunk: the delta rule as chunk-parallel matrix products against the CPU path's token-by-token recurrence, outputs and
+    the state left behind. Same f32 arithmetic, another association: held to 2e-4 of the largest magnitude (the recurrence
+    compounds rounding over the tokens of a call). Cases: one full chunk, ragged last chunks, the benchmark's head counts, and
+    keys that are strongly correlated inside a chunk (corr: the weight of a shared direction; the model's keys pass through
+    SiLU and are mostly positive), normalised like the model's."""
+    from inferred_thoughts_b200 import host
+    sk = 128
+    ops = host.B200Ops(0, "gdn=chunk")
+    rng = np.random.default_rng(900 + nt)
+
+    def unit(x):
+        x = x.reshape(-1, sk)
+        return np.ascontiguousarray(x / np.maximum(np.linalg.norm(x, axis=1, keepdims=True), 1e-6), np.float32).reshape(-1)
+    shared = rng.standard_normal(sk).astype(np.float32)
+    q = unit(noise(nt * nk * sk, 310, 1.0).reshape(-1, sk) + 3 * corr * shared)
+    k = unit(noise(nt * nk * sk, 311, 1.0).reshape(-1, sk) + 3 * corr * shared)
+    v = noise(nt * nv * sk, 312)
+    al = noise(nt * nv, 313); be = noise(nt * nv, 314); sa = -np.abs(noise(nv, 315)); dt = noise(nv, 316, 0.02)
+    st = keep(noise(nv * sk * sk, 317, 0.1)); st2 = st.copy()
+    out = np.zeros(nt * nv * sk, np.float32); want = np.zeros_like(out)
+    ops.begin_pass(nt)
+    ops.delta_rule(q, k, v, al, be, sa, dt, sk, sk, nk, nv, st, out); ops.host_needs(out); ops.read_state(st); ops.check()
+    L.orc_delta_rule(q, k, v, al, be, sa, dt, nt, sk, sk, nk, nv, st2, want)
+    eo = float(np.abs(out - want).max()) / max(1.0, float(np.abs(want).max()))
+    es = float(np.abs(st - st2).max()) / max(1.0, float(np.abs(st2).max()))
+    print(f"chunked delta rule nk={nk} nv={nv} nt={nt} corr={corr}: output err {eo:.2e}, state err {es:.2e}")
+    assert eo <= 2e-4 and es <= 2e-4
+    ops.forget_state(); ops.close()
+
+
+@pytest.mark.parametrize("hd,nh,nkv,n_pos,n_q,kv", [(256, 16, 2, 700, 150, "f16"), (256, 16, 2, 700, 150, "bf16"), (64, 4, 1, 200, 200, "f16"),
+                                                    (128, 8, 2, 333, 77, "f16"), (256, 32, 4, 130, 16, "bf16")])
+def test_tensor_core_attention_against_the_cpu_order(hd, nh, nkv, n_pos, n_q, kv):
+    """attn=mma at op level: n_q consecutive query rows deep in a cache of n_pos positions (row i sees n_pos - n_q + 1 + i of
+    them) through the many-token kernel, against the CPU path. q and the softmax weights are rounded to the cache's 16-bit
+    type (2^-11 relative for f16, 2^-8 for bf16) before their matrix products, so the bound is that rounding times the
+    largest value, with head room for the sums' association; ragged last tiles in tokens and positions, 4 and 8 heads per
+    KV head, every head_dim."""
+    from inferred_thoughts_b200 import host
+    bf = kv == "bf16"
+    ops = host.B200Ops(0, "attn=mma" + (",kv=bf16" if bf else ""))
+    kvd = hd * nkv; n_ctx = n_pos + 8
+    q = noise(n_q * nh * hd, 440)
+    kf = noise(n_ctx * kvd, 441); vf = noise(n_ctx * kvd, 442)
+    ks = keep(np.zeros(n_ctx * kvd, np.uint16)); vs = keep(np.zeros_like(ks))
+    L.orc_kv_write(ks, 0, kf, kf.size, int(bf)); L.orc_kv_write(vs, 0, vf, vf.size, int(bf))
+    out = np.zeros(n_q * nh * hd, np.float32); want = np.zeros_like(out)
+    scale = 1.0 / np.sqrt(hd)
+    ops.begin_pass(n_q)
+    ops.attend(q, ks, vs, kvd, n_pos, hd, nh, nkv, scale, out); ops.host_needs(out); ops.check()
+    L.orc_attend(q, q.size, ks, vs, kvd, n_pos, hd, nh, nkv, scale, int(bf), want)
+    err = float(np.abs(out - want).max()); tol = (2.0 ** -8 if bf else 2.0 ** -11) * 4 * float(np.abs(vf).max())
+    print(f"attn=mma hd={hd} heads {nh}/{nkv} n_pos={n_pos} n_q={n_q} kv={kv}: max err {err:.2e} (bound {tol:.2e})")
+    assert err <= tol
+    ops.close()
