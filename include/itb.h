@@ -106,6 +106,9 @@ void itb_moe_glu(itb_ctx*, const itb_experts* gate, const itb_experts* up, const
                  size_t x_len, float* out, size_t out_len, float* scratch);                                       /* :1105 */
 void itb_moe_finish(itb_ctx*, float* out, size_t out_len, size_t at, size_t n, const float* rows, size_t rows_len,
                     const itb_route_t*, const float* shared, const float* logit, size_t logit_at);                  /* :1134 */
+/* "A hint, not work" (src/ops/mod.rs:915-924): at this seam every expert stack a context has seen is wholly resident in HBM, so
+ * there is nothing to fetch ahead and the call returns at once, as the trait's default does. The tiered engine applies the hint
+ * itself (itb_tier_counters below). */
 void itb_prefetch_hint(itb_ctx*, const itb_weights* next_router, const float* x, size_t x_len, size_t k);         /* :924 */
 /* Brings the current device route home: n_tok*n_used ids and weights (tests; breaks graph capture). */
 void itb_read_route(itb_ctx*, int32_t* ids, float* weights, size_t n);
@@ -163,6 +166,18 @@ int  itb_engine_create(itb_model*, uint32_t n_ctx, uint32_t n_seq, itb_engine** 
 int  itb_model_offload_experts(itb_model*);
 int  itb_engine_create_tiered(itb_model*, uint32_t n_ctx, uint32_t n_seq, uint32_t capacity, itb_engine** out);
 void itb_engine_tier_stats(itb_engine*, uint64_t* out4);
+/* The reference's TierCounters (src/ops/mod.rs:360-401) for one engine, as far as they exist here: fetched / fetch_bytes: experts
+ * copied from the host tier into an HBM slot; picks_wait_us: host time waiting for a layer's routing ids; prefetch_reads /
+ * prefetch_used: experts brought in by the prefetch hint and how many of those a later pick hit (the hint of src/ops/mod.rs:915-924
+ * is applied inside the tiered engine when ITB_TIER_PREFETCH=<guesses per row> is set at its creation: layer il + 1's router on
+ * layer il's router input, copies on a second stream while layer il's experts run; it changes no value the model computes);
+ * lookups / host_reads: expert picks and how many missed the pool; slots, slot_bytes, pool_bytes; vram_free / vram_total from the
+ * driver; mirrors / mirror_bytes: activation copies of the op seam; weight_bytes, kv_bytes, resident_bytes. The reference's
+ * file-tier fields (read_us, upload_us, writes_us, picks_copy_us, oversubscribed) have no counterpart: the lower tier is pinned
+ * host memory. */
+typedef struct { uint64_t fetched, fetch_bytes, picks_wait_us, prefetch_reads, prefetch_used, lookups, host_reads, slot_bytes, slots, pool_bytes,
+                 vram_free, vram_total, mirrors, mirror_bytes, weight_bytes, kv_bytes, resident_bytes; } itb_tier_counters_t;
+int  itb_tier_counters(itb_engine*, itb_tier_counters_t* out);
 void* itb_gclock_create(uint32_t capacity, uint32_t n_keys);
 void itb_gclock_destroy(void*);
 void itb_gclock_next_pass(void*);
@@ -244,6 +259,12 @@ int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t*
  * tflops_out: dense TFLOP/s, best of `reps` launches by CUDA events; status_out: 0 verified, 1 a (bounded) wait ran out,
  * 2 accumulators wrong; mma_cycles_out: SM cycles per MMA on the slowest block. Returns non-zero on a call error. */
 int  itb_fp4_ceiling(itb_ctx*, int n, int iters, int reps, double* tflops_out, int* status_out, double* mma_cycles_out);
+/* Expert parallelism, many-row passes: the send/receive plan of the packed all-to-all that carries every (row, pick) pair to
+ * the rank holding its expert and its output row back (the reference places experts by contiguous range, src/ops/mod.rs:1024-1048;
+ * it has no multi-GPU path of its own). cnt[s * world + d] = pairs rank s sends to rank d (every rank has the whole matrix
+ * after one small all-gather). Fills send_off[world + 1] (offsets into this rank's pairs sorted by owner rank) and
+ * recv_off[world + 1] (offsets into its receive buffer, source-rank order) and *n_recv. Host arithmetic only; 0 ok. */
+int  itb_ep_a2a_plan(const int* cnt, int world, int rank, int* send_off, int* recv_off, int* n_recv);
 /* The FP4 activation quantiser of the tensor-core expert path on its own (opts "experts=fp4tc" selects that path for
  * itb_matmul_experts / itb_moe_glu and for the engine's many-row passes): x[n], n a multiple of 16 -> one UE4M3 scale code per
  * 16 elements and one E2M1 code (0..15) per element, the CPU statement's record (Fp4Row::from_f32, src/ops/naive.rs:755-788),

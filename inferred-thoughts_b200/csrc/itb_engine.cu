@@ -6,6 +6,7 @@
 // (src/engine/mod.rs:352-437). The arithmetic of every matmul, norm, conv, delta-rule and routing
 // step keeps the CPU path's order; only exp() and the attention reduction are tolerance class.
 #include <algorithm>
+#include <chrono>
 #include <array>
 #include <memory>
 
@@ -379,6 +380,8 @@ struct NcclApi {
     int (*CommAbort)(void*) = nullptr;
     int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*Send)(const void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*Recv)(void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*GroupStart)() = nullptr;
     int (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
@@ -395,7 +398,7 @@ static NcclApi& nccl_api() {
     if (!h) return api;
 #define NCCL_SYM(f) *(void**)&api.f = dlsym(h, "nccl" #f)
     NCCL_SYM(GetUniqueId); NCCL_SYM(CommInitRank); NCCL_SYM(CommDestroy); NCCL_SYM(AllGather); NCCL_SYM(ReduceScatter);
-    NCCL_SYM(GroupStart); NCCL_SYM(GroupEnd); NCCL_SYM(GetErrorString); NCCL_SYM(CommAbort);
+    NCCL_SYM(GroupStart); NCCL_SYM(GroupEnd); NCCL_SYM(GetErrorString); NCCL_SYM(CommAbort); NCCL_SYM(Send); NCCL_SYM(Recv);
 #undef NCCL_SYM
     api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllGather && api.ReduceScatter && api.GroupStart && api.GroupEnd;
     return api;
@@ -409,7 +412,53 @@ struct EpState {
     float* grouter = nullptr;                                               // gathered router logits [world][n_expert] (fused one-token step)
     int* agree_dev = nullptr; int* agree_host = nullptr;                    // one "this rank is ready" flag per rank (ep_agree)
     bool broken = false;                                                    // the communicator was aborted after a failure mid-pass
+    // packed all-to-all dispatch/combine of eager many-row passes: this rank's pairs sorted by owner rank (send side), the
+    // pairs it received (every one names a local expert), the per-rank counts of all ranks
+    int8_t* sxq = nullptr; float* sxs = nullptr; int32_t* sids = nullptr;   // [R*K] rows in owner order
+    int8_t* rxq = nullptr; float* rxs = nullptr; int32_t* rids = nullptr;   // received pairs (capacity a2a_cap)
+    float* o_back = nullptr;                                                // this rank's pairs' outputs, in owner order
+    int32_t* owner = nullptr; int* own_off = nullptr; int* own_list = nullptr;
+    int* cnt_dev = nullptr; int* cnt_host = nullptr;                        // [W][W]: cnt[s][d] = pairs rank s sends to rank d
+    size_t a2a_cap = 0;
 };
+
+// ---- packed all-to-all dispatch/combine (expert parallel, eager many-row passes) ----
+// The send/receive plan of one rank from the count matrix cnt[s][d] (pairs rank s sends to rank d): offsets into its send
+// buffer (owner order) and into its receive buffer (source-rank order), and the total it receives. Plain host arithmetic,
+// exported for the CPU tests.
+extern "C" int itb_ep_a2a_plan(const int* cnt, int world, int rank, int* send_off, int* recv_off, int* n_recv) {
+    if (world < 1 || rank < 0 || rank >= world) return 1;
+    int so = 0, ro = 0;
+    for (int r = 0; r < world; ++r) {
+        if (cnt[rank * world + r] < 0 || cnt[r * world + rank] < 0) return 1;
+        send_off[r] = so; so += cnt[rank * world + r];
+        recv_off[r] = ro; ro += cnt[r * world + rank];
+    }
+    send_off[world] = so; recv_off[world] = ro;
+    *n_recv = ro;
+    return 0;
+}
+__global__ void k_ep_owner(const int32_t* ids, int n, int per_rank, int32_t* owner) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) owner[i] = ids[i] / per_rank;
+}
+// Slot s of the owner-sorted order holds pair list[s] of row list[s] / n_used: its quantised row, scales and expert id.
+__global__ void k_ep_pack(const int8_t* xq, const float* xs, const int32_t* ids, const int* list, int n_pairs, int n_used, int H,
+                          int8_t* sxq, float* sxs, int32_t* sids) {
+    const int cpr = H / 16, spr = H / 32;                 // 16-byte chunks and scales per row
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_pairs * cpr) return;
+    const int slot = (int)(i / cpr), ch = (int)(i % cpr), pair = list[slot], row = pair / n_used;
+    ((uint4*)(sxq + (size_t)slot * H))[ch] = ((const uint4*)(xq + (size_t)row * H))[ch];
+    if (ch < spr) sxs[(size_t)slot * spr + ch] = xs[(size_t)row * spr + ch];
+    if (ch == 0) sids[slot] = ids[pair];
+}
+__global__ void k_ep_unsort(const float* o_back, const int* list, int n_pairs, int H, float* o_mine) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)n_pairs * (H / 4)) return;
+    const int slot = (int)(i / (H / 4)), c4 = (int)(i % (H / 4));
+    ((float4*)(o_mine + (size_t)list[slot] * H))[c4] = ((const float4*)(o_back + (size_t)slot * H))[c4];
+}
 
 // Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
 // slots of gate+up+down live in HBM pools, chosen by GCLOCK. Per MoE layer of a pass the routing ids come to the host,
@@ -428,6 +477,14 @@ struct TierState {
     size_t s2_at = 0;
     uint64_t bytes_moved = 0;
     std::vector<char> dirty;                 // slot_map rows to refresh
+    // the prefetch hint (src/ops/mod.rs:915-924), applied inside the engine: while layer il's experts run, the experts layer
+    // il + 1's router would pick on THIS layer's router input are copied in on a second stream
+    int prefetch_k = 0;                      // guesses per row (0: off)
+    cudaStream_t stream2 = nullptr; cudaEvent_t ev_fetch = nullptr; bool fetch_pending = false;
+    int32_t* guess_dev = nullptr; int32_t* guess_host = nullptr; float* guess_w = nullptr; float* guess_logits = nullptr;
+    float* s2_guess = nullptr; size_t s2_guess_cap = 0;     // pinned staging of the guesses' second scales (their copies outlive the call)
+    std::vector<char> guessed;               // per slot: filled by a guess and not used yet
+    uint64_t fetched = 0, prefetch_reads = 0, prefetch_used = 0, picks_wait_us = 0, lookups = 0, host_reads = 0;
 };
 
 struct itb_engine {
@@ -785,11 +842,32 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
 }
 
 // Make the experts a layer's routing names resident (see TierState). Blocks on the stream once to read the ids.
-static bool tier_ensure(itb_engine* e, cudaStream_t st, uint32_t il, const int32_t* ids_dev, size_t n_pairs) {
+static void tier_copy_in(itb_engine* e, cudaStream_t st, uint32_t il, int32_t ex, int slot, float* stage, size_t* stage_at) {
+    TierState* t = e->tier;
+    for (int k = 0; k < 3; ++k) {
+        const itb_model::HostStack& h = e->m->host_experts[il][k];
+        cudaMemcpyAsync(t->pool_nib[k] + (size_t)slot * h.nib_per, h.nib + (size_t)ex * h.nib_per, h.nib_per, cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(t->pool_sc[k] + (size_t)slot * h.sc_per, h.sc + (size_t)ex * h.sc_per, h.sc_per, cudaMemcpyHostToDevice, st);
+        stage[*stage_at] = h.s2[(size_t)ex];
+        cudaMemcpyAsync(t->pool_s2[k] + slot, stage + *stage_at, 4, cudaMemcpyHostToDevice, st);
+        ++*stage_at;
+        t->bytes_moved += h.nib_per + h.sc_per + 4;
+    }
+    t->fetched++;
+}
+// n_guess: guesses for layer il + 1 in t->guess_dev (0: none). Their copies go to the second stream and overlap this layer's
+// expert kernels; the next call makes the engine's stream wait for them before anything reads the pools.
+static bool tier_ensure(itb_engine* e, cudaStream_t st, uint32_t il, const int32_t* ids_dev, size_t n_pairs, size_t n_guess) {
     TierState* t = e->tier; itb_model* m = e->m; itb_ctx* c = e->c;
     const size_t E = m->d.n_expert;
-    if (cudaMemcpyAsync(t->ids_host, ids_dev, n_pairs * 4, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
-        return itb_fail_msg(c, "tiered experts: cannot read the routing ids");
+    const auto w0 = std::chrono::steady_clock::now();
+    bool got = cudaMemcpyAsync(t->ids_host, ids_dev, n_pairs * 4, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    if (n_guess) got = got && cudaMemcpyAsync(t->guess_host, t->guess_dev, n_guess * 4, cudaMemcpyDeviceToHost, st) == cudaSuccess;
+    if (!got || cudaStreamSynchronize(st) != cudaSuccess) return itb_fail_msg(c, "tiered experts: cannot read the routing ids");
+    t->picks_wait_us += (uint64_t)std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - w0).count();
+    if (t->fetch_pending) {      // the guesses made for this layer: landed before it reads (device), and their staging is free again (host)
+        cudaStreamWaitEvent(st, t->ev_fetch, 0); cudaEventSynchronize(t->ev_fetch); t->fetch_pending = false;
+    }
     t->g->next_pass();
     t->s2_at = 0;
     for (size_t i = 0; i < n_pairs; ++i) {
@@ -799,18 +877,34 @@ static bool tier_ensure(itb_engine* e, cudaStream_t st, uint32_t il, const int32
         bool hit = false; int64_t evicted = -1;
         const int slot = t->g->touch(key, &hit, &evicted);
         if (slot < 0) return itb_fail_msg(c, "tiered experts: a pass needs more distinct experts than the HBM pool holds");
-        if (hit) continue;
-        if (evicted >= 0) { t->slot_map_host[evicted] = -1; t->dirty[(size_t)evicted / E] = 1; }
-        for (int k = 0; k < 3; ++k) {
-            const itb_model::HostStack& h = m->host_experts[il][k];
-            cudaMemcpyAsync(t->pool_nib[k] + (size_t)slot * h.nib_per, h.nib + (size_t)ex * h.nib_per, h.nib_per, cudaMemcpyHostToDevice, st);
-            cudaMemcpyAsync(t->pool_sc[k] + (size_t)slot * h.sc_per, h.sc + (size_t)ex * h.sc_per, h.sc_per, cudaMemcpyHostToDevice, st);
-            t->s2_stage[t->s2_at] = h.s2[(size_t)ex];
-            cudaMemcpyAsync(t->pool_s2[k] + slot, t->s2_stage + t->s2_at, 4, cudaMemcpyHostToDevice, st);
-            t->s2_at++;
-            t->bytes_moved += h.nib_per + h.sc_per + 4;
+        t->lookups++;
+        if (hit) {
+            if (t->guessed[(size_t)slot]) { t->guessed[(size_t)slot] = 0; t->prefetch_used++; }
+            continue;
         }
+        t->host_reads++;
+        t->guessed[(size_t)slot] = 0;
+        if (evicted >= 0) { t->slot_map_host[evicted] = -1; t->dirty[(size_t)evicted / E] = 1; }
+        tier_copy_in(e, st, il, ex, slot, t->s2_stage, &t->s2_at);
         t->slot_map_host[key] = slot; t->dirty[il] = 1;
+    }
+    if (n_guess && il + 1 < m->d.n_layer) {
+        bool any = false;
+        size_t g_at = 0;
+        for (size_t i = 0; i < n_guess; ++i) {
+            const int32_t ex = t->guess_host[i];
+            if (ex < 0 || (size_t)ex >= E || g_at + 3 > t->s2_guess_cap) continue;
+            const int64_t key = (int64_t)(il + 1) * (int64_t)E + ex;
+            int64_t evicted = -1;
+            const int slot = t->g->prefetch(key, &evicted);
+            if (slot < 0) continue;
+            if (evicted >= 0) { t->slot_map_host[evicted] = -1; t->dirty[(size_t)evicted / E] = 1; }
+            tier_copy_in(e, t->stream2, il + 1, ex, slot, t->s2_guess, &g_at);
+            t->guessed[(size_t)slot] = 1; t->prefetch_reads++;
+            t->slot_map_host[key] = slot; t->dirty[il + 1] = 1;
+            any = true;
+        }
+        if (any) { cudaEventRecord(t->ev_fetch, t->stream2); t->fetch_pending = true; }
     }
     for (size_t r = 0; r < t->dirty.size(); ++r)
         if (t->dirty[r]) { cudaMemcpyAsync(t->slot_map + r * E, t->slot_map_host + r * E, E * 4, cudaMemcpyHostToDevice, st); t->dirty[r] = 0; }
@@ -830,6 +924,34 @@ static DevFp4 tier_stack(const itb_engine* e, uint32_t il, int k, const DevFp4& 
 // The multi-row pass: n_seq sequences x n_tok consecutive tokens each (rows = n_seq * n_tok <= e->R), token ids in
 // `tok_rows` (device, row-major). Batched decode is (B, 1); a prefill chunk of one sequence is (1, T).
 // Ends with the LM head on each sequence's last row, the greedy argmax and the position advance.
+// Buffers of the packed all-to-all of an expert-parallel engine, made by the prefill entry point BEFORE the ranks exchange
+// their ready flags (so a rank that cannot allocate makes every rank refuse, and all ranks take the same path afterwards).
+// A rank can receive every pair of every rank: capacity world * R * n_used pairs. False only when memory ran out.
+static bool ep_a2a_prepare(itb_engine* e) {
+    EpState* q = e->ep;
+    NcclApi& nc = nccl_api();
+    if (!q || !nc.Send || !nc.Recv || getenv("ITB_EP_A2A_OFF")) return true;      // the all-gather / reduce-scatter form serves
+    const itb_model_dims& d = e->m->d;
+    if (d.n_expert % q->world || d.n_embd % 32) return true;
+    const size_t H = d.n_embd, K = d.n_expert_used, W = q->world, mine = (size_t)e->R * K, cap = W * mine;
+    if (q->a2a_cap >= cap) return true;
+    cudaStreamSynchronize(e->c->stream);
+    bool ok = cudaMalloc(&q->sxq, mine * H) == cudaSuccess && cudaMalloc(&q->sxs, mine * (H / 32) * 4) == cudaSuccess && cudaMalloc(&q->sids, mine * 4) == cudaSuccess &&
+              cudaMalloc(&q->rxq, cap * H) == cudaSuccess && cudaMalloc(&q->rxs, cap * (H / 32) * 4) == cudaSuccess && cudaMalloc(&q->rids, cap * 4) == cudaSuccess &&
+              cudaMalloc(&q->o_back, mine * H * 4) == cudaSuccess && cudaMalloc(&q->owner, mine * 4) == cudaSuccess && cudaMalloc(&q->own_off, (W + 1) * 4) == cudaSuccess &&
+              cudaMalloc(&q->own_list, mine * 4) == cudaSuccess && cudaMalloc(&q->cnt_dev, W * (W + 1) * 4) == cudaSuccess &&
+              cudaMallocHost(&q->cnt_host, W * (W + 1) * 4) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        cudaFree(q->sxq); cudaFree(q->sxs); cudaFree(q->sids); cudaFree(q->rxq); cudaFree(q->rxs); cudaFree(q->rids); cudaFree(q->o_back); cudaFree(q->owner);
+        cudaFree(q->own_off); cudaFree(q->own_list); cudaFree(q->cnt_dev); if (q->cnt_host) cudaFreeHost(q->cnt_host);
+        q->sxq = q->rxq = nullptr; q->sxs = q->rxs = q->o_back = nullptr; q->sids = q->rids = q->owner = nullptr; q->own_off = q->own_list = q->cnt_dev = q->cnt_host = nullptr;
+        return itb_fail_msg(e->c, "expert-parallel engine: out of device memory for the all-to-all buffers");
+    }
+    q->a2a_cap = cap;
+    return true;
+}
+
 static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_tok, const int32_t* tok_rows) {
     itb_model* m = e->m; itb_ctx* c = e->c;
     const itb_model_dims& d = m->d;
@@ -1006,9 +1128,50 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             float* wts = e->route_w + (size_t)il * e->R * K;
             k_route_rows<<<(R + 3) / 4, 128, (size_t)4 * ((E + 31) & ~31) * 4, st>>>(e->router, R, E, K, ids, wts); launches++;
             // expert parallel: the pairs of every rank's rows, rank-major; otherwise just ours
-            const int W = e->ep ? e->ep->world : 1, P = W * R * K;
+            const int W = e->ep ? e->ep->world : 1;
+            int P = W * R * K, Kt = K;                  // pairs the expert kernels see; pairs per activation row among them
             const int8_t* xq_src = e->xq; const float* xs_src = e->xs; const int32_t* ids_src = ids;
-            if (e->ep) {
+            const bool a2a = e->ep && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone && e->ep->a2a_cap >= (size_t)e->ep->world * e->R * K;
+            std::vector<int> a2a_soff, a2a_roff;
+            if (a2a) {
+                // eager many-row pass: packed all-to-all. Every (row, pick) pair goes to the rank that holds its expert -- its
+                // quantised row, scales and id, nothing else -- and its output row comes back; no rank touches a pair it does
+                // not serve. Counts are exchanged first (one small all-gather, read on the host: the sends are sized by them).
+                EpState* q = e->ep;
+                NcclApi& nc = nccl_api();
+                const int PK = R * K;
+                k_ep_owner<<<(PK + 255) / 256, 256, 0, st>>>(ids, PK, E / W, q->owner);
+                k_group_pairs_fast<<<1, 1024, (size_t)W * 4, st>>>(q->owner, PK, W, q->own_off, q->own_list);
+                k_ep_pack<<<(unsigned)(((size_t)PK * (H / 16) + 255) / 256), 256, 0, st>>>(e->xq, e->xs, ids, q->own_list, PK, K, H, q->sxq, q->sxs, q->sids);
+                nc.AllGather(q->own_off, q->cnt_dev, (size_t)W + 1, NcclApi::Int32, q->comm, st);
+                cudaMemcpyAsync(q->cnt_host, q->cnt_dev, (size_t)W * (W + 1) * 4, cudaMemcpyDeviceToHost, st);
+                if (cudaStreamSynchronize(st) != cudaSuccess) { itb_fail_msg(c, "expert-parallel pass: the pair counts could not be read"); return launches; }
+                std::vector<int> cnt((size_t)W * W);
+                for (int sr = 0; sr < W; ++sr)
+                    for (int dr = 0; dr < W; ++dr) cnt[(size_t)sr * W + dr] = q->cnt_host[sr * (W + 1) + dr + 1] - q->cnt_host[sr * (W + 1) + dr];
+                a2a_soff.assign(W + 1, 0); a2a_roff.assign(W + 1, 0);
+                int n_recv = 0;
+                if (itb_ep_a2a_plan(cnt.data(), W, q->rank, a2a_soff.data(), a2a_roff.data(), &n_recv) || (size_t)n_recv > q->a2a_cap || a2a_soff[W] != PK) {
+                    itb_fail_msg(c, "expert-parallel pass: inconsistent pair counts"); return launches;
+                }
+                nc.GroupStart();
+                for (int r = 0; r < W; ++r) {
+                    const size_t so = a2a_soff[r], sn = a2a_soff[r + 1] - a2a_soff[r], ro = a2a_roff[r], rn = a2a_roff[r + 1] - a2a_roff[r];
+                    if (sn) {
+                        nc.Send(q->sxq + so * H, sn * H, NcclApi::Int8, r, q->comm, st);
+                        nc.Send(q->sxs + so * (H / 32), sn * (H / 32), NcclApi::Float32, r, q->comm, st);
+                        nc.Send(q->sids + so, sn, NcclApi::Int32, r, q->comm, st);
+                    }
+                    if (rn) {
+                        nc.Recv(q->rxq + ro * H, rn * H, NcclApi::Int8, r, q->comm, st);
+                        nc.Recv(q->rxs + ro * (H / 32), rn * (H / 32), NcclApi::Float32, r, q->comm, st);
+                        nc.Recv(q->rids + ro, rn, NcclApi::Int32, r, q->comm, st);
+                    }
+                }
+                nc.GroupEnd();
+                launches += 5;
+                xq_src = q->rxq; xs_src = q->rxs; ids_src = q->rids; P = n_recv; Kt = 1;
+            } else if (e->ep) {
                 NcclApi& nc = nccl_api();
                 nc.GroupStart();
                 nc.AllGather(e->xq, e->ep->gxq, (size_t)R * H, NcclApi::Int8, e->ep->comm, st);
@@ -1021,14 +1184,22 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             }
             DevFp4 Lg = L.gate, Lu = L.up, Ld = L.down;
             if (e->tier) {
-                if (!tier_ensure(e, st, il, ids, (size_t)R * K)) return launches;
+                size_t n_guess = 0;
+                if (e->tier->prefetch_k > 0 && il + 1 < d.n_layer) {
+                    // the hint: layer il + 1's router on THIS layer's router input, top prefetch_k per row (src/ops/mod.rs:915-924)
+                    const int pk = std::min<int>(e->tier->prefetch_k, std::min<int>(16, E));
+                    f32mm(m->layers[il + 1].gate_inp, e->xn, e->tier->guess_logits);
+                    k_route_rows<<<(R + 3) / 4, 128, (size_t)4 * ((E + 31) & ~31) * 4, st>>>(e->tier->guess_logits, R, E, pk, e->tier->guess_dev, e->tier->guess_w); launches++;
+                    n_guess = (size_t)R * pk;
+                }
+                if (!tier_ensure(e, st, il, ids, (size_t)R * K, n_guess)) return launches;
                 Lg = tier_stack(e, il, 0, L.gate); Lu = tier_stack(e, il, 1, L.up); Ld = tier_stack(e, il, 2, L.down);
             }
+            if (P > 0) {
             if (E <= 1024) k_group_pairs_fast<<<1, 1024, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             else k_group_pairs<<<1, 256, (size_t)E * 4, st>>>(ids_src, P, E, e->pair_off, e->pair_list);
             launches++;
-            cudaStreamCaptureStatus cap_st = cudaStreamCaptureStatusNone;
-            cudaStreamIsCapturing(st, &cap_st);
+            const cudaStreamCaptureStatus cap_st = cap_rows;
             if (c->fp4tc && n_tok > 1 && !e->ep && !e->tier && cap_st == cudaStreamCaptureStatusNone && itb_tc_shape_ok(Lg) && itb_tc_shape_ok(Lu) && itb_tc_shape_ok(Ld)) {
                 // many rows, experts=fp4tc: FP4 activations times FP4 weights on the tensor cores (the reference's default device
                 // arithmetic, src/ops/cuda/mod.rs:239-248 there); gate/up + SiLU in one GEMM's epilogue, then down
@@ -1041,10 +1212,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64
                 const int per_e = (P + E - 1) / E, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
                 const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
-#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(Lg, Lu, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all, ns_g)
+#define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(Lg, Lu, xq_src, xs_src, Kt, e->pair_off, e->pair_list, e->h_all, ns_g)
 #define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(Ld, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
                 if (tile_w) { if (nj == 1) GLU_TILE(1, 1); else if (nj == 2) GLU_TILE(2, 1); else if (nj == 4) GLU_TILE(4, 1); else GLU_TILE(4, 2); }
-                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(Lg, Lu, xq_src, xs_src, K, e->pair_off, e->pair_list, e->h_all);
+                else k_glu_grouped<<<dim3(E, (ff + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(H), st>>>(Lg, Lu, xq_src, xs_src, Kt, e->pair_off, e->pair_list, e->h_all);
                 launches++;
                 k_quant_rows<<<P, 128, 0, st>>>(e->h_all, ff, e->hq, e->hs); launches++;
                 if (tile_w) { if (nj == 1) DOWN_TILE(1, 1); else if (nj == 2) DOWN_TILE(2, 1); else if (nj == 4) DOWN_TILE(4, 1); else DOWN_TILE(4, 2); }
@@ -1053,8 +1224,23 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 else k_down_grouped<<<dim3(E, (H + MMA_ROWS - 1) / MMA_ROWS), 256, gemm_smem(ff), st>>>(Ld, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all);
                 launches++;
             }
+            }
             const float* o_src = e->o_all;
-            if (e->ep) {
+            if (a2a) {
+                // combine: every served pair's output row back to the rank that owns the row, then into pair order
+                EpState* q = e->ep;
+                NcclApi& nc = nccl_api();
+                nc.GroupStart();
+                for (int r = 0; r < W; ++r) {
+                    const size_t so = a2a_soff[r], sn = a2a_soff[r + 1] - a2a_soff[r], ro = a2a_roff[r], rn = a2a_roff[r + 1] - a2a_roff[r];
+                    if (rn) nc.Send(e->o_all + ro * H, rn * H, NcclApi::Float32, r, q->comm, st);
+                    if (sn) nc.Recv(q->o_back + so * H, sn * H, NcclApi::Float32, r, q->comm, st);
+                }
+                nc.GroupEnd();
+                k_ep_unsort<<<(unsigned)(((size_t)R * K * (H / 4) + 255) / 256), 256, 0, st>>>(q->o_back, q->own_list, R * K, H, q->o_mine);
+                launches += 2;
+                o_src = q->o_mine;
+            } else if (e->ep) {
                 nccl_api().ReduceScatter(e->o_all, e->ep->o_mine, (size_t)R * K * H, NcclApi::Float32, NcclApi::Sum, e->ep->comm, st);
                 launches++;
                 o_src = e->ep->o_mine;
@@ -1178,8 +1364,42 @@ extern "C" int itb_engine_create_tiered(itb_model* m, uint32_t n_ctx, uint32_t n
     ok = ok && dalloc(e, &t->slot_map, n_keys);
     ok = ok && cudaMallocHost(&t->slot_map_host, n_keys * 4) == cudaSuccess && cudaMallocHost(&t->ids_host, (size_t)e->R * d.n_expert_used * 4) == cudaSuccess &&
          cudaMallocHost(&t->s2_stage, (size_t)capacity * 3 * 4) == cudaSuccess;
+    t->guessed.assign(capacity, 0);
+    t->s2_guess_cap = (size_t)e->R * 16 * 3;
+    t->prefetch_k = getenv("ITB_TIER_PREFETCH") ? std::max(0, atoi(getenv("ITB_TIER_PREFETCH"))) : 0;
+    if (t->prefetch_k > 0) {
+        ok = ok && dalloc(e, &t->guess_dev, (size_t)e->R * 16) && dalloc(e, &t->guess_w, (size_t)e->R * 16) && dalloc(e, &t->guess_logits, (size_t)e->R * d.n_expert) &&
+             cudaMallocHost(&t->guess_host, (size_t)e->R * 16 * 4) == cudaSuccess && cudaMallocHost(&t->s2_guess, (size_t)e->R * 16 * 3 * 4) == cudaSuccess &&
+             cudaStreamCreateWithFlags(&t->stream2, cudaStreamNonBlocking) == cudaSuccess && cudaEventCreateWithFlags(&t->ev_fetch, cudaEventDisableTiming) == cudaSuccess;
+    }
     if (!ok) { itb_fail_msg(c, "tiered engine: out of memory"); itb_engine_destroy(e); *out = nullptr; return 1; }
     for (size_t i = 0; i < n_keys; ++i) t->slot_map_host[i] = -1;
+    return 0;
+}
+// The reference's TierCounters (src/ops/mod.rs:360-401), as far as they exist here: what this engine's expert tier did since it
+// was created, and the device's memory at the snapshot. Fields of the reference that describe its file tier (read_us,
+// upload_us, writes_us, picks_copy_us, oversubscribed) have no counterpart: the lower tier here is pinned host memory.
+extern "C" int itb_tier_counters(itb_engine* e, itb_tier_counters_t* o) {
+    memset(o, 0, sizeof *o);
+    size_t fr = 0, tot = 0;
+    if (cudaMemGetInfo(&fr, &tot) == cudaSuccess) { o->vram_free = fr; o->vram_total = tot; }
+    itb_ctx* c = e->c;
+    o->mirrors = c->mirrors.size(); o->mirror_bytes = c->mirror_bytes; o->weight_bytes = e->m->bytes;
+    {
+        const itb_model_dims& d = e->m->d;
+        size_t n_attn = 0;
+        for (const DevLayer& L : e->m->layers) n_attn += L.recurrent ? 0 : 1;
+        o->kv_bytes = n_attn * (size_t)e->B * e->n_ctx * d.head_dim * d.n_head_kv * 2 * 2;
+    }
+    if (e->tier) {
+        const TierState* t = e->tier;
+        size_t slot_bytes = 0;
+        for (int k = 0; k < 3; ++k) slot_bytes += e->m->host_experts[0][k].nib_per + e->m->host_experts[0][k].sc_per + 4;
+        o->fetched = t->fetched; o->fetch_bytes = t->bytes_moved; o->picks_wait_us = t->picks_wait_us; o->prefetch_reads = t->prefetch_reads;
+        o->prefetch_used = t->prefetch_used; o->lookups = t->lookups; o->host_reads = t->host_reads; o->slot_bytes = slot_bytes; o->slots = t->capacity;
+        o->pool_bytes = slot_bytes * t->capacity;
+    }
+    o->resident_bytes = o->weight_bytes + o->kv_bytes + o->mirror_bytes + o->pool_bytes;
     return 0;
 }
 // hits, misses, evictions, bytes copied host -> HBM since the engine was created
@@ -1244,8 +1464,21 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
     if (!e) return;
     cudaStreamSynchronize(e->c->stream);
     drop_graph(e);
-    if (e->ep) { if (e->ep->comm && !e->ep->broken) nccl_api().CommDestroy(e->ep->comm); cudaFreeHost(e->ep->agree_host); delete e->ep; e->ep = nullptr; }
-    if (e->tier) { cudaFreeHost(e->tier->slot_map_host); cudaFreeHost(e->tier->ids_host); cudaFreeHost(e->tier->s2_stage); delete e->tier->g; delete e->tier; e->tier = nullptr; }
+    if (e->ep) {
+        EpState* q = e->ep;
+        if (q->comm && !q->broken) nccl_api().CommDestroy(q->comm);
+        cudaFreeHost(q->agree_host);
+        cudaFree(q->sxq); cudaFree(q->sxs); cudaFree(q->sids); cudaFree(q->rxq); cudaFree(q->rxs); cudaFree(q->rids); cudaFree(q->o_back); cudaFree(q->owner);
+        cudaFree(q->own_off); cudaFree(q->own_list); cudaFree(q->cnt_dev); if (q->cnt_host) cudaFreeHost(q->cnt_host);
+        delete q; e->ep = nullptr;
+    }
+    if (e->tier) {
+        TierState* t = e->tier;
+        if (t->stream2) { cudaStreamSynchronize(t->stream2); cudaStreamDestroy(t->stream2); }
+        if (t->ev_fetch) cudaEventDestroy(t->ev_fetch);
+        cudaFreeHost(t->slot_map_host); cudaFreeHost(t->ids_host); cudaFreeHost(t->s2_stage); cudaFreeHost(t->guess_host); cudaFreeHost(t->s2_guess);
+        delete t->g; delete t; e->tier = nullptr;
+    }
     for (void* p : e->allocs) cudaFree(p);
     cudaFree(e->history); cudaFree(e->prompt); cudaFree(e->scores); cudaFree(e->gdn_scratch);
     cudaEventDestroy(e->ev0); cudaEventDestroy(e->ev1);
@@ -1640,6 +1873,7 @@ extern "C" int itb_engine_prefill(itb_engine* e, const uint32_t* tokens, size_t 
         }
     }
     ok = ok && steps_ready(e, 0);   // a one-token pass replays the step graph: have it captured before anything is enqueued
+    if (ok && e->ep && getenv("ITB_PREFILL_STEPWISE") == nullptr) ok = ep_a2a_prepare(e);
     if (!ep_agree(e, ok)) return 1;
     const bool stepwise = getenv("ITB_PREFILL_STEPWISE") != nullptr;
     const size_t chunk = stepwise ? 1 : std::max<size_t>(1, e->R / e->B);

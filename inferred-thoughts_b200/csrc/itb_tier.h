@@ -46,4 +46,25 @@ struct GClock {
         }
         return -1;
     }
+    // A guess, not a use: bring `key` in if it is absent and a slot can be had without touching this pass's leases. The
+    // entry starts at count 0 (the first to go if the guess was wrong) and is leased like any other until the pass ends,
+    // so the copy in flight is not overwritten. Returns the slot to fill, or -1 (already resident, or no slot). Hits and
+    // misses are not counted: a guess is neither.
+    int prefetch(int64_t key, int64_t* evicted) {
+        *evicted = -1;
+        if (slot_of[(size_t)key] >= 0) return -1;
+        const size_t n = slots.size();
+        for (size_t tries = 0; tries < 2 * n; ++tries) {
+            Slot& sl = slots[hand];
+            const size_t at = hand;
+            hand = (hand + 1) % n;
+            if (sl.lease == pass) continue;
+            if (sl.key >= 0 && sl.count > 0) { --sl.count; continue; }
+            if (sl.key >= 0) { slot_of[(size_t)sl.key] = -1; *evicted = sl.key; ++evictions; }
+            sl.key = key; sl.count = 0; sl.lease = pass;
+            slot_of[(size_t)key] = (int32_t)at;
+            return (int)at;
+        }
+        return -1;
+    }
 };

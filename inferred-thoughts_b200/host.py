@@ -322,6 +322,16 @@ def expert_range(rank, world, n_expert):
     return per * rank, per * (rank + 1)
 
 
+def ep_a2a_plan(cnt, rank):
+    """cnt[s][d] = pairs rank s sends to rank d -> (send_off[world + 1], recv_off[world + 1], n_recv) of rank `rank`."""
+    cnt = np.ascontiguousarray(cnt, np.int32)
+    world = cnt.shape[0]
+    so, ro, n = np.zeros(world + 1, np.int32), np.zeros(world + 1, np.int32), C.c_int()
+    if lib().itb_ep_a2a_plan(_p(cnt), world, rank, _p(so), _p(ro), C.byref(n)):
+        raise ValueError("bad count matrix or rank")
+    return so, ro, n.value
+
+
 def ep_unique_id(lib_=None):
     """128 bytes that name a new NCCL communicator; rank 0 makes them, every rank passes the same bytes to Engine(ep=...)."""
     L = lib_ or lib()
@@ -395,6 +405,15 @@ class Engine:
         out = (C.c_uint64 * 4)()
         self.L.itb_engine_tier_stats(self.h, out)
         return dict(hits=out[0], misses=out[1], evictions=out[2], bytes_moved=out[3])
+
+    def tier_counters(self):
+        """The reference's TierCounters as far as they exist here (see itb.h), as a dict."""
+        names = ("fetched fetch_bytes picks_wait_us prefetch_reads prefetch_used lookups host_reads slot_bytes slots pool_bytes "
+                 "vram_free vram_total mirrors mirror_bytes weight_bytes kv_bytes resident_bytes").split()
+        out = (C.c_uint64 * len(names))()
+        if self.L.itb_tier_counters(self.h, out):
+            raise RuntimeError("tier_counters failed")
+        return dict(zip(names, (int(v) for v in out)))
 
     def reset(self): self.L.itb_engine_reset(self.h)
     def pos(self, seq=0): return self.L.itb_engine_pos(self.h, seq)

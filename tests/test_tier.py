@@ -76,3 +76,53 @@ def test_tiered_engine_equals_plain_engine(capacity):
         assert st["evictions"] > st["misses"] // 2
     ops.check()
     e1.close(); e2.close(); cold.close(); plain.close(); ops.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prefetch", [0, 8])
+def test_tiered_engine_against_the_oracle_with_and_without_the_prefetch_hint(prefetch):
+    """The tiered engine against the CPU oracle (not against another engine): prompt logits, teacher-forced decode logits and
+    routing ids bit for bit on the tiny model with a pool of 24 of its 64 (layer, expert) entries. With the prefetch hint on
+    (8 guesses per row for the next layer, copied on a second stream) nothing the model computes may change; the counters
+    must show the guesses being made and some of them being used, and must add up."""
+    import os
+    from inferred_thoughts_b200 import host
+    from oracle import oracle_py as O
+    from tests.util import oracle_dims
+    ops = host.B200Ops(0, "exact=1")
+    cold = host.Model(ops, host_dims(TINY)); cold.synth(0)
+    om = O.OracleModel(oracle_dims(TINY))
+    for sp in om.specs:
+        data, sc = cold.synth_read(0, sp["name"], sp["bytes"], sp["n_expert"] if sp["has_scale"] else 0)
+        om.set_tensor(sp["name"], data, sc)
+    cold.offload_experts()
+    if prefetch:
+        os.environ["ITB_TIER_PREFETCH"] = str(prefetch)
+    try:
+        eng = host.Engine(cold, 64, 1, tier_capacity=24)
+    finally:
+        os.environ.pop("ITB_TIER_PREFETCH", None)
+    L, K = TINY["n_layer"], TINY["n_expert_used"]
+    prompt = prompt_ids(12, 30, TINY["n_vocab"])
+    om.begin(64, log_routes=True)
+    o = om.forward(prompt); g = eng.prefill(prompt)
+    assert o.view(np.uint32).tolist() == g.view(np.uint32).tolist(), "prompt logits"
+    for step in range(10):
+        t = int(np.argmax(o))
+        om.clear_route_log()
+        o = om.forward([t]); lg, _ = eng.decode([t])
+        assert o.view(np.uint32).tolist() == lg[0].view(np.uint32).tolist(), f"decode step {step}"
+        assert eng.read_routes(L, K)[:, 0, :].tolist() == om.route_log().reshape(L, K).tolist(), f"routing at step {step}"
+    c, st = eng.tier_counters(), eng.tier_stats()
+    print(prefetch, c)
+    assert c["lookups"] == st["hits"] + st["misses"] and c["host_reads"] == st["misses"]
+    assert c["fetch_bytes"] == st["bytes_moved"] and c["fetched"] * c["slot_bytes"] == c["fetch_bytes"]
+    assert c["slots"] == 24 and c["pool_bytes"] == 24 * c["slot_bytes"] and c["vram_total"] > c["vram_free"] > 0
+    assert c["resident_bytes"] >= c["weight_bytes"] + c["kv_bytes"] + c["pool_bytes"] and c["kv_bytes"] > 0
+    if prefetch:
+        assert c["prefetch_reads"] > 0 and 0 < c["prefetch_used"] <= c["prefetch_reads"]
+        assert c["fetched"] == c["host_reads"] + c["prefetch_reads"]
+    else:
+        assert c["prefetch_reads"] == 0 and c["prefetch_used"] == 0 and c["fetched"] == c["host_reads"]
+    ops.check()
+    eng.close(); cold.close(); ops.close()
