@@ -190,7 +190,6 @@ __device__ __forceinline__ uint32_t e2m1_of(float x, float inv) {
 }
 // One 16-element block: the scale code of least squared error among the seed and its four neighbours, then the codes.
 __device__ __forceinline__ void fp4_quant_block(const float* blk, uint32_t* scale_code, uint32_t* codes_lo, uint32_t* codes_hi) {
-    const float kv[8] = {0.f, 1.f, 2.f, 3.f, 4.f, 6.f, 8.f, 12.f};
     float v[16];
     float amax = 0.0f;
 #pragma unroll
@@ -208,8 +207,11 @@ __device__ __forceinline__ void fp4_quant_block(const float* blk, uint32_t* scal
         float err = 0.0f;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-            const uint32_t q = e2m1_of(v[j], inv);
-            const float d = fabsf(v[j]) - kv[q & 7] * sc;
+            // the code's doubled magnitude {0,1,2,3,4,6,8,12} built by the same comparisons that pick the code (no table look-up)
+            const float ax = fabsf(v[j]) * inv;
+            const float mag = (ax > 0.25f ? 1.0f : 0.0f) + (ax > 0.75f ? 1.0f : 0.0f) + (ax > 1.25f ? 1.0f : 0.0f) + (ax > 1.75f ? 1.0f : 0.0f) +
+                              (ax > 2.5f ? 2.0f : 0.0f) + (ax > 3.5f ? 2.0f : 0.0f) + (ax > 5.0f ? 4.0f : 0.0f);
+            const float d = fabsf(v[j]) - mag * sc;
             err = __fmaf_rn(d, d, err);
         }
         if (err < best_err) { best_err = err; best_code = code; best_scale = sc; }
