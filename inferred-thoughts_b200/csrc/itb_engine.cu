@@ -650,7 +650,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             for (int m = 0; m < p.nf; ++m) units += (p.f[m].n_out + 31) / 32;
             bool kmajor = true;
             for (int m = 0; m < p.nf; ++m) kmajor = kmajor && p.f[m].wt;
-            if (kmajor && units <= gx && H % F32S_K == 0 && in_proj_smem(H, 1, p.br, 1) <= SMEM_BUDGET) p.f32_ring = 1;
+            if (kmajor && units <= gx && NWG >= 4 && H % F32S_K == 0 && H / F32S_K >= F32S_STAGES && in_proj_smem(H, 1, p.br, 1) <= SMEM_BUDGET) p.f32_ring = units;
             else {
                 const int want = (H + H / 32) / (H / 32 + 1) + 1;
                 p.br = std::max(p.br, std::min((want + pass_in - 1) / pass_in * pass_in, cap / pass_in * pass_in));
@@ -968,6 +968,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         set_smem((const void*)k_matmul_f32_rows<20>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<24>, 64 * 1024);
         set_smem((const void*)k_matmul_f32_rows<28>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<32>, 64 * 1024);
         set_smem((const void*)k_tile_q8<1, 256, 4>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
+        set_smem((const void*)k_sgemm_serial_small, sgemm_small_smem());
         set_smem((const void*)k_gdn_chunk_prep<128>, gdn_chunk_prep_smem<128>()); set_smem((const void*)k_gdn_chunk_scan<128>, gdn_chunk_scan_smem<128>());
         set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<2, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256, 1>, 226 * 1024);
@@ -1012,11 +1013,11 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             launches++;
             return;
         }
-        if (c->exact && w.n_in % SG_K == 0) {
+        if (c->exact && w.n_in % SGS_K == 0) {
             // a chain per (row, output), a thread per 4 x 4 of them, k in order (also for a few rows: the tile's k loop is as long as a row's chain either way)
             const int big = ((w.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T);
             if (big >= sms / 2) k_sgemm_serial<<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
-            else k_sgemm_serial_small<<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, 0, st>>>(w, x, R, out);
+            else k_sgemm_serial_small<<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, sgemm_small_smem(), st>>>(w, x, R, out);
             launches++;
             return;
         }

@@ -23,7 +23,7 @@ struct InProj {
     const float* conv_w; float* conv_state; int conv_kernel; size_t conv_state_stride;
     int8_t* xq_out; float* xs_out;                // optional copy of the quantised normed row, [B][n_embd]
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
-    int f32_ring; int* err;                        // serial-k F32 rows through the block's ring (in_proj_smem counts it); status word of its bounded waits
+    int f32_ring; int* err;                        // serial-k F32 rows through the block's ring (in_proj_smem counts it): the number of 32-row units, 0 = off; status word of its bounded waits
     int tl_slot;                                   // phase-timeline slot of this launch (-1: none)
 };
 
@@ -45,20 +45,41 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
     // (offset arithmetic on the shared array itself: a pointer that went through an integer would be read with generic loads)
     const size_t ring_off = ((size_t)((const unsigned char*)(tile + (p.exact ? 32 * 33 : 0) + nw * (tfl + CONV_CAP * 8)) - smem) + 127) & ~(size_t)127;
     float* ring = (float*)(smem + ring_off);
-    unsigned long long* ring_bars = (unsigned long long*)(ring + F32S_FLOATS);
-    if (p.f32_ring && threadIdx.x == 0) {
-        for (int i = 0; i < F32S_STAGES; ++i)
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(ring_bars + i)) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    unsigned long long* ring_full = (unsigned long long*)(ring + F32S_FLOATS);
+    unsigned long long* ring_empty = ring_full + F32S_STAGES;
+    // serial-k F32 units: unit u belongs to block gridDim.x - 1 - u; there the last warp folds and the one before it feeds the
+    // ring, and neither takes Q8_0 rows (the fold is the longest thing in the kernel)
+    const int my_unit = p.f32_ring ? (int)gridDim.x - 1 - (int)blockIdx.x : -1;
+    const bool unit_block = my_unit >= 0 && my_unit < p.f32_ring;
+    const float* unit_w = nullptr; float* unit_out = nullptr; int unit_r0 = 0, unit_nr = 0;
+    if (unit_block) {
+        int u = my_unit;
+        for (int m = 0; m < p.nf; ++m) {
+            const int units = (p.f[m].n_out + 31) / 32;
+            if (u < units) {
+                unit_w = p.f[m].wt + (size_t)u * 32 * n; unit_out = p.fout[m] + (size_t)b * p.fstride[m];
+                unit_r0 = u * 32; unit_nr = min(32, p.f[m].n_out - u * 32);
+                break;
+            }
+            u -= units;
+        }
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < F32S_STAGES; ++i) {
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(ring_full + i)) : "memory");
+                asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(ring_empty + i)) : "memory");
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
     }
-
+    const int nwq = unit_block ? nw - 2 : nw;                     // warps that take Q8_0 rows
     // this warp's share of the concatenated Q8_0 rows
     int total = 0;
     for (int m = 0; m < p.nq; ++m) total += p.q[m].n_out;
     int b0, b1, r0, r1;
     share(total, gridDim.x, blockIdx.x, b0, b1);
-    share(b1 - b0, nw, wid, r0, r1);
+    share(b1 - b0, nwq, min(wid, nwq - 1), r0, r1);
     r0 += b0; r1 += b0;
+    if (wid >= nwq) r1 = r0;
     const int keep = p.conv_kernel - 1;
     int conv_lo = 0;
     if (p.conv_w && r0 < min(r1, p.q[0].n_out)) {
@@ -70,6 +91,11 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = lane; i < nr * p.conv_kernel; i += 32) cpre[(i / p.conv_kernel) * 8 + keep + i % p.conv_kernel] = cw[i];
         conv_lo = r0;
     }
+    if (unit_block) {
+        __syncthreads();                                          // the ring's barriers exist
+        if (wid == nw - 2 && lane == 0)
+            for (int t = 0; t < F32S_STAGES && t < n / F32S_K; ++t) f32_unit_issue(unit_w, t, ring, ring_full);
+    }
     pdl_wait();
     TL(TLK_IN_PROJ, 1);
     const bool quantised = block_rms_norm(p.x + (size_t)b * p.x_stride, p.norm_w, n, p.eps, xn, red, xq, xs);
@@ -80,29 +106,25 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         for (int i = threadIdx.x; i < n / 16; i += blockDim.x) ((uint4*)(p.xq_out + (size_t)b * n))[i] = ((const uint4*)xq)[i];
         for (int i = threadIdx.x; i < nb; i += blockDim.x) p.xs_out[(size_t)b * nb + i] = xs[i];
     }
-    // F32 rows, handed out from the far end of the grid's warps so that consecutive units land on different blocks.
-    // Serial-k: units of 32 rows, a lane per row (each lane folds its own row in k order); otherwise a row per warp, shuffle tree.
-    {
+    // F32 rows. Serial-k: this block's unit, if it has one (the weights' first stages were requested before the norm; see below).
+    // Otherwise a row per warp handed out from the far end of the grid's warps: serial fold over staged products, or shuffle tree.
+    if (p.f32_ring) {
+        if (unit_block && wid == nw - 1)
+            f32_rows32_serial(n, unit_r0, unit_nr, xn, ring, ring_full, ring_empty, p.err, [&](int row, float v) { unit_out[row] = v; });
+        else if (unit_block && wid == nw - 2 && lane == 0)
+            f32_unit_feed(unit_w, n, ring, ring_full, ring_empty, p.err);
+    } else {
         const int ngw = gridDim.x * nw, gw = ngw - 1 - (wid * (int)gridDim.x + (int)blockIdx.x);
         int ubase = 0;
 #pragma unroll 1
         for (int m = 0; m < p.nf; ++m) {
             float* o = p.fout[m] + (size_t)b * p.fstride[m];
-            if (p.f32_ring) {
-                // one unit per block at most (the host checked): unit u goes to the last warp of block gridDim.x - 1 - u
-                const int units = (p.f[m].n_out + 31) / 32, u = gw - ubase;
-                if (u >= 0 && u < units) {
-                    f32_rows32_serial(p.f[m].wt + (size_t)u * 32 * n, n, u * 32, min(32, p.f[m].n_out - u * 32), xn, ring, ring_bars, p.err, [&](int row, float v) { o[row] = v; });
-                }
-                ubase += units;
-            } else {
-                for (int r = gw - ubase; r < p.f[m].n_out; r += ngw) {
-                    if (r < 0) continue;
-                    if (p.exact) f32_rows<true>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; }, tfl);
-                    else f32_rows<false>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; });
-                }
-                ubase = (ubase + p.f[m].n_out) % ngw;
+            for (int r = gw - ubase; r < p.f[m].n_out; r += ngw) {
+                if (r < 0) continue;
+                if (p.exact) f32_rows<true>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; }, tfl);
+                else f32_rows<false>(p.f[m].w, n, r, r + 1, xn, terms, [&](int row, float v) { o[row] = v; });
             }
+            ubase = (ubase + p.f[m].n_out) % ngw;
         }
     }
     int base = 0;
@@ -141,7 +163,7 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
 size_t in_proj_smem(int n, int exact, int br, int f32_ring = 0) {
     int nb = n / 32;
     return 256 + (size_t)n * 5 + (size_t)nb * 4 + (exact ? 32 * 33 * 4 : 0) + (size_t)NWG * (br * (nb + 1) + CONV_CAP * 8) * 4 + 64 +
-           (f32_ring ? (size_t)F32S_FLOATS * 4 + F32S_STAGES * 8 + 128 : 0);
+           (f32_ring ? (size_t)F32S_FLOATS * 4 + 2 * F32S_STAGES * 8 + 128 : 0);
 }
 
 // ------------------------------------------------------------------------------------------------------

@@ -402,41 +402,50 @@ __device__ __forceinline__ void f32_rows(const float* __restrict__ w, int n_in, 
 
 // Serial-k F32 rows, 32 rows per warp: lane = row, every lane folds ITS row in k order (product and sum rounded separately,
 // src/ops/naive.rs:49-56), so 32 chains run side by side at one add latency per k for all of them. The unit's weights come
-// from the k-major copy (DevF32::wt): a stage of 128 k is 16 KB in one piece, fetched by ONE bulk asynchronous copy that
-// signals the stage's mbarrier; in shared memory lane r reads word k * 32 + r, no conflicts. Five stages keep enough bytes
-// in flight for one warp to stream at the pace of the chain. Waits are bounded: one that runs out stores `F32S_FAIL` in *err
-// and the fold goes on over whatever the slot holds (the host reads *err after the step). n_in a multiple of 128.
-constexpr int F32S_K = 128, F32S_STAGES = 5, F32S_STAGE_FLOATS = 32 * F32S_K, F32S_FLOATS = F32S_STAGES * F32S_STAGE_FLOATS;
+// from the k-major copy (DevF32::wt): a stage of 256 k is 32 KB in one piece, fetched by ONE bulk asynchronous copy that
+// signals the stage's `full` mbarrier; in shared memory lane r reads word k * 32 + r, no conflicts. The copies are issued
+// by ANOTHER warp (f32_unit_feed): the folding warp does nothing but wait for a stage, fold it and hand the slot back
+// (`empty` mbarrier), so the chain of adds is the only thing on its critical path. Four stages keep enough bytes in flight
+// for one warp to stream at the pace of the chain. Waits are bounded: one that runs out stores `F32S_FAIL` in *err and the
+// fold goes on over whatever the slot holds (the host reads *err after the step). n_in a multiple of 256.
+constexpr int F32S_K = 256, F32S_STAGES = 4, F32S_STAGE_FLOATS = 32 * F32S_K, F32S_FLOATS = F32S_STAGES * F32S_STAGE_FLOATS;
 constexpr int F32S_FAIL = 0x7001;
+__device__ __forceinline__ bool f32s_wait(unsigned long long* bar, uint32_t parity, int* err) {
+    const uint32_t b = (uint32_t)__cvta_generic_to_shared(bar);
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(b), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - t0 > 2000000000ll) { if (err) atomicExch(err, F32S_FAIL); return false; }
+    }
+}
+// One lane of the feeding warp: stage t of the unit into slot t % stages; first = the stages issued before anything was folded
+// (no slot to wait for), then one stage per slot the folding warp hands back.
+__device__ __forceinline__ void f32_unit_issue(const float* wt_unit, int t, float* ring, unsigned long long* full) {
+    const int slot = t % F32S_STAGES;
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(full + slot);
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + slot * F32S_STAGE_FLOATS);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)) : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(wt_unit + (size_t)t * F32S_STAGE_FLOATS), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void f32_unit_feed(const float* wt_unit, int n_in, float* ring, unsigned long long* full, unsigned long long* empty, int* err) {
+    const int nst = n_in / F32S_K;
+    for (int t = F32S_STAGES; t < nst; ++t) {
+        if (!f32s_wait(empty + t % F32S_STAGES, (uint32_t)(t / F32S_STAGES - 1) & 1u, err)) return;
+        f32_unit_issue(wt_unit, t, ring, full);
+    }
+}
 template <class Epi>
-__device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_unit, int n_in, int r0, int nr, const float* x, float* ring,
-                                                  unsigned long long* bars, int* err, Epi epi) {
+__device__ __forceinline__ void f32_rows32_serial(int n_in, int r0, int nr, const float* x, const float* ring, unsigned long long* full,
+                                                  unsigned long long* empty, int* err, Epi epi) {
     const int lane = threadIdx.x & 31, nst = n_in / F32S_K;
-    auto issue = [&](int t) {
-        if (t < nst && lane == 0) {
-            const int slot = t % F32S_STAGES;
-            const uint32_t bar = (uint32_t)__cvta_generic_to_shared(bars + slot);
-            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(ring + slot * F32S_STAGE_FLOATS);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)) : "memory");
-            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(dst), "l"(wt_unit + (size_t)t * F32S_STAGE_FLOATS), "r"((uint32_t)(F32S_STAGE_FLOATS * 4)), "r"(bar) : "memory");
-        }
-    };
-    for (int t = 0; t < F32S_STAGES; ++t) issue(t);
     float sum = 0.0f;
 #pragma unroll 1
     for (int t = 0; t < nst; ++t) {
         const int slot = t % F32S_STAGES;
-        const uint32_t bar = (uint32_t)__cvta_generic_to_shared(bars + slot), parity = (uint32_t)(t / F32S_STAGES) & 1u;
-        {
-            const long long t0 = clock64();
-            for (;;) {
-                uint32_t ok;
-                asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }" : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-                if (ok) break;
-                if (clock64() - t0 > 2000000000ll) { if (err) atomicExch(err, F32S_FAIL); break; }
-            }
-        }
+        f32s_wait(full + slot, (uint32_t)(t / F32S_STAGES) & 1u, err);
         const float* col = ring + slot * F32S_STAGE_FLOATS + lane;
         const float* xs = x + t * F32S_K;
         // the products of the next 16 k are formed while the current 16 are added: the adds are the only chain
@@ -450,7 +459,7 @@ __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_u
             }
         };
         prod(pa, 0);
-#pragma unroll
+#pragma unroll 2
         for (int k0 = 0; k0 < F32S_K; k0 += 32) {
             prod(pb, k0 + 16);
 #pragma unroll
@@ -459,8 +468,8 @@ __device__ __forceinline__ void f32_rows32_serial(const float* __restrict__ wt_u
 #pragma unroll
             for (int i = 0; i < 16; ++i) sum = __fadd_rn(sum, pb[i]);
         }
-        __syncwarp();                           // every lane has read the slot: it may be refilled
-        issue(t + F32S_STAGES);
+        __syncwarp();                           // every lane has read the slot: hand it back
+        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"((uint32_t)__cvta_generic_to_shared(empty + slot)) : "memory");
     }
     if (lane < nr) epi(r0 + lane, sum);
 }

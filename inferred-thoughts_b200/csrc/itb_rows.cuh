@@ -111,29 +111,45 @@ __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __r
 }
 
 // The same for few rows or few outputs, where 64 x 64 tiles would leave most SMs idle: a thread per (row, output), 16 x 16 of
-// them per block; every thread's k loop is the row's whole chain either way, so the small tile costs nothing but reuse.
-// grid (ceil(n_out / 16), ceil(n_rows / 16)), block 256.
+// them per block; every thread's k loop is the row's whole chain either way, so the small tile costs nothing but reuse. With
+// so few blocks the global loads are what must not be waited for: tiles of 128 k arrive through a four-stage cp.async ring
+// (three tiles in flight while one is folded). grid (ceil(n_out / 16), ceil(n_rows / 16)), block 256, dynamic shared memory
+// sgemm_small_smem(); n_in a multiple of 128.
+constexpr int SGS_K = 128, SGS_ST = SGS_K + 4, SGS_STAGES = 4;
+constexpr size_t sgemm_small_smem() { return (size_t)SGS_STAGES * 2 * 16 * SGS_ST * 4; }
 __global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
-    __shared__ float ws[2][SG_K][16 + 1], xs[2][SG_K][16 + 1];
-    const int o0 = blockIdx.x * 16, r0 = blockIdx.y * 16, n = w.n_in;
+    extern __shared__ __align__(16) unsigned char smem[];
+    float* ring = (float*)smem;                    // [stage][w | x][16 lines][SGS_ST]
+    const int o0 = blockIdx.x * 16, r0 = blockIdx.y * 16, n = w.n_in, nk = n / SGS_K;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;            // output o0 + tx, row r0 + ty
-    // loader: thread -> (line 0..15 of either tile, 4 consecutive k): threads 0..127 the weights, 128..255 the rows
-    const int half = threadIdx.x >> 7, ll = (threadIdx.x & 127) >> 3, lk = (threadIdx.x & 7) * 4;
-    const float* src = half ? x + (size_t)min(r0 + ll, n_rows - 1) * n + lk : w.w + (size_t)min(o0 + ll, w.n_out - 1) * n + lk;
-    float (*dst)[SG_K][17] = half ? xs : ws;
-    float4 v = __ldg((const float4*)src);
-    dst[0][lk][ll] = v.x; dst[0][lk + 1][ll] = v.y; dst[0][lk + 2][ll] = v.z; dst[0][lk + 3][ll] = v.w;
-    __syncthreads();
-    float acc = 0.0f;
-    const int nk = n / SG_K;
-    for (int t = 0; t < nk; ++t) {
-        const int buf = t & 1;
-        if (t + 1 < nk) v = __ldg((const float4*)(src + (size_t)(t + 1) * SG_K));
+    auto fetch = [&](int t) {
+        if (t < nk) {
+            float* st = ring + (size_t)(t % SGS_STAGES) * 2 * 16 * SGS_ST;
 #pragma unroll
-        for (int kk = 0; kk < SG_K; ++kk) acc = __fadd_rn(acc, __fmul_rn(ws[buf][kk][tx], xs[buf][kk][ty]));
-        if (t + 1 < nk) { dst[buf ^ 1][lk][ll] = v.x; dst[buf ^ 1][lk + 1][ll] = v.y; dst[buf ^ 1][lk + 2][ll] = v.z; dst[buf ^ 1][lk + 3][ll] = v.w; }
-        __syncthreads();
+            for (int i = 0; i < 4; ++i) {
+                const int c = threadIdx.x + 256 * i, m = c >> 9, line = (c & 511) >> 5, k4 = (c & 31) * 4;      // 2 matrices x 16 lines x 32 chunks
+                const float* src = m ? x + (size_t)min(r0 + line, n_rows - 1) * n : w.w + (size_t)min(o0 + line, w.n_out - 1) * n;
+                cp_async16(st + (m * 16 + line) * SGS_ST + k4, src + (size_t)t * SGS_K + k4, true);
+            }
+        }
+        cp_async_commit();
+    };
+    for (int t = 0; t < SGS_STAGES - 1; ++t) fetch(t);
+    float acc = 0.0f;
+    for (int t = 0; t < nk; ++t) {
+        cp_async_wait<SGS_STAGES - 2>();
+        __syncthreads();                           // tile t has landed for everyone; everyone is done with tile t - 1
+        fetch(t + SGS_STAGES - 1);                 // into the slot tile t - 1 used
+        const float* st = ring + (size_t)(t % SGS_STAGES) * 2 * 16 * SGS_ST;
+        const float* wr = st + tx * SGS_ST; const float* xr = st + (16 + ty) * SGS_ST;
+#pragma unroll 8
+        for (int kk = 0; kk < SGS_K; kk += 4) {
+            const float4 a = *(const float4*)(wr + kk), c = *(const float4*)(xr + kk);
+            acc = __fadd_rn(acc, __fmul_rn(a.x, c.x)); acc = __fadd_rn(acc, __fmul_rn(a.y, c.y));
+            acc = __fadd_rn(acc, __fmul_rn(a.z, c.z)); acc = __fadd_rn(acc, __fmul_rn(a.w, c.w));
+        }
     }
+    cp_async_wait<0>();
     if (r0 + ty < n_rows && o0 + tx < w.n_out) out[(size_t)(r0 + ty) * w.n_out + o0 + tx] = acc;
 }
 
