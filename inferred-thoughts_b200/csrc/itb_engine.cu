@@ -51,6 +51,9 @@ struct DevLayer {
     DevQ8 wqkv, wgate, ssm_out; DevF32 ssm_alpha, ssm_beta;
     const float *conv1d = nullptr, *ssm_a = nullptr, *dt_bias = nullptr, *ssm_norm = nullptr;
     DevF32 gate_inp, shared_gate_inp; DevFp4 gate, up, down; DevQ8 shared_gate, shared_up, shared_down;
+    // a file may carry the shared expert as NVFP4 with one second scale per matmul (src/model/mod.rs:351-361,
+    // src/model/qwen35.rs:1668-1682): then the Q8_0 views above are empty and these hold it (gate, up, down)
+    DevFp4 shared4[3]; float shared_s[3] = {1.0f, 1.0f, 1.0f}; bool has_shared_s[3] = {false, false, false};
 };
 struct itb_model {
     itb_ctx* c = nullptr;
@@ -58,6 +61,9 @@ struct itb_model {
     std::map<std::string, DevTensor> t;
     std::vector<DevLayer> layers;
     DevF32 tok_embd; const float* output_norm = nullptr; DevQ8 output;
+    DevFp4 output4; float output_s = 1.0f; bool has_output_s = false;   // the LM head as NVFP4 with `output.scale` (src/model/qwen35.rs:736-737, :1118)
+    bool dense_fp4 = false;                  // some shared expert or the LM head is NVFP4: steps run the multi-row kernels
+    std::map<std::string, float> scalars;    // `<weight>.scale` of the dense NVFP4 matrices
     bool finalized = false;
     uint32_t expert_lo = 0, expert_hi = 0;
     size_t bytes = 0;
@@ -145,10 +151,25 @@ extern "C" int itb_model_set_tensor(itb_model* m, const char* name, uint32_t ty,
                                     const float* scale, size_t n_scale) {
     itb_ctx* c = m->c;
     auto specs = synth::model_tensors(to_synth(m->d));
+    const std::string nm(name);
+    auto dense_fp4_ok = [](const std::string& n) {
+        return n == "output.weight" || n.find("ffn_gate_shexp.weight") != std::string::npos || n.find("ffn_up_shexp.weight") != std::string::npos ||
+               n.find("ffn_down_shexp.weight") != std::string::npos;
+    };
+    if (nm.size() > 6 && nm.compare(nm.size() - 6, 6, ".scale") == 0) {
+        // `<weight>.scale`: the one-element second scale of a dense NVFP4 matrix (the experts' per-expert scales travel with set_tensor's `scale`)
+        const std::string wname = nm.substr(0, nm.size() - 6) + ".weight";
+        if (!dense_fp4_ok(wname) || !find_spec(specs, wname.c_str())) { itb_fail_msg(c, std::string("set_tensor: no weight takes the scalar ") + name); return 1; }
+        if (ty != ITB_F32 || bytes != 4) { itb_fail_msg(c, std::string("set_tensor: ") + name + " must be one f32"); return 1; }
+        float v; memcpy(&v, data, 4);
+        m->scalars[nm] = v; m->finalized = false;
+        return 0;
+    }
     const synth::TensorSpec* s = find_spec(specs, name);
     if (!s) { itb_fail_msg(c, std::string("set_tensor: unknown tensor ") + name); return 1; }
-    if (s->ty != ty) { itb_fail_msg(c, std::string("set_tensor: ") + name + " has a storage type this path has no kernel for"); return 1; }
-    if (bytes != s->bytes()) { itb_fail_msg(c, std::string("set_tensor: wrong byte count for ") + name); return 1; }
+    const bool as_fp4 = ty == ITB_NVFP4 && s->ty == synth::TY_Q8_0 && dense_fp4_ok(nm) && s->n_in % 64 == 0;
+    if (s->ty != ty && !as_fp4) { itb_fail_msg(c, std::string("set_tensor: ") + name + " has a storage type this path has no kernel for"); return 1; }
+    if (bytes != (as_fp4 ? s->n_in * s->n_out / 64 * 36 : s->bytes())) { itb_fail_msg(c, std::string("set_tensor: wrong byte count for ") + name); return 1; }
     if (ty == ITB_F32) {
         DevTensor t; t.ty = ty; t.n_in = s->n_in; t.n_out = s->n_out; t.bytes = bytes;
         ITB_CUDA_RET(c, cudaMalloc(&t.a, bytes), 1);
@@ -158,6 +179,12 @@ extern "C" int itb_model_set_tensor(itb_model* m, const char* name, uint32_t ty,
         if (it != m->t.end()) { cudaFree(it->second.a); m->bytes -= it->second.bytes; }
         m->t[name] = t; m->bytes += bytes; m->finalized = false;
         return 0;
+    }
+    if (as_fp4) {
+        // a dense NVFP4 matrix: its one-element `.scale` (handed over with the weight, as the GGUF loader does, or set by name)
+        // is kept on the host and applied to the matmul's result
+        if (scale && n_scale >= 1) m->scalars[nm.substr(0, nm.size() - 7) + ".scale"] = scale[0];
+        scale = nullptr; n_scale = 0;
     }
     uint8_t* raw = nullptr;
     ITB_CUDA_RET(c, cudaMalloc(&raw, bytes), 1);
@@ -279,9 +306,22 @@ static bool finalize(itb_model* m) {
         const DevTensor* t = get(n);
         return t ? DevFp4{(const uint8_t*)t->a, (const uint8_t*)t->b, t->scale2, (int)t->n_in, (int)t->n_out, (int)t->e_cnt, (int)t->e_lo} : DevFp4{};
     };
+    // a dense matrix that may be stored as Q8_0 or as NVFP4: one of the two views is filled
+    auto dense = [&](const std::string& n, DevQ8* q, DevFp4* f4, float* sc, bool* has_sc) {
+        const DevTensor* t = get(n);
+        *q = DevQ8{}; *f4 = DevFp4{}; *has_sc = false;
+        if (!t) return;
+        if (t->ty == ITB_NVFP4) {
+            *f4 = DevFp4{(const uint8_t*)t->a, (const uint8_t*)t->b, nullptr, (int)t->n_in, (int)t->n_out, 1, 0};
+            m->dense_fp4 = true;
+            auto it = m->scalars.find(n.substr(0, n.size() - 7) + ".scale");
+            if (it != m->scalars.end()) { *sc = it->second; *has_sc = true; }
+        } else *q = DevQ8{(const int8_t*)t->a, (const uint16_t*)t->b, (int)t->n_in, (int)t->n_out};
+    };
+    m->dense_fp4 = false;
     m->tok_embd = f32("token_embd.weight");
     m->output_norm = vec("output_norm.weight");
-    m->output = q8("output.weight");
+    dense("output.weight", &m->output, &m->output4, &m->output_s, &m->has_output_s);
     m->layers.assign(d.n_layer, DevLayer{});
     for (uint32_t i = 0; i < d.n_layer && ok; ++i) {
         std::string P = "blk." + std::to_string(i) + ".";
@@ -301,8 +341,9 @@ static bool finalize(itb_model* m) {
         }
         L.gate_inp = f32k(P + "ffn_gate_inp.weight"); L.shared_gate_inp = f32k(P + "ffn_gate_inp_shexp.weight");
         L.gate = fp4(P + "ffn_gate_exps.weight"); L.up = fp4(P + "ffn_up_exps.weight"); L.down = fp4(P + "ffn_down_exps.weight");
-        L.shared_gate = q8(P + "ffn_gate_shexp.weight"); L.shared_up = q8(P + "ffn_up_shexp.weight");
-        L.shared_down = q8(P + "ffn_down_shexp.weight");
+        dense(P + "ffn_gate_shexp.weight", &L.shared_gate, &L.shared4[0], &L.shared_s[0], &L.has_shared_s[0]);
+        dense(P + "ffn_up_shexp.weight", &L.shared_up, &L.shared4[1], &L.shared_s[1], &L.has_shared_s[1]);
+        dense(P + "ffn_down_shexp.weight", &L.shared_down, &L.shared4[2], &L.shared_s[2], &L.has_shared_s[2]);
     }
     m->finalized = ok;
     return ok;
@@ -1001,6 +1042,24 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         launches++;
     };
     auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, bool same = false) { gemm_n(w, xq, xs, out, stride, mode, R, same); };
+    // A dense matrix stored as NVFP4 (shared experts, LM head of an NVFP4 file): int8 activations x E2M1 weights in the CPU
+    // order (src/ops/naive.rs:714-734), then the tensor's second scale on the result (src/model/qwen35.rs:1668-1682).
+    auto gemm_fp4d = [&](const DevFp4& w, const int8_t* xq, const float* xs, float* out, int rows, bool has_s, float sc) {
+        if (rows >= 2 && gemm_smem(w.n_in) <= 200 * 1024) {
+            set_smem((const void*)k_gemm_fp4, gemm_smem(w.n_in));
+            k_gemm_fp4<<<dim3((w.n_out + MMA_ROWS - 1) / MMA_ROWS, (rows + MMA_TOK - 1) / MMA_TOK), 256, gemm_smem(w.n_in), st>>>(
+                w.nib, w.sc, w.n_in, w.n_out, xq, xs, rows, out, (size_t)w.n_out, sc, has_s ? 1 : 0);
+            launches++;
+            return;
+        }
+        const int nb = w.n_in / 32, nsb = w.n_in / 16, gsh = lanes_shift(nb), nw = 8;
+        const int gx = std::max(1, std::min((w.n_out + 31) / 32, 2 * sms));
+        const size_t smem = (size_t)w.n_in + (size_t)nb * 4 + (size_t)nw * terms_floats(4, gsh, nsb) * 4;
+        set_smem((const void*)k_matmul_fp4, smem);
+        k_matmul_fp4<<<dim3(gx, rows), nw * 32, smem, st>>>(w, nullptr, 1, 0, xq, xs, out);
+        launches++;
+        if (has_s) { const size_t n = (size_t)rows * w.n_out; k_scale<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, n, sc); launches++; }
+    };
     auto f32mm = [&](const DevF32& w, const float* x, float* out) {
         if (!c->exact && w.n_in % 512 == 0 && w.n_in <= 4096) {
             const dim3 g((w.n_out + 7) / 8, (R + F32_TOK - 1) / F32_TOK);
@@ -1119,8 +1178,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         }
         // routed FFN
         k_norm_quant<<<R, 256, smem_nq, st>>>(e->x, L.ffn_norm, H, d.rms_eps, e->xn, e->xq, e->xs); launches++;
-        gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
-        gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, true);
+        if (L.shared4[0].nib) gemm_fp4d(L.shared4[0], e->xq, e->xs, e->sg, R, L.has_shared_s[0], L.shared_s[0]);
+        else gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
+        if (L.shared4[1].nib) gemm_fp4d(L.shared4[1], e->xq, e->xs, e->su, R, L.has_shared_s[1], L.shared_s[1]);
+        else gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, !L.shared4[0].nib);
         f32mm(L.gate_inp, e->xn, e->router);
         f32mm(L.shared_gate_inp, e->xn, e->shlogit);
         {
@@ -1247,7 +1308,8 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 o_src = e->ep->o_mine;
             }
             k_shared_act_rows<<<R, 128, 0, st>>>(e->sg, e->su, d.shared_ff, e->sq, e->ss); launches++;
-            gemm(L.shared_down, e->sq, e->ss, e->shd, H, 0);
+            if (L.shared4[2].nib) gemm_fp4d(L.shared4[2], e->sq, e->ss, e->shd, R, L.has_shared_s[2], L.shared_s[2]);
+            else gemm(L.shared_down, e->sq, e->ss, e->shd, H, 0);
             const size_t total = (size_t)R * H;
             k_moe_finish_rows<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(e->x, H, o_src, wts, K, e->shd, e->shlogit, total); launches++;
         }
@@ -1258,7 +1320,11 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     if (n_seq > 1) {
         // several sequences: one pass over the output matrix for all of them
         k_norm_quant<<<n_seq, 256, smem_nq, st>>>(xl, m->output_norm, H, d.rms_eps, nullptr, e->xq, e->xs); launches++;
-        gemm_n(m->output, e->xq, e->xs, e->logits, d.n_vocab, 0, n_seq);
+        if (m->output4.nib) gemm_fp4d(m->output4, e->xq, e->xs, e->logits, n_seq, m->has_output_s, m->output_s);
+        else gemm_n(m->output, e->xq, e->xs, e->logits, d.n_vocab, 0, n_seq);
+    } else if (m->output4.nib) {
+        k_norm_quant<<<1, 256, smem_nq, st>>>(xl, m->output_norm, H, d.rms_eps, nullptr, e->xq, e->xs); launches++;
+        gemm_fp4d(m->output4, e->xq, e->xs, e->logits, 1, m->has_output_s, m->output_s);
     } else {
         InProj hp{};
         hp.x = xl; hp.x_stride = H; hp.norm_w = m->output_norm; hp.eps = d.rms_eps; hp.n_embd = H;
@@ -1551,7 +1617,7 @@ static bool mega_prepare(itb_engine* e) {
     const itb_model_dims& d = m->d;
     auto no = [&](const char* why) { e->mega_why = why; return false; };
     if (!(getenv("ITB_MEGA") && atoi(getenv("ITB_MEGA")) == 1)) return no("not asked for (ITB_MEGA=1 selects the one-kernel step)");
-    if (e->B != 1 || e->ep || e->tier) return no("single-sequence plain engines only");
+    if (e->B != 1 || e->ep || e->tier || e->m->dense_fp4) return no("single-sequence plain engines only");
     const int H = d.n_embd, sk = d.ssm_d_state, n_k = d.ssm_n_group, n_v = d.ssm_dt_rank;
     const int key_dim = sk * n_k, vd = d.ssm_d_inner, cd = 2 * key_dim + vd;
     const int qd = d.head_dim * d.n_head, kvd = d.head_dim * d.n_head_kv, ff = d.expert_ff, sff = d.shared_ff, K = d.n_expert_used;
@@ -1703,7 +1769,7 @@ static bool ensure_graph(itb_engine* e) {
     cudaStream_t st = c->stream;
     // one eager step's worth of attribute set-up happens inside enqueue_step; capture it once
     if (cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal) != cudaSuccess) return itb_fail_msg(c, "engine: cannot begin capture");
-    if (e->B == 1 && !e->tier) enqueue_step(e, st);   // expert-parallel engines too: the step gathers and scatters around its expert kernels
+    if (e->B == 1 && !e->tier && !e->m->dense_fp4) enqueue_step(e, st);   // expert-parallel engines too: the step gathers and scatters around its expert kernels
     else e->launches_per_step = enqueue_rows(e, st, (int)e->B, 1, e->tokens);
     cudaError_t err = cudaStreamEndCapture(st, &e->graph);
     if (err != cudaSuccess) return itb_fail(c, "engine: capture", err);
@@ -1792,7 +1858,7 @@ static bool run_steps(itb_engine* e, uint32_t steps, bool timed) {
             cudaError_t err = cudaGraphLaunch(e->exec, c->stream);
             if (err != cudaSuccess) { ep_abort(e); return itb_fail(c, "engine: graph launch", err); }
         } else {
-            if (e->B == 1 && !e->tier) enqueue_step(e, c->stream);
+            if (e->B == 1 && !e->tier && !e->m->dense_fp4) enqueue_step(e, c->stream);
             else e->launches_per_step = enqueue_rows(e, c->stream, (int)e->B, 1, e->tokens);
             if (!c->error.empty()) { ep_abort(e); return false; }
         }
@@ -1954,7 +2020,7 @@ extern "C" int itb_engine_read_ssm_state(itb_engine* e, uint32_t seq, uint32_t i
 extern "C" int itb_engine_profile_step(itb_engine* e, const uint32_t* tokens, itb_kernel_stat* out, size_t cap, size_t* n_out) {
     itb_ctx* c = e->c;
     cudaStream_t st = c->stream;
-    if (e->B != 1 || e->ep || e->tier) { itb_fail_msg(c, "profile_step: plain single-sequence engines only"); return 1; }
+    if (e->B != 1 || e->ep || e->tier || e->m->dense_fp4) { itb_fail_msg(c, "profile_step: plain single-sequence engines only"); return 1; }
     if (!tokens_in_range(e, tokens, e->B) || !steps_ready(e, 1)) return 1;  // function attributes are set during capture
     ITB_CUDA_RET(c, cudaMemcpyAsync(e->tokens, tokens, e->B * 4, cudaMemcpyHostToDevice, st), 1);
     StepProf prof;

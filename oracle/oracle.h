@@ -153,6 +153,8 @@ struct LayerWeights {
     // routed FFN
     Weights gate_inp, shared_gate, shared_up, shared_down, shared_gate_inp;
     Experts gate, up, down;
+    // An NVFP4 file's second scale per shared-expert matmul (gate, up, down), applied to its output (src/model/qwen35.rs:1668-1682)
+    float shared_s[3] = {1.0f, 1.0f, 1.0f}; bool has_shared_s[3] = {false, false, false};
 };
 
 struct ModelWeights {
@@ -160,6 +162,7 @@ struct ModelWeights {
     Weights tok_embd;  // F32 [n_vocab][n_embd]
     const float* output_norm;
     Weights output;
+    float output_s = 1.0f; bool has_output_s = false;   // `output.scale`, the LM head's second scale, NVFP4 only (src/model/qwen35.rs:736-737, :1118)
     std::vector<LayerWeights> layers;
 };
 

@@ -36,6 +36,19 @@ Experts E(OrcModel& m, const std::string& name, size_t n_in, size_t n_out, size_
                    it == m.scales.end() ? nullptr : it->second.data()};
 }
 const float* V(OrcModel& m, const std::string& name) { return (const float*)m.data.at(name).data(); }
+// A dense matrix that a file may carry as Q8_0 or as NVFP4 (shared experts, LM head): told apart by its byte count.
+Weights WQ(OrcModel& m, const std::string& name, size_t n_in, size_t n_out) {
+    const auto& d = m.data.at(name);
+    const uint32_t ty = d.size() == n_in * n_out / 64 * 36 ? T_NVFP4 : T_Q8_0;
+    return Weights{d.data(), ty, n_in, n_out};
+}
+// `<weight>.scale`, one f32 (src/model/mod.rs:351-361): true and *v set when the model carries it.
+bool scalar(OrcModel& m, const std::string& name, float* v) {
+    auto it = m.data.find(name);
+    if (it == m.data.end() || it->second.size() != 4) return false;
+    std::memcpy(v, it->second.data(), 4);
+    return true;
+}
 
 void link(OrcModel& m) {
     const auto& d = m.dims;
@@ -49,7 +62,8 @@ void link(OrcModel& m) {
     w.cfg = c;
     w.tok_embd = W(m, "token_embd.weight", T_F32, c.n_embd, c.n_vocab);
     w.output_norm = V(m, "output_norm.weight");
-    w.output = W(m, "output.weight", T_Q8_0, c.n_embd, c.n_vocab);
+    w.output = WQ(m, "output.weight", c.n_embd, c.n_vocab);
+    w.has_output_s = scalar(m, "output.scale", &w.output_s);
     w.layers.assign(c.n_layer, LayerWeights{});
     for (size_t i = 0; i < c.n_layer; ++i) {
         std::string P = "blk." + std::to_string(i) + ".";
@@ -78,9 +92,12 @@ void link(OrcModel& m) {
         L.gate = E(m, P + "ffn_gate_exps.weight", c.n_embd, c.expert_ff, c.n_expert);
         L.up = E(m, P + "ffn_up_exps.weight", c.n_embd, c.expert_ff, c.n_expert);
         L.down = E(m, P + "ffn_down_exps.weight", c.expert_ff, c.n_embd, c.n_expert);
-        L.shared_gate = W(m, P + "ffn_gate_shexp.weight", T_Q8_0, c.n_embd, c.shared_ff);
-        L.shared_up = W(m, P + "ffn_up_shexp.weight", T_Q8_0, c.n_embd, c.shared_ff);
-        L.shared_down = W(m, P + "ffn_down_shexp.weight", T_Q8_0, c.shared_ff, c.n_embd);
+        L.shared_gate = WQ(m, P + "ffn_gate_shexp.weight", c.n_embd, c.shared_ff);
+        L.shared_up = WQ(m, P + "ffn_up_shexp.weight", c.n_embd, c.shared_ff);
+        L.shared_down = WQ(m, P + "ffn_down_shexp.weight", c.shared_ff, c.n_embd);
+        L.has_shared_s[0] = scalar(m, P + "ffn_gate_shexp.scale", &L.shared_s[0]);
+        L.has_shared_s[1] = scalar(m, P + "ffn_up_shexp.scale", &L.shared_s[1]);
+        L.has_shared_s[2] = scalar(m, P + "ffn_down_shexp.scale", &L.shared_s[2]);
         L.shared_gate_inp = W(m, P + "ffn_gate_inp_shexp.weight", T_F32, c.n_embd, 1);
     }
     m.linked = true;

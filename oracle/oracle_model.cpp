@@ -79,8 +79,12 @@ static void moe_batch(const Config& c, const LayerWeights& L, size_t at, size_t 
     size_t sff = n * c.shared_ff;
     matmul(L.shared_gate, x, n * nd, s.e_gate.data());
     matmul(L.shared_up, x, n * nd, s.e_up.data());
+    // src/model/qwen35.rs:1668-1682: an NVFP4 file's second scale per matmul, applied to its output before anything reads it
+    if (L.has_shared_s[1]) scale(s.e_up.data(), sff, L.shared_s[1]);
+    if (L.has_shared_s[0]) scale(s.e_gate.data(), sff, L.shared_s[0]);
     silu_mul(s.e_gate.data(), s.e_up.data(), sff);
     matmul(L.shared_down, s.e_gate.data(), sff, s.e_out.data());
+    if (L.has_shared_s[2]) scale(s.e_out.data(), n * nd, L.shared_s[2]);
     moe_finish(s.ffn_out.data(), at, nd, s.o_all.data(), r, s.e_out.data(), s.shexp_logit.data(), 0);
 }
 
@@ -133,6 +137,7 @@ int Model::forward(const uint32_t* tokens, size_t n, size_t start_pos, KvCache& 
     gather_chunks(s.x.data(), nd, nd, (n - 1) * nd, s.last.data(), nd);
     rms_norm(s.last.data(), nd, w.output_norm, nd, c.rms_eps, s.final_norm.data());
     matmul(w.output, s.final_norm.data(), nd, logits);
+    if (w.has_output_s) scale(logits, c.n_vocab, w.output_s);   // src/model/qwen35.rs:1117-1120
     return 0;
 }
 

@@ -61,10 +61,19 @@ def write(path, kv, tensors, alignment=32):
             f.write(b)
 
 
-def from_oracle(path, dims, oracle):
-    """Every tensor of an oracle model (its specs: name, type id, shape, block bytes) into a GGUF file."""
+def from_oracle(path, dims, oracle, override=None):
+    """Every tensor of an oracle model (its specs: name, type id, shape, block bytes) into a GGUF file. override: name ->
+    (ggml type id, bytes, second scale or None) for tensors written in another storage type than the spec's (an NVFP4
+    shared expert or LM head with its one-element `.scale`)."""
     tensors = []
     for s in oracle.specs:
+        if override and s["name"] in override:
+            ty, data, sc = override[s["name"]]
+            shape = [s["n_in"], s["n_out"]]
+            tensors.append((s["name"], ty, shape, np.asarray(data).tobytes()))
+            if sc is not None:
+                tensors.append((s["name"].replace(".weight", ".scale"), GGML["F32"], [1], np.asarray([sc], np.float32).tobytes()))
+            continue
         data, sc = oracle.tensor(s["name"])
         if s["n_expert"] > 1 or s["has_scale"]:
             shape = [s["n_in"], s["n_out"], s["n_expert"]]
