@@ -259,6 +259,11 @@ int  itb_attend_decode_noalloc(void* stream, const float* q_dev, const uint16_t*
  * tflops_out: dense TFLOP/s, best of `reps` launches by CUDA events; status_out: 0 verified, 1 a (bounded) wait ran out,
  * 2 accumulators wrong; mma_cycles_out: SM cycles per MMA on the slowest block. Returns non-zero on a call error. */
 int  itb_fp4_ceiling(itb_ctx*, int n, int iters, int reps, double* tflops_out, int* status_out, double* mma_cycles_out);
+/* How an expert-parallel engine's one-token step moves rows between ranks: 2 = through peer memory (each rank stores its
+ * quantised row and router logits into every rank's CUDA-IPC-mapped region and the served picks' output rows into their
+ * owner's, with one flag per (layer, peer) and bounded waits; set up at creation when every rank could map every peer, and
+ * ITB_EP_P2P is not 0), 1 = NCCL all-gather + reduce-scatter per layer, 0 = the engine is not expert parallel. */
+int  itb_engine_ep_transport(itb_engine*);
 /* Expert parallelism, many-row passes: the send/receive plan of the packed all-to-all that carries every (row, pick) pair to
  * the rank holding its expert and its output row back (the reference places experts by contiguous range, src/ops/mod.rs:1024-1048;
  * it has no multi-GPU path of its own). cnt[s * world + d] = pairs rank s sends to rank d (every rank has the whole matrix

@@ -461,6 +461,16 @@ struct EpState {
     int32_t* owner = nullptr; int* own_off = nullptr; int* own_list = nullptr;
     int* cnt_dev = nullptr; int* cnt_host = nullptr;                        // [W][W]: cnt[s][d] = pairs rank s sends to rank d
     size_t a2a_cap = 0;
+    // the one-token step over peer memory (NVLink loads and stores instead of two small NCCL collectives per layer): one
+    // region per rank, the same layout on every rank -- per layer the rows all ranks push here (quantised activation, its
+    // scales, router logits), the output rows of this rank's picks that the serving ranks store here, and one flag per
+    // (layer, peer) for each direction; peers' regions are opened through CUDA IPC
+    bool p2p = false;
+    unsigned char* region = nullptr; size_t region_bytes = 0;
+    unsigned char* peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // peer[rank] = region
+    unsigned char** peer_dev = nullptr;      // the same table on the device
+    unsigned* seq = nullptr;                 // device: the step number the flags carry
+    size_t g_slot = 0, g_layer = 0, o_layer = 0, off_g = 0, off_o = 0, off_gf = 0, off_of = 0;
 };
 
 // ---- packed all-to-all dispatch/combine (expert parallel, eager many-row passes) ----
@@ -499,6 +509,53 @@ __global__ void k_ep_unsort(const float* o_back, const int* list, int n_pairs, i
     if (i >= (size_t)n_pairs * (H / 4)) return;
     const int slot = (int)(i / (H / 4)), c4 = (int)(i % (H / 4));
     ((float4*)(o_mine + (size_t)list[slot] * H))[c4] = ((const float4*)(o_back + (size_t)slot * H))[c4];
+}
+
+// ---- the expert-parallel one-token step over peer memory ----
+__global__ void k_ep_tick(unsigned* seq) { if (threadIdx.x == 0 && blockIdx.x == 0) seq[0] += 1; }
+// This rank's row of layer il -- quantised activation, scales, router logits -- stored into every rank's region (its own
+// included), then that rank's flag for (layer, this rank) set to the step number with system-scope release. A block per
+// destination rank. The predecessor produced the row: wait for it (programmatic dependent launch) before reading.
+__global__ void __launch_bounds__(256) k_ep_push(const int8_t* xq, const float* xs, const float* router, int H, int E, unsigned char* const* peer,
+                                                 size_t off_xq, size_t off_xs, size_t off_router, size_t off_flag, const unsigned* seq) {
+    pdl_trigger(); pdl_wait();
+    unsigned char* base = peer[blockIdx.x];
+    const int nq = H / 16, ns = H / 32 / 4, nr = E / 4;           // 16-byte pieces of the three parts
+    for (int i = threadIdx.x; i < nq + ns + nr; i += blockDim.x) {
+        if (i < nq) ((uint4*)(base + off_xq))[i] = ((const uint4*)xq)[i];
+        else if (i < nq + ns) ((uint4*)(base + off_xs))[i - nq] = ((const uint4*)xs)[i - nq];
+        else ((uint4*)(base + off_router))[i - nq - ns] = ((const uint4*)router)[i - nq - ns];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* flag = (unsigned*)(base + off_flag);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq[0]) : "memory");
+    }
+}
+// After the down projection stored this rank's served picks into their owners' regions: tell every rank so. The stores
+// came from the predecessor kernel; its completion (waited for here) made them visible.
+__global__ void k_ep_signal(unsigned char* const* peer, size_t off_flag, const unsigned* seq) {
+    pdl_trigger(); pdl_wait();
+    __threadfence_system();
+    unsigned* flag = (unsigned*)(peer[blockIdx.x] + off_flag);
+    if (threadIdx.x == 0) asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq[0]) : "memory");
+}
+// k_moe_finish_rows for the one local row, once every rank has signalled (bounded wait): weighted sum of the picks' rows in
+// pick order, the sigmoid-gated shared expert, the residual (src/ops/mod.rs:1134-1190). The rows were written by other GPUs:
+// read past L1.
+__global__ void __launch_bounds__(256) k_ep_finish(float* x, int n, const float* o, const float* wts, int n_used, const float* shared, const float* logit,
+                                                   const unsigned* flags, int world, const unsigned* seq, int* err) {
+    pdl_trigger(); pdl_wait();
+    if (threadIdx.x < world) ep_wait_flag(flags + threadIdx.x, seq[0], err);
+    __syncthreads();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = sigmoid_f(logit[0]);
+    float v = 0.0f;
+    for (int k = 0; k < n_used; ++k) v += wts[k] * __ldcg(o + (size_t)k * n + i);
+    v += shared[i] * g;
+    x[i] += v;
 }
 
 // Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
@@ -721,6 +778,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         attrs_set = true;
     }
     if (prof) prof->mark(-1, 0, st);
+    const bool p2p = e->ep && e->ep->p2p;
+    if (p2p) { k_ep_tick<<<1, 32, 0, st>>>(e->ep->seq); launches++; }    // the step number the peers' flags will carry
     launch_k(pdl, k_embed, B, 256, 0, st, m->tok_embd.w, H, e->tokens, e->x); MARK(KC_EMBED, (uint64_t)B * H * 8);
     for (uint32_t il = 0; il < d.n_layer; ++il) {
         const DevLayer& L = m->layers[il];
@@ -818,7 +877,20 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
         g.shared_row = -1;
-        if (e->ep) {
+        if (p2p) {
+            // every rank's quantised row and router logits (B is 1 here), pushed by each rank into every rank's region over NVLink;
+            // k_moe_glu's blocks for row r wait for rank r's flag. No NCCL call, no zero-filled buffer.
+            EpState* q = e->ep;
+            const size_t base = q->off_g + (size_t)il * q->g_layer, o_xq = base, o_xs = base + (size_t)W * H, o_r = o_xs + (size_t)W * (H / 32) * 4;
+            launch_k(pdl, k_ep_push, dim3(W), dim3(256), 0, st, (const int8_t*)e->xq, (const float*)e->xs, (const float*)e->router, (int)H, (int)d.n_expert,
+                     (unsigned char* const*)q->peer_dev, o_xq + (size_t)q->rank * H, o_xs + (size_t)q->rank * (H / 32) * 4, o_r + (size_t)q->rank * d.n_expert * 4,
+                     q->off_gf + ((size_t)il * 8 + q->rank) * 4, (const unsigned*)q->seq);
+            launches++;
+            g.router = (const float*)(q->region + o_r); g.xq = (const int8_t*)(q->region + o_xq); g.xs = (const float*)(q->region + o_xs);
+            g.shared_row = q->rank; g.ids_out = q->gids; g.w_out = q->gw;
+            g.wait_flags = (const unsigned*)(q->region + q->off_gf + (size_t)il * 8 * 4); g.wait_seq = q->seq; g.err = e->err;
+        }
+        if (e->ep && !p2p) {
             // every rank's quantised row and router logits (B is 1 here): the kernels below then serve the picks that name a local expert
             NcclApi& nc = nccl_api();
             nc.GroupStart();
@@ -838,6 +910,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         w.hq = e->hq; w.hs = e->hs; w.n_used = d.n_expert_used; w.ff = d.expert_ff; w.ids = g.ids_out; w.wts = g.w_out; w.down = L.down;
         w.sq = e->sq; w.ss = e->ss; w.sff = d.shared_ff; w.shared_down = L.shared_down; w.logit = e->shlogit; w.x = e->x; w.x_stride = H;
         if (e->ep) { w.o_pairs = e->o_all; w.own_row = e->ep->rank; w.shd = e->shd; }
+        if (p2p) for (int r = 0; r < W; ++r) w.o_rows[r] = (float*)(e->ep->peer[r] + e->ep->off_o + (size_t)il * e->ep->o_layer);
         {
             int slots = 32 >> lanes_shift(d.expert_ff / 32), need = ((int)d.n_expert_used + slots - 1) / slots;
             int rp = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
@@ -854,7 +927,18 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             else if (rp == 4) launch_k(pdl, k_moe_down<4>, grid, TPB, smem_d, st, w);
             else launch_k(pdl, k_moe_down<8>, grid, TPB, smem_d, st, w);
         }
-        if (e->ep) {
+        if (p2p) {
+            // the served picks' rows were stored straight into their owners' regions: tell every rank, then combine this rank's
+            // own row once every rank has told it (pick order, gated shared expert, residual: as k_moe_down does on one GPU)
+            EpState* q = e->ep;
+            launch_k(pdl, k_ep_signal, dim3(W), dim3(32), 0, st, (unsigned char* const*)q->peer_dev, q->off_of + ((size_t)il * 8 + q->rank) * 4, (const unsigned*)q->seq);
+            launch_k(pdl, k_ep_finish, dim3((H + 255) / 256), dim3(256), 0, st, e->x, (int)H, (const float*)(q->region + q->off_o + (size_t)il * q->o_layer),
+                     (const float*)(q->gw + (size_t)q->rank * d.n_expert_used), (int)d.n_expert_used, (const float*)e->shd, (const float*)e->shlogit,
+                     (const unsigned*)(q->region + q->off_of + (size_t)il * 8 * 4), W, (const unsigned*)q->seq, e->err);
+            launches += 2;
+            cudaMemcpyAsync(e->route_ids + (size_t)il * e->R * d.n_expert_used, q->gids + (size_t)q->rank * d.n_expert_used, d.n_expert_used * 4, cudaMemcpyDeviceToDevice, st);
+            cudaMemcpyAsync(e->route_w + (size_t)il * e->R * d.n_expert_used, q->gw + (size_t)q->rank * d.n_expert_used, d.n_expert_used * 4, cudaMemcpyDeviceToDevice, st);
+        } else if (e->ep) {
             // each pick's output row comes home (exactly one rank wrote it: an exact sum), then the pick-order combine, the
             // gated shared expert and the residual add, as k_moe_down does them on one GPU
             const size_t KH = (size_t)d.n_expert_used * H;
@@ -991,6 +1075,61 @@ static bool ep_a2a_prepare(itb_engine* e) {
     }
     q->a2a_cap = cap;
     return true;
+}
+
+// The region and the peers' mappings for the one-token step over peer memory. Every rank runs this at engine creation, in
+// step: allocate, exchange the IPC handles through the communicator, open the peers', then agree (one more all-gather) that
+// EVERY rank succeeded -- otherwise all of them keep the NCCL form. ITB_EP_P2P=0 keeps the NCCL form too.
+static void ep_p2p_setup(itb_engine* e) {
+    EpState* q = e->ep;
+    itb_ctx* c = e->c;
+    NcclApi& nc = nccl_api();
+    const itb_model_dims& d = e->m->d;
+    const int W = q->world;
+    if (e->B != 1 || W > 8 || d.n_embd % 128 || d.n_expert % 4 || (getenv("ITB_EP_P2P") && atoi(getenv("ITB_EP_P2P")) == 0)) return;
+    const size_t H = d.n_embd, E = d.n_expert, K = d.n_expert_used, NL = d.n_layer;
+    q->g_slot = 0;
+    q->g_layer = ((size_t)W * (H + H / 32 * 4 + E * 4) + 127) & ~(size_t)127;      // per layer: [W][H] int8 | [W][H/32] f32 | [W][E] f32
+    q->o_layer = K * H * 4;
+    q->off_g = 0; q->off_o = q->off_g + NL * q->g_layer; q->off_gf = q->off_o + NL * q->o_layer; q->off_of = q->off_gf + NL * 8 * 4;
+    q->region_bytes = q->off_of + NL * 8 * 4;
+    bool ok = cudaMalloc(&q->region, q->region_bytes) == cudaSuccess && cudaMalloc(&q->seq, 4) == cudaSuccess && cudaMalloc(&q->peer_dev, 8 * sizeof(void*)) == cudaSuccess;
+    cudaIpcMemHandle_t mine{}, *all_h = nullptr; unsigned char* hbuf = nullptr; int* flags_dev = nullptr;
+    std::vector<cudaIpcMemHandle_t> handles(W);
+    std::vector<int> flags(W, 0);
+    if (ok) {
+        cudaMemsetAsync(q->region, 0, q->region_bytes, c->stream); cudaMemsetAsync(q->seq, 0, 4, c->stream);
+        ok = cudaIpcGetMemHandle(&mine, q->region) == cudaSuccess;
+    }
+    ok = cudaMalloc(&hbuf, (size_t)(W + 1) * sizeof mine) == cudaSuccess && cudaMalloc(&flags_dev, (size_t)(W + 1) * 4) == cudaSuccess && ok;
+    // the handle exchange is a collective: every rank enters it whatever happened before (a failed rank sends zeros)
+    if (hbuf && flags_dev) {
+        cudaMemcpyAsync(hbuf + (size_t)W * sizeof mine, &mine, sizeof mine, cudaMemcpyHostToDevice, c->stream);
+        nc.AllGather(hbuf + (size_t)W * sizeof mine, hbuf, sizeof mine, NcclApi::Int8, q->comm, c->stream);
+        cudaMemcpyAsync(handles.data(), hbuf, (size_t)W * sizeof mine, cudaMemcpyDeviceToHost, c->stream);
+        if (cudaStreamSynchronize(c->stream) != cudaSuccess) ok = false;
+        (void)all_h;
+        for (int r = 0; r < W && ok; ++r) {
+            if (r == q->rank) { q->peer[r] = q->region; continue; }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, handles[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+            q->peer[r] = (unsigned char*)ptr;
+        }
+        int okf = ok ? 1 : 0;
+        cudaMemcpyAsync(flags_dev + W, &okf, 4, cudaMemcpyHostToDevice, c->stream);
+        nc.AllGather(flags_dev + W, flags_dev, 1, NcclApi::Int32, q->comm, c->stream);
+        cudaMemcpyAsync(flags.data(), flags_dev, (size_t)W * 4, cudaMemcpyDeviceToHost, c->stream);
+        if (cudaStreamSynchronize(c->stream) != cudaSuccess) ok = false;
+        for (int r = 0; r < W; ++r) ok = ok && flags[r] == 1;
+    } else ok = false;       // (a rank that could not even allocate the exchange buffers cannot take part: with identical ranks this is all or none)
+    cudaFree(hbuf); cudaFree(flags_dev);
+    if (ok) {
+        cudaMemcpy(q->peer_dev, q->peer, 8 * sizeof(void*), cudaMemcpyHostToDevice);
+        q->p2p = true;
+    } else {
+        for (int r = 0; r < W; ++r) if (r != q->rank && q->peer[r]) { cudaIpcCloseMemHandle(q->peer[r]); q->peer[r] = nullptr; }
+        cudaFree(q->region); cudaFree(q->seq); cudaFree(q->peer_dev); q->region = nullptr; q->seq = nullptr; q->peer_dev = nullptr;
+    }
 }
 
 static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_tok, const int32_t* tok_rows) {
@@ -1518,8 +1657,11 @@ extern "C" int itb_engine_create_ep(itb_model* m, uint32_t n_ctx, uint32_t n_seq
         itb_fail_msg(c, (std::string("expert-parallel engine: ncclCommInitRank failed: ") + (nc.GetErrorString ? nc.GetErrorString(rc) : "?")).c_str());
         itb_engine_destroy(e); *out = nullptr; return 1;
     }
+    ep_p2p_setup(e);
     return 0;
 }
+
+extern "C" int itb_engine_ep_transport(itb_engine* e) { return !e->ep ? 0 : e->ep->p2p ? 2 : 1; }
 
 static void drop_graph(itb_engine* e) {
     if (e->exec) cudaGraphExecDestroy(e->exec);
@@ -1535,6 +1677,8 @@ extern "C" void itb_engine_destroy(itb_engine* e) {
         EpState* q = e->ep;
         if (q->comm && !q->broken) nccl_api().CommDestroy(q->comm);
         cudaFreeHost(q->agree_host);
+        for (int r = 0; r < q->world && r < 8; ++r) if (r != q->rank && q->peer[r]) cudaIpcCloseMemHandle(q->peer[r]);
+        cudaFree(q->region); cudaFree(q->seq); cudaFree(q->peer_dev);
         cudaFree(q->sxq); cudaFree(q->sxs); cudaFree(q->sids); cudaFree(q->rxq); cudaFree(q->rxs); cudaFree(q->rids); cudaFree(q->o_back); cudaFree(q->owner);
         cudaFree(q->own_off); cudaFree(q->own_list); cudaFree(q->cnt_dev); if (q->cnt_host) cudaFreeHost(q->cnt_host);
         delete q; e->ep = nullptr;
@@ -1781,9 +1925,13 @@ static bool ensure_graph(itb_engine* e) {
 // The one-kernel step's waits are bounded: a wait that ran out stores (stage << 8) | reason in the status word and every
 // block returns. Turn it into the sticky error and put the grid barrier's counters back.
 static bool check_flag(itb_engine* e) {
-    if (e->mega != 1 && !e->c->exact) return true;
+    if (e->mega != 1 && !e->c->exact && !(e->ep && e->ep->p2p)) return true;
     int f = 0;
     if (cudaMemcpy(&f, e->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return itb_fail_msg(e->c, "engine: cannot read the device status word");
+    if (f == EP_WAIT_FAIL) {
+        cudaMemset(e->err, 0, 4);
+        return itb_fail_msg(e->c, "expert-parallel engine: a peer's rows never arrived in this rank's memory (bounded wait ran out)");
+    }
     if (f == F32S_FAIL) {
         cudaMemset(e->err, 0, 4);
         return itb_fail_msg(e->c, "engine: an F32 weight row never arrived in its shared-memory ring (bounded wait ran out)");

@@ -452,8 +452,23 @@ struct MoeGlu {
     int8_t* sq; float* ss;                          // [B][sff] int8, [B][sff/32]: silu(sg)*su quantised
     int32_t* ids_out; float* w_out;
     int shared_row;                                 // -1: every row has a shared expert activation; r: only row r, held at index 0 (expert-parallel step)
+    // expert-parallel step over peer memory: row b's quantised activation and router logits were stored into this GPU's memory
+    // by rank b; its flag wait_flags[b] reaches *wait_seq when they are all there (bounded wait; *err set if it runs out)
+    const unsigned* wait_flags; const unsigned* wait_seq; int* err;
     int tl_slot;
 };
+constexpr int EP_WAIT_FAIL = 0x7002;
+// Bounded wait of one thread for a flag another GPU stores (system scope); the caller synchronises its block afterwards.
+__device__ __forceinline__ void ep_wait_flag(const unsigned* flag, unsigned seq, int* err) {
+    if (err && *(volatile int*)err) return;      // a wait of this step already ran out: the step is lost, do not wait again
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v == seq) return;
+        if (clock64() - t0 > 10000000000ll) { if (err) atomicExch(err, EP_WAIT_FAIL); return; }     // about five seconds: ranks may enter a step that far apart
+    }
+}
 __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
     extern __shared__ __align__(16) unsigned char smem[];
     __shared__ int32_t s_ids[16];
@@ -480,6 +495,10 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
             if (lane == 0) p.ss[sb * (p.sff / 32) + (unit - n_units)] = dq;
         }
         return;
+    }
+    if (p.wait_flags) {
+        if (tid == 0) ep_wait_flag(p.wait_flags + b, *p.wait_seq, p.err);
+        __syncthreads();
     }
     float* probs = (float*)smem;                  // [n_expert rounded up to 32]
     int8_t* xq = (int8_t*)(probs + ((p.n_expert + 31) & ~31));
@@ -633,6 +652,7 @@ struct MoeDown {
     // o_pairs[(b * n_used + k)][n_out] (others are left as they are: zero), and only row own_row (activation at index 0)
     // gets its shared-expert row into shd; no combine and no residual here.
     float* o_pairs; int own_row; float* shd;
+    float* o_rows[8];                               // non-null: row b's picks go to o_rows[b][k][n_out] (rank b's memory) instead of o_pairs
     int tl_slot;
 };
 template <int RP, bool PAIRS = false>
@@ -706,8 +726,10 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_down(MoeDown p) {
                     [&](int, float v) { p.shd[row] = v; });
             }
             __syncwarp();
-            if (lane < p.n_used && s_el[lane] >= 0)
-                p.o_pairs[((size_t)b * p.n_used + lane) * n_out + row] = has_s ? outv[lane] * s2k : outv[lane];
+            if (lane < p.n_used && s_el[lane] >= 0) {
+                float* orow = p.o_rows[0] ? p.o_rows[b] + (size_t)lane * n_out : p.o_pairs + ((size_t)b * p.n_used + lane) * n_out;
+                orow[row] = has_s ? outv[lane] * s2k : outv[lane];
+            }
             __syncwarp();
             continue;
         }

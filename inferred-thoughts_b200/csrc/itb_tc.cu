@@ -336,9 +336,10 @@ struct TcGemm {
 __device__ __forceinline__ void tc_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-// grid (max tiles, n_out / 128); block 192: warps 0-3 epilogue (tensor-memory lane quarter = warp), warp 4 producer, warp 5 MMA.
+// grid (max tiles, n_out / 128); block 320: warps 0-7 epilogue (tensor-memory lane quarter = warp % 4, column half = warp / 4),
+// warp 8 producer, warp 9 MMA.
 template <bool GLU>
-__global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
+__global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc;
     __shared__ uint32_t s_tmem;
@@ -362,7 +363,7 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (wid == 5) {
+    if (wid == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem(&s_tmem)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -375,7 +376,7 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
     // tensor memory: D_g at 0, D_u at 128, scale factors from 256: per stage slot 48 columns (SFA_g 16, SFA_u 16, SFB 16)
     const uint32_t d_g = tm, d_u = tm + 128, sf0 = tm + 256;
     bool ok = true;
-    if (wid == 4 && lane == 0) {
+    if (wid == 8 && lane == 0) {
         const size_t w_tile = ((size_t)el * (p.n_out / TC_M) + mt) * kbs;
         for (int st = 0; st < n_stage && ok; ++st) {
             const int s = st % TC_STAGES;
@@ -395,7 +396,7 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
             tc_bulk(dst + o_sfb, p.b_sf + ((size_t)t.sf_off + kb0) * 512, sf_bytes, full);
         }
         if (!ok) atomicCAS(p.status, 0, 3);
-    } else if (wid == 5 && lane == 0) {
+    } else if (wid == 9 && lane == 0) {
         const uint32_t idesc = tc_idesc_fp4(TC_M, t.npad);
         // descriptors of stage slot 0; a slot or K block further on only moves the 14-bit start-address field (address >> 4), which
         // cannot carry out of it (shared memory ends below 256 KB), so the low words are advanced by plain adds
@@ -427,38 +428,52 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
         if (pf) pf[2] = clock64();
         if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc)) : "memory");
         else { atomicCAS(p.status, 0, 4); asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_acc)) : "memory"); }
-    } else if (wid < 4) {
-        // epilogue: lane quarter `wid` of tensor memory = weight rows 32 * wid .. of this tile; columns = the tile's tokens
+    } else if (wid < 8) {
+        // epilogue: lane quarter `wid % 4` of tensor memory = weight rows 32 * (wid % 4) .. of this tile; the tile's token columns are
+        // split between the two warps of a quarter. All of a warp's accumulator reads are issued before the one wait.
         ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull));      // one verdict per warp: the loads below are warp-wide
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (pf && tid == 0) pf[3] = clock64();
         if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
-            const int row = mt * TC_M + wid * 32 + lane;
+            const int quarter = wid & 3, half = wid >> 2;
+            const int row = mt * TC_M + quarter * 32 + lane;
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
-            for (int c = 0; c < t.npad; c += 16) {                    // npad is a multiple of 16
-                uint32_t g[16], u[16];
-                const uint32_t ta = ((uint32_t)(wid * 32) << 16) + (uint32_t)c;
-                asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                             : "=r"(g[0]), "=r"(g[1]), "=r"(g[2]), "=r"(g[3]), "=r"(g[4]), "=r"(g[5]), "=r"(g[6]), "=r"(g[7]), "=r"(g[8]), "=r"(g[9]),
-                               "=r"(g[10]), "=r"(g[11]), "=r"(g[12]), "=r"(g[13]), "=r"(g[14]), "=r"(g[15]) : "r"(d_g + ta) : "memory");
-                if (GLU)
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                 : "=r"(u[0]), "=r"(u[1]), "=r"(u[2]), "=r"(u[3]), "=r"(u[4]), "=r"(u[5]), "=r"(u[6]), "=r"(u[7]), "=r"(u[8]), "=r"(u[9]),
-                                   "=r"(u[10]), "=r"(u[11]), "=r"(u[12]), "=r"(u[13]), "=r"(u[14]), "=r"(u[15]) : "r"(d_u + ta) : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            const int split = ((t.npad / 16 + 1) / 2) * 16;          // npad is a multiple of 16
+            const int c0 = half ? split : 0, nchunk = ((half ? t.npad : split) - c0) / 16;      // up to 4 chunks of 16 columns
+            uint32_t g[64], u[64];
+            const uint32_t ta = ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int pair = s_pair[c + j];
-                    if (pair >= 0) {
-                        float v = __uint_as_float(g[j]);
-                        if (p.s2g) v = v * sg;
-                        if (GLU) {
-                            // SiLU(gate) * up (src/ops/mod.rs:1105-1117). exact=0: the fast exponential (this path is tolerance class
-                            // through the tensor core's summation order anyway); exact=1: the library-exact one, on the f64 unit
-                            float w = __uint_as_float(u[j]); if (p.s2u) w = w * su;
-                            v = (p.exact_silu ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * w;
+            for (int ch = 0; ch < 4; ++ch) {
+                if (ch < nchunk) {
+                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                 : "=r"(g[16 * ch]), "=r"(g[16 * ch + 1]), "=r"(g[16 * ch + 2]), "=r"(g[16 * ch + 3]), "=r"(g[16 * ch + 4]), "=r"(g[16 * ch + 5]),
+                                   "=r"(g[16 * ch + 6]), "=r"(g[16 * ch + 7]), "=r"(g[16 * ch + 8]), "=r"(g[16 * ch + 9]), "=r"(g[16 * ch + 10]), "=r"(g[16 * ch + 11]),
+                                   "=r"(g[16 * ch + 12]), "=r"(g[16 * ch + 13]), "=r"(g[16 * ch + 14]), "=r"(g[16 * ch + 15]) : "r"(d_g + ta + 16u * ch) : "memory");
+                    if (GLU)
+                        asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                     : "=r"(u[16 * ch]), "=r"(u[16 * ch + 1]), "=r"(u[16 * ch + 2]), "=r"(u[16 * ch + 3]), "=r"(u[16 * ch + 4]), "=r"(u[16 * ch + 5]),
+                                       "=r"(u[16 * ch + 6]), "=r"(u[16 * ch + 7]), "=r"(u[16 * ch + 8]), "=r"(u[16 * ch + 9]), "=r"(u[16 * ch + 10]), "=r"(u[16 * ch + 11]),
+                                       "=r"(u[16 * ch + 12]), "=r"(u[16 * ch + 13]), "=r"(u[16 * ch + 14]), "=r"(u[16 * ch + 15]) : "r"(d_u + ta + 16u * ch) : "memory");
+                }
+            }
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                if (ch < nchunk) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int pair = s_pair[c0 + 16 * ch + j];
+                        if (pair >= 0) {
+                            float v = __uint_as_float(g[16 * ch + j]);
+                            if (p.s2g) v = v * sg;
+                            if (GLU) {
+                                // SiLU(gate) * up (src/ops/mod.rs:1105-1117). exact=0: the fast exponential (this path is tolerance class
+                                // through the tensor core's summation order anyway); exact=1: the library-exact one, on the f64 unit
+                                float w = __uint_as_float(u[16 * ch + j]); if (p.s2u) w = w * su;
+                                v = (p.exact_silu ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * w;
+                            }
+                            p.out[(size_t)pair * p.out_stride + row] = v;
                         }
-                        p.out[(size_t)pair * p.out_stride + row] = v;
                     }
                 }
             }
@@ -467,7 +482,7 @@ __global__ void __launch_bounds__(192) k_tc_gemm(TcGemm p) {
     if (pf && tid == 0) pf[4] = clock64();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (wid == 5) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+    if (wid == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
     if (pf && tid == 0) pf[5] = clock64();
 }
 inline size_t tc_gemm_smem(bool glu) {
@@ -547,8 +562,8 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
     static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
     const size_t n_blocks = (size_t)grid.x * grid.y;
     if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
-    if (wu) k_tc_gemm<true><<<grid, 192, tc_gemm_smem(true), st>>>(g);
-    else k_tc_gemm<false><<<grid, 192, tc_gemm_smem(false), st>>>(g);
+    if (wu) k_tc_gemm<true><<<grid, 320, tc_gemm_smem(true), st>>>(g);
+    else k_tc_gemm<false><<<grid, 320, tc_gemm_smem(false), st>>>(g);
     if (prof_on && g.prof) {
         std::vector<long long> h(n_blocks * 8);
         cudaStreamSynchronize(st);

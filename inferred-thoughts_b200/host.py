@@ -406,6 +406,10 @@ class Engine:
         self.L.itb_engine_tier_stats(self.h, out)
         return dict(hits=out[0], misses=out[1], evictions=out[2], bytes_moved=out[3])
 
+    def ep_step_transport(self):
+        """How an expert-parallel engine's one-token step moves rows between ranks: 'peer-memory', 'nccl', or 'none' (not expert parallel)."""
+        return {0: "none", 1: "nccl", 2: "peer-memory"}[self.L.itb_engine_ep_transport(self.h)]
+
     def tier_counters(self):
         """The reference's TierCounters as far as they exist here (see itb.h), as a dict."""
         names = ("fetched fetch_bytes picks_wait_us prefetch_reads prefetch_used lookups host_reads slot_bytes slots pool_bytes "

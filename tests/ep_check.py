@@ -35,11 +35,14 @@ def main():
         prompts = rng.integers(0, dims["n_vocab"], (n_seq, 40)).astype(np.uint32)
         e1 = host.Engine(full, 128, n_seq)
         e2 = host.Engine(shard, 128, n_seq, ep=(rank, world, host.share_unique_id(rank)))
+        if n_seq == 1:
+            want = "nccl" if os.environ.get("ITB_EP_P2P") == "0" else "peer-memory"
+            ok = ok and e2.ep_step_transport() == want
         a, b = e1.prefill(prompts), e2.prefill(prompts)
         a, b = np.atleast_2d(a), np.atleast_2d(b)
         ok = ok and a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
         toks = np.argmax(a, 1).astype(np.uint32)
-        for _ in range(4):
+        for _ in range(6):
             (la, na), (lb, nb) = e1.decode(toks), e2.decode(toks)
             ok = ok and la.view(np.uint32).tolist() == lb.view(np.uint32).tolist() and na.tolist() == nb.tolist()
             toks = na

@@ -12,16 +12,18 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
-@pytest.mark.parametrize("a2a", [True, False])
-def test_two_rank_expert_parallel_equals_single_gpu(a2a):
-    """a2a: many-row passes dispatch and combine by packed all-to-all (the default); otherwise every pass uses the all-gather /
-    reduce-scatter form (which the captured decode steps always use)."""
+@pytest.mark.parametrize("nccl_only", [False, True])
+def test_two_rank_expert_parallel_equals_single_gpu(nccl_only):
+    """Default: many-row passes dispatch and combine by packed all-to-all, and the one-token step exchanges rows and results
+    through peer memory (stores over NVLink into CUDA-IPC-mapped regions, flags with bounded waits). nccl_only: every pass
+    uses the NCCL all-gather / reduce-scatter form (which batched decode steps always use). Both must give the single-GPU
+    engine's bits."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    if not a2a:
-        env["ITB_EP_A2A_OFF"] = "1"
+    if nccl_only:
+        env["ITB_EP_A2A_OFF"] = "1"; env["ITB_EP_P2P"] = "0"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
            "--master-port", "29511", "-m", "tests.ep_check"]
     # own process group, so that a rank stuck in a collective is ended with the launcher instead of outliving the test
