@@ -67,3 +67,35 @@ def test_greedy_generation_is_deterministic_and_logs_routes(model):
     model.begin(64)
     b, _ = model.generate(ids, 8)
     assert a.tolist() == b.tolist() and len(a) == 8 and (margins >= 0).all()
+
+
+def test_nvfp4_shared_expert_and_lm_head_scales_are_applied_to_the_matmul_results():
+    """An NVFP4 file's shared expert and LM head (src/model/mod.rs:351-361; src/model/qwen35.rs:1668-1682, :1117-1120): the oracle
+    tells the storage type by byte count and multiplies each matmul's result by the tensor's `.scale`. Checked against the
+    same model with the scale folded in by hand: a power-of-two `output.scale` must scale the logits exactly, and the batched
+    == token-by-token invariant must survive the other storage type."""
+    m = O.OracleModel(oracle_dims(TINY)); m.synth(0, threads=8)
+    rng = np.random.default_rng(5)
+
+    def fp4(n_in, n_out):
+        nb = n_out * n_in // 64
+        blk = np.zeros((nb, 36), np.uint8)
+        blk[:, :4] = rng.integers(0x20, 0x50, (nb, 4)); blk[:, 4:] = rng.integers(0, 256, (nb, 32))
+        return blk.reshape(-1)
+    m.set_tensor("output.weight", fp4(TINY["n_embd"], TINY["n_vocab"]))
+    for il in range(TINY["n_layer"]):
+        m.set_tensor(f"blk.{il}.ffn_gate_shexp.weight", fp4(TINY["n_embd"], TINY["shared_ff"]))
+        m.set_tensor(f"blk.{il}.ffn_up_shexp.weight", fp4(TINY["n_embd"], TINY["shared_ff"]))
+        m.set_tensor(f"blk.{il}.ffn_down_shexp.weight", fp4(TINY["shared_ff"], TINY["n_embd"]))
+        m.set_tensor(f"blk.{il}.ffn_gate_shexp.scale", np.array([0.05], np.float32))
+        m.set_tensor(f"blk.{il}.ffn_down_shexp.scale", np.array([0.03], np.float32))
+    ids = prompt_ids(3, 12, TINY["n_vocab"])
+    m.begin(32); plain = m.forward(ids).copy()
+    m.set_tensor("output.scale", np.array([0.25], np.float32))
+    m.begin(32); scaled = m.forward(ids).copy()
+    assert (scaled.view(np.uint32) == (plain * np.float32(0.25)).view(np.uint32)).all()
+    m.begin(32)
+    for t in ids:
+        one = m.forward([t])
+    assert one.view(np.uint32).tolist() == scaled.view(np.uint32).tolist()
+    assert np.isfinite(scaled).all() and float(np.abs(scaled).max()) > 0
