@@ -276,7 +276,7 @@ def tiered_decode(host, ops, dims, seed, frac=0.5, steps=32):
     return out
 
 
-FAST_MODE = "kv=bf16,exact=0,experts=fp4tc,dense=q8tc"
+FAST_MODE = "kv=bf16,exact=0,experts=fp4tc,dense=bf16tc"
 PREFILL_ROWS = 2048
 
 
@@ -340,7 +340,7 @@ def other_configs(host, model, dims, seed, hbm, args, mode):
                                "expert_flop_per_token": flop_tok, "expert_TFLOPs_if_the_whole_pass_were_experts": flop_tok * 5548 / (ms / 1e3) / 1e12,
                                "fp4_peak_TFLOPs_measured": peak,
                                "note": "tolerance class: routed experts as FP4 x FP4 tcgen05 block-scaled GEMMs, causal attention as 16-bit matrix products, "
-                                       "chunk-parallel delta rule, tree-summed F32 dots; dense Q8_0 as tcgen05 int8 MMAs (exact)"}
+                                       "chunk-parallel delta rule, tree-summed F32 dots; dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands"}
         eng = host.Engine(fast_model, N_CTX, 1)
         eng.prefill(prompts(1, seed, n_vocab), want_logits=False)
         first = eng.decode_loop(np.zeros(1, np.uint32), 8)[-1]
@@ -402,11 +402,16 @@ def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_s, pre_ms = float(t[0]), float(t[1]), float(t[2])
     n_moe = dims["n_layer"]
+    transport = eng.ep_step_transport()
     out = {"value": world * B * args.steps / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms / args.steps, "batch_per_gpu": B,
            "e2e_tok_s": world * B * args.steps / e2e_s,
-           "experts_per_gpu": hi - lo, "collectives_per_step": 2 * n_moe, "launches_per_step": int(eng.launches_per_step()),
-           "note": "experts sharded by range, dense replicated, every rank its own sequences; decode steps: per MoE layer all-gather(rows, routing) + exact sum "
-                   "reduce-scatter(pair outputs) over NCCL, captured in the step's CUDA graph; many-row passes: packed all-to-all dispatch and combine"}
+           "experts_per_gpu": hi - lo, "launches_per_step": int(eng.launches_per_step()), "step_transport": transport,
+           "collectives_per_step": 0 if transport == "peer-memory" else 2 * n_moe,
+           "note": "experts sharded by range, dense replicated, every rank its own sequences; one-token steps per MoE layer: " +
+                   ("each rank's row and router logits stored into every rank's memory over NVLink and the served picks' rows stored straight into their "
+                    "owner's memory by the expert kernels (own kernels, flags with bounded waits, no collective call)" if transport == "peer-memory" else
+                    "all-gather(rows, routing) + exact-sum reduce-scatter(pair outputs) over NCCL") +
+                   ", captured in the step's CUDA graph; many-row passes: packed all-to-all dispatch and combine"}
     if pre_ms:
         out["prefill_2048_per_rank"] = {"value": world * PREFILL_ROWS / (pre_ms / 1e3), "unit": "tok/s", "ms": pre_ms, "dispatch": "packed all-to-all (NCCL send/recv sized by exchanged counts)"}
     eng.close(); shard.close()

@@ -766,6 +766,31 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         o.tl_slot = tl++;
         launch_k(pdl, k_out_proj, dim3(gx, B), TPB, out_proj_smem(n_in, o.br), st, o);
     };
+    // L2 hints: each kernel names what the kernels after it will stream. Off unless ITB_L2_HINT=1: measured on the 35B shape the
+    // step does not get faster with them (2.99 ms against 2.94 ms without, hints issued as each block finishes its own rows; 3.17 ms
+    // with the hints issued at the start of each kernel, where they queue ahead of the kernel's own loads) -- the kernels wait on
+    // their dependent stages, not on the latency of the weight stream.
+    static const bool hints_on = getenv("ITB_L2_HINT") && atoi(getenv("ITB_L2_HINT")) == 1;
+    const bool hints = hints_on && !prof;
+    auto hint_add = [&](L2Hint& h, const void* ptr, size_t bytes) {
+        if (!hints || !ptr || !bytes) return;
+        for (int i = 0; i < 8; ++i)
+            if (!h.p[i]) { h.p[i] = ptr; h.n[i] = (unsigned)std::min<size_t>(bytes, 64u << 20); return; }
+    };
+    auto hint_q8 = [&](L2Hint& h, const DevQ8& w) {
+        hint_add(h, w.q, (size_t)w.n_in * w.n_out); hint_add(h, w.s, (size_t)(w.n_in / 32) * w.n_out * 2);
+    };
+    auto hint_f32 = [&](L2Hint& h, const DevF32& w) {
+        if (c->exact && w.wt) hint_add(h, w.wt, (size_t)((w.n_out + 31) / 32) * 32 * w.n_in * 4);
+        else hint_add(h, w.w, (size_t)w.n_in * w.n_out * 4);
+    };
+    // the input projections of layer `il` (what its first kernel streams)
+    auto hint_layer_in = [&](L2Hint& h, uint32_t il) {
+        if (il >= d.n_layer) return;
+        const DevLayer& L = m->layers[il];
+        if (L.recurrent) { hint_q8(h, L.wqkv); hint_q8(h, L.wgate); hint_f32(h, L.ssm_alpha); hint_f32(h, L.ssm_beta); }
+        else { hint_q8(h, L.wq); hint_q8(h, L.wk); hint_q8(h, L.wv); }
+    };
     static bool attrs_set = false;
     if (!attrs_set) {
         set_smem((const void*)k_in_proj, 200 * 1024); set_smem((const void*)k_out_proj, 200 * 1024);
@@ -794,6 +819,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             p.conv_w = L.conv1d; p.conv_kernel = d.ssm_d_conv; p.conv_state_stride = (size_t)cd * (d.ssm_d_conv - 1);
             p.conv_state = e->conv_state + (size_t)rs * B * p.conv_state_stride;
             p.exact = c->exact;
+            hint_q8(p.hint, L.ssm_out);
+            hint_add(p.hint, e->ssm_state + (size_t)rs * B * state_stride, std::min<size_t>((size_t)B, 4) * state_stride * 4);
             launch_in(p, cd + vd, grid_rows(cd + vd));
             MARK(KC_GDN_IN, q8b(H, cd) + q8b(H, vd) + 2ull * H * d.ssm_dt_rank * 4 + (uint64_t)cd * d.ssm_d_conv * 4 +
                                 (uint64_t)B * (2ull * cd * (d.ssm_d_conv - 1) * 4 + (H + cd + vd) * 4));
@@ -808,6 +835,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             else launch_k(pdl, k_gdn_core<64>, dim3(d.ssm_dt_rank, B), 256, smem_g, st, g);
             MARK(KC_GDN_CORE, (uint64_t)B * (2ull * g.state_stride * 4 + (cd + 2ull * vd) * 4));
             OutProj o{e->aq, e->as, vd, L.ssm_out, e->x, H};
+            hint_q8(o.hint, L.shared_gate); hint_q8(o.hint, L.shared_up); hint_f32(o.hint, L.gate_inp); hint_f32(o.hint, L.shared_gate_inp);
             launch_out(o, vd);
             MARK(KC_OUT_PROJ, q8b(vd, H) + (uint64_t)B * (vd + 2ull * H) * 4);
         } else {
@@ -817,6 +845,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             p.nq = 3; p.q[0] = L.wq; p.qout[0] = e->qg; p.qstride[0] = 2 * qd; p.q[1] = L.wk; p.qout[1] = e->kbuf; p.qstride[1] = kvd;
             p.q[2] = L.wv; p.qout[2] = e->vbuf; p.qstride[2] = kvd;
             p.exact = c->exact;
+            hint_q8(p.hint, L.wo);
             launch_in(p, 2 * qd + 2 * kvd, grid_rows(2 * qd + 2 * kvd));
             MARK(KC_ATTN_IN, q8b(H, 2 * qd) + 2 * q8b(H, kvd) + (uint64_t)B * (H + 2ull * qd + 2ull * kvd) * 4);
             AttnPrep a{};
@@ -857,6 +886,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
             MARK(KC_ATTN, 0);
             }
             OutProj o{e->aq, e->as, qd, L.wo, e->x, H};
+            hint_q8(o.hint, L.shared_gate); hint_q8(o.hint, L.shared_up); hint_f32(o.hint, L.gate_inp); hint_f32(o.hint, L.shared_gate_inp);
             launch_out(o, qd);
             MARK(KC_OUT_PROJ, q8b(qd, H) + (uint64_t)B * (qd + 2ull * H) * 4);
         }
@@ -867,6 +897,8 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         f.nf = 2; f.f[0] = L.gate_inp; f.fout[0] = e->router; f.fstride[0] = d.n_expert;
         f.f[1] = L.shared_gate_inp; f.fout[1] = e->shlogit; f.fstride[1] = 1;
         f.xq_out = e->xq; f.xs_out = e->xs; f.exact = c->exact;
+        hint_q8(f.hint, L.shared_down);
+        if (il + 1 < d.n_layer) hint_layer_in(f.hint, il + 1); else hint_add(f.hint, m->output.q, std::min((size_t)48 << 20, (size_t)m->output.n_in * m->output.n_out));
         int gxf = c->exact ? sms : std::max(grid_rows(2 * d.shared_ff), std::min(2 * sms, (int)(d.n_expert + 1 + NWG - 1) / NWG));   // serial-k F32 rows: one per SM
         launch_in(f, 2 * d.shared_ff, gxf);
         MARK(KC_FFN_IN, (uint64_t)H * d.n_expert * 4 + 2 * q8b(H, d.shared_ff) + (uint64_t)H * 4 + (uint64_t)B * (2ull * H + d.n_expert + 2ull * d.shared_ff) * 4);
@@ -877,6 +909,7 @@ static void enqueue_step(itb_engine* e, cudaStream_t st, StepProf* prof = nullpt
         g.hq = e->hq; g.hs = e->hs; g.sq = e->sq; g.ss = e->ss;
         g.ids_out = e->route_ids + (size_t)il * e->R * d.n_expert_used; g.w_out = e->route_w + (size_t)il * e->R * d.n_expert_used;
         g.shared_row = -1;
+        if (hints && !L.down.slot_map) { g.down_nib = L.down.nib; g.down_sc = L.down.sc; g.down_bytes = (size_t)L.down.n_out * (L.down.n_in / 2); }
         if (p2p) {
             // every rank's quantised row and router logits (B is 1 here), pushed by each rank into every rank's region over NVLink;
             // k_moe_glu's blocks for row r wait for rank r's flag. No NCCL call, no zero-filled buffer.
@@ -1162,9 +1195,14 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     cudaStreamCaptureStatus cap_rows = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(st, &cap_rows);
     const bool q8tc = c->q8tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
+    const bool bf16tc = c->bf16tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
     // same: this matmul reads the quantised rows the previous one read (their tensor-core images are still current)
     auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R, bool same = false) {
         const int k = w.n_in;
+        if (bf16tc && R >= 64 && itb_tc_bf16_shape_ok(w)) {
+            // many rows, dense=bf16tc (tolerance class): both operands dequantised to bf16, one tcgen05 GEMM with f32 accumulators
+            if (itb_tc_bf16_gemm(c, st, w, xq, xs, R, out, stride, mode, same)) { launches++; return; }
+        }
         if (q8tc && R >= 64 && itb_tc_q8_shape_ok(w)) {
             // many rows, dense=q8tc: integer dots of 128 x 128 (row, token) pairs per tcgen05 MMA, scaled and summed in the CPU's order
             if (itb_tc_q8_gemm(c, st, w, xq, xs, R, out, stride, mode, same)) { launches++; return; }

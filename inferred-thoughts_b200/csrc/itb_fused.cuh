@@ -25,6 +25,7 @@ struct InProj {
     int exact; int br;                             // br: rows whose terms a warp collects before folding them together
     int f32_ring; int* err;                        // serial-k F32 rows through the block's ring (in_proj_smem counts it): the number of 32-row units, 0 = off; status word of its bounded waits
     int tl_slot;                                   // phase-timeline slot of this launch (-1: none)
+    L2Hint hint;                                   // what the kernels after this one will stream
 };
 
 __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
@@ -156,6 +157,8 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
         }
         base += p.q[m].n_out;
     }
+    // this warp's own rows are in: the memory system is free for what the next kernels will stream
+    if (wid == 0) l2_hint(p.hint, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, lane);
     TL(TLK_IN_PROJ, 4);
     TL(TLK_IN_PROJ, 5);
 }
@@ -169,7 +172,7 @@ size_t in_proj_smem(int n, int exact, int br, int f32_ring = 0) {
 // ------------------------------------------------------------------------------------------------------
 // Output projection with the residual add fused: x[b] += W . a[b], the activation arriving already quantised
 // (src/model/qwen35.rs:1017, :1220, :1325).
-struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; int tl_slot; };
+struct OutProj { const int8_t* aq; const float* as; int n_in; DevQ8 w; float* x; int x_stride; int br; int tl_slot; L2Hint hint; };
 __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     extern __shared__ __align__(16) unsigned char smem[];
     const int n = p.n_in, nb = n / 32, gsh = lanes_shift(nb);
@@ -191,6 +194,7 @@ __global__ void __launch_bounds__(NWG * 32) k_out_proj(OutProj p) {
     float* x = p.x + (size_t)b * p.x_stride;
     rows_batched<MK_Q8, 1, 4>((const uint8_t*)p.w.q, (const uint8_t*)p.w.s, n, b0 + r0, b0 + r1, aq, as, terms, p.br, gsh,
                               [&](int row, float v) { x[row] += v; });
+    if (wid == 0) l2_hint(p.hint, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, threadIdx.x & 31);
     TL(TLK_OUT_PROJ, 3);
 }
 size_t out_proj_smem(int n, int br) {
@@ -455,6 +459,7 @@ struct MoeGlu {
     // expert-parallel step over peer memory: row b's quantised activation and router logits were stored into this GPU's memory
     // by rank b; its flag wait_flags[b] reaches *wait_seq when they are all there (bounded wait; *err set if it runs out)
     const unsigned* wait_flags; const unsigned* wait_seq; int* err;
+    const uint8_t* down_nib; const uint8_t* down_sc; size_t down_bytes;   // the down stack (nibble bytes per expert), for the L2 hint; null: none
     int tl_slot;
 };
 constexpr int EP_WAIT_FAIL = 0x7002;
@@ -615,6 +620,13 @@ __global__ void __launch_bounds__(NWG * 32) k_moe_glu(MoeGlu p) {
             q = xq; s = xs;
         },
         [&](int k, float v) { s_gu[k0 + k] = v; });
+    if (p.down_nib && b < 4 && wid == (int)(blockDim.x >> 5) - 1) {
+        // this pick's down-projection weights, which the next kernel streams: into L2 while this one runs (the pick's blocks share them out)
+        L2Hint h{};
+        h.p[0] = p.down_nib + (size_t)el * p.down_bytes; h.n[0] = (unsigned)p.down_bytes;
+        h.p[1] = p.down_sc + (size_t)el * (p.down_bytes / 8); h.n[1] = (unsigned)(p.down_bytes / 8);
+        l2_hint(h, unit % upp, upp, lane);
+    }
     __syncthreads();
     TL(TLK_MOE_GLU, 4);
     if (wid == 0) {

@@ -95,6 +95,9 @@ struct itb_ctx {
     // Q8_0 tensor path: the pass's activation rows as K32 block images (kept for a following matmul over the same rows)
     uint8_t* tc_q8_b = nullptr; float* tc_q8_sx = nullptr; size_t tc_cap_q8b = 0, tc_cap_q8sx = 0;
     const void* tc_q8_src = nullptr; int tc_q8_src_rows = 0, tc_q8_src_in = 0;
+    uint8_t* tc_bf_b = nullptr; size_t tc_cap_bfb = 0;                 // dense=bf16tc: the pass's activation rows as bf16 operand tiles
+    const void* tc_bf_src = nullptr; int tc_bf_src_rows = 0, tc_bf_src_in = 0;
+    bool bf16tc = false;     // opts dense=bf16tc: many-row passes run the dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands (tolerance class)
     bool q8tc = false;       // opts dense=q8tc: many-row passes run the dense Q8_0 matmuls as tcgen05 int8 MMAs (bit-identical results)
     bool fp4tc = false;      // opts experts=fp4tc: many-row passes multiply FP4 activations on the tensor cores
     bool gdn_chunk = false;  // opts gdn=chunk: many-token passes run the delta rule chunk-parallel even under exact=1 (exact=0 always does)
@@ -106,6 +109,8 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
                     const int* pair_list, int n_pairs, float* out);
 bool itb_tc_shape_ok(const DevFp4& w);
 bool itb_tc_q8_shape_ok(const DevQ8& w);
+bool itb_tc_bf16_shape_ok(const DevQ8& w);
+bool itb_tc_bf16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
 bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
 void itb_tc_free(itb_ctx* c);
 
@@ -198,6 +203,27 @@ enum { TLK_EMBED = 1, TLK_IN_PROJ, TLK_GDN_CORE, TLK_OUT_PROJ, TLK_ATTN_PREP, TL
 // kernel of the same chain writes (weights, its own layer's state). Both are no-ops in an ordinary launch.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Byte ranges a later kernel of the step will stream (weights and state: they do not depend on what the kernels in between
+// compute). Every block of the kernel that carries the hint asks for its share of them to be brought into L2 while the kernel
+// runs, so the memory system keeps streaming through the step's dependent stages. (Every block, because a bulk prefetch is
+// carried out by the issuing SM's copy engine at that SM's bandwidth: one block asking for 27 MB holds its kernel open for
+// far longer than the kernel lasts.) A hint only: nothing waits for it.
+struct L2Hint { const void* p[8]; unsigned n[8]; };
+__device__ __forceinline__ void l2_hint(const L2Hint& h, unsigned part, unsigned n_parts, int lane) {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+        if (!h.p[i]) continue;
+        const uintptr_t a = ((uintptr_t)h.p[i] + 15) & ~(uintptr_t)15, z = ((uintptr_t)h.p[i] + h.n[i]) & ~(uintptr_t)15;
+        if (z <= a) continue;
+        // this block's share, in 16-byte units, split over the warp's lanes in pieces of 4 KB
+        const unsigned long long units = (z - a) >> 4, per = (units + n_parts - 1) / n_parts;
+        const unsigned long long u0 = min(units, per * part), u1 = min(units, u0 + per);
+        for (unsigned long long u = u0 + (unsigned long long)lane * 256u; u < u1; u += 32u * 256u) {
+            const unsigned sz = (unsigned)(min((unsigned long long)256u, u1 - u) << 4);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a + (u << 4)), "r"(sz) : "memory");
+        }
+    }
+}
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));

@@ -330,26 +330,30 @@ struct TcGemm {
     int n_out, n_in;                                     // rows of one matrix, K
     float* out; int out_stride;                          // out[pair][n_out]
     int* status;
-    int exact_silu;                                      // SiLU through the library-exact exponential (f64 unit: several times the epilogue)
     long long* prof;                                     // optional: 8 clock64 stamps per block (ITB_TC_PROF=1)
 };
 __device__ __forceinline__ void tc_bulk(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
-// grid (max tiles, n_out / 128); block 320: warps 0-7 epilogue (tensor-memory lane quarter = warp % 4, column half = warp / 4),
-// warp 8 producer, warp 9 MMA.
-template <bool GLU>
+// Persistent: grid = one block per SM; block b takes work items b, b + grid, ... of the (tile, row tile) list, row tile fastest, so
+// the blocks running at one time share activation tiles and an expert's weights in L2. Block 320: warps 0-7 epilogue (tensor-
+// memory lane quarter = warp % 4, column half = warp / 4), warp 8 producer, warp 9 MMA. The three roles run as a pipeline over
+// the block's items: the producer's stage ring runs on into the next item; the epilogue warps read an item's accumulators into
+// registers, hand tensor memory back (s_free), and do their arithmetic and stores while the next item's MMAs run.
+// EXACT_SILU is a template parameter, not a flag read in the loop: the library-exact exponential is some hundred instructions, and
+// both forms inside the 64-times unrolled epilogue overflow the instruction cache (measured: 14,900 cycles per tile against 5,300 for
+// the same stores without the activation).
+template <bool GLU, bool EXACT_SILU>
 __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc;
+    __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc, s_free;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_pair[TC_NMAX];
+    __shared__ int s_pair[8][TC_NMAX / 2 + 16];
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-    if ((int)blockIdx.x >= *p.n_tiles) return;
-    const TcTile t = p.tiles[blockIdx.x];
-    if (tid < TC_NMAX) s_pair[tid] = tid < t.cnt ? p.pair_list[t.n0 + tid] : -1;      // where each column's result goes
-    const int mt = blockIdx.y, kbs = p.n_in / 64, n_stage = kbs / TC_KS, el = t.expert - p.expert_lo;
-    const uint32_t a_bytes = TC_KS * 4096, b_bytes = (uint32_t)t.npad * 32 * TC_KS, sf_bytes = TC_KS * 512;
+    const int n_mt = p.n_out / TC_M, n_work = *p.n_tiles * n_mt;
+    if ((int)blockIdx.x >= n_work) return;
+    const int kbs = p.n_in / 64, n_stage = kbs / TC_KS;
+    const uint32_t a_bytes = TC_KS * 4096, sf_bytes = TC_KS * 512;
     // stage layout: A_g | A_u | B | SFA_g | SFA_u | SFB
     const uint32_t o_au = a_bytes, o_b = a_bytes * (GLU ? 2 : 1), o_sfg = o_b + TC_NMAX * 32 * TC_KS, o_sfu = o_sfg + sf_bytes, o_sfb = o_sfu + (GLU ? sf_bytes : 0);
     const uint32_t stage_bytes = o_sfb + sf_bytes;
@@ -360,6 +364,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_empty[s])) : "memory");
         }
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_acc)) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(tc_smem(&s_free)) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
@@ -371,75 +376,108 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tm = s_tmem;
-    long long* pf = p.prof ? p.prof + ((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 : nullptr;
-    if (pf && tid == 0) { pf[0] = clock64(); pf[7] = t.npad; }
+    // optional stamps of this block: [0] start, [1] MMA thread's cycles waiting for operands, [2] waiting for tensor memory to be
+    // handed back, [3] epilogue warp 0 waiting for accumulators, [4] its arithmetic and stores, [5] end, [6] items, [7] columns
+    long long* pf = p.prof ? p.prof + (size_t)blockIdx.x * 8 : nullptr;
+    if (pf && tid == 0) pf[0] = clock64();
     // tensor memory: D_g at 0, D_u at 128, scale factors from 256: per stage slot 48 columns (SFA_g 16, SFA_u 16, SFB 16)
     const uint32_t d_g = tm, d_u = tm + 128, sf0 = tm + 256;
+    const unsigned long long limit = 2000000000ull;
     bool ok = true;
     if (wid == 8 && lane == 0) {
-        const size_t w_tile = ((size_t)el * (p.n_out / TC_M) + mt) * kbs;
-        for (int st = 0; st < n_stage && ok; ++st) {
-            const int s = st % TC_STAGES;
-            if (st >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((st / TC_STAGES) - 1) & 1, 2000000000ull);
-            if (!ok) break;
-            const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * stage_bytes;
+        int it = 0;                                           // stages issued so far, over all items
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            const TcTile t = p.tiles[w / n_mt];
+            const int mt = w % n_mt;
+            const size_t w_tile = ((size_t)(t.expert - p.expert_lo) * n_mt + mt) * kbs;
+            const uint32_t b_bytes = (uint32_t)t.npad * 32 * TC_KS;
             const uint32_t total = a_bytes * (GLU ? 2 : 1) + b_bytes + sf_bytes * (GLU ? 3 : 2);
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(total) : "memory");
-            const size_t kb0 = (size_t)st * TC_KS;
-            tc_bulk(dst, p.wg_img + (w_tile + kb0) * 4096, a_bytes, full);
-            tc_bulk(dst + o_sfg, p.wg_sf + (w_tile + kb0) * 512, sf_bytes, full);
-            if (GLU) {
-                tc_bulk(dst + o_au, p.wu_img + (w_tile + kb0) * 4096, a_bytes, full);
-                tc_bulk(dst + o_sfu, p.wu_sf + (w_tile + kb0) * 512, sf_bytes, full);
+            for (int st = 0; st < n_stage; ++st, ++it) {
+                const int s = it % TC_STAGES;
+                if (it >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / TC_STAGES) - 1) & 1, limit);
+                if (!ok) break;
+                const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * stage_bytes;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(total) : "memory");
+                const size_t kb0 = (size_t)st * TC_KS;
+                tc_bulk(dst, p.wg_img + (w_tile + kb0) * 4096, a_bytes, full);
+                tc_bulk(dst + o_sfg, p.wg_sf + (w_tile + kb0) * 512, sf_bytes, full);
+                if (GLU) {
+                    tc_bulk(dst + o_au, p.wu_img + (w_tile + kb0) * 4096, a_bytes, full);
+                    tc_bulk(dst + o_sfu, p.wu_sf + (w_tile + kb0) * 512, sf_bytes, full);
+                }
+                tc_bulk(dst + o_b, p.b_img + (size_t)t.b_off * (p.n_in / 2) + kb0 * (t.npad * 32), b_bytes, full);
+                tc_bulk(dst + o_sfb, p.b_sf + ((size_t)t.sf_off + kb0) * 512, sf_bytes, full);
             }
-            tc_bulk(dst + o_b, p.b_img + (size_t)t.b_off * (p.n_in / 2) + kb0 * (t.npad * 32), b_bytes, full);
-            tc_bulk(dst + o_sfb, p.b_sf + ((size_t)t.sf_off + kb0) * 512, sf_bytes, full);
         }
         if (!ok) atomicCAS(p.status, 0, 3);
     } else if (wid == 9 && lane == 0) {
-        const uint32_t idesc = tc_idesc_fp4(TC_M, t.npad);
         // descriptors of stage slot 0; a slot or K block further on only moves the 14-bit start-address field (address >> 4), which
         // cannot carry out of it (shared memory ends below 256 KB), so the low words are advanced by plain adds
-        const uint64_t dA = tc_desc(sbase, 2048, 128), dAu = tc_desc(sbase + o_au, 2048, 128), dB = tc_desc(sbase + o_b, (uint32_t)t.npad * 16, 128);
+        const uint64_t dA = tc_desc(sbase, 2048, 128), dAu = tc_desc(sbase + o_au, 2048, 128);
         const uint64_t dSg = tc_desc(sbase + o_sfg, 128, 128), dSu = tc_desc(sbase + o_sfu, 128, 128), dSb = tc_desc(sbase + o_sfb, 128, 128);
-        const uint32_t b_step = (uint32_t)(t.npad * 32) >> 4;
-        for (int st = 0; st < n_stage && ok; ++st) {
-            const int s = st % TC_STAGES;
-            ok = tc_mbar_wait(tc_smem(&s_full[s]), (st / TC_STAGES) & 1, 2000000000ull);
+        int it = 0, item = 0;
+        long long t_load = 0, t_free = 0;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++item) {
+            const TcTile t = p.tiles[w / n_mt];
+            const uint32_t idesc = tc_idesc_fp4(TC_M, t.npad);
+            const uint64_t dB = tc_desc(sbase + o_b, (uint32_t)t.npad * 16, 128);
+            const uint32_t b_step = (uint32_t)(t.npad * 32) >> 4;
+            if (item) {                                       // the epilogue warps have read the previous item's accumulators
+                const long long c0 = pf ? clock64() : 0;
+                ok = tc_mbar_wait(tc_smem(&s_free), (item - 1) & 1, limit);
+                if (pf) t_free += clock64() - c0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            for (int st = 0; st < n_stage; ++st, ++it) {
+                const int s = it % TC_STAGES;
+                const long long c0 = pf ? clock64() : 0;
+                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / TC_STAGES) & 1, limit);
+                if (pf) t_load += clock64() - c0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t so = (uint32_t)s * (stage_bytes >> 4), sft = sf0 + s * 48;
+#pragma unroll
+                for (int k = 0; k < TC_KS; ++k) {
+                    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 4 * k), "l"(dSg + so + 32u * k) : "memory");
+                    if (GLU) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 16 + 4 * k), "l"(dSu + so + 32u * k) : "memory");
+                    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 32 + 4 * k), "l"(dSb + so + 32u * k) : "memory");
+                }
+#pragma unroll
+                for (int k = 0; k < TC_KS; ++k) {
+                    const uint64_t db = dB + so + b_step * k;
+                    const uint32_t acc = (st | k) ? 1u : 0u;
+                    tc_mma_fp4(d_g, dA + so + 256u * k, db, idesc, sft + 4 * k, sft + 32 + 4 * k, acc);
+                    if (GLU) tc_mma_fp4(d_u, dAu + so + 256u * k, db, idesc, sft + 16 + 4 * k, sft + 32 + 4 * k, acc);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
+            }
             if (!ok) break;
-            if (pf && st == 0) pf[1] = clock64();
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t so = (uint32_t)s * (stage_bytes >> 4), sft = sf0 + s * 48;
-#pragma unroll
-            for (int k = 0; k < TC_KS; ++k) {
-                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 4 * k), "l"(dSg + so + 32u * k) : "memory");
-                if (GLU) asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 16 + 4 * k), "l"(dSu + so + 32u * k) : "memory");
-                asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(sft + 32 + 4 * k), "l"(dSb + so + 32u * k) : "memory");
-            }
-#pragma unroll
-            for (int k = 0; k < TC_KS; ++k) {
-                const uint64_t db = dB + so + b_step * k;
-                const uint32_t acc = (st | k) ? 1u : 0u;
-                tc_mma_fp4(d_g, dA + so + 256u * k, db, idesc, sft + 4 * k, sft + 32 + 4 * k, acc);
-                if (GLU) tc_mma_fp4(d_u, dAu + so + 256u * k, db, idesc, sft + 16 + 4 * k, sft + 32 + 4 * k, acc);
-            }
-            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc)) : "memory");
         }
-        if (pf) pf[2] = clock64();
-        if (ok) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc)) : "memory");
-        else { atomicCAS(p.status, 0, 4); asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_acc)) : "memory"); }
+        if (!ok) atomicCAS(p.status, 0, 4);
+        if (pf) { pf[1] = t_load; pf[2] = t_free; }
     } else if (wid < 8) {
-        // epilogue: lane quarter `wid % 4` of tensor memory = weight rows 32 * (wid % 4) .. of this tile; the tile's token columns are
+        // epilogue: lane quarter `wid % 4` of tensor memory = weight rows 32 * (wid % 4) .. of the tile; the tile's token columns are
         // split between the two warps of a quarter. All of a warp's accumulator reads are issued before the one wait.
-        ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), 0, 2000000000ull));      // one verdict per warp: the loads below are warp-wide
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (pf && tid == 0) pf[3] = clock64();
-        if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
-            const int quarter = wid & 3, half = wid >> 2;
-            const int row = mt * TC_M + quarter * 32 + lane;
-            const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
+        const int quarter = wid & 3, half = wid >> 2;
+        int item = 0;
+        long long t_wait = 0, t_work = 0, cols = 0;
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++item) {
+            const TcTile t = p.tiles[w / n_mt];
+            const int mt = w % n_mt, el = t.expert - p.expert_lo;
             const int split = ((t.npad / 16 + 1) / 2) * 16;          // npad is a multiple of 16
             const int c0 = half ? split : 0, nchunk = ((half ? t.npad : split) - c0) / 16;      // up to 4 chunks of 16 columns
+            // where each of this warp's columns goes (read before the wait, so the latency hides behind the MMAs)
+            for (int j = lane; j < 16 * nchunk; j += 32) s_pair[wid][j] = c0 + j < t.cnt ? p.pair_list[t.n0 + c0 + j] : -1;
+            const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
+            __syncwarp();
+            const long long k0 = pf ? clock64() : 0;
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), item & 1, limit));      // one verdict per warp: the loads below are warp-wide
+            if (!ok || __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) != 0) break;
+            const long long k1 = pf ? clock64() : 0;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = mt * TC_M + quarter * 32 + lane;
             uint32_t g[64], u[64];
             const uint32_t ta = ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
 #pragma unroll
@@ -457,29 +495,35 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
                 }
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // the accumulators are in registers: tensor memory goes back to the MMA warp for the next item
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_free)) : "memory");
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 if (ch < nchunk) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int pair = s_pair[c0 + 16 * ch + j];
+                        const int pair = s_pair[wid][16 * ch + j];
                         if (pair >= 0) {
                             float v = __uint_as_float(g[16 * ch + j]);
                             if (p.s2g) v = v * sg;
                             if (GLU) {
                                 // SiLU(gate) * up (src/ops/mod.rs:1105-1117). exact=0: the fast exponential (this path is tolerance class
                                 // through the tensor core's summation order anyway); exact=1: the library-exact one, on the f64 unit
-                                float w = __uint_as_float(u[16 * ch + j]); if (p.s2u) w = w * su;
-                                v = (p.exact_silu ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * w;
+                                float x = __uint_as_float(u[16 * ch + j]); if (p.s2u) x = x * su;
+                                v = (EXACT_SILU ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * x;
                             }
                             p.out[(size_t)pair * p.out_stride + row] = v;
                         }
                     }
                 }
             }
+            __syncwarp();                                     // s_pair[wid] is rewritten for the next item
+            if (pf) { t_wait += k1 - k0; t_work += clock64() - k1; cols += t.npad; }
         }
+        if (pf && tid == 0) { pf[3] = t_wait; pf[4] = t_work; pf[6] = item; pf[7] = cols; }
     }
-    if (pf && tid == 0) pf[4] = clock64();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (wid == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
@@ -496,7 +540,8 @@ bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n
 void itb_tc_free(itb_ctx* c) {
     for (auto& kv : c->tc_weights) { cudaFree(kv.second.img); cudaFree(kv.second.sf); }
     c->tc_weights.clear();
-    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales); cudaFree(c->tc_q8_b); cudaFree(c->tc_q8_sx);
+    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales); cudaFree(c->tc_q8_b); cudaFree(c->tc_q8_sx); cudaFree(c->tc_bf_b);
+    c->tc_bf_b = nullptr; c->tc_cap_bfb = 0; c->tc_bf_src = nullptr;
     c->tc_q8_b = nullptr; c->tc_q8_sx = nullptr; c->tc_cap_q8b = c->tc_cap_q8sx = 0; c->tc_q8_src = nullptr;
     c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr; c->tc_codes = nullptr; c->tc_scales = nullptr; c->tc_cap_codes = c->tc_cap_scales = 0;
     c->tc_cap_tiles = c->tc_cap_slots = c->tc_cap_b = c->tc_cap_sf = 0;
@@ -551,33 +596,36 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
     g.wg_img = tg->img; g.wg_sf = tg->sf; g.wu_img = tu ? tu->img : nullptr; g.wu_sf = tu ? tu->sf : nullptr;
     g.s2g = wg.scale2; g.s2u = wu ? wu->scale2 : nullptr; g.expert_lo = wg.expert_lo;
     g.b_img = c->tc_b_img; g.b_sf = c->tc_b_sf; g.tiles = tiles; g.n_tiles = c->tc_n_tiles; g.pair_list = pair_list;
-    g.n_out = wg.n_out; g.n_in = wg.n_in; g.out = out; g.out_stride = wg.n_out; g.status = c->tc_status; g.exact_silu = c->exact ? 1 : 0;
+    g.n_out = wg.n_out; g.n_in = wg.n_in; g.out = out; g.out_stride = wg.n_out; g.status = c->tc_status;
     static bool attr = false;
     if (!attr) {
-        cudaFuncSetAttribute(k_tc_gemm<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(true));
-        cudaFuncSetAttribute(k_tc_gemm<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(false));
+        cudaFuncSetAttribute(k_tc_gemm<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(true));
+        cudaFuncSetAttribute(k_tc_gemm<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(true));
+        cudaFuncSetAttribute(k_tc_gemm<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_gemm_smem(false));
         attr = true;
     }
-    const dim3 grid((unsigned)max_tiles, (unsigned)(wg.n_out / TC_M));
+    const size_t n_blocks = std::min<size_t>((size_t)c->sm_count, max_tiles * (size_t)(wg.n_out / TC_M));
+    const dim3 grid((unsigned)n_blocks);
     static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
-    const size_t n_blocks = (size_t)grid.x * grid.y;
     if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
-    if (wu) k_tc_gemm<true><<<grid, 320, tc_gemm_smem(true), st>>>(g);
-    else k_tc_gemm<false><<<grid, 320, tc_gemm_smem(false), st>>>(g);
+    if (wu && c->exact) k_tc_gemm<true, true><<<grid, 320, tc_gemm_smem(true), st>>>(g);
+    else if (wu) k_tc_gemm<true, false><<<grid, 320, tc_gemm_smem(true), st>>>(g);
+    else k_tc_gemm<false, false><<<grid, 320, tc_gemm_smem(false), st>>>(g);
     if (prof_on && g.prof) {
         std::vector<long long> h(n_blocks * 8);
         cudaStreamSynchronize(st);
         cudaMemcpy(h.data(), g.prof, n_blocks * 64, cudaMemcpyDeviceToHost);
         cudaFree(g.prof);
-        double acc[5] = {0, 0, 0, 0, 0}; size_t n = 0; double cols = 0;
+        double acc[5] = {0, 0, 0, 0, 0}, items = 0, cols = 0; size_t n = 0;
         for (size_t b = 0; b < n_blocks; ++b) {
             const long long* q = &h[b * 8];
-            if (!q[0] || !q[5]) continue;
-            acc[0] += (double)(q[1] - q[0]); acc[1] += (double)(q[2] - q[1]); acc[2] += (double)(q[3] - q[2]); acc[3] += (double)(q[4] - q[3]); acc[4] += (double)(q[5] - q[0]);
-            cols += (double)q[7]; ++n;
+            if (!q[0] || !q[5] || !q[6]) continue;
+            acc[0] += (double)q[1]; acc[1] += (double)q[2]; acc[2] += (double)q[3]; acc[3] += (double)q[4]; acc[4] += (double)(q[5] - q[0]);
+            items += (double)q[6]; cols += (double)q[7]; ++n;
         }
-        if (n) fprintf(stderr, "tc_gemm glu=%d blocks %zu (avg cols %.0f): cycles start->first stage %.0f, main loop issue %.0f, issue end->accumulators ready %.0f, epilogue %.0f, whole block %.0f\n",
-                       wu ? 1 : 0, n, cols / n, acc[0] / n, acc[1] / n, acc[2] / n, acc[3] / n, acc[4] / n);
+        if (n) fprintf(stderr, "tc_gemm glu=%d blocks %zu, items %.0f (avg cols %.0f): cycles per item: MMA thread waiting for operands %.0f, for tensor memory %.0f; "
+                               "epilogue waiting for accumulators %.0f, reading + arithmetic + stores %.0f; whole block per item %.0f\n",
+                       wu ? 1 : 0, n, items, cols / items, acc[0] / items, acc[1] / items, acc[2] / items, acc[3] / items, acc[4] / items);
     }
     c->launches += 4;
     cudaError_t e = cudaGetLastError();
@@ -860,5 +908,267 @@ bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* x
     }
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return itb_fail(c, "Q8_0 tensor path: launch", e);
+    return true;
+}
+
+// =====================================================================================================
+// Dense Q8_0 matmuls of many-row passes as bf16 tensor-core GEMMs (tolerance class, opts dense=bf16tc)
+// =====================================================================================================
+// Both operands are dequantised once -- the weights when first used, the pass's Q8_0-quantised activation rows (the same
+// quantisation the CPU path applies, src/ops/naive.rs:676-712) once per row set -- to bf16 (value = int8 * block scale, rounded
+// to nearest even: 2^-9 relative per element), laid out as K-major operand tiles, and multiplied by tcgen05.mma kind::f16 with
+// f32 accumulators in tensor memory. What differs from the CPU path: that rounding, and the tensor core's summation order in
+// place of the per-block order. A tile is 128 weight rows x 256 tokens; two accumulator buffers fill the 512 columns of tensor
+// memory, so the MMAs of one tile run while eight warps store the previous one. Persistent blocks, one per SM, token tile
+// fastest: the blocks running at one time share a few weight tiles and all of the pass's activation tiles in L2.
+// Operand images ("K16 block": rows x 16 bf16 = rows x 32 B as [2 chunks of 16 B][rows / 8][8 rows][16 B], no swizzle; descriptor
+// leading offset rows * 16, stride offset 128).
+namespace {
+
+constexpr int BF_KB = 4;                 // K16 blocks per pipeline stage (64 elements)
+constexpr int BF_STAGES = 4;
+constexpr int BF_N = 256;                // tokens per tile
+constexpr int BF_A_BLK = 128 * 32, BF_B_BLK = BF_N * 32;
+constexpr int BF_STAGE_BYTES = BF_KB * (BF_A_BLK + BF_B_BLK);
+
+// kind::f16: f32 accumulators (1 at bit 4), bf16 operands (1 at bits 7 and 10), both K-major, M x N
+__host__ __device__ constexpr uint32_t tc_idesc_bf16(int m, int n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
+
+__device__ __forceinline__ uint32_t bf16x2_rn(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// Q8_0 rows -> bf16 K16 block images of ROWS-row tiles. One thread per (row, K16 block); a warp takes 8 rows x 4 blocks, so it
+// reads 64 contiguous bytes per row and writes 128 contiguous bytes per block and chunk. Rows past n_rows are zeros.
+// scales16 (f16, per weight row and 32-element block) or scales32 (f32, per activation row and block): whichever is not null.
+template <int ROWS>
+__global__ void k_bf16_tile(const int8_t* q, const uint16_t* scales16, const float* scales32, int n_rows, int n_in, uint8_t* img) {
+    const int kbs = n_in / 16;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x, total = (size_t)((n_rows + ROWS - 1) / ROWS) * ROWS * kbs;
+    if (idx >= total) return;
+    const int r_lo = (int)(idx & 7), kb_lo = (int)((idx >> 3) & 3);
+    const size_t rest = idx >> 5;
+    const int kb = (int)(rest % (size_t)(kbs / 4)) * 4 + kb_lo;
+    const size_t row = (rest / (size_t)(kbs / 4)) * 8 + r_lo;
+    const int rt = (int)(row / ROWS), r = (int)(row % ROWS);
+    uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+    if (row < (size_t)n_rows) {
+        const uint4 v = *(const uint4*)(q + row * n_in + (size_t)kb * 16);
+        const size_t si = row * (size_t)(n_in / 32) + (kb >> 1);
+        const float sc = scales16 ? f16_bits_to_f32(scales16[si]) : scales32[si];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float f0 = (float)(int8_t)(w[i] & 0xff) * sc, f1 = (float)(int8_t)((w[i] >> 8) & 0xff) * sc;
+            const float f2 = (float)(int8_t)((w[i] >> 16) & 0xff) * sc, f3 = (float)(int8_t)(w[i] >> 24) * sc;
+            o[2 * i] = bf16x2_rn(f0, f1); o[2 * i + 1] = bf16x2_rn(f2, f3);
+        }
+        lo = make_uint4(o[0], o[1], o[2], o[3]); hi = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+    uint8_t* blk = img + ((size_t)rt * kbs + kb) * (size_t)(ROWS * 32);
+    *(uint4*)(blk + (r >> 3) * 128 + (r & 7) * 16) = lo;
+    *(uint4*)(blk + ROWS * 16 + (r >> 3) * 128 + (r & 7) * 16) = hi;
+}
+
+struct TcBf {
+    const uint8_t* a_img;                         // weights: [row tile][K16 block][4096 B]
+    const uint8_t* b_img;                         // activations of the pass: [token tile][K16 block][8192 B]
+    int kbs, n_rows, n_rt, n_tt;                  // K16 blocks, tokens, row tiles, token tiles
+    float* out; size_t stride; int mode;          // out[token][row]; mode 1: += (the residual add of an output projection)
+    int* status;
+    long long* prof;                              // optional: 8 cycle counts per block (ITB_TC_PROF=1)
+};
+// grid: one block per SM (or per work item, if fewer); block 320: warps 0-7 store accumulators (lane quarter = warp % 4, column half
+// = warp / 4), warp 8 fetches operands, warp 9 issues the MMAs.
+__global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ unsigned long long s_full[BF_STAGES], s_empty[BF_STAGES], s_acc[2], s_free[2];
+    __shared__ uint32_t s_tmem;
+    const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
+    const int n_work = p.n_rt * p.n_tt, kbs = p.kbs, n_stage = kbs / BF_KB;
+    if ((int)blockIdx.x >= n_work) return;
+    const uint32_t sbase = tc_smem(smem);
+    if (tid == 0) {
+        for (int s = 0; s < BF_STAGES; ++s) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_full[s])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_empty[s])) : "memory");
+        }
+        for (int i = 0; i < 2; ++i) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_acc[i])) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 8;" ::"r"(tc_smem(&s_free[i])) : "memory");
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (wid == 9) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(tc_smem(&s_tmem)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tm = s_tmem;
+    const unsigned long long limit = 2000000000ull;
+    long long* pf = p.prof ? p.prof + (size_t)blockIdx.x * 8 : nullptr;
+    if (pf && tid == 0) pf[0] = clock64();
+    bool ok = true;
+    if (wid == 8 && lane == 0) {
+        int it = 0;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+            const size_t a0 = (size_t)(w / p.n_tt) * kbs, b0 = (size_t)(w % p.n_tt) * kbs;
+            for (int st = 0; st < n_stage; ++st, ++it) {
+                const int s = it % BF_STAGES;
+                if (it >= BF_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / BF_STAGES) - 1) & 1, limit);
+                if (!ok) break;
+                const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * BF_STAGE_BYTES;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"((uint32_t)BF_STAGE_BYTES) : "memory");
+                const size_t kb0 = (size_t)st * BF_KB;
+                tc_bulk(dst, p.a_img + (a0 + kb0) * BF_A_BLK, BF_KB * BF_A_BLK, full);
+                tc_bulk(dst + BF_KB * BF_A_BLK, p.b_img + (b0 + kb0) * BF_B_BLK, BF_KB * BF_B_BLK, full);
+            }
+        }
+        if (!ok) atomicCAS(p.status, 0, 3);
+    } else if (wid == 9 && lane == 0) {
+        const uint32_t idesc = tc_idesc_bf16(128, BF_N);
+        const uint64_t dA = tc_desc(sbase, 128 * 16, 128), dB = tc_desc(sbase + BF_KB * BF_A_BLK, BF_N * 16, 128);
+        int it = 0, item = 0;
+        long long t_load = 0, t_free = 0;
+        for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++item) {
+            const int buf = item & 1;
+            if (item >= 2) {                                  // the warps that store have read this buffer's previous tile
+                const long long c0 = pf ? clock64() : 0;
+                ok = tc_mbar_wait(tc_smem(&s_free[buf]), ((item >> 1) - 1) & 1, limit);
+                if (pf) t_free += clock64() - c0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            }
+            for (int st = 0; st < n_stage; ++st, ++it) {
+                const int s = it % BF_STAGES;
+                const long long c0 = pf ? clock64() : 0;
+                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / BF_STAGES) & 1, limit);
+                if (pf) t_load += clock64() - c0;
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t so = (uint32_t)s * (BF_STAGE_BYTES >> 4);
+#pragma unroll
+                for (int k = 0; k < BF_KB; ++k) {
+                    asm volatile(
+                        "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }\n"
+                        ::"r"(tm + (uint32_t)(BF_N * buf)), "l"(dA + so + (uint32_t)(k * (BF_A_BLK >> 4))), "l"(dB + so + (uint32_t)(k * (BF_B_BLK >> 4))), "r"(idesc),
+                          "r"((st | k) ? 1u : 0u) : "memory");
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
+            }
+            if (!ok) break;
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_acc[buf])) : "memory");
+        }
+        if (!ok) atomicCAS(p.status, 0, 4);
+        if (pf) { pf[1] = t_load; pf[2] = t_free; }
+    } else if (wid < 8) {
+        const int quarter = wid & 3, half = wid >> 2, row = quarter * 32 + lane;
+        int item = 0;
+        long long t_wait = 0, t_work = 0;
+        for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++item) {
+            const int buf = item & 1, rt = w / p.n_tt, tt = w % p.n_tt;
+            const long long k0 = pf ? clock64() : 0;
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc[buf]), (item >> 1) & 1, limit));
+            if (!ok || __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) != 0) break;
+            const long long k1 = pf ? clock64() : 0;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            float* ocol = p.out + (size_t)rt * 128 + row;
+#pragma unroll 1
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t d[32];
+                const uint32_t ta = tm + (uint32_t)(BF_N * buf + 128 * half + 32 * ch) + ((uint32_t)(quarter * 32) << 16);
+                asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                             : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]),
+                               "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]),
+                               "=r"(d[23]), "=r"(d[24]), "=r"(d[25]), "=r"(d[26]), "=r"(d[27]), "=r"(d[28]), "=r"(d[29]), "=r"(d[30]), "=r"(d[31]) : "r"(ta) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ch == 3) {
+                    // the whole buffer has been read: it goes back to the MMA warp
+                    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_free[buf])) : "memory");
+                }
+                const int tok0 = tt * BF_N + 128 * half + 32 * ch;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    if (tok0 + j < p.n_rows) {
+                        float* o = ocol + (size_t)(tok0 + j) * p.stride;
+                        const float v = __uint_as_float(d[j]);
+                        *o = p.mode ? *o + v : v;
+                    }
+                }
+            }
+            if (pf) { t_wait += k1 - k0; t_work += clock64() - k1; }
+        }
+        if (!ok) atomicCAS(p.status, 0, 5);
+        if (pf && tid == 0) { pf[3] = t_wait; pf[4] = t_work; pf[6] = item; }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (wid == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
+    if (pf && tid == 0) pf[5] = clock64();
+}
+constexpr size_t tc_bf16_smem() { return (size_t)BF_STAGES * BF_STAGE_BYTES + 128; }
+
+}  // namespace
+
+bool itb_tc_bf16_shape_ok(const DevQ8& w) { return w.n_in % (16 * BF_KB) == 0 && w.n_out % 128 == 0 && w.q && w.s; }
+// out[token][row] (+)= W x for n_rows quantised activation rows (xq int8 [n_rows][n_in], xs f32 [n_rows][n_in / 32]). False: not run.
+bool itb_tc_bf16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts) {
+    if (!itb_tc_bf16_shape_ok(w) || n_rows <= 0) return false;
+    const size_t kbs = w.n_in / 16, rts = w.n_out / 128, tts = ((size_t)n_rows + BF_N - 1) / BF_N;
+    auto it = c->tc_weights.find(w.s);                       // keyed by the scale array: the int8 images of dense=q8tc are keyed by w.q
+    if (it == c->tc_weights.end()) {
+        itb_ctx::TcWeights t;
+        if (cudaMalloc(&t.img, rts * kbs * BF_A_BLK) != cudaSuccess) { cudaGetLastError(); return itb_fail_msg(c, "bf16 tensor path: out of device memory for the tiled weights"); }
+        t.sf = nullptr; t.bytes = rts * kbs * BF_A_BLK;
+        const size_t n = rts * 128 * kbs;
+        k_bf16_tile<128><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.q, w.s, nullptr, w.n_out, w.n_in, t.img);
+        c->launches++;
+        it = c->tc_weights.emplace(w.s, t).first;
+    }
+    size_t cap1 = c->tc_status ? 1 : 0;
+    bool ok = tc_grow(&c->tc_status, &cap1, 1, st) && tc_grow(&c->tc_bf_b, &c->tc_cap_bfb, tts * kbs * BF_B_BLK, st);
+    if (!ok) return itb_fail_msg(c, "bf16 tensor path: out of device memory for the pass");
+    // same_acts: the caller vouches that xq/xs hold what the previous call's did (consecutive matmuls over one quantised row set)
+    if (!same_acts || c->tc_bf_src != xq || c->tc_bf_src_rows != n_rows || c->tc_bf_src_in != w.n_in) {
+        const size_t n = tts * BF_N * kbs;
+        k_bf16_tile<BF_N><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xq, nullptr, xs, n_rows, w.n_in, c->tc_bf_b);
+        c->launches++;
+        c->tc_bf_src = xq; c->tc_bf_src_rows = n_rows; c->tc_bf_src_in = w.n_in;
+    }
+    cudaMemsetAsync(c->tc_status, 0, 4, st);
+    TcBf g{};
+    g.a_img = it->second.img; g.b_img = c->tc_bf_b; g.kbs = (int)kbs; g.n_rows = n_rows; g.n_rt = (int)rts; g.n_tt = (int)tts;
+    g.out = out; g.stride = stride; g.mode = mode; g.status = c->tc_status;
+    static bool attr = false;
+    if (!attr) { cudaFuncSetAttribute(k_tc_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_bf16_smem()); attr = true; }
+    static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
+    const size_t n_blocks = std::min<size_t>((size_t)c->sm_count, rts * tts);
+    if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
+    k_tc_bf16<<<(unsigned)n_blocks, 320, tc_bf16_smem(), st>>>(g);
+    c->launches++;
+    if (prof_on && g.prof) {
+        std::vector<long long> h(n_blocks * 8);
+        cudaStreamSynchronize(st);
+        cudaMemcpy(h.data(), g.prof, n_blocks * 64, cudaMemcpyDeviceToHost);
+        cudaFree(g.prof);
+        double a[5] = {0, 0, 0, 0, 0}, items = 0;
+        for (size_t b = 0; b < n_blocks; ++b) {
+            const long long* q = &h[b * 8];
+            if (!q[0] || !q[5] || !q[6]) continue;
+            a[0] += (double)q[1]; a[1] += (double)q[2]; a[2] += (double)q[3]; a[3] += (double)q[4]; a[4] += (double)(q[5] - q[0]); items += (double)q[6];
+        }
+        if (items > 0) fprintf(stderr, "tc_bf16 %d x %d x %d, items %.0f: cycles per item: MMA thread waiting for operands %.0f, for tensor memory %.0f; stores waiting for accumulators %.0f, "
+                                       "reading + stores %.0f; whole block per item %.0f\n", w.n_out, n_rows, w.n_in, items, a[0] / items, a[1] / items, a[2] / items, a[3] / items, a[4] / items);
+    }
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return itb_fail(c, "bf16 tensor path: launch", e);
     return true;
 }

@@ -155,14 +155,16 @@ def test_prefill_pass_with_fp4_tensor_core_experts_against_the_oracle_with_fp4_a
 
 
 @pytest.mark.parametrize("shape,kv,fast", [("mid", "f16", "attn=mma"), ("m35b", "f16", "attn=mma"), ("m35b", "bf16", "attn=mma"),
-                                           ("m35b", "f16", "gdn=chunk"), ("m35b", "bf16", "attn=mma,gdn=chunk")])
+                                           ("m35b", "f16", "gdn=chunk"), ("m35b", "bf16", "attn=mma,gdn=chunk"),
+                                           ("mid", "f16", "dense=bf16tc"), ("m35b", "f16", "dense=bf16tc")])
 def test_prefill_with_the_many_token_kernels_against_the_oracle(shape, kv, fast):
     """The kernels many-token passes may use in place of the CPU-order ones, each selectable under exact=1 so that it is the
     only difference from the oracle:
       attn=mma   causal attention as 16-bit matrix products over (token, head) tiles with a running softmax (q and the
                  probabilities rounded to the cache's type, sums reassociated);
-      gdn=chunk  the delta rule chunk-parallel (64-token chunks; everything off the state for all chunks at once).
-    Both reassociate sums: tolerance class. A 150-token prompt in one pass (several K/V tiles and chunks, ragged last ones), 70
+      gdn=chunk  the delta rule chunk-parallel (64-token chunks; everything off the state for all chunks at once);
+      dense=bf16tc  the dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands (int8 * scale rounded to bf16).
+    All reassociate sums: tolerance class. A 150-token prompt in one pass (several K/V tiles and chunks, ragged last ones), 70
     more tokens in a second pass (queries deep in the cache, a state carried over), then two teacher-forced single-token steps
     over the cache and state the passes left.
 
