@@ -276,7 +276,8 @@ def tiered_decode(host, ops, dims, seed, frac=0.5, steps=32):
     return out
 
 
-FAST_MODE = "kv=bf16,exact=0,experts=fp4tc,dense=bf16tc"
+FAST_MODE = "kv=bf16,exact=0,experts=fp4tc,dense=f16tc"
+FAST_MODE_Q8 = "kv=bf16,exact=0,experts=fp4tc,dense=q8tc"
 PREFILL_ROWS = 2048
 
 
@@ -340,7 +341,9 @@ def other_configs(host, model, dims, seed, hbm, args, mode):
                                "expert_flop_per_token": flop_tok, "expert_TFLOPs_if_the_whole_pass_were_experts": flop_tok * 5548 / (ms / 1e3) / 1e12,
                                "fp4_peak_TFLOPs_measured": peak,
                                "note": "tolerance class: routed experts as FP4 x FP4 tcgen05 block-scaled GEMMs, causal attention as 16-bit matrix products, "
-                                       "chunk-parallel delta rule, tree-summed F32 dots; dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands"}
+                                       "chunk-parallel delta rule; dense Q8_0 matmuls as f16 tcgen05 GEMMs over dequantised operands (2^-12 per operand), small F32 "
+                                       "matrices as fused-multiply-add tiles. On this random-weight model the dense rounding is past the router's margins: picks flip, "
+                                       "so logits are held to a sanity bound only (tests); prefill_5548_exact_dense keeps the dense results bit-exact"}
         eng = host.Engine(fast_model, N_CTX, 1)
         eng.prefill(prompts(1, seed, n_vocab), want_logits=False)
         first = eng.decode_loop(np.zeros(1, np.uint32), 8)[-1]
@@ -353,6 +356,22 @@ def other_configs(host, model, dims, seed, hbm, args, mode):
         eng.close()
     except Exception as ex:
         out.setdefault("prefill_5548", {"error": str(ex)})
+    finally:
+        if fast_model is not None:
+            fast_model.close()
+        if fast_ops is not None:
+            fast_ops.close()
+    # the same tolerance-class pass with the dense matmuls kept bit-exact (int8 MMAs, scales in CPU order)
+    fast_ops = fast_model = None
+    try:
+        fast_ops = host.B200Ops(0, FAST_MODE_Q8)
+        fast_model = host.Model(fast_ops, host.ModelDims(**dims)); fast_model.synth(configs.SEEDS[args.model])
+        ms = timed_prefill(host, fast_model, n_vocab, seed)
+        out["prefill_5548_exact_dense"] = {"value": 5548 / (ms / 1e3), "unit": "tok/s", "ms": ms, "rows_per_pass": PREFILL_ROWS, "ops": FAST_MODE_Q8,
+                                           "note": "as prefill_5548, but the dense Q8_0 matmuls as tcgen05 int8 MMAs per 32-element block with the scales applied in CPU "
+                                                   "order (bit-identical dense results)"}
+    except Exception as ex:
+        out["prefill_5548_exact_dense"] = {"error": str(ex)}
     finally:
         if fast_model is not None:
             fast_model.close()

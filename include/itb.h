@@ -51,9 +51,9 @@ typedef struct { const float *q, *k, *v, *alpha, *beta, *ssm_a, *dt_bias; size_t
  *   so results equal the CPU path bit for bit; 0: tree-summed F32 dots, split-K attention, and the many-token kernels below),
  * many-token passes (each also selectable on its own under exact=1; all tolerance class except dense=q8tc):
  *   dense=q8tc     dense Q8_0 matmuls as tcgen05 int8 MMAs per 32-element block, scales applied in CPU order (bit-identical),
- *   dense=bf16tc   dense Q8_0 matmuls as bf16 tcgen05 GEMMs: weights and the Q8_0-quantised activation rows dequantised to bf16
+ *   dense=f16tc    dense Q8_0 matmuls as f16 tcgen05 GEMMs: weights and the Q8_0-quantised activation rows dequantised to f16
  *                  (int8 * block scale, rounded to nearest), f32 accumulators; 2 more bytes of device memory per dense weight;
- *                  wins over dense=q8tc where both are given,
+ *                  wins over dense=q8tc where both are given; with exact=0 the small F32 matrices run as fused-multiply-add tiles,
  *   experts=fp4tc  routed experts as FP4 x FP4 block-scaled tcgen05 GEMMs (the reference's default device arithmetic,
  *                  src/ops/cuda/mod.rs:239-248; exact=1 keeps the library-exact SiLU in their epilogue),
  *   attn=mma       causal attention as 16-bit matrix products over (token, head) tiles,

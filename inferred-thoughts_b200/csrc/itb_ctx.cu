@@ -103,7 +103,7 @@ extern "C" int itb_create(int device_ordinal, const char* opts, itb_ctx** out) {
     if (o.find("experts=fp4tc") != std::string::npos) c->fp4tc = true;
     if (o.find("attn=mma") != std::string::npos) c->attn_mma = true;
     if (o.find("dense=q8tc") != std::string::npos) c->q8tc = true;
-    if (o.find("dense=bf16tc") != std::string::npos) c->bf16tc = true;
+    if (o.find("dense=f16tc") != std::string::npos) c->f16tc = true;
     if (o.find("gdn=chunk") != std::string::npos) c->gdn_chunk = true;
     // libm=cr keeps log correctly rounded instead of following the host C library's logf (see itb_internal.cuh)
     const uint32_t* fix = o.find("libm=cr") != std::string::npos ? nullptr : logf_fix_on_device(device_ordinal);

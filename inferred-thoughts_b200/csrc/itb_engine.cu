@@ -1181,7 +1181,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         set_smem((const void*)k_matmul_f32_rows<20>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<24>, 64 * 1024);
         set_smem((const void*)k_matmul_f32_rows<28>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<32>, 64 * 1024);
         set_smem((const void*)k_tile_q8<1, 256, 4>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
-        set_smem((const void*)k_sgemm_serial_small, sgemm_small_smem());
+        set_smem((const void*)k_sgemm_serial_small<false>, sgemm_small_smem()); set_smem((const void*)k_sgemm_serial_small<true>, sgemm_small_smem());
         set_smem((const void*)k_gdn_chunk_prep<128>, gdn_chunk_prep_smem<128>()); set_smem((const void*)k_gdn_chunk_scan<128>, gdn_chunk_scan_smem<128>());
         set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
         set_smem((const void*)k_tile_glu<2, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<2, 256, 1>, 226 * 1024);
@@ -1195,13 +1195,13 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
     cudaStreamCaptureStatus cap_rows = cudaStreamCaptureStatusNone;
     cudaStreamIsCapturing(st, &cap_rows);
     const bool q8tc = c->q8tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
-    const bool bf16tc = c->bf16tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
+    const bool f16tc = c->f16tc && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone;
     // same: this matmul reads the quantised rows the previous one read (their tensor-core images are still current)
     auto gemm_n = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, int R, bool same = false) {
         const int k = w.n_in;
-        if (bf16tc && R >= 64 && itb_tc_bf16_shape_ok(w)) {
-            // many rows, dense=bf16tc (tolerance class): both operands dequantised to bf16, one tcgen05 GEMM with f32 accumulators
-            if (itb_tc_bf16_gemm(c, st, w, xq, xs, R, out, stride, mode, same)) { launches++; return; }
+        if (f16tc && R >= 64 && itb_tc_f16_shape_ok(w)) {
+            // many rows, dense=f16tc (tolerance class): both operands dequantised to f16, one tcgen05 GEMM with f32 accumulators
+            if (itb_tc_f16_gemm(c, st, w, xq, xs, R, out, stride, mode, same)) { launches++; return; }
         }
         if (q8tc && R >= 64 && itb_tc_q8_shape_ok(w)) {
             // many rows, dense=q8tc: integer dots of 128 x 128 (row, token) pairs per tcgen05 MMA, scaled and summed in the CPU's order
@@ -1238,6 +1238,14 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         if (has_s) { const size_t n = (size_t)rows * w.n_out; k_scale<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(out, n, sc); launches++; }
     };
     auto f32mm = [&](const DevF32& w, const float* x, float* out) {
+        if (!c->exact && f16tc && w.n_in % SGS_K == 0 && R >= 64) {
+            // tolerance-class passes: the serial-order tiles with fused multiply-adds (a chain per (row, output), k in order)
+            const int big = ((w.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T);
+            if (big >= sms / 2) k_sgemm_serial<true><<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
+            else k_sgemm_serial_small<true><<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, sgemm_small_smem(), st>>>(w, x, R, out);
+            launches++;
+            return;
+        }
         if (!c->exact && w.n_in % 512 == 0 && w.n_in <= 4096) {
             const dim3 g((w.n_out + 7) / 8, (R + F32_TOK - 1) / F32_TOK);
             const size_t sm = (size_t)F32_TOK * w.n_in * 4;
@@ -1252,8 +1260,8 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         if (c->exact && w.n_in % SGS_K == 0) {
             // a chain per (row, output), a thread per 4 x 4 of them, k in order (also for a few rows: the tile's k loop is as long as a row's chain either way)
             const int big = ((w.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T);
-            if (big >= sms / 2) k_sgemm_serial<<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
-            else k_sgemm_serial_small<<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, sgemm_small_smem(), st>>>(w, x, R, out);
+            if (big >= sms / 2) k_sgemm_serial<false><<<dim3((w.n_out + SG_T - 1) / SG_T, (R + SG_T - 1) / SG_T), 256, 0, st>>>(w, x, R, out);
+            else k_sgemm_serial_small<false><<<dim3((w.n_out + 15) / 16, (R + 15) / 16), 256, sgemm_small_smem(), st>>>(w, x, R, out);
             launches++;
             return;
         }

@@ -95,9 +95,9 @@ struct itb_ctx {
     // Q8_0 tensor path: the pass's activation rows as K32 block images (kept for a following matmul over the same rows)
     uint8_t* tc_q8_b = nullptr; float* tc_q8_sx = nullptr; size_t tc_cap_q8b = 0, tc_cap_q8sx = 0;
     const void* tc_q8_src = nullptr; int tc_q8_src_rows = 0, tc_q8_src_in = 0;
-    uint8_t* tc_bf_b = nullptr; size_t tc_cap_bfb = 0;                 // dense=bf16tc: the pass's activation rows as bf16 operand tiles
-    const void* tc_bf_src = nullptr; int tc_bf_src_rows = 0, tc_bf_src_in = 0;
-    bool bf16tc = false;     // opts dense=bf16tc: many-row passes run the dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands (tolerance class)
+    uint8_t* tc_hf_b = nullptr; size_t tc_cap_hfb = 0;                 // dense=f16tc: the pass's activation rows as f16 operand tiles
+    const void* tc_hf_src = nullptr; int tc_hf_src_rows = 0, tc_hf_src_in = 0;
+    bool f16tc = false;     // opts dense=f16tc: many-row passes run the dense Q8_0 matmuls as f16 tcgen05 GEMMs over dequantised operands (tolerance class)
     bool q8tc = false;       // opts dense=q8tc: many-row passes run the dense Q8_0 matmuls as tcgen05 int8 MMAs (bit-identical results)
     bool fp4tc = false;      // opts experts=fp4tc: many-row passes multiply FP4 activations on the tensor cores
     bool gdn_chunk = false;  // opts gdn=chunk: many-token passes run the delta rule chunk-parallel even under exact=1 (exact=0 always does)
@@ -109,8 +109,8 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
                     const int* pair_list, int n_pairs, float* out);
 bool itb_tc_shape_ok(const DevFp4& w);
 bool itb_tc_q8_shape_ok(const DevQ8& w);
-bool itb_tc_bf16_shape_ok(const DevQ8& w);
-bool itb_tc_bf16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
+bool itb_tc_f16_shape_ok(const DevQ8& w);
+bool itb_tc_f16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
 bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts);
 void itb_tc_free(itb_ctx* c);
 

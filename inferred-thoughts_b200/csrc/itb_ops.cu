@@ -195,6 +195,10 @@ static bool quantize_rows(itb_ctx* c, const float* xd, size_t n_rows, size_t n_i
 
 static void launch_q8(itb_ctx* c, const WeightEntry* w, size_t n_tok, float* od) {
     DevQ8 dw{(const int8_t*)w->a, (const uint16_t*)w->b, (int)w->n_in, (int)w->n_out};
+    if (c->f16tc && n_tok >= 64 && itb_tc_f16_shape_ok(dw) && itb_tc_f16_gemm(c, c->stream, dw, c->xq, c->xs, (int)n_tok, od, w->n_out, 0, false)) {
+        ITB_LAUNCHED(c);      // opts dense=f16tc: many rows as one f16 tensor-core GEMM (tolerance class)
+        return;
+    }
     if (n_tok >= 2 && w->n_in % 32 == 0 && gemm_smem((int)w->n_in) <= 200 * 1024) {
         // several tokens: every weight row is read once per 32 tokens, on the int8 tensor-core path
         size_t sm = gemm_smem((int)w->n_in);

@@ -55,7 +55,10 @@ __global__ void __launch_bounds__(256) k_matmul_f32_rows(DevF32 w, const float* 
 // product and sum rounded separately). With many rows there is a chain per (row, output), so no chain needs to be spread over
 // lanes: a thread owns a 4 x 4 block of outputs and walks k in order -- a plain tiled SGEMM whose k loop is never reassociated
 // or fused. grid (ceil(n_out / 64), ceil(n_rows / 64)), block 256; k tiles of 32 through shared memory, next tile in flight.
+// FUSED (tolerance class, with opts dense=bf16tc): the same walk with one fused multiply-add per step -- half the instructions, and
+// sums that differ from the CPU's by the product's rounding only.
 constexpr int SG_T = 64, SG_K = 32;
+template <bool FUSED = false>
 __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
     __shared__ float ws[2][SG_K][SG_T + 4], xs[2][SG_K][SG_T + 4];      // [k][output] and [k][row]: a thread reads 4 consecutive of each
     const int o0 = blockIdx.x * SG_T, r0 = blockIdx.y * SG_T, n = w.n_in;
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __r
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = __fadd_rn(acc[i][j], __fmul_rn(wq[j], xq[i]));
+                for (int j = 0; j < 4; ++j) acc[i][j] = FUSED ? fmaf(wq[j], xq[i], acc[i][j]) : __fadd_rn(acc[i][j], __fmul_rn(wq[j], xq[i]));
         }
         if (t + 1 < nk) stash(buf ^ 1);
         __syncthreads();
@@ -117,6 +120,7 @@ __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __r
 // sgemm_small_smem(); n_in a multiple of 128.
 constexpr int SGS_K = 128, SGS_ST = SGS_K + 4, SGS_STAGES = 4;
 constexpr size_t sgemm_small_smem() { return (size_t)SGS_STAGES * 2 * 16 * SGS_ST * 4; }
+template <bool FUSED = false>
 __global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
     extern __shared__ __align__(16) unsigned char smem[];
     float* ring = (float*)smem;                    // [stage][w | x][16 lines][SGS_ST]
@@ -145,8 +149,11 @@ __global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w, const floa
 #pragma unroll 8
         for (int kk = 0; kk < SGS_K; kk += 4) {
             const float4 a = *(const float4*)(wr + kk), c = *(const float4*)(xr + kk);
-            acc = __fadd_rn(acc, __fmul_rn(a.x, c.x)); acc = __fadd_rn(acc, __fmul_rn(a.y, c.y));
-            acc = __fadd_rn(acc, __fmul_rn(a.z, c.z)); acc = __fadd_rn(acc, __fmul_rn(a.w, c.w));
+            if (FUSED) { acc = fmaf(a.x, c.x, acc); acc = fmaf(a.y, c.y, acc); acc = fmaf(a.z, c.z, acc); acc = fmaf(a.w, c.w, acc); }
+            else {
+                acc = __fadd_rn(acc, __fmul_rn(a.x, c.x)); acc = __fadd_rn(acc, __fmul_rn(a.y, c.y));
+                acc = __fadd_rn(acc, __fmul_rn(a.z, c.z)); acc = __fadd_rn(acc, __fmul_rn(a.w, c.w));
+            }
         }
     }
     cp_async_wait<0>();

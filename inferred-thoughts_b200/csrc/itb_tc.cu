@@ -540,8 +540,8 @@ bool itb_tc_shape_ok(const DevFp4& w) { return w.n_in % (64 * TC_KS) == 0 && w.n
 void itb_tc_free(itb_ctx* c) {
     for (auto& kv : c->tc_weights) { cudaFree(kv.second.img); cudaFree(kv.second.sf); }
     c->tc_weights.clear();
-    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales); cudaFree(c->tc_q8_b); cudaFree(c->tc_q8_sx); cudaFree(c->tc_bf_b);
-    c->tc_bf_b = nullptr; c->tc_cap_bfb = 0; c->tc_bf_src = nullptr;
+    cudaFree(c->tc_tiles); cudaFree(c->tc_n_tiles); cudaFree(c->tc_slot_tile); cudaFree(c->tc_b_img); cudaFree(c->tc_b_sf); cudaFree(c->tc_status); cudaFree(c->tc_codes); cudaFree(c->tc_scales); cudaFree(c->tc_q8_b); cudaFree(c->tc_q8_sx); cudaFree(c->tc_hf_b);
+    c->tc_hf_b = nullptr; c->tc_cap_hfb = 0; c->tc_hf_src = nullptr;
     c->tc_q8_b = nullptr; c->tc_q8_sx = nullptr; c->tc_cap_q8b = c->tc_cap_q8sx = 0; c->tc_q8_src = nullptr;
     c->tc_tiles = nullptr; c->tc_n_tiles = nullptr; c->tc_slot_tile = nullptr; c->tc_b_img = nullptr; c->tc_b_sf = nullptr; c->tc_status = nullptr; c->tc_codes = nullptr; c->tc_scales = nullptr; c->tc_cap_codes = c->tc_cap_scales = 0;
     c->tc_cap_tiles = c->tc_cap_slots = c->tc_cap_b = c->tc_cap_sf = 0;
@@ -844,10 +844,22 @@ __global__ void __launch_bounds__(320, 1) k_tc_q8(TcQ8 p) {
         if (pf && tid == 0) { pf[0] = clock64() - t_begin; pf[1] = t_wait; pf[2] = t_fetch; pf[3] = kbs; }
         if (ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0) {
             const size_t orow = (size_t)rt * 128 + row;
+            // mode 1 reads what it adds to: all of a batch's reads first, then the stores (a read placed after a store that may
+            // alias it waits for nothing, but the compiler keeps their order, and one read-add-store at a time is a memory round
+            // trip per column)
 #pragma unroll
-            for (int j = 0; j < 64; ++j) {
-                const int tok = tt * 128 + 64 * half + j;
-                if (tok < p.n_rows) { float* o = p.out + (size_t)tok * p.stride + orow; *o = p.mode ? __fadd_rn(*o, acc[j]) : acc[j]; }
+            for (int j0 = 0; j0 < 64; j0 += 16) {
+                float old[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = tt * 128 + 64 * half + j0 + j;
+                    old[j] = (p.mode && tok < p.n_rows) ? p.out[(size_t)tok * p.stride + orow] : 0.0f;
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = tt * 128 + 64 * half + j0 + j;
+                    if (tok < p.n_rows) p.out[(size_t)tok * p.stride + orow] = p.mode ? __fadd_rn(old[j], acc[j0 + j]) : acc[j0 + j];
+                }
             }
         } else if (!ok) atomicCAS(p.status, 0, 5);
     }
@@ -912,38 +924,38 @@ bool itb_tc_q8_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* x
 }
 
 // =====================================================================================================
-// Dense Q8_0 matmuls of many-row passes as bf16 tensor-core GEMMs (tolerance class, opts dense=bf16tc)
+// Dense Q8_0 matmuls of many-row passes as f16 tensor-core GEMMs (tolerance class, opts dense=f16tc)
 // =====================================================================================================
 // Both operands are dequantised once -- the weights when first used, the pass's Q8_0-quantised activation rows (the same
-// quantisation the CPU path applies, src/ops/naive.rs:676-712) once per row set -- to bf16 (value = int8 * block scale, rounded
-// to nearest even: 2^-9 relative per element), laid out as K-major operand tiles, and multiplied by tcgen05.mma kind::f16 with
-// f32 accumulators in tensor memory. What differs from the CPU path: that rounding, and the tensor core's summation order in
+// quantisation the CPU path applies, src/ops/naive.rs:676-712) once per row set -- to f16 (value = int8 * block scale, rounded
+// to nearest even: 2^-12 relative per element; with bf16 operands, 2^-9, a 4-layer model's logits were 0.3 off), laid out as
+// K-major operand tiles, and multiplied by tcgen05.mma kind::f16 with f32 accumulators in tensor memory. What differs from the CPU path: that rounding, and the tensor core's summation order in
 // place of the per-block order. A tile is 128 weight rows x 256 tokens; two accumulator buffers fill the 512 columns of tensor
 // memory, so the MMAs of one tile run while eight warps store the previous one. Persistent blocks, one per SM, token tile
 // fastest: the blocks running at one time share a few weight tiles and all of the pass's activation tiles in L2.
-// Operand images ("K16 block": rows x 16 bf16 = rows x 32 B as [2 chunks of 16 B][rows / 8][8 rows][16 B], no swizzle; descriptor
+// Operand images ("K16 block": rows x 16 f16 = rows x 32 B as [2 chunks of 16 B][rows / 8][8 rows][16 B], no swizzle; descriptor
 // leading offset rows * 16, stride offset 128).
 namespace {
 
-constexpr int BF_KB = 4;                 // K16 blocks per pipeline stage (64 elements)
-constexpr int BF_STAGES = 4;
-constexpr int BF_N = 256;                // tokens per tile
-constexpr int BF_A_BLK = 128 * 32, BF_B_BLK = BF_N * 32;
-constexpr int BF_STAGE_BYTES = BF_KB * (BF_A_BLK + BF_B_BLK);
+constexpr int HF_KB = 4;                 // K16 blocks per pipeline stage (64 elements)
+constexpr int HF_STAGES = 4;
+constexpr int HF_N = 256;                // tokens per tile
+constexpr int HF_A_BLK = 128 * 32, HF_B_BLK = HF_N * 32;
+constexpr int HF_STAGE_BYTES = HF_KB * (HF_A_BLK + HF_B_BLK);
 
-// kind::f16: f32 accumulators (1 at bit 4), bf16 operands (1 at bits 7 and 10), both K-major, M x N
-__host__ __device__ constexpr uint32_t tc_idesc_bf16(int m, int n) { return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
+// kind::f16: f32 accumulators (1 at bit 4), f16 operands (0 at bits 7 and 10), both K-major, M x N
+__host__ __device__ constexpr uint32_t tc_idesc_f16(int m, int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24); }
 
-__device__ __forceinline__ uint32_t bf16x2_rn(float lo, float hi) {
+__device__ __forceinline__ uint32_t f16x2_rn(float lo, float hi) {
     uint32_t r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
-// Q8_0 rows -> bf16 K16 block images of ROWS-row tiles. One thread per (row, K16 block); a warp takes 8 rows x 4 blocks, so it
+// Q8_0 rows -> f16 K16 block images of ROWS-row tiles. One thread per (row, K16 block); a warp takes 8 rows x 4 blocks, so it
 // reads 64 contiguous bytes per row and writes 128 contiguous bytes per block and chunk. Rows past n_rows are zeros.
 // scales16 (f16, per weight row and 32-element block) or scales32 (f32, per activation row and block): whichever is not null.
 template <int ROWS>
-__global__ void k_bf16_tile(const int8_t* q, const uint16_t* scales16, const float* scales32, int n_rows, int n_in, uint8_t* img) {
+__global__ void k_f16_tile(const int8_t* q, const uint16_t* scales16, const float* scales32, int n_rows, int n_in, uint8_t* img) {
     const int kbs = n_in / 16;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x, total = (size_t)((n_rows + ROWS - 1) / ROWS) * ROWS * kbs;
     if (idx >= total) return;
@@ -963,7 +975,7 @@ __global__ void k_bf16_tile(const int8_t* q, const uint16_t* scales16, const flo
         for (int i = 0; i < 4; ++i) {
             const float f0 = (float)(int8_t)(w[i] & 0xff) * sc, f1 = (float)(int8_t)((w[i] >> 8) & 0xff) * sc;
             const float f2 = (float)(int8_t)((w[i] >> 16) & 0xff) * sc, f3 = (float)(int8_t)(w[i] >> 24) * sc;
-            o[2 * i] = bf16x2_rn(f0, f1); o[2 * i + 1] = bf16x2_rn(f2, f3);
+            o[2 * i] = f16x2_rn(f0, f1); o[2 * i + 1] = f16x2_rn(f2, f3);
         }
         lo = make_uint4(o[0], o[1], o[2], o[3]); hi = make_uint4(o[4], o[5], o[6], o[7]);
     }
@@ -972,7 +984,7 @@ __global__ void k_bf16_tile(const int8_t* q, const uint16_t* scales16, const flo
     *(uint4*)(blk + ROWS * 16 + (r >> 3) * 128 + (r & 7) * 16) = hi;
 }
 
-struct TcBf {
+struct TcHf {
     const uint8_t* a_img;                         // weights: [row tile][K16 block][4096 B]
     const uint8_t* b_img;                         // activations of the pass: [token tile][K16 block][8192 B]
     int kbs, n_rows, n_rt, n_tt;                  // K16 blocks, tokens, row tiles, token tiles
@@ -982,16 +994,16 @@ struct TcBf {
 };
 // grid: one block per SM (or per work item, if fewer); block 320: warps 0-7 store accumulators (lane quarter = warp % 4, column half
 // = warp / 4), warp 8 fetches operands, warp 9 issues the MMAs.
-__global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
+__global__ void __launch_bounds__(320, 1) k_tc_f16(TcHf p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ unsigned long long s_full[BF_STAGES], s_empty[BF_STAGES], s_acc[2], s_free[2];
+    __shared__ unsigned long long s_full[HF_STAGES], s_empty[HF_STAGES], s_acc[2], s_free[2];
     __shared__ uint32_t s_tmem;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
-    const int n_work = p.n_rt * p.n_tt, kbs = p.kbs, n_stage = kbs / BF_KB;
+    const int n_work = p.n_rt * p.n_tt, kbs = p.kbs, n_stage = kbs / HF_KB;
     if ((int)blockIdx.x >= n_work) return;
     const uint32_t sbase = tc_smem(smem);
     if (tid == 0) {
-        for (int s = 0; s < BF_STAGES; ++s) {
+        for (int s = 0; s < HF_STAGES; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_empty[s])) : "memory");
         }
@@ -1019,20 +1031,20 @@ __global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
             const size_t a0 = (size_t)(w / p.n_tt) * kbs, b0 = (size_t)(w % p.n_tt) * kbs;
             for (int st = 0; st < n_stage; ++st, ++it) {
-                const int s = it % BF_STAGES;
-                if (it >= BF_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / BF_STAGES) - 1) & 1, limit);
+                const int s = it % HF_STAGES;
+                if (it >= HF_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / HF_STAGES) - 1) & 1, limit);
                 if (!ok) break;
-                const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * BF_STAGE_BYTES;
-                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"((uint32_t)BF_STAGE_BYTES) : "memory");
-                const size_t kb0 = (size_t)st * BF_KB;
-                tc_bulk(dst, p.a_img + (a0 + kb0) * BF_A_BLK, BF_KB * BF_A_BLK, full);
-                tc_bulk(dst + BF_KB * BF_A_BLK, p.b_img + (b0 + kb0) * BF_B_BLK, BF_KB * BF_B_BLK, full);
+                const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * HF_STAGE_BYTES;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"((uint32_t)HF_STAGE_BYTES) : "memory");
+                const size_t kb0 = (size_t)st * HF_KB;
+                tc_bulk(dst, p.a_img + (a0 + kb0) * HF_A_BLK, HF_KB * HF_A_BLK, full);
+                tc_bulk(dst + HF_KB * HF_A_BLK, p.b_img + (b0 + kb0) * HF_B_BLK, HF_KB * HF_B_BLK, full);
             }
         }
         if (!ok) atomicCAS(p.status, 0, 3);
     } else if (wid == 9 && lane == 0) {
-        const uint32_t idesc = tc_idesc_bf16(128, BF_N);
-        const uint64_t dA = tc_desc(sbase, 128 * 16, 128), dB = tc_desc(sbase + BF_KB * BF_A_BLK, BF_N * 16, 128);
+        const uint32_t idesc = tc_idesc_f16(128, HF_N);
+        const uint64_t dA = tc_desc(sbase, 128 * 16, 128), dB = tc_desc(sbase + HF_KB * HF_A_BLK, HF_N * 16, 128);
         int it = 0, item = 0;
         long long t_load = 0, t_free = 0;
         for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++item) {
@@ -1045,19 +1057,19 @@ __global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
             for (int st = 0; st < n_stage; ++st, ++it) {
-                const int s = it % BF_STAGES;
+                const int s = it % HF_STAGES;
                 const long long c0 = pf ? clock64() : 0;
-                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / BF_STAGES) & 1, limit);
+                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / HF_STAGES) & 1, limit);
                 if (pf) t_load += clock64() - c0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t so = (uint32_t)s * (BF_STAGE_BYTES >> 4);
+                const uint32_t so = (uint32_t)s * (HF_STAGE_BYTES >> 4);
 #pragma unroll
-                for (int k = 0; k < BF_KB; ++k) {
+                for (int k = 0; k < HF_KB; ++k) {
                     asm volatile(
                         "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
                         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }\n"
-                        ::"r"(tm + (uint32_t)(BF_N * buf)), "l"(dA + so + (uint32_t)(k * (BF_A_BLK >> 4))), "l"(dB + so + (uint32_t)(k * (BF_B_BLK >> 4))), "r"(idesc),
+                        ::"r"(tm + (uint32_t)(HF_N * buf)), "l"(dA + so + (uint32_t)(k * (HF_A_BLK >> 4))), "l"(dB + so + (uint32_t)(k * (HF_B_BLK >> 4))), "r"(idesc),
                           "r"((st | k) ? 1u : 0u) : "memory");
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_smem(&s_empty[s])) : "memory");
@@ -1082,7 +1094,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
 #pragma unroll 1
             for (int ch = 0; ch < 4; ++ch) {
                 uint32_t d[32];
-                const uint32_t ta = tm + (uint32_t)(BF_N * buf + 128 * half + 32 * ch) + ((uint32_t)(quarter * 32) << 16);
+                const uint32_t ta = tm + (uint32_t)(HF_N * buf + 128 * half + 32 * ch) + ((uint32_t)(quarter * 32) << 16);
                 asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                              : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3]), "=r"(d[4]), "=r"(d[5]), "=r"(d[6]), "=r"(d[7]), "=r"(d[8]), "=r"(d[9]), "=r"(d[10]), "=r"(d[11]),
                                "=r"(d[12]), "=r"(d[13]), "=r"(d[14]), "=r"(d[15]), "=r"(d[16]), "=r"(d[17]), "=r"(d[18]), "=r"(d[19]), "=r"(d[20]), "=r"(d[21]), "=r"(d[22]),
@@ -1094,14 +1106,18 @@ __global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
                     __syncwarp();
                     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_free[buf])) : "memory");
                 }
-                const int tok0 = tt * BF_N + 128 * half + 32 * ch;
+                const int tok0 = tt * HF_N + 128 * half + 32 * ch;
+                // mode 1 reads what it adds to: 16 reads first, then their stores (one read-add-store at a time is a memory round
+                // trip per column: the compiler keeps a read behind the store before it)
 #pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    if (tok0 + j < p.n_rows) {
-                        float* o = ocol + (size_t)(tok0 + j) * p.stride;
-                        const float v = __uint_as_float(d[j]);
-                        *o = p.mode ? *o + v : v;
-                    }
+                for (int j0 = 0; j0 < 32; j0 += 16) {
+                    float old[16];
+                    float* o0 = ocol + (size_t)(tok0 + j0) * p.stride;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) old[j] = (p.mode && tok0 + j0 + j < p.n_rows) ? o0[(size_t)j * p.stride] : 0.0f;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (tok0 + j0 + j < p.n_rows) o0[(size_t)j * p.stride] = old[j] + __uint_as_float(d[j0 + j]);
                 }
             }
             if (pf) { t_wait += k1 - k0; t_work += clock64() - k1; }
@@ -1114,45 +1130,45 @@ __global__ void __launch_bounds__(320, 1) k_tc_bf16(TcBf p) {
     if (wid == 9) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tm) : "memory");
     if (pf && tid == 0) pf[5] = clock64();
 }
-constexpr size_t tc_bf16_smem() { return (size_t)BF_STAGES * BF_STAGE_BYTES + 128; }
+constexpr size_t tc_f16_smem() { return (size_t)HF_STAGES * HF_STAGE_BYTES + 128; }
 
 }  // namespace
 
-bool itb_tc_bf16_shape_ok(const DevQ8& w) { return w.n_in % (16 * BF_KB) == 0 && w.n_out % 128 == 0 && w.q && w.s; }
+bool itb_tc_f16_shape_ok(const DevQ8& w) { return w.n_in % (16 * HF_KB) == 0 && w.n_out % 128 == 0 && w.q && w.s; }
 // out[token][row] (+)= W x for n_rows quantised activation rows (xq int8 [n_rows][n_in], xs f32 [n_rows][n_in / 32]). False: not run.
-bool itb_tc_bf16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts) {
-    if (!itb_tc_bf16_shape_ok(w) || n_rows <= 0) return false;
-    const size_t kbs = w.n_in / 16, rts = w.n_out / 128, tts = ((size_t)n_rows + BF_N - 1) / BF_N;
+bool itb_tc_f16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t* xq, const float* xs, int n_rows, float* out, size_t stride, int mode, bool same_acts) {
+    if (!itb_tc_f16_shape_ok(w) || n_rows <= 0) return false;
+    const size_t kbs = w.n_in / 16, rts = w.n_out / 128, tts = ((size_t)n_rows + HF_N - 1) / HF_N;
     auto it = c->tc_weights.find(w.s);                       // keyed by the scale array: the int8 images of dense=q8tc are keyed by w.q
     if (it == c->tc_weights.end()) {
         itb_ctx::TcWeights t;
-        if (cudaMalloc(&t.img, rts * kbs * BF_A_BLK) != cudaSuccess) { cudaGetLastError(); return itb_fail_msg(c, "bf16 tensor path: out of device memory for the tiled weights"); }
-        t.sf = nullptr; t.bytes = rts * kbs * BF_A_BLK;
+        if (cudaMalloc(&t.img, rts * kbs * HF_A_BLK) != cudaSuccess) { cudaGetLastError(); return itb_fail_msg(c, "f16 tensor path: out of device memory for the tiled weights"); }
+        t.sf = nullptr; t.bytes = rts * kbs * HF_A_BLK;
         const size_t n = rts * 128 * kbs;
-        k_bf16_tile<128><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.q, w.s, nullptr, w.n_out, w.n_in, t.img);
+        k_f16_tile<128><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(w.q, w.s, nullptr, w.n_out, w.n_in, t.img);
         c->launches++;
         it = c->tc_weights.emplace(w.s, t).first;
     }
     size_t cap1 = c->tc_status ? 1 : 0;
-    bool ok = tc_grow(&c->tc_status, &cap1, 1, st) && tc_grow(&c->tc_bf_b, &c->tc_cap_bfb, tts * kbs * BF_B_BLK, st);
-    if (!ok) return itb_fail_msg(c, "bf16 tensor path: out of device memory for the pass");
+    bool ok = tc_grow(&c->tc_status, &cap1, 1, st) && tc_grow(&c->tc_hf_b, &c->tc_cap_hfb, tts * kbs * HF_B_BLK, st);
+    if (!ok) return itb_fail_msg(c, "f16 tensor path: out of device memory for the pass");
     // same_acts: the caller vouches that xq/xs hold what the previous call's did (consecutive matmuls over one quantised row set)
-    if (!same_acts || c->tc_bf_src != xq || c->tc_bf_src_rows != n_rows || c->tc_bf_src_in != w.n_in) {
-        const size_t n = tts * BF_N * kbs;
-        k_bf16_tile<BF_N><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xq, nullptr, xs, n_rows, w.n_in, c->tc_bf_b);
+    if (!same_acts || c->tc_hf_src != xq || c->tc_hf_src_rows != n_rows || c->tc_hf_src_in != w.n_in) {
+        const size_t n = tts * HF_N * kbs;
+        k_f16_tile<HF_N><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(xq, nullptr, xs, n_rows, w.n_in, c->tc_hf_b);
         c->launches++;
-        c->tc_bf_src = xq; c->tc_bf_src_rows = n_rows; c->tc_bf_src_in = w.n_in;
+        c->tc_hf_src = xq; c->tc_hf_src_rows = n_rows; c->tc_hf_src_in = w.n_in;
     }
     cudaMemsetAsync(c->tc_status, 0, 4, st);
-    TcBf g{};
-    g.a_img = it->second.img; g.b_img = c->tc_bf_b; g.kbs = (int)kbs; g.n_rows = n_rows; g.n_rt = (int)rts; g.n_tt = (int)tts;
+    TcHf g{};
+    g.a_img = it->second.img; g.b_img = c->tc_hf_b; g.kbs = (int)kbs; g.n_rows = n_rows; g.n_rt = (int)rts; g.n_tt = (int)tts;
     g.out = out; g.stride = stride; g.mode = mode; g.status = c->tc_status;
     static bool attr = false;
-    if (!attr) { cudaFuncSetAttribute(k_tc_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_bf16_smem()); attr = true; }
+    if (!attr) { cudaFuncSetAttribute(k_tc_f16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tc_f16_smem()); attr = true; }
     static const bool prof_on = getenv("ITB_TC_PROF") != nullptr;
     const size_t n_blocks = std::min<size_t>((size_t)c->sm_count, rts * tts);
     if (prof_on) { cudaMalloc(&g.prof, n_blocks * 64); cudaMemsetAsync(g.prof, 0, n_blocks * 64, st); }
-    k_tc_bf16<<<(unsigned)n_blocks, 320, tc_bf16_smem(), st>>>(g);
+    k_tc_f16<<<(unsigned)n_blocks, 320, tc_f16_smem(), st>>>(g);
     c->launches++;
     if (prof_on && g.prof) {
         std::vector<long long> h(n_blocks * 8);
@@ -1165,10 +1181,10 @@ bool itb_tc_bf16_gemm(itb_ctx* c, cudaStream_t st, const DevQ8& w, const int8_t*
             if (!q[0] || !q[5] || !q[6]) continue;
             a[0] += (double)q[1]; a[1] += (double)q[2]; a[2] += (double)q[3]; a[3] += (double)q[4]; a[4] += (double)(q[5] - q[0]); items += (double)q[6];
         }
-        if (items > 0) fprintf(stderr, "tc_bf16 %d x %d x %d, items %.0f: cycles per item: MMA thread waiting for operands %.0f, for tensor memory %.0f; stores waiting for accumulators %.0f, "
+        if (items > 0) fprintf(stderr, "tc_f16 %d x %d x %d, items %.0f: cycles per item: MMA thread waiting for operands %.0f, for tensor memory %.0f; stores waiting for accumulators %.0f, "
                                        "reading + stores %.0f; whole block per item %.0f\n", w.n_out, n_rows, w.n_in, items, a[0] / items, a[1] / items, a[2] / items, a[3] / items, a[4] / items);
     }
     cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return itb_fail(c, "bf16 tensor path: launch", e);
+    if (e != cudaSuccess) return itb_fail(c, "f16 tensor path: launch", e);
     return true;
 }

@@ -156,14 +156,14 @@ def test_prefill_pass_with_fp4_tensor_core_experts_against_the_oracle_with_fp4_a
 
 @pytest.mark.parametrize("shape,kv,fast", [("mid", "f16", "attn=mma"), ("m35b", "f16", "attn=mma"), ("m35b", "bf16", "attn=mma"),
                                            ("m35b", "f16", "gdn=chunk"), ("m35b", "bf16", "attn=mma,gdn=chunk"),
-                                           ("mid", "f16", "dense=bf16tc"), ("m35b", "f16", "dense=bf16tc")])
+                                           ("mid", "f16", "dense=f16tc"), ("m35b", "f16", "dense=f16tc")])
 def test_prefill_with_the_many_token_kernels_against_the_oracle(shape, kv, fast):
     """The kernels many-token passes may use in place of the CPU-order ones, each selectable under exact=1 so that it is the
     only difference from the oracle:
       attn=mma   causal attention as 16-bit matrix products over (token, head) tiles with a running softmax (q and the
                  probabilities rounded to the cache's type, sums reassociated);
       gdn=chunk  the delta rule chunk-parallel (64-token chunks; everything off the state for all chunks at once);
-      dense=bf16tc  the dense Q8_0 matmuls as bf16 tcgen05 GEMMs over dequantised operands (int8 * scale rounded to bf16).
+      dense=f16tc  the dense Q8_0 matmuls as f16 tcgen05 GEMMs over dequantised operands (int8 * scale rounded to f16).
     All reassociate sums: tolerance class. A 150-token prompt in one pass (several K/V tiles and chunks, ragged last ones), 70
     more tokens in a second pass (queries deep in the cache, a state carried over), then two teacher-forced single-token steps
     over the cache and state the passes left.
@@ -175,7 +175,14 @@ def test_prefill_with_the_many_token_kernels_against_the_oracle(shape, kv, fast)
     150-token pass and moves a logit by 0.03-0.14, and by up to 0.7 two teacher-forced steps later (measured). So the small
     model is held to the north-star bound (max-abs 2e-2, cosine 0.999) and the 35B shape only to a sanity bound (cosine
     0.98, max-abs 1.0: an indexing mistake gives cosine near 0); the 2e-2 bar at that shape is met by the bit-exact kernels
-    only (the other tests of this file)."""
+    only (the other tests of this file).
+
+    dense=f16tc perturbs every dense output by ~3e-4 of the outputs' root mean square (tests/test_gpu_ops.py holds the GEMM itself
+    to that), a thousand times the reassociation level of the other two. On these random-weight models that is past the
+    router's margins: picks of the last prompt token differ from the oracle's in several (layer, pick) places on the small
+    model too (printed below), and a swapped expert moves a logit by tenths -- bf16 operands (eight times the rounding) gave
+    the same 0.35 / cosine 0.973 as f16, i.e. the error is the flipped picks, not the rounding. So this option is held to
+    the sanity bound on both shapes (cosine 0.95, max-abs 1.5) and its precision claim rests on the op-level test."""
     from inferred_thoughts_b200 import host
     dims, seed = (configs.MID, configs.SEEDS["mid"]) if shape == "mid" else SHAPES["m35b"]
     ops = host.B200Ops(0, "exact=1," + fast + (",kv=bf16" if kv == "bf16" else ""))
@@ -187,8 +194,9 @@ def test_prefill_with_the_many_token_kernels_against_the_oracle(shape, kv, fast)
     O.lib().orc_set_threads(max(1, O.lib().orc_hw_threads()))
     prompt = prompt_ids(51, 220, dims["n_vocab"])
     eng = host.Engine(model, 256, 1)
-    om.begin(256, kv_bf16=(kv == "bf16"))
+    om.begin(256, kv_bf16=(kv == "bf16"), log_routes=True)
     bound, cos_min = (2e-2, 0.999) if shape == "mid" else (1.0, 0.98)
+    if "f16tc" in fast: bound, cos_min = 1.5, 0.95
 
     def check(o, g, what):
         err, cos = float(np.abs(o - g).max()), cosine(o, g)
@@ -196,6 +204,9 @@ def test_prefill_with_the_many_token_kernels_against_the_oracle(shape, kv, fast)
         return err
     o = om.forward(prompt[:150]); g = eng.prefill(prompt[:150])
     worst = check(o, g, "first pass")
+    L, K = dims["n_layer"], dims["n_expert_used"]
+    mism = int((eng.read_routes(L, K)[:, 0, :] != om.route_log().reshape(L, 150, K)[:, -1, :]).sum())
+    print(f"{fast} {shape}: routing ids of the last prompt token differing from the oracle's: {mism}/{L * K}")
     o = om.forward(prompt[150:]); g = eng.prefill(prompt[150:])
     worst = max(worst, check(o, g, "second pass"))
     for step in range(2):
