@@ -624,12 +624,14 @@ def run_probe(args):
     if mode != "experts":
         model = host.Model(ops, host.ModelDims(**dims)); model.synth(configs.SEEDS[args.model])
     if mode == "decode":
-        eng = host.Engine(model, 2048, n)
-        eng.prefill(rng.integers(0, dims["n_vocab"], (n, 64)).astype(np.uint32), want_logits=False)
-        t = eng.decode_loop(np.zeros(n, np.uint32), 2)[-1]
+        eng = host.Engine(model, args.probe_ctx, n)
+        eng.prefill(rng.integers(0, dims["n_vocab"], (n, args.probe_prompt)).astype(np.uint32), want_logits=False)
+        t = eng.decode_loop(np.zeros(n, np.uint32), max(2, args.probe_steps))[-1]
         torch.cuda.synchronize(); torch.cuda.profiler.start()
-        eng.decode_loop(t, 1)
+        eng.decode_loop(t, args.probe_steps)
         torch.cuda.synchronize(); torch.cuda.profiler.stop()
+        if args.probe_steps > 1:
+            print(f"per step: {eng.last_ms() / args.probe_steps:.3f} ms", file=sys.stderr)
     elif mode == "prefill":
         eng = host.Engine(model, max(2048, n + 64), 1)
         pr = rng.integers(0, dims["n_vocab"], n).astype(np.uint32)
@@ -749,6 +751,9 @@ def main():
     ap.add_argument("--probe", default="", help="profiler aid, prints no bench line: 'decode:N' one batched decode step of N sequences, 'prefill:N' one pass of "
                     "N prompt rows, 'step:N' one fused one-token step at N positions, each inside a CUDA profiler range (ncu --profile-from-start off); "
                     "'timeline:N' the per-stage timeline of one step at N positions. Use with --layers.")
+    ap.add_argument("--probe-steps", type=int, default=1, help="profiling aid: decode steps inside a 'decode:N' probe's timed region")
+    ap.add_argument("--probe-ctx", type=int, default=2048, help="profiling aid: context length of a 'decode:N' probe's engine")
+    ap.add_argument("--probe-prompt", type=int, default=64, help="profiling aid: prompt tokens per sequence before a 'decode:N' probe's step")
     ap.add_argument("--layers", type=int, default=0, help="profiling aid: the same shape with fewer layers (small device footprint for ncu captures)")
     args = ap.parse_args()
     # Libraries print banners on stdout (NCCL's version line, for one); stdout must carry the JSON line alone, so everything
