@@ -380,7 +380,7 @@ def other_configs(host, model, dims, seed, hbm, args, mode):
     return out
 
 
-def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
+def expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch):
     """The same decode workload with the routed experts sharded over the ranks (each rank: its expert range, the dense
     layers replicated, its own sequences; per MoE layer an all-gather and a reduce-scatter over NCCL). Every rank runs
     this in lockstep; returns the whole-job figure (max time over ranks)."""
@@ -417,9 +417,27 @@ def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
         pe.prefill(pr, want_logits=False)
         pre_ms = pe.last_ms()
         pe.close()
-    t = torch.tensor([dev_ms, e2e_s, pre_ms or 0.0], device="cuda", dtype=torch.float64)
+    # the same comparison at 16 sequences per GPU, where the expert kernels' weight traffic (a rank streams only its shard's
+    # experts, for every rank's rows) starts to pay for the exchange: expert parallel against a full copy per GPU
+    ms16 = [0.0, 0.0]
+    if not args.no_extra:
+        B16, S16 = 16, 16
+
+        def steps16(m, ep):
+            e = host.Engine(m, N_CTX, B16, ep=ep) if ep else host.Engine(m, N_CTX, B16)
+            try:
+                pr = np.stack([np.random.default_rng(seed + 1000 * rank + i).integers(0, dims["n_vocab"], PROMPT).astype(np.uint32) for i in range(B16)])
+                e.prefill(pr, want_logits=False)
+                f = e.decode_loop(np.zeros(B16, np.uint32), S16)[-1]
+                dist.barrier(); torch.cuda.synchronize()
+                e.decode_loop(f, S16)
+                return e.last_ms() / S16
+            finally:
+                e.close()
+        ms16 = [steps16(shard, (rank, world, host.share_unique_id(rank))), steps16(model, None)]
+    t = torch.tensor([dev_ms, e2e_s, pre_ms or 0.0, ms16[0], ms16[1]], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_s, pre_ms = float(t[0]), float(t[1]), float(t[2])
+    ms, e2e_s, pre_ms, ms16 = float(t[0]), float(t[1]), float(t[2]), [float(t[3]), float(t[4])]
     n_moe = dims["n_layer"]
     transport = eng.ep_step_transport()
     out = {"value": world * B * args.steps / (ms / 1e3), "unit": "tok/s", "ms_per_step": ms / args.steps, "batch_per_gpu": B,
@@ -433,6 +451,11 @@ def expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch):
                    ", captured in the step's CUDA graph; many-row passes: packed all-to-all dispatch and combine"}
     if pre_ms:
         out["prefill_2048_per_rank"] = {"value": world * PREFILL_ROWS / (pre_ms / 1e3), "unit": "tok/s", "ms": pre_ms, "dispatch": "packed all-to-all (NCCL send/recv sized by exchanged counts)"}
+    if ms16[0] > 0 and ms16[1] > 0:
+        out["batch16_per_gpu"] = {"expert_parallel": {"value": world * 16 / (ms16[0] / 1e3), "unit": "tok/s", "ms_per_step": ms16[0]},
+                                  "replicas": {"value": world * 16 / (ms16[1] / 1e3), "unit": "tok/s", "ms_per_step": ms16[1]},
+                                  "note": "decode steps of 16 sequences per GPU (512-token prompts), device time, max over ranks; the expert-parallel steps of more than "
+                                          "one sequence per rank use the NCCL all-gather / reduce-scatter form inside the step's CUDA graph"}
     eng.close(); shard.close()
     return out
 
@@ -491,7 +514,7 @@ def run_product(args, rank, world):
     ep = None
     if world > 1 and not args.no_extra and dims["n_expert"] % world == 0:
         try:
-            ep = expert_parallel(host, ops, dims, seed, args, rank, world, dist, torch)
+            ep = expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch)
         except Exception as ex:   # every rank takes the same branch: failures here are set-up failures common to all
             ep = {"error": str(ex)}
     if rank != 0:

@@ -167,7 +167,8 @@ namespace {
 constexpr int TC_M = 128;          // weight rows per tile
 constexpr int TC_NMAX = 128;       // tokens per tile at most
 constexpr int TC_KS = 4;           // K64 blocks per pipeline stage
-constexpr int TC_STAGES = 4;
+constexpr int TC_STAGES = 4;         // pipeline stages of the down form (33 KB each)
+constexpr int TC_STAGES_GLU = 3;     // of the gate+up form (50 KB each): three stages and the 64 KB staging tile fill shared memory
 
 // ---- E2M1 / UE4M3 helpers (src/ops/naive.rs:794-806, src/quant/mod.rs:265-336) ----
 __device__ __forceinline__ float ue4m3_half(uint32_t c) { return ue4m3_half_dev(c & 0x7f); }
@@ -346,9 +347,11 @@ __device__ __forceinline__ void tc_bulk(uint32_t dst, const void* src, uint32_t 
 template <bool GLU, bool EXACT_SILU>
 __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
     extern __shared__ __align__(128) unsigned char smem[];
-    __shared__ unsigned long long s_full[TC_STAGES], s_empty[TC_STAGES], s_acc, s_free;
+    constexpr int NST = GLU ? TC_STAGES_GLU : TC_STAGES;
+    __shared__ unsigned long long s_full[NST], s_empty[NST], s_acc, s_free;
     __shared__ uint32_t s_tmem;
-    __shared__ int s_pair[8][TC_NMAX / 2 + 16];
+    __shared__ int s_pair[TC_NMAX];
+    __shared__ int s_bad;
     const int tid = threadIdx.x, wid = tid >> 5, lane = tid & 31;
     const int n_mt = p.n_out / TC_M, n_work = *p.n_tiles * n_mt;
     if ((int)blockIdx.x >= n_work) return;
@@ -358,8 +361,10 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
     const uint32_t o_au = a_bytes, o_b = a_bytes * (GLU ? 2 : 1), o_sfg = o_b + TC_NMAX * 32 * TC_KS, o_sfu = o_sfg + sf_bytes, o_sfb = o_sfu + (GLU ? sf_bytes : 0);
     const uint32_t stage_bytes = o_sfb + sf_bytes;
     const uint32_t sbase = tc_smem(smem);
+    float* stg = (float*)(smem + (size_t)NST * stage_bytes);      // the epilogue's staging tile: [token column][128 weight rows]
     if (tid == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) {
+        s_bad = 0;
+        for (int s = 0; s < NST; ++s) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_full[s])) : "memory");
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(tc_smem(&s_empty[s])) : "memory");
         }
@@ -393,8 +398,8 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
             const uint32_t b_bytes = (uint32_t)t.npad * 32 * TC_KS;
             const uint32_t total = a_bytes * (GLU ? 2 : 1) + b_bytes + sf_bytes * (GLU ? 3 : 2);
             for (int st = 0; st < n_stage; ++st, ++it) {
-                const int s = it % TC_STAGES;
-                if (it >= TC_STAGES) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / TC_STAGES) - 1) & 1, limit);
+                const int s = it % NST;
+                if (it >= NST) ok = tc_mbar_wait(tc_smem(&s_empty[s]), ((it / NST) - 1) & 1, limit);
                 if (!ok) break;
                 const uint32_t full = tc_smem(&s_full[s]), dst = sbase + s * stage_bytes;
                 asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full), "r"(total) : "memory");
@@ -430,9 +435,9 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             }
             for (int st = 0; st < n_stage; ++st, ++it) {
-                const int s = it % TC_STAGES;
+                const int s = it % NST;
                 const long long c0 = pf ? clock64() : 0;
-                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / TC_STAGES) & 1, limit);
+                ok = tc_mbar_wait(tc_smem(&s_full[s]), (it / NST) & 1, limit);
                 if (pf) t_load += clock64() - c0;
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -459,7 +464,11 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
         if (pf) { pf[1] = t_load; pf[2] = t_free; }
     } else if (wid < 8) {
         // epilogue: lane quarter `wid % 4` of tensor memory = weight rows 32 * (wid % 4) .. of the tile; the tile's token columns are
-        // split between the two warps of a quarter. All of a warp's accumulator reads are issued before the one wait.
+        // split between the two warps of a quarter. All of a warp's accumulator reads are issued before the one wait; the values
+        // (after SiLU * up for the gated form) go to the staging tile, column-major, and from there each warp writes whole
+        // 512-byte pieces of output rows (one 16-byte store per lane) instead of 128-byte pieces per quarter.
+        // The eight warps meet at two named barriers per item; none leaves the loop except after the first of them and on a
+        // verdict all of them read there, so no warp is ever left waiting at a barrier.
         const int quarter = wid & 3, half = wid >> 2;
         int item = 0;
         long long t_wait = 0, t_work = 0, cols = 0;
@@ -468,44 +477,42 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
             const int mt = w % n_mt, el = t.expert - p.expert_lo;
             const int split = ((t.npad / 16 + 1) / 2) * 16;          // npad is a multiple of 16
             const int c0 = half ? split : 0, nchunk = ((half ? t.npad : split) - c0) / 16;      // up to 4 chunks of 16 columns
-            // where each of this warp's columns goes (read before the wait, so the latency hides behind the MMAs)
-            for (int j = lane; j < 16 * nchunk; j += 32) s_pair[wid][j] = c0 + j < t.cnt ? p.pair_list[t.n0 + c0 + j] : -1;
+            // where each column goes (read before the wait, so the latency hides behind the MMAs)
+            if (tid < TC_NMAX) s_pair[tid] = tid < t.cnt ? p.pair_list[t.n0 + tid] : -1;
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
-            __syncwarp();
             const long long k0 = pf ? clock64() : 0;
             ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), item & 1, limit));      // one verdict per warp: the loads below are warp-wide
-            if (!ok || __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) != 0) break;
+            ok = ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0;
             const long long k1 = pf ? clock64() : 0;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = mt * TC_M + quarter * 32 + lane;
-            uint32_t g[64], u[64];
-            const uint32_t ta = ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t g[64], u[64];
+                const uint32_t ta = ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0;
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                if (ch < nchunk) {
-                    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                 : "=r"(g[16 * ch]), "=r"(g[16 * ch + 1]), "=r"(g[16 * ch + 2]), "=r"(g[16 * ch + 3]), "=r"(g[16 * ch + 4]), "=r"(g[16 * ch + 5]),
-                                   "=r"(g[16 * ch + 6]), "=r"(g[16 * ch + 7]), "=r"(g[16 * ch + 8]), "=r"(g[16 * ch + 9]), "=r"(g[16 * ch + 10]), "=r"(g[16 * ch + 11]),
-                                   "=r"(g[16 * ch + 12]), "=r"(g[16 * ch + 13]), "=r"(g[16 * ch + 14]), "=r"(g[16 * ch + 15]) : "r"(d_g + ta + 16u * ch) : "memory");
-                    if (GLU)
+                for (int ch = 0; ch < 4; ++ch) {
+                    if (ch < nchunk) {
                         asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                                     : "=r"(u[16 * ch]), "=r"(u[16 * ch + 1]), "=r"(u[16 * ch + 2]), "=r"(u[16 * ch + 3]), "=r"(u[16 * ch + 4]), "=r"(u[16 * ch + 5]),
-                                       "=r"(u[16 * ch + 6]), "=r"(u[16 * ch + 7]), "=r"(u[16 * ch + 8]), "=r"(u[16 * ch + 9]), "=r"(u[16 * ch + 10]), "=r"(u[16 * ch + 11]),
-                                       "=r"(u[16 * ch + 12]), "=r"(u[16 * ch + 13]), "=r"(u[16 * ch + 14]), "=r"(u[16 * ch + 15]) : "r"(d_u + ta + 16u * ch) : "memory");
+                                     : "=r"(g[16 * ch]), "=r"(g[16 * ch + 1]), "=r"(g[16 * ch + 2]), "=r"(g[16 * ch + 3]), "=r"(g[16 * ch + 4]), "=r"(g[16 * ch + 5]),
+                                       "=r"(g[16 * ch + 6]), "=r"(g[16 * ch + 7]), "=r"(g[16 * ch + 8]), "=r"(g[16 * ch + 9]), "=r"(g[16 * ch + 10]), "=r"(g[16 * ch + 11]),
+                                       "=r"(g[16 * ch + 12]), "=r"(g[16 * ch + 13]), "=r"(g[16 * ch + 14]), "=r"(g[16 * ch + 15]) : "r"(d_g + ta + 16u * ch) : "memory");
+                        if (GLU)
+                            asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                                         : "=r"(u[16 * ch]), "=r"(u[16 * ch + 1]), "=r"(u[16 * ch + 2]), "=r"(u[16 * ch + 3]), "=r"(u[16 * ch + 4]), "=r"(u[16 * ch + 5]),
+                                           "=r"(u[16 * ch + 6]), "=r"(u[16 * ch + 7]), "=r"(u[16 * ch + 8]), "=r"(u[16 * ch + 9]), "=r"(u[16 * ch + 10]), "=r"(u[16 * ch + 11]),
+                                           "=r"(u[16 * ch + 12]), "=r"(u[16 * ch + 13]), "=r"(u[16 * ch + 14]), "=r"(u[16 * ch + 15]) : "r"(d_u + ta + 16u * ch) : "memory");
+                    }
                 }
-            }
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            // the accumulators are in registers: tensor memory goes back to the MMA warp for the next item
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_free)) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                // the accumulators are in registers: tensor memory goes back to the MMA warp for the next item
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc_smem(&s_free)) : "memory");
+                float* srow = stg + (size_t)c0 * TC_M + quarter * 32 + lane;
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                if (ch < nchunk) {
+                for (int ch = 0; ch < 4; ++ch) {
+                    if (ch < nchunk) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int pair = s_pair[wid][16 * ch + j];
-                        if (pair >= 0) {
+                        for (int j = 0; j < 16; ++j) {
                             float v = __uint_as_float(g[16 * ch + j]);
                             if (p.s2g) v = v * sg;
                             if (GLU) {
@@ -514,12 +521,19 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
                                 float x = __uint_as_float(u[16 * ch + j]); if (p.s2u) x = x * su;
                                 v = (EXACT_SILU ? silu_f(v) : __fdividef(v, 1.0f + __expf(-v))) * x;
                             }
-                            p.out[(size_t)pair * p.out_stride + row] = v;
+                            srow[(16 * ch + j) * TC_M] = v;
                         }
                     }
                 }
+            } else s_bad = 1;
+            asm volatile("bar.sync 1, 256;" ::: "memory");        // the tile is staged (or some warp gave up: every warp reads that here)
+            if (s_bad) break;
+            const size_t obase = (size_t)mt * TC_M + lane * 4;
+            for (int col = wid; col < t.npad; col += 8) {
+                const int pair = s_pair[col];
+                if (pair >= 0) *(float4*)(p.out + (size_t)pair * p.out_stride + obase) = *(const float4*)(stg + (size_t)col * TC_M + lane * 4);
             }
-            __syncwarp();                                     // s_pair[wid] is rewritten for the next item
+            asm volatile("bar.sync 1, 256;" ::: "memory");        // the staging tile and the pair list are free for the next item
             if (pf) { t_wait += k1 - k0; t_work += clock64() - k1; cols += t.npad; }
         }
         if (pf && tid == 0) { pf[3] = t_wait; pf[4] = t_work; pf[6] = item; pf[7] = cols; }
@@ -531,7 +545,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
 }
 inline size_t tc_gemm_smem(bool glu) {
     const size_t a = TC_KS * 4096, b = (size_t)TC_NMAX * 32 * TC_KS, sf = TC_KS * 512;
-    return TC_STAGES * (a * (glu ? 2 : 1) + b + sf * (glu ? 3 : 2)) + 128;
+    return (glu ? TC_STAGES_GLU : TC_STAGES) * (a * (glu ? 2 : 1) + b + sf * (glu ? 3 : 2)) + (size_t)TC_NMAX * TC_M * 4 + 128;
 }
 
 }  // namespace
