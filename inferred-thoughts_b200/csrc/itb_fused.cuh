@@ -72,12 +72,16 @@ __global__ void __launch_bounds__(NWG * 32) k_in_proj(InProj p) {
             asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         }
     }
+    // Q8_0 rows go to the blocks without a unit when those are most of the grid: the folding warp then has its scheduler to
+    // itself from the start (its fold is the longest thing in the kernel, and four warps to a scheduler slow its chain)
+    const bool spare_units = p.f32_ring > 0 && 2 * p.f32_ring <= (int)gridDim.x;
+    const int gq = spare_units ? (int)gridDim.x - p.f32_ring : (int)gridDim.x;
     const int nwq = unit_block ? nw - 2 : nw;                     // warps that take Q8_0 rows
     // this warp's share of the concatenated Q8_0 rows
     int total = 0;
     for (int m = 0; m < p.nq; ++m) total += p.q[m].n_out;
-    int b0, b1, r0, r1;
-    share(total, gridDim.x, blockIdx.x, b0, b1);
+    int b0 = 0, b1 = 0, r0, r1;
+    if ((int)blockIdx.x < gq) share(total, gq, blockIdx.x, b0, b1);
     share(b1 - b0, nwq, min(wid, nwq - 1), r0, r1);
     r0 += b0; r1 += b0;
     if (wid >= nwq) r1 = r0;
@@ -311,7 +315,8 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
         if (lane == 0) red2[wid] = acc;
         __syncthreads();
         double tot = 0.0;
-        for (int w = 0; w < 8; ++w) tot += red2[w];
+        if (lane == 0) for (int w = 0; w < 8; ++w) tot += red2[w];      // one lane per warp adds (slow f64 unit), the rest get it by shuffle
+        tot = __shfl_sync(0xffffffffu, tot, 0);
         float mean = (float)(tot / (double)sv);
         float sc = 1.0f / sqrtf(mean + p.eps);
         if (tid < sv) {   // whole warps: sv is a multiple of 32
@@ -369,7 +374,8 @@ __global__ void k_attn_prep(AttnPrep p) {
         if ((d & 31) == 0) red[d >> 5] = acc;
         __syncthreads();
         double tot = 0.0;
-        for (int w = 0; w < hd / 32; ++w) tot += red[w];
+        if ((d & 31) == 0) for (int w = 0; w < hd / 32; ++w) tot += red[w];      // one lane per warp adds (slow f64 unit), the rest get it by shuffle
+        tot = __shfl_sync(0xffffffffu, tot, 0);
         float mean = (float)(tot / (double)hd);
         float sc = 1.0f / sqrtf(mean + p.eps);
         v = v * sc * (is_q ? p.q_norm : p.k_norm)[d];

@@ -45,8 +45,11 @@ __device__ __forceinline__ bool block_rms_norm(const float* __restrict__ x, cons
         acc = warp_sum_d(acc);
         if ((threadIdx.x & 31) == 0) red[wid] = acc;
         __syncthreads();
+        // the warps' partial sums in warp order, by one lane per warp (the f64 unit is slow: every thread adding all of them
+        // was most of this prologue), handed to the others by shuffle
         double tot = 0.0;
-        for (int i = 0; i < nw; ++i) tot += red[i];
+        if ((threadIdx.x & 31) == 0) for (int i = 0; i < nw; ++i) tot += red[i];
+        tot = __shfl_sync(0xffffffffu, tot, 0);
         const float mean = (float)(tot / (double)n);
         const float sc = 1.0f / sqrtf(mean + eps);
 #pragma unroll
@@ -78,7 +81,8 @@ __device__ __forceinline__ bool block_rms_norm(const float* __restrict__ x, cons
     if ((threadIdx.x & 31) == 0) red[wid] = acc;
     __syncthreads();
     double tot = 0.0;
-    for (int i = 0; i < nw; ++i) tot += red[i];
+    if ((threadIdx.x & 31) == 0) for (int i = 0; i < nw; ++i) tot += red[i];
+    tot = __shfl_sync(0xffffffffu, tot, 0);
     float mean = (float)(tot / (double)n);
     float sc = 1.0f / sqrtf(mean + eps);
     for (int i = threadIdx.x; i < n; i += blockDim.x) xn[i] = xn[i] * sc * w[i];
