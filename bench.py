@@ -419,7 +419,7 @@ def expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch
         pe.close()
     # the same comparison at 16 sequences per GPU, where the expert kernels' weight traffic (a rank streams only its shard's
     # experts, for every rank's rows) starts to pay for the exchange: expert parallel against a full copy per GPU
-    ms16 = [0.0, 0.0]
+    ms16, tr16 = [0.0, 0.0], []
     if not args.no_extra:
         B16, S16 = 16, 16
 
@@ -431,6 +431,8 @@ def expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch
                 f = e.decode_loop(np.zeros(B16, np.uint32), S16)[-1]
                 dist.barrier(); torch.cuda.synchronize()
                 e.decode_loop(f, S16)
+                if ep:
+                    tr16.append(e.ep_step_transport())
                 return e.last_ms() / S16
             finally:
                 e.close()
@@ -454,8 +456,10 @@ def expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch
     if ms16[0] > 0 and ms16[1] > 0:
         out["batch16_per_gpu"] = {"expert_parallel": {"value": world * 16 / (ms16[0] / 1e3), "unit": "tok/s", "ms_per_step": ms16[0]},
                                   "replicas": {"value": world * 16 / (ms16[1] / 1e3), "unit": "tok/s", "ms_per_step": ms16[1]},
-                                  "note": "decode steps of 16 sequences per GPU (512-token prompts), device time, max over ranks; the expert-parallel steps of more than "
-                                          "one sequence per rank use the NCCL all-gather / reduce-scatter form inside the step's CUDA graph"}
+                                  "step_transport": tr16[0] if tr16 else None,
+                                  "note": "decode steps of 16 sequences per GPU (512-token prompts), device time, max over ranks; peer-memory: every rank's rows and "
+                                          "routing ids stored into every rank's memory, each served pair's output row stored into its owner's memory, flags with "
+                                          "bounded waits (own kernels inside the step's CUDA graph); nccl: all-gather + zero-filled exact-sum reduce-scatter"}
     eng.close(); shard.close()
     return out
 

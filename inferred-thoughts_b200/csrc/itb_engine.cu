@@ -466,6 +466,7 @@ struct EpState {
     // scales, router logits), the output rows of this rank's picks that the serving ranks store here, and one flag per
     // (layer, peer) for each direction; peers' regions are opened through CUDA IPC
     bool p2p = false;
+    bool p2p_rows = false;                   // the same for the steps of an engine with several sequences (rows form, see ep_p2p_setup)
     unsigned char* region = nullptr; size_t region_bytes = 0;
     unsigned char* peer[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // peer[rank] = region
     unsigned char** peer_dev = nullptr;      // the same table on the device
@@ -556,6 +557,39 @@ __global__ void __launch_bounds__(256) k_ep_finish(float* x, int n, const float*
     for (int k = 0; k < n_used; ++k) v += wts[k] * __ldcg(o + (size_t)k * n + i);
     v += shared[i] * g;
     x[i] += v;
+}
+
+// ---- the same for steps of several sequences per rank (the multi-row kernels) ----
+// This rank's rows of layer il -- quantised activations, scales, routing ids -- stored into every rank's region, then that
+// rank's flag for (layer, this rank). A block per destination rank.
+__global__ void __launch_bounds__(256) k_ep_push_rows(const int8_t* xq, const float* xs, const int32_t* ids, int n_xq16, int n_xs16, int n_ids,
+                                                      unsigned char* const* peer, size_t off_xq, size_t off_xs, size_t off_ids, size_t off_flag, const unsigned* seq) {
+    unsigned char* base = peer[blockIdx.x];
+    for (int i = threadIdx.x; i < n_xq16; i += blockDim.x) ((uint4*)(base + off_xq))[i] = ((const uint4*)xq)[i];
+    for (int i = threadIdx.x; i < n_xs16; i += blockDim.x) ((uint4*)(base + off_xs))[i] = ((const uint4*)xs)[i];
+    for (int i = threadIdx.x; i < n_ids; i += blockDim.x) ((int32_t*)(base + off_ids))[i] = ids[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* flag = (unsigned*)(base + off_flag);
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(seq[0]) : "memory");
+    }
+}
+// Every rank's flag of one layer and direction has reached this step's number (bounded waits; *err set if one runs out).
+// One warp; the kernels after it read what the peers stored.
+__global__ void k_ep_wait(const unsigned* flags, int world, const unsigned* seq, int* err) {
+    if ((int)threadIdx.x < world) ep_wait_flag(flags + threadIdx.x, seq[0], err);
+}
+// The output rows of the pairs this rank served (the pairs of all ranks' rows that name one of its experts), each stored
+// into its OWNER's region at the pair's place; rows of pairs served elsewhere are never read. A block per pair.
+__global__ void __launch_bounds__(256) k_ep_scatter_rows(const float* o_all, const int32_t* gids, int pairs_per_rank, int e_per, int rank, int H,
+                                                         unsigned char* const* peer, size_t off_o) {
+    const int pr = blockIdx.x;
+    if (gids[pr] / e_per != rank) return;
+    const int src = pr / pairs_per_rank, j = pr % pairs_per_rank;
+    float4* dst = (float4*)(peer[src] + off_o) + (size_t)j * (H / 4);
+    const float4* from = (const float4*)(o_all + (size_t)pr * H);
+    for (int i = threadIdx.x; i < H / 4; i += blockDim.x) dst[i] = from[i];
 }
 
 // Expert tiering: the routed experts live in pinned host memory (itb_model_offload_experts); `capacity` (layer, expert)
@@ -1119,11 +1153,15 @@ static void ep_p2p_setup(itb_engine* e) {
     NcclApi& nc = nccl_api();
     const itb_model_dims& d = e->m->d;
     const int W = q->world;
-    if (e->B != 1 || W > 8 || d.n_embd % 128 || d.n_expert % 4 || (getenv("ITB_EP_P2P") && atoi(getenv("ITB_EP_P2P")) == 0)) return;
-    const size_t H = d.n_embd, E = d.n_expert, K = d.n_expert_used, NL = d.n_layer;
+    if (e->B > 64 || W > 8 || d.n_embd % 128 || d.n_expert % 4 || d.n_expert % W || (getenv("ITB_EP_P2P") && atoi(getenv("ITB_EP_P2P")) == 0)) return;
+    const size_t H = d.n_embd, E = d.n_expert, K = d.n_expert_used, NL = d.n_layer, RB = e->B;
+    // one sequence: the fused one-token kernels (they gather the router logits and route every rank's row themselves);
+    // several: the multi-row kernels (each rank routes its own rows and the ids travel)
+    const bool rows = RB != 1;
     q->g_slot = 0;
-    q->g_layer = ((size_t)W * (H + H / 32 * 4 + E * 4) + 127) & ~(size_t)127;      // per layer: [W][H] int8 | [W][H/32] f32 | [W][E] f32
-    q->o_layer = K * H * 4;
+    q->g_layer = rows ? (((size_t)W * RB * (H + H / 32 * 4 + K * 4) + 127) & ~(size_t)127)      // per layer: [W][RB][H] int8 | [W][RB][H/32] f32 | [W][RB][K] i32
+                      : (((size_t)W * (H + H / 32 * 4 + E * 4) + 127) & ~(size_t)127);          // per layer: [W][H] int8 | [W][H/32] f32 | [W][E] f32
+    q->o_layer = RB * K * H * 4;
     q->off_g = 0; q->off_o = q->off_g + NL * q->g_layer; q->off_gf = q->off_o + NL * q->o_layer; q->off_of = q->off_gf + NL * 8 * 4;
     q->region_bytes = q->off_of + NL * 8 * 4;
     bool ok = cudaMalloc(&q->region, q->region_bytes) == cudaSuccess && cudaMalloc(&q->seq, 4) == cudaSuccess && cudaMalloc(&q->peer_dev, 8 * sizeof(void*)) == cudaSuccess;
@@ -1158,7 +1196,7 @@ static void ep_p2p_setup(itb_engine* e) {
     cudaFree(hbuf); cudaFree(flags_dev);
     if (ok) {
         cudaMemcpy(q->peer_dev, q->peer, 8 * sizeof(void*), cudaMemcpyHostToDevice);
-        q->p2p = true;
+        if (rows) q->p2p_rows = true; else q->p2p = true;
     } else {
         for (int r = 0; r < W; ++r) if (r != q->rank && q->peer[r]) { cudaIpcCloseMemHandle(q->peer[r]); q->peer[r] = nullptr; }
         cudaFree(q->region); cudaFree(q->seq); cudaFree(q->peer_dev); q->region = nullptr; q->seq = nullptr; q->peer_dev = nullptr;
@@ -1273,6 +1311,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         launches++;
     };
     const size_t smem_nq = 256 + (size_t)H * 4;
+    if (e->ep && e->ep->p2p_rows && n_tok == 1 && R == (int)e->B) { k_ep_tick<<<1, 32, 0, st>>>(e->ep->seq); launches++; }    // the step number the peers' flags will carry
     k_embed<<<R, 256, 0, st>>>(m->tok_embd.w, H, tok_rows, e->x); launches++;
     for (uint32_t il = 0; il < d.n_layer; ++il) {
         const DevLayer& L = m->layers[il];
@@ -1379,6 +1418,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             int P = W * R * K, Kt = K;                  // pairs the expert kernels see; pairs per activation row among them
             const int8_t* xq_src = e->xq; const float* xs_src = e->xs; const int32_t* ids_src = ids;
             const bool a2a = e->ep && n_tok > 1 && cap_rows == cudaStreamCaptureStatusNone && e->ep->a2a_cap >= (size_t)e->ep->world * e->R * K;
+            const bool p2r = e->ep && e->ep->p2p_rows && n_tok == 1 && R == (int)e->B;
             std::vector<int> a2a_soff, a2a_roff;
             if (a2a) {
                 // eager many-row pass: packed all-to-all. Every (row, pick) pair goes to the rank that holds its expert -- its
@@ -1418,6 +1458,17 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 nc.GroupEnd();
                 launches += 5;
                 xq_src = q->rxq; xs_src = q->rxs; ids_src = q->rids; P = n_recv; Kt = 1;
+            } else if (p2r) {
+                // a step of several sequences over peer memory: this rank's rows and routing ids stored into every rank's region,
+                // then wait (bounded) until every rank's have arrived here. No collective call, nothing zero-filled.
+                EpState* q = e->ep;
+                const size_t base = q->off_g + (size_t)il * q->g_layer, o_xq = base, o_xs = o_xq + (size_t)W * R * H, o_id = o_xs + (size_t)W * R * (H / 32) * 4;
+                k_ep_push_rows<<<W, 256, 0, st>>>(e->xq, e->xs, ids, R * H / 16, R * (H / 32) / 4, R * K, (unsigned char* const*)q->peer_dev,
+                                                  o_xq + (size_t)q->rank * R * H, o_xs + (size_t)q->rank * R * (H / 32) * 4, o_id + (size_t)q->rank * R * K * 4,
+                                                  q->off_gf + ((size_t)il * 8 + q->rank) * 4, (const unsigned*)q->seq);
+                k_ep_wait<<<1, 32, 0, st>>>((const unsigned*)(q->region + q->off_gf + (size_t)il * 8 * 4), W, (const unsigned*)q->seq, e->err);
+                launches += 2;
+                xq_src = (const int8_t*)(q->region + o_xq); xs_src = (const float*)(q->region + o_xs); ids_src = (const int32_t*)(q->region + o_id);
             } else if (e->ep) {
                 NcclApi& nc = nccl_api();
                 nc.GroupStart();
@@ -1487,6 +1538,15 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 k_ep_unsort<<<(unsigned)(((size_t)R * K * (H / 4) + 255) / 256), 256, 0, st>>>(q->o_back, q->own_list, R * K, H, q->o_mine);
                 launches += 2;
                 o_src = q->o_mine;
+            } else if (p2r) {
+                // every served pair's output row straight into its owner's region, every rank told, and this rank's rows complete
+                // once every rank has told it (bounded wait)
+                EpState* q = e->ep;
+                k_ep_scatter_rows<<<P, 256, 0, st>>>(e->o_all, ids_src, R * K, E / W, q->rank, H, (unsigned char* const*)q->peer_dev, q->off_o + (size_t)il * q->o_layer);
+                k_ep_signal<<<W, 32, 0, st>>>((unsigned char* const*)q->peer_dev, q->off_of + ((size_t)il * 8 + q->rank) * 4, (const unsigned*)q->seq);
+                k_ep_wait<<<1, 32, 0, st>>>((const unsigned*)(q->region + q->off_of + (size_t)il * 8 * 4), W, (const unsigned*)q->seq, e->err);
+                launches += 3;
+                o_src = (const float*)(q->region + q->off_o + (size_t)il * q->o_layer);
             } else if (e->ep) {
                 nccl_api().ReduceScatter(e->o_all, e->ep->o_mine, (size_t)R * K * H, NcclApi::Float32, NcclApi::Sum, e->ep->comm, st);
                 launches++;
@@ -1707,7 +1767,7 @@ extern "C" int itb_engine_create_ep(itb_model* m, uint32_t n_ctx, uint32_t n_seq
     return 0;
 }
 
-extern "C" int itb_engine_ep_transport(itb_engine* e) { return !e->ep ? 0 : e->ep->p2p ? 2 : 1; }
+extern "C" int itb_engine_ep_transport(itb_engine* e) { return !e->ep ? 0 : (e->ep->p2p || e->ep->p2p_rows) ? 2 : 1; }
 
 static void drop_graph(itb_engine* e) {
     if (e->exec) cudaGraphExecDestroy(e->exec);
@@ -1971,7 +2031,7 @@ static bool ensure_graph(itb_engine* e) {
 // The one-kernel step's waits are bounded: a wait that ran out stores (stage << 8) | reason in the status word and every
 // block returns. Turn it into the sticky error and put the grid barrier's counters back.
 static bool check_flag(itb_engine* e) {
-    if (e->mega != 1 && !e->c->exact && !(e->ep && e->ep->p2p)) return true;
+    if (e->mega != 1 && !e->c->exact && !(e->ep && (e->ep->p2p || e->ep->p2p_rows))) return true;
     int f = 0;
     if (cudaMemcpy(&f, e->err, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return itb_fail_msg(e->c, "engine: cannot read the device status word");
     if (f == EP_WAIT_FAIL) {

@@ -230,6 +230,7 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
     float* kq = S + sv * (sk + 1);           // k[sk] | q[sk]
     float* o = kq + 2 * sk;                  // [sv]
     __shared__ double red2[8];
+    __shared__ float s_gb[2];
     const int key_dim = p.n_k * sk;
     const float* cv = p.conv + (size_t)b * p.conv_stride;
     float* sg = p.state + (size_t)b * p.state_stride + (size_t)h * sv * sk;
@@ -270,14 +271,19 @@ __global__ void __launch_bounds__(256) k_gdn_core(GdnCore p) {
             float v = src[i] * sc;
             src[i] = wid == 0 ? v : v * qs;
         }
-    }
-    __syncthreads();
-    TL(TLK_GDN_CORE, 3);
-    if (tid < sv) {
+    } else if (wid == 2) {
+        // the head's decay and write strength, once (three library-exact exponentials and a logarithm: on the f64 unit they were
+        // half of the update phase when each of its four warps computed them for itself)
         float a = r_alpha + r_dt;
         float sp = a > 20.0f ? a : log_f(1.0f + exp_f(a));
         float g = exp_f(sp * r_a);
         float bt = sigmoid_f(r_beta);
+        if (lane == 0) { s_gb[0] = g; s_gb[1] = bt; }
+    }
+    __syncthreads();
+    TL(TLK_GDN_CORE, 3);
+    if (tid < sv) {
+        const float g = s_gb[0], bt = s_gb[1];
         // the thread's state row lives in registers for both passes (src/ops/naive.rs:109-132 order: decay, predict, update, read out)
         float* row = S + tid * (sk + 1);
         float R[SK];

@@ -31,13 +31,13 @@ def main():
     shard = host.Model(ops, host.ModelDims(**dims)); shard.synth(seed, lo, hi)
     ok = True
     rng = np.random.default_rng(100 + rank)                 # every rank its own sequences
-    for n_seq in (3, 1):                                     # 3: the multi-row passes; 1: the fused one-token step around the collectives
+    for n_seq in (3, 1):                                     # 3: the multi-row passes and steps; 1: the fused one-token step
         prompts = rng.integers(0, dims["n_vocab"], (n_seq, 40)).astype(np.uint32)
         e1 = host.Engine(full, 128, n_seq)
         e2 = host.Engine(shard, 128, n_seq, ep=(rank, world, host.share_unique_id(rank)))
-        if n_seq == 1:
-            want = "nccl" if os.environ.get("ITB_EP_P2P") == "0" else "peer-memory"
-            ok = ok and e2.ep_step_transport() == want
+        # steps of one sequence (fused one-token kernels) and of several (multi-row kernels) both exchange through peer memory
+        want = "nccl" if os.environ.get("ITB_EP_P2P") == "0" else "peer-memory"
+        ok = ok and e2.ep_step_transport() == want
         a, b = e1.prefill(prompts), e2.prefill(prompts)
         a, b = np.atleast_2d(a), np.atleast_2d(b)
         ok = ok and a.view(np.uint32).tolist() == b.view(np.uint32).tolist()
