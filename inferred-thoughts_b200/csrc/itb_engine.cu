@@ -1310,6 +1310,19 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         else k_matmul_f32<false><<<g, nw * 32, sm, st>>>(w, x, out);
         launches++;
     };
+    // two F32 matrices over the same rows: one launch where both take the small serial-order tiles, else one after the other
+    auto f32mm2 = [&](const DevF32& wa, float* oa, const DevF32& wb, float* ob, const float* x) {
+        const bool fused = !c->exact && f16tc && R >= 64;
+        const int big_a = ((wa.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T), big_b = ((wb.n_out + SG_T - 1) / SG_T) * ((R + SG_T - 1) / SG_T);
+        if ((c->exact || fused) && wa.n_in == wb.n_in && wa.n_in % SGS_K == 0 && big_a < sms / 2 && big_b < sms / 2) {
+            const dim3 g((std::max(wa.n_out, wb.n_out) + 15) / 16, (R + 15) / 16, 2);
+            if (fused) k_sgemm_serial_small<true><<<g, 256, sgemm_small_smem(), st>>>(wa, x, R, oa, wb, ob);
+            else k_sgemm_serial_small<false><<<g, 256, sgemm_small_smem(), st>>>(wa, x, R, oa, wb, ob);
+            launches++;
+            return;
+        }
+        f32mm(wa, x, oa); f32mm(wb, x, ob);
+    };
     const size_t smem_nq = 256 + (size_t)H * 4;
     if (e->ep && e->ep->p2p_rows && n_tok == 1 && R == (int)e->B) { k_ep_tick<<<1, 32, 0, st>>>(e->ep->seq); launches++; }    // the step number the peers' flags will carry
     k_embed<<<R, 256, 0, st>>>(m->tok_embd.w, H, tok_rows, e->x); launches++;
@@ -1321,8 +1334,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             const size_t state_stride = (size_t)n_v * sk * sk, conv_stride = (size_t)cd * (d.ssm_d_conv - 1);
             gemm(L.wqkv, e->xq, e->xs, e->qkvc, cd, 0);
             gemm(L.wgate, e->xq, e->xs, e->z, vd, 0, true);
-            f32mm(L.ssm_alpha, e->xn, e->alpha);
-            f32mm(L.ssm_beta, e->xn, e->beta);
+            f32mm2(L.ssm_alpha, e->alpha, L.ssm_beta, e->beta, e->xn);
             float* cst = e->conv_state + (size_t)rs * e->B * conv_stride;
             k_conv_rows<<<dim3((cd + 127) / 128, R), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
             k_conv_state<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(cst, conv_stride, e->qkvc, n_tok, cd, d.ssm_d_conv); launches++;
@@ -1406,8 +1418,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         else gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
         if (L.shared4[1].nib) gemm_fp4d(L.shared4[1], e->xq, e->xs, e->su, R, L.has_shared_s[1], L.shared_s[1]);
         else gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, !L.shared4[0].nib);
-        f32mm(L.gate_inp, e->xn, e->router);
-        f32mm(L.shared_gate_inp, e->xn, e->shlogit);
+        f32mm2(L.gate_inp, e->router, L.shared_gate_inp, e->shlogit, e->xn);
         {
             const int K = d.n_expert_used, E = d.n_expert, ff = d.expert_ff;
             int32_t* ids = e->route_ids + (size_t)il * e->R * K;

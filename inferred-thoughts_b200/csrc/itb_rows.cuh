@@ -120,10 +120,15 @@ __global__ void __launch_bounds__(256) k_sgemm_serial(DevF32 w, const float* __r
 // sgemm_small_smem(); n_in a multiple of 128.
 constexpr int SGS_K = 128, SGS_ST = SGS_K + 4, SGS_STAGES = 4;
 constexpr size_t sgemm_small_smem() { return (size_t)SGS_STAGES * 2 * 16 * SGS_ST * 4; }
+// Two matrices over the same rows in one launch (blockIdx.z picks; w1.w null: one matrix): the router and the shared expert's
+// gate, or alpha and beta -- each alone is a handful of blocks walking a 2,048-long chain, and one after the other they cost twice.
 template <bool FUSED = false>
-__global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w, const float* __restrict__ x, int n_rows, float* out) {
+__global__ void __launch_bounds__(256) k_sgemm_serial_small(DevF32 w0, const float* __restrict__ x, int n_rows, float* out0, DevF32 w1 = DevF32{}, float* out1 = nullptr) {
     extern __shared__ __align__(16) unsigned char smem[];
     float* ring = (float*)smem;                    // [stage][w | x][16 lines][SGS_ST]
+    const DevF32 w = blockIdx.z ? w1 : w0;
+    float* out = blockIdx.z ? out1 : out0;
+    if ((int)blockIdx.x * 16 >= w.n_out) return;
     const int o0 = blockIdx.x * 16, r0 = blockIdx.y * 16, n = w.n_in, nk = n / SGS_K;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;            // output o0 + tx, row r0 + ty
     auto fetch = [&](int t) {
