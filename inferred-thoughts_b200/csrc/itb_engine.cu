@@ -1219,6 +1219,7 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         set_smem((const void*)k_matmul_f32_rows<20>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<24>, 64 * 1024);
         set_smem((const void*)k_matmul_f32_rows<28>, 64 * 1024); set_smem((const void*)k_matmul_f32_rows<32>, 64 * 1024);
         set_smem((const void*)k_tile_q8<1, 256, 4>, 226 * 1024); set_smem((const void*)k_tile_q8<4, 256, 2>, 226 * 1024);
+        set_smem((const void*)k_tile_q8_multi<1, 256, 4>, 226 * 1024);
         set_smem((const void*)k_sgemm_serial_small<false>, sgemm_small_smem()); set_smem((const void*)k_sgemm_serial_small<true>, sgemm_small_smem());
         set_smem((const void*)k_gdn_chunk_prep<128>, gdn_chunk_prep_smem<128>()); set_smem((const void*)k_gdn_chunk_scan<128>, gdn_chunk_scan_smem<128>());
         set_smem((const void*)k_tile_glu<1, 256, 1>, 226 * 1024); set_smem((const void*)k_tile_down<1, 256, 1>, 226 * 1024);
@@ -1257,6 +1258,23 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         launches++;
     };
     auto gemm = [&](const DevQ8& w, const int8_t* xq, const float* xs, float* out, size_t stride, int mode, bool same = false) { gemm_n(w, xq, xs, out, stride, mode, R, same); };
+    // two or three dense matrices over the same quantised rows (mode 0): with few rows (batched decode) one launch for all of
+    // them; otherwise one after the other, the later ones told that the rows' tensor-core images are current
+    auto gemm_multi = [&](int n, const DevQ8* const* w, float* const* out, const size_t* stride, const int8_t* xq, const float* xs) {
+        bool one = R <= 32 && n <= 3;
+        for (int i = 0; i < n; ++i) one = one && w[i]->q && w[i]->n_in == w[0]->n_in && w[i]->n_in % 256 == 0;
+        if (one) {
+            Q8Multi p{};
+            p.n = n;
+            int tiles = 0;
+            for (int i = 0; i < n; ++i) { p.w[i] = *w[i]; p.out[i] = out[i]; p.stride[i] = stride[i]; p.tiles[i] = (w[i]->n_out + 31) / 32; tiles += p.tiles[i]; }
+            const int k = w[0]->n_in, ns = std::min(k / 256, TILE_STAGES);
+            k_tile_q8_multi<1, 256, 4><<<dim3(tiles, (R + 31) / 32), 256, tile_smem<MK_Q8, 1, 256, 4>(k), st>>>(p, xq, xs, R, ns);
+            launches++;
+            return;
+        }
+        for (int i = 0; i < n; ++i) gemm(*w[i], xq, xs, out[i], stride[i], 0, i > 0);
+    };
     // A dense matrix stored as NVFP4 (shared experts, LM head of an NVFP4 file): int8 activations x E2M1 weights in the CPU
     // order (src/ops/naive.rs:714-734), then the tensor's second scale on the result (src/model/qwen35.rs:1668-1682).
     auto gemm_fp4d = [&](const DevFp4& w, const int8_t* xq, const float* xs, float* out, int rows, bool has_s, float sc) {
@@ -1332,8 +1350,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         if (L.recurrent) {
             const int rs = e->slot_of[il];
             const size_t state_stride = (size_t)n_v * sk * sk, conv_stride = (size_t)cd * (d.ssm_d_conv - 1);
-            gemm(L.wqkv, e->xq, e->xs, e->qkvc, cd, 0);
-            gemm(L.wgate, e->xq, e->xs, e->z, vd, 0, true);
+            {
+                const DevQ8* ws[2] = {&L.wqkv, &L.wgate}; float* os[2] = {e->qkvc, e->z}; const size_t ss[2] = {(size_t)cd, (size_t)vd};
+                gemm_multi(2, ws, os, ss, e->xq, e->xs);
+            }
             f32mm2(L.ssm_alpha, e->alpha, L.ssm_beta, e->beta, e->xn);
             float* cst = e->conv_state + (size_t)rs * e->B * conv_stride;
             k_conv_rows<<<dim3((cd + 127) / 128, R), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
@@ -1358,9 +1378,10 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             gemm(L.ssm_out, e->aq, e->as, e->x, H, 1);
         } else {
             const int as = e->slot_of[il];
-            gemm(L.wq, e->xq, e->xs, e->qg, 2 * qd, 0);
-            gemm(L.wk, e->xq, e->xs, e->kbuf, kvd, 0, true);
-            gemm(L.wv, e->xq, e->xs, e->vbuf, kvd, 0, true);
+            {
+                const DevQ8* ws[3] = {&L.wq, &L.wk, &L.wv}; float* os[3] = {e->qg, e->kbuf, e->vbuf}; const size_t ss[3] = {(size_t)2 * qd, (size_t)kvd, (size_t)kvd};
+                gemm_multi(3, ws, os, ss, e->xq, e->xs);
+            }
             AttnPrepRows a{};
             a.qg = e->qg; a.k = e->kbuf; a.v = e->vbuf; a.q_norm = L.q_norm; a.k_norm = L.k_norm; a.q_out = e->qn; a.g_out = e->gate;
             a.slab_stride = (size_t)e->n_ctx * kvd;
@@ -1414,10 +1435,15 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
         }
         // routed FFN
         k_norm_quant<<<R, 256, smem_nq, st>>>(e->x, L.ffn_norm, H, d.rms_eps, e->xn, e->xq, e->xs); launches++;
-        if (L.shared4[0].nib) gemm_fp4d(L.shared4[0], e->xq, e->xs, e->sg, R, L.has_shared_s[0], L.shared_s[0]);
-        else gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
-        if (L.shared4[1].nib) gemm_fp4d(L.shared4[1], e->xq, e->xs, e->su, R, L.has_shared_s[1], L.shared_s[1]);
-        else gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, !L.shared4[0].nib);
+        if (!L.shared4[0].nib && !L.shared4[1].nib) {
+            const DevQ8* ws[2] = {&L.shared_gate, &L.shared_up}; float* os[2] = {e->sg, e->su}; const size_t ss[2] = {(size_t)d.shared_ff, (size_t)d.shared_ff};
+            gemm_multi(2, ws, os, ss, e->xq, e->xs);
+        } else {
+            if (L.shared4[0].nib) gemm_fp4d(L.shared4[0], e->xq, e->xs, e->sg, R, L.has_shared_s[0], L.shared_s[0]);
+            else gemm(L.shared_gate, e->xq, e->xs, e->sg, d.shared_ff, 0);
+            if (L.shared4[1].nib) gemm_fp4d(L.shared4[1], e->xq, e->xs, e->su, R, L.has_shared_s[1], L.shared_s[1]);
+            else gemm(L.shared_up, e->xq, e->xs, e->su, d.shared_ff, 0, !L.shared4[0].nib);
+        }
         f32mm2(L.gate_inp, e->router, L.shared_gate_inp, e->shlogit, e->xn);
         {
             const int K = d.n_expert_used, E = d.n_expert, ff = d.expert_ff;

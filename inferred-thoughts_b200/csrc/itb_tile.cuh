@@ -180,6 +180,29 @@ __global__ void __launch_bounds__(256) k_tile_q8(DevQ8 w, const int8_t* xq, cons
     });
 }
 
+// Up to three dense Q8_0 matrices over the same quantised rows in one launch (the input projections of a layer; the shared
+// expert's gate and up): grid.x runs over the matrices' row tiles one after the other. A matrix of 512 rows alone is 16 blocks.
+struct Q8Multi { DevQ8 w[3]; float* out[3]; size_t stride[3]; int tiles[3]; int n; };
+template <int NJ, int KC, int TH>
+__global__ void __launch_bounds__(256) k_tile_q8_multi(Q8Multi p, const int8_t* xq, const float* xs, int n_tok, int n_stage) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    using C = TileCfg<MK_Q8, NJ, KC, TH>;
+    int* tok_idx = (int*)smem;
+    int m = 0, bx = blockIdx.x;
+    while (m + 1 < p.n && bx >= p.tiles[m]) { bx -= p.tiles[m]; ++m; }
+    const DevQ8 w = p.w[m];
+    float* out = p.out[m];
+    const size_t out_stride = p.stride[m];
+    const int t0 = blockIdx.y * C::TOK, r0 = bx * C::ROWS;
+    if ((int)threadIdx.x < C::TOK) { const int ti = t0 + (int)threadIdx.x; tok_idx[threadIdx.x] = ti < n_tok ? ti : -1; }
+    __syncthreads();
+    float acc[NJ][4];
+    tile_gemm<MK_Q8, NJ, KC, TH>((const uint8_t*)w.q, (const uint8_t*)w.s, w.n_in, w.n_out, r0, xq, xs, tok_idx, smem + 256, n_stage, acc);
+    tile_foreach<NJ, TH>(acc, r0, w.n_out, [&](int t, int row, float v) {
+        if (t0 + t < n_tok) out[(size_t)(t0 + t) * out_stride + row] = v;
+    });
+}
+
 // Gate and up of one expert for the pairs routed to it, SiLU-gated (src/ops/mod.rs:1105-1117):
 // h[pair][row] = silu(gate.x * s_gate) * (up.x * s_up). grid (n_expert, ceil(ff/ROWS)); pair p reads activation row p / n_used.
 template <int NJ, int KC, int TH>
