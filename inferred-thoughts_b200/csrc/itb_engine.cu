@@ -1356,7 +1356,9 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
             }
             f32mm2(L.ssm_alpha, e->alpha, L.ssm_beta, e->beta, e->xn);
             float* cst = e->conv_state + (size_t)rs * e->B * conv_stride;
-            k_conv_rows<<<dim3((cd + 127) / 128, R), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d, d.ssm_d_conv); launches++;
+            if (d.ssm_d_conv == 4 && n_tok >= CONV_T) k_conv_rows4<<<dim3((cd + 127) / 128, n_seq * ((n_tok + CONV_T - 1) / CONV_T)), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d);
+            else k_conv_rows<<<dim3((cd + 127) / 128, R), 128, 0, st>>>(cst, conv_stride, e->qkvc, e->qkvc2, n_tok, cd, L.conv1d, d.ssm_d_conv);
+            launches++;
             k_conv_state<<<dim3((cd + 127) / 128, n_seq), 128, 0, st>>>(cst, conv_stride, e->qkvc, n_tok, cd, d.ssm_d_conv); launches++;
             k_gdn_pre<<<dim3(R, 2 * n_k + n_v), sk, 0, st>>>(e->qkvc2, cd, e->alpha, e->beta, L.ssm_a, L.dt_bias, sk, n_k, n_v, d.rms_eps,
                                                             e->qh, e->kh, e->vh, e->gb); launches++;

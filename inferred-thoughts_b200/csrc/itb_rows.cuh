@@ -203,6 +203,33 @@ __global__ void k_conv_rows(const float* state, size_t state_stride, const float
     sum += x[r * nc + c] * w[(size_t)c * kernel + keep];
     out[r * nc + c] = sum;
 }
+// The same for a kernel of 4 taps, CONV_T consecutive tokens of one sequence per thread: the three earlier inputs slide along
+// in registers and the channel's taps are read once, so an output costs one load and one store instead of eight loads. The sums
+// are the same expressions in the same order. grid (ceil(nc/128), n_seq * ceil(n_tok / CONV_T)).
+constexpr int CONV_T = 8;
+__global__ void __launch_bounds__(128) k_conv_rows4(const float* state, size_t state_stride, const float* __restrict__ x, float* __restrict__ out, int n_tok, int nc, const float* __restrict__ w) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= nc) return;
+    const int chunks = (n_tok + CONV_T - 1) / CONV_T, s = blockIdx.y / chunks, t0 = (blockIdx.y % chunks) * CONV_T;
+    const float4 wv = *(const float4*)(w + (size_t)c * 4);
+    const float* st = state + (size_t)s * state_stride + (size_t)c * 3;
+    const float* xs = x + (size_t)s * n_tok * nc + c;
+    float p0 = t0 >= 3 ? xs[(size_t)(t0 - 3) * nc] : st[t0], p1 = t0 >= 2 ? xs[(size_t)(t0 - 2) * nc] : st[t0 + 1], p2 = t0 >= 1 ? xs[(size_t)(t0 - 1) * nc] : st[t0 + 2];
+    float cur[CONV_T];
+#pragma unroll
+    for (int i = 0; i < CONV_T; ++i) cur[i] = t0 + i < n_tok ? xs[(size_t)(t0 + i) * nc] : 0.0f;
+#pragma unroll
+    for (int i = 0; i < CONV_T; ++i) {
+        if (t0 + i >= n_tok) break;
+        float sum = 0.0f;
+        sum += p0 * wv.x;
+        sum += p1 * wv.y;
+        sum += p2 * wv.z;
+        sum += cur[i] * wv.w;
+        out[((size_t)s * n_tok + t0 + i) * nc + c] = sum;
+        p0 = p1; p1 = p2; p2 = cur[i];
+    }
+}
 // The window each sequence leaves behind: its last kernel-1 inputs, oldest first. grid (ceil(nc/128), n_seq).
 __global__ void k_conv_state(float* state, size_t state_stride, const float* x, int n_tok, int nc, int kernel) {
     const int c = blockIdx.x * blockDim.x + threadIdx.x, s = blockIdx.y;

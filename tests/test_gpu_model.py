@@ -505,3 +505,17 @@ def test_seam_ops_drive_a_whole_layer_like_the_reference_model_does(oracle, gpu)
     so = om.ssm_state(0)
     assert np.abs(ssm_state - so).max() <= 1e-5 * max(1.0, float(np.abs(so).max()))
     ops.forget_state()
+
+
+def test_l2_hints_leave_the_step_bit_identical():
+    """ITB_L2_HINT=1: every kernel of the one-token step asks for what the kernels after it will stream to be brought into L2
+    (`cp.async.bulk.prefetch.L2`). Hints move no results: the smoke run (prefill against the oracle, routing ids, 8 greedy
+    tokens) must pass unchanged with them on. A child process, because the library reads the variable once per process."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, ITB_L2_HINT="1")
+    p = subprocess.run([sys.executable, "-c", "import __graft_entry__ as g; g.smoke()"], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "smoke ok" in p.stdout, p.stdout[-2000:] + p.stderr[-2000:]
