@@ -436,7 +436,10 @@ def expert_parallel(host, ops, model, dims, seed, args, rank, world, dist, torch
                 return e.last_ms() / S16
             finally:
                 e.close()
-        ms16 = [steps16(shard, (rank, world, host.share_unique_id(rank))), steps16(model, None)]
+        try:      # a failure here is a set-up failure common to all ranks (the ranks agree before anything is enqueued): keep the figures above
+            ms16 = [steps16(shard, (rank, world, host.share_unique_id(rank))), steps16(model, None)]
+        except Exception:
+            ms16 = [0.0, 0.0]
     t = torch.tensor([dev_ms, e2e_s, pre_ms or 0.0, ms16[0], ms16[1]], device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_s, pre_ms, ms16 = float(t[0]), float(t[1]), float(t[2]), [float(t[3]), float(t[4])]

@@ -20,9 +20,23 @@ def _stale():
 
 
 def build(force=False, verbose=False):
-    """Compile every CUDA source for sm_100a and link libitb.so next to this file."""
+    """Compile every CUDA source for sm_100a and link libitb.so next to this file. Safe when several processes call it at once
+    (the ranks of a multi-GPU run importing the package with a stale library): one of them builds under a file lock, the others
+    wait and find the library fresh; the link goes to a temporary name and is moved into place, so a reader never maps half a file."""
     if not force and not _stale():
         return SO
+    import fcntl
+    with open(PKG / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not _stale():      # another process built it while this one waited
+                return SO
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose):
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objs = []
     procs = []
@@ -39,7 +53,9 @@ def build(force=False, verbose=False):
     for p, cmd in procs:
         if p.wait() != 0:
             raise RuntimeError("nvcc failed: " + " ".join(cmd))
-    subprocess.check_call([nvcc, "-shared", "-o", str(SO), *objs, "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+    tmp = PKG / f".libitb.{os.getpid()}.tmp"
+    subprocess.check_call([nvcc, "-shared", "-o", str(tmp), *objs, "-lcudart_static", "-lpthread", "-ldl", "-lrt"])
+    os.replace(tmp, SO)
     return SO
 
 

@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
         // (after SiLU * up for the gated form) go to the staging tile, column-major, and from there each warp writes whole
         // 512-byte pieces of output rows (one 16-byte store per lane) instead of 128-byte pieces per quarter.
         // The eight warps meet at two named barriers per item; none leaves the loop except after the first of them and on a
-        // verdict all of them read there, so no warp is ever left waiting at a barrier.
+        // decision all of them read there, so no warp is ever left waiting at a barrier.
         const int quarter = wid & 3, half = wid >> 2;
         int item = 0;
         long long t_wait = 0, t_work = 0, cols = 0;
@@ -481,7 +481,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
             if (tid < TC_NMAX) s_pair[tid] = tid < t.cnt ? p.pair_list[t.n0 + tid] : -1;
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
             const long long k0 = pf ? clock64() : 0;
-            ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), item & 1, limit));      // one verdict per warp: the loads below are warp-wide
+            ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), item & 1, limit));      // one answer per warp: the loads below are warp-wide
             ok = ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0;
             const long long k1 = pf ? clock64() : 0;
             if (ok) {
