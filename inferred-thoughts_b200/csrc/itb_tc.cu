@@ -482,6 +482,7 @@ __global__ void __launch_bounds__(320, 1) k_tc_gemm(TcGemm p) {
             const float sg = p.s2g ? p.s2g[el] : 1.0f, su = (GLU && p.s2u) ? p.s2u[el] : 1.0f;
             const long long k0 = pf ? clock64() : 0;
             ok = __all_sync(0xffffffffu, tc_mbar_wait(tc_smem(&s_acc), item & 1, limit));      // one answer per warp: the loads below are warp-wide
+            if (!ok && lane == 0) atomicCAS(p.status, 0, 5);                                    // the accumulators never came
             ok = ok && __shfl_sync(0xffffffffu, *(volatile int*)p.status, 0) == 0;
             const long long k1 = pf ? clock64() : 0;
             if (ok) {
@@ -646,7 +647,7 @@ bool itb_tc_experts(itb_ctx* c, cudaStream_t st, const DevFp4& wg, const DevFp4*
     if (e != cudaSuccess) return itb_fail(c, "FP4 tensor path: launch", e);
     return true;
 }
-// The status word of the last pass: 0 fine; 3 / 4: a (bounded) wait of the producer / the MMA warp ran out.
+// The status word of the last pass: 0 fine; 3 / 4 / 5: a (bounded) wait of the producer / the MMA warp / an epilogue warp ran out.
 int itb_tc_status(itb_ctx* c, cudaStream_t st) {
     int v = 0;
     if (!c->tc_status) return 0;
