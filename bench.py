@@ -47,7 +47,7 @@ def peaks():
 
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled every 50 ms while the timed region runs (20 steps are about 60 ms)."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device):
@@ -62,6 +62,8 @@ class ClockSampler:
     def stop(self):
         if self.p is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        import datetime
+        t_stop = datetime.datetime.now()
         time.sleep(0.25)
         self.p.terminate(); self.p.wait()
         self.f.flush(); self.f.seek(0)
@@ -70,6 +72,12 @@ class ClockSampler:
             c = [x.strip() for x in line.split(",")]
             if len(c) < 9:
                 continue
+            try:
+                # samples taken after the timed region ended (the GPU idling while this sampler is shut down) do not count
+                if datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f") > t_stop and sm:
+                    continue
+            except ValueError:
+                pass
             try:
                 sm.append(float(c[1])); mx.append(float(c[2]))
             except ValueError:
