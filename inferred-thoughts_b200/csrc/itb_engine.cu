@@ -1547,7 +1547,9 @@ static uint64_t enqueue_rows(itb_engine* e, cudaStream_t st, int n_seq, int n_to
                 // rows per expert decide the tile shape (a tile's empty token columns cost as much as full ones)
                 const bool tile_w = H % 256 == 0 && ff % 256 == 0;
                 // up to 32 rows per expert: 128 weight rows x 8*NJ tokens per block (every weight decoded by one warp); more: 64 x 64
-                const int per_e = (P + E - 1) / E, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
+                // (an expert-parallel rank serves all the pairs it sees with its own E / W experts)
+                const int e_here = e->ep ? std::max(1, E / W) : E;
+                const int per_e = (P + e_here - 1) / e_here, nj = per_e <= 8 ? 1 : per_e <= 16 ? 2 : per_e <= 32 ? 4 : 0;
                 const int ns_g = std::min(H / 256, TILE_STAGES), ns_d = std::min(ff / 256, TILE_STAGES);
 #define GLU_TILE(NJ, TH) k_tile_glu<NJ, 256, TH><<<dim3(E, (ff + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(H), st>>>(Lg, Lu, xq_src, xs_src, Kt, e->pair_off, e->pair_list, e->h_all, ns_g)
 #define DOWN_TILE(NJ, TH) k_tile_down<NJ, 256, TH><<<dim3(E, (H + 128 / TH - 1) / (128 / TH)), 256, tile_smem<MK_FP4, NJ, 256, TH>(ff), st>>>(Ld, e->hq, e->hs, e->pair_off, e->pair_list, e->o_all, ns_d)
