@@ -6,8 +6,9 @@ A step is one decode step (one token for each of B sequences) after a 512-token 
 capacity of 8192 (BASELINE.json config 3). Prints ONE JSON line: device-timed throughput (`value`), the same
 through the C ABI with host buffers (`e2e`), the roofline of the dominant kernel measured live with CUDA
 events, the CPU oracle timed on the host cores beside it, clocks sampled during the timed region.
-With N > 1 (torchrun) every rank decodes its own sequences on its own full copy of the model: the path
-shards by sequence with no data-path collective, and the whole-job value is the sum.
+With N > 1 (torchrun) the headline is expert parallelism: the routed experts sharded over the ranks, dense layers
+replicated, every rank its own sequences, rows exchanged through peer memory (`expert_parallel`); the figure with a full
+copy of the model per rank and no exchange at all stays beside it (`replicas`), and both again at 16 sequences per GPU.
 """
 import argparse
 import ctypes as C
